@@ -1,0 +1,60 @@
+.section .rodata
+.balign 16
+hc_img_name_0: .asciz "copy2d"
+.balign 16
+hc_img_begin_0: .incbin "/root/repo/hc_b200/_native/copy2d.cubin"
+hc_img_end_0:
+.balign 16
+hc_img_name_1: .asciz "softmax_rows"
+.balign 16
+hc_img_begin_1: .incbin "/root/repo/hc_b200/_native/softmax_rows.cubin"
+hc_img_end_1:
+.balign 16
+hc_img_name_2: .asciz "reduce_rows"
+.balign 16
+hc_img_begin_2: .incbin "/root/repo/hc_b200/_native/reduce_rows.cubin"
+hc_img_end_2:
+.balign 16
+hc_img_name_3: .asciz "gemm_tiled"
+.balign 16
+hc_img_begin_3: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
+hc_img_end_3:
+.balign 16
+hc_img_name_4: .asciz "gemm_bf16_umma"
+.balign 16
+hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
+hc_img_end_4:
+.balign 16
+hc_img_name_5: .asciz "dequant_w8"
+.balign 16
+hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_end_5:
+.balign 16
+.section .data.rel.ro,"aw"
+.globl hc_b200_images
+.balign 8
+hc_b200_images:
+  .quad hc_img_name_0
+  .quad hc_img_begin_0
+  .quad hc_img_end_0
+  .quad hc_img_name_1
+  .quad hc_img_begin_1
+  .quad hc_img_end_1
+  .quad hc_img_name_2
+  .quad hc_img_begin_2
+  .quad hc_img_end_2
+  .quad hc_img_name_3
+  .quad hc_img_begin_3
+  .quad hc_img_end_3
+  .quad hc_img_name_4
+  .quad hc_img_begin_4
+  .quad hc_img_end_4
+  .quad hc_img_name_5
+  .quad hc_img_begin_5
+  .quad hc_img_end_5
+.section .rodata
+.globl hc_b200_image_count
+.balign 4
+hc_b200_image_count:
+  .long 6
+.section .note.GNU-stack,"",@progbits

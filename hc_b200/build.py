@@ -1,0 +1,193 @@
+"""In-tree build of the native parts of hc_b200.
+
+Produces, under ``hc_b200/_native/``:
+
+* one sm_100a cubin per ``csrc/kernels/*.cu`` (``nvcc -cubin``),
+* ``libhc-cuda-runtime.so``        - the ol* ABI over the CUDA driver API,
+* ``libhc-gpu-runtime-loader.so``  - the backend-agnostic ol* shim,
+* ``libhc-b200-kernels.so``        - the cubins (embedded) + workload launchers,
+* ``libhc-python-runtime.so``      - the hcgpu* ABI (needs Python headers),
+* ``_dispatcher.so``               - the pybind11 entry used by ``hckernel``.
+
+The library names and the split follow the reference's CMake targets
+(gpu-runtime/cuda-runtime/CMakeLists.txt, gpu-runtime/loader/CMakeLists.txt,
+python/cpp/py-runtime/CMakeLists.txt).  Nothing here needs a GPU: nvcc
+cross-compiles.  Run as ``python -m hc_b200.build`` or call :func:`build_all`.
+"""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+OUT = ROOT / "_native"
+INCLUDE = ROOT.parent / "include"
+
+KERNEL_SOURCES = [
+    "copy2d",
+    "softmax_rows",
+    "reduce_rows",
+    "gemm_tiled",
+    "gemm_bf16_umma",
+    "dequant_w8",
+]
+
+NVCC_FLAGS = [
+    "-gencode",
+    "arch=compute_100a,code=sm_100a",
+    "-lineinfo",
+    "-O3",
+    "-std=c++17",
+]
+CXX_FLAGS = [
+    "-std=c++20",
+    "-O2",
+    "-fPIC",
+    "-shared",
+    "-fvisibility=hidden",
+    "-Wall",
+    "-Wl,-Bsymbolic",
+    "-Wl,--exclude-libs,ALL",
+    "-Wl,-rpath,$ORIGIN",
+]
+
+
+def _cuda_home() -> Path:
+    for cand in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if cand and (Path(cand) / "bin" / "nvcc").exists():
+            return Path(cand)
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        return Path(nvcc).resolve().parent.parent
+    raise RuntimeError("nvcc not found: set CUDA_HOME")
+
+
+def _stale(target: Path, sources) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in sources)
+
+
+def _run(cmd, verbose):
+    cmd = [str(c) for c in cmd]
+    if verbose:
+        print("+", " ".join(cmd), flush=True)
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(
+            "build step failed:\n  " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr
+        )
+    if verbose and (proc.stdout or proc.stderr):
+        print(proc.stdout + proc.stderr, flush=True)
+
+
+def build_cubins(verbose=False, force=False):
+    """Compile every kernel source to an sm_100a cubin."""
+    cuda = _cuda_home()
+    OUT.mkdir(exist_ok=True)
+    headers = list((CSRC / "kernels").glob("*.cuh"))
+    outs = []
+    for name in KERNEL_SOURCES:
+        src = CSRC / "kernels" / f"{name}.cu"
+        out = OUT / f"{name}.cubin"
+        if force or _stale(out, [src, *headers]):
+            _run([cuda / "bin" / "nvcc", *NVCC_FLAGS, "-cubin", "-o", out, src], verbose)
+        outs.append(out)
+    return outs
+
+
+def _write_images_asm(cubins, path: Path):
+    """Assembly that embeds each cubin and a name/begin/end table."""
+    lines = ['.section .rodata', '.balign 16']
+    for i, c in enumerate(cubins):
+        lines += [
+            f"hc_img_name_{i}: .asciz \"{c.stem}\"",
+            ".balign 16",
+            f"hc_img_begin_{i}: .incbin \"{c}\"",
+            f"hc_img_end_{i}:",
+            ".balign 16",
+        ]
+    # The table holds addresses, so it lives in a relocatable read-only section.
+    lines += ['.section .data.rel.ro,"aw"', ".globl hc_b200_images", ".balign 8",
+              "hc_b200_images:"]
+    for i in range(len(cubins)):
+        lines += [f"  .quad hc_img_name_{i}", f"  .quad hc_img_begin_{i}", f"  .quad hc_img_end_{i}"]
+    lines += [
+        ".section .rodata",
+        ".globl hc_b200_image_count",
+        ".balign 4",
+        "hc_b200_image_count:",
+        f"  .long {len(cubins)}",
+        '.section .note.GNU-stack,"",@progbits',
+    ]
+    path.write_text("\n".join(lines) + "\n")
+
+
+def build_libs(verbose=False, force=False):
+    cuda = _cuda_home()
+    cxx = os.environ.get("CXX", "g++")
+    inc = ["-I", INCLUDE, "-I", cuda / "include"]
+    cubins = build_cubins(verbose, force)
+
+    backend = OUT / "libhc-cuda-runtime.so"
+    srcs = [CSRC / "runtime" / "cuda_runtime.cpp", CSRC / "runtime" / "driver_api.hpp",
+            INCLUDE / "offload_api.h"]
+    if force or _stale(backend, srcs):
+        _run([cxx, *CXX_FLAGS, *inc, "-o", backend, srcs[0], "-ldl"], verbose)
+
+    loader = OUT / "libhc-gpu-runtime-loader.so"
+    srcs = [CSRC / "loader" / "loader.cpp", INCLUDE / "offload_api.h"]
+    if force or _stale(loader, srcs):
+        _run([cxx, *CXX_FLAGS, *inc, "-o", loader, srcs[0], "-ldl"], verbose)
+
+    kernels = OUT / "libhc-b200-kernels.so"
+    srcs = [CSRC / "launch" / "kernels_api.cpp", INCLUDE / "hc_b200_kernels.h",
+            INCLUDE / "offload_api.h", loader, *cubins]
+    if force or _stale(kernels, srcs):
+        asm = OUT / "images_gen.S"
+        _write_images_asm(cubins, asm)
+        _run([cxx, *CXX_FLAGS, *inc, "-o", kernels, srcs[0], asm,
+              "-L", OUT, "-lhc-gpu-runtime-loader", "-ldl"], verbose)
+
+    pyinc = sysconfig.get_paths()["include"]
+    have_python_headers = (Path(pyinc) / "Python.h").exists()
+    built = [backend, loader, kernels]
+    if have_python_headers:
+        import pybind11
+
+        pyflags = ["-I", pyinc, "-I", pybind11.get_include()]
+        pyrt = OUT / "libhc-python-runtime.so"
+        srcs = [CSRC / "pyruntime" / "py_runtime.cpp", CSRC / "pyruntime" / "array_arg.hpp",
+                INCLUDE / "hc_python_runtime.h", loader]
+        if all(Path(s).exists() for s in srcs) and (force or _stale(pyrt, srcs)):
+            _run([cxx, *CXX_FLAGS, *inc, *pyflags, "-o", pyrt, srcs[0],
+                  "-L", OUT, "-lhc-gpu-runtime-loader", "-ldl"], verbose)
+        if pyrt.exists():
+            built.append(pyrt)
+        disp = OUT / "_dispatcher.so"
+        srcs = [CSRC / "dispatch" / "dispatcher.cpp", CSRC / "pyruntime" / "array_arg.hpp",
+                INCLUDE / "hc_b200_kernels.h", kernels]
+        if all(Path(s).exists() for s in srcs) and (force or _stale(disp, srcs)):
+            _run([cxx, *CXX_FLAGS, *inc, *pyflags, "-I", CSRC / "pyruntime", "-o", disp, srcs[0],
+                  "-L", OUT, "-lhc-b200-kernels", "-lhc-gpu-runtime-loader", "-ldl"], verbose)
+        if disp.exists():
+            built.append(disp)
+    return built
+
+
+def build_all(verbose=False, force=False):
+    """Build everything; returns the list of shared libraries produced."""
+    return build_libs(verbose, force)
+
+
+if __name__ == "__main__":
+    libs = build_all(verbose="-q" not in sys.argv, force="--force" in sys.argv)
+    for lib in libs:
+        print(lib)

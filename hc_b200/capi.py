@@ -1,0 +1,264 @@
+"""ctypes bindings of the C-ABI libraries in ``hc_b200/_native``.
+
+This module only declares prototypes and loads the libraries; it holds no
+logic of its own.  It is what a foreign-language host would write against
+``include/*.h``, and the GPU parity tests call the kernels through it so that
+they exercise the C-ABI itself.
+
+The libraries are never built implicitly.  If one is missing the import fails
+with an error that names the build command: there is no CPU fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+NATIVE_DIR = Path(__file__).resolve().parent / "_native"
+
+OlErrorCallback = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_char_p)
+
+# hc_b200_kernels.h: enum HcDType
+HC_F32, HC_F64, HC_BF16, HC_I8 = 0, 1, 2, 3
+
+# offload_api.h: OLX_DEVICE_*
+OLX_DEVICE_SM_COUNT = 1
+OLX_DEVICE_CC_MAJOR = 2
+OLX_DEVICE_CC_MINOR = 3
+OLX_DEVICE_L2_BYTES = 4
+OLX_DEVICE_MAX_SMEM_OPTIN = 5
+
+_sz = C.c_size_t
+_vp = C.c_void_p
+_ll = C.c_longlong
+
+# name -> (restype, argtypes), exactly as declared in include/offload_api.h
+OL_PROTOTYPES = {
+    "olCreateDevice": (_vp, [C.c_char_p, OlErrorCallback, _vp]),
+    "olReleaseDevice": (None, [_vp]),
+    "olCreateModule": (_vp, [_vp, _vp, _sz]),
+    "olReleaseModule": (None, [_vp]),
+    "olGetKernel": (_vp, [_vp, C.c_char_p]),
+    "olReleaseKernel": (None, [_vp]),
+    "olSuggestBlockSize": (C.c_int, [_vp, C.POINTER(_sz), C.POINTER(_sz), _sz]),
+    "olCreateQueue": (_vp, [_vp]),
+    "olReleaseQueue": (None, [_vp]),
+    "olSyncQueue": (C.c_int, [_vp]),
+    "olAllocDevice": (_vp, [_vp, _sz, _sz]),
+    "olDeallocDevice": (None, [_vp, _vp]),
+    "olLaunchKernel": (
+        C.c_int,
+        [_vp, _vp, C.POINTER(_sz), C.POINTER(_sz), _sz, C.POINTER(_vp), _sz, _sz],
+    ),
+}
+OLX_PROTOTYPES = {
+    "olxQueueNativeHandle": (_vp, [_vp]),
+    "olxMemcpyHtoD": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "olxMemcpyDtoH": (C.c_int, [_vp, _vp, _vp, _sz]),
+    "olxMemsetD8": (C.c_int, [_vp, _vp, C.c_int, _sz]),
+    "olxDeviceAttribute": (C.c_int, [_vp, C.c_int, C.POINTER(_ll)]),
+    "olxEncodeTensorMap2D": (
+        C.c_int,
+        [_vp, _vp, C.c_int, _vp, _sz, _sz, _sz, C.c_uint, C.c_uint, C.c_int],
+    ),
+}
+LOADER_EXTRA_PROTOTYPES = {
+    "setGPULoaderSearchPaths": (None, [C.POINTER(C.c_char_p), _sz]),
+    "enableFuncTracing": (None, [C.c_int]),
+}
+# include/hc_b200_kernels.h
+KERNELS_PROTOTYPES = {
+    "hcImageCount": (C.c_int, []),
+    "hcImageName": (C.c_char_p, [C.c_int]),
+    "hcImageData": (_vp, [C.c_int, C.POINTER(_sz)]),
+    "hcImageOfKernel": (C.c_int, [C.c_char_p]),
+    "hcCreateContext": (_vp, [C.c_char_p, OlErrorCallback, _vp]),
+    "hcReleaseContext": (None, [_vp]),
+    "hcContextDevice": (_vp, [_vp]),
+    "hcContextQueue": (_vp, [_vp]),
+    "hcContextStream": (_vp, [_vp]),
+    "hcSynchronize": (C.c_int, [_vp]),
+    "hcLastError": (C.c_char_p, [_vp]),
+    "hcLaunchCount": (_ll, [_vp]),
+    "hcKernelStatus": (C.c_int, [_vp, C.POINTER(C.c_int)]),
+    "hcSetOption": (C.c_int, [_vp, C.c_char_p, _ll]),
+    "hcCopy2D": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
+    "hcSoftmaxRows": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
+    "hcReduceRows": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),
+    "hcGemmTiled": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]),
+    "hcGemmBf16": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
+    "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
+    "hcGemmW8A16": (
+        C.c_int,
+        [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll],
+    ),
+    "hcDequantW8": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll]),
+}
+# include/hc_python_runtime.h
+PYRUNTIME_PROTOTYPES = {
+    "hcgpuEnableTraceFunctions": (None, [C.c_int]),
+    "hcgpuSetRuntimeSearchPaths": (None, [C.py_object]),
+    "hcgpuConvertPyArray": (C.c_int, [_vp, C.py_object, C.c_int, _vp]),
+    "hcgpuConvertPyInt64": (C.c_int, [_vp, C.py_object, C.POINTER(C.c_int64)]),
+    "hcgpuGetKernel": (_vp, [C.POINTER(_vp), C.c_char_p, _vp, _sz, C.c_char_p]),
+    "hcgpuSuggestBlockSize": (None, [_vp, C.POINTER(_sz), C.POINTER(_sz), _sz]),
+    "hcgpuLaunchKernel": (
+        None,
+        [_vp, C.POINTER(_sz), C.POINTER(_sz), _sz, C.POINTER(_vp), _sz, _sz],
+    ),
+}
+
+
+def _declare(lib, table):
+    for name, (restype, argtypes) in table.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def _open(name: str, loader=C.CDLL):
+    path = NATIVE_DIR / name
+    if not path.exists():
+        raise ImportError(
+            f"{path} is missing: build the native libraries first "
+            f"(`python -m hc_b200.build`); hc_b200 has no CPU fallback"
+        )
+    return loader(str(path))
+
+
+def load_backend():
+    """libhc-cuda-runtime.so (the 13 ol* + the olx* additions)."""
+    return _declare(_declare(_open("libhc-cuda-runtime.so"), OL_PROTOTYPES), OLX_PROTOTYPES)
+
+
+def load_loader():
+    """libhc-gpu-runtime-loader.so (same ABI + the two loader-only exports)."""
+    lib = _declare(_declare(_open("libhc-gpu-runtime-loader.so"), OL_PROTOTYPES), OLX_PROTOTYPES)
+    return _declare(lib, LOADER_EXTRA_PROTOTYPES)
+
+
+def load_kernels():
+    """libhc-b200-kernels.so (images + workload launchers)."""
+    return _declare(_open("libhc-b200-kernels.so"), KERNELS_PROTOTYPES)
+
+
+def load_python_runtime():
+    """libhc-python-runtime.so (hcgpu*); holds the GIL while called."""
+    return _declare(_open("libhc-python-runtime.so", C.PyDLL), PYRUNTIME_PROTOTYPES)
+
+
+class HcError(RuntimeError):
+    """A C-ABI call reported failure; the message is the library's own text."""
+
+
+class Context:
+    """Owns one HcContext and turns nonzero returns into :class:`HcError`.
+
+    Arguments of the workload methods are raw device addresses (ints) and
+    sizes, as in ``include/hc_b200_kernels.h``.
+    """
+
+    def __init__(self, device_desc: str = "cuda:0"):
+        self.lib = load_kernels()
+        self.messages = []
+
+        def _on_message(_ctx, severity, text):
+            self.messages.append((severity, (text or b"").decode(errors="replace")))
+
+        self._callback = OlErrorCallback(_on_message)  # keep alive
+        self.handle = self.lib.hcCreateContext(device_desc.encode(), self._callback, None)
+        if not self.handle:
+            errors = [m for s, m in self.messages if s == 0] or [m for _, m in self.messages]
+            raise HcError(
+                f"hcCreateContext({device_desc!r}) failed: " + ("; ".join(errors) or "no detail")
+            )
+        self.device_desc = device_desc
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.hcReleaseContext(self.handle)
+            self.handle = None
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, what):
+        if rc:
+            raise HcError(f"{what} failed: {self.lib.hcLastError(self.handle).decode(errors='replace')}")
+
+    @property
+    def stream(self) -> int:
+        return self.lib.hcContextStream(self.handle) or 0
+
+    @property
+    def queue(self) -> int:
+        return self.lib.hcContextQueue(self.handle)
+
+    @property
+    def device(self) -> int:
+        return self.lib.hcContextDevice(self.handle)
+
+    @property
+    def launch_count(self) -> int:
+        return self.lib.hcLaunchCount(self.handle)
+
+    def synchronize(self):
+        self._check(self.lib.hcSynchronize(self.handle), "hcSynchronize")
+
+    def kernel_status(self) -> int:
+        value = C.c_int(0)
+        self._check(self.lib.hcKernelStatus(self.handle, C.byref(value)), "hcKernelStatus")
+        return value.value
+
+    def set_option(self, name: str, value: int):
+        self._check(self.lib.hcSetOption(self.handle, name.encode(), value), "hcSetOption")
+
+    def copy2d(self, src, dst, rows, cols, src_pitch, dst_pitch, elem_bytes):
+        self._check(
+            self.lib.hcCopy2D(self.handle, src, dst, rows, cols, src_pitch, dst_pitch, elem_bytes),
+            "hcCopy2D",
+        )
+
+    def softmax_rows(self, x, y, rows, cols, x_pitch, y_pitch, dtype=HC_F32):
+        self._check(
+            self.lib.hcSoftmaxRows(self.handle, x, y, rows, cols, x_pitch, y_pitch, dtype),
+            "hcSoftmaxRows",
+        )
+
+    def reduce_rows(self, x, sum_out, max_out, rows, cols, pitch, dtype=HC_F32):
+        self._check(
+            self.lib.hcReduceRows(self.handle, x, sum_out, max_out, rows, cols, pitch, dtype),
+            "hcReduceRows",
+        )
+
+    def gemm_tiled(self, a, b, c, m, n, k, lda, ldb, ldc, dtype=HC_F32):
+        self._check(
+            self.lib.hcGemmTiled(self.handle, a, b, c, m, n, k, lda, ldb, ldc, dtype),
+            "hcGemmTiled",
+        )
+
+    def gemm_bf16(self, a, b, c, m, n, k, lda, ldb, ldc):
+        self._check(
+            self.lib.hcGemmBf16(self.handle, a, b, c, m, n, k, lda, ldb, ldc), "hcGemmBf16"
+        )
+
+    def gemm_w8a16_workspace_bytes(self, n, k) -> int:
+        return self.lib.hcGemmW8A16WorkspaceBytes(n, k)
+
+    def gemm_w8a16(self, a, w, scale, out, workspace, workspace_bytes, m, n, k, lda, ldw, ldc):
+        self._check(
+            self.lib.hcGemmW8A16(
+                self.handle, a, w, scale, out, workspace, workspace_bytes, m, n, k, lda, ldw, ldc
+            ),
+            "hcGemmW8A16",
+        )
+
+    def dequant_w8(self, w, out, rows, cols, w_pitch, out_pitch):
+        self._check(
+            self.lib.hcDequantW8(self.handle, w, out, rows, cols, w_pitch, out_pitch),
+            "hcDequantW8",
+        )

@@ -1,0 +1,383 @@
+// Dense bf16 GEMM on the 5th-generation tensor cores:
+//   C[M, N] = bf16( (A[M, K] @ B[K, N]) (* scale[N]) ),  fp32 accumulation,
+// A, B, C row-major with explicit row pitches.
+//
+// It computes what the reference's dot kernels compute (python/hckernel/tests/
+// test_examples.py:88-111 K-blocked, :136-155 full-K): every work-group owns
+// one output tile, accumulates A-tile x B-tile products over K in a zero-
+// initialised accumulator and stores the tile clipped to the matrix; tiles
+// loaded past the matrix edge read as zero (python/hckernel/kernel_api.py:
+// 297-342).  B is [K, N] row-major as in the reference's `b: Buffer[K, N]`.
+//
+// Mapping to the hardware (one persistent CTA per SM, 192 threads):
+//   warp 0     TMA producer: cp.async.bulk.tensor boxes of 64 bf16 per row,
+//              128-byte swizzle, into a ring of shared-memory stages; out-of-
+//              range parts of a box are zero-filled by the TMA unit, which is
+//              exactly the reference's zero-padded edge tile.  No cluster
+//              multicast is used anywhere.
+//   warp 1     allocates TMEM and issues tcgen05.mma (one thread): A is
+//              K-major, B is N-major (row-major [K, N] needs no transpose),
+//              the fp32 accumulator (128 lanes x 256 columns) lives in TMEM
+//              and is double-buffered so the epilogue of tile i overlaps the
+//              main loop of tile i+1.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator, optional per-column
+//              scale, round to bf16 (nearest even), store clipped to M x N.
+//
+// PAIR = true runs two CTAs (a cluster of 2 neighbouring SMs) on one 256 x 256
+// tile with tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A
+// and its own 128 columns of B, so a CTA moves 32 KiB per 64-deep K-block
+// instead of 48 KiB for the same flops, and the leader CTA issues the MMAs for
+// both.
+//
+// Every mbarrier wait is bounded (hc_ptx.cuh); a wait that runs out records a
+// code in `status`, raises a CTA-wide abort flag that makes all roles leave
+// their loops, and the kernel exits through the normal teardown.
+#include "hc_ptx.cuh"
+
+namespace {
+
+using namespace hc;
+
+constexpr int BM = 128;      // accumulator rows per CTA (TMEM lanes)
+constexpr int BN = 256;      // accumulator columns per tile
+constexpr int BK = 64;       // K depth of one stage: 64 bf16 = one 128-byte row
+constexpr int UMMA_K = 16;   // K depth of one tcgen05.mma with 16-bit inputs
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512; // two 256-column accumulators
+
+template <bool PAIR> struct Config {
+  static constexpr int kCtas = PAIR ? 2 : 1;
+  static constexpr int kTileM = BM * kCtas;
+  static constexpr int kBColsPerCta = BN / kCtas; // B columns a CTA stages
+  static constexpr int kBChunks = kBColsPerCta / 64;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBChunkBytes = BK * 64 * 2;
+  static constexpr int kStageBytes = kABytes + kBChunks * kBChunkBytes;
+  static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr uint32_t kInstrDesc =
+      makeInstrDescBf16(kTileM, BN, /*aMnMajor=*/false, /*bMnMajor=*/true);
+};
+
+struct alignas(8) Barriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmemFull[2];
+  uint64_t tmemEmpty[2];
+  uint32_t tmemBase;
+  int abortFlag;
+};
+
+struct Params {
+  long long M, N, K;
+  long long ldc;     // elements
+  int tilesM, tilesN;
+  int bandM;         // M-tiles per rasterisation band
+  int vecStore;      // C base 16-byte aligned and ldc % 8 == 0
+};
+
+__device__ __forceinline__ void tileCoords(int t, const Params &p, int &tm,
+                                           int &tn) {
+  const int perBand = p.bandM * p.tilesN;
+  const int band = t / perBand;
+  const int rem = t - band * perBand;
+  const int rowsInBand = min(p.bandM, p.tilesM - band * p.bandM);
+  tm = band * p.bandM + rem % rowsInBand;
+  tn = rem / rowsInBand;
+}
+
+template <bool PAIR, bool SCALED>
+__device__ __forceinline__ void
+gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
+         __nv_bfloat16 *__restrict__ c, const float *__restrict__ scale,
+         const Params &p, int *status, unsigned char *smemRaw) {
+  using Cfg = Config<PAIR>;
+  // The swizzled stages need 1024-byte alignment.
+  const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
+  Barriers *bars = reinterpret_cast<Barriers *>(
+      smemRaw + (smemBase - smemAddr(smemRaw)) + Cfg::kStages * Cfg::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t ctaRank = PAIR ? clusterCtaRank() : 0u;
+  const bool leader = ctaRank == 0;
+  volatile int *abortFlag = &bars->abortFlag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbarInit(smemAddr(&bars->full[s]), Cfg::kCtas); // one expect_tx per CTA
+      mbarInit(smemAddr(&bars->empty[s]), 1);         // one MMA commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbarInit(smemAddr(&bars->tmemFull[a]), 1);
+      mbarInit(smemAddr(&bars->tmemEmpty[a]), 4 * Cfg::kCtas); // epilogue warps
+    }
+    bars->abortFlag = 0;
+    fenceBarrierInit();
+    prefetchTensorMap(mapA);
+    prefetchTensorMap(mapB);
+  }
+  if (warp == 1) {
+    tmemAlloc<Cfg::kCtas>(smemAddr(&bars->tmemBase), TMEM_COLS);
+    tmemRelinquish<Cfg::kCtas>();
+  }
+  tcgen05FenceBefore();
+  if constexpr (PAIR)
+    clusterSync();
+  else
+    __syncthreads();
+  tcgen05FenceAfter();
+  const uint32_t tmemBase = bars->tmemBase;
+
+  const int kBlocks = int((p.K + BK - 1) / BK);
+  const int numTiles = p.tilesM * p.tilesN;
+  const int firstTile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tileStep = PAIR ? (gridDim.x >> 1) : gridDim.x;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep) {
+        int tm, tn;
+        tileCoords(t, p, tm, tn);
+        const int row0 = tm * Cfg::kTileM + int(ctaRank) * BM;
+        const int col0 = tn * BN + int(ctaRank) * Cfg::kBColsPerCta;
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const uint32_t s = it % Cfg::kStages;
+          const uint32_t phase = (it / Cfg::kStages) & 1u;
+          if (!mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag,
+                        status, kStatusProducerWait))
+            break;
+          // Completion bytes of both CTAs are counted on the leader's barrier.
+          uint32_t fullBar = smemAddr(&bars->full[s]);
+          if constexpr (PAIR)
+            fullBar = mapSharedToCta(fullBar, 0);
+          const uint32_t stage = smemBase + s * Cfg::kStageBytes;
+          if constexpr (PAIR) {
+            asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::"
+                         "cluster.b64 _, [%0], %1;" ::"r"(fullBar),
+                         "r"(uint32_t(Cfg::kStageBytes))
+                         : "memory");
+            tmaLoad2DPair(stage, mapA, fullBar, kb * BK, row0);
+            for (int ch = 0; ch < Cfg::kBChunks; ++ch)
+              tmaLoad2DPair(stage + Cfg::kABytes + ch * Cfg::kBChunkBytes, mapB,
+                            fullBar, col0 + ch * 64, kb * BK);
+          } else {
+            mbarExpectTx(fullBar, Cfg::kStageBytes);
+            tmaLoad2D(stage, mapA, fullBar, kb * BK, row0);
+            for (int ch = 0; ch < Cfg::kBChunks; ++ch)
+              tmaLoad2D(stage + Cfg::kABytes + ch * Cfg::kBChunkBytes, mapB,
+                        fullBar, col0 + ch * 64, kb * BK);
+          }
+        }
+      }
+      // Tail: the commits that free the last stages must have landed in this
+      // CTA's barriers before its shared memory goes away.
+      for (int i = 0; i < Cfg::kStages && !*abortFlag; ++i, ++it) {
+        const uint32_t s = it % Cfg::kStages;
+        const uint32_t phase = (it / Cfg::kStages) & 1u;
+        if (!mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
+                      kStatusDrainWait))
+          break;
+      }
+      if (*abortFlag) {
+        // Copies may still be landing in this CTA's stages: give them time.
+        const unsigned long long t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0 && leader) {
+      uint32_t it = 0;
+      int tileIter = 0;
+      for (int t = firstTile; t < numTiles && !*abortFlag;
+           t += tileStep, ++tileIter) {
+        const int acc = tileIter & 1;
+        const uint32_t accPhase = (tileIter >> 1) & 1u;
+        if (!mbarWait(smemAddr(&bars->tmemEmpty[acc]), accPhase ^ 1u, abortFlag,
+                      status, kStatusMmaWaitTmem))
+          break;
+        tcgen05FenceAfter();
+        const uint32_t dTmem = tmemBase + uint32_t(acc * BN);
+        bool ok = true;
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const uint32_t s = it % Cfg::kStages;
+          const uint32_t phase = (it / Cfg::kStages) & 1u;
+          if (!mbarWait(smemAddr(&bars->full[s]), phase, abortFlag, status,
+                        kStatusMmaWaitData)) {
+            ok = false;
+            break;
+          }
+          tcgen05FenceAfter();
+          const uint32_t stage = smemBase + s * Cfg::kStageBytes;
+          // A: K-major, rows 128 bytes apart, 8-row groups 1024 bytes apart.
+          const uint64_t aDesc = makeSmemDesc(stage, 16, 1024);
+          // B: N-major, 64-column chunks BK*128 bytes apart (leading), 8-deep
+          // K groups 1024 bytes apart (stride).
+          const uint64_t bDesc =
+              makeSmemDesc(stage + Cfg::kABytes, Cfg::kBChunkBytes, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 K-elements further: 32 bytes along an A row, 16 rows of
+            // 128 bytes down a B chunk.
+            umma<Cfg::kCtas>(dTmem, aDesc + uint64_t(kk * 2),
+                             bDesc + uint64_t(kk * 128), Cfg::kInstrDesc,
+                             (kb | kk) != 0);
+          }
+          // Frees the stage (in both CTAs of a pair) once these MMAs are done.
+          if constexpr (PAIR)
+            ummaCommitPair(smemAddr(&bars->empty[s]), 0x3);
+          else
+            ummaCommit(smemAddr(&bars->empty[s]));
+        }
+        if (!ok)
+          break;
+        if constexpr (PAIR)
+          ummaCommitPair(smemAddr(&bars->tmemFull[acc]), 0x3);
+        else
+          ummaCommit(smemAddr(&bars->tmemFull[acc]));
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32) for this warp
+    uint32_t tmemEmptyBar[2];
+    for (int a = 0; a < 2; ++a) {
+      tmemEmptyBar[a] = smemAddr(&bars->tmemEmpty[a]);
+      if constexpr (PAIR)
+        tmemEmptyBar[a] = mapSharedToCta(tmemEmptyBar[a], 0);
+    }
+    int tileIter = 0;
+    for (int t = firstTile; t < numTiles; t += tileStep, ++tileIter) {
+      int tm, tn;
+      tileCoords(t, p, tm, tn);
+      const int acc = tileIter & 1;
+      const uint32_t accPhase = (tileIter >> 1) & 1u;
+      bool ok = true;
+      if (lane == 0)
+        ok = mbarWait(smemAddr(&bars->tmemFull[acc]), accPhase, abortFlag,
+                      status, kStatusEpilogueWait);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok)
+        break;
+      tcgen05FenceAfter();
+      const long long row =
+          (long long)tm * Cfg::kTileM + int(ctaRank) * BM + quad * 32 + lane;
+      const long long colBase = (long long)tn * BN;
+      const uint32_t taddr =
+          tmemBase + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
+      __nv_bfloat16 *crow = c + row * p.ldc;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t v[32];
+        __syncwarp(); // tcgen05.ld needs the whole warp, converged
+        tmemLoad32x32(taddr + uint32_t(ch * 32), v);
+        tmemLoadWait();
+        const long long col = colBase + ch * 32;
+        if (row >= p.M || col >= p.N)
+          continue;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          f[j] = __uint_as_float(v[j]);
+        if constexpr (SCALED) {
+          if (col + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 s =
+                  __ldg(reinterpret_cast<const float4 *>(scale + col + j));
+              f[j] *= s.x;
+              f[j + 1] *= s.y;
+              f[j + 2] *= s.z;
+              f[j + 3] *= s.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N)
+                f[j] *= __ldg(scale + col + j);
+          }
+        }
+        if (p.vecStore && col + 32 <= p.N) {
+          uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h =
+                  __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t *>(&h);
+            }
+            dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col + j < p.N)
+              crow[col + j] = __float2bfloat16_rn(f[j]);
+        }
+      }
+      // This warp has read its quarter of the accumulator.
+      tcgen05FenceBefore();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (PAIR)
+          mbarArriveCluster(tmemEmptyBar[acc]);
+        else
+          mbarArrive(tmemEmptyBar[acc]);
+      }
+    }
+  }
+
+  // -------------------------------- teardown ----------------------------------
+  __syncwarp();
+  tcgen05FenceBefore();
+  if constexpr (PAIR)
+    clusterSync();
+  else
+    __syncthreads();
+  if (warp == 1) {
+    tcgen05FenceAfter();
+    tmemFree<Cfg::kCtas>(tmemBase, TMEM_COLS);
+  }
+}
+
+} // namespace
+
+// Dynamic shared memory: stages + barriers + 1 KiB alignment slack; the host
+// computes the same numbers (kernels_api.cpp).
+#define HC_GEMM_ARGS                                                           \
+  const __grid_constant__ CUtensorMap mapA,                                    \
+      const __grid_constant__ CUtensorMap mapB, __nv_bfloat16 *c,              \
+      const float *scale, long long M, long long N, long long K,               \
+      long long ldc, int tilesM, int tilesN, int bandM, int vecStore,          \
+      int *status
+
+#define HC_GEMM_BODY(PAIR, SCALED)                                             \
+  extern __shared__ __align__(1024) unsigned char smemRaw[];                   \
+  Params p{M, N, K, ldc, tilesM, tilesN, bandM, vecStore};                     \
+  gemmUmma<PAIR, SCALED>(&mapA, &mapB, c, scale, p, status, smemRaw);
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma(HC_GEMM_ARGS) {
+  HC_GEMM_BODY(false, false)
+}
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma_scaled(HC_GEMM_ARGS) {
+  HC_GEMM_BODY(false, true)
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1)
+    __launch_bounds__(NUM_THREADS, 1) hc_gemm_bf16_umma_pair(HC_GEMM_ARGS) {
+  HC_GEMM_BODY(true, false)
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1)
+    __launch_bounds__(NUM_THREADS, 1)
+        hc_gemm_bf16_umma_pair_scaled(HC_GEMM_ARGS) {
+  HC_GEMM_BODY(true, true)
+}

@@ -1,0 +1,173 @@
+// Tiled GEMM on the CUDA cores: C[M, N] = A[M, K] @ B[K, N] (* scale[N]), all
+// row-major with explicit row pitches, any M, N, K.
+//
+// This is the reference's K-blocked dot kernel (python/hckernel/tests/
+// test_examples.py:88-111): a 2-D grid of work-groups, each owning an
+// (m_block x n_block) tile of the output, walks K in blocks of KB, loads the
+// A and B tiles (zero-filled past the matrix edge, python/hckernel/
+// kernel_api.py:297-316), accumulates their product and finally stores the
+// tile clipped to the matrix (kernel_api.py:318-342).  Here a work-group is a
+// CTA of 256 threads that owns a 64 x 64 tile and walks K in blocks of 16 -
+// the group shape and KB of the reference's fp32 benchmark case - with a 4 x 4
+// register tile per thread, fp32 (or fp64) FMA accumulation, and the next
+// K-block prefetched into registers while the current one is multiplied.
+//
+// The same template also serves as the any-shape fallback of the tensor-core
+// kernels: bf16 inputs with fp32 accumulation and bf16 output, and bf16 x int8
+// with a per-output-column fp32 scale applied to the accumulator before
+// rounding (the weight-only dequant GEMM).
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16, THREADS = 256;
+
+template <typename T> struct Conv;
+template <> struct Conv<float> {
+  static __device__ __forceinline__ float load(float v) { return v; }
+  static __device__ __forceinline__ float store(float v) { return v; }
+};
+template <> struct Conv<double> {
+  static __device__ __forceinline__ double load(double v) { return v; }
+  static __device__ __forceinline__ double store(double v) { return v; }
+};
+template <> struct Conv<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+  }
+  static __device__ __forceinline__ __nv_bfloat16 store(float v) {
+    return __float2bfloat16_rn(v);
+  }
+};
+template <> struct Conv<int8_t> {
+  static __device__ __forceinline__ float load(int8_t v) { return float(v); }
+};
+
+template <typename TA, typename TB, typename TC, typename TAcc>
+__device__ __forceinline__ void
+gemmTile(const TA *__restrict__ a, const TB *__restrict__ b,
+         TC *__restrict__ c, const float *__restrict__ scale, long long M,
+         long long N, long long K, long long lda, long long ldb,
+         long long ldc) {
+  // +4 padding keeps the transposed A stores and the row reads conflict-free.
+  __shared__ TAcc sA[2][TK][TM + 4];
+  __shared__ TAcc sB[2][TK][TN + 4];
+
+  const int tid = threadIdx.x;
+  const long long m0 = (long long)blockIdx.y * TM;
+  const long long n0 = (long long)blockIdx.x * TN;
+
+  // Global -> register staging: each thread moves 4 elements of A and of B.
+  const int aRow = tid >> 2, aCol = (tid & 3) << 2; // A tile is 64 x 16
+  const int bRow = tid >> 4, bCol = (tid & 15) << 2; // B tile is 16 x 64
+  TAcc ra[4], rb[4];
+
+  auto fetch = [&](long long k0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      long long gm = m0 + aRow, gk = k0 + aCol + i;
+      ra[i] = (gm < M && gk < K) ? TAcc(Conv<TA>::load(a[gm * lda + gk]))
+                                 : TAcc(0);
+      long long gkb = k0 + bRow, gn = n0 + bCol + i;
+      rb[i] = (gkb < K && gn < N) ? TAcc(Conv<TB>::load(b[gkb * ldb + gn]))
+                                  : TAcc(0);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sA[buf][aCol + i][aRow] = ra[i];
+      sB[buf][bRow][bCol + i] = rb[i];
+    }
+  };
+
+  const int ty = tid >> 4, tx = tid & 15; // 16 x 16 threads, 4 x 4 outputs each
+  TAcc acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      acc[i][j] = TAcc(0);
+
+  const long long kBlocks = (K + TK - 1) / TK;
+  if (kBlocks > 0) {
+    fetch(0);
+    stash(0);
+  }
+  __syncthreads();
+  for (long long kb = 0; kb < kBlocks; ++kb) {
+    const int cur = kb & 1;
+    if (kb + 1 < kBlocks)
+      fetch((kb + 1) * TK);
+#pragma unroll
+    for (int k = 0; k < TK; ++k) {
+      TAcc av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        av[i] = sA[cur][k][ty * 4 + i];
+        bv[i] = sB[cur][k][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] += av[i] * bv[j];
+    }
+    if (kb + 1 < kBlocks)
+      stash(cur ^ 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    long long gm = m0 + ty * 4 + i;
+    if (gm >= M)
+      continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      long long gn = n0 + tx * 4 + j;
+      if (gn >= N)
+        continue;
+      TAcc v = acc[i][j];
+      if (scale)
+        v *= TAcc(scale[gn]);
+      c[gm * ldc + gn] = Conv<TC>::store(v);
+    }
+  }
+}
+
+} // namespace
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+    hc_gemm_tiled_f32(const float *a, const float *b, float *c, long long M,
+                      long long N, long long K, long long lda, long long ldb,
+                      long long ldc) {
+  gemmTile<float, float, float, float>(a, b, c, nullptr, M, N, K, lda, ldb,
+                                       ldc);
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+    hc_gemm_tiled_f64(const double *a, const double *b, double *c, long long M,
+                      long long N, long long K, long long lda, long long ldb,
+                      long long ldc) {
+  gemmTile<double, double, double, double>(a, b, c, nullptr, M, N, K, lda, ldb,
+                                           ldc);
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+    hc_gemm_tiled_bf16(const __nv_bfloat16 *a, const __nv_bfloat16 *b,
+                       __nv_bfloat16 *c, long long M, long long N, long long K,
+                       long long lda, long long ldb, long long ldc) {
+  gemmTile<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, float>(
+      a, b, c, nullptr, M, N, K, lda, ldb, ldc);
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+    hc_gemm_tiled_w8a16(const __nv_bfloat16 *a, const int8_t *w,
+                        const float *scale, __nv_bfloat16 *c, long long M,
+                        long long N, long long K, long long lda, long long ldw,
+                        long long ldc) {
+  gemmTile<__nv_bfloat16, int8_t, __nv_bfloat16, float>(a, w, c, scale, M, N, K,
+                                                        lda, ldw, ldc);
+}

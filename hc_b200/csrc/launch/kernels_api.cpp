@@ -1,0 +1,544 @@
+// libhc-b200-kernels.so: owns the precompiled sm_100a images and launches the
+// workload kernels through the ol* ABI of the loader.
+//
+// This is the host side that the reference generates with its JIT: create the
+// module from a blob, look the kernel up, pack `void *args[]`, launch
+// (mlir/lib/Transforms/GpuToGpuRuntime.cpp:163-309 emits that sequence;
+// python/cpp/py-runtime/src/GpuRuntime.cpp:26-69 executes it).  Here the blobs
+// are fixed, so the sequence is ordinary C++ and each workload gets a typed
+// entry point that validates its arguments and chooses a kernel variant.
+#include "hc_b200_kernels.h"
+
+#include <cuda.h> // CUtensorMap (type only; no driver call is made here)
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+// Loader-only export (gpu-runtime/loader/src/Loader.cpp:20-39 in the
+// reference); declared here because offload_api.h covers the shared ABI only.
+extern "C" void setGPULoaderSearchPaths(const char *paths[], size_t count);
+
+// ---- embedded images (images_gen.S) -------------------------------------------
+struct HcImage {
+  const char *name;
+  const unsigned char *begin;
+  const unsigned char *end;
+};
+extern "C" const HcImage hc_b200_images[];
+extern "C" const int hc_b200_image_count;
+
+namespace {
+
+struct KernelEntry {
+  const char *kernel;
+  const char *image;
+};
+
+// Which image defines which kernel.
+const KernelEntry kKernelTable[] = {
+    {"hc_copy2d", "copy2d"},
+    {"hc_softmax_rows_f32_w1", "softmax_rows"},
+    {"hc_softmax_rows_f32_w2", "softmax_rows"},
+    {"hc_softmax_rows_f32_w4", "softmax_rows"},
+    {"hc_softmax_rows_f32_w8", "softmax_rows"},
+    {"hc_softmax_rows_f32_w16", "softmax_rows"},
+    {"hc_softmax_rows_f32_w32", "softmax_rows"},
+    {"hc_softmax_rows_generic_f32", "softmax_rows"},
+    {"hc_softmax_rows_generic_f64", "softmax_rows"},
+    {"hc_reduce_rows_warp_f32", "reduce_rows"},
+    {"hc_reduce_rows_warp_f64", "reduce_rows"},
+    {"hc_reduce_rows_block_f32", "reduce_rows"},
+    {"hc_reduce_rows_block_f64", "reduce_rows"},
+    {"hc_gemm_tiled_f32", "gemm_tiled"},
+    {"hc_gemm_tiled_f64", "gemm_tiled"},
+    {"hc_gemm_tiled_bf16", "gemm_tiled"},
+    {"hc_gemm_tiled_w8a16", "gemm_tiled"},
+    {"hc_gemm_bf16_umma", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_scaled", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_pair", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_pair_scaled", "gemm_bf16_umma"},
+    {"hc_dequant_w8_bf16", "dequant_w8"},
+};
+
+int findImage(const char *name) {
+  for (int i = 0; i < hc_b200_image_count; ++i)
+    if (std::strcmp(hc_b200_images[i].name, name) == 0)
+      return i;
+  return -1;
+}
+
+long long ceilDiv(long long a, long long b) { return (a + b - 1) / b; }
+long long roundUp(long long a, long long b) { return ceilDiv(a, b) * b; }
+bool aligned(const void *p, size_t a) {
+  return reinterpret_cast<uintptr_t>(p) % a == 0;
+}
+
+// Geometry of the tensor-core GEMM kernels (gemm_bf16_umma.cu).
+constexpr int kUmmaBM = 128, kUmmaBN = 256, kUmmaBK = 64;
+constexpr int kUmmaThreads = 192;
+constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
+                                  512 /*barriers*/;
+
+} // namespace
+
+struct HcContextImpl {
+  OlErrorCallback callback = nullptr;
+  void *callbackCtx = nullptr;
+  OlDevice device = nullptr;
+  OlQueue queue = nullptr;
+  std::vector<OlModule> modules; // one slot per image, loaded on first use
+  std::map<std::string, OlKernel> kernels;
+  int *statusWord = nullptr; // device
+  std::string lastError;
+  long long launches = 0;
+  long long smCount = 0;
+  long long ccMajor = 0;
+  long long gemmVariant = 0;
+
+  int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
+    char text[320];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(text, sizeof(text), fmt, ap);
+    va_end(ap);
+    lastError = text;
+    if (callback)
+      callback(callbackCtx, OlSeverity::Error, text);
+    return 1;
+  }
+
+  // ol* failures arrive here through the loader/backend callback.
+  static void onBackendMessage(void *self, OlSeverity sev, const char *desc) {
+    auto *c = static_cast<HcContextImpl *>(self);
+    if (sev == OlSeverity::Error)
+      c->lastError = desc ? desc : "";
+    if (c->callback)
+      c->callback(c->callbackCtx, sev, desc);
+  }
+
+  OlKernel kernel(const char *name) {
+    auto it = kernels.find(name);
+    if (it != kernels.end())
+      return it->second;
+    const char *imageName = nullptr;
+    for (const auto &e : kKernelTable)
+      if (std::strcmp(e.kernel, name) == 0)
+        imageName = e.image;
+    int idx = imageName ? findImage(imageName) : -1;
+    if (idx < 0) {
+      fail("Unknown kernel: %s", name);
+      return nullptr;
+    }
+    if (!modules[idx]) {
+      const HcImage &img = hc_b200_images[idx];
+      modules[idx] = olCreateModule(device, img.begin, size_t(img.end - img.begin));
+      if (!modules[idx]) {
+        fail("olCreateModule failed for image %s: %s", img.name,
+             lastError.c_str());
+        return nullptr;
+      }
+    }
+    OlKernel k = olGetKernel(modules[idx], name);
+    if (!k) {
+      fail("olGetKernel failed for %s: %s", name, lastError.c_str());
+      return nullptr;
+    }
+    kernels[name] = k;
+    return k;
+  }
+
+  int launch(const char *name, size_t gx, size_t gy, size_t gz, size_t threads,
+             void **args, size_t nArgs, size_t smem) {
+    OlKernel k = kernel(name);
+    if (!k)
+      return 1;
+    const size_t grid[3] = {gx, gy, gz};
+    const size_t block[3] = {threads, 1, 1};
+    if (olLaunchKernel(queue, k, grid, block, 3, args, nArgs, smem))
+      return fail("olLaunchKernel failed for %s: %s", name, lastError.c_str());
+    ++launches;
+    return 0;
+  }
+};
+
+namespace {
+
+// Directory this shared library was loaded from; the backend library lives
+// next to it.
+std::string ownDirectory() {
+  Dl_info info;
+  if (!dladdr(reinterpret_cast<const void *>(&hcImageCount), &info) ||
+      !info.dli_fname)
+    return ".";
+  std::string path(info.dli_fname);
+  auto slash = path.rfind('/');
+  return slash == std::string::npos ? "." : path.substr(0, slash);
+}
+
+} // namespace
+
+extern "C" {
+
+int hcImageCount(void) { return hc_b200_image_count; }
+
+const char *hcImageName(int index) {
+  return index >= 0 && index < hc_b200_image_count ? hc_b200_images[index].name
+                                                   : nullptr;
+}
+
+const void *hcImageData(int index, size_t *lenRet) {
+  if (index < 0 || index >= hc_b200_image_count)
+    return nullptr;
+  if (lenRet)
+    *lenRet = size_t(hc_b200_images[index].end - hc_b200_images[index].begin);
+  return hc_b200_images[index].begin;
+}
+
+int hcImageOfKernel(const char *kernelName) {
+  if (!kernelName)
+    return -1;
+  for (const auto &e : kKernelTable)
+    if (std::strcmp(e.kernel, kernelName) == 0)
+      return findImage(e.image);
+  return -1;
+}
+
+HcContext hcCreateContext(const char *deviceDesc, OlErrorCallback errCallback,
+                          void *ctx) {
+  auto c = std::make_unique<HcContextImpl>();
+  c->callback = errCallback;
+  c->callbackCtx = ctx;
+  c->modules.assign(size_t(hc_b200_image_count), nullptr);
+
+  static const std::string dir = ownDirectory();
+  const char *paths[1] = {dir.c_str()};
+  setGPULoaderSearchPaths(paths, 1);
+
+  c->device = olCreateDevice(deviceDesc, &HcContextImpl::onBackendMessage, c.get());
+  if (!c->device)
+    return nullptr;
+  c->queue = olCreateQueue(c->device);
+  if (!c->queue) {
+    olReleaseDevice(c->device);
+    return nullptr;
+  }
+  olxDeviceAttribute(c->device, OLX_DEVICE_SM_COUNT, &c->smCount);
+  olxDeviceAttribute(c->device, OLX_DEVICE_CC_MAJOR, &c->ccMajor);
+  if (c->smCount <= 0)
+    c->smCount = 1;
+  c->statusWord = static_cast<int *>(olAllocDevice(c->queue, 256, 256));
+  if (!c->statusWord || olxMemsetD8(c->queue, c->statusWord, 0, 256) ||
+      olSyncQueue(c->queue)) {
+    hcReleaseContext(c.release());
+    return nullptr;
+  }
+  return c.release();
+}
+
+void hcReleaseContext(HcContext c) {
+  if (!c)
+    return;
+  if (c->queue)
+    olSyncQueue(c->queue);
+  for (auto &kv : c->kernels)
+    olReleaseKernel(kv.second);
+  for (OlModule m : c->modules)
+    if (m)
+      olReleaseModule(m);
+  if (c->statusWord)
+    olDeallocDevice(c->queue, c->statusWord);
+  if (c->queue)
+    olReleaseQueue(c->queue);
+  if (c->device)
+    olReleaseDevice(c->device);
+  delete c;
+}
+
+OlDevice hcContextDevice(HcContext c) { return c ? c->device : nullptr; }
+OlQueue hcContextQueue(HcContext c) { return c ? c->queue : nullptr; }
+void *hcContextStream(HcContext c) {
+  return c ? olxQueueNativeHandle(c->queue) : nullptr;
+}
+int hcSynchronize(HcContext c) { return c ? olSyncQueue(c->queue) : 1; }
+const char *hcLastError(HcContext c) { return c ? c->lastError.c_str() : ""; }
+long long hcLaunchCount(HcContext c) { return c ? c->launches : 0; }
+
+int hcKernelStatus(HcContext c, int *statusRet) {
+  if (!c || !statusRet)
+    return 1;
+  int value = 0;
+  if (olxMemcpyDtoH(c->queue, &value, c->statusWord, sizeof(int)) ||
+      olSyncQueue(c->queue))
+    return c->fail("reading the kernel status word failed: %s",
+                   c->lastError.c_str());
+  if (value != 0 && (olxMemsetD8(c->queue, c->statusWord, 0, sizeof(int)) ||
+                     olSyncQueue(c->queue)))
+    return 1;
+  *statusRet = value;
+  return 0;
+}
+
+int hcSetOption(HcContext c, const char *name, long long value) {
+  if (!c || !name)
+    return 1;
+  if (std::strcmp(name, "gemm_variant") == 0 && value >= 0 && value <= 3) {
+    c->gemmVariant = value;
+    return 0;
+  }
+  return c->fail("Invalid option: %s = %lld", name, value);
+}
+
+// ---- copy -----------------------------------------------------------------------
+int hcCopy2D(HcContext c, const void *src, void *dst, long long rows,
+             long long cols, long long srcPitch, long long dstPitch,
+             int elemBytes) {
+  if (!c)
+    return 1;
+  if (elemBytes != 1 && elemBytes != 2 && elemBytes != 4 && elemBytes != 8)
+    return c->fail("hcCopy2D: unsupported element size %d", elemBytes);
+  if (rows < 0 || cols < 0 || srcPitch < cols || dstPitch < cols)
+    return c->fail("hcCopy2D: invalid shape %lld x %lld (pitch %lld -> %lld)",
+                   rows, cols, srcPitch, dstPitch);
+  if (rows == 0 || cols == 0)
+    return 0;
+  if (!src || !dst)
+    return c->fail("hcCopy2D: null buffer");
+  long long rowBytes = cols * elemBytes;
+  long long sp = srcPitch * elemBytes, dp = dstPitch * elemBytes;
+  // A fully contiguous matrix is one long row.
+  if (sp == rowBytes && dp == rowBytes) {
+    rowBytes *= rows;
+    sp = dp = rowBytes;
+    rows = 1;
+  }
+  int packet = 16;
+  while (packet > elemBytes &&
+         (rowBytes % packet || sp % packet || dp % packet ||
+          !aligned(src, packet) || !aligned(dst, packet)))
+    packet >>= 1;
+  long long perRow = rowBytes / packet;
+  long long gx = std::min<long long>(ceilDiv(perRow, 256 * 4), c->smCount * 8);
+  gx = std::max<long long>(gx, 1);
+  long long gy = std::min<long long>(rows, std::max<long long>(1, c->smCount * 8 / gx));
+  void *args[] = {&src, &dst, &rows, &rowBytes, &sp, &dp, &packet};
+  return c->launch("hc_copy2d", size_t(gx), size_t(gy), 1, 256, args, 7, 0);
+}
+
+// ---- softmax --------------------------------------------------------------------
+int hcSoftmaxRows(HcContext c, const void *x, void *y, long long rows,
+                  long long cols, long long xPitch, long long yPitch,
+                  int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcSoftmaxRows: unsupported dtype %d", dtype);
+  if (rows < 0 || cols < 0 || xPitch < cols || yPitch < cols)
+    return c->fail("hcSoftmaxRows: invalid shape %lld x %lld", rows, cols);
+  if (rows == 0 || cols == 0)
+    return 0;
+  if (!x || !y)
+    return c->fail("hcSoftmaxRows: null buffer");
+  const bool vecOk = dtype == HC_F32 && cols % 4 == 0 && cols <= 4096 &&
+                     xPitch % 4 == 0 && yPitch % 4 == 0 && aligned(x, 16) &&
+                     aligned(y, 16);
+  if (vecOk) {
+    int v = 1;
+    while (128 * v < cols)
+      v <<= 1;
+    // Resident 128-thread CTAs per SM, from each variant's __launch_bounds__.
+    const int residency = v <= 8 ? 8 : (v == 16 ? 5 : 3);
+    char name[48];
+    snprintf(name, sizeof(name), "hc_softmax_rows_f32_w%d", v);
+    long long grid = std::min<long long>(ceilDiv(rows, 4), c->smCount * residency);
+    int icols = int(cols);
+    void *args[] = {&x, &y, &rows, &icols, &xPitch, &yPitch};
+    return c->launch(name, size_t(grid), 1, 1, 128, args, 6, 0);
+  }
+  const size_t elem = dtype == HC_F32 ? 4 : 8;
+  long long cacheElems = cols;
+  size_t smem = size_t(roundUp(cols * (long long)elem, 16));
+  if (smem > 160 * 1024) { // does not fit: the kernel re-reads the row instead
+    smem = 0;
+    cacheElems = 0;
+  }
+  long long grid = std::min<long long>(rows, c->smCount * 8);
+  void *args[] = {&x, &y, &rows, &cols, &xPitch, &yPitch, &cacheElems};
+  return c->launch(dtype == HC_F32 ? "hc_softmax_rows_generic_f32"
+                                   : "hc_softmax_rows_generic_f64",
+                   size_t(grid), 1, 1, 256, args, 7, smem);
+}
+
+// ---- reductions -----------------------------------------------------------------
+int hcReduceRows(HcContext c, const void *x, void *sumOut, void *maxOut,
+                 long long rows, long long cols, long long pitch, int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcReduceRows: unsupported dtype %d", dtype);
+  if (rows < 0 || cols < 0 || pitch < cols)
+    return c->fail("hcReduceRows: invalid shape %lld x %lld", rows, cols);
+  if (rows == 0 || (!sumOut && !maxOut))
+    return 0;
+  if (!x && cols > 0)
+    return c->fail("hcReduceRows: null buffer");
+  int vec = dtype == HC_F32 && cols % 4 == 0 && pitch % 4 == 0 && aligned(x, 16);
+  const bool f32 = dtype == HC_F32;
+  void *args[] = {&x, &sumOut, &maxOut, &rows, &cols, &pitch, &vec};
+  if (rows >= c->smCount * 8) {
+    long long grid = std::min<long long>(ceilDiv(rows, 8), c->smCount * 8);
+    return c->launch(f32 ? "hc_reduce_rows_warp_f32" : "hc_reduce_rows_warp_f64",
+                     size_t(grid), 1, 1, 256, args, 7, 0);
+  }
+  long long grid = std::min<long long>(rows, c->smCount * 8);
+  return c->launch(f32 ? "hc_reduce_rows_block_f32" : "hc_reduce_rows_block_f64",
+                   size_t(grid), 1, 1, 256, args, 7, 0);
+}
+
+// ---- GEMMs ----------------------------------------------------------------------
+static int checkGemmShape(HcContext c, const char *who, const void *a,
+                          const void *b, const void *out, long long M,
+                          long long N, long long K, long long lda,
+                          long long ldb, long long ldc) {
+  if (M < 0 || N < 0 || K < 0 || lda < K || ldb < N || ldc < N)
+    return c->fail("%s: invalid shape M=%lld N=%lld K=%lld (lda %lld ldb %lld "
+                   "ldc %lld)",
+                   who, M, N, K, lda, ldb, ldc);
+  if (M > 0 && N > 0 && (!out || (K > 0 && (!a || !b))))
+    return c->fail("%s: null buffer", who);
+  return 0;
+}
+
+int hcGemmTiled(HcContext c, const void *a, const void *b, void *out,
+                long long M, long long N, long long K, long long lda,
+                long long ldb, long long ldc, int dtype) {
+  if (!c)
+    return 1;
+  const char *name = dtype == HC_F32    ? "hc_gemm_tiled_f32"
+                     : dtype == HC_F64  ? "hc_gemm_tiled_f64"
+                     : dtype == HC_BF16 ? "hc_gemm_tiled_bf16"
+                                        : nullptr;
+  if (!name)
+    return c->fail("hcGemmTiled: unsupported dtype %d", dtype);
+  if (checkGemmShape(c, "hcGemmTiled", a, b, out, M, N, K, lda, ldb, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  void *args[] = {&a, &b, &out, &M, &N, &K, &lda, &ldb, &ldc};
+  return c->launch(name, size_t(ceilDiv(N, 64)), size_t(ceilDiv(M, 64)), 1, 256,
+                   args, 9, 0);
+}
+
+// Launches one of the tcgen05 kernels; `b` is bf16 [K, N].
+static int launchUmma(HcContext c, const void *a, const void *b,
+                      const float *scale, void *out, long long M, long long N,
+                      long long K, long long lda, long long ldb, long long ldc,
+                      bool pair) {
+  alignas(64) CUtensorMap mapA, mapB;
+  if (olxEncodeTensorMap2D(c->device, &mapA, /*bf16*/ 0, a, size_t(M), size_t(K),
+                           size_t(lda) * 2, kUmmaBM, kUmmaBK, 128) ||
+      olxEncodeTensorMap2D(c->device, &mapB, /*bf16*/ 0, b, size_t(K), size_t(N),
+                           size_t(ldb) * 2, kUmmaBK, 64, 128))
+    return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
+  const int tileM = pair ? 2 * kUmmaBM : kUmmaBM;
+  int tilesM = int(ceilDiv(M, tileM)), tilesN = int(ceilDiv(N, kUmmaBN));
+  // Tiles that run concurrently should form a compact block of the output so
+  // that the A and B panels they share stay in L2.
+  int bandM = pair ? 8 : 16;
+  int vecStore = aligned(out, 16) && ldc % 8 == 0;
+  long long tiles = (long long)tilesM * tilesN;
+  long long grid = pair ? 2 * std::min<long long>(tiles, c->smCount / 2)
+                        : std::min<long long>(tiles, c->smCount);
+  const char *name = pair ? (scale ? "hc_gemm_bf16_umma_pair_scaled"
+                                   : "hc_gemm_bf16_umma_pair")
+                          : (scale ? "hc_gemm_bf16_umma_scaled"
+                                   : "hc_gemm_bf16_umma");
+  void *args[] = {&mapA,   &mapB,   &out,   &scale,    &M,           &N, &K,
+                  &ldc,    &tilesM, &tilesN, &bandM,   &vecStore, &c->statusWord};
+  return c->launch(name, size_t(grid), 1, 1, kUmmaThreads, args, 13,
+                   kUmmaSmemBytes);
+}
+
+static bool ummaEligible(HcContext c, const void *a, const void *b,
+                         long long K, long long lda, long long ldb) {
+  return c->ccMajor == 10 && K > 0 && lda % 8 == 0 && ldb % 8 == 0 &&
+         aligned(a, 16) && aligned(b, 16);
+}
+
+int hcGemmBf16(HcContext c, const void *a, const void *b, void *out,
+               long long M, long long N, long long K, long long lda,
+               long long ldb, long long ldc) {
+  if (!c)
+    return 1;
+  if (checkGemmShape(c, "hcGemmBf16", a, b, out, M, N, K, lda, ldb, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  if (c->gemmVariant == 3 || !ummaEligible(c, a, b, K, lda, ldb))
+    return hcGemmTiled(c, a, b, out, M, N, K, lda, ldb, ldc, HC_BF16);
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
+  return launchUmma(c, a, b, nullptr, out, M, N, K, lda, ldb, ldc, pair);
+}
+
+size_t hcGemmW8A16WorkspaceBytes(long long N, long long K) {
+  if (N <= 0 || K <= 0)
+    return 0;
+  return size_t(roundUp(N, 16)) * size_t(K) * 2;
+}
+
+int hcDequantW8(HcContext c, const void *w, void *out, long long rows,
+                long long cols, long long wPitch, long long outPitch) {
+  if (!c)
+    return 1;
+  if (rows < 0 || cols < 0 || wPitch < cols || outPitch < cols)
+    return c->fail("hcDequantW8: invalid shape %lld x %lld", rows, cols);
+  if (rows == 0 || cols == 0)
+    return 0;
+  if (!w || !out)
+    return c->fail("hcDequantW8: null buffer");
+  int vec = cols % 16 == 0 && wPitch % 16 == 0 && outPitch % 16 == 0 &&
+            aligned(w, 16) && aligned(out, 16);
+  long long perRow = vec ? cols / 16 : cols;
+  long long gx = std::max<long long>(
+      1, std::min<long long>(ceilDiv(perRow, 256), c->smCount * 8));
+  long long gy = std::min<long long>(rows, std::max<long long>(1, c->smCount * 16 / gx));
+  void *args[] = {&w, &out, &rows, &cols, &wPitch, &outPitch, &vec};
+  return c->launch("hc_dequant_w8_bf16", size_t(gx), size_t(gy), 1, 256, args, 7,
+                   0);
+}
+
+int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
+                void *out, void *workspace, size_t workspaceBytes, long long M,
+                long long N, long long K, long long lda, long long ldw,
+                long long ldc) {
+  if (!c)
+    return 1;
+  if (checkGemmShape(c, "hcGemmW8A16", a, w, out, M, N, K, lda, ldw, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  if (!scale)
+    return c->fail("hcGemmW8A16: null scale");
+  const long long wsPitch = roundUp(N, 16);
+  if (c->gemmVariant == 3 || !ummaEligible(c, a, workspace, K, lda, wsPitch)) {
+    void *args[] = {&a, &w, &scale, &out, &M, &N, &K, &lda, &ldw, &ldc};
+    return c->launch("hc_gemm_tiled_w8a16", size_t(ceilDiv(N, 64)),
+                     size_t(ceilDiv(M, 64)), 1, 256, args, 10, 0);
+  }
+  if (!workspace || workspaceBytes < hcGemmW8A16WorkspaceBytes(N, K))
+    return c->fail("hcGemmW8A16: workspace of %zu bytes is too small, need %zu",
+                   workspaceBytes, hcGemmW8A16WorkspaceBytes(N, K));
+  if (hcDequantW8(c, w, workspace, K, N, ldw, wsPitch))
+    return 1;
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
+  return launchUmma(c, a, workspace, scale, out, M, N, K, lda, wsPitch, ldc, pair);
+}
+
+} // extern "C"

@@ -1,0 +1,125 @@
+/* C-ABI of libhc-b200-kernels.so: the precompiled sm_100a kernel images and
+ * one launch entry point per workload.
+ *
+ * In the reference a kernel reaches the GPU as a binary blob that JIT-compiled
+ * host code hands to hcgpuGetKernel / hcgpuLaunchKernel
+ * (python/cpp/py-runtime/src/GpuRuntime.cpp:26-69) and from there to the ol*
+ * ABI (gpu-runtime/common/include/offload_api.h:29-63).  This library takes
+ * the place of that JIT-compiled host code: it owns the blobs (now cubins
+ * built ahead of time), picks the kernel variant for the argument shapes,
+ * packs the kernel parameters and launches through the same ol* ABI of the
+ * loader (olCreateModule / olGetKernel / olLaunchKernel).  It never computes
+ * on the host and has no fallback when no GPU is present.
+ *
+ * All pointers are device pointers unless stated otherwise; pitches are in
+ * elements; every launch is asynchronous on the context's queue.  Functions
+ * returning int return 0 on success; on failure they return nonzero, call the
+ * context's OlErrorCallback and keep the text for hcLastError.
+ */
+#pragma once
+
+#include "offload_api.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HC_B200_API __attribute__((visibility("default")))
+
+typedef struct HcContextImpl *HcContext;
+
+/* Element types of the workload entry points. */
+enum HcDType {
+  HC_F32 = 0,
+  HC_F64 = 1,
+  HC_BF16 = 2,
+  HC_I8 = 3
+};
+
+/* ---- kernel images -------------------------------------------------------
+ * The blobs a caller would pass to olCreateModule / hcgpuGetKernel, replacing
+ * the output of the reference's gpu-module-to-binary step
+ * (mlir/lib/Pipelines/BackendPipeline.cpp:55-61). */
+HC_B200_API int hcImageCount(void);
+HC_B200_API const char *hcImageName(int index);
+HC_B200_API const void *hcImageData(int index, size_t *lenRet);
+/* Image that defines `kernelName`, or -1. */
+HC_B200_API int hcImageOfKernel(const char *kernelName);
+
+/* ---- context: device + queue + loaded images ------------------------------
+ * Plays the role of the process-global device/queue pair of the reference's
+ * py-runtime (GpuRuntime.cpp:23-39), but one per device description so that
+ * several GPUs can be driven from one process. */
+HC_B200_API HcContext hcCreateContext(const char *deviceDesc,
+                                      OlErrorCallback errCallback, void *ctx);
+HC_B200_API void hcReleaseContext(HcContext c);
+HC_B200_API OlDevice hcContextDevice(HcContext c);
+HC_B200_API OlQueue hcContextQueue(HcContext c);
+/* The CUstream behind the context's queue. */
+HC_B200_API void *hcContextStream(HcContext c);
+HC_B200_API int hcSynchronize(HcContext c);
+HC_B200_API const char *hcLastError(HcContext c);
+/* Kernel launches issued through this context so far. */
+HC_B200_API long long hcLaunchCount(HcContext c);
+/* Synchronizes, then returns in *statusRet the status word the tensor-core
+ * kernels write when one of their bounded waits gives up (0 = none did) and
+ * clears it. */
+HC_B200_API int hcKernelStatus(HcContext c, int *statusRet);
+/* Tuning and test switches.  "gemm_variant": 0 = automatic, 1 = one CTA per
+ * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel. */
+HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
+
+/* ---- workloads -------------------------------------------------------------
+ * 2-D copy; the reference's compiled copy kernels
+ * (python/hckernel/tests/test_e2e.py:57-136). */
+HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
+                         long long rows, long long cols, long long srcPitch,
+                         long long dstPitch, int elemBytes);
+
+/* Row softmax over the last axis, HC_F32 or HC_F64
+ * (python/hckernel/tests/test_examples.py:304-321). */
+HC_B200_API int hcSoftmaxRows(HcContext c, const void *x, void *y,
+                              long long rows, long long cols, long long xPitch,
+                              long long yPitch, int dtype);
+
+/* Last-axis sum and/or max (either output may be NULL), HC_F32 or HC_F64
+ * (python/hckernel/tests/test_examples.py:31-71 for the sum form). */
+HC_B200_API int hcReduceRows(HcContext c, const void *x, void *sumOut,
+                             void *maxOut, long long rows, long long cols,
+                             long long pitch, int dtype);
+
+/* C[M,N] = A[M,K] @ B[K,N] on the CUDA cores; HC_F32, HC_F64, or HC_BF16
+ * (bf16 in and out, fp32 accumulation)
+ * (python/hckernel/tests/test_examples.py:74-165). */
+HC_B200_API int hcGemmTiled(HcContext c, const void *a, const void *b, void *cOut,
+                            long long M, long long N, long long K,
+                            long long lda, long long ldb, long long ldc,
+                            int dtype);
+
+/* bf16 GEMM with fp32 accumulation on the tensor cores (tcgen05); falls back
+ * to the bf16 tiled kernel for layouts TMA cannot describe (a pitch that is
+ * not a multiple of 8 elements or a base that is not 16-byte aligned). */
+HC_B200_API int hcGemmBf16(HcContext c, const void *a, const void *b, void *cOut,
+                           long long M, long long N, long long K,
+                           long long lda, long long ldb, long long ldc);
+
+/* int8 weight-only dequant GEMM:
+ *   out[m,n] = bf16( scale[n] * sum_k a[m,k] * float(w[k,n]) )
+ * a bf16 [M,K], w int8 [K,N], scale fp32 [N], out bf16 [M,N].  `workspace`
+ * must hold hcGemmW8A16WorkspaceBytes(N, K) bytes of device memory (the
+ * weights converted to bf16); it is written by every call. */
+HC_B200_API size_t hcGemmW8A16WorkspaceBytes(long long N, long long K);
+HC_B200_API int hcGemmW8A16(HcContext c, const void *a, const void *w,
+                            const float *scale, void *out, void *workspace,
+                            size_t workspaceBytes, long long M, long long N,
+                            long long K, long long lda, long long ldw,
+                            long long ldc);
+
+/* The conversion step alone: out[k,n] = bf16(w[k,n]). */
+HC_B200_API int hcDequantW8(HcContext c, const void *w, void *out,
+                            long long rows, long long cols, long long wPitch,
+                            long long outPitch);
+
+#ifdef __cplusplus
+}
+#endif

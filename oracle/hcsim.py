@@ -1,0 +1,129 @@
+"""CPU oracle: a NumPy restatement of the reference's kernel simulator.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the ``hc_b200`` package imports this
+module; it exists so that tests, ``__graft_entry__.smoke()`` and the CPU-baseline
+leg of ``bench.py`` can check (and time) what the reference computes.  The
+product path has no CPU fallback.
+
+What is restated, and from where (paths are relative to the reference tree):
+
+* work-group enumeration - ``ceil(work/group)`` groups per dimension, visited in
+  row-major order, each seeing ``work_offset = group_id * group_shape``
+  (python/hckernel/kernel_sim.py:13-14, 159-163;
+  python/hckernel/kernel_api.py:293-295);
+* ``group.load`` - a zero-filled tile of the requested shape, the in-bounds part
+  copied from the array view, a mask marking which elements are real
+  (python/hckernel/kernel_api.py:297-316);
+* ``group.store`` - the tile clipped to the destination view; with a masked
+  source only the valid elements are written
+  (python/hckernel/kernel_api.py:318-342);
+* tile allocators ``zeros``/``full`` (python/hckernel/kernel_api.py:347-369,
+  433-434);
+* masked reductions that ignore padding (numpy.ma behaviour reached through
+  python/hckernel/kernel_api.py:150-151).
+
+Parity pin: ``tests/golden/make_golden.py`` runs the reference simulator itself
+(imported from the reference tree) and this restatement on the same inputs and
+stores the reference's outputs; ``tests/test_oracle_golden.py`` then checks this
+module against those stored outputs bit for bit, including the reference's own
+test vectors for dot, softmax and reduction
+(python/hckernel/tests/test_examples.py:31-165, 304-335).  The row-max, bf16
+and int8-dequant workloads have no test in the reference; their golden outputs
+come from the same workload written in the reference's DSL and run on the
+reference simulator, so they pin this restatement to the reference's tile
+semantics, not to an independent known answer.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from itertools import product
+
+import numpy as np
+
+
+def ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def iter_groups(work_shape, group_shape):
+    """Yield ``(group_id, work_offset)`` in the simulator's order.
+
+    python/hckernel/kernel_sim.py:13-14 (group count) and :159-163 (row-major
+    ``product`` over the group ranges); offsets as in
+    python/hckernel/kernel_api.py:293-295.
+    """
+    work_shape = tuple(np.atleast_1d(work_shape).tolist())
+    group_shape = tuple(np.atleast_1d(group_shape).tolist())
+    if len(work_shape) != len(group_shape):
+        raise ValueError("work_shape and group_shape differ in rank")
+    counts = [ceil_div(w, g) for w, g in zip(work_shape, group_shape)]
+    for gid in product(*(range(c) for c in counts)):
+        yield gid, tuple(i * g for i, g in zip(gid, group_shape))
+
+
+@dataclass
+class Tile:
+    """A work-group tile: values plus a validity mask (True = real element)."""
+
+    data: np.ndarray
+    valid: np.ndarray
+
+    @property
+    def shape(self):
+        return self.data.shape
+
+
+def load_tile(view: np.ndarray, shape) -> Tile:
+    """``group.load(view, shape)``: python/hckernel/kernel_api.py:297-316.
+
+    ``view`` is the array sliced so that it starts at the tile origin; the tile
+    is zero-filled (``_get_uninit_value`` returns 0, kernel_api.py:222-223) and
+    only the part that exists in ``view`` is copied and marked valid.
+    """
+    shape = tuple(np.atleast_1d(shape).tolist())
+    data = np.zeros(shape, dtype=view.dtype)
+    valid = np.zeros(shape, dtype=bool)
+    inside = tuple(slice(0, min(have, want)) for have, want in zip(view.shape, shape))
+    data[inside] = view[inside]
+    valid[inside] = True
+    return Tile(data, valid)
+
+
+def alloc_tile(shape, dtype, fill=0) -> Tile:
+    """``group.zeros/ones/full``: every element valid
+    (python/hckernel/kernel_api.py:347-369, 433-434)."""
+    shape = tuple(np.atleast_1d(shape).tolist())
+    return Tile(np.full(shape, fill, dtype=dtype), np.ones(shape, dtype=bool))
+
+
+def store_tile(dst_view: np.ndarray, src) -> None:
+    """``group.store(dst_view, src)``: python/hckernel/kernel_api.py:318-342.
+
+    The source is clipped to the destination view.  A :class:`Tile` writes only
+    its valid elements (the ``np.where(src.mask, ...)`` branch, :339-340); a
+    plain array is assigned as is (:341-342), which is what reaches ``store``
+    after ``np.dot`` / ``np.exp`` / a reduction turned the tile into an
+    ordinary (masked) NumPy array.
+    """
+    if isinstance(src, Tile):
+        region = tuple(slice(0, min(a, b)) for a, b in zip(src.shape, dst_view.shape))
+        dst_view[region] = np.where(src.valid[region], src.data[region], dst_view[region])
+    else:
+        src = np.asarray(src)
+        region = tuple(slice(0, min(a, b)) for a, b in zip(src.shape, dst_view.shape))
+        dst_view[region] = src[region]
+
+
+def valid_rows(tile: Tile) -> int:
+    """Number of leading rows of a row-block tile that exist in the array.
+
+    For tiles loaded as whole rows (no column padding) the mask is a prefix of
+    rows; masked reductions over the last axis (numpy.ma ``max``/``sum`` reached
+    through kernel_api.py:150-151) then equal plain reductions over these rows,
+    and rows past the end are dropped again when the result is stored.
+    """
+    if tile.valid.ndim == 1:
+        return int(tile.valid.sum())
+    rows = tile.valid.all(axis=tuple(range(1, tile.valid.ndim)))
+    return int(rows.sum())

@@ -1,0 +1,240 @@
+"""CPU oracle: the workload kernels, restated on top of :mod:`oracle.hcsim`.
+
+TEST INFRASTRUCTURE ONLY - see the header of ``oracle/hcsim.py``.
+
+Each function follows one kernel body of the reference (or, where the
+reference has none, the same computation written with the reference's
+primitives) group by group, so tiling and edge handling are the reference's.
+bf16 is represented the way the reference would have to represent it (NumPy
+has no bf16): float32 arrays whose values are bf16-representable, fp32
+arithmetic, and a final round-to-nearest-even to bf16.
+"""
+
+from __future__ import annotations
+
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+from .hcsim import alloc_tile, ceil_div, iter_groups, load_tile, store_tile, valid_rows
+
+
+# ---- bf16 helpers ------------------------------------------------------------
+def round_to_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 -> nearest-even bf16, returned as float32 holding bf16 values."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    bits = x.view(np.uint32).astype(np.uint64)
+    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+    out = rounded.astype(np.uint32).view(np.float32)
+    nan = np.isnan(x)
+    if nan.any():
+        out = out.copy()
+        out[nan] = np.nan
+    return out.reshape(x.shape)
+
+
+def bf16_bits(x: np.ndarray) -> np.ndarray:
+    """uint16 bit patterns of float32 values that are already bf16-exact."""
+    return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def bf16_from_bits(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+# ---- copy --------------------------------------------------------------------
+def copy2d(src: np.ndarray, dst: np.ndarray, group_shape=(1, 64), unroll: int = 1) -> None:
+    """The compiled path's copy kernels, run tile by tile.
+
+    python/hckernel/tests/test_e2e.py:66-70 (unroll 1) and :95-100 (each group
+    covers ``group_shape[1] * V`` columns); work shape (W, ceil(H / V)).
+    """
+    w, h = src.shape
+    for _, (x, y) in iter_groups((w, ceil_div(h, unroll)), group_shape):
+        tile = load_tile(src[x:, y * unroll :], (group_shape[0], group_shape[1] * unroll))
+        store_tile(dst[x:, y * unroll :], tile)
+
+
+# ---- GEMM --------------------------------------------------------------------
+def gemm_kblocked(a, b, out, group_shape=(64, 64), kb: int = 16, mi: int = 1, ni: int = 1) -> None:
+    """K-blocked tiled GEMM: python/hckernel/tests/test_examples.py:88-111.
+
+    Work shape (ceil(M/MI), ceil(N/NI)); a group owns an (gm*MI, gn*NI) output
+    tile, accumulates ``np.dot`` of (m_block, KB) x (KB, n_block) tiles over
+    ceil(K/KB) steps into a zero tile of the output dtype, then stores it.
+    """
+    m, k = a.shape
+    n = b.shape[1]
+    gm, gn = group_shape
+    m_block, n_block = gm * mi, gn * ni
+    steps = ceil_div(k, kb)
+    for _, (wm, wn) in iter_groups((ceil_div(m, mi), ceil_div(n, ni)), group_shape):
+        m0, n0 = wm * mi, wn * ni
+        acc = alloc_tile((m_block, n_block), out.dtype)
+        for step in range(steps):
+            k0 = step * kb
+            a_tile = load_tile(a[m0:, k0:], (m_block, kb))
+            b_tile = load_tile(b[k0:, n0:], (kb, n_block))
+            # `r += np.dot(...)` (kernel_api.py:142-145): the product is a plain
+            # array, so every element of the accumulator is updated.
+            acc.data[...] = acc.data + np.dot(a_tile.data, b_tile.data)
+        store_tile(out[m0:, n0:], acc)
+
+
+def gemm_fullk(a, b, out, group_shape=(64, 64), mi: int = 1, ni: int = 1, acc_dtype=None) -> None:
+    """Full-K tiled GEMM: python/hckernel/tests/test_examples.py:136-155."""
+    m, k = a.shape
+    n = b.shape[1]
+    gm, gn = group_shape
+    m_block, n_block = gm * mi, gn * ni
+    acc_dtype = acc_dtype or out.dtype
+    for _, (wm, wn) in iter_groups((ceil_div(m, mi), ceil_div(n, ni)), group_shape):
+        m0, n0 = wm * mi, wn * ni
+        acc = alloc_tile((m_block, n_block), acc_dtype)
+        a_tile = load_tile(a[m0:, :], (m_block, k))
+        b_tile = load_tile(b[:, n0:], (k, n_block))
+        acc.data[...] = acc.data + np.dot(a_tile.data, b_tile.data)
+        store_tile(out[m0:, n0:], acc)
+
+
+def gemm_bf16(a, b, out, group_shape=(256, 256)) -> None:
+    """bf16 GEMM, fp32 accumulation, bf16-rounded output.
+
+    The full-K kernel above with float32 arrays holding bf16 values; the
+    rounding happens where the reference would cast on store.  ``out`` is
+    float32 and receives bf16-representable values.
+    """
+    tmp = np.zeros(out.shape, dtype=np.float32)
+    gemm_fullk(a, b, tmp, group_shape, acc_dtype=np.float32)
+    out[...] = round_to_bf16(tmp)
+
+
+def gemm_w8a16(a, w, scale, out, group_shape=(256, 256)) -> None:
+    """int8 weight-only dequant GEMM with the reference's primitives.
+
+    Per group: ``r = np.dot(a_tile, w_tile.astype(float32)) * scale_tile``,
+    stored with a cast to bf16.  ``a`` is float32 holding bf16 values, ``w``
+    int8 [K, N] (the reference's ``b: Buffer[K, N]`` convention,
+    python/hckernel/tests/test_examples.py:91), ``scale`` float32 [N].
+    """
+    m, k = a.shape
+    n = w.shape[1]
+    gm, gn = group_shape
+    tmp = np.zeros(out.shape, dtype=np.float32)
+    for _, (m0, n0) in iter_groups((m, n), group_shape):
+        a_tile = load_tile(a[m0:, :], (gm, k))
+        w_tile = load_tile(w[:, n0:], (k, gn))
+        s_tile = load_tile(scale[n0:], (gn,))
+        r = np.dot(a_tile.data, w_tile.data.astype(np.float32)) * s_tile.data
+        store_tile(tmp[m0:, n0:], r)
+    out[...] = round_to_bf16(tmp)
+
+
+# ---- softmax -----------------------------------------------------------------
+def softmax_rows(a, out, group_rows: int = 8, mi: int = 1) -> None:
+    """Row softmax: python/hckernel/tests/test_examples.py:312-321.
+
+    A group loads ``group_rows * MI`` whole rows, subtracts the row maximum,
+    exponentiates and divides by the row sum; rows past the end of the array
+    are padding and are dropped by the clipped store.
+    """
+    m, n = a.shape
+    m_block = group_rows * mi
+    for _, (wm,) in iter_groups((ceil_div(m, mi),), (group_rows,)):
+        m0 = wm * mi
+        tile = load_tile(a[m0:, :], (m_block, n))
+        rows = valid_rows(tile)
+        x = tile.data[:rows]
+        e = np.exp(x - x.max(axis=1, keepdims=True))
+        store_tile(out[m0:, :], e / e.sum(axis=1, keepdims=True))
+
+
+# ---- reductions ----------------------------------------------------------------
+def reduce_sum_all(a, result, group_size: int = 8, n_per_item: int = 2) -> None:
+    """Whole-array sum: python/hckernel/tests/test_examples.py:36-40.
+
+    Each group loads ``group_size * N`` elements (zero padded) and adds the
+    tile's sum to ``result[0]`` (``atomic_ref`` is the identity on the
+    simulator, python/hckernel/kernel_api.py:450-451).
+    """
+    ws = a.shape[0]
+    for _, (off,) in iter_groups((ceil_div(ws, n_per_item),), (group_size,)):
+        tile = load_tile(a[off * n_per_item :], (group_size * n_per_item,))
+        result[0] += tile.data[tile.valid].sum()
+
+
+def reduce_rows(x, sum_out=None, max_out=None, group_rows: int = 256) -> None:
+    """Last-axis sum and max, written with the reference's primitives:
+
+    ``v = group.load(x[m0:, :], (gm, N)); group.store(s[m0:], v.sum(axis=1));
+    group.store(mx[m0:], v.max(axis=1))`` - masked reductions ignore padding
+    rows, and the clipped store drops them.
+    """
+    m, n = x.shape
+    for _, (m0,) in iter_groups((m,), (group_rows,)):
+        tile = load_tile(x[m0:, :], (group_rows, n))
+        rows = valid_rows(tile)
+        v = tile.data[:rows]
+        if sum_out is not None:
+            store_tile(sum_out[m0:], v.sum(axis=1))
+        if max_out is not None:
+            store_tile(max_out[m0:], v.max(axis=1))
+
+
+# ---- seeded inputs of the benchmark configurations -----------------------------
+def make_inputs(config: str, scale_rows: int | None = None, shape=None):
+    """Seeded synthetic inputs of the five benchmark configurations.
+
+    ``config`` is one of ``gemm_f32``, ``softmax``, ``reduce``, ``gemm_bf16``,
+    ``gemm_w8a16``; seeds, distributions and draw order are fixed (NumPy PCG64
+    ``default_rng(seed)``), so every process regenerates the same arrays.
+    ``shape`` overrides the full-size shape for reduced-size parity cases.
+    """
+    if config == "gemm_f32":
+        m, n, k = shape or (256, 256, 256)
+        rng = np.random.default_rng(0)
+        a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+        b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+        return a, b
+    if config == "softmax":
+        m, n = shape or (32768, 4096)
+        return (np.random.default_rng(1).standard_normal((m, n), dtype=np.float32),)
+    if config == "reduce":
+        m, n = shape or (65536, 8192)
+        rng = np.random.default_rng(2)
+        # Drawn in float32 directly: the full-size float64 draw would need 4 GiB.
+        return ((rng.random((m, n), dtype=np.float32) * np.float32(20.0) - np.float32(10.0)),)
+    if config == "gemm_bf16":
+        m, n, k = shape or (8192, 8192, 8192)
+        rng = np.random.default_rng(3)
+        a = round_to_bf16((rng.standard_normal((m, k), dtype=np.float32) * np.float32(0.02)))
+        b = round_to_bf16((rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.02)))
+        return a, b
+    if config == "gemm_w8a16":
+        m, n, k = shape or (4096, 8192, 8192)
+        rng = np.random.default_rng(4)
+        a = round_to_bf16(rng.standard_normal((m, k), dtype=np.float32))
+        w = rng.integers(-127, 128, (k, n), dtype=np.int8)
+        s = rng.uniform(0.001, 0.02, n).astype(np.float32)
+        return a, w, s
+    raise ValueError(f"unknown config {config!r}")
+
+
+# ---- multi-threaded drivers for the timed CPU baseline ---------------------------
+def run_row_groups_parallel(fn, m: int, group_rows: int, threads: int) -> None:
+    """Run ``fn(row_begin, row_end)`` over row blocks on a thread pool.
+
+    The simulator visits groups one after another; groups of these workloads
+    are independent, so the timed CPU baseline may spread them over the host
+    cores (NumPy releases the GIL inside its loops).  ``row_begin`` is always a
+    multiple of ``group_rows`` so the tiling is unchanged.
+    """
+    groups = ceil_div(m, group_rows)
+    per = ceil_div(groups, max(1, threads)) * group_rows
+    spans = [(r0, min(m, r0 + per)) for r0 in range(0, m, per)]
+    if threads <= 1 or len(spans) == 1:
+        for r0, r1 in spans:
+            fn(r0, r1)
+        return
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        list(pool.map(lambda s: fn(*s), spans))
