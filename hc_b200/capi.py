@@ -61,6 +61,10 @@ OLX_PROTOTYPES = {
         C.c_int,
         [_vp, _vp, C.c_int, _vp, _sz, _sz, _sz, C.c_uint, C.c_uint, C.c_int],
     ),
+    "olxMaxActiveClusters": (
+        C.c_int,
+        [_vp, _vp, C.c_uint, _sz, C.c_uint, C.POINTER(C.c_int)],
+    ),
 }
 LOADER_EXTRA_PROTOTYPES = {
     "setGPULoaderSearchPaths": (None, [C.POINTER(C.c_char_p), _sz]),

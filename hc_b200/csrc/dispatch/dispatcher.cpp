@@ -1,0 +1,266 @@
+// hc_b200._native._dispatcher: the Python entry of the launch path.
+//
+// In the reference a call of a @kernel-decorated function lands in a nanobind
+// Dispatcher that checks the arguments, builds a specialization key, JIT
+// compiles on a miss and calls the compiled host wrapper
+// (python/cpp/compiler/src/DispatcherBase.cpp:250-280, 542-585;
+// python/cpp/compiler/src/Dispatcher.cpp:20-42).  The JIT is gone here, so what
+// remains is argument checking and the call into the precompiled kernels:
+// every function below reads its array arguments (array_arg.hpp), validates
+// device, element type, rank and layout, and forwards to one entry point of
+// libhc-b200-kernels.so.  Validation errors raise ValueError/TypeError, launch
+// errors RuntimeError with the library's own message - never abort().
+#include "array_arg.hpp"
+#include "hc_b200_kernels.h"
+
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <charconv>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace py = pybind11;
+using hc::ArrayArg;
+using hc::ElemKind;
+
+namespace {
+
+class Context {
+public:
+  explicit Context(const std::string &desc) : description(desc) {
+    handle = hcCreateContext(desc.c_str(), &Context::onMessage, this);
+    if (!handle)
+      throw std::runtime_error("cannot open device '" + desc + "': " +
+                               (errors.empty() ? "no detail" : errors));
+    auto colon = desc.find(':');
+    if (colon != std::string::npos)
+      std::from_chars(desc.data() + colon + 1, desc.data() + desc.size(), ordinal);
+  }
+  ~Context() { close(); }
+  Context(const Context &) = delete;
+  Context &operator=(const Context &) = delete;
+
+  void close() {
+    if (handle)
+      hcReleaseContext(handle);
+    handle = nullptr;
+  }
+
+  HcContext get() const {
+    if (!handle)
+      throw std::runtime_error("context is closed");
+    return handle;
+  }
+
+  void check(int rc, const char *what) const {
+    if (rc)
+      throw std::runtime_error(std::string(what) + " failed: " + hcLastError(handle));
+  }
+
+  std::string description;
+  int ordinal = 0;
+
+private:
+  static void onMessage(void *self, OlSeverity sev, const char *text) {
+    auto *c = static_cast<Context *>(self);
+    if (sev == OlSeverity::Error) {
+      if (!c->errors.empty())
+        c->errors += "; ";
+      c->errors += text ? text : "";
+    }
+  }
+  HcContext handle = nullptr;
+  std::string errors;
+};
+
+// Reads an argument and checks what every kernel needs: device memory on the
+// context's GPU, the expected rank, contiguous rows.
+ArrayArg deviceArray(const Context &ctx, py::handle obj, const char *name,
+                     int rank) {
+  ArrayArg a;
+  try {
+    a = hc::arrayFromPython(obj);
+  } catch (const std::exception &e) {
+    throw py::type_error(std::string(name) + ": " + e.what());
+  }
+  if (!a.onDevice)
+    throw py::value_error(std::string(name) +
+                          ": expected device memory (a CUDA tensor), got host memory");
+  if (a.deviceIndex >= 0 && a.deviceIndex != ctx.ordinal)
+    throw py::value_error(std::string(name) + ": lives on cuda:" +
+                          std::to_string(a.deviceIndex) + " but the kernel runs on " +
+                          ctx.description);
+  if (a.rank() != rank)
+    throw py::value_error(std::string(name) + ": expected rank " + std::to_string(rank) +
+                          ", got " + std::to_string(a.rank()));
+  if (!a.rowMajor())
+    throw py::value_error(std::string(name) + ": rows must be contiguous (last stride 1)");
+  for (auto s : a.strides)
+    if (s < 0)
+      throw py::value_error(std::string(name) + ": negative strides are not supported");
+  return a;
+}
+
+void sameKind(const ArrayArg &a, const ArrayArg &b, const char *an, const char *bn) {
+  if (a.kind != b.kind || a.itemsize != b.itemsize)
+    throw py::type_error(std::string(an) + " is " + hc::kindName(a.kind) + " but " + bn +
+                         " is " + hc::kindName(b.kind));
+}
+
+void sameShape(const ArrayArg &a, const ArrayArg &b, const char *an, const char *bn) {
+  if (a.shape != b.shape)
+    throw py::value_error(std::string(an) + " and " + bn + " differ in shape");
+}
+
+long long pitch(const ArrayArg &a) {
+  // Row pitch of a rank-2 array; a single row may report any stride.
+  return a.shape[0] > 1 ? a.strides[0] : std::max<long long>(a.strides[0], a.shape[1]);
+}
+
+int floatDType(const ArrayArg &a, const char *name) {
+  if (a.kind == ElemKind::F32)
+    return HC_F32;
+  if (a.kind == ElemKind::F64)
+    return HC_F64;
+  throw py::type_error(std::string(name) + ": float32 or float64 expected, got " +
+                       hc::kindName(a.kind));
+}
+
+void copy2d(Context &ctx, py::handle src, py::handle dst) {
+  ArrayArg s = deviceArray(ctx, src, "src", 2), d = deviceArray(ctx, dst, "dst", 2);
+  sameKind(s, d, "src", "dst");
+  sameShape(s, d, "src", "dst");
+  ctx.check(hcCopy2D(ctx.get(), s.data, d.data, s.shape[0], s.shape[1], pitch(s), pitch(d),
+                     int(s.itemsize)),
+            "copy2d");
+}
+
+void softmaxRows(Context &ctx, py::handle x, py::handle y) {
+  ArrayArg a = deviceArray(ctx, x, "x", 2), b = deviceArray(ctx, y, "out", 2);
+  sameKind(a, b, "x", "out");
+  sameShape(a, b, "x", "out");
+  ctx.check(hcSoftmaxRows(ctx.get(), a.data, b.data, a.shape[0], a.shape[1], pitch(a),
+                          pitch(b), floatDType(a, "x")),
+            "softmax_rows");
+}
+
+void reduceRows(Context &ctx, py::handle x, py::object sumOut, py::object maxOut) {
+  ArrayArg a = deviceArray(ctx, x, "x", 2);
+  int dtype = floatDType(a, "x");
+  void *sp = nullptr, *mp = nullptr;
+  auto output = [&](py::object &o, const char *name) -> void * {
+    if (o.is_none())
+      return nullptr;
+    ArrayArg r = deviceArray(ctx, o, name, 1);
+    sameKind(a, r, "x", name);
+    if (r.shape[0] != a.shape[0])
+      throw py::value_error(std::string(name) + ": expected " +
+                            std::to_string(a.shape[0]) + " elements");
+    if (r.shape[0] > 1 && r.strides[0] != 1)
+      throw py::value_error(std::string(name) + ": must be contiguous");
+    return r.data;
+  };
+  sp = output(sumOut, "sum_out");
+  mp = output(maxOut, "max_out");
+  ctx.check(hcReduceRows(ctx.get(), a.data, sp, mp, a.shape[0], a.shape[1], pitch(a), dtype),
+            "reduce_rows");
+}
+
+void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
+  ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
+           C = deviceArray(ctx, out, "out", 2);
+  sameKind(A, B, "a", "b");
+  sameKind(A, C, "a", "out");
+  long long M = A.shape[0], K = A.shape[1], N = B.shape[1];
+  if (B.shape[0] != K || C.shape[0] != M || C.shape[1] != N)
+    throw py::value_error("gemm: shapes do not form [M,K] @ [K,N] -> [M,N]");
+  if (A.kind == ElemKind::BF16) {
+    ctx.check(hcGemmBf16(ctx.get(), A.data, B.data, C.data, M, N, K, pitch(A), pitch(B),
+                         pitch(C)),
+              "gemm (bf16)");
+    return;
+  }
+  ctx.check(hcGemmTiled(ctx.get(), A.data, B.data, C.data, M, N, K, pitch(A), pitch(B),
+                        pitch(C), floatDType(A, "a")),
+            "gemm");
+}
+
+size_t w8a16WorkspaceBytes(long long n, long long k) {
+  return hcGemmW8A16WorkspaceBytes(n, k);
+}
+
+void gemmW8A16(Context &ctx, py::handle a, py::handle w, py::handle scale, py::handle out,
+               py::object workspace) {
+  ArrayArg A = deviceArray(ctx, a, "a", 2), W = deviceArray(ctx, w, "w", 2),
+           S = deviceArray(ctx, scale, "scale", 1), C = deviceArray(ctx, out, "out", 2);
+  if (A.kind != ElemKind::BF16 || C.kind != ElemKind::BF16)
+    throw py::type_error("gemm_w8a16: a and out must be bfloat16");
+  if (W.kind != ElemKind::I8)
+    throw py::type_error(std::string("gemm_w8a16: w must be int8, got ") + hc::kindName(W.kind));
+  if (S.kind != ElemKind::F32)
+    throw py::type_error("gemm_w8a16: scale must be float32");
+  long long M = A.shape[0], K = A.shape[1], N = W.shape[1];
+  if (W.shape[0] != K || C.shape[0] != M || C.shape[1] != N || S.shape[0] != N)
+    throw py::value_error("gemm_w8a16: shapes do not form [M,K] @ [K,N] * [N] -> [M,N]");
+  if (N > 1 && S.strides[0] != 1)
+    throw py::value_error("scale: must be contiguous");
+  void *ws = nullptr;
+  size_t wsBytes = 0;
+  if (!workspace.is_none()) {
+    ArrayArg Wk = hc::arrayFromPython(workspace);
+    if (!Wk.onDevice)
+      throw py::value_error("workspace: expected device memory");
+    ws = Wk.data;
+    wsBytes = size_t(Wk.itemsize);
+    for (auto d : Wk.shape)
+      wsBytes *= size_t(d);
+  }
+  ctx.check(hcGemmW8A16(ctx.get(), A.data, W.data, static_cast<const float *>(S.data), C.data,
+                        ws, wsBytes, M, N, K, pitch(A), pitch(W), pitch(C)),
+            "gemm_w8a16");
+}
+
+} // namespace
+
+PYBIND11_MODULE(_dispatcher, m) {
+  m.doc() = "Launch path of hc_b200: argument checking + precompiled sm_100a kernels";
+
+  py::class_<Context>(m, "Context")
+      .def(py::init<const std::string &>(), py::arg("device") = "cuda:0")
+      .def("close", &Context::close)
+      .def_readonly("device", &Context::description)
+      .def_readonly("ordinal", &Context::ordinal)
+      .def_property_readonly("stream",
+                             [](Context &c) {
+                               return reinterpret_cast<uintptr_t>(hcContextStream(c.get()));
+                             })
+      .def_property_readonly("launch_count",
+                             [](Context &c) { return hcLaunchCount(c.get()); })
+      .def("synchronize", [](Context &c) { c.check(hcSynchronize(c.get()), "synchronize"); })
+      .def("kernel_status",
+           [](Context &c) {
+             int v = 0;
+             c.check(hcKernelStatus(c.get(), &v), "kernel_status");
+             return v;
+           })
+      .def("set_option", [](Context &c, const std::string &name, long long v) {
+        c.check(hcSetOption(c.get(), name.c_str(), v), "set_option");
+      });
+
+  m.def("copy2d", &copy2d, py::arg("ctx"), py::arg("src"), py::arg("dst"));
+  m.def("softmax_rows", &softmaxRows, py::arg("ctx"), py::arg("x"), py::arg("out"));
+  m.def("reduce_rows", &reduceRows, py::arg("ctx"), py::arg("x"),
+        py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
+  m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"));
+  m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
+        py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());
+  m.def("w8a16_workspace_bytes", &w8a16WorkspaceBytes, py::arg("n"), py::arg("k"));
+  m.def("image_names", [] {
+    std::vector<std::string> names;
+    for (int i = 0; i < hcImageCount(); ++i)
+      names.emplace_back(hcImageName(i));
+    return names;
+  });
+}

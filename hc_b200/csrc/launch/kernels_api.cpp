@@ -102,6 +102,7 @@ struct HcContextImpl {
   long long smCount = 0;
   long long ccMajor = 0;
   long long gemmVariant = 0;
+  long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
     char text[320];
@@ -454,12 +455,24 @@ static int launchUmma(HcContext c, const void *a, const void *b,
   int bandM = pair ? 8 : 16;
   int vecStore = aligned(out, 16) && ldc % 8 == 0;
   long long tiles = (long long)tilesM * tilesN;
-  long long grid = pair ? 2 * std::min<long long>(tiles, c->smCount / 2)
-                        : std::min<long long>(tiles, c->smCount);
   const char *name = pair ? (scale ? "hc_gemm_bf16_umma_pair_scaled"
                                    : "hc_gemm_bf16_umma_pair")
                           : (scale ? "hc_gemm_bf16_umma_scaled"
                                    : "hc_gemm_bf16_umma");
+  long long grid = std::min<long long>(tiles, c->smCount);
+  if (pair) {
+    // The kernel is persistent: CTA pairs beyond what the GPU can hold at once
+    // would only start when the first wave has finished all its tiles.
+    if (c->pairSlots == 0) {
+      OlKernel k = c->kernel(name);
+      int slots = 0;
+      if (!k || olxMaxActiveClusters(c->queue, k, kUmmaThreads, kUmmaSmemBytes, 2,
+                                     &slots) || slots <= 0)
+        return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
+      c->pairSlots = slots;
+    }
+    grid = 2 * std::min<long long>(tiles, c->pairSlots);
+  }
   void *args[] = {&mapA,   &mapB,   &out,   &scale,    &M,           &N, &K,
                   &ldc,    &tilesM, &tilesN, &bandM,   &vecStore, &c->statusWord};
   return c->launch(name, size_t(grid), 1, 1, kUmmaThreads, args, 13,
@@ -483,7 +496,8 @@ int hcGemmBf16(HcContext c, const void *a, const void *b, void *out,
     return 0;
   if (c->gemmVariant == 3 || !ummaEligible(c, a, b, K, lda, ldb))
     return hcGemmTiled(c, a, b, out, M, N, K, lda, ldb, ldc, HC_BF16);
-  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
+  // The CTA-pair kernel is opt-in: it measured slower than one CTA per tile.
+  const bool pair = c->gemmVariant == 2;
   return launchUmma(c, a, b, nullptr, out, M, N, K, lda, ldb, ldc, pair);
 }
 
@@ -537,7 +551,8 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
                    workspaceBytes, hcGemmW8A16WorkspaceBytes(N, K));
   if (hcDequantW8(c, w, workspace, K, N, ldw, wsPitch))
     return 1;
-  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
+  // The CTA-pair kernel is opt-in: it measured slower than one CTA per tile.
+  const bool pair = c->gemmVariant == 2;
   return launchUmma(c, a, workspace, scale, out, M, N, K, lda, wsPitch, ldc, pair);
 }
 

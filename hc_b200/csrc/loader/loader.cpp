@@ -91,6 +91,7 @@ struct Backend {
   decltype(&olxMemsetD8) MemsetD8 = nullptr;
   decltype(&olxDeviceAttribute) DeviceAttribute = nullptr;
   decltype(&olxEncodeTensorMap2D) EncodeTensorMap2D = nullptr;
+  decltype(&olxMaxActiveClusters) MaxActiveClusters = nullptr;
 };
 
 struct Reporter {
@@ -160,6 +161,7 @@ std::unique_ptr<Backend> openBackend(const std::string &path,
   HC_BIND_OPT(MemsetD8);
   HC_BIND_OPT(DeviceAttribute);
   HC_BIND_OPT(EncodeTensorMap2D);
+  HC_BIND_OPT(MaxActiveClusters);
 #undef HC_BIND_OPT
   return b;
 }
@@ -430,6 +432,19 @@ int olxEncodeTensorMap2D(OlDevice d, void *mapOut, int elemKind,
   return fn ? fn(dev->inner, mapOut, elemKind, base, rows, cols, rowPitchBytes,
                  boxRows, boxCols, swizzle)
             : missing(dev, "olxEncodeTensorMap2D");
+}
+
+int olxMaxActiveClusters(OlQueue q, OlKernel k, unsigned blockThreads,
+                         size_t sharedMemSize, unsigned clusterSize,
+                         int *clustersRet) noexcept {
+  auto *queue = static_cast<QueueHandle *>(q);
+  auto *kernel = static_cast<KernelHandle *>(k);
+  if (!queue || !kernel)
+    return 1;
+  auto fn = queue->device->api->MaxActiveClusters;
+  return fn ? fn(queue->inner, kernel->inner, blockThreads, sharedMemSize,
+                 clusterSize, clustersRet)
+            : missing(queue->device, "olxMaxActiveClusters");
 }
 
 } // extern "C"

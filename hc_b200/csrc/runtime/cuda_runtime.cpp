@@ -461,6 +461,48 @@ int olxDeviceAttribute(OlDevice d, int what, long long *valueRet) noexcept {
   return 0;
 }
 
+int olxMaxActiveClusters(OlQueue queue, OlKernel kernel, unsigned blockThreads,
+                         size_t sharedMemSize, unsigned clusterSize,
+                         int *clustersRet) noexcept {
+  auto *q = static_cast<QueueState *>(queue);
+  auto *k = static_cast<KernelState *>(kernel);
+  if (!q || !k || !clustersRet || clusterSize == 0)
+    return 1;
+  DeviceState *dev = q->device;
+  const DriverApi &cu = DriverApi::get();
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  if (sharedMemSize > size_t(k->dynSmemLimit)) {
+    if (dev->check("cuFuncSetAttribute",
+                   cu.FuncSetAttribute(
+                       k->function,
+                       CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                       static_cast<int>(sharedMemSize))))
+      return 1;
+    k->dynSmemLimit = static_cast<int>(sharedMemSize);
+  }
+  CUlaunchAttribute attr{};
+  attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+  attr.value.clusterDim.x = clusterSize;
+  attr.value.clusterDim.y = 1;
+  attr.value.clusterDim.z = 1;
+  CUlaunchConfig config{};
+  config.gridDimX = clusterSize;
+  config.gridDimY = 1;
+  config.gridDimZ = 1;
+  config.blockDimX = blockThreads;
+  config.blockDimY = 1;
+  config.blockDimZ = 1;
+  config.sharedMemBytes = static_cast<unsigned>(sharedMemSize);
+  config.hStream = q->stream;
+  config.attrs = &attr;
+  config.numAttrs = 1;
+  return dev->check("cuOccupancyMaxActiveClusters",
+                    cu.OccupancyMaxActiveClusters(clustersRet, k->function,
+                                                  &config));
+}
+
 int olxEncodeTensorMap2D(OlDevice d, void *mapOut, int elemKind,
                          const void *base, size_t rows, size_t cols,
                          size_t rowPitchBytes, unsigned boxRows,

@@ -48,6 +48,9 @@ struct DriverApi {
       const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
       CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
 
+  CUresult (*OccupancyMaxActiveClusters)(int *, CUfunction,
+                                         const CUlaunchConfig *) = nullptr;
+
   bool ok = false;
   std::string error;
 
@@ -105,7 +108,8 @@ private:
          bind(MemcpyDtoHAsync, "cuMemcpyDtoHAsync_v2") &&
          bind(MemsetD8Async, "cuMemsetD8Async") &&
          bind(LaunchKernel, "cuLaunchKernel") &&
-         bind(TensorMapEncodeTiled, "cuTensorMapEncodeTiled");
+         bind(TensorMapEncodeTiled, "cuTensorMapEncodeTiled") &&
+         bind(OccupancyMaxActiveClusters, "cuOccupancyMaxActiveClusters");
   }
 };
 

@@ -1,0 +1,508 @@
+"""Objects a kernel body is written against: ``CurrentGroup``, ``Buffer``,
+``TunableParam``, ``sym``, ``typename`` ... - the names the reference exports
+from ``hckernel/kernel_api.py`` (:21-23, :35-40, :214-220, :255-463).
+
+In the reference these objects have two lives: the simulator executes them on
+NumPy, the compiler reads them from the Python AST.  Here they have one: the
+body is *run once with recording objects*.  ``group.load`` returns a
+:class:`Tile` that remembers where it was loaded from, arithmetic and NumPy
+calls on tiles build an expression graph, ``group.store`` appends to the
+group's list of stores.  ``hckernel.kernel`` then recognises the recorded
+graph as one of the precompiled kernel families (copy, row softmax, last-axis
+reductions, GEMM, weight-only dequant GEMM) and launches that kernel on the
+whole arrays.  Nothing is computed on the host.
+
+Semantics the recording keeps from the reference:
+
+* ``group.work_offset[d] == group.id[d] * group.shape[d]``
+  (kernel_api.py:293-295) - here an :class:`Affine` expression in the group id,
+  so one recording stands for every work-group;
+* ``group.load(view, shape)`` reads a tile whose origin is where ``view``
+  starts, zero-padded past the array edge (kernel_api.py:297-316);
+* ``group.store(view, tile)`` writes the tile clipped to the array
+  (kernel_api.py:318-342);
+* ``zeros/ones/full/empty`` and their ``v*`` twins allocate tiles
+  (kernel_api.py:347-369).
+"""
+
+from collections.abc import Iterable
+from math import prod
+
+import numpy as np
+import sympy
+
+from .indexing import sym  # noqa: F401  (re-exported, as the reference does)
+from .typename import Typename, typename  # noqa: F401
+
+
+class UnsupportedKernel(NotImplementedError):
+    """The body uses a construct no precompiled kernel family provides."""
+
+
+def _verify_kernel_params(work_shape, group_shape, subgroup_size, literals, tunables):
+    # Same two checks as the reference (kernel_api.py:26-32), as exceptions.
+    if not (subgroup_size is None or isinstance(subgroup_size, int) or subgroup_size in literals):
+        raise AssertionError("Subgroup size must be const or literal")
+    if not isinstance(literals, Iterable):
+        raise AssertionError(f"literals must iterable, got {literals}")
+
+
+def _divup(a, b):
+    return (a + b - 1) // b
+
+
+class TunableParam:
+    """A symbol the kernel may be tuned over, with its default
+    (reference: kernel_api.py:35-40)."""
+
+    def __init__(self, sym, default, vals, strategy=None):
+        self.sym = sym
+        self.default = default
+        self.vals = vals
+        self.strategy = strategy
+
+
+class Buffer(type):
+    """``Buffer[M, K, DT]``: an array argument whose shape binds the symbols
+    (reference: kernel_api.py:437-447)."""
+
+    def __class_getitem__(cls, shape_and_dtype):
+        if not isinstance(shape_and_dtype, tuple) or len(shape_and_dtype) == 0:
+            raise AssertionError("Invalid shape and dtype")
+
+        class _Annotated(cls):
+            shape = tuple(shape_and_dtype[:-1])
+            dtype = shape_and_dtype[-1]
+
+        return _Annotated
+
+
+class Mapping:
+    def __init__(self, func):
+        self.func = func
+
+
+def create_mapping(func):
+    """Index mapping for gather/scatter loads (reference: kernel_api.py:214-220).
+    Accepted so that programs import cleanly; a kernel that uses one is not in
+    any precompiled family and fails at its first call."""
+    return Mapping(func)
+
+
+def atomic_ref(a):
+    return a
+
+
+# ---- recording values -----------------------------------------------------------
+class Affine:
+    """``const + sum(coef[d] * group_id[d])`` with integer coefficients."""
+
+    __slots__ = ("const", "coefs")
+
+    def __init__(self, const=0, coefs=None):
+        self.const = int(const)
+        self.coefs = {d: int(c) for d, c in (coefs or {}).items() if c}
+
+    @staticmethod
+    def of(value):
+        if isinstance(value, Affine):
+            return value
+        if isinstance(value, (int, np.integer)):
+            return Affine(int(value))
+        if isinstance(value, sympy.Integer):
+            return Affine(int(value))
+        raise UnsupportedKernel(f"index expression {value!r} is not an integer or group offset")
+
+    def is_const(self):
+        return not self.coefs
+
+    def __add__(self, other):
+        o = Affine.of(other)
+        coefs = dict(self.coefs)
+        for d, c in o.coefs.items():
+            coefs[d] = coefs.get(d, 0) + c
+        return Affine(self.const + o.const, coefs)
+
+    __radd__ = __add__
+
+    def __neg__(self):
+        return Affine(-self.const, {d: -c for d, c in self.coefs.items()})
+
+    def __sub__(self, other):
+        return self + (-Affine.of(other))
+
+    def __rsub__(self, other):
+        return Affine.of(other) - self
+
+    def __mul__(self, other):
+        o = Affine.of(other)
+        if o.is_const():
+            return Affine(self.const * o.const, {d: c * o.const for d, c in self.coefs.items()})
+        if self.is_const():
+            return o * self
+        raise UnsupportedKernel("product of two group offsets")
+
+    __rmul__ = __mul__
+
+    def _as_int(self, what):
+        if not self.is_const():
+            raise UnsupportedKernel(f"{what} of a group offset")
+        return self.const
+
+    def __floordiv__(self, other):
+        return Affine(self._as_int("division") // Affine.of(other)._as_int("division"))
+
+    def __mod__(self, other):
+        return Affine(self._as_int("modulo") % Affine.of(other)._as_int("modulo"))
+
+    def __index__(self):
+        return self._as_int("integer value")
+
+    __int__ = __index__
+
+    def __eq__(self, other):
+        try:
+            o = Affine.of(other)
+        except UnsupportedKernel:
+            return NotImplemented
+        return self.const == o.const and self.coefs == o.coefs
+
+    def __hash__(self):
+        return hash((self.const, tuple(sorted(self.coefs.items()))))
+
+    def key(self):
+        return (self.const, tuple(sorted(self.coefs.items())))
+
+    def __repr__(self):
+        terms = [str(self.const)] if self.const or not self.coefs else []
+        terms += [f"{c}*gid{d}" for d, c in sorted(self.coefs.items())]
+        return " + ".join(terms)
+
+
+def dtype_name(dtype):
+    """Canonical element-type name of a torch/NumPy dtype or dtype-like."""
+    if isinstance(dtype, str):
+        return dtype
+    text = str(dtype)
+    if text.startswith("torch."):
+        return text[len("torch."):]
+    try:
+        return np.dtype(dtype).name
+    except TypeError:
+        return text
+
+
+class BufferRef:
+    """Stands for an array argument while the body is recorded."""
+
+    def __init__(self, index, name, shape, dtype):
+        self.index = index
+        self.name = name
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = dtype_name(dtype)
+
+    @property
+    def ndim(self):
+        return len(self.shape)
+
+    def __len__(self):
+        return self.shape[0]
+
+    def _origin(self, key):
+        if not isinstance(key, tuple):
+            key = (key,)
+        if len(key) > self.ndim:
+            raise IndexError(f"too many indices for {self.name}")
+        origin = []
+        for k in key:
+            if not isinstance(k, slice):
+                raise UnsupportedKernel(
+                    f"{self.name}[...]: only `start:` slices select a tile origin; element "
+                    f"indexing (e.g. the scalar atomic-reduction form) is not supported"
+                )
+            if k.stop is not None or k.step is not None:
+                raise UnsupportedKernel(f"{self.name}[...]: slices with stop/step are not supported")
+            origin.append(Affine.of(0 if k.start is None else k.start))
+        origin += [Affine(0)] * (self.ndim - len(origin))
+        return tuple(origin)
+
+    def __getitem__(self, key):
+        return BufferView(self, self._origin(key))
+
+    def __setitem__(self, key, value):
+        raise UnsupportedKernel(f"direct assignment into {self.name}; use group.store")
+
+    def __repr__(self):
+        return f"<buffer {self.name}{list(self.shape)} {self.dtype}>"
+
+
+class BufferView:
+    """``buffer[m0:, k0:]`` - a buffer seen from a tile origin onwards."""
+
+    def __init__(self, buffer, origin):
+        self.buffer = buffer
+        self.origin = origin
+
+    @property
+    def dtype(self):
+        return self.buffer.dtype
+
+    @property
+    def shape(self):
+        raise UnsupportedKernel("shape of a sliced buffer depends on the work-group")
+
+    def key(self):
+        return ("view", self.buffer.index, tuple(o.key() for o in self.origin))
+
+
+def _shape_tuple(shape):
+    if isinstance(shape, Iterable):
+        return tuple(int(Affine.of(s)) for s in shape)
+    return (int(Affine.of(shape)),)
+
+
+def _broadcast(a, b):
+    out = []
+    for x, y in zip(((1,) * (len(b) - len(a)) + tuple(a)), ((1,) * (len(a) - len(b)) + tuple(b))):
+        if x != y and 1 not in (x, y):
+            raise ValueError(f"tile shapes {a} and {b} do not broadcast")
+        out.append(max(x, y))
+    return tuple(out)
+
+
+class Tile:
+    """A node of the recorded expression graph.
+
+    ``op`` is one of ``load``, ``alloc``, ``const``, ``add``/``sub``/``mul``/
+    ``div``, ``exp``, ``dot``, ``astype``, ``sum``/``max`` (with ``axis`` and
+    ``keepdims``).
+    """
+
+    __array_priority__ = 1000
+
+    def __init__(self, op, args=(), shape=(), dtype="float32", **attrs):
+        self.op = op
+        self.args = tuple(args)
+        self.shape = tuple(shape)
+        self.dtype = dtype
+        self.attrs = attrs
+
+    # -- structure ---------------------------------------------------------------
+    def key(self):
+        parts = []
+        for a in self.args:
+            parts.append(a.key() if hasattr(a, "key") else ("lit", a))
+        return (self.op, tuple(parts), self.shape, tuple(sorted(self.attrs.items())))
+
+    def __repr__(self):
+        return f"<tile {self.op}{list(self.shape)} {self.dtype}>"
+
+    @property
+    def ndim(self):
+        return len(self.shape)
+
+    @property
+    def size(self):
+        return prod(self.shape)
+
+    # -- arithmetic --------------------------------------------------------------
+    @staticmethod
+    def _wrap(value):
+        if isinstance(value, Tile):
+            return value
+        if isinstance(value, (int, float, np.integer, np.floating)):
+            return Tile("const", (float(value),), (), "scalar")
+        raise UnsupportedKernel(f"operand {value!r} is not a tile or a number")
+
+    def _binary(self, op, other, swapped=False):
+        o = Tile._wrap(other)
+        lhs, rhs = (o, self) if swapped else (self, o)
+        dtype = lhs.dtype if lhs.dtype != "scalar" else rhs.dtype
+        return Tile(op, (lhs, rhs), _broadcast(lhs.shape, rhs.shape), dtype)
+
+    def __add__(self, o): return self._binary("add", o)
+    def __radd__(self, o): return self._binary("add", o, True)
+    def __sub__(self, o): return self._binary("sub", o)
+    def __rsub__(self, o): return self._binary("sub", o, True)
+    def __mul__(self, o): return self._binary("mul", o)
+    def __rmul__(self, o): return self._binary("mul", o, True)
+    def __truediv__(self, o): return self._binary("div", o)
+    def __rtruediv__(self, o): return self._binary("div", o, True)
+    def __matmul__(self, o): return _dot(self, o)
+    # `acc += x` rebinds the name to the new node, like any immutable value.
+    def __iadd__(self, o): return self._binary("add", o)
+    def __isub__(self, o): return self._binary("sub", o)
+    def __imul__(self, o): return self._binary("mul", o)
+
+    def _reduce(self, op, axis, keepdims):
+        if axis is None:
+            shape = (1,) * self.ndim if keepdims else ()
+        else:
+            axis = axis % self.ndim
+            shape = tuple(
+                (1 if i == axis else s) for i, s in enumerate(self.shape) if keepdims or i != axis
+            )
+        return Tile(op, (self,), shape, self.dtype, axis=axis, keepdims=bool(keepdims))
+
+    def sum(self, axis=None, keepdims=False, **_):
+        return self._reduce("sum", axis, keepdims)
+
+    def max(self, axis=None, keepdims=False, **_):
+        return self._reduce("max", axis, keepdims)
+
+    def astype(self, dtype, **_):
+        return Tile("astype", (self,), self.shape, dtype_name(dtype))
+
+    def copy(self):
+        return self
+
+    def __getitem__(self, key):
+        raise UnsupportedKernel("slicing a loaded tile is not supported by the precompiled kernels")
+
+    # -- NumPy protocols: np.exp(tile), np.dot(a, b), np.add(a, b) ... -------------
+    def __array_ufunc__(self, ufunc, method, *inputs, **kwargs):
+        if method != "__call__" or kwargs.get("out") is not None:
+            raise UnsupportedKernel(f"np.{ufunc.__name__}.{method} on a tile")
+        names = {"add": "add", "subtract": "sub", "multiply": "mul", "true_divide": "div",
+                 "divide": "div"}
+        if ufunc.__name__ == "exp":
+            (x,) = inputs
+            return Tile("exp", (x,), x.shape, x.dtype)
+        if ufunc.__name__ in names:
+            a, b = (Tile._wrap(v) for v in inputs)
+            return a._binary(names[ufunc.__name__], b)
+        raise UnsupportedKernel(f"np.{ufunc.__name__} on a tile")
+
+    def __array_function__(self, func, types, args, kwargs):
+        if func in (np.dot, np.matmul):
+            return _dot(*args)
+        if func is np.sum:
+            return args[0].sum(*args[1:], **kwargs)
+        if func in (np.max, np.amax):
+            return args[0].max(*args[1:], **kwargs)
+        raise UnsupportedKernel(f"np.{func.__name__} on a tile")
+
+
+def _dot(a, b):
+    a, b = Tile._wrap(a), Tile._wrap(b)
+    if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError(f"np.dot of tiles shaped {a.shape} and {b.shape}")
+    # NumPy's result type: float wins over int, wider wins over narrower.
+    order = ["int8", "bfloat16", "float16", "float32", "float64"]
+    dtype = max((a.dtype, b.dtype), key=lambda d: order.index(d) if d in order else -1)
+    return Tile("dot", (a, b), (a.shape[0], b.shape[1]), dtype)
+
+
+class CurrentSubGroup:
+    """Importable for source compatibility (reference: kernel_api.py:231-240)."""
+
+    def __init__(self, size, subgroup_id):
+        self._size, self._subgroup_id = size, subgroup_id
+
+    def size(self):
+        return self._size
+
+    def subgroup_id(self):
+        return self._subgroup_id
+
+
+class CurrentWorkitem:
+    """Importable for source compatibility (reference: kernel_api.py:243-252)."""
+
+    def __init__(self, lid, gid):
+        self._local_id, self._global_id = lid, gid
+
+    def local_id(self):
+        return self._local_id
+
+    def global_id(self):
+        return self._global_id
+
+
+class CurrentGroup:
+    """The work-group a kernel body sees (reference: kernel_api.py:255-434),
+    recording instead of computing."""
+
+    def __init__(self, group_shape, subgroup_size):
+        self._group_shape = tuple(int(g) for g in group_shape)
+        self._subgroup_size = subgroup_size
+        self._group_id = tuple(Affine(0, {d: 1}) for d in range(len(self._group_shape)))
+        self.stores = []
+
+    @property
+    def id(self):
+        return self._group_id
+
+    @property
+    def shape(self):
+        return self._group_shape
+
+    @property
+    def size(self):
+        return prod(self._group_shape)
+
+    @property
+    def work_offset(self):
+        return tuple(g * s for g, s in zip(self._group_id, self._group_shape))
+
+    # -- memory ------------------------------------------------------------------
+    def load(self, array, shape, mapping=None):
+        if mapping is not None:
+            raise UnsupportedKernel("group.load(mapping=...) is not supported")
+        if isinstance(array, BufferRef):
+            array = array[()]
+        if not isinstance(array, BufferView):
+            raise UnsupportedKernel(f"group.load source {array!r} is not a kernel buffer")
+        return Tile("load", (array,), _shape_tuple(shape), array.dtype)
+
+    def vload(self, array, shape, mapping=None):
+        return self.load(array, shape, mapping)
+
+    def store(self, dst, src, mapping=None):
+        if mapping is not None:
+            raise UnsupportedKernel("group.store(mapping=...) is not supported")
+        if isinstance(dst, BufferRef):
+            dst = dst[()]
+        if not isinstance(dst, BufferView):
+            raise UnsupportedKernel(f"group.store destination {dst!r} is not a kernel buffer")
+        self.stores.append((dst, Tile._wrap(src)))
+
+    # -- allocators ---------------------------------------------------------------
+    def _alloc(self, shape, dtype, fill):
+        return Tile("alloc", (float(fill),), _shape_tuple(shape), dtype_name(dtype))
+
+    def empty(self, shape, dtype): return self._alloc(shape, dtype, 0)
+    def zeros(self, shape, dtype): return self._alloc(shape, dtype, 0)
+    def ones(self, shape, dtype): return self._alloc(shape, dtype, 1)
+    def full(self, shape, dtype, fill_value): return self._alloc(shape, dtype, fill_value)
+    def vempty(self, shape, dtype): return self._alloc(shape, dtype, 0)
+    def vzeros(self, shape, dtype): return self._alloc(shape, dtype, 0)
+    def vones(self, shape, dtype): return self._alloc(shape, dtype, 1)
+    def vfull(self, shape, dtype, fill_value): return self._alloc(shape, dtype, fill_value)
+
+    def vec(self, src, shape=None):
+        if shape is not None and _shape_tuple(shape) != src.shape:
+            raise UnsupportedKernel("group.vec with a different shape")
+        return src
+
+    # -- scopes the precompiled kernels do not need ---------------------------------
+    def subgroups(self, func):
+        raise UnsupportedKernel("group.subgroups is not supported by the precompiled kernels")
+
+    def workitems(self, func):
+        raise UnsupportedKernel("group.workitems is not supported by the precompiled kernels")
+
+    def barrier(self):
+        raise UnsupportedKernel("group.barrier is not supported by the precompiled kernels")
+
+
+class CurrentGroup1(CurrentGroup):
+    pass
+
+
+class CurrentGroup2(CurrentGroup):
+    pass
+
+
+class CurrentGroup3(CurrentGroup):
+    pass

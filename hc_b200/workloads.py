@@ -1,0 +1,91 @@
+"""The benchmark workloads written in the kernel DSL, bound to a device.
+
+Each body is what a user of the reference would write (and what its tests
+write: python/hckernel/tests/test_examples.py:88-111, 136-155, 312-321;
+tests/test_e2e.py:66-70); :func:`make_kernels` decorates them for one GPU.
+Calling one of the returned kernels goes through the whole product path:
+symbol binding, recording, family recognition, the C++ dispatcher, the C-ABI
+and a precompiled sm_100a kernel.
+"""
+
+import types
+
+import numpy as np
+
+from .hckernel.kernel import Buffer, CurrentGroup, TunableParam, kernel, sym, typename
+
+DT = typename.DT
+
+
+def _cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def make_kernels(device="cuda:0"):
+    """Namespace with ``copy``, ``softmax``, ``reduce_rows``, ``dot``,
+    ``dot_fullk`` and ``dequant_dot`` kernels that run on ``device``."""
+    target = dict(backend="nvvm", device=device)
+    M, N, K, W, H = sym.M, sym.N, sym.K, sym.W, sym.H
+    GM, GN, MI, NI, KB = sym.GM, sym.GN, sym.MI, sym.NI, sym.KB
+
+    @kernel(work_shape=(W, H), **target)
+    def copy(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT]):
+        x, y = group.work_offset
+        group.store(dst[x:, y:], group.load(src[x:, y:], shape=group.shape))
+
+    @kernel(work_shape=M, group_shape=GM, **target)
+    def softmax(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
+        m0 = gr.work_offset[0]
+        rows = gr.load(a[m0:, :], shape=(gr.shape[0], N))
+        e = np.exp(rows - rows.max(axis=1, keepdims=True))
+        gr.store(out[m0:, :], e / e.sum(axis=1, keepdims=True))
+
+    @kernel(work_shape=M, group_shape=GM, **target)
+    def reduce_rows(gr: CurrentGroup, x: Buffer[M, N, DT], s: Buffer[M, DT], mx: Buffer[M, DT],
+                    gshape: GM):
+        m0 = gr.work_offset[0]
+        rows = gr.load(x[m0:, :], shape=(gr.shape[0], N))
+        gr.store(s[m0:], rows.sum(axis=1))
+        gr.store(mx[m0:], rows.max(axis=1))
+
+    steps = _cdiv(K, KB)
+    tunables = (
+        TunableParam(MI, 1, range(1, 8)),
+        TunableParam(NI, 1, range(1, 8)),
+        TunableParam(KB, 16, range(8, 128)),
+    )
+
+    @kernel(work_shape=(_cdiv(M, MI), _cdiv(N, NI)), group_shape=(GM, GN), tunables=tunables,
+            **target)
+    def dot(gr: CurrentGroup, a: Buffer[M, K, DT], b: Buffer[K, N, DT], out: Buffer[M, N, DT],
+            gshape: (GM, GN)):
+        m0, n0 = gr.work_offset[0] * MI, gr.work_offset[1] * NI
+        mb, nb = gr.shape[0] * MI, gr.shape[1] * NI
+        acc = gr.zeros(shape=(mb, nb), dtype=out.dtype)
+        for step in range(steps):
+            k0 = step * KB
+            acc += np.dot(gr.load(a[m0:, k0:], shape=(mb, KB)),
+                          gr.load(b[k0:, n0:], shape=(KB, nb)))
+        gr.store(out[m0:, n0:], acc)
+
+    @kernel(work_shape=(M, N), group_shape=(GM, GN), **target)
+    def dot_fullk(gr: CurrentGroup, a: Buffer[M, K, DT], b: Buffer[K, N, DT],
+                  out: Buffer[M, N, DT], gshape: (GM, GN)):
+        m0, n0 = gr.work_offset
+        mb, nb = gr.shape
+        acc = gr.zeros(shape=(mb, nb), dtype=out.dtype)
+        acc += np.dot(gr.load(a[m0:, :], shape=(mb, K)), gr.load(b[:, n0:], shape=(K, nb)))
+        gr.store(out[m0:, n0:], acc)
+
+    @kernel(work_shape=(M, N), group_shape=(GM, GN), **target)
+    def dequant_dot(gr: CurrentGroup, a: Buffer[M, K, DT], w: Buffer[K, N, DT], s: Buffer[N, DT],
+                    out: Buffer[M, N, DT], gshape: (GM, GN)):
+        m0, n0 = gr.work_offset
+        mb, nb = gr.shape
+        a_t = gr.load(a[m0:, :], shape=(mb, K))
+        w_t = gr.load(w[:, n0:], shape=(K, nb))
+        s_t = gr.load(s[n0:], shape=nb)
+        gr.store(out[m0:, n0:], np.dot(a_t, w_t.astype(np.float32)) * s_t)
+
+    return types.SimpleNamespace(copy=copy, softmax=softmax, reduce_rows=reduce_rows, dot=dot,
+                                 dot_fullk=dot_fullk, dequant_dot=dequant_dot, device=device)

@@ -128,6 +128,16 @@ OFFLOAD_API_EXPORT int olxEncodeTensorMap2D(OlDevice dev, void *mapOut,
                                             unsigned boxRows, unsigned boxCols,
                                             int swizzle) HC_NOEXCEPT;
 
+/* How many clusters of `clusterSize` CTAs (each `blockThreads` threads and
+ * `sharedMemSize` bytes of dynamic shared memory) of kernel `k` the device can
+ * hold at once.  A persistent kernel launched with more CTAs than that runs
+ * the excess as a second wave.  Returns 0 on success. */
+OFFLOAD_API_EXPORT int olxMaxActiveClusters(OlQueue q, OlKernel k,
+                                            unsigned blockThreads,
+                                            size_t sharedMemSize,
+                                            unsigned clusterSize,
+                                            int *clustersRet) HC_NOEXCEPT;
+
 #ifdef __cplusplus
 }
 #endif

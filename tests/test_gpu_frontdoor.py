@@ -1,0 +1,201 @@
+"""GPU tests of the ``@kernel`` call surface: the reference's own end-to-end
+tests (python/hckernel/tests/test_e2e.py:57-136, same kernels, same shapes,
+same assertions) and the benchmark workloads written in the DSL, each checked
+against the CPU oracle.
+"""
+
+import numpy as np
+import pytest
+import sympy
+import torch
+from torch.testing import assert_close
+
+from hc_b200.hckernel.kernel import *  # noqa: F401,F403  (as the reference's tests import)
+from hc_b200.hckernel.kernel import UnsupportedKernel, get_context
+from hc_b200.workloads import make_kernels
+from oracle import workloads as oracle
+
+pytestmark = pytest.mark.gpu
+
+BACKEND, DEVICE = "nvvm", "cuda:0"
+
+_copy_shapes = [(1, 27), (1, 72), (1, 128), (10, 20), (111, 813), (256, 64), (256, 1024)]
+
+
+def to_device(array):
+    return array.to("cuda")
+
+
+@pytest.mark.parametrize("shape", _copy_shapes)
+def test_copy(shape):
+    W, H, DT = sym.W, sym.H, typename.DT
+
+    @kernel(work_shape=(W, H), backend=BACKEND, device=DEVICE)
+    def copy_kernel(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT]):
+        x, y = group.work_offset
+        val = group.load(src[x:, y:], shape=group.shape)
+        group.store(dst[x:, y:], val)
+
+    a = to_device(torch.arange(shape[0] * shape[1], dtype=torch.int32).reshape(shape))
+    b = torch.zeros_like(a)
+    copy_kernel(a, b)
+    assert_close(b, a)
+
+
+@pytest.mark.parametrize("shape", _copy_shapes)
+@pytest.mark.parametrize("unroll", [1, 2, 4])
+def test_copy_unroll(shape, unroll):
+    W, H, DT, V = sym.W, sym.H, typename.DT, sym.V
+    H1 = sympy.ceiling(H / V)
+
+    @kernel(work_shape=(W, H1), backend=BACKEND, device=DEVICE)
+    def copy_kernel(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT], v: V):
+        x, y = group.work_offset
+        val = group.load(src[x:, y * V :], shape=(group.shape[0], group.shape[1] * V))
+        group.store(dst[x:, y * V :], val)
+
+    a = to_device(torch.arange(shape[0] * shape[1], dtype=torch.int32).reshape(shape))
+    b = torch.zeros_like(a)
+    copy_kernel(a, b, unroll)
+    assert_close(b, a)
+
+
+@pytest.mark.parametrize("shape", _copy_shapes)
+@pytest.mark.parametrize("unroll", [1, 2, 4])
+def test_copy_vec(shape, unroll):
+    W, H, DT, V = sym.W, sym.H, typename.DT, sym.V
+    H1 = sympy.ceiling(H / V)
+
+    @kernel(work_shape=(W, H1), backend=BACKEND, device=DEVICE, literals=[V])
+    def copy_kernel(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT], v: V):
+        x, y = group.work_offset
+        val = group.vload(src[x:, y * V :], shape=(group.shape[0], group.shape[1] * V))
+        group.store(dst[x:, y * V :], val)
+
+    a = to_device(torch.arange(shape[0] * shape[1], dtype=torch.int32).reshape(shape))
+    b = torch.zeros_like(a)
+    copy_kernel(a, b, unroll)
+    assert_close(b, a)
+
+
+@pytest.fixture(scope="module")
+def k():
+    return make_kernels(DEVICE)
+
+
+def test_softmax_kernel_matches_oracle(k):
+    (x,) = oracle.make_inputs("softmax", shape=(100, 4096))
+    d_x = to_device(torch.from_numpy(x))
+    d_y = torch.empty_like(d_x)
+    k.softmax(d_x, d_y, 8)
+    expect = np.zeros_like(x)
+    oracle.softmax_rows(x, expect, 8)
+    got = d_y.cpu().numpy()
+    assert np.all(np.abs(got - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+
+
+def test_softmax_reference_vector_f64(k, golden):
+    m, n = 30, 25
+    a = 2 * np.arange(m * n).reshape(m, n) / (m * n)
+    d_x = to_device(torch.from_numpy(a))
+    d_y = torch.zeros_like(d_x)
+    k.softmax(d_x, d_y, 8)
+    np.testing.assert_allclose(d_y.cpu().numpy(), golden["kat_softmax_f64"], rtol=1e-12)
+
+
+def test_reduce_rows_kernel_matches_oracle(k):
+    (x,) = oracle.make_inputs("reduce", shape=(1500, 2048))
+    d_x = to_device(torch.from_numpy(x))
+    d_s = torch.empty(1500, device="cuda")
+    d_m = torch.empty(1500, device="cuda")
+    k.reduce_rows(d_x, d_s, d_m, 256)
+    assert np.array_equal(d_m.cpu().numpy(), x.max(axis=1))
+    exact = x.astype(np.float64).sum(axis=1)
+    assert np.all(np.abs(d_s.cpu().numpy() - exact) <= 1e-5 * np.abs(x).sum(axis=1))
+
+
+def test_dot_kernels_f32_f64_bf16(k, golden):
+    a, b = oracle.make_inputs("gemm_f32")
+    d_a, d_b = to_device(torch.from_numpy(a)), to_device(torch.from_numpy(b))
+    d_c = torch.zeros(256, 256, device="cuda")
+    k.dot(d_a, d_b, d_c, (64, 64))
+    bound = 1e-5 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64))
+    assert np.all(np.abs(d_c.cpu().numpy().astype(np.float64) - golden["cfg1_gemm_f32_256"]) <= bound)
+    # Tunables change the tiling of the reference, not the result.
+    d_c2 = torch.zeros_like(d_c)
+    k.dot.parametrize({sym.KB: 32, sym.MI: 2})(d_a, d_b, d_c2, (32, 64))
+    assert np.all(np.abs(d_c2.cpu().numpy().astype(np.float64) - golden["cfg1_gemm_f32_256"]) <= bound)
+
+    m, n, kk = 16, 32, 64
+    a64 = 2 * np.arange(m * kk).reshape(m, kk) / (m * kk)
+    b64 = np.arange(n * kk).reshape(kk, n) / (n * kk)
+    d_c = torch.zeros(m, n, dtype=torch.float64, device="cuda")
+    k.dot(to_device(torch.from_numpy(a64)), to_device(torch.from_numpy(b64)), d_c, (8, 8))
+    np.testing.assert_allclose(d_c.cpu().numpy(), golden["kat_dot_kblocked_f64"], rtol=1e-12)
+
+    a, b = oracle.make_inputs("gemm_bf16", shape=(256, 512, 384))
+    d_a = to_device(torch.from_numpy(a)).bfloat16()
+    d_b = to_device(torch.from_numpy(b)).bfloat16()
+    d_c = torch.zeros(256, 512, dtype=torch.bfloat16, device="cuda")
+    k.dot_fullk(d_a, d_b, d_c, (128, 256))
+    expect = oracle.bf16_from_bits(golden["cfg4_gemm_bf16_256x512x384_bits"])
+    got = d_c.float().cpu().numpy()
+    assert np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * (np.abs(a) @ np.abs(b)))
+
+
+def test_dequant_dot_kernel(k, golden):
+    a, w, s = oracle.make_inputs("gemm_w8a16", shape=(128, 256, 512))
+    d_a = to_device(torch.from_numpy(a)).bfloat16()
+    d_w, d_s = to_device(torch.from_numpy(w)), to_device(torch.from_numpy(s))
+    d_c = torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda")
+    k.dequant_dot(d_a, d_w, d_s, d_c, (128, 128))
+    expect = oracle.bf16_from_bits(golden["cfg5_gemm_w8a16_128x256x512_bits"])
+    got = d_c.float().cpu().numpy()
+    mag = np.abs(a) @ (np.abs(w.astype(np.float32)) * s)
+    assert np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * mag)
+
+
+def test_launch_is_ordered_with_torch_streams(k):
+    # The kernel runs on the context's own stream; results must still be
+    # ordered after torch work that produced the inputs and before torch work
+    # that consumes the outputs, without any host synchronisation here.
+    x = torch.randn(4096, 4096, device="cuda")
+    for _ in range(3):
+        x = x * 1.0001 + 0.5  # queued on torch's stream
+    y = torch.empty_like(x)
+    k.softmax(x, y, 256)
+    total = y.sum(dim=1)  # queued on torch's stream right after
+    assert torch.allclose(total, torch.ones_like(total), atol=1e-4)
+
+
+def test_argument_errors(k):
+    x = torch.randn(8, 16, device="cuda")
+    with pytest.raises(ValueError, match="host memory"):
+        k.softmax(torch.randn(8, 16), torch.randn(8, 16), 8)
+    with pytest.raises(ValueError, match="Symbol value conflict"):
+        k.softmax(x, torch.empty(9, 16, device="cuda"), 8)
+    with pytest.raises(TypeError, match="float32 but out is float64"):
+        k.softmax(x, torch.empty(8, 16, device="cuda", dtype=torch.float64), 8)
+    with pytest.raises(ValueError, match="rows must be contiguous"):
+        k.softmax(x.t().contiguous().t(), torch.empty(8, 16, device="cuda"), 8)
+    with pytest.raises(TypeError, match="float32 or float64"):
+        k.softmax(x.half(), torch.empty(8, 16, device="cuda", dtype=torch.half), 8)
+
+    W, H, DT = sym.W, sym.H, typename.DT
+
+    @kernel(work_shape=(W, H), backend="rocm", device="hip:0")
+    def on_hip(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT]):
+        x0, y0 = group.work_offset
+        group.store(dst[x0:, y0:], group.load(src[x0:, y0:], shape=group.shape))
+
+    with pytest.raises(ValueError, match="backend 'rocm' is not available"):
+        on_hip(x, torch.empty_like(x))
+
+    @kernel(work_shape=(W, H), backend=BACKEND, device=DEVICE)
+    def shifted(group: CurrentGroup, src: Buffer[W, H, DT], dst: Buffer[W, H, DT]):
+        x0, y0 = group.work_offset
+        group.store(dst[x0:, y0:], group.load(src[x0:, y0 + 1 :], shape=group.shape))
+
+    with pytest.raises(UnsupportedKernel):
+        shifted(x, torch.empty_like(x))
+    assert get_context(DEVICE).kernel_status() == 0
