@@ -150,11 +150,20 @@ def build_libs(verbose=False, force=False):
     kernels = OUT / "libhc-b200-kernels.so"
     srcs = [CSRC / "launch" / "kernels_api.cpp", INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", loader, *cubins]
+    static_src = CSRC / "launch" / "w8a16_static.cu"
+    srcs.append(static_src)
     if force or _stale(kernels, srcs):
         asm = OUT / "images_gen.S"
         _write_images_asm(cubins, asm)
-        _run([cxx, *CXX_FLAGS, *inc, "-o", kernels, srcs[0], asm,
-              "-L", OUT, "-lhc-gpu-runtime-loader", "-ldl"], verbose)
+        # The one translation unit that uses the CUDA runtime API (it owns a
+        # __device__ array and needs cudaGetSymbolAddress): host + device code
+        # in one object, CUDA runtime linked statically.
+        static_obj = OUT / "w8a16_static.o"
+        _run([cuda / "bin" / "nvcc", *NVCC_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
+              "-cudart", "static", *inc, "-c", "-o", static_obj, static_src], verbose)
+        _run([cxx, *CXX_FLAGS, *inc, "-o", kernels, srcs[0], asm, static_obj,
+              "-L", OUT, "-lhc-gpu-runtime-loader", "-L", cuda / "lib64", "-lcudart_static",
+              "-lrt", "-lpthread", "-ldl"], verbose)
 
     pyinc = sysconfig.get_paths()["include"]
     have_python_headers = (Path(pyinc) / "Python.h").exists()

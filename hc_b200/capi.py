@@ -97,6 +97,9 @@ KERNELS_PROTOTYPES = {
         [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll],
     ),
     "hcDequantW8": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll]),
+    "hcGemmW8A16StaticMaxBytes": (_sz, []),
+    "hcGemmW8A16Static": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
+    "hcReportError": (C.c_int, [_vp, C.c_char_p]),
 }
 # include/hc_python_runtime.h
 PYRUNTIME_PROTOTYPES = {
@@ -259,6 +262,12 @@ class Context:
                 self.handle, a, w, scale, out, workspace, workspace_bytes, m, n, k, lda, ldw, ldc
             ),
             "hcGemmW8A16",
+        )
+
+    def gemm_w8a16_static(self, a, w, scale, out, m, n, k, lda, ldw, ldc):
+        self._check(
+            self.lib.hcGemmW8A16Static(self.handle, a, w, scale, out, m, n, k, lda, ldw, ldc),
+            "hcGemmW8A16Static",
         )
 
     def dequant_w8(self, w, out, rows, cols, w_pitch, out_pitch):

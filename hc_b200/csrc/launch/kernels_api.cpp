@@ -287,6 +287,10 @@ int hcKernelStatus(HcContext c, int *statusRet) {
   return 0;
 }
 
+int hcReportError(HcContext c, const char *text) {
+  return c ? c->fail("%s", text ? text : "") : 1;
+}
+
 int hcSetOption(HcContext c, const char *name, long long value) {
   if (!c || !name)
     return 1;

@@ -115,6 +115,30 @@ HC_B200_API int hcGemmW8A16(HcContext c, const void *a, const void *w,
                             long long K, long long lda, long long ldw,
                             long long ldc);
 
+/* hcGemmW8A16 without a caller-provided workspace, for callers that must not
+ * allocate device memory (a serving loop whose memory is handed out once at
+ * start-up; a host that lends the library a stream but owns all allocations).
+ * The converted weights go into a fixed scratch array built into the
+ * library's device image instead, so roundUp(N,16) * K * 2 bytes must not
+ * exceed hcGemmW8A16StaticMaxBytes() (32 MiB); larger problems are rejected
+ * with an error that says so.  All calls on a device share that array: calls
+ * ordered on one context are safe, calls whose GPU work overlaps race.  The
+ * first call on a device resolves the array's address and loads the kernel
+ * images; make it before starting any stream capture.  Later calls only look
+ * up cached state and launch.
+ * No counterpart in the reference: its runtime allocates with cuMemAlloc
+ * whenever asked (gpu-runtime/cuda-runtime/src/Runtime.cpp:242-256) and has no
+ * scratch-using kernels. */
+HC_B200_API size_t hcGemmW8A16StaticMaxBytes(void);
+HC_B200_API int hcGemmW8A16Static(HcContext c, const void *a, const void *w,
+                                  const float *scale, void *out, long long M,
+                                  long long N, long long K, long long lda,
+                                  long long ldw, long long ldc);
+
+/* Records `text` as the context's last error, reports it through the
+ * context's callback and returns 1.  For code layered on this library. */
+HC_B200_API int hcReportError(HcContext c, const char *text);
+
 /* The conversion step alone: out[k,n] = bf16(w[k,n]). */
 HC_B200_API int hcDequantW8(HcContext c, const void *w, void *out,
                             long long rows, long long cols, long long wPitch,
