@@ -39,6 +39,17 @@ SHAPES = {
 }
 
 
+# Reduced shapes for profiler captures (--small): the streaming kernels still
+# move more than the 126 MB L2 holds, but a launch lasts tens of microseconds.
+SMALL_SHAPES = {
+    "softmax": (8192, 4096),
+    "reduce": (16384, 8192),
+    "gemm_f32": (256, 256, 256),
+    "gemm_bf16": (2048, 2048, 2048),
+    "gemm_w8a16": (1024, 2048, 2048),
+}
+
+
 def algorithmic(name):
     """(bytes, flops, bound) one launch of the workload must move / compute."""
     s = SHAPES[name]
@@ -347,6 +358,8 @@ def run_gpu(args):
             "roofline": head["roofline"], "gpu_launches": head["launches"],
             "kernel_status": head["status"], "clocks": sampler.summary(),
         }
+        if args.small:
+            line["config"]["small"] = "reduced shape for profiling; not a benchmark result"
         if e2e is not None:
             line["e2e"] = e2e
         if extras:
@@ -372,8 +385,12 @@ def main():
     ap.add_argument("--impl", default="hc_b200", choices=["hc_b200", "reference"])
     ap.add_argument("--workload", default="softmax", choices=sorted(SHAPES))
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="reduced shapes, for profiler captures; not a benchmark result")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.small:
+        SHAPES.update(SMALL_SHAPES)
     if args.impl == "reference":
         run_reference(args)
     else:
