@@ -70,8 +70,11 @@ def algorithmic(name):
 # dram bytes per launch of the headline kernels from the ncu captures summarised
 # under profiles/ (None until a capture exists for that kernel).
 NCU_TRAFFIC = {
-    "softmax": None,
-    "reduce": None,
+    # profiles/softmax_rows_f32_w32_8192x4096.md: (134.26 + 79.48) MB for a quarter of
+    # the rows, scaled by 4 (the part of Y still in L2 at kernel end is not counted).
+    "softmax": 854.9e6,
+    # profiles/reduce_rows_warp_f32_16384x8192.md: (536.92 + 3.38) MB for a quarter of the rows.
+    "reduce": 2161.2e6,
     "gemm_bf16": None,
     "gemm_w8a16": None,
     "gemm_f32": None,
