@@ -104,7 +104,7 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbarInit(smemAddr(&bars->full[s]), Cfg::kCtas); // one expect_tx per CTA
+      mbarInit(smemAddr(&bars->full[s]), 1);          // the (leader's) expect_tx
       mbarInit(smemAddr(&bars->empty[s]), 1);         // one MMA commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -154,10 +154,14 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
             fullBar = mapSharedToCta(fullBar, 0);
           const uint32_t stage = smemBase + s * Cfg::kStageBytes;
           if constexpr (PAIR) {
-            asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::"
-                         "cluster.b64 _, [%0], %1;" ::"r"(fullBar),
-                         "r"(uint32_t(Cfg::kStageBytes))
-                         : "memory");
+            // Only the leader arrives, expecting the bytes of both CTAs.  The
+            // peer's copies may land before this arrival; they only drive the
+            // barrier's byte count negative for a moment, and the phase cannot
+            // complete before the leader has arrived.  (A remote
+            // arrive.expect_tx from the peer instead serialised the stages and
+            // halved the throughput.)
+            if (leader)
+              mbarExpectTx(smemAddr(&bars->full[s]), 2 * Cfg::kStageBytes);
             tmaLoad2DPair(stage, mapA, fullBar, kb * BK, row0);
             for (int ch = 0; ch < Cfg::kBChunks; ++ch)
               tmaLoad2DPair(stage + Cfg::kABytes + ch * Cfg::kBChunkBytes, mapB,

@@ -500,8 +500,9 @@ int hcGemmBf16(HcContext c, const void *a, const void *b, void *out,
     return 0;
   if (c->gemmVariant == 3 || !ummaEligible(c, a, b, K, lda, ldb))
     return hcGemmTiled(c, a, b, out, M, N, K, lda, ldb, ldc, HC_BF16);
-  // The CTA-pair kernel is opt-in: it measured slower than one CTA per tile.
-  const bool pair = c->gemmVariant == 2;
+  // A CTA pair per 256 x 256 tile moves a third less data per CTA than one CTA
+  // per 128 x 256 tile; it needs at least two row blocks to be worth a cluster.
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
   return launchUmma(c, a, b, nullptr, out, M, N, K, lda, ldb, ldc, pair);
 }
 
@@ -555,8 +556,9 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
                    workspaceBytes, hcGemmW8A16WorkspaceBytes(N, K));
   if (hcDequantW8(c, w, workspace, K, N, ldw, wsPitch))
     return 1;
-  // The CTA-pair kernel is opt-in: it measured slower than one CTA per tile.
-  const bool pair = c->gemmVariant == 2;
+  // A CTA pair per 256 x 256 tile moves a third less data per CTA than one CTA
+  // per 128 x 256 tile; it needs at least two row blocks to be worth a cluster.
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
   return launchUmma(c, a, workspace, scale, out, M, N, K, lda, wsPitch, ldc, pair);
 }
 

@@ -1,0 +1,128 @@
+"""Full-size parity: the five benchmark configurations at their real shapes.
+
+The CPU oracle cannot redo 10^12 flops in a test, so each configuration is
+checked (a) against the oracle on a sample of rows, computed from the same
+seeded inputs, and (b) through properties that do not depend on size:
+
+* softmax: rows sum to one, order of elements preserved, values in [0, 1];
+* reductions: max is bit-exact against the oracle on every row; the sum of
+  2x is exactly twice the sum of x (scaling by a power of two is exact, so
+  the reduction order must be the same in both runs);
+* GEMMs: scaling B by two scales the bf16 result by exactly two; computing a
+  row block (M-shard) or a column block (N-shard) alone gives bit-identical
+  values to the same block of the full result - which is what makes the
+  multi-GPU launcher's sharded output equal to the single-GPU output.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import workloads as oracle
+from tests.gpu_util import dev, dev_bf16, empty_like_dev, finish, host_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config1_fp32_gemm_256(hc, golden):
+    a, b = oracle.make_inputs("gemm_f32")
+    d_a, d_b, d_c = dev(a), dev(b), empty_like_dev((256, 256), torch.float32)
+    hc.gemm_tiled(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), 256, 256, 256, 256, 256, 256)
+    finish(hc)
+    got = d_c.cpu().numpy().astype(np.float64)
+    bound = 1e-5 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64))
+    assert np.all(np.abs(got - golden["cfg1_gemm_f32_256"]) <= bound)
+    # Relative form of the same statement: well inside 1e-5 of the result scale.
+    assert np.abs(got - golden["cfg1_gemm_f32_256"]).max() <= 1e-5 * np.abs(got).max()
+
+
+def test_config2_softmax_32768x4096(hc):
+    m, n = 32768, 4096
+    (x,) = oracle.make_inputs("softmax")
+    d_x, d_y = dev(x), empty_like_dev((m, n), torch.float32)
+    hc.softmax_rows(d_x.data_ptr(), d_y.data_ptr(), m, n, n, n)
+    finish(hc)
+    sums = d_y.sum(dim=1, dtype=torch.float64)
+    assert torch.all((sums - 1).abs() < 1e-5)
+    assert float(d_y.min()) >= 0.0 and float(d_y.max()) <= 1.0
+    assert torch.equal(d_y.argmax(dim=1), d_x.argmax(dim=1))
+    rows = np.r_[0:64, 16000:16064, m - 64:m]
+    expect = np.zeros((len(rows), n), np.float32)
+    oracle.softmax_rows(x[rows], expect, 32)
+    got = d_y[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert np.all(np.abs(got - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+
+
+def test_config3_row_sum_and_max_65536x8192(hc):
+    m, n = 65536, 8192
+    (x,) = oracle.make_inputs("reduce")
+    d_x = dev(x)
+    d_s, d_m = empty_like_dev((m,), torch.float32), empty_like_dev((m,), torch.float32)
+    hc.reduce_rows(d_x.data_ptr(), d_s.data_ptr(), d_m.data_ptr(), m, n, n)
+    finish(hc)
+    got_s, got_m = d_s.cpu().numpy(), d_m.cpu().numpy()
+    assert np.array_equal(got_m, x.max(axis=1))  # bit-exact on every row
+    rows = np.r_[0:256, 40000:40256, m - 256:m]
+    exact = x[rows].astype(np.float64).sum(axis=1)
+    bound = 1e-5 * np.abs(x[rows]).astype(np.float64).sum(axis=1)
+    assert np.all(np.abs(got_s[rows] - exact) <= bound)
+    d_x.mul_(2.0)
+    d_s2 = empty_like_dev((m,), torch.float32)
+    hc.reduce_rows(d_x.data_ptr(), d_s2.data_ptr(), 0, m, n, n)
+    finish(hc)
+    assert np.array_equal(d_s2.cpu().numpy(), 2.0 * got_s)
+
+
+def _bf16_close(got, expect, mag):
+    return np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * mag)
+
+
+def test_config4_bf16_gemm_8192(hc):
+    m = n = k = 8192
+    a, b = oracle.make_inputs("gemm_bf16")
+    d_a, d_b = dev_bf16(a), dev_bf16(b)
+    d_c = empty_like_dev((m, n), torch.bfloat16)
+    hc.gemm_bf16(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), m, n, k, k, n, n)
+    finish(hc)
+    rows = np.r_[0:32, 4000:4032, m - 32:m]
+    expect = oracle.round_to_bf16(a[rows] @ b)  # the oracle's full-K GEMM on these rows
+    got = host_bf16(d_c[torch.from_numpy(rows).cuda()])
+    assert _bf16_close(got, expect, np.abs(a[rows]) @ np.abs(b))
+
+    # M-shard: rows [2048, 4096) computed alone equal the same rows of the full result.
+    d_part = empty_like_dev((2048, n), torch.bfloat16)
+    hc.gemm_bf16(d_a[2048:].data_ptr(), d_b.data_ptr(), d_part.data_ptr(), 2048, n, k, k, n, n)
+    finish(hc)
+    assert torch.equal(d_part.view(torch.int16), d_c[2048:4096].view(torch.int16))
+
+    # Scaling B by two scales the result by exactly two.
+    d_b.mul_(2.0)
+    d_c2 = empty_like_dev((m, n), torch.bfloat16)
+    hc.gemm_bf16(d_a.data_ptr(), d_b.data_ptr(), d_c2.data_ptr(), m, n, k, k, n, n)
+    finish(hc)
+    assert torch.equal(d_c2.float(), 2.0 * d_c.float())
+
+
+def test_config5_w8a16_4096x8192x8192(hc):
+    m, n, k = 4096, 8192, 8192
+    a, w, s = oracle.make_inputs("gemm_w8a16")
+    d_a, d_w, d_s = dev_bf16(a), dev(w), dev(s)
+    d_c = empty_like_dev((m, n), torch.bfloat16)
+    ws_bytes = hc.gemm_w8a16_workspace_bytes(n, k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    hc.gemm_w8a16(d_a.data_ptr(), d_w.data_ptr(), d_s.data_ptr(), d_c.data_ptr(), ws.data_ptr(),
+                  ws_bytes, m, n, k, k, n, n)
+    finish(hc)
+    rows = np.r_[0:16, 2000:2016, m - 16:m]
+    expect = oracle.round_to_bf16((a[rows] @ w.astype(np.float32)) * s)
+    got = host_bf16(d_c[torch.from_numpy(rows).cuda()])
+    assert _bf16_close(got, expect, np.abs(a[rows]) @ (np.abs(w.astype(np.float32)) * s))
+
+    # N-shard: columns [1024, 2048) computed alone (as one rank of eight would).
+    d_part = empty_like_dev((m, n), torch.bfloat16)
+    hc.gemm_w8a16(d_a.data_ptr(), d_w[:, 1024:].data_ptr(), d_s[1024:].data_ptr(),
+                  d_part[:, 1024:].data_ptr(), ws.data_ptr(), ws_bytes, m, 1024, k, k, n, n)
+    finish(hc)
+    assert torch.equal(d_part[:, 1024:2048].contiguous().view(torch.int16),
+                       d_c[:, 1024:2048].contiguous().view(torch.int16))
