@@ -456,7 +456,7 @@ static int launchUmma(HcContext c, const void *a, const void *b,
   int tilesM = int(ceilDiv(M, tileM)), tilesN = int(ceilDiv(N, kUmmaBN));
   // Tiles that run concurrently should form a compact block of the output so
   // that the A and B panels they share stay in L2.
-  int bandM = pair ? 8 : 16;
+  int bandM = 16;
   int vecStore = aligned(out, 16) && ldc % 8 == 0;
   long long tiles = (long long)tilesM * tilesN;
   const char *name = pair ? (scale ? "hc_gemm_bf16_umma_pair_scaled"
