@@ -9,13 +9,19 @@ roofline, next to the CPU restatement of the reference timed on the host cores.
 One JSON line is printed by rank 0.  The headline workload is the row softmax
 over X[32768, 4096] fp32 (HBM-bound); ``metric`` is its algorithmic throughput
 in GB/s: bytes that must move (read X once, write Y once) divided by the time
-of the timed region.  ``--workload`` selects another headline
-(``reduce``, ``gemm_f32``, ``gemm_bf16``, ``gemm_w8a16``); with the default
-headline the other four are measured too and reported under ``workloads``.
+of the timed region.  ``--workload`` selects another headline (``reduce``,
+``gemm_f32``, ``gemm_bf16``, ``gemm_w8a16``; GEMMs report TFLOP/s); with the
+default headline the other four are measured too and reported under
+``workloads``.
 
-Scaling is weak: every rank runs the full single-GPU workload on its own rows
-(the shards are independent, so there is no collective in the timed path);
-``value`` is the sum over ranks divided by the slowest rank's time.
+* ``value``  device-resident inputs, the C++ dispatcher called directly,
+             CUDA events on the stream the kernels run on.
+* ``e2e``    the same workload through the public ``@kernel`` call with HOST
+             buffers: per step a pinned host->device copy of the inputs, the
+             call, and a device->host copy of the result.
+* scaling is weak: every rank runs the full single-GPU workload on its own
+  rows (shards are independent, so no collective is in the timed path);
+  ``value`` is the sum over ranks divided by the slowest rank's time.
 """
 
 import argparse
@@ -29,7 +35,7 @@ import time
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-# Algorithmic work of each workload at its full size.
+# Full-size shapes of the five configurations.
 SHAPES = {
     "softmax": (32768, 4096),
     "reduce": (65536, 8192),
@@ -37,7 +43,6 @@ SHAPES = {
     "gemm_bf16": (8192, 8192, 8192),
     "gemm_w8a16": (4096, 8192, 8192),
 }
-
 
 # Reduced shapes for profiler captures (--small): the streaming kernels still
 # move more than the 126 MB L2 holds, but a launch lasts tens of microseconds.
@@ -48,6 +53,16 @@ SMALL_SHAPES = {
     "gemm_bf16": (2048, 2048, 2048),
     "gemm_w8a16": (1024, 2048, 2048),
 }
+
+METRIC = {
+    "softmax": "softmax_rows_f32_algorithmic_bandwidth",
+    "reduce": "reduce_rows_f32_algorithmic_bandwidth",
+    "gemm_f32": "gemm_f32_tiled_throughput",
+    "gemm_bf16": "gemm_bf16_throughput",
+    "gemm_w8a16": "gemm_w8a16_throughput",
+}
+DTYPE = {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32", "gemm_bf16": "bf16",
+         "gemm_w8a16": "bf16"}
 
 
 def algorithmic(name):
@@ -67,8 +82,22 @@ def algorithmic(name):
     return m * k * 2 + k * n + n * 4 + m * n * 2, 2 * m * n * k, "tensor"
 
 
-# dram bytes per launch of the headline kernels from the ncu captures summarised
-# under profiles/ (None until a capture exists for that kernel).
+def unit_of(name):
+    return "GB/s" if algorithmic(name)[2] == "hbm" else "TFLOP/s"
+
+
+def throughput(name, seconds, scale=1.0):
+    """Algorithmic throughput in the workload's unit for `scale` x full size."""
+    nbytes, flops, bound = algorithmic(name)
+    return (nbytes * scale / seconds / 1e9) if bound == "hbm" else (flops * scale / seconds / 1e12)
+
+
+def describe(name):
+    return f"{name} {list(SHAPES[name])} per GPU"
+
+
+# dram bytes per launch from the ncu captures summarised under profiles/ (None
+# where no capture scales to the full-size launch).
 NCU_TRAFFIC = {
     # profiles/softmax_rows_f32_w32_8192x4096.md: (134.26 + 79.48) MB for a quarter of
     # the rows, scaled by 4 (the part of Y still in L2 at kernel end is not counted).
@@ -151,49 +180,101 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-# ---- CPU arm ----------------------------------------------------------------------------
-def cpu_softmax_sample(rows, threads, repeats):
-    """Times the oracle's softmax (oracle/workloads.py) on `rows` rows of the
-    headline workload; returns (GB/s, seconds per pass)."""
+# ---- CPU arm: the oracle (NumPy port of the reference simulator) --------------------------
+def cpu_sample(name, threads, repeats):
+    """Time the oracle on a bounded sample of workload `name`.
+
+    Returns (throughput in the workload's unit, seconds per pass, description).
+    The sample is a block of rows of the full-size problem, so that a pass takes
+    a fraction of a second to a few seconds on one host.
+    """
     import numpy as np
 
     from oracle import workloads as oracle
 
-    (x,) = oracle.make_inputs("softmax", shape=(rows, SHAPES["softmax"][1]))
-    out = np.empty_like(x)
+    try:
+        from threadpoolctl import threadpool_limits
+    except ImportError:  # BLAS then uses its own default thread count
+        from contextlib import nullcontext as threadpool_limits
 
-    def one_pass():
-        oracle.run_row_groups_parallel(
-            lambda r0, r1: oracle.softmax_rows(x[r0:r1], out[r0:r1], 256), rows, 256, threads)
+    s = SHAPES[name]
+    if name == "softmax":
+        rows = min(s[0], 8192 if threads > 1 else 4096)
+        (x,) = oracle.make_inputs("softmax", shape=(rows, s[1]))
+        out = np.empty_like(x)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows"
 
-    one_pass()
-    t0 = time.perf_counter()
-    for _ in range(repeats):
+        def one_pass():
+            oracle.run_row_groups_parallel(
+                lambda r0, r1: oracle.softmax_rows(x[r0:r1], out[r0:r1], 256), rows, 256, threads)
+    elif name == "reduce":
+        rows = min(s[0], 8192 if threads > 1 else 4096)
+        (x,) = oracle.make_inputs("reduce", shape=(rows, s[1]))
+        so, mo = np.empty(rows, np.float32), np.empty(rows, np.float32)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows"
+
+        def one_pass():
+            oracle.run_row_groups_parallel(
+                lambda r0, r1: oracle.reduce_rows(x[r0:r1], so[r0:r1], mo[r0:r1], 256),
+                rows, 256, threads)
+    elif name == "gemm_f32":
+        a, b = oracle.make_inputs("gemm_f32", shape=s)
+        out = np.zeros((s[0], s[1]), np.float32)
+        scale = 1.0
+        what = "the full 256^3 problem, 64x64 groups, KB=16"
+
+        def one_pass():
+            oracle.gemm_kblocked(a, b, out, (64, 64), kb=16)
+    elif name == "gemm_bf16":
+        rows = min(s[0], 512)
+        a, b = oracle.make_inputs("gemm_bf16", shape=(rows, s[1], s[2]))
+        out = np.zeros((rows, s[1]), np.float32)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows of A against the full B, 256x256 groups"
+
+        def one_pass():
+            oracle.gemm_bf16(a, b, out, (256, 256))
+    else:
+        rows = min(s[0], 256)
+        a, w, sc = oracle.make_inputs("gemm_w8a16", shape=(rows, s[1], s[2]))
+        out = np.zeros((rows, s[1]), np.float32)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows of A against the full W, 256x256 groups"
+
+        def one_pass():
+            oracle.gemm_w8a16(a, w, sc, out, (256, 256))
+
+    with threadpool_limits(limits=threads):
         one_pass()
-    dt = (time.perf_counter() - t0) / repeats
-    return 2 * x.nbytes / dt / 1e9, dt
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            one_pass()
+        dt = (time.perf_counter() - t0) / repeats
+    return throughput(name, dt, scale), dt, what
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
+    name = args.workload
     threads = len(os.sched_getaffinity(0))
-    rows = 8192  # one step = a quarter of the 32768-row workload
     t0 = time.perf_counter()
-    gbs, dt = cpu_softmax_sample(rows, threads, max(1, args.warmup))  # warm-up passes
-    gbs, dt = cpu_softmax_sample(rows, threads, max(1, args.steps))
-    sample = f"{rows} of 32768 rows per step, NumPy oracle, {threads} threads"
+    # Heavy samples get fewer passes so that any --steps stays within minutes.
+    passes = max(1, min(args.steps, 20 if name in ("softmax", "reduce", "gemm_f32") else 5))
+    value, dt, what = cpu_sample(name, threads, passes)
+    sample = f"{what}; NumPy oracle on {threads} threads; {passes} timed passes"
     line = {
-        "impl": "reference", "metric": "softmax_rows_f32_algorithmic_bandwidth", "value": gbs,
-        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "impl": "reference", "metric": METRIC[name], "value": value, "unit": unit_of(name),
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "row softmax fp32 X[32768,4096] (bounded sample per step)",
-                   "rows_per_step": rows, "cols": 4096},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+        "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
+        "config": {"workload": describe(name), "sample_per_step": what},
+        "cpu_baseline": {"value": value, "unit": unit_of(name), "cores": threads, "kind": "port",
                          "sample": sample},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": value, "unit": unit_of(name), "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
@@ -204,10 +285,10 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
 
+    from hc_b200._native import _dispatcher as native
     from hc_b200.hckernel.kernel import get_context
     from hc_b200.launcher import init_process_group
     from hc_b200.workloads import make_kernels
-    from hc_b200._native import _dispatcher as native
 
     rank, world, local = init_process_group()
     if world != args.gpus:
@@ -248,132 +329,141 @@ def run_gpu(args):
         barrier()
         return max_over_ranks(e0.elapsed_time(e1)), ctx.launch_count - before
 
-    def measure(name, steps, warmup):
-        """Device-resident throughput of one workload; returns a result dict."""
-        nbytes, flops, bound = algorithmic(name)
+    def device_inputs(name):
+        """Device-resident synthetic inputs and outputs of one workload."""
         g = torch.Generator(device=dev).manual_seed(1000 + rank)
+        s = SHAPES[name]
         if name == "softmax":
-            m, n = SHAPES[name]
-            x = torch.randn(m, n, device=dev, generator=g)
-            y = torch.empty_like(x)
-            fn = lambda: native.softmax_rows(ctx, x, y)  # noqa: E731
-        elif name == "reduce":
-            m, n = SHAPES[name]
-            x = torch.rand(m, n, device=dev, generator=g) * 20 - 10
-            s, mx = torch.empty(m, device=dev), torch.empty(m, device=dev)
-            fn = lambda: native.reduce_rows(ctx, x, s, mx)  # noqa: E731
-        elif name == "gemm_f32":
-            m, n, k = SHAPES[name]
+            x = torch.randn(*s, device=dev, generator=g)
+            return [x], [torch.empty_like(x)]
+        if name == "reduce":
+            x = torch.rand(*s, device=dev, generator=g) * 20 - 10
+            return [x], [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
+        m, n, k = s
+        if name == "gemm_f32":
             a = torch.rand(m, k, device=dev, generator=g) * 2 - 1
             b = torch.rand(k, n, device=dev, generator=g) * 2 - 1
-            c = torch.empty(m, n, device=dev)
-            fn = lambda: native.gemm(ctx, a, b, c)  # noqa: E731
-        elif name == "gemm_bf16":
-            m, n, k = SHAPES[name]
+            return [a, b], [torch.empty(m, n, device=dev)]
+        if name == "gemm_bf16":
             a = (torch.randn(m, k, device=dev, generator=g) * 0.02).bfloat16()
             b = (torch.randn(k, n, device=dev, generator=g) * 0.02).bfloat16()
-            c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-            fn = lambda: native.gemm(ctx, a, b, c)  # noqa: E731
-        else:
-            m, n, k = SHAPES[name]
-            a = torch.randn(m, k, device=dev, generator=g).bfloat16()
-            w = torch.randint(-127, 128, (k, n), device=dev, generator=g, dtype=torch.int8)
-            sc = torch.rand(n, device=dev, generator=g) * 0.019 + 0.001
-            c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-            ws = torch.empty(native.w8a16_workspace_bytes(n, k), dtype=torch.uint8, device=dev)
-            fn = lambda: native.gemm_w8a16(ctx, a, w, sc, c, ws)  # noqa: E731
+            return [a, b], [torch.empty(m, n, device=dev, dtype=torch.bfloat16)]
+        a = torch.randn(m, k, device=dev, generator=g).bfloat16()
+        w = torch.randint(-127, 128, (k, n), device=dev, generator=g, dtype=torch.int8)
+        sc = torch.rand(n, device=dev, generator=g) * 0.019 + 0.001
+        return [a, w, sc], [torch.empty(m, n, device=dev, dtype=torch.bfloat16)]
+
+    def direct_call(name, ins, outs):
+        """The C++ dispatcher entry of the workload (no Python front door)."""
+        if name == "softmax":
+            return lambda: native.softmax_rows(ctx, ins[0], outs[0])
+        if name == "reduce":
+            return lambda: native.reduce_rows(ctx, ins[0], outs[0], outs[1])
+        if name in ("gemm_f32", "gemm_bf16"):
+            return lambda: native.gemm(ctx, ins[0], ins[1], outs[0])
+        n, k = ins[1].shape[1], ins[1].shape[0]
+        ws = torch.empty(native.w8a16_workspace_bytes(n, k), dtype=torch.uint8, device=dev)
+        return lambda: native.gemm_w8a16(ctx, ins[0], ins[1], ins[2], outs[0], ws)
+
+    def public_call(name, ins, outs):
+        """The same workload through the @kernel call surface."""
+        if name == "softmax":
+            return lambda: kernels.softmax(ins[0], outs[0], 256)
+        if name == "reduce":
+            return lambda: kernels.reduce_rows(ins[0], outs[0], outs[1], 256)
+        if name == "gemm_f32":
+            return lambda: kernels.dot(ins[0], ins[1], outs[0], (64, 64))
+        if name == "gemm_bf16":
+            return lambda: kernels.dot_fullk(ins[0], ins[1], outs[0], (256, 256))
+        return lambda: kernels.dequant_dot(ins[0], ins[1], ins[2], outs[0], (256, 256))
+
+    def roofline(name, per_step_ms):
+        nbytes, flops, bound = algorithmic(name)
+        if bound == "hbm":
+            ach = nbytes / per_step_ms / 1e6
+            return ach, {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name],
+                         "peak_source": peaks["source"]}
+        ach = flops / per_step_ms / 1e9
+        return ach, {"bound": "tensor" if bound == "tensor" else "latency", "achieved": ach,
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": ach / peaks["bf16_tflops"],
+                     "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
+                     "traffic": NCU_TRAFFIC[name], "peak_source": peaks["source"]}
+
+    def measure(name, steps, warmup):
+        """Device-resident throughput of one workload; returns a result dict."""
+        ins, outs = device_inputs(name)
+        fn = direct_call(name, ins, outs)
         torch.cuda.synchronize(dev)
         ms, launches = timed(fn, steps, warmup)
-        status = ctx.kernel_status()
-        per_step = ms / steps
-        out = {"ms_per_step": per_step, "steps": steps, "launches": launches, "status": status}
-        if bound == "hbm":
-            ach = nbytes / per_step / 1e6
-            out.update(value=ach * world, unit="GB/s",
-                       roofline={"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
-                                 "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                                 "traffic": NCU_TRAFFIC[name], "peak_source": peaks["source"]})
-        else:
-            ach = flops / per_step / 1e9
-            out.update(value=ach * world, unit="TFLOP/s",
-                       roofline={"bound": "tensor" if bound == "tensor" else "latency",
-                                 "achieved": ach, "peak": peaks["bf16_tflops"],
-                                 "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                                 "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
-                                 "traffic": NCU_TRAFFIC[name], "peak_source": peaks["source"]})
-        return out
+        ach, roof = roofline(name, ms / steps)
+        return {"ms_per_step": ms / steps, "steps": steps, "launches": launches,
+                "status": ctx.kernel_status(), "value": ach * world, "unit": roof["unit"],
+                "roofline": roof}
 
     def measure_e2e(name, steps, warmup):
-        """Same workload through the public call surface with HOST buffers: per
-        step, pinned host -> device copy of the inputs, the @kernel call, and a
-        device -> host copy of the result."""
-        if name != "softmax":
-            return None
-        m, n = SHAPES[name]
-        hx = torch.randn(m, n).pin_memory()
-        hy = torch.empty(m, n).pin_memory()
-        dx, dy = torch.empty(m, n, device=dev), torch.empty(m, n, device=dev)
+        """Host buffers in, host buffers out, through the public call surface."""
+        ins, outs = device_inputs(name)
+        h_ins = [t.cpu().pin_memory() for t in ins]
+        h_outs = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
+        call = public_call(name, ins, outs)
 
         def step():
             with torch.cuda.stream(stream):
-                dx.copy_(hx, non_blocking=True)
-                kernels.softmax(dx, dy, 256)
-                hy.copy_(dy, non_blocking=True)
+                for d, h in zip(ins, h_ins):
+                    d.copy_(h, non_blocking=True)
+                call()
+                for h, d in zip(h_outs, outs):
+                    h.copy_(d, non_blocking=True)
 
-        ms, launches = timed(step, steps, warmup)
-        nbytes, _, _ = algorithmic(name)
-        row_sums = hy[:64].sum(dim=1)
-        assert torch.allclose(row_sums, torch.ones_like(row_sums), atol=1e-4), "softmax rows != 1"
-        return {"value": nbytes * world / (ms / steps) / 1e6, "unit": "GB/s",
-                "h2d_bytes_per_step": hx.numel() * 4, "d2h_bytes_per_step": hy.numel() * 4,
+        ms, _ = timed(step, steps, warmup)
+        if name == "softmax":  # the result really came back
+            sums = h_outs[0][:64].sum(dim=1)
+            assert torch.allclose(sums, torch.ones_like(sums), atol=1e-4), "softmax rows != 1"
+        ach, roof = roofline(name, ms / steps)
+        return {"value": ach * world, "unit": roof["unit"],
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in h_ins),
+                "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in h_outs),
                 "ms_per_step": ms / steps, "steps": steps}
 
+    name = args.workload
     sampler = ClockSampler(local)
     with sampler:
-        head = measure(args.workload, args.steps, args.warmup)
-        e2e = measure_e2e(args.workload, max(3, min(args.steps, 20)), 3)
+        head = measure(name, args.steps, args.warmup)
+        e2e = measure_e2e(name, max(3, min(args.steps, 20)), 3)
         extras = {}
-        if args.workload == "softmax" and not args.no_extras:
-            for name, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
-                                ("gemm_f32", 500)):
-                extras[name] = measure(name, steps, 5)
+        if name == "softmax" and not args.no_extras:
+            for other, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
+                                 ("gemm_f32", 500)):
+                # Each kernel is timed alone: let the board's power state settle
+                # after the previous one (a dense GEMM runs into the 1 kW cap and
+                # would hand lower clocks to whatever is measured right after it).
+                time.sleep(1.5)
+                extras[other] = measure(other, steps, 5)
 
     if rank == 0:
-        nbytes, flops, bound = algorithmic(args.workload)
-        metric = {
-            "softmax": "softmax_rows_f32_algorithmic_bandwidth",
-            "reduce": "reduce_rows_f32_algorithmic_bandwidth",
-            "gemm_f32": "gemm_f32_tiled_throughput",
-            "gemm_bf16": "gemm_bf16_throughput",
-            "gemm_w8a16": "gemm_w8a16_throughput",
-        }[args.workload]
         line = {
-            "metric": metric, "value": head["value"], "unit": head["unit"], "n_gpus": world,
+            "metric": METRIC[name], "value": head["value"], "unit": head["unit"], "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32",
-                      "gemm_bf16": "bf16", "gemm_w8a16": "bf16"}[args.workload],
-            "data": "synthetic",
-            "config": {"workload": f"{args.workload} {list(SHAPES[args.workload])} per GPU",
-                       "rows_or_tiles_sharded": "independent shards, no collective in the timed path",
+            "dtype": DTYPE[name], "data": "synthetic",
+            "config": {"workload": describe(name),
+                       "sharding": "independent shards, no collective in the timed path",
                        "l2": "inputs and outputs larger than L2 (no flush needed)"
-                       if args.workload != "gemm_f32" else "operands fit in L2 (latency-bound case)"},
+                       if name != "gemm_f32" else "operands fit in L2 (latency-bound case)"},
             "roofline": head["roofline"], "gpu_launches": head["launches"],
-            "kernel_status": head["status"], "clocks": sampler.summary(),
+            "kernel_status": head["status"], "clocks": sampler.summary(), "e2e": e2e,
         }
         if args.small:
             line["config"]["small"] = "reduced shape for profiling; not a benchmark result"
-        if e2e is not None:
-            line["e2e"] = e2e
         if extras:
             line["workloads"] = extras
         if world == 1 and not args.no_cpu_baseline:
-            threads = 1
-            gbs, dt = cpu_softmax_sample(4096, threads, 5)
-            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads,
+            value, dt, what = cpu_sample(name, 1, 3)
+            line["cpu_baseline"] = {"value": value, "unit": unit_of(name), "cores": 1,
                                     "kind": "port",
-                                    "sample": "4096 of 32768 rows of the softmax workload, "
-                                              "5 passes, NumPy oracle, single thread"}
+                                    "sample": f"{what}; NumPy oracle, single thread, 3 passes"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -388,9 +478,9 @@ def main():
     ap.add_argument("--impl", default="hc_b200", choices=["hc_b200", "reference"])
     ap.add_argument("--workload", default="softmax", choices=sorted(SHAPES))
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="reduced shapes, for profiler captures; not a benchmark result")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.small:
         SHAPES.update(SMALL_SHAPES)

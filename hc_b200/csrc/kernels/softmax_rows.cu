@@ -180,6 +180,180 @@ HC_SOFTMAX_WARP(8, 8)
 HC_SOFTMAX_WARP(16, 5)
 HC_SOFTMAX_WARP(32, 3)
 
+// ---- bulk-copy pipelined variant --------------------------------------------------
+// One persistent CTA per SM: a producer thread streams whole rows into a ring
+// of shared-memory slots with cp.async.bulk (completion counted on an mbarrier
+// per slot), eight consumer warps each take a landed row into registers, free
+// the slot at once, and then compute and store from registers.  Loads for the
+// next dozen rows stay in flight while the current rows are exponentiated and
+// written, which the register-only kernel above cannot do (a warp there has
+// nothing in flight between its load burst and its store burst).
+namespace {
+
+constexpr int kTmaMaxSlots = 16;
+
+struct TmaBarriers {
+  uint64_t full[kTmaMaxSlots];
+  uint64_t empty[kTmaMaxSlots];
+  int abortFlag;
+};
+
+__device__ __forceinline__ void bulkLoad(uint32_t dst, const void *src,
+                                         uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::"
+               "bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Which slot, and which use of that slot, iteration i of a CTA maps to.  Rows
+// are dealt to the C consumer warps round-robin and every warp owns `depth`
+// slots of its own, so all uses of a slot are waited for by ONE warp, in
+// order.  (With slots shared between warps a fast warp could wait for the
+// second use of a slot before the first had landed; a parity wait cannot tell
+// "not yet" from "already over", and the ring would come apart.)
+template <int C>
+__device__ __forceinline__ void slotOf(long long i, int depth, int &slot,
+                                       uint32_t &phase) {
+  const long long turn = i / C; // how many rows this warp has taken before
+  slot = int(i % C) + C * int(turn % depth);
+  phase = uint32_t(turn / depth) & 1u;
+}
+
+// `cols` is a multiple of 4 and at most 128 * V; pitches are multiples of 4
+// elements and the bases 16-byte aligned, so every row is a legal bulk copy.
+// C * depth rows of `slotBytes` each fit in the dynamic shared memory.
+template <int V, int C>
+__device__ __forceinline__ void
+softmaxTmaRows(const float *__restrict__ x, float *__restrict__ y,
+               long long rows, int cols, long long xPitch, long long yPitch,
+               int depth, int slotBytes, int *status, unsigned char *smemRaw) {
+  const uint32_t ring = (hc::smemAddr(smemRaw) + 127u) & ~127u;
+  unsigned char *ringPtr = smemRaw + (ring - hc::smemAddr(smemRaw));
+  const int slots = C * depth;
+  TmaBarriers *bars =
+      reinterpret_cast<TmaBarriers *>(ringPtr + (size_t)slots * slotBytes);
+  volatile int *abortFlag = &bars->abortFlag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < slots; ++s) {
+      hc::mbarInit(hc::smemAddr(&bars->full[s]), 1);
+      hc::mbarInit(hc::smemAddr(&bars->empty[s]), 1);
+    }
+    bars->abortFlag = 0;
+    hc::fenceBarrierInit();
+  }
+  __syncthreads();
+
+  // Row of iteration i for this CTA: blockIdx.x + i * gridDim.x.
+  const long long myRows =
+      rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint32_t rowBytes = uint32_t(cols) * 4u;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (long long i = 0; i < myRows; ++i) {
+        int s;
+        uint32_t phase;
+        slotOf<C>(i, depth, s, phase);
+        if (!hc::mbarWait(hc::smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag,
+                          status, hc::kStatusProducerWait))
+          break;
+        const long long r = blockIdx.x + i * (long long)gridDim.x;
+        const uint32_t bar = hc::smemAddr(&bars->full[s]);
+        hc::mbarExpectTx(bar, rowBytes);
+        bulkLoad(ring + uint32_t(s) * uint32_t(slotBytes), x + r * xPitch,
+                 rowBytes, bar);
+      }
+      if (*abortFlag) { // copies may still be landing: give them time
+        const unsigned long long t0 = hc::globalTimerNs();
+        while (hc::globalTimerNs() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else {
+    const int cw = warp - 1;
+    const int packets = cols >> 2;
+    for (long long i = cw; i < myRows; i += C) {
+      int s;
+      uint32_t phase;
+      slotOf<C>(i, depth, s, phase);
+      bool ok = true;
+      if (lane == 0)
+        ok = hc::mbarWait(hc::smemAddr(&bars->full[s]), phase, abortFlag, status,
+                          hc::kStatusEpilogueWait);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok)
+        break;
+      const float4 *src =
+          reinterpret_cast<const float4 *>(ringPtr + (size_t)s * slotBytes);
+      float4 v[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int p = lane + 32 * j;
+        v[j] = p < packets
+                   ? src[p]
+                   : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+      // The row is in registers: hand the slot back before computing.
+      __syncwarp();
+      if (lane == 0)
+        hc::mbarArrive(hc::smemAddr(&bars->empty[s]));
+
+      float m = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        m = hc::maxNan(hc::maxNan(hc::maxNan(v[j].x, v[j].y),
+                                  hc::maxNan(v[j].z, v[j].w)),
+                       m);
+      m = warpMax(m);
+      const float shift = (m == -INFINITY) ? 0.f : m * kLog2e;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        v[j].x = fastExp2(fmaf(v[j].x, kLog2e, -shift));
+        v[j].y = fastExp2(fmaf(v[j].y, kLog2e, -shift));
+        v[j].z = fastExp2(fmaf(v[j].z, kLog2e, -shift));
+        v[j].w = fastExp2(fmaf(v[j].w, kLog2e, -shift));
+        s0 += v[j].x + v[j].z;
+        s1 += v[j].y + v[j].w;
+      }
+      const float inv = 1.0f / warpSum(s0 + s1);
+      const long long r = blockIdx.x + i * (long long)gridDim.x;
+      float4 *dst = reinterpret_cast<float4 *>(y + r * yPitch);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int p = lane + 32 * j;
+        if (p < packets)
+          hc::storeStream(dst + p, make_float4(v[j].x * inv, v[j].y * inv,
+                                               v[j].z * inv, v[j].w * inv));
+      }
+    }
+  }
+  // Nobody leaves while a bulk copy could still target this CTA's memory: the
+  // consumers have waited for every copy they used, and after an abort the
+  // producer has waited above.
+  __syncthreads();
+}
+
+} // namespace
+
+// V float4 per lane, C consumer warps (+ 1 producer warp).
+#define HC_SOFTMAX_TMA(V, C)                                                   \
+  extern "C" __global__ void __launch_bounds__(32 * (C + 1), 1)                \
+      hc_softmax_rows_f32_tma_v##V(const float *x, float *y, long long rows,   \
+                                   int cols, long long xPitch,                 \
+                                   long long yPitch, int depth, int slotBytes, \
+                                   int *status) {                              \
+    extern __shared__ __align__(128) unsigned char tmaSmem[];                  \
+    softmaxTmaRows<V, C>(x, y, rows, cols, xPitch, yPitch, depth, slotBytes,   \
+                         status, tmaSmem);                                     \
+  }
+
+HC_SOFTMAX_TMA(16, 8)
+HC_SOFTMAX_TMA(32, 6)
+
 extern "C" __global__ void __launch_bounds__(256)
     hc_softmax_rows_generic_f32(const float *x, float *y, long long rows,
                                 long long cols, long long xPitch,

@@ -409,3 +409,22 @@ def test_gemm_w8a16_needs_workspace(hc):
     with pytest.raises(capi.HcError, match="workspace"):
         hc.gemm_w8a16(d_a.data_ptr(), d_w.data_ptr(), d_s.data_ptr(), d_c.data_ptr(), 0, 0,
                       128, 256, 512, 512, 256, 256)
+
+
+# ---- softmax kernel variants ------------------------------------------------------------
+@pytest.mark.parametrize("variant", [1, 2])  # 1: row in registers, 2: bulk-copy pipeline
+@pytest.mark.parametrize("rows,cols", [(40, 2048), (7, 3000), (600, 4096), (3000, 1028),
+                                       (149, 1280), (5000, 4096)])
+def test_softmax_variants_agree_with_oracle(hc, variant, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = (rng.standard_normal((rows, cols)) * 2).astype(np.float32)
+    d_x, d_y = dev(x), empty_like_dev(x.shape, torch.float32)
+    hc.set_option("softmax_variant", variant)
+    try:
+        hc.softmax_rows(d_x.data_ptr(), d_y.data_ptr(), rows, cols, cols, cols)
+        finish(hc)
+    finally:
+        hc.set_option("softmax_variant", 0)
+    expect = np.zeros_like(x)
+    oracle.softmax_rows(x, expect, 8)
+    _softmax_check(d_y.cpu().numpy(), expect)
