@@ -15,20 +15,25 @@ hc_img_name_2: .asciz "reduce_rows"
 hc_img_begin_2: .incbin "/root/repo/hc_b200/_native/reduce_rows.cubin"
 hc_img_end_2:
 .balign 16
-hc_img_name_3: .asciz "gemm_tiled"
+hc_img_name_3: .asciz "reduce_all"
 .balign 16
-hc_img_begin_3: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
+hc_img_begin_3: .incbin "/root/repo/hc_b200/_native/reduce_all.cubin"
 hc_img_end_3:
 .balign 16
-hc_img_name_4: .asciz "gemm_bf16_umma"
+hc_img_name_4: .asciz "gemm_tiled"
 .balign 16
-hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
+hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
 hc_img_end_4:
 .balign 16
-hc_img_name_5: .asciz "dequant_w8"
+hc_img_name_5: .asciz "gemm_bf16_umma"
 .balign 16
-hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
 hc_img_end_5:
+.balign 16
+hc_img_name_6: .asciz "dequant_w8"
+.balign 16
+hc_img_begin_6: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_end_6:
 .balign 16
 .section .data.rel.ro,"aw"
 .globl hc_b200_images
@@ -52,9 +57,12 @@ hc_b200_images:
   .quad hc_img_name_5
   .quad hc_img_begin_5
   .quad hc_img_end_5
+  .quad hc_img_name_6
+  .quad hc_img_begin_6
+  .quad hc_img_end_6
 .section .rodata
 .globl hc_b200_image_count
 .balign 4
 hc_b200_image_count:
-  .long 6
+  .long 7
 .section .note.GNU-stack,"",@progbits

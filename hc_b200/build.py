@@ -33,6 +33,7 @@ KERNEL_SOURCES = [
     "copy2d",
     "softmax_rows",
     "reduce_rows",
+    "reduce_all",
     "gemm_tiled",
     "gemm_bf16_umma",
     "dequant_w8",

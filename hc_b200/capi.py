@@ -19,7 +19,7 @@ NATIVE_DIR = Path(__file__).resolve().parent / "_native"
 OlErrorCallback = C.CFUNCTYPE(None, C.c_void_p, C.c_int, C.c_char_p)
 
 # hc_b200_kernels.h: enum HcDType
-HC_F32, HC_F64, HC_BF16, HC_I8 = 0, 1, 2, 3
+HC_F32, HC_F64, HC_BF16, HC_I8, HC_I32, HC_I64 = 0, 1, 2, 3, 4, 5
 
 # offload_api.h: OLX_DEVICE_*
 OLX_DEVICE_SM_COUNT = 1
@@ -89,6 +89,7 @@ KERNELS_PROTOTYPES = {
     "hcCopy2D": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcSoftmaxRows": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcReduceRows": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),
+    "hcReduceAll": (C.c_int, [_vp, _vp, _ll, _vp, C.c_int, C.c_int]),
     "hcGemmTiled": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]),
     "hcGemmBf16": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
     "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
@@ -240,6 +241,11 @@ class Context:
         self._check(
             self.lib.hcReduceRows(self.handle, x, sum_out, max_out, rows, cols, pitch, dtype),
             "hcReduceRows",
+        )
+
+    def reduce_all(self, a, n, result, in_dtype=HC_F32, result_dtype=HC_F32):
+        self._check(
+            self.lib.hcReduceAll(self.handle, a, n, result, in_dtype, result_dtype), "hcReduceAll"
         )
 
     def gemm_tiled(self, a, b, c, m, n, k, lda, ldb, ldc, dtype=HC_F32):

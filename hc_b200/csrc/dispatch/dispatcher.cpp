@@ -168,6 +168,24 @@ void reduceRows(Context &ctx, py::handle x, py::object sumOut, py::object maxOut
             "reduce_rows");
 }
 
+void reduceAll(Context &ctx, py::handle a, py::handle result) {
+  ArrayArg A = deviceArray(ctx, a, "a", 1), R = deviceArray(ctx, result, "result", 1);
+  if (A.shape[0] > 1 && A.strides[0] != 1)
+    throw py::value_error("a: must be contiguous");
+  if (R.shape[0] < 1)
+    throw py::value_error("result: needs at least one element");
+  int in = A.kind == ElemKind::F32   ? HC_F32
+           : A.kind == ElemKind::F64 ? HC_F64
+           : A.kind == ElemKind::I32 ? HC_I32
+           : A.kind == ElemKind::I64 ? HC_I64
+                                     : -1;
+  if (in < 0)
+    throw py::type_error(std::string("a: float32, float64, int32 or int64 expected, got ") +
+                         hc::kindName(A.kind));
+  ctx.check(hcReduceAll(ctx.get(), A.data, A.shape[0], R.data, in, floatDType(R, "result")),
+            "reduce_all");
+}
+
 void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
   ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
            C = deviceArray(ctx, out, "out", 2);
@@ -253,6 +271,7 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("softmax_rows", &softmaxRows, py::arg("ctx"), py::arg("x"), py::arg("out"));
   m.def("reduce_rows", &reduceRows, py::arg("ctx"), py::arg("x"),
         py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
+  m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
   m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());

@@ -59,6 +59,14 @@ const KernelEntry kKernelTable[] = {
     {"hc_reduce_rows_warp_f64", "reduce_rows"},
     {"hc_reduce_rows_block_f32", "reduce_rows"},
     {"hc_reduce_rows_block_f64", "reduce_rows"},
+    {"hc_reduce_all_f32_f32", "reduce_all"},
+    {"hc_reduce_all_f32_f64", "reduce_all"},
+    {"hc_reduce_all_f64_f64", "reduce_all"},
+    {"hc_reduce_all_f64_f32", "reduce_all"},
+    {"hc_reduce_all_i32_f32", "reduce_all"},
+    {"hc_reduce_all_i32_f64", "reduce_all"},
+    {"hc_reduce_all_i64_f32", "reduce_all"},
+    {"hc_reduce_all_i64_f64", "reduce_all"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
     {"hc_gemm_tiled_bf16", "gemm_tiled"},
@@ -431,6 +439,33 @@ int hcReduceRows(HcContext c, const void *x, void *sumOut, void *maxOut,
   long long grid = std::min<long long>(rows, c->smCount * 8);
   return c->launch(f32 ? "hc_reduce_rows_block_f32" : "hc_reduce_rows_block_f64",
                    size_t(grid), 1, 1, 256, args, 7, 0);
+}
+
+int hcReduceAll(HcContext c, const void *a, long long n, void *result,
+                int inDtype, int resultDtype) {
+  if (!c)
+    return 1;
+  const char *in = inDtype == HC_F32   ? "f32"
+                   : inDtype == HC_F64 ? "f64"
+                   : inDtype == HC_I32 ? "i32"
+                   : inDtype == HC_I64 ? "i64"
+                                       : nullptr;
+  const char *out = resultDtype == HC_F32 ? "f32" : resultDtype == HC_F64 ? "f64" : nullptr;
+  if (!in || !out)
+    return c->fail("hcReduceAll: unsupported dtypes %d -> %d", inDtype, resultDtype);
+  if (n < 0)
+    return c->fail("hcReduceAll: invalid length %lld", n);
+  if (n == 0)
+    return 0;
+  if (!a || !result)
+    return c->fail("hcReduceAll: null buffer");
+  char name[48];
+  snprintf(name, sizeof(name), "hc_reduce_all_%s_%s", in, out);
+  // Enough CTAs to fill the GPU, each with at least a few elements per thread.
+  long long grid = std::max<long long>(
+      1, std::min<long long>(ceilDiv(n, 256 * 8), c->smCount * 8));
+  void *args[] = {&a, &n, &result};
+  return c->launch(name, size_t(grid), 1, 1, 256, args, 3, 0);
 }
 
 // ---- GEMMs ----------------------------------------------------------------------

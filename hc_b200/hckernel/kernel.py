@@ -372,6 +372,52 @@ def _match_gemm(stores, counts):
     return _Plan("gemm", a=a_buf.index, b=b_buf.index, out=dst.buffer.index)
 
 
+def _match_reduce_all(atomics, counts):
+    """``atomic_ref(result)[0] += tile.sum()`` where the tiles of all groups
+    partition a 1-D buffer: no gaps (every element is summed) and no overlap
+    (none is summed twice)."""
+    if len(atomics) != 1:
+        return None
+    update = atomics[0]
+    expr = update.value
+    if expr.op != "sum" or expr.attrs.get("axis") is not None:
+        return None
+    loads = []
+    for term in _flatten_sum(expr.args[0]):
+        if term.op == "alloc" and term.args[0] == 0.0:
+            continue  # the zero accumulator of the reference's second form
+        if not _is_load(term, 1):
+            return None
+        loads.append(term)
+    if not loads:
+        return None
+    source = _view(loads[0]).buffer
+    if source.ndim != 1 or any(_view(t).buffer is not source for t in loads):
+        raise UnsupportedKernel("whole-array sum over more than one 1-D buffer")
+    if update.buffer is source or tuple(update.index) != (0,) * update.buffer.ndim:
+        raise UnsupportedKernel("whole-array sum must accumulate into element 0 of another buffer")
+    # Within a group: pieces in order, touching, starting at the group's offset.
+    pieces = sorted((_view(t).origin[0].const, t.shape[0], _view(t).origin[0].coefs) for t in loads)
+    coefs = pieces[0][2]
+    if pieces[0][0] != 0 or len(coefs) > 1 or any(p[2] != coefs for p in pieces):
+        raise UnsupportedKernel("whole-array sum: tile offsets are not gid*step + piece")
+    reach = 0
+    for start, length, _ in pieces:
+        if start != reach:
+            raise UnsupportedKernel("whole-array sum: tiles overlap or leave gaps inside a group")
+        reach += length
+    n = source.shape[0]
+    if coefs:
+        ((axis, step),) = coefs.items()
+        if step != reach:
+            raise UnsupportedKernel("whole-array sum: groups overlap or leave gaps")
+        if step * (counts[axis] - 1) + reach < n:
+            raise UnsupportedKernel("whole-array sum: work shape does not reach the end")
+    elif reach < n or any(c != 1 for c in counts):
+        raise UnsupportedKernel("whole-array sum: a single tile must cover the array once")
+    return _Plan("reduce_all", a=source.index, result=update.buffer.index)
+
+
 _MATCHERS = (_match_copy, _match_softmax, _match_reduce, _match_gemm)
 
 
@@ -450,19 +496,26 @@ class KernelDispatcher:
         for i, a in enumerate(args):
             if hasattr(a, "shape") and hasattr(a, "dtype"):
                 name = params[i] if i < len(params) else f"arg{i}"
-                stand_ins.append(BufferRef(i, name, a.shape, a.dtype))
+                stand_ins.append(BufferRef(i, name, a.shape, a.dtype, recorder))
             else:
                 stand_ins.append(a)
         body(recorder, *stand_ins)
-        if not recorder.stores:
+        if not recorder.stores and not recorder.atomics:
             raise UnsupportedKernel(f"{self.func.__name__}: the kernel stores nothing")
-        for matcher in _MATCHERS:
-            plan = matcher(recorder.stores, counts)
+        if recorder.atomics:
+            if recorder.stores:
+                raise UnsupportedKernel("kernels that mix stores and atomic updates")
+            plan = _match_reduce_all(recorder.atomics, counts)
             if plan is not None:
                 return plan
+        else:
+            for matcher in _MATCHERS:
+                plan = matcher(recorder.stores, counts)
+                if plan is not None:
+                    return plan
         raise UnsupportedKernel(
             f"{self.func.__name__}: the body matches none of the precompiled kernel families "
-            f"(copy, row softmax, last-axis sum/max, GEMM, int8 dequant GEMM)"
+            f"(copy, row softmax, last-axis sum/max, whole-array sum, GEMM, int8 dequant GEMM)"
         )
 
     # -- step 4 -----------------------------------------------------------------------
@@ -493,6 +546,8 @@ class KernelDispatcher:
             native.reduce_rows(ctx, args[r["x"]],
                                args[r["sum_out"]] if "sum_out" in r else None,
                                args[r["max_out"]] if "max_out" in r else None)
+        elif plan.family == "reduce_all":
+            native.reduce_all(ctx, args[r["a"]], args[r["result"]])
         elif plan.family == "gemm":
             native.gemm(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
         elif plan.family == "gemm_w8a16":

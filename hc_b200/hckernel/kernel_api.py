@@ -195,11 +195,12 @@ def dtype_name(dtype):
 class BufferRef:
     """Stands for an array argument while the body is recorded."""
 
-    def __init__(self, index, name, shape, dtype):
+    def __init__(self, index, name, shape, dtype, recorder=None):
         self.index = index
         self.name = name
         self.shape = tuple(int(s) for s in shape)
         self.dtype = dtype_name(dtype)
+        self.recorder = recorder  # the CurrentGroup that collects element updates
 
     @property
     def ndim(self):
@@ -226,14 +227,50 @@ class BufferRef:
         origin += [Affine(0)] * (self.ndim - len(origin))
         return tuple(origin)
 
+    @staticmethod
+    def _is_element(key):
+        keys = key if isinstance(key, tuple) else (key,)
+        return all(isinstance(k, (int, np.integer)) for k in keys)
+
     def __getitem__(self, key):
+        if self._is_element(key):
+            # `atomic_ref(result)[0]`: one element, to be updated in place.
+            index = tuple(int(k) for k in (key if isinstance(key, tuple) else (key,)))
+            if len(index) != self.ndim or any(not 0 <= i < s for i, s in zip(index, self.shape)):
+                raise IndexError(f"{self.name}{list(index)} is out of range")
+            return ElementRef(self, index)
         return BufferView(self, self._origin(key))
 
     def __setitem__(self, key, value):
+        # `buf[i] += tile` arrives here after ElementRef.__iadd__.
+        if isinstance(value, AtomicUpdate) and self._is_element(key):
+            if self.recorder is None:
+                raise UnsupportedKernel("element update outside a kernel body")
+            self.recorder.atomics.append(value)
+            return
         raise UnsupportedKernel(f"direct assignment into {self.name}; use group.store")
 
     def __repr__(self):
         return f"<buffer {self.name}{list(self.shape)} {self.dtype}>"
+
+
+class AtomicUpdate:
+    """``buffer[index] += value`` recorded as an atomic add."""
+
+    def __init__(self, buffer, index, value):
+        self.buffer, self.index, self.value = buffer, index, value
+
+
+class ElementRef:
+    """One element of a buffer; only ``+=`` with a tile expression is recorded
+    (the ``atomic_ref(result)[0] += tile.sum()`` idiom of the reference,
+    python/hckernel/tests/test_examples.py:40,64)."""
+
+    def __init__(self, buffer, index):
+        self.buffer, self.index = buffer, index
+
+    def __iadd__(self, value):
+        return AtomicUpdate(self.buffer, self.index, Tile._wrap(value))
 
 
 class BufferView:
@@ -428,6 +465,7 @@ class CurrentGroup:
         self._subgroup_size = subgroup_size
         self._group_id = tuple(Affine(0, {d: 1}) for d in range(len(self._group_shape)))
         self.stores = []
+        self.atomics = []
 
     @property
     def id(self):

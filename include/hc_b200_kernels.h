@@ -33,7 +33,9 @@ enum HcDType {
   HC_F32 = 0,
   HC_F64 = 1,
   HC_BF16 = 2,
-  HC_I8 = 3
+  HC_I8 = 3,
+  HC_I32 = 4,
+  HC_I64 = 5
 };
 
 /* ---- kernel images -------------------------------------------------------
@@ -87,6 +89,13 @@ HC_B200_API int hcSoftmaxRows(HcContext c, const void *x, void *y,
 HC_B200_API int hcReduceRows(HcContext c, const void *x, void *sumOut,
                              void *maxOut, long long rows, long long cols,
                              long long pitch, int dtype);
+
+/* Whole-array sum added to one element: result[0] += sum(a[0:n]).  `a` is
+ * HC_F32, HC_F64, HC_I32 or HC_I64; `result` is HC_F32 or HC_F64 and is not
+ * cleared first (the reference's atomic_ref(result)[0] += tile.sum(),
+ * python/hckernel/tests/test_examples.py:31-71). */
+HC_B200_API int hcReduceAll(HcContext c, const void *a, long long n,
+                            void *result, int inDtype, int resultDtype);
 
 /* C[M,N] = A[M,K] @ B[K,N] on the CUDA cores; HC_F32, HC_F64, or HC_BF16
  * (bf16 in and out, fp32 accumulation)

@@ -78,6 +78,33 @@ def test_unrolled_copy_from_the_reference_tests():
             assert copy_kernel.plan_for((F(shape, "int32"), F(shape, "int32"), unroll)).family == "copy2d"
 
 
+def test_scalar_reductions_from_the_reference_tests():
+    # python/hckernel/tests/test_examples.py:31-71, both forms.
+    WS, GS, N = sym.WS, sym.GS, sym.N
+    TN = TunableParam(N, 2, range(1, 64))
+
+    def ceil_div(a, b):
+        return (a + b - 1) // b
+
+    @kernel(work_shape=ceil_div(WS, N), group_shape=GS, tunables=TN, **TARGET)
+    def reduction_1(gr: CurrentGroup, a: Buffer[WS, DT], result: Buffer[1, DT], gshape: GS):
+        a_view = gr.load(a[gr.work_offset[0] * N :], shape=gr.size * N)
+        atomic_ref(result)[0] += a_view.sum()
+
+    @kernel(work_shape=ceil_div(WS, N), group_shape=GS, tunables=TN, **TARGET)
+    def reduction_2(group: CurrentGroup, a: Buffer[WS, DT], result: Buffer[1, DT], gshape: GS):
+        temp_result = group.zeros(group.size, dtype=a.dtype)
+        for i in range(N):
+            work_offset = group.work_offset[0] * N + i * group.size
+            a_view = group.load(a[work_offset:], shape=group.size)
+            temp_result += a_view
+        atomic_ref(result)[0] += temp_result.sum()
+
+    for kern in (reduction_1, reduction_2, reduction_2.parametrize({N: 5})):
+        plan = kern.plan_for((F((20,), "int64"), F((1,), "float64"), 8))
+        assert (plan.family, plan.roles) == ("reduce_all", {"a": 0, "result": 1})
+
+
 def test_symbol_conflicts_and_rank_errors(k):
     with pytest.raises(ValueError, match="Symbol value conflict for M"):
         k.softmax.plan_for((F((30, 25)), F((31, 25)), 8))
@@ -112,12 +139,12 @@ def test_bodies_outside_the_families_are_refused():
     WS, GS = sym.WS, sym.GS
 
     @kernel(work_shape=WS, group_shape=GS, **TARGET)
-    def scalar_reduce(gr: CurrentGroup, a: Buffer[WS, DT], result: Buffer[1, DT], gshape: GS):
-        v = gr.load(a[gr.work_offset[0] :], shape=gr.size)
+    def overlapping_reduce(gr: CurrentGroup, a: Buffer[WS, DT], result: Buffer[1, DT], gshape: GS):
+        v = gr.load(a[gr.work_offset[0] :], shape=gr.size * 2)  # tiles twice as long as the step
         atomic_ref(result)[0] += v.sum()
 
-    with pytest.raises(UnsupportedKernel, match="element indexing"):
-        scalar_reduce.plan_for((F((20,)), F((1,)), 8))
+    with pytest.raises(UnsupportedKernel, match="overlap"):
+        overlapping_reduce.plan_for((F((20,)), F((1,)), 8))
 
     @kernel(work_shape=M, group_shape=GM, **TARGET)
     def squares(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):

@@ -199,3 +199,50 @@ def test_argument_errors(k):
     with pytest.raises(UnsupportedKernel):
         shifted(x, torch.empty_like(x))
     assert get_context(DEVICE).kernel_status() == 0
+
+
+def ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def test_reduction_1():
+    # python/hckernel/tests/test_examples.py:31-47, on the GPU.
+    WS, GS, N = sym.WS, sym.GS, sym.N
+    TN = TunableParam(N, 2, range(1, 64))
+
+    @kernel(work_shape=ceil_div(WS, N), group_shape=GS, tunables=TN, backend=BACKEND, device=DEVICE)
+    def reduction(gr: CurrentGroup, a: Buffer[WS, typename.DT], result: Buffer[1, typename.DT],
+                  gshape: GS):
+        a_view = gr.load(a[gr.work_offset[0] * N :], shape=gr.size * N)
+        atomic_ref(result)[0] += a_view.sum()
+
+    a = np.arange(0, 20)
+    d_a = to_device(torch.from_numpy(a))
+    d_result = torch.zeros(1, dtype=torch.float64, device="cuda")
+    reduction(d_a, d_result, 8)
+    assert d_result.cpu().numpy()[0] == a.sum()
+
+
+def test_reduction_2():
+    # python/hckernel/tests/test_examples.py:50-71, on the GPU.
+    WS, GS, N = sym.WS, sym.GS, sym.N
+    TN = TunableParam(N, 2, range(1, 64))
+
+    @kernel(work_shape=ceil_div(WS, N), group_shape=GS, tunables=TN, backend=BACKEND, device=DEVICE)
+    def reduction(group: CurrentGroup, a: Buffer[WS, typename.DT], result: Buffer[1, typename.DT],
+                  gshape: GS):
+        temp_result = group.zeros(group.size, dtype=a.dtype)
+        for i in range(N):
+            work_offset = group.work_offset[0] * N + i * group.size
+            a_view = group.load(a[work_offset:], shape=group.size)
+            temp_result += a_view
+        atomic_ref(result)[0] += temp_result.sum()
+
+    a = np.arange(0, 20)
+    d_a = to_device(torch.from_numpy(a))
+    d_result = torch.zeros(1, dtype=torch.float64, device="cuda")
+    reduction(d_a, d_result, 8)
+    assert d_result.cpu().numpy()[0] == a.sum()
+    # The kernel adds to what is already there, like `+=` on the simulator.
+    reduction(d_a, d_result, 8)
+    assert d_result.cpu().numpy()[0] == 2 * a.sum()

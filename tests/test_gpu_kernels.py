@@ -428,3 +428,40 @@ def test_softmax_variants_agree_with_oracle(hc, variant, rows, cols):
     expect = np.zeros_like(x)
     oracle.softmax_rows(x, expect, 8)
     _softmax_check(d_y.cpu().numpy(), expect)
+
+
+# ---- whole-array sum ------------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 20, 1000, 1 << 20, 5_000_003])
+@pytest.mark.parametrize("in_dtype", ["f32", "f64", "i32", "i64"])
+def test_reduce_all_matches_oracle(hc, n, in_dtype):
+    np_t = {"f32": np.float32, "f64": np.float64, "i32": np.int32, "i64": np.int64}[in_dtype]
+    code = {"f32": capi.HC_F32, "f64": capi.HC_F64, "i32": capi.HC_I32, "i64": capi.HC_I64}[in_dtype]
+    rng = np.random.default_rng(n)
+    a = (rng.integers(-1000, 1000, n) if in_dtype.startswith("i")
+         else rng.uniform(-10, 10, n)).astype(np_t)
+    d_a = dev(a)
+    d_r = torch.full((1,), 5.0, dtype=torch.float64, device="cuda")  # pre-existing content is kept
+    torch.cuda.synchronize()
+    hc.reduce_all(d_a.data_ptr(), n, d_r.data_ptr(), code, capi.HC_F64)
+    finish(hc)
+    expect = np.zeros(1)
+    oracle.reduce_sum_all(a, expect, 8, 2)
+    got = d_r.cpu().numpy()[0] - 5.0
+    if in_dtype.startswith("i"):
+        assert got == expect[0] == a.sum()  # integers are exact in float64
+    else:
+        assert abs(got - a.astype(np.float64).sum()) <= 1e-12 * np.abs(a).astype(np.float64).sum() + 1e-9
+    d_r32 = torch.zeros(1, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    hc.reduce_all(d_a.data_ptr(), n, d_r32.data_ptr(), code, capi.HC_F32)
+    finish(hc)
+    bound = 1e-5 * np.abs(a).astype(np.float64).sum() + 1e-6
+    assert abs(float(d_r32.cpu().numpy()[0]) - a.astype(np.float64).sum()) <= bound
+
+
+def test_reduce_all_errors(hc):
+    hc.reduce_all(0, 0, 0)  # nothing to do
+    with pytest.raises(capi.HcError, match="unsupported dtypes"):
+        hc.reduce_all(0, 4, 0, capi.HC_BF16, capi.HC_F32)
+    with pytest.raises(capi.HcError, match="null buffer"):
+        hc.reduce_all(0, 4, 0, capi.HC_F32, capi.HC_F32)
