@@ -137,7 +137,123 @@ gemmTile(const TA *__restrict__ a, const TB *__restrict__ b,
   }
 }
 
+// ---- fp32 variant with an asynchronous-copy pipeline ------------------------------
+// Same tiling (64 x 64 per CTA, 4 x 4 per thread) but K blocks of 32 travel
+// global -> shared with 16-byte cp.async copies, three blocks ahead of the
+// FMAs, so a small problem (the 256^3 case runs on 16 CTAs) is no longer paced
+// by one global-memory round trip per K block.  Needs 16-byte aligned A and B
+// and row pitches that are multiples of 4 floats; edges are zero-filled by
+// giving cp.async a short (or zero) source size.
+constexpr int AK = 32, ASTAGES = 3;
+constexpr int A_PITCH = AK + 4;  // floats; keeps 16-byte alignment, spreads banks
+constexpr int B_PITCH = TN + 4;
+
+struct AsyncStage {
+  float a[TM][A_PITCH];
+  float b[AK][B_PITCH];
+};
+
+__device__ __forceinline__ void cpAsync16(void *smemDst, const void *gmemSrc,
+                                          int srcBytes) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smemDst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst),
+               "l"(gmemSrc), "r"(srcBytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
+                                              const float *__restrict__ b,
+                                              float *__restrict__ c, long long M,
+                                              long long N, long long K,
+                                              long long lda, long long ldb,
+                                              long long ldc, AsyncStage *stages) {
+  const int tid = threadIdx.x;
+  const long long m0 = (long long)blockIdx.y * TM;
+  const long long n0 = (long long)blockIdx.x * TN;
+
+  // Copy assignment: A tile 64 x 32 = 512 packets of 4 floats, B tile 32 x 64
+  // = 512 packets; each thread moves two of each.
+  auto issue = [&](int stage, long long k0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int ar = (tid >> 3) + 32 * h, ac = (tid & 7) << 2;
+      const long long gm = m0 + ar, gk = k0 + ac;
+      int bytes = 0;
+      if (gm < M && gk < K)
+        bytes = int(min((long long)4, K - gk)) * 4;
+      // A clamped in-range address keeps the copy legal when nothing is read.
+      const float *src = a + (gm < M ? gm : 0) * lda + (gk < K ? gk : 0);
+      cpAsync16(&stages[stage].a[ar][ac], src, bytes);
+
+      const int br = (tid >> 4) + 16 * h, bc = (tid & 15) << 2;
+      const long long gkb = k0 + br, gn = n0 + bc;
+      bytes = 0;
+      if (gkb < K && gn < N)
+        bytes = int(min((long long)4, N - gn)) * 4;
+      const float *srcB = b + (gkb < K ? gkb : 0) * ldb + (gn < N ? gn : 0);
+      cpAsync16(&stages[stage].b[br][bc], srcB, bytes);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  const long long kBlocks = (K + AK - 1) / AK;
+  // Prologue: fill the pipeline (empty commits keep the group count uniform).
+  for (int s = 0; s < ASTAGES - 1; ++s) {
+    if (s < kBlocks)
+      issue(s, (long long)s * AK);
+    else
+      asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (long long kb = 0; kb < kBlocks; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(ASTAGES - 2) : "memory");
+    __syncthreads(); // block kb has landed; block kb-1's buffer is free
+    const long long next = kb + ASTAGES - 1;
+    if (next < kBlocks)
+      issue(int(next % ASTAGES), next * AK);
+    else
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    const AsyncStage &st = stages[kb % ASTAGES];
+#pragma unroll
+    for (int k = 0; k < AK; ++k) {
+      float av[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        av[i] = st.a[ty * 4 + i][k];
+      const float4 bv = *reinterpret_cast<const float4 *>(&st.b[k][tx * 4]);
+      const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] = fmaf(av[i], bb[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long gm = m0 + ty * 4 + i;
+    if (gm >= M)
+      continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long gn = n0 + tx * 4 + j;
+      if (gn < N)
+        c[gm * ldc + gn] = acc[i][j];
+    }
+  }
+}
+
 } // namespace
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+    hc_gemm_tiled_f32_async(const float *a, const float *b, float *c,
+                            long long M, long long N, long long K,
+                            long long lda, long long ldb, long long ldc) {
+  extern __shared__ __align__(16) unsigned char asyncSmem[];
+  gemmTileAsync(a, b, c, M, N, K, lda, ldb, ldc,
+                reinterpret_cast<AsyncStage *>(asyncSmem));
+}
 
 extern "C" __global__ void __launch_bounds__(THREADS)
     hc_gemm_tiled_f32(const float *a, const float *b, float *c, long long M,

@@ -68,6 +68,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_reduce_all_i64_f32", "reduce_all"},
     {"hc_reduce_all_i64_f64", "reduce_all"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
+    {"hc_gemm_tiled_f32_async", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
     {"hc_gemm_tiled_bf16", "gemm_tiled"},
     {"hc_gemm_tiled_w8a16", "gemm_tiled"},
@@ -113,6 +114,7 @@ struct HcContextImpl {
   long long ccMajor = 0;
   long long gemmVariant = 0;
   long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
+  long long tiledVariant = 0;
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
@@ -313,6 +315,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->softmaxVariant = value;
     return 0;
   }
+  if (std::strcmp(name, "tiled_variant") == 0 && value >= 0 && value <= 1) {
+    c->tiledVariant = value; // 1: never use the cp.async pipelined fp32 kernel
+    return 0;
+  }
   return c->fail("Invalid option: %s = %lld", name, value);
 }
 
@@ -498,6 +504,13 @@ int hcGemmTiled(HcContext c, const void *a, const void *b, void *out,
   if (M == 0 || N == 0)
     return 0;
   void *args[] = {&a, &b, &out, &M, &N, &K, &lda, &ldb, &ldc};
+  // fp32 operands that 16-byte cp.async can fetch take the pipelined variant
+  // (3 stages of a 64x36 A block and a 32x68 B block of floats).
+  if (dtype == HC_F32 && K > 0 && c->tiledVariant != 1 && lda % 4 == 0 &&
+      ldb % 4 == 0 && aligned(a, 16) && aligned(b, 16))
+    return c->launch("hc_gemm_tiled_f32_async", size_t(ceilDiv(N, 64)),
+                     size_t(ceilDiv(M, 64)), 1, 256, args, 9,
+                     3 * (64 * 36 + 32 * 68) * sizeof(float));
   return c->launch(name, size_t(ceilDiv(N, 64)), size_t(ceilDiv(M, 64)), 1, 256,
                    args, 9, 0);
 }

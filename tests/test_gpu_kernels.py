@@ -253,6 +253,26 @@ def test_gemm_tiled_f32_shapes(hc, shape):
     _gemm_f32_check(a, b, d_c.cpu().numpy(), expect)
 
 
+@pytest.mark.parametrize("variant", [0, 1])  # 0: cp.async pipeline when legal, 1: never
+@pytest.mark.parametrize("shape", [(256, 256, 256), (70, 44, 36), (130, 68, 100), (64, 64, 4),
+                                   (1, 4, 8), (200, 260, 1028)])
+def test_gemm_tiled_f32_pipelined_and_plain_agree(hc, variant, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    d_a, d_b, d_c = dev(a), dev(b), empty_like_dev((m, n), torch.float32)
+    hc.set_option("tiled_variant", variant)
+    try:
+        hc.gemm_tiled(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), m, n, k, k, n, n)
+        finish(hc)
+    finally:
+        hc.set_option("tiled_variant", 0)
+    expect = np.zeros((m, n), np.float32)
+    oracle.gemm_kblocked(a, b, expect, (64, 64), kb=16)
+    _gemm_f32_check(a, b, d_c.cpu().numpy(), expect)
+
+
 # ---- bf16 GEMM (tensor cores) -------------------------------------------------------
 VARIANTS = {"single": 1, "pair": 2, "tiled": 3, "auto": 0}
 
