@@ -601,7 +601,10 @@ int hcDequantW8(HcContext c, const void *w, void *out, long long rows,
   long long perRow = vec ? cols / 16 : cols;
   long long gx = std::max<long long>(
       1, std::min<long long>(ceilDiv(perRow, 256), c->smCount * 8));
-  long long gy = std::min<long long>(rows, std::max<long long>(1, c->smCount * 16 / gx));
+  // Rows are walked four at a time by each thread: give every CTA row at
+  // least eight of them when the matrix is tall enough.
+  long long gy = std::max<long long>(
+      1, std::min<long long>(ceilDiv(rows, 8), c->smCount * 8 / gx));
   void *args[] = {&w, &out, &rows, &cols, &wPitch, &outPitch, &vec};
   return c->launch("hc_dequant_w8_bf16", size_t(gx), size_t(gy), 1, 256, args, 7,
                    0);
