@@ -1,0 +1,112 @@
+"""Two-GPU run of the sharded launcher with the real kernels and NCCL: every
+rank computes its shard on its own GPU, the outputs are all-gathered, and each
+rank checks the gathered result against the CPU oracle of the whole problem.
+Skipped on a box with fewer than two GPUs (the single-GPU suite covers the
+kernels; tests/test_launcher_gloo.py covers the sharding logic on CPU)."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import workloads as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from hc_b200.hckernel.kernel import get_context
+        from hc_b200.launcher import ShardedLauncher
+        from hc_b200.workloads import make_kernels
+
+        L = ShardedLauncher(make_kernels(f"cuda:{rank}"), rank, world)
+        ok = {}
+
+        rows = 600
+        (x,) = oracle.make_inputs("softmax", shape=(rows, 2048))
+        span = L.rows(rows)
+        xs = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        ys = torch.empty_like(xs)
+        L.softmax(xs, ys)
+        full = torch.empty(rows, 2048, device=dev)
+        L.gather_rows(ys, full)
+        expect = np.zeros_like(x)
+        oracle.softmax_rows(x, expect, 256)
+        got = full.cpu().numpy()
+        ok["softmax"] = bool(np.all(np.abs(got - expect) <= 1e-6 + 1e-5 * np.abs(expect)))
+
+        (x,) = oracle.make_inputs("reduce", shape=(rows + 1, 1024))  # ragged: 301 + 300 rows
+        span = L.rows(rows + 1)
+        xs = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        ss, ms = torch.empty(span.size, device=dev), torch.empty(span.size, device=dev)
+        L.reduce_rows(xs, ss, ms)
+        fs, fm = torch.empty(rows + 1, device=dev), torch.empty(rows + 1, device=dev)
+        L.gather_rows(ss, fs)
+        L.gather_rows(ms, fm)
+        bound = 1e-5 * np.abs(x).astype(np.float64).sum(axis=1)
+        ok["reduce"] = bool(np.array_equal(fm.cpu().numpy(), x.max(axis=1)) and np.all(
+            np.abs(fs.cpu().numpy() - x.astype(np.float64).sum(axis=1)) <= bound))
+
+        m, n, k = 512, 768, 256
+        a, b = oracle.make_inputs("gemm_bf16", shape=(m, n, k))
+        span = L.rows(m)
+        a_s = torch.from_numpy(a[span.begin:span.end]).to(dev).bfloat16()
+        b_d = torch.from_numpy(b).to(dev).bfloat16()  # replicated
+        c_s = torch.empty(span.size, n, device=dev, dtype=torch.bfloat16)
+        L.gemm_rows(a_s, b_d, c_s)
+        c_full = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        L.gather_rows(c_s, c_full)
+        expect = np.zeros((m, n), np.float32)
+        oracle.gemm_bf16(a, b, expect, (256, 256))
+        got = c_full.float().cpu().numpy()
+        ok["gemm_rows"] = bool(np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect)
+                                      + 1e-4 * (np.abs(a) @ np.abs(b))))
+
+        m, n, k = 256, 544, 512  # column shards of 272 each
+        a, w, s = oracle.make_inputs("gemm_w8a16", shape=(m, n, k))
+        cs = L.cols(n)
+        a_d = torch.from_numpy(a).to(dev).bfloat16()  # replicated
+        w_d = torch.from_numpy(w).to(dev)
+        s_d = torch.from_numpy(s).to(dev)
+        o_s = torch.empty(m, cs.size, device=dev, dtype=torch.bfloat16)
+        L.dequant_gemm_cols(a_d, w_d[:, cs.begin:cs.end], s_d[cs.begin:cs.end], o_s)
+        o_full = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        L.gather_cols(o_s, o_full)
+        expect = np.zeros((m, n), np.float32)
+        oracle.gemm_w8a16(a, w, s, expect, (256, 256))
+        got = o_full.float().cpu().numpy()
+        mag = np.abs(a) @ (np.abs(w.astype(np.float32)) * s)
+        ok["dequant_cols"] = bool(np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * mag))
+
+        ok["status"] = get_context(f"cuda:{rank}").kernel_status() == 0
+        results[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_two_gpu_sharded_workloads_with_nccl_gather():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert len(results) == world
+        for rank in range(world):
+            assert all(results[rank].values()), (rank, dict(results[rank]))
