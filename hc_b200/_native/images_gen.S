@@ -20,20 +20,25 @@ hc_img_name_3: .asciz "reduce_all"
 hc_img_begin_3: .incbin "/root/repo/hc_b200/_native/reduce_all.cubin"
 hc_img_end_3:
 .balign 16
-hc_img_name_4: .asciz "gemm_tiled"
+hc_img_name_4: .asciz "pairwise_distance"
 .balign 16
-hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
+hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/pairwise_distance.cubin"
 hc_img_end_4:
 .balign 16
-hc_img_name_5: .asciz "gemm_bf16_umma"
+hc_img_name_5: .asciz "gemm_tiled"
 .balign 16
-hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
+hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
 hc_img_end_5:
 .balign 16
-hc_img_name_6: .asciz "dequant_w8"
+hc_img_name_6: .asciz "gemm_bf16_umma"
 .balign 16
-hc_img_begin_6: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_begin_6: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
 hc_img_end_6:
+.balign 16
+hc_img_name_7: .asciz "dequant_w8"
+.balign 16
+hc_img_begin_7: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_end_7:
 .balign 16
 .section .data.rel.ro,"aw"
 .globl hc_b200_images
@@ -60,9 +65,12 @@ hc_b200_images:
   .quad hc_img_name_6
   .quad hc_img_begin_6
   .quad hc_img_end_6
+  .quad hc_img_name_7
+  .quad hc_img_begin_7
+  .quad hc_img_end_7
 .section .rodata
 .globl hc_b200_image_count
 .balign 4
 hc_b200_image_count:
-  .long 7
+  .long 8
 .section .note.GNU-stack,"",@progbits

@@ -34,6 +34,7 @@ KERNEL_SOURCES = [
     "softmax_rows",
     "reduce_rows",
     "reduce_all",
+    "pairwise_distance",
     "gemm_tiled",
     "gemm_bf16_umma",
     "dequant_w8",

@@ -90,6 +90,9 @@ KERNELS_PROTOTYPES = {
     "hcSoftmaxRows": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcReduceRows": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),
     "hcReduceAll": (C.c_int, [_vp, _vp, _ll, _vp, C.c_int, C.c_int]),
+    "hcPairwiseDistance": (
+        C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]
+    ),
     "hcGemmTiled": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]),
     "hcGemmBf16": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
     "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
@@ -246,6 +249,12 @@ class Context:
     def reduce_all(self, a, n, result, in_dtype=HC_F32, result_dtype=HC_F32):
         self._check(
             self.lib.hcReduceAll(self.handle, a, n, result, in_dtype, result_dtype), "hcReduceAll"
+        )
+
+    def pairwise_distance(self, a, b, out, m, n, d, lda, ldb, ldo, dtype=HC_F32):
+        self._check(
+            self.lib.hcPairwiseDistance(self.handle, a, b, out, m, n, d, lda, ldb, ldo, dtype),
+            "hcPairwiseDistance",
         )
 
     def gemm_tiled(self, a, b, c, m, n, k, lda, ldb, ldc, dtype=HC_F32):

@@ -186,6 +186,18 @@ void reduceAll(Context &ctx, py::handle a, py::handle result) {
             "reduce_all");
 }
 
+void pairwiseDistance(Context &ctx, py::handle a, py::handle b, py::handle out) {
+  ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
+           O = deviceArray(ctx, out, "out", 2);
+  sameKind(A, B, "a", "b");
+  sameKind(A, O, "a", "out");
+  if (A.shape[1] != B.shape[1] || O.shape[0] != A.shape[0] || O.shape[1] != B.shape[0])
+    throw py::value_error("pairwise_distance: shapes do not form [M,D], [N,D] -> [M,N]");
+  ctx.check(hcPairwiseDistance(ctx.get(), A.data, B.data, O.data, A.shape[0], B.shape[0],
+                               A.shape[1], pitch(A), pitch(B), pitch(O), floatDType(A, "a")),
+            "pairwise_distance");
+}
+
 void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
   ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
            C = deviceArray(ctx, out, "out", 2);
@@ -272,6 +284,8 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("reduce_rows", &reduceRows, py::arg("ctx"), py::arg("x"),
         py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
   m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
+  m.def("pairwise_distance", &pairwiseDistance, py::arg("ctx"), py::arg("a"), py::arg("b"),
+        py::arg("out"));
   m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());

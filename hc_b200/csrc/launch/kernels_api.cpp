@@ -67,6 +67,8 @@ const KernelEntry kKernelTable[] = {
     {"hc_reduce_all_i32_f64", "reduce_all"},
     {"hc_reduce_all_i64_f32", "reduce_all"},
     {"hc_reduce_all_i64_f64", "reduce_all"},
+    {"hc_pairwise_distance_f32", "pairwise_distance"},
+    {"hc_pairwise_distance_f64", "pairwise_distance"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f32_async", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
@@ -472,6 +474,24 @@ int hcReduceAll(HcContext c, const void *a, long long n, void *result,
       1, std::min<long long>(ceilDiv(n, 256 * 8), c->smCount * 8));
   void *args[] = {&a, &n, &result};
   return c->launch(name, size_t(grid), 1, 1, 256, args, 3, 0);
+}
+
+int hcPairwiseDistance(HcContext c, const void *a, const void *b, void *out,
+                       long long M, long long N, long long D, long long lda,
+                       long long ldb, long long ldo, int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcPairwiseDistance: unsupported dtype %d", dtype);
+  if (M < 0 || N < 0 || D < 0 || lda < D || ldb < D || ldo < N)
+    return c->fail("hcPairwiseDistance: invalid shape M=%lld N=%lld D=%lld", M, N, D);
+  if (M == 0 || N == 0)
+    return 0;
+  if (!out || (D > 0 && (!a || !b)))
+    return c->fail("hcPairwiseDistance: null buffer");
+  void *args[] = {&a, &b, &out, &M, &N, &D, &lda, &ldb, &ldo};
+  return c->launch(dtype == HC_F32 ? "hc_pairwise_distance_f32" : "hc_pairwise_distance_f64",
+                   size_t(ceilDiv(N, 64)), size_t(ceilDiv(M, 64)), 1, 256, args, 9, 0);
 }
 
 // ---- GEMMs ----------------------------------------------------------------------

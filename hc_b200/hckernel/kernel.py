@@ -58,13 +58,16 @@ from .kernel_api import (
 __all__ = [
     "kernel", "sym", "typename", "Buffer", "CurrentGroup", "CurrentGroup1", "CurrentGroup2",
     "CurrentGroup3", "CurrentSubGroup", "CurrentWorkitem", "TunableParam", "create_mapping",
-    "atomic_ref", "UnsupportedKernel", "Typename",
+    "atomic_ref", "UnsupportedKernel", "Typename", "autotune", "TunedParams",
 ]
 
 _BACKENDS = {"nvvm": "cuda", "cuda": "cuda"}
 
 # One native context (device + queue + loaded images) per device description.
 _contexts = {}
+
+# What a context's options go back to after a call that overrode them.
+_DEFAULT_OPTIONS = {"gemm_variant": settings.GEMM_VARIANT}
 
 
 def get_context(device):
@@ -418,7 +421,37 @@ def _match_reduce_all(atomics, counts):
     return _Plan("reduce_all", a=source.index, result=update.buffer.index)
 
 
-_MATCHERS = (_match_copy, _match_softmax, _match_reduce, _match_gemm)
+def _match_pairwise(stores, counts):
+    """``store(out[m0:, n0:], np.linalg.norm(a_t[:, None, :] - b_t[None, :, :], axis=2))``
+    with a_t, b_t row blocks of [M, D] and [N, D] that hold whole rows."""
+    if len(stores) != 1:
+        return None
+    dst, expr = stores[0]
+    if expr.op != "norm" or expr.attrs != {"axis": 2, "keepdims": False}:
+        return None
+    diff = expr.args[0]
+    if diff.op != "sub":
+        return None
+    ea, eb = diff.args
+    if not (ea.op == "expand" and eb.op == "expand" and ea.attrs["axes"] == (1,)
+            and eb.attrs["axes"] == (0,)):
+        return None
+    a, b = ea.args[0], eb.args[0]
+    if not (_is_load(a, 2) and _is_load(b, 2)):
+        return None
+    av, bv = _view(a), _view(b)
+    (m, d), (n, d2) = av.buffer.shape, bv.buffer.shape
+    if d != d2 or dst.buffer.shape != (m, n):
+        raise UnsupportedKernel("pairwise distance: shapes do not form [M,D], [N,D] -> [M,N]")
+    if a.shape[1] != d or b.shape[1] != d or av.origin[1] != 0 or bv.origin[1] != 0:
+        raise UnsupportedKernel("pairwise distance tiles must hold whole rows")
+    if (av.origin[0], bv.origin[0]) != tuple(dst.origin):
+        raise UnsupportedKernel("pairwise distance: output tile origin differs from its operands")
+    _covers(dst.origin, (a.shape[0], b.shape[0]), (m, n), counts, "pairwise distance")
+    return _Plan("pairwise_distance", a=av.buffer.index, b=bv.buffer.index, out=dst.buffer.index)
+
+
+_MATCHERS = (_match_copy, _match_softmax, _match_reduce, _match_gemm, _match_pairwise)
 
 
 # ---- the callable the decorator returns ----------------------------------------------
@@ -427,7 +460,8 @@ class KernelDispatcher:
     ``Dispatcher`` (python/cpp/compiler/src/Dispatcher.cpp:20-42)."""
 
     def __init__(self, func, work_shape, group_shape, subgroup_size, literals, tunables,
-                 backend, device, tuned=None):
+                 backend, device, tuned=None, options=None):
+        self.options = dict(options or {})  # native launch options chosen by autotune
         self.func = func
         self.work_shape = work_shape
         self.group_shape = group_shape
@@ -441,10 +475,13 @@ class KernelDispatcher:
         functools.update_wrapper(self, func)
 
     def parametrize(self, tuned):
-        """A copy with tunable symbols fixed (reference kernel_sim.py:165-174)."""
+        """A copy with tunable symbols fixed (reference kernel_sim.py:165-174).
+        ``tuned`` may be the result of :func:`hckernel.autotune.autotune`, which
+        also carries native launch options."""
+        options = {**self.options, **getattr(tuned, "options", {})}
         return KernelDispatcher(self.func, self.work_shape, self.group_shape, self.subgroup_size,
                                 self.literals, self.tunables, self.backend, self.device,
-                                {**self.tuned, **tuned})
+                                {**self.tuned, **tuned}, options)
 
     # -- steps 1-3 -------------------------------------------------------------------
     def _default_tunables(self):
@@ -515,7 +552,8 @@ class KernelDispatcher:
                     return plan
         raise UnsupportedKernel(
             f"{self.func.__name__}: the body matches none of the precompiled kernel families "
-            f"(copy, row softmax, last-axis sum/max, whole-array sum, GEMM, int8 dequant GEMM)"
+            f"(copy, row softmax, last-axis sum/max, whole-array sum, pairwise distance, GEMM, "
+            f"int8 dequant GEMM)"
         )
 
     # -- step 4 -----------------------------------------------------------------------
@@ -532,9 +570,13 @@ class KernelDispatcher:
         r = plan.roles
         fence = _StreamFence(ctx, args)
         fence.before()
+        for name, value in self.options.items():
+            ctx.set_option(name, value)
         try:
             self._launch(native, ctx, plan, r, args, workspace)
         finally:
+            for name in self.options:
+                ctx.set_option(name, _DEFAULT_OPTIONS.get(name, 0))
             fence.after()
 
     def _launch(self, native, ctx, plan, r, args, workspace):
@@ -548,6 +590,8 @@ class KernelDispatcher:
                                args[r["max_out"]] if "max_out" in r else None)
         elif plan.family == "reduce_all":
             native.reduce_all(ctx, args[r["a"]], args[r["result"]])
+        elif plan.family == "pairwise_distance":
+            native.pairwise_distance(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
         elif plan.family == "gemm":
             native.gemm(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
         elif plan.family == "gemm_w8a16":
@@ -636,3 +680,6 @@ def kernel(
                                 backend, device)
 
     return decorate
+
+
+from .autotune import TunedParams, autotune  # noqa: E402  (needs the names above)

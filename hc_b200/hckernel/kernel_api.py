@@ -394,7 +394,23 @@ class Tile:
         return self
 
     def __getitem__(self, key):
-        raise UnsupportedKernel("slicing a loaded tile is not supported by the precompiled kernels")
+        # Only `tile[:, None, :]`-style indexing: full slices and new axes.
+        if not isinstance(key, tuple):
+            key = (key,)
+        shape, dims = [], iter(self.shape)
+        for k in key:
+            if k is None:
+                shape.append(1)
+            elif isinstance(k, slice) and k == slice(None):
+                shape.append(next(dims))
+            else:
+                raise UnsupportedKernel(
+                    "slicing a loaded tile is not supported by the precompiled kernels")
+        shape.extend(dims)
+        if tuple(shape) == self.shape:
+            return self
+        axes = tuple(i for i, k in enumerate(key) if k is None)
+        return Tile("expand", (self,), shape, self.dtype, axes=axes)
 
     # -- NumPy protocols: np.exp(tile), np.dot(a, b), np.add(a, b) ... -------------
     def __array_ufunc__(self, ufunc, method, *inputs, **kwargs):
@@ -417,6 +433,11 @@ class Tile:
             return args[0].sum(*args[1:], **kwargs)
         if func in (np.max, np.amax):
             return args[0].max(*args[1:], **kwargs)
+        if func is np.linalg.norm:
+            extra = {k: v for k, v in kwargs.items() if k != "axis" and v is not None and v is not False}
+            if len(args) != 1 or extra or not isinstance(kwargs.get("axis"), int):
+                raise UnsupportedKernel("np.linalg.norm on a tile: only norm(x, axis=<int>)")
+            return args[0]._reduce("norm", kwargs["axis"], False)
         raise UnsupportedKernel(f"np.{func.__name__} on a tile")
 
 

@@ -97,6 +97,14 @@ HC_B200_API int hcReduceRows(HcContext c, const void *x, void *sumOut,
 HC_B200_API int hcReduceAll(HcContext c, const void *a, long long n,
                             void *result, int inDtype, int resultDtype);
 
+/* Pairwise Euclidean distance: out[i,j] = sqrt(sum_d (a[i,d] - b[j,d])^2) for
+ * a [M,D], b [N,D], out [M,N]; HC_F32 or HC_F64
+ * (python/hckernel/tests/test_examples.py:261-301). */
+HC_B200_API int hcPairwiseDistance(HcContext c, const void *a, const void *b,
+                                   void *out, long long M, long long N,
+                                   long long D, long long lda, long long ldb,
+                                   long long ldo, int dtype);
+
 /* C[M,N] = A[M,K] @ B[K,N] on the CUDA cores; HC_F32, HC_F64, or HC_BF16
  * (bf16 in and out, fp32 accumulation)
  * (python/hckernel/tests/test_examples.py:74-165). */

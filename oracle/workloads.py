@@ -181,6 +181,26 @@ def reduce_rows(x, sum_out=None, max_out=None, group_rows: int = 256) -> None:
             store_tile(max_out[m0:], v.max(axis=1))
 
 
+# ---- pairwise distance ---------------------------------------------------------------
+def pairwise_distance(a, b, out, group_shape=(8, 8), mi: int = 1, ni: int = 1) -> None:
+    """Pairwise Euclidean distance: python/hckernel/tests/test_examples.py:274-301.
+
+    A group loads (m_block, D) rows of ``a`` and (n_block, D) rows of ``b`` (zero
+    padded past the ends), forms the broadcast difference and stores its norm
+    over the last axis; the clipped store drops the rows that were padding.
+    """
+    m, d = a.shape
+    n = b.shape[0]
+    gm, gn = group_shape
+    m_block, n_block = gm * mi, gn * ni
+    for _, (wm, wn) in iter_groups((ceil_div(m, mi), ceil_div(n, ni)), group_shape):
+        m0, n0 = wm * mi, wn * ni
+        a_tile = load_tile(a[m0:, :], (m_block, d))
+        b_tile = load_tile(b[n0:, :], (n_block, d))
+        diff = a_tile.data[:, None, :] - b_tile.data[None, :, :]
+        store_tile(out[m0:, n0:], np.linalg.norm(diff, axis=2))
+
+
 # ---- seeded inputs of the benchmark configurations -----------------------------
 def make_inputs(config: str, scale_rows: int | None = None, shape=None):
     """Seeded synthetic inputs of the five benchmark configurations.

@@ -152,6 +152,20 @@ def ref_reduce_all():
     return red
 
 
+def ref_pairwise():
+    M, N, D, GM, GN = sym.M, sym.N, sym.D, sym.GM, sym.GN
+
+    @kernel(work_shape=(M, N), group_shape=(GM, GN))
+    def pw(gr: CurrentGroup, a: Buffer[M, D, DT], b: Buffer[N, D, DT], out: Buffer[M, N, DT],
+           gshape: (GM, GN)):
+        m0, n0 = gr.work_offset
+        a_t = gr.load(a[m0:, :], shape=(gr.shape[0], D))
+        b_t = gr.load(b[n0:, :], shape=(gr.shape[1], D))
+        gr.store(out[m0:, n0:], np.linalg.norm(a_t[:, None, :] - b_t[None, :, :], axis=2))
+
+    return pw
+
+
 def ref_copy():
     W, H = sym.W, sym.H
 
@@ -287,6 +301,28 @@ def main():
     oracle.gemm_w8a16(a, w, s, o, (128, 128))
     same("cfg5", r, o)
     out["cfg5_gemm_w8a16_128x256x512_bits"] = oracle.bf16_bits(r)
+
+    # 4. Pairwise distance: the reference's own vector (test_examples.py:291-301)
+    #    and a ragged float32 case.
+    m, n, d = 16, 32, 8
+    a = 2 * np.arange(m * d).reshape(m, d) / (m * d)
+    b = np.arange(n * d).reshape(n, d) / (n * d)
+    r = np.zeros((m, n))
+    ref_pairwise()(a, b, r, (8, 8))
+    assert np.array_equal(r, np.linalg.norm(a[:, None, :] - b[None, :, :], axis=2))
+    o = np.zeros((m, n))
+    oracle.pairwise_distance(a, b, o, (8, 8))
+    same("pairwise_f64", r, o)
+    out["kat_pairwise_f64"] = r
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((70, 19)).astype(np.float32)
+    b = rng.standard_normal((45, 19)).astype(np.float32)
+    r = np.zeros((70, 45), np.float32)
+    ref_pairwise()(a, b, r, (16, 8))
+    o = np.zeros_like(r)
+    oracle.pairwise_distance(a, b, o, (16, 8))
+    same("pairwise_f32", r, o)
+    out["pairwise_f32_70x45x19"] = r
 
     np.savez_compressed(HERE / "reference_outputs.npz", **out)
     (HERE / "VERSIONS.txt").write_text(

@@ -105,6 +105,51 @@ def test_scalar_reductions_from_the_reference_tests():
         assert (plan.family, plan.roles) == ("reduce_all", {"a": 0, "result": 1})
 
 
+def test_pairwise_distance_from_the_reference_tests():
+    # python/hckernel/tests/test_examples.py:261-289
+    M, N, D, GM, GN, MI, NI = sym.M, sym.N, sym.D, sym.GM, sym.GN, sym.MI, sym.NI
+
+    def ceil_div(a, b):
+        return (a + b - 1) // b
+
+    tun = (TunableParam(MI, 1, range(1, 8)), TunableParam(NI, 1, range(1, 8)))
+
+    @kernel(work_shape=(ceil_div(M, MI), ceil_div(N, NI)), group_shape=(GM, GN), tunables=tun,
+            **TARGET)
+    def pw_distance(gr: CurrentGroup, a: Buffer[M, D, DT], b: Buffer[N, D, DT],
+                    out: Buffer[M, N, DT], gshape: (GM, GN)):
+        m_start = gr.work_offset[0] * MI
+        n_start = gr.work_offset[1] * NI
+        m_block = gr.shape[0] * MI
+        n_block = gr.shape[1] * NI
+        a_view = gr.load(a[m_start:, :], shape=(m_block, D))
+        b_view = gr.load(b[n_start:, :], shape=(n_block, D))
+        diff = a_view[:, None, :] - b_view[None, :, :]
+        gr.store(out[m_start:, n_start:], np.linalg.norm(diff, axis=2))
+
+    plan = pw_distance.plan_for((F((16, 8), "float64"), F((32, 8), "float64"),
+                                 F((16, 32), "float64"), (8, 8)))
+    assert (plan.family, plan.roles) == ("pairwise_distance", {"a": 0, "b": 1, "out": 2})
+    assert pw_distance.parametrize({MI: 3}).plan_for(
+        (F((70, 19)), F((45, 19)), F((70, 45)), (8, 8))).family == "pairwise_distance"
+
+
+def test_tuned_params_round_trip_and_parametrize(tmp_path, k):
+    from hc_b200.hckernel.kernel import TunedParams, autotune
+
+    KB, MI = sym.KB, sym.MI
+    tp = TunedParams({KB: 32, MI: 2}, {"gemm_variant": 2}, {"{}": 0.5})
+    path = tmp_path / "tuned.json"
+    tp.save(path)
+    back = autotune.load(path)
+    assert dict(back) == {KB: 32, MI: 2} and back.options == {"gemm_variant": 2}
+    tuned = k.dot.parametrize(back)
+    assert tuned.tuned == {KB: 32, MI: 2} and tuned.options == {"gemm_variant": 2}
+    assert k.dot.options == {}
+    # Options survive a further parametrize with plain symbols.
+    assert tuned.parametrize({KB: 64}).options == {"gemm_variant": 2}
+
+
 def test_symbol_conflicts_and_rank_errors(k):
     with pytest.raises(ValueError, match="Symbol value conflict for M"):
         k.softmax.plan_for((F((30, 25)), F((31, 25)), 8))

@@ -205,6 +205,66 @@ def ceil_div(a, b):
     return (a + b - 1) // b
 
 
+def test_autotune_picks_a_variant_and_keeps_results_right(k, tmp_path):
+    # The API of the reference's RFC (docs/langref.md:526-560):
+    # tparams = autotune(kernel, *args); tuned = kernel.parametrize(tparams).
+    a, b = oracle.make_inputs("gemm_bf16", shape=(512, 512, 256))
+    d_a = to_device(torch.from_numpy(a)).bfloat16()
+    d_b = to_device(torch.from_numpy(b)).bfloat16()
+    d_c = torch.zeros(512, 512, dtype=torch.bfloat16, device="cuda")
+    tparams = autotune(k.dot_fullk, d_a, d_b, d_c, (128, 128), repeats=3)
+    assert isinstance(tparams, TunedParams) and len(tparams.timings) >= 2
+    assert set(tparams.options) <= {"gemm_variant", "tiled_variant"}
+    tparams.save(tmp_path / "gemm.json")
+    tuned = k.dot_fullk.parametrize(autotune.load(tmp_path / "gemm.json"))
+    d_c.zero_()
+    tuned(d_a, d_b, d_c, (128, 128))
+    expect = np.zeros((512, 512), np.float32)
+    oracle.gemm_bf16(a, b, expect, (256, 256))
+    got = d_c.float().cpu().numpy()
+    assert np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * (np.abs(a) @ np.abs(b)))
+
+    (x,) = oracle.make_inputs("softmax", shape=(3000, 2048))
+    d_x = to_device(torch.from_numpy(x))
+    d_y = torch.empty_like(d_x)
+    tparams = autotune(k.softmax, d_x, d_y, 64, repeats=3)
+    assert tparams.options.get("softmax_variant") in (1, 2)
+    k.softmax.parametrize(tparams)(d_x, d_y, 64)
+    expect = np.zeros_like(x)
+    oracle.softmax_rows(x, expect, 64)
+    assert np.all(np.abs(d_y.cpu().numpy() - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+    assert get_context(DEVICE).kernel_status() == 0
+
+
+def test_pairwise_distance():
+    # python/hckernel/tests/test_examples.py:261-301, on the GPU.
+    M, N, D = sym.M, sym.N, sym.D
+    GM, GN, MI, NI = sym.GM, sym.GN, sym.MI, sym.NI
+    TMI = TunableParam(MI, 1, range(1, 8))
+    TNI = TunableParam(NI, 1, range(1, 8))
+
+    @kernel(work_shape=(ceil_div(M, MI), ceil_div(N, NI)), group_shape=(GM, GN),
+            tunables=(TMI, TNI), backend=BACKEND, device=DEVICE)
+    def pw_distance(gr: CurrentGroup, a: Buffer[M, D, typename.DT], b: Buffer[N, D, typename.DT],
+                    out: Buffer[M, N, typename.DT], gshape: (GM, GN)):
+        m_start = gr.work_offset[0] * MI
+        n_start = gr.work_offset[1] * NI
+        m_block = gr.shape[0] * MI
+        n_block = gr.shape[1] * NI
+        a_view = gr.load(a[m_start:, :], shape=(m_block, D))
+        b_view = gr.load(b[n_start:, :], shape=(n_block, D))
+        diff = a_view[:, None, :] - b_view[None, :, :]
+        gr.store(out[m_start:, n_start:], np.linalg.norm(diff, axis=2))
+
+    m, n, d = 16, 32, 8
+    a = 2 * np.arange(m * d).reshape(m, d) / (m * d)
+    b = np.arange(n * d).reshape(n, d) / (n * d)
+    result = torch.zeros(m, n, dtype=torch.float64, device="cuda")
+    pw_distance(to_device(torch.from_numpy(a)), to_device(torch.from_numpy(b)), result, (8, 8))
+    np.testing.assert_allclose(result.cpu().numpy(),
+                               np.linalg.norm(a[:, None, :] - b[None, :, :], axis=2), rtol=1e-13)
+
+
 def test_reduction_1():
     # python/hckernel/tests/test_examples.py:31-47, on the GPU.
     WS, GS, N = sym.WS, sym.GS, sym.N

@@ -479,6 +479,35 @@ def test_reduce_all_matches_oracle(hc, n, in_dtype):
     assert abs(float(d_r32.cpu().numpy()[0]) - a.astype(np.float64).sum()) <= bound
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f64"])
+@pytest.mark.parametrize("shape", [(16, 32, 8), (70, 45, 19), (1, 1, 1), (200, 130, 300), (64, 64, 0)])
+def test_pairwise_distance_matches_oracle(hc, golden, dtype, shape):
+    m, n, d = shape
+    np_t, t_t, code = ((np.float32, torch.float32, capi.HC_F32) if dtype == "f32"
+                       else (np.float64, torch.float64, capi.HC_F64))
+    if shape == (16, 32, 8):  # the reference's own test vector
+        a = (2 * np.arange(m * d).reshape(m, d) / (m * d)).astype(np_t)
+        b = (np.arange(n * d).reshape(n, d) / (n * d)).astype(np_t)
+    else:
+        rng = np.random.default_rng(5)
+        a = rng.standard_normal((m, d)).astype(np_t)
+        b = rng.standard_normal((n, d)).astype(np_t)
+    d_a, d_b = dev(a), dev(b)
+    d_o = empty_like_dev((m, n), t_t)
+    hc.pairwise_distance(d_a.data_ptr() if d else 0, d_b.data_ptr() if d else 0, d_o.data_ptr(),
+                         m, n, d, max(d, 1), max(d, 1), n, code)
+    finish(hc)
+    expect = np.zeros((m, n), np_t)
+    oracle.pairwise_distance(a, b, expect, (8, 8))
+    rtol = 1e-5 if dtype == "f32" else 1e-13
+    np.testing.assert_allclose(d_o.cpu().numpy(), expect, rtol=rtol, atol=rtol)
+    if shape == (16, 32, 8) and dtype == "f64":
+        np.testing.assert_allclose(d_o.cpu().numpy(), golden["kat_pairwise_f64"], rtol=1e-13)
+    if shape == (70, 45, 19) and dtype == "f32":
+        np.testing.assert_allclose(d_o.cpu().numpy(), golden["pairwise_f32_70x45x19"], rtol=1e-5,
+                                   atol=1e-6)
+
+
 def test_reduce_all_errors(hc):
     hc.reduce_all(0, 0, 0)  # nothing to do
     with pytest.raises(capi.HcError, match="unsupported dtypes"):

@@ -90,6 +90,23 @@ def test_benchmark_configs_reduced(golden):
     assert np.array_equal(oracle.bf16_bits(out), golden["cfg5_gemm_w8a16_128x256x512_bits"])
 
 
+def test_pairwise_distance_vectors(golden):
+    # python/hckernel/tests/test_examples.py:291-301
+    m, n, d = 16, 32, 8
+    a = 2 * np.arange(m * d).reshape(m, d) / (m * d)
+    b = np.arange(n * d).reshape(n, d) / (n * d)
+    out = np.zeros((m, n))
+    oracle.pairwise_distance(a, b, out, (8, 8))
+    assert np.array_equal(out, golden["kat_pairwise_f64"])
+    assert np.array_equal(out, np.linalg.norm(a[:, None, :] - b[None, :, :], axis=2))
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((70, 19)).astype(np.float32)
+    b = rng.standard_normal((45, 19)).astype(np.float32)
+    out = np.zeros((70, 45), np.float32)
+    oracle.pairwise_distance(a, b, out, (16, 8))
+    assert np.array_equal(out, golden["pairwise_f32_70x45x19"])
+
+
 def test_group_order_and_offsets():
     # python/hckernel/tests/test_kernel_sim.py:26-54 checks the same facts on
     # the simulator: row-major group order, offsets = id * group shape.
