@@ -117,6 +117,7 @@ struct HcContextImpl {
   long long gemmVariant = 0;
   long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
   long long tiledVariant = 0;
+  long long reduceVariant = 0;
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
@@ -317,6 +318,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->softmaxVariant = value;
     return 0;
   }
+  if (std::strcmp(name, "reduce_variant") == 0 && value >= 0 && value <= 1) {
+    c->reduceVariant = value; // 1: persistent grid for the warp-per-row kernel
+    return 0;
+  }
   if (std::strcmp(name, "tiled_variant") == 0 && value >= 0 && value <= 1) {
     c->tiledVariant = value; // 1: never use the cp.async pipelined fp32 kernel
     return 0;
@@ -379,7 +384,7 @@ int hcSoftmaxRows(HcContext c, const void *x, void *y, long long rows,
                      aligned(y, 16);
   // The bulk-copy pipelined kernel (one persistent CTA per SM, a ring of row
   // slots in shared memory) is opt-in: at 32768 x 4096 it measured 5.88 TB/s
-  // against 6.06 TB/s for the register kernel below.
+  // against 6.76 TB/s for the register kernel below.
   if (vecOk && cols > 1024 && c->ccMajor >= 9 && c->softmaxVariant == 2) {
     // Long rows: 32 float4 per lane and 6 consumer warps; else 16 and 8.
     const int v = cols > 2048 ? 32 : 16;
@@ -400,11 +405,14 @@ int hcSoftmaxRows(HcContext c, const void *x, void *y, long long rows,
     int v = 1;
     while (128 * v < cols)
       v <<= 1;
-    // Resident 128-thread CTAs per SM, from each variant's __launch_bounds__.
-    const int residency = v <= 8 ? 8 : (v == 16 ? 5 : 3);
     char name[48];
     snprintf(name, sizeof(name), "hc_softmax_rows_f32_w%d", v);
-    long long grid = std::min<long long>(ceilDiv(rows, 4), c->smCount * residency);
+    // One row per warp, four rows per CTA, as many CTAs as that takes.  A
+    // persistent grid (SMs x resident CTAs walking the rows) measured 6.03 TB/s
+    // at 32768 x 4096 against 6.76 TB/s for this: CTAs that start and retire
+    // independently keep loads and stores of different rows interleaved,
+    // while resident warps drift into doing the same phase at the same time.
+    long long grid = std::min<long long>(ceilDiv(rows, 4), 0x7fffffffLL);
     int icols = int(cols);
     void *args[] = {&x, &y, &rows, &icols, &xPitch, &yPitch};
     return c->launch(name, size_t(grid), 1, 1, 128, args, 6, 0);
@@ -440,7 +448,9 @@ int hcReduceRows(HcContext c, const void *x, void *sumOut, void *maxOut,
   const bool f32 = dtype == HC_F32;
   void *args[] = {&x, &sumOut, &maxOut, &rows, &cols, &pitch, &vec};
   if (rows >= c->smCount * 8) {
-    long long grid = std::min<long long>(ceilDiv(rows, 8), c->smCount * 8);
+    long long grid = ceilDiv(rows, 8);
+    if (c->reduceVariant == 1) // persistent: SMs x 8 CTAs walking the rows
+      grid = std::min<long long>(grid, c->smCount * 8);
     return c->launch(f32 ? "hc_reduce_rows_warp_f32" : "hc_reduce_rows_warp_f64",
                      size_t(grid), 1, 1, 256, args, 7, 0);
   }
