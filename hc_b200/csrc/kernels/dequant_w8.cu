@@ -67,26 +67,29 @@ extern "C" __global__ void __launch_bounds__(256)
   if (vec) {
     constexpr int R = 4;                 // rows in flight per thread
     const long long packets = cols >> 4; // 16 weights per packet
-    const long long rowStep = gridDim.y;
+    // blockIdx.y picks a band of R adjacent rows; bands stride by gridDim.y.
     for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
          p < packets; p += (long long)gridDim.x * blockDim.x) {
-      long long r = blockIdx.y;
-      for (; r + (R - 1) * rowStep < rows; r += R * rowStep) {
-        int4 q[R];
+      for (long long r = (long long)blockIdx.y * R; r < rows;
+           r += (long long)gridDim.y * R) {
+        if (r + R <= rows) {
+          int4 q[R];
 #pragma unroll
-        for (int i = 0; i < R; ++i)
-          q[i] = loadStream16(
-              reinterpret_cast<const int4 *>(w + (r + i * rowStep) * wPitch) + p);
+          for (int i = 0; i < R; ++i)
+            q[i] = loadStream16(
+                reinterpret_cast<const int4 *>(w + (r + i) * wPitch) + p);
 #pragma unroll
-        for (int i = 0; i < R; ++i)
-          convertAndStore(q[i], reinterpret_cast<uint4 *>(
-                                    out + (r + i * rowStep) * outPitch) +
-                                    2 * p);
+          for (int i = 0; i < R; ++i)
+            convertAndStore(q[i], reinterpret_cast<uint4 *>(
+                                      out + (r + i) * outPitch) +
+                                      2 * p);
+        } else {
+          for (long long t = r; t < rows; ++t)
+            convertAndStore(
+                loadStream16(reinterpret_cast<const int4 *>(w + t * wPitch) + p),
+                reinterpret_cast<uint4 *>(out + t * outPitch) + 2 * p);
+        }
       }
-      for (; r < rows; r += rowStep)
-        convertAndStore(
-            loadStream16(reinterpret_cast<const int4 *>(w + r * wPitch) + p),
-            reinterpret_cast<uint4 *>(out + r * outPitch) + 2 * p);
     }
   } else {
     for (long long r = blockIdx.y; r < rows; r += gridDim.y)

@@ -631,10 +631,9 @@ int hcDequantW8(HcContext c, const void *w, void *out, long long rows,
   long long perRow = vec ? cols / 16 : cols;
   long long gx = std::max<long long>(
       1, std::min<long long>(ceilDiv(perRow, 256), c->smCount * 8));
-  // Rows are walked four at a time by each thread: give every CTA row at
-  // least eight of them when the matrix is tall enough.
-  long long gy = std::max<long long>(
-      1, std::min<long long>(ceilDiv(rows, 8), c->smCount * 8 / gx));
+  // Each thread converts four rows (one batch of four loads in flight); one
+  // CTA row per batch rather than a persistent grid, as for the softmax.
+  long long gy = std::max<long long>(1, std::min<long long>(ceilDiv(rows, 4), 65535));
   void *args[] = {&w, &out, &rows, &cols, &wPitch, &outPitch, &vec};
   return c->launch("hc_dequant_w8_bf16", size_t(gx), size_t(gy), 1, 256, args, 7,
                    0);
