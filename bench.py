@@ -99,11 +99,11 @@ def describe(name):
 # dram bytes per launch from the ncu captures summarised under profiles/ (None
 # where no capture scales to the full-size launch).
 NCU_TRAFFIC = {
-    # profiles/softmax_rows_f32_w32_8192x4096.md: (134.26 + 79.48) MB for a quarter of
+    # profiles/softmax_rows_f32_w32_8192x4096.md: (134.25 + 77.85) MB for a quarter of
     # the rows, scaled by 4 (the part of Y still in L2 at kernel end is not counted).
-    "softmax": 854.9e6,
-    # profiles/reduce_rows_warp_f32_16384x8192.md: (536.92 + 3.38) MB for a quarter of the rows.
-    "reduce": 2161.2e6,
+    "softmax": 848.4e6,
+    # profiles/reduce_rows_warp_f32_16384x8192.md: (536.89 + 3.88) MB for a quarter of the rows.
+    "reduce": 2163.1e6,
     "gemm_bf16": None,
     "gemm_w8a16": None,
     "gemm_f32": None,
