@@ -508,6 +508,39 @@ def test_pairwise_distance_matches_oracle(hc, golden, dtype, shape):
                                    atol=1e-6)
 
 
+def test_empty_and_degenerate_shapes(hc):
+    # Nothing to do: no launch, no error.
+    before = hc.launch_count
+    hc.softmax_rows(0, 0, 0, 128, 128, 128)
+    hc.softmax_rows(0, 0, 16, 0, 0, 0)
+    hc.reduce_rows(0, 0, 0, 0, 64, 64)
+    hc.gemm_tiled(0, 0, 0, 0, 64, 64, 64, 64, 64)
+    hc.gemm_bf16(0, 0, 0, 64, 0, 64, 64, 0, 0)
+    hc.dequant_w8(0, 0, 0, 64, 64, 64)
+    assert hc.launch_count == before
+    # K = 0: an empty sum, so the product is all zeros (and must be written).
+    for dtype, t, fn in ((capi.HC_F32, torch.float32, "tiled"), (None, torch.bfloat16, "bf16")):
+        d_c = empty_like_dev((70, 40), t)
+        if fn == "tiled":
+            hc.gemm_tiled(0, 0, d_c.data_ptr(), 70, 40, 0, 0, 40, 40, dtype)
+        else:
+            hc.gemm_bf16(0, 0, d_c.data_ptr(), 70, 40, 0, 0, 40, 40)
+        finish(hc)
+        assert torch.count_nonzero(d_c.float()) == 0 and not torch.isnan(d_c.float()).any()
+    # One row, one column.
+    x = np.array([[3.5]], np.float32)
+    d_x, d_y = dev(x), empty_like_dev((1, 1), torch.float32)
+    hc.softmax_rows(d_x.data_ptr(), d_y.data_ptr(), 1, 1, 1, 1)
+    d_s, d_m = empty_like_dev((1,), torch.float32), empty_like_dev((1,), torch.float32)
+    hc.reduce_rows(d_x.data_ptr(), d_s.data_ptr(), d_m.data_ptr(), 1, 1, 1)
+    finish(hc)
+    assert d_y.item() == 1.0 and d_s.item() == 3.5 and d_m.item() == 3.5
+    with pytest.raises(capi.HcError, match="invalid shape"):
+        hc.gemm_bf16(0, 0, 0, 8, 8, 8, 4, 8, 8)  # lda smaller than K
+    with pytest.raises(capi.HcError, match="null buffer"):
+        hc.gemm_bf16(0, 0, 0, 8, 8, 8, 8, 8, 8)
+
+
 def test_reduce_all_errors(hc):
     hc.reduce_all(0, 0, 0)  # nothing to do
     with pytest.raises(capi.HcError, match="unsupported dtypes"):
