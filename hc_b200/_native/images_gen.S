@@ -40,6 +40,11 @@ hc_img_name_7: .asciz "dequant_w8"
 hc_img_begin_7: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
 hc_img_end_7:
 .balign 16
+hc_img_name_8: .asciz "selftest"
+.balign 16
+hc_img_begin_8: .incbin "/root/repo/hc_b200/_native/selftest.cubin"
+hc_img_end_8:
+.balign 16
 .section .data.rel.ro,"aw"
 .globl hc_b200_images
 .balign 8
@@ -68,9 +73,12 @@ hc_b200_images:
   .quad hc_img_name_7
   .quad hc_img_begin_7
   .quad hc_img_end_7
+  .quad hc_img_name_8
+  .quad hc_img_begin_8
+  .quad hc_img_end_8
 .section .rodata
 .globl hc_b200_image_count
 .balign 4
 hc_b200_image_count:
-  .long 8
+  .long 9
 .section .note.GNU-stack,"",@progbits

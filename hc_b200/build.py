@@ -38,6 +38,7 @@ KERNEL_SOURCES = [
     "gemm_tiled",
     "gemm_bf16_umma",
     "dequant_w8",
+    "selftest",
 ]
 
 NVCC_FLAGS = [

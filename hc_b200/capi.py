@@ -86,6 +86,10 @@ KERNELS_PROTOTYPES = {
     "hcLaunchCount": (_ll, [_vp]),
     "hcKernelStatus": (C.c_int, [_vp, C.POINTER(C.c_int)]),
     "hcSetOption": (C.c_int, [_vp, C.c_char_p, _ll]),
+    "hcSelfTestWaitTimeout": (
+        C.c_int,
+        [_vp, C.c_ulonglong, C.POINTER(C.c_int), C.POINTER(C.c_ulonglong), C.POINTER(C.c_int)],
+    ),
     "hcCopy2D": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcSoftmaxRows": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcReduceRows": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),

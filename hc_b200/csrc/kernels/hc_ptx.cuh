@@ -97,7 +97,8 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
 // the flag.
 __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity,
                                          volatile int *abortFlag, int *status,
-                                         int code) {
+                                         int code,
+                                         unsigned long long limitNs = kWaitLimitNs) {
   if (mbarTryWait(bar, parity))
     return true;
   unsigned long long start = globalTimerNs();
@@ -107,7 +108,7 @@ __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity,
     if ((spin & 63u) == 0) {
       if (*abortFlag)
         return false;
-      if (globalTimerNs() - start > kWaitLimitNs) {
+      if (globalTimerNs() - start > limitNs) {
         *abortFlag = 1;
         atomicCAS(status, kStatusOk, code);
         return false;

@@ -67,6 +67,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_reduce_all_i32_f64", "reduce_all"},
     {"hc_reduce_all_i64_f32", "reduce_all"},
     {"hc_reduce_all_i64_f64", "reduce_all"},
+    {"hc_selftest_wait_timeout", "selftest"},
     {"hc_pairwise_distance_f32", "pairwise_distance"},
     {"hc_pairwise_distance_f64", "pairwise_distance"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
@@ -301,6 +302,31 @@ int hcKernelStatus(HcContext c, int *statusRet) {
     return 1;
   *statusRet = value;
   return 0;
+}
+
+int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs, int *statusRet,
+                          unsigned long long *elapsedNsRet, int observedRet[2]) {
+  if (!c || !statusRet || !elapsedNsRet || !observedRet)
+    return 1;
+  if (limitNs == 0 || limitNs > 1000000000ull)
+    return c->fail("hcSelfTestWaitTimeout: limit must be between 1 ns and 1 s");
+  // Scratch: [0] elapsed ns (8 bytes), [8..16) the two observed flags.
+  auto *scratch = static_cast<unsigned char *>(olAllocDevice(c->queue, 256, 256));
+  if (!scratch)
+    return c->fail("hcSelfTestWaitTimeout: allocation failed: %s", c->lastError.c_str());
+  int rc = olxMemsetD8(c->queue, scratch, 0xff, 256);
+  auto *elapsed = reinterpret_cast<unsigned long long *>(scratch);
+  auto *observed = reinterpret_cast<int *>(scratch + 8);
+  void *args[] = {&limitNs, &c->statusWord, &elapsed, &observed};
+  rc = rc || c->launch("hc_selftest_wait_timeout", 1, 1, 1, 64, args, 4, 0);
+  unsigned char host[16] = {0};
+  rc = rc || olxMemcpyDtoH(c->queue, host, scratch, sizeof(host)) || olSyncQueue(c->queue);
+  olDeallocDevice(c->queue, scratch);
+  if (rc)
+    return c->fail("hcSelfTestWaitTimeout failed: %s", c->lastError.c_str());
+  std::memcpy(elapsedNsRet, host, 8);
+  std::memcpy(observedRet, host + 8, 8);
+  return hcKernelStatus(c, statusRet);
 }
 
 int hcReportError(HcContext c, const char *text) {

@@ -67,6 +67,18 @@ HC_B200_API long long hcLaunchCount(HcContext c);
  * kernels write when one of their bounded waits gives up (0 = none did) and
  * clears it. */
 HC_B200_API int hcKernelStatus(HcContext c, int *statusRet);
+/* Runs a one-CTA kernel whose barrier wait can never be satisfied, with the
+ * given time limit, waits for it and returns what happened: the status word
+ * it published (expected 1, "producer wait"), how long the kernel was inside
+ * (nanoseconds), and whether its two waiting threads saw their waits succeed
+ * (expected 0 and 0: one ran out of time, the other left on the abort flag).
+ * Exercises, without any fault, the mechanism that keeps a protocol bug in the
+ * TMA/tcgen05 kernels from hanging the GPU.  No counterpart in the reference. */
+HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
+                                      int *statusRet,
+                                      unsigned long long *elapsedNsRet,
+                                      int observedRet[2]);
+
 /* Tuning and test switches.  "gemm_variant": 0 = automatic, 1 = one CTA per
  * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);

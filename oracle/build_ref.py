@@ -2,7 +2,7 @@
 
 TEST INFRASTRUCTURE ONLY.  The two C++ runtime libraries of the reference
 build from a handful of source files with plain g++ (its compiler, which needs
-LLVM/MLIR and nanobind, does not - see DESIGN.md).  The sources are compiled
+LLVM/MLIR at a pinned commit and nanobind, does not).  The sources are compiled
 where they lie in the reference tree; nothing is copied into this repository,
 and the outputs go to ``oracle/_ref/`` (git-ignored):
 

@@ -1,7 +1,7 @@
 """Generate the golden vectors under ``tests/golden/`` from the reference itself.
 
-Run in a checkout that has the reference tree (default ``/root/reference``;
-override with ``HC_REFERENCE_ROOT``)::
+Run on a machine that has the reference tree (its location is taken from
+``HC_REFERENCE_ROOT``)::
 
     python tests/golden/make_golden.py
 
