@@ -409,13 +409,27 @@ def run_gpu(args):
         h_outs = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
         call = public_call(name, ins, outs)
 
-        def step():
-            with torch.cuda.stream(stream):
-                for d, h in zip(ins, h_ins):
-                    d.copy_(h, non_blocking=True)
-                call()
-                for h, d in zip(h_outs, outs):
-                    h.copy_(d, non_blocking=True)
+        if name in ("softmax", "reduce"):
+            # Row-wise workloads have a host-buffer entry point that streams row
+            # chunks through the GPU (upload, kernel and download overlapped).
+            from hc_b200 import host as hc_host
+
+            del ins, outs  # the pipeline brings its own device slots
+
+            def step():
+                with torch.cuda.stream(stream):
+                    if name == "softmax":
+                        hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
+                    else:
+                        hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
+        else:
+            def step():
+                with torch.cuda.stream(stream):
+                    for d, h in zip(ins, h_ins):
+                        d.copy_(h, non_blocking=True)
+                    call()
+                    for h, d in zip(h_outs, outs):
+                        h.copy_(d, non_blocking=True)
 
         ms, _ = timed(step, steps, warmup)
         if name == "softmax":  # the result really came back

@@ -1,0 +1,155 @@
+r"""Host-buffer entry points: run a row-wise workload on data that lives in
+(pinned) host memory, streaming it through the GPU in row chunks so that the
+upload of chunk i+1, the kernel on chunk i and the download of chunk i-1
+overlap.
+
+The reference's callers hand device tensors to a kernel and fetch results
+themselves, one blocking launch at a time (python/cpp/py-runtime/src/
+GpuRuntime.cpp:60-69).  For data that starts and ends on the host that
+serialises three transfers that the hardware can do at once: PCIe is full
+duplex and the copy engines run beside the SMs.  Rows are independent in the
+softmax and in the last-axis reductions, so the matrix is cut into row chunks
+and three streams are chained with events:
+
+    upload stream    H2D chunk i+1 ----\
+    kernel stream        kernel chunk i ----\      (the native context's own stream)
+    download stream          D2H chunk i-1
+
+Two device slots per stream pair are enough to keep all three busy.  The
+kernels are the same precompiled ones, reached through the same ``@kernel``
+objects; only whole rows are ever passed, so results are bit-identical to a
+single launch on the whole matrix.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .hckernel.kernel import get_context
+from .workloads import make_kernels
+
+_kernel_sets = {}
+
+
+def _kernels(device: str):
+    ks = _kernel_sets.get(device)
+    if ks is None:
+        ks = _kernel_sets[device] = make_kernels(device)
+    return ks
+
+
+class _RowPipeline:
+    """Chunked upload -> kernel -> download over the rows of host tensors."""
+
+    def __init__(self, device: str, chunk_rows: int):
+        self.device = device
+        self.ctx = get_context(device)
+        self.dev = torch.device("cuda", self.ctx.ordinal)
+        self.chunk_rows = int(chunk_rows)
+        self.s_up = torch.cuda.Stream(self.dev)
+        self.s_down = torch.cuda.Stream(self.dev)
+        self.s_kernel = torch.cuda.ExternalStream(self.ctx.stream, device=self.dev)
+        self._slots = {}
+
+    def _slot_buffers(self, key, shapes_dtypes):
+        bufs = self._slots.get(key)
+        if bufs is None:
+            bufs = self._slots[key] = [
+                [torch.empty(shape, dtype=dtype, device=self.dev) for shape, dtype in shapes_dtypes]
+                for _ in range(2)
+            ]
+        return bufs
+
+    def run(self, launch, host_ins, host_outs):
+        """``launch(dev_ins, dev_outs)`` is called once per chunk with device
+        views of ``rows`` rows; ``host_ins``/``host_outs`` are host tensors whose
+        first dimension is the row dimension (pinned memory makes the copies
+        asynchronous; pageable memory works but serialises them)."""
+        rows = host_ins[0].shape[0]
+        step = max(1, min(self.chunk_rows, rows))
+        d_ins = self._slot_buffers(
+            ("in", step) + tuple((tuple(t.shape[1:]), t.dtype) for t in host_ins),
+            [((step,) + tuple(t.shape[1:]), t.dtype) for t in host_ins])
+        d_outs = self._slot_buffers(
+            ("out", step) + tuple((tuple(t.shape[1:]), t.dtype) for t in host_outs),
+            [((step,) + tuple(t.shape[1:]), t.dtype) for t in host_outs])
+        kernel_done = [None, None]    # kernel finished reading/writing slot s
+        download_done = [None, None]  # download finished reading slot s
+        caller = torch.cuda.current_stream(self.dev)
+        start = torch.cuda.Event()
+        start.record(caller)
+        for s in (self.s_up, self.s_kernel, self.s_down):
+            s.wait_event(start)
+        for i, r0 in enumerate(range(0, rows, step)):
+            n = min(step, rows - r0)
+            slot = i & 1
+            if kernel_done[slot] is not None:
+                self.s_up.wait_event(kernel_done[slot])
+            with torch.cuda.stream(self.s_up):
+                for d, h in zip(d_ins[slot], host_ins):
+                    d[:n].copy_(h[r0:r0 + n], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(self.s_up)
+            self.s_kernel.wait_event(uploaded)
+            if download_done[slot] is not None:
+                self.s_kernel.wait_event(download_done[slot])
+            with torch.cuda.stream(self.s_kernel):
+                launch([d[:n] for d in d_ins[slot]], [d[:n] for d in d_outs[slot]])
+                kernel_done[slot] = torch.cuda.Event()
+                kernel_done[slot].record(self.s_kernel)
+            self.s_down.wait_event(kernel_done[slot])
+            with torch.cuda.stream(self.s_down):
+                for h, d in zip(host_outs, d_outs[slot]):
+                    h[r0:r0 + n].copy_(d[:n], non_blocking=True)
+                download_done[slot] = torch.cuda.Event()
+                download_done[slot].record(self.s_down)
+        # The caller's stream continues only after the last download.
+        caller.wait_stream(self.s_down)
+        caller.wait_stream(self.s_kernel)
+
+
+_pipelines = {}
+
+
+# Chunks of about this many bytes per matrix: small enough that the first
+# upload and the last download (which nothing overlaps) are a few percent of the
+# whole, large enough that each copy runs at full PCIe speed.
+_CHUNK_BYTES = 16 << 20
+
+
+def _default_chunk_rows(t):
+    row_bytes = max(1, t[0].numel() * t.element_size()) if t.shape[0] else 1
+    return max(1, _CHUNK_BYTES // row_bytes)
+
+
+def _pipeline(device, chunk_rows):
+    key = (device, int(chunk_rows))
+    p = _pipelines.get(key)
+    if p is None:
+        p = _pipelines[key] = _RowPipeline(device, chunk_rows)
+    return p
+
+
+def softmax_rows_host(x_host, out_host, device="cuda:0", chunk_rows=None, group_rows=256):
+    """Row softmax of a host matrix into a host matrix (both [M, N], same dtype)."""
+    if x_host.shape != out_host.shape or x_host.dtype != out_host.dtype or x_host.dim() != 2:
+        raise ValueError("softmax_rows_host: x and out must be matrices of one shape and dtype")
+    k = _kernels(device)
+    _pipeline(device, chunk_rows or _default_chunk_rows(x_host)).run(
+        lambda ins, outs: k.softmax(ins[0], outs[0], group_rows), [x_host], [out_host])
+
+
+def reduce_rows_host(x_host, sum_host, max_host, device="cuda:0", chunk_rows=None,
+                     group_rows=256):
+    """Last-axis sum and max of a host matrix [M, N] into host vectors [M]."""
+    if x_host.dim() != 2 or sum_host.shape != (x_host.shape[0],) or max_host.shape != sum_host.shape:
+        raise ValueError("reduce_rows_host: expected x [M, N], sum [M], max [M]")
+    k = _kernels(device)
+    _pipeline(device, chunk_rows or _default_chunk_rows(x_host)).run(
+        lambda ins, outs: k.reduce_rows(ins[0], outs[0], outs[1], group_rows),
+        [x_host], [sum_host, max_host])
+
+
+def synchronize(device="cuda:0"):
+    """Block until everything queued by the host entry points has finished."""
+    torch.cuda.synchronize(torch.device("cuda", get_context(device).ordinal))

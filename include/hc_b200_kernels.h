@@ -51,7 +51,10 @@ HC_B200_API int hcImageOfKernel(const char *kernelName);
 /* ---- context: device + queue + loaded images ------------------------------
  * Plays the role of the process-global device/queue pair of the reference's
  * py-runtime (GpuRuntime.cpp:23-39), but one per device description so that
- * several GPUs can be driven from one process. */
+ * several GPUs can be driven from one process.  Like the reference's runtime
+ * (no locks anywhere, gpu-runtime/cuda-runtime/src/Runtime.cpp), a context is
+ * not thread-safe: use it from one thread at a time.  Different contexts may
+ * be used from different threads. */
 HC_B200_API HcContext hcCreateContext(const char *deviceDesc,
                                       OlErrorCallback errCallback, void *ctx);
 HC_B200_API void hcReleaseContext(HcContext c);

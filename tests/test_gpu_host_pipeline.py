@@ -1,0 +1,50 @@
+"""Host-buffer entry points (hc_b200/host.py): row chunks streamed through the
+GPU with upload, kernel and download overlapped must give exactly what one
+launch on the whole matrix gives, for ragged chunking, pinned and pageable
+host memory, and repeated calls that reuse the device slots."""
+
+import numpy as np
+import pytest
+import torch
+
+from hc_b200 import host as hc_host
+from hc_b200.workloads import make_kernels
+from oracle import workloads as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("rows,cols,chunk", [(1000, 2048, 300), (64, 4096, 4096), (257, 100, 64)])
+def test_softmax_rows_host_equals_single_launch(pinned, rows, cols, chunk):
+    (x,) = oracle.make_inputs("softmax", shape=(rows, cols))
+    hx = torch.from_numpy(x)
+    hy = torch.full((rows, cols), float("nan"))
+    if pinned:
+        hx, hy = hx.pin_memory(), hy.pin_memory()
+    for _ in range(2):  # the second call reuses the device slots
+        hy.fill_(float("nan"))
+        hc_host.softmax_rows_host(hx, hy, "cuda:0", chunk_rows=chunk, group_rows=32)
+        hc_host.synchronize("cuda:0")
+        k = make_kernels("cuda:0")
+        d_x = hx.cuda()
+        d_y = torch.empty_like(d_x)
+        k.softmax(d_x, d_y, 32)
+        assert torch.equal(hy, d_y.cpu())  # bit-identical to one launch
+    expect = np.zeros_like(x)
+    oracle.softmax_rows(x, expect, 32)
+    assert np.all(np.abs(hy.numpy() - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+
+
+def test_reduce_rows_host_matches_oracle():
+    rows, cols = 3000, 1024
+    (x,) = oracle.make_inputs("reduce", shape=(rows, cols))
+    hx = torch.from_numpy(x).pin_memory()
+    hs, hm = torch.empty(rows).pin_memory(), torch.empty(rows).pin_memory()
+    hc_host.reduce_rows_host(hx, hs, hm, "cuda:0", chunk_rows=700)
+    hc_host.synchronize("cuda:0")
+    assert np.array_equal(hm.numpy(), x.max(axis=1))
+    exact = x.astype(np.float64).sum(axis=1)
+    assert np.all(np.abs(hs.numpy() - exact) <= 1e-5 * np.abs(x).astype(np.float64).sum(axis=1))
+    with pytest.raises(ValueError, match="expected x"):
+        hc_host.reduce_rows_host(hx, hs[:10], hm, "cuda:0")
