@@ -115,6 +115,49 @@ def store_tile(dst_view: np.ndarray, src) -> None:
         dst_view[region] = src[region]
 
 
+def _mapped_indices(func, shape, extents):
+    """Index arrays ``func(*index)`` for every ``index`` of a tile of ``shape``
+    plus the mask of those that fall inside ``extents``; ``func`` is applied to
+    whole index grids (the mapping lambdas only use ``+ * // %``, which NumPy
+    evaluates element-wise with the same floor semantics as Python ints)."""
+    grids = np.indices(shape, dtype=np.int64)
+    mapped = func(*grids)
+    if len(mapped) != len(extents):
+        raise ValueError("mapping returns a different rank than the array has")
+    mapped = [np.broadcast_to(np.asarray(m, dtype=np.int64), shape) for m in mapped]
+    inside = np.ones(shape, dtype=bool)
+    for m, extent in zip(mapped, extents):
+        inside &= (m >= 0) & (m < extent)
+    return mapped, inside
+
+
+def load_tile_mapped(view: np.ndarray, shape, func) -> Tile:
+    """``group.load(view, shape, mapping=m)``: python/hckernel/kernel_api.py:303-310.
+
+    Element ``index`` of the tile is ``view[func(*index)]`` when every component
+    of the mapped index lies inside ``view`` (which already starts at the tile
+    origin); otherwise it stays zero and is marked invalid.
+    """
+    shape = tuple(np.atleast_1d(shape).tolist())
+    data = np.zeros(shape, dtype=view.dtype)
+    mapped, inside = _mapped_indices(func, shape, view.shape)
+    data[inside] = view[tuple(m[inside] for m in mapped)]
+    return Tile(data, inside)
+
+
+def store_tile_mapped(dst_view: np.ndarray, src: Tile, func) -> None:
+    """``group.store(dst_view, src, mapping=m)``: python/hckernel/kernel_api.py:319-336.
+
+    Valid element ``index`` of the tile goes to ``dst_view[func(*index)]`` when
+    the mapped index lies inside ``dst_view``; everything else is dropped.  The
+    reference visits the elements in row-major order, so of two elements mapped
+    to one place the later one wins; NumPy's fancy assignment does the same.
+    """
+    mapped, inside = _mapped_indices(func, src.shape, dst_view.shape)
+    keep = inside & src.valid
+    dst_view[tuple(m[keep] for m in mapped)] = src.data[keep]
+
+
 def valid_rows(tile: Tile) -> int:
     """Number of leading rows of a row-block tile that exist in the array.
 

@@ -16,7 +16,16 @@ from concurrent.futures import ThreadPoolExecutor
 
 import numpy as np
 
-from .hcsim import alloc_tile, ceil_div, iter_groups, load_tile, store_tile, valid_rows
+from .hcsim import (
+    alloc_tile,
+    ceil_div,
+    iter_groups,
+    load_tile,
+    load_tile_mapped,
+    store_tile,
+    store_tile_mapped,
+    valid_rows,
+)
 
 
 # ---- bf16 helpers ------------------------------------------------------------
@@ -199,6 +208,128 @@ def pairwise_distance(a, b, out, group_shape=(8, 8), mi: int = 1, ni: int = 1) -
         b_tile = load_tile(b[n0:, :], (n_block, d))
         diff = a_tile.data[:, None, :] - b_tile.data[None, :, :]
         store_tile(out[m0:, n0:], np.linalg.norm(diff, axis=2))
+
+
+# ---- implicit-GEMM convolution (gathers through index mappings) ---------------------
+def conv_mappings(hf: int, wf: int):
+    """The three index mappings of the reference's convolution example
+    (python/hckernel/tests/test_examples.py:220-226): tile element -> index in
+    the sliced image / filter / output array."""
+    win = hf * wf
+
+    def x_map(i, j):
+        return (i, j // win, (j % win) % wf, (j % win) // wf)
+
+    def f_map(i, j):
+        return (j, i // win, i % wf, (i % win) // wf)
+
+    def out_map(i, j):
+        return (i, j, 0, 0)
+
+    return x_map, f_map, out_map
+
+
+def conv_implicit_gemm(x, f, out, stride: int = 1, tn: int = 8, tnf: int = 8, kb: int = 16) -> None:
+    """Convolution as an implicit GEMM: python/hckernel/tests/test_examples.py:203-252.
+
+    ``x`` [N, C, H, W], ``f`` [NF, C, HF, WF], ``out`` [N, NF, H_OUT, W_OUT], no
+    padding.  Work shape (N, NF, H_OUT*W_OUT) in groups of (TN, TNF, 1): a group
+    gathers a (TN, C*HF*WF) tile of image patches and a (C*HF*WF, TNF) tile of
+    filters through the index mappings, multiplies them in K blocks of ``kb``
+    and scatters the (TN, TNF) result to one output position.
+
+    Kept as the reference has them: ``H_OUT = (H - HF)/stride + 1`` is an exact
+    fraction, the work shape is truncated to an integer
+    (python/hckernel/kernel_sim.py:121-127), and the linear position ``w`` is
+    split as ``i = w % W_OUT`` (used on the H axis) and ``j = w // W_OUT`` (used
+    on the W axis), test_examples.py:237-240, 252.
+    """
+    from fractions import Fraction
+
+    n_img, c, h, w = x.shape
+    n_flt, cf, hf, wf = f.shape
+    if cf != c:
+        raise ValueError("image and filter channel counts differ")
+    h_out = Fraction(h - hf, stride) + 1
+    w_out = Fraction(w - wf, stride) + 1
+    sz = hf * wf * c
+    steps = ceil_div(sz, kb)
+    x_map, f_map, out_map = conv_mappings(hf, wf)
+
+    def as_index(value):
+        if Fraction(value).denominator != 1:
+            raise TypeError(f"tile origin {value} is not an integer")
+        return int(value)
+
+    work = (n_img, n_flt, int(h_out * w_out))
+    for _, (n0, q0, pos) in iter_groups(work, (tn, tnf, 1)):
+        i = as_index(pos % w_out)
+        j = as_index(pos // w_out)
+        x_view = load_tile_mapped(x[n0:, :, i * stride:, j * stride:], (tn, sz), x_map)
+        f_view = load_tile_mapped(f[q0:, :, :, :], (sz, tnf), f_map)
+        acc = alloc_tile((tn, tnf), out.dtype)
+        for step in range(steps):
+            k0 = step * kb
+            # vload of a slice of a loaded tile: zero-padded to (TN, KB); the
+            # elements the gather left invalid already hold zero.
+            x_slice = load_tile(x_view.data[:, k0:], (tn, kb))
+            f_slice = load_tile(f_view.data[k0:, :], (kb, tnf))
+            acc.data[...] = acc.data + np.dot(x_slice.data, f_slice.data)
+        store_tile_mapped(out[n0:, q0:, i:, j:], acc, out_map)
+
+
+def conv_direct(x, f, stride: int = 1) -> np.ndarray:
+    """Plain correlation, the textbook form the reference's test compares with
+    (python/hckernel/tests/test_examples.py:179-199) for square images and
+    filters: out[n, q, oh, ow] = sum x[n, :, oh*s : oh*s+HF, ow*s : ow*s+WF] * f[q]."""
+    n_img, c, h, w = x.shape
+    n_flt, _, hf, wf = f.shape
+    h_out = (h - hf) // stride + 1
+    w_out = (w - wf) // stride + 1
+    out = np.zeros((n_img, n_flt, h_out, w_out), dtype=np.result_type(x, f))
+    for oh in range(h_out):
+        for ow in range(w_out):
+            patch = x[:, :, oh * stride: oh * stride + hf, ow * stride: ow * stride + wf]
+            out[:, :, oh, ow] = np.einsum("nchw,qchw->nq", patch, f)
+    return out
+
+
+def conv_golden_cases():
+    """``(name, x shape, f shape, stride, dtype, tiles)`` of the convolution
+    vectors stored under ``tests/golden``: the grid of the reference's own test
+    (python/hckernel/tests/test_examples.py:168-176, float64) and cases it does
+    not reach - ragged tiles, rectangular images and filters, other tile sizes,
+    float32.  ``tiles`` is (TN, TNF, KB)."""
+    cases = []
+    for n in (1, 2, 4):
+        for c in (1, 3):
+            for nf in (1, 2, 8):
+                for stride in (1, 2, 3):
+                    cases.append((f"conv_n{n}_c{c}_nf{nf}_s{stride}", (n, c, 4, 4), (nf, c, 2, 2),
+                                  stride, "float64", (8, 8, 16)))
+    cases.append(("conv_ragged_tiles", (11, 3, 7, 7), (10, 3, 3, 3), 1, "float64", (8, 8, 16)))
+    cases.append(("conv_stride2_f32", (3, 2, 9, 9), (5, 2, 3, 3), 2, "float32", (8, 8, 16)))
+    cases.append(("conv_wide_image", (2, 2, 5, 8), (3, 2, 2, 2), 1, "float64", (8, 8, 16)))
+    cases.append(("conv_tall_image", (2, 2, 8, 5), (3, 2, 2, 2), 1, "float64", (8, 8, 16)))
+    cases.append(("conv_wide_filter", (2, 2, 6, 6), (3, 2, 2, 3), 1, "float64", (8, 8, 16)))
+    cases.append(("conv_tall_filter", (2, 2, 6, 6), (3, 2, 3, 2), 1, "float64", (8, 8, 16)))
+    cases.append(("conv_tiles_4x16_kb8_f32", (9, 3, 6, 6), (20, 3, 3, 3), 1, "float32", (4, 16, 8)))
+    return cases
+
+
+def make_conv_inputs(x_shape, f_shape, dtype="float32", seed: int = 6):
+    """Seeded standard-normal image and filter arrays."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(x_shape).astype(dtype)
+    f = rng.standard_normal(f_shape).astype(dtype)
+    return x, f
+
+
+def conv_out_shape(x_shape, f_shape, stride):
+    """Output shape as the reference's test computes it (test_examples.py:182-185):
+    ``int((extent - filter) / stride) + 1`` per spatial axis."""
+    return (x_shape[0], f_shape[0], int((x_shape[2] - f_shape[2]) / stride) + 1,
+            int((x_shape[3] - f_shape[3]) / stride) + 1)
 
 
 # ---- seeded inputs of the benchmark configurations -----------------------------

@@ -45,6 +45,7 @@ from hckernel.kernel_sim import (  # noqa: E402  (the reference)
     CurrentGroup,
     TunableParam,
     atomic_ref,
+    create_mapping,
     kernel,
     sym,
     typename,
@@ -164,6 +165,41 @@ def ref_pairwise():
         gr.store(out[m0:, n0:], np.linalg.norm(a_t[:, None, :] - b_t[None, :, :], axis=2))
 
     return pw
+
+
+def ref_conv(stride):
+    """The reference's implicit-GEMM convolution (test_examples.py:203-252)."""
+    N, C, H, W, NF, HF, WF = sym.N, sym.C, sym.H, sym.W, sym.NF, sym.HF, sym.WF
+    KB, TN, TNF = sym.KB, sym.TN, sym.TNF
+    H_OUT = (H - HF) / stride + 1
+    W_OUT = (W - WF) / stride + 1
+    SZ = HF * WF * C
+    steps = cdiv(SZ, KB)
+    tun = (
+        TunableParam(TN, 8, range(1, 64)),
+        TunableParam(TNF, 8, range(1, 64)),
+        TunableParam(KB, 16, range(8, 128)),
+    )
+    x_map = create_mapping(
+        lambda i, j: (i, j // (HF * WF), (j % (HF * WF)) % WF, (j % (HF * WF)) // WF))
+    f_map = create_mapping(lambda i, j: (j, i // (HF * WF), i % WF, (i % (HF * WF)) // WF))
+    out_map = create_mapping(lambda i, j: (i, j, 0, 0))
+
+    @kernel(work_shape=(N, NF, H_OUT * W_OUT), group_shape=(TN, TNF, 1), tunables=tun)
+    def conv(gr: CurrentGroup, x: Buffer[N, C, H, W, DT], f: Buffer[NF, C, HF, WF, DT],
+             out: Buffer[N, NF, H_OUT, W_OUT, DT]):
+        n0, q0, pos = gr.work_offset
+        i, j = pos % W_OUT, pos // W_OUT
+        x_view = gr.load(x[n0:, :, i * stride:, j * stride:], shape=(TN, SZ), mapping=x_map)
+        f_view = gr.load(f[q0:, :, :, :], shape=(SZ, TNF), mapping=f_map)
+        acc = gr.zeros(shape=(x_view.shape[0], f_view.shape[1]), dtype=out.dtype)
+        for step in range(steps):
+            k0 = step * KB
+            acc += np.dot(gr.vload(x_view[:, k0:], shape=(TN, KB)),
+                          gr.vload(f_view[k0:, :], shape=(KB, TNF)))
+        gr.store(out[n0:, q0:, i:, j:], acc, mapping=out_map)
+
+    return conv
 
 
 def ref_copy():
@@ -323,6 +359,25 @@ def main():
     oracle.pairwise_distance(a, b, o, (16, 8))
     same("pairwise_f32", r, o)
     out["pairwise_f32_70x45x19"] = r
+
+    # 5. Implicit-GEMM convolution through index mappings: the grid of the
+    #    reference's own test (test_examples.py:168-176; for square images and
+    #    filters the result also equals the plain correlation that test compares
+    #    with) and cases beyond it.
+    TN, TNF, KB = sym.TN, sym.TNF, sym.KB
+    for name, x_shape, f_shape, stride, dtype, (tn, tnf, kb) in oracle.conv_golden_cases():
+        x, f = oracle.make_conv_inputs(x_shape, f_shape, dtype)
+        shape = oracle.conv_out_shape(x_shape, f_shape, stride)
+        r = np.zeros(shape, dtype)
+        ref_conv(stride).parametrize({TN: tn, TNF: tnf, KB: kb})(x, f, r)
+        o = np.zeros(shape, dtype)
+        oracle.conv_implicit_gemm(x, f, o, stride, tn, tnf, kb)
+        same(name, r, o)
+        square = x_shape[2] == x_shape[3] and f_shape[2] == f_shape[3]
+        if square and (x_shape[2] - f_shape[2]) % stride == 0:
+            np.testing.assert_allclose(r, oracle.conv_direct(x, f, stride),
+                                       rtol=1e-4 if dtype == "float32" else 1e-10, atol=1e-5)
+        out[name] = r
 
     np.savez_compressed(HERE / "reference_outputs.npz", **out)
     (HERE / "VERSIONS.txt").write_text(

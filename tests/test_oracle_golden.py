@@ -107,6 +107,34 @@ def test_pairwise_distance_vectors(golden):
     assert np.array_equal(out, golden["pairwise_f32_70x45x19"])
 
 
+@pytest.mark.parametrize("case", oracle.conv_golden_cases(), ids=lambda c: c[0])
+def test_conv_implicit_gemm_vectors(golden, case):
+    """Gathers and scatters through index mappings
+    (python/hckernel/tests/test_examples.py:168-258), bit for bit."""
+    name, x_shape, f_shape, stride, dtype, (tn, tnf, kb) = case
+    x, f = oracle.make_conv_inputs(x_shape, f_shape, dtype)
+    out = np.zeros(oracle.conv_out_shape(x_shape, f_shape, stride), dtype)
+    oracle.conv_implicit_gemm(x, f, out, stride, tn, tnf, kb)
+    assert np.array_equal(out, golden[name])
+    square = x_shape[2] == x_shape[3] and f_shape[2] == f_shape[3]
+    if square and (x_shape[2] - f_shape[2]) % stride == 0:
+        # What the reference test asserts: the plain correlation.
+        tol = dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(out, oracle.conv_direct(x, f, stride), **tol)
+
+
+def test_mapped_tiles_mask_and_scatter():
+    """kernel_api.py:303-310, 319-336: out-of-range mapped indices leave zeros
+    (load) or are dropped (store); invalid tile elements are not stored."""
+    a = np.arange(12.0).reshape(3, 4)
+    t = hcsim.load_tile_mapped(a[1:, 2:], (3, 3), lambda i, j: (j, i))  # transposed gather
+    assert np.array_equal(t.data, [[6, 10, 0], [7, 11, 0], [0, 0, 0]])
+    assert np.array_equal(t.valid, [[1, 1, 0], [1, 1, 0], [0, 0, 0]])
+    dst = np.full((3, 4), -1.0)
+    hcsim.store_tile_mapped(dst[1:, :], t, lambda i, j: (i, j + 1))
+    assert np.array_equal(dst, [[-1, -1, -1, -1], [-1, 6, 10, -1], [-1, 7, 11, -1]])
+
+
 def test_group_order_and_offsets():
     # python/hckernel/tests/test_kernel_sim.py:26-54 checks the same facts on
     # the simulator: row-major group order, offsets = id * group shape.
