@@ -25,25 +25,30 @@ hc_img_name_4: .asciz "pairwise_distance"
 hc_img_begin_4: .incbin "/root/repo/hc_b200/_native/pairwise_distance.cubin"
 hc_img_end_4:
 .balign 16
-hc_img_name_5: .asciz "gemm_tiled"
+hc_img_name_5: .asciz "mapped_gemm"
 .balign 16
-hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
+hc_img_begin_5: .incbin "/root/repo/hc_b200/_native/mapped_gemm.cubin"
 hc_img_end_5:
 .balign 16
-hc_img_name_6: .asciz "gemm_bf16_umma"
+hc_img_name_6: .asciz "gemm_tiled"
 .balign 16
-hc_img_begin_6: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
+hc_img_begin_6: .incbin "/root/repo/hc_b200/_native/gemm_tiled.cubin"
 hc_img_end_6:
 .balign 16
-hc_img_name_7: .asciz "dequant_w8"
+hc_img_name_7: .asciz "gemm_bf16_umma"
 .balign 16
-hc_img_begin_7: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
+hc_img_begin_7: .incbin "/root/repo/hc_b200/_native/gemm_bf16_umma.cubin"
 hc_img_end_7:
 .balign 16
-hc_img_name_8: .asciz "selftest"
+hc_img_name_8: .asciz "dequant_w8"
 .balign 16
-hc_img_begin_8: .incbin "/root/repo/hc_b200/_native/selftest.cubin"
+hc_img_begin_8: .incbin "/root/repo/hc_b200/_native/dequant_w8.cubin"
 hc_img_end_8:
+.balign 16
+hc_img_name_9: .asciz "selftest"
+.balign 16
+hc_img_begin_9: .incbin "/root/repo/hc_b200/_native/selftest.cubin"
+hc_img_end_9:
 .balign 16
 .section .data.rel.ro,"aw"
 .globl hc_b200_images
@@ -76,9 +81,12 @@ hc_b200_images:
   .quad hc_img_name_8
   .quad hc_img_begin_8
   .quad hc_img_end_8
+  .quad hc_img_name_9
+  .quad hc_img_begin_9
+  .quad hc_img_end_9
 .section .rodata
 .globl hc_b200_image_count
 .balign 4
 hc_b200_image_count:
-  .long 9
+  .long 10
 .section .note.GNU-stack,"",@progbits

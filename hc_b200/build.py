@@ -35,6 +35,7 @@ KERNEL_SOURCES = [
     "reduce_rows",
     "reduce_all",
     "pairwise_distance",
+    "mapped_gemm",
     "gemm_tiled",
     "gemm_bf16_umma",
     "dequant_w8",
@@ -95,7 +96,7 @@ def build_cubins(verbose=False, force=False):
     """Compile every kernel source to an sm_100a cubin."""
     cuda = _cuda_home()
     OUT.mkdir(exist_ok=True)
-    headers = list((CSRC / "kernels").glob("*.cuh"))
+    headers = [*(CSRC / "kernels").glob("*.cuh"), *(CSRC / "kernels").glob("*.h")]
     outs = []
     for name in KERNEL_SOURCES:
         src = CSRC / "kernels" / f"{name}.cu"
@@ -152,7 +153,7 @@ def build_libs(verbose=False, force=False):
 
     kernels = OUT / "libhc-b200-kernels.so"
     srcs = [CSRC / "launch" / "kernels_api.cpp", INCLUDE / "hc_b200_kernels.h",
-            INCLUDE / "offload_api.h", loader, *cubins]
+            INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h", loader, *cubins]
     static_src = CSRC / "launch" / "w8a16_static.cu"
     srcs.append(static_src)
     if force or _stale(kernels, srcs):

@@ -32,6 +32,23 @@ _sz = C.c_size_t
 _vp = C.c_void_p
 _ll = C.c_longlong
 
+
+
+class HcMappedOperand(C.Structure):
+    """include/hc_b200_kernels.h: one array of hcMappedGemm with its tables."""
+
+    _fields_ = [
+        ("base", _vp),
+        ("map", _vp),
+        ("lin", _vp),
+        ("origins", _vp),
+        ("shape", C.c_int * 4),
+        ("stride", _ll * 4),
+        ("lo", C.c_int * 4),
+        ("hi", C.c_int * 4),
+    ]
+
+
 # name -> (restype, argtypes), exactly as declared in include/offload_api.h
 OL_PROTOTYPES = {
     "olCreateDevice": (_vp, [C.c_char_p, OlErrorCallback, _vp]),
@@ -96,6 +113,11 @@ KERNELS_PROTOTYPES = {
     "hcReduceAll": (C.c_int, [_vp, _vp, _ll, _vp, C.c_int, C.c_int]),
     "hcPairwiseDistance": (
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]
+    ),
+    "hcMappedGemm": (
+        C.c_int,
+        [_vp, C.POINTER(HcMappedOperand), C.POINTER(HcMappedOperand),
+         C.POINTER(HcMappedOperand), _ll, C.c_int, C.c_int, C.c_int, C.c_int],
     ),
     "hcGemmTiled": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]),
     "hcGemmBf16": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
@@ -259,6 +281,14 @@ class Context:
         self._check(
             self.lib.hcPairwiseDistance(self.handle, a, b, out, m, n, d, lda, ldb, ldo, dtype),
             "hcPairwiseDistance",
+        )
+
+    def mapped_gemm(self, x, f, out, groups, tm, tn, k, dtype=HC_F32):
+        """``x``, ``f``, ``out``: :class:`HcMappedOperand`."""
+        self._check(
+            self.lib.hcMappedGemm(self.handle, C.byref(x), C.byref(f), C.byref(out), groups,
+                                  tm, tn, k, dtype),
+            "hcMappedGemm",
         )
 
     def gemm_tiled(self, a, b, c, m, n, k, lda, ldb, ldc, dtype=HC_F32):

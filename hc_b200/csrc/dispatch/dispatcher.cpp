@@ -198,6 +198,84 @@ void pairwiseDistance(Context &ctx, py::handle a, py::handle b, py::handle out) 
             "pairwise_distance");
 }
 
+// One operand of the gathered tile product: the array (any rank up to 4, any
+// non-negative strides) and its tables (map int32 [E,4], lin int32 [E],
+// origins int32 [G,4], lo and hi as 4 ints each).
+HcMappedOperand mappedOperand(const Context &ctx, py::handle array, py::handle tables,
+                              const char *name, long long elems, long long groups,
+                              ElemKind *kind) {
+  ArrayArg a;
+  try {
+    a = hc::arrayFromPython(array);
+  } catch (const std::exception &e) {
+    throw py::type_error(std::string(name) + ": " + e.what());
+  }
+  if (!a.onDevice)
+    throw py::value_error(std::string(name) + ": expected device memory (a CUDA tensor)");
+  if (a.deviceIndex >= 0 && a.deviceIndex != ctx.ordinal)
+    throw py::value_error(std::string(name) + ": lives on another GPU than " + ctx.description);
+  if (a.rank() < 1 || a.rank() > 4)
+    throw py::value_error(std::string(name) + ": rank 1 to 4 expected");
+  *kind = a.kind;
+  HcMappedOperand op{};
+  op.base = a.data;
+  for (int d = 0; d < 4; ++d) {
+    op.shape[d] = 1;
+    op.stride[d] = 0;
+  }
+  for (int d = 0; d < a.rank(); ++d) {
+    if (a.strides[d] < 0 || a.shape[d] > 0x7fffffffLL)
+      throw py::value_error(std::string(name) + ": negative stride or extent above 2^31");
+    op.shape[d] = int(a.shape[d]);
+    op.stride[d] = a.strides[d];
+  }
+  auto t = py::cast<py::tuple>(tables);
+  if (t.size() != 5)
+    throw py::value_error(std::string(name) + ": tables must be (map, lin, origins, lo, hi)");
+  const std::string nm(name);
+  ArrayArg map = deviceArray(ctx, t[0], (nm + " map").c_str(), 2);
+  ArrayArg lin = deviceArray(ctx, t[1], (nm + " lin").c_str(), 1);
+  ArrayArg org = deviceArray(ctx, t[2], (nm + " origins").c_str(), 2);
+  for (const ArrayArg *tab : {&map, &lin, &org})
+    if (tab->kind != ElemKind::I32)
+      throw py::type_error(nm + ": tables must be int32");
+  if (map.shape[0] != elems || map.shape[1] != 4 || (elems > 1 && map.strides[0] != 4) ||
+      lin.shape[0] != elems)
+    throw py::value_error(nm + ": map/lin tables do not match the tile");
+  if (org.shape[0] != groups || org.shape[1] != 4 || (groups > 1 && org.strides[0] != 4))
+    throw py::value_error(nm + ": origins table does not match the work-groups");
+  op.map = static_cast<const int *>(map.data);
+  op.lin = static_cast<const int *>(lin.data);
+  op.origins = static_cast<const int *>(org.data);
+  auto lo = py::cast<std::vector<int>>(t[3]), hi = py::cast<std::vector<int>>(t[4]);
+  if (lo.size() != 4 || hi.size() != 4)
+    throw py::value_error(nm + ": lo and hi must have 4 entries");
+  for (int d = 0; d < 4; ++d) {
+    op.lo[d] = lo[d];
+    op.hi[d] = hi[d];
+  }
+  return op;
+}
+
+void mappedGemm(Context &ctx, py::handle x, py::handle xTables, py::handle f,
+                py::handle fTables, py::handle out, py::handle outTables, long long groups,
+                int tm, int tn, int k) {
+  if (groups < 0 || tm < 0 || tn < 0 || k < 0)
+    throw py::value_error("mapped_gemm: negative size");
+  ElemKind kx, kf, ko;
+  HcMappedOperand X = mappedOperand(ctx, x, xTables, "x", (long long)tm * k, groups, &kx);
+  HcMappedOperand F = mappedOperand(ctx, f, fTables, "f", (long long)k * tn, groups, &kf);
+  HcMappedOperand O = mappedOperand(ctx, out, outTables, "out", (long long)tm * tn, groups, &ko);
+  if (kx != kf || kx != ko)
+    throw py::type_error("mapped_gemm: x, f and out differ in element type");
+  if (kx != ElemKind::F32 && kx != ElemKind::F64)
+    throw py::type_error(std::string("mapped_gemm: float32 or float64 expected, got ") +
+                         hc::kindName(kx));
+  ctx.check(hcMappedGemm(ctx.get(), &X, &F, &O, groups, tm, tn, k,
+                         kx == ElemKind::F32 ? HC_F32 : HC_F64),
+            "mapped_gemm");
+}
+
 void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
   ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
            C = deviceArray(ctx, out, "out", 2);
@@ -286,6 +364,9 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
   m.def("pairwise_distance", &pairwiseDistance, py::arg("ctx"), py::arg("a"), py::arg("b"),
         py::arg("out"));
+  m.def("mapped_gemm", &mappedGemm, py::arg("ctx"), py::arg("x"), py::arg("x_tables"),
+        py::arg("f"), py::arg("f_tables"), py::arg("out"), py::arg("out_tables"),
+        py::arg("groups"), py::arg("tm"), py::arg("tn"), py::arg("k"));
   m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());

@@ -1,0 +1,23 @@
+// Kernel parameter block of the gathered tile product (mapped_gemm.cu), shared
+// by the kernel and by the host code that fills it, so both see one layout.
+#pragma once
+
+#include <stdint.h>
+
+// One array as a work-group sees it through an index mapping.  Ranks below 4
+// are padded: shape 1, stride 0, origin 0, relative index 0.
+struct HcMappedOperandDev {
+  void *base;             // element [0, 0, 0, 0] of the array
+  const int32_t *map;     // [tile elements][4]: index relative to the tile origin
+  const int32_t *lin;     // [tile elements]: sum(map[d] * stride[d]), in elements
+  const int32_t *origins; // [groups][4]: tile origin of every work-group
+  int32_t shape[4];
+  int64_t stride[4]; // in elements
+  int32_t lo[4];     // smallest relative index per dimension over the tile
+  int32_t hi[4];     // largest relative index per dimension over the tile
+};
+
+struct HcMappedGemmParams {
+  HcMappedOperandDev x, f, out; // tiles [TM, K], [K, TN], [TM, TN], row-major
+  int32_t TM, TN, K;
+};

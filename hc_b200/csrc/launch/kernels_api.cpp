@@ -9,11 +9,14 @@
 // entry point that validates its arguments and chooses a kernel variant.
 #include "hc_b200_kernels.h"
 
+#include "../kernels/mapped_params.h"
+
 #include <cuda.h> // CUtensorMap (type only; no driver call is made here)
 #include <dlfcn.h>
 
 #include <algorithm>
 #include <cstdarg>
+#include <cstddef>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -70,6 +73,12 @@ const KernelEntry kKernelTable[] = {
     {"hc_selftest_wait_timeout", "selftest"},
     {"hc_pairwise_distance_f32", "pairwise_distance"},
     {"hc_pairwise_distance_f64", "pairwise_distance"},
+    {"hc_mapped_gemm_f32_t1", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_t2", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_t4", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_t1", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_t2", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_t4", "mapped_gemm"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f32_async", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
@@ -528,6 +537,66 @@ int hcPairwiseDistance(HcContext c, const void *a, const void *b, void *out,
   void *args[] = {&a, &b, &out, &M, &N, &D, &lda, &ldb, &ldo};
   return c->launch(dtype == HC_F32 ? "hc_pairwise_distance_f32" : "hc_pairwise_distance_f64",
                    size_t(ceilDiv(N, 64)), size_t(ceilDiv(M, 64)), 1, 256, args, 9, 0);
+}
+
+// ---- gathered tile product --------------------------------------------------------
+static_assert(sizeof(HcMappedOperand) == sizeof(HcMappedOperandDev) &&
+                  offsetof(HcMappedOperand, shape) == offsetof(HcMappedOperandDev, shape) &&
+                  offsetof(HcMappedOperand, stride) == offsetof(HcMappedOperandDev, stride) &&
+                  offsetof(HcMappedOperand, lo) == offsetof(HcMappedOperandDev, lo) &&
+                  offsetof(HcMappedOperand, hi) == offsetof(HcMappedOperandDev, hi),
+              "public operand description and kernel parameter block differ");
+
+int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f,
+                 const HcMappedOperand *out, long long groups, int TM, int TN, int K,
+                 int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcMappedGemm: unsupported dtype %d", dtype);
+  if (!x || !f || !out)
+    return c->fail("hcMappedGemm: null operand description");
+  if (groups < 0 || TM < 0 || TN < 0 || K < 0)
+    return c->fail("hcMappedGemm: invalid sizes groups=%lld TM=%d TN=%d K=%d", groups, TM, TN,
+                   K);
+  if (groups > 0x7fffffffLL)
+    return c->fail("hcMappedGemm: %lld work-groups exceed one launch", groups);
+  // Tile element indices are ints inside the kernel.
+  if ((long long)TM * K > 0x7fffffffLL || (long long)K * TN > 0x7fffffffLL ||
+      (long long)TM * TN > 0x7fffffffLL)
+    return c->fail("hcMappedGemm: tile of %d x %d x %d is too large", TM, TN, K);
+  if (groups == 0 || TM == 0 || TN == 0)
+    return 0;
+  const HcMappedOperand *ops[3] = {x, f, out};
+  const char *names[3] = {"x", "f", "out"};
+  for (int i = 0; i < 3; ++i) {
+    const bool used = i == 2 || K > 0; // with K == 0 the operands are never read
+    if (!used)
+      continue;
+    if (!ops[i]->base || !ops[i]->map || !ops[i]->lin || !ops[i]->origins)
+      return c->fail("hcMappedGemm: null buffer or table in %s", names[i]);
+    if (!aligned(ops[i]->map, 16) || !aligned(ops[i]->origins, 16))
+      return c->fail("hcMappedGemm: tables of %s are not 16-byte aligned", names[i]);
+    for (int d = 0; d < 4; ++d)
+      if (ops[i]->shape[d] < 0 || ops[i]->stride[d] < 0)
+        return c->fail("hcMappedGemm: negative extent or stride in %s", names[i]);
+  }
+  HcMappedGemmParams p;
+  std::memcpy(&p.x, x, sizeof(HcMappedOperand));
+  std::memcpy(&p.f, f, sizeof(HcMappedOperand));
+  std::memcpy(&p.out, out, sizeof(HcMappedOperand));
+  p.TM = TM;
+  p.TN = TN;
+  p.K = K;
+  // Smallest 16*MT square that holds the tile, up to 64; larger tiles are
+  // walked in 64 x 64 pieces by the kernel.
+  const int side = std::max(TM, TN);
+  const char *variant = side <= 16 ? "t1" : side <= 32 ? "t2" : "t4";
+  char name[48];
+  std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_%s", dtype == HC_F32 ? "f32" : "f64",
+                variant);
+  void *args[] = {&p};
+  return c->launch(name, size_t(groups), 1, 1, 256, args, 1, 0);
 }
 
 // ---- GEMMs ----------------------------------------------------------------------

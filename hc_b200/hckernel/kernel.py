@@ -37,6 +37,7 @@ import sympy
 
 from . import settings
 from .kernel_api import *  # noqa: F401,F403  (the reference re-exports kernel_api)
+from .mapped import match_mapped
 from .kernel_api import (
     Affine,
     Buffer,
@@ -139,20 +140,29 @@ def _to_int(value, subs, what):
         return tuple(_to_int(v, subs, what) for v in value)
     if isinstance(value, sympy.Expr):
         value = value.subs(subs)
-        if not value.is_Integer:
-            raise ValueError(f"{what} does not resolve to an integer: {value}")
+        if value.free_symbols:
+            raise ValueError(f"{what} does not resolve to a number: {value}")
+    # A fraction is truncated, as the reference's int() does
+    # (kernel_sim.py:121-127); its convolution example relies on it.
     return int(value)
 
 
-def _resolve_symbols(func, subs, extra):
+def _resolve_symbols(func, subs, extra, _open=()):
     """``func`` with every global and closure value that is a symbol or symbolic
     expression replaced by its integer value, and ``extra`` objects swapped
-    (reference kernel_api.py:43-90 does the same for the simulator)."""
+    (reference kernel_api.py:43-90 does the same for the simulator).  The
+    functions of index mappings are resolved the same way (kernel_api.py:53-54);
+    ``_open`` holds the mappings being resolved, so that one that is visible
+    from its own function's globals does not recurse for ever."""
 
     def resolve(value):
         if isinstance(value, sympy.Expr) and value.free_symbols:
             out = value.subs(subs)
             return int(out) if out.is_Integer else out
+        if isinstance(value, Mapping):
+            if any(value is m for m in _open):
+                return value
+            return Mapping(_resolve_symbols(value.func, subs, extra, _open + (value,)))
         try:
             return extra.get(value, value)
         except TypeError:  # unhashable
@@ -537,8 +547,13 @@ class KernelDispatcher:
             else:
                 stand_ins.append(a)
         body(recorder, *stand_ins)
-        if not recorder.stores and not recorder.atomics:
+        if not recorder.stores and not recorder.atomics and not recorder.scatters:
             raise UnsupportedKernel(f"{self.func.__name__}: the kernel stores nothing")
+        if recorder.scatters:
+            if recorder.atomics:
+                raise UnsupportedKernel("kernels that mix mapped stores and atomic updates")
+            spec = match_mapped(recorder.scatters, recorder.stores, counts)
+            return _Plan("mapped_gemm", x=spec.x.arg, f=spec.f.arg, out=spec.out.arg, spec=spec)
         if recorder.atomics:
             if recorder.stores:
                 raise UnsupportedKernel("kernels that mix stores and atomic updates")
@@ -568,6 +583,10 @@ class KernelDispatcher:
 
         ctx = get_context(self.device)
         r = plan.roles
+        if plan.family == "mapped_gemm":
+            # Upload the index tables (first call only) on torch's stream, before
+            # the fence orders the launch after that stream.
+            r["spec"].device_tables((args[r["x"]], args[r["f"]], args[r["out"]]))
         fence = _StreamFence(ctx, args)
         fence.before()
         for name, value in self.options.items():
@@ -592,6 +611,11 @@ class KernelDispatcher:
             native.reduce_all(ctx, args[r["a"]], args[r["result"]])
         elif plan.family == "pairwise_distance":
             native.pairwise_distance(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
+        elif plan.family == "mapped_gemm":
+            spec = r["spec"]
+            x, f, out = args[r["x"]], args[r["f"]], args[r["out"]]
+            tx, tf, to = spec.device_tables((x, f, out))
+            native.mapped_gemm(ctx, x, tx, f, tf, out, to, spec.groups, spec.tm, spec.tn, spec.k)
         elif plan.family == "gemm":
             native.gemm(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
         elif plan.family == "gemm_w8a16":

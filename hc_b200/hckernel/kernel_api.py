@@ -22,9 +22,15 @@ Semantics the recording keeps from the reference:
 * ``group.store(view, tile)`` writes the tile clipped to the array
   (kernel_api.py:318-342);
 * ``zeros/ones/full/empty`` and their ``v*`` twins allocate tiles
-  (kernel_api.py:347-369).
+  (kernel_api.py:347-369);
+* ``group.load(view, shape, mapping=m)`` gathers: tile element ``index`` is
+  ``view[m.func(*index)]`` or zero when that falls outside ``view``
+  (kernel_api.py:303-310); ``group.store(view, tile, mapping=m)`` scatters the
+  same way and drops what falls outside (kernel_api.py:319-336).  The recording
+  keeps the mapping object; the launch plan evaluates it into index tables.
 """
 
+import fractions
 from collections.abc import Iterable
 from math import prod
 
@@ -83,9 +89,9 @@ class Mapping:
 
 
 def create_mapping(func):
-    """Index mapping for gather/scatter loads (reference: kernel_api.py:214-220).
-    Accepted so that programs import cleanly; a kernel that uses one is not in
-    any precompiled family and fails at its first call."""
+    """Index mapping for gathering loads and scattering stores (reference:
+    kernel_api.py:214-220): ``func(*tile_index)`` gives the index, relative to
+    the sliced array, that the tile element is read from or written to."""
     return Mapping(func)
 
 
@@ -117,6 +123,8 @@ class Affine:
         return not self.coefs
 
     def __add__(self, other):
+        if isinstance(other, IndexExpr):
+            return NotImplemented
         o = Affine.of(other)
         coefs = dict(self.coefs)
         for d, c in o.coefs.items():
@@ -135,12 +143,14 @@ class Affine:
         return Affine.of(other) - self
 
     def __mul__(self, other):
+        if isinstance(other, IndexExpr):
+            return NotImplemented
         o = Affine.of(other)
         if o.is_const():
             return Affine(self.const * o.const, {d: c * o.const for d, c in self.coefs.items()})
         if self.is_const():
             return o * self
-        raise UnsupportedKernel("product of two group offsets")
+        return IndexExpr("mul", self, o)
 
     __rmul__ = __mul__
 
@@ -149,11 +159,30 @@ class Affine:
             raise UnsupportedKernel(f"{what} of a group offset")
         return self.const
 
+    # `w // W_OUT` and `w % W_OUT` (reference tests/test_examples.py:237-238):
+    # the divisor is a constant, possibly a fraction; a group offset on the
+    # left makes the result a non-affine IndexExpr.
     def __floordiv__(self, other):
-        return Affine(self._as_int("division") // Affine.of(other)._as_int("division"))
+        p, q = _ratio(other, "division")
+        if self.is_const():
+            return Affine((self.const * q) // p)
+        return IndexExpr("floordiv", self, p, q)
 
     def __mod__(self, other):
-        return Affine(self._as_int("modulo") % Affine.of(other)._as_int("modulo"))
+        p, q = _ratio(other, "modulo")
+        if self.is_const():
+            rest = (self.const * q) % p
+            if rest % q:
+                raise UnsupportedKernel(f"{self.const} % {p}/{q} is not an integer")
+            return Affine(rest // q)
+        return IndexExpr("mod", self, p, q)
+
+    def evaluate(self, gids):
+        """Value for group ids given as one integer array per group axis."""
+        out = np.full(np.shape(gids[0]) if len(gids) else (), self.const, dtype=np.int64)
+        for d, c in self.coefs.items():
+            out = out + c * gids[d]
+        return out
 
     def __index__(self):
         return self._as_int("integer value")
@@ -177,6 +206,113 @@ class Affine:
         terms = [str(self.const)] if self.const or not self.coefs else []
         terms += [f"{c}*gid{d}" for d, c in sorted(self.coefs.items())]
         return " + ".join(terms)
+
+
+def _ratio(value, what):
+    """A positive constant divisor as (numerator, denominator)."""
+    if isinstance(value, Affine) and value.is_const():
+        value = value.const
+    if isinstance(value, (int, np.integer, sympy.Integer)):
+        p, q = int(value), 1
+    elif isinstance(value, sympy.Rational):
+        p, q = int(value.p), int(value.q)
+    elif isinstance(value, fractions.Fraction):
+        p, q = value.numerator, value.denominator
+    else:
+        raise UnsupportedKernel(f"{what} by {value!r}: the divisor must be a constant")
+    if p <= 0:
+        raise UnsupportedKernel(f"{what} by the non-positive constant {value}")
+    return p, q
+
+
+class IndexExpr:
+    """An integer that depends on the group id in a non-affine way: quotients
+    and remainders of group offsets by constants, and sums and products built
+    from them.  Evaluated for all work-groups at once when a launch plan is
+    made; never needed as a single number while the body is recorded."""
+
+    __slots__ = ("op", "args")
+
+    def __init__(self, op, *args):
+        self.op = op
+        self.args = args
+
+    @staticmethod
+    def of(value):
+        return value if isinstance(value, (Affine, IndexExpr)) else Affine.of(value)
+
+    def is_const(self):
+        return False
+
+    # The affine view the family matchers read: a non-affine origin fits none.
+    @property
+    def const(self):
+        raise UnsupportedKernel(f"tile origin {self!r} is not affine in the group id")
+
+    coefs = const
+
+    def __add__(self, other):
+        return IndexExpr("add", self, IndexExpr.of(other))
+
+    __radd__ = __add__
+
+    def __sub__(self, other):
+        return IndexExpr("add", self, IndexExpr.of(other) * -1)
+
+    def __rsub__(self, other):
+        return IndexExpr("add", IndexExpr.of(other), self * -1)
+
+    def __neg__(self):
+        return self * -1
+
+    def __mul__(self, other):
+        return IndexExpr("mul", self, IndexExpr.of(other))
+
+    __rmul__ = __mul__
+
+    def __floordiv__(self, other):
+        return IndexExpr("floordiv", self, *_ratio(other, "division"))
+
+    def __mod__(self, other):
+        return IndexExpr("mod", self, *_ratio(other, "modulo"))
+
+    def __index__(self):
+        raise UnsupportedKernel(f"{self!r} has no single value: it depends on the group id")
+
+    __int__ = __index__
+
+    def key(self):
+        return (self.op,) + tuple(a.key() if hasattr(a, "key") else a for a in self.args)
+
+    def __eq__(self, other):
+        return isinstance(other, IndexExpr) and self.key() == other.key()
+
+    def __hash__(self):
+        return hash(self.key())
+
+    def evaluate(self, gids):
+        a = self.args[0].evaluate(gids)
+        if self.op == "add":
+            return a + self.args[1].evaluate(gids)
+        if self.op == "mul":
+            return a * self.args[1].evaluate(gids)
+        p, q = self.args[1], self.args[2]
+        if self.op == "floordiv":
+            return (a * q) // p
+        rest = (a * q) % p  # self.op == "mod"
+        if q != 1:
+            if np.any(rest % q):
+                raise UnsupportedKernel(f"{self!r} is not an integer for every work-group")
+            rest = rest // q
+        return rest
+
+    def __repr__(self):
+        if self.op in ("add", "mul"):
+            sign = " + " if self.op == "add" else " * "
+            return f"({self.args[0]!r}{sign}{self.args[1]!r})"
+        sign = " // " if self.op == "floordiv" else " % "
+        divisor = str(self.args[1]) if self.args[2] == 1 else f"({self.args[1]}/{self.args[2]})"
+        return f"({self.args[0]!r}{sign}{divisor})"
 
 
 def dtype_name(dtype):
@@ -223,14 +359,14 @@ class BufferRef:
                 )
             if k.stop is not None or k.step is not None:
                 raise UnsupportedKernel(f"{self.name}[...]: slices with stop/step are not supported")
-            origin.append(Affine.of(0 if k.start is None else k.start))
+            origin.append(IndexExpr.of(0 if k.start is None else k.start))
         origin += [Affine(0)] * (self.ndim - len(origin))
         return tuple(origin)
 
     @staticmethod
     def _is_element(key):
         keys = key if isinstance(key, tuple) else (key,)
-        return all(isinstance(k, (int, np.integer)) for k in keys)
+        return len(keys) > 0 and all(isinstance(k, (int, np.integer)) for k in keys)
 
     def __getitem__(self, key):
         if self._is_element(key):
@@ -312,7 +448,9 @@ class Tile:
 
     ``op`` is one of ``load``, ``alloc``, ``const``, ``add``/``sub``/``mul``/
     ``div``, ``exp``, ``dot``, ``astype``, ``sum``/``max`` (with ``axis`` and
-    ``keepdims``).
+    ``keepdims``), ``gather`` (a load through a mapping), ``slice`` (a tile
+    seen from ``offsets`` onwards) and ``window`` (a slice cut or zero-padded
+    to a shape by ``vload``).
     """
 
     __array_priority__ = 1000
@@ -393,10 +531,29 @@ class Tile:
     def copy(self):
         return self
 
+    def _window(self, key):
+        """``tile[:, k0:]`` - the tile seen from an offset onwards (to be cut to
+        size by ``group.vload(..., shape)``)."""
+        if len(key) > self.ndim:
+            raise IndexError("too many indices for a tile")
+        offsets = []
+        for k in key:
+            if k.stop is not None or k.step is not None:
+                raise UnsupportedKernel("tile slices with stop or step are not supported")
+            start = 0 if k.start is None else int(Affine.of(k.start))
+            if start < 0:
+                raise UnsupportedKernel("tile slices from a negative offset are not supported")
+            offsets.append(start)
+        offsets += [0] * (self.ndim - len(offsets))
+        shape = tuple(max(0, s - o) for s, o in zip(self.shape, offsets))
+        return Tile("slice", (self,), shape, self.dtype, offsets=tuple(offsets))
+
     def __getitem__(self, key):
-        # Only `tile[:, None, :]`-style indexing: full slices and new axes.
+        # `tile[:, None, :]` (full slices and new axes) or `tile[:, k0:]`.
         if not isinstance(key, tuple):
             key = (key,)
+        if all(isinstance(k, slice) for k in key) and any(k != slice(None) for k in key):
+            return self._window(key)
         shape, dims = [], iter(self.shape)
         for k in key:
             if k is None:
@@ -486,6 +643,7 @@ class CurrentGroup:
         self._subgroup_size = subgroup_size
         self._group_id = tuple(Affine(0, {d: 1}) for d in range(len(self._group_shape)))
         self.stores = []
+        self.scatters = []  # stores through a mapping: (view, tile, mapping)
         self.atomics = []
 
     @property
@@ -506,24 +664,41 @@ class CurrentGroup:
 
     # -- memory ------------------------------------------------------------------
     def load(self, array, shape, mapping=None):
-        if mapping is not None:
-            raise UnsupportedKernel("group.load(mapping=...) is not supported")
+        if mapping is not None and not isinstance(mapping, Mapping):
+            raise TypeError("mapping must come from create_mapping")
+        if isinstance(array, Tile):
+            # A tile (or a slice of one) loaded again: cut or zero-padded to
+            # `shape`, as the reference's load does with any array-like source.
+            if mapping is not None:
+                raise UnsupportedKernel("a mapping on a load from a tile is not supported")
+            base, offsets = array, (0,) * array.ndim
+            if array.op == "slice":
+                base, offsets = array.args[0], array.attrs["offsets"]
+            shape = _shape_tuple(shape)
+            if len(shape) != base.ndim:
+                raise UnsupportedKernel("load from a tile with a different rank")
+            return Tile("window", (base,), shape, base.dtype, offsets=offsets)
         if isinstance(array, BufferRef):
             array = array[()]
         if not isinstance(array, BufferView):
             raise UnsupportedKernel(f"group.load source {array!r} is not a kernel buffer")
+        if mapping is not None:
+            return Tile("gather", (array,), _shape_tuple(shape), array.dtype, mapping=mapping)
         return Tile("load", (array,), _shape_tuple(shape), array.dtype)
 
     def vload(self, array, shape, mapping=None):
         return self.load(array, shape, mapping)
 
     def store(self, dst, src, mapping=None):
-        if mapping is not None:
-            raise UnsupportedKernel("group.store(mapping=...) is not supported")
         if isinstance(dst, BufferRef):
             dst = dst[()]
         if not isinstance(dst, BufferView):
             raise UnsupportedKernel(f"group.store destination {dst!r} is not a kernel buffer")
+        if mapping is not None:
+            if not isinstance(mapping, Mapping):
+                raise TypeError("mapping must come from create_mapping")
+            self.scatters.append((dst, Tile._wrap(src), mapping))
+            return
         self.stores.append((dst, Tile._wrap(src)))
 
     # -- allocators ---------------------------------------------------------------

@@ -89,3 +89,47 @@ def make_kernels(device="cuda:0"):
 
     return types.SimpleNamespace(copy=copy, softmax=softmax, reduce_rows=reduce_rows, dot=dot,
                                  dot_fullk=dot_fullk, dequant_dot=dequant_dot, device=device)
+
+
+def make_conv(stride=1, device="cuda:0"):
+    """The convolution written as an implicit GEMM, as in the reference's
+    example (python/hckernel/tests/test_examples.py:203-252): ``conv(x, f, out)``
+    with x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, H_OUT, W_OUT], no
+    padding.  A work-group of (TN, TNF, 1) gathers TN receptive fields and TNF
+    filters through index mappings, multiplies them in K blocks of KB and
+    scatters the (TN, TNF) products to one output position.  TN, TNF and KB are
+    tunables (defaults 8, 8, 16): ``conv.parametrize({sym.TN: 32, ...})``."""
+    from .hckernel.kernel import create_mapping
+
+    N, C, H, W, NF, HF, WF = sym.N, sym.C, sym.H, sym.W, sym.NF, sym.HF, sym.WF
+    KB, TN, TNF = sym.KB, sym.TN, sym.TNF
+    H_OUT = (H - HF) / stride + 1
+    W_OUT = (W - WF) / stride + 1
+    SZ = HF * WF * C
+    steps = _cdiv(SZ, KB)
+    tunables = (
+        TunableParam(TN, 8, range(1, 64)),
+        TunableParam(TNF, 8, range(1, 64)),
+        TunableParam(KB, 16, range(8, 128)),
+    )
+    x_map = create_mapping(
+        lambda i, j: (i, j // (HF * WF), (j % (HF * WF)) % WF, (j % (HF * WF)) // WF))
+    f_map = create_mapping(lambda i, j: (j, i // (HF * WF), i % WF, (i % (HF * WF)) // WF))
+    out_map = create_mapping(lambda i, j: (i, j, 0, 0))
+
+    @kernel(work_shape=(N, NF, H_OUT * W_OUT), group_shape=(TN, TNF, 1), tunables=tunables,
+            backend="nvvm", device=device)
+    def conv(gr: CurrentGroup, x: Buffer[N, C, H, W, DT], f: Buffer[NF, C, HF, WF, DT],
+             out: Buffer[N, NF, H_OUT, W_OUT, DT]):
+        n0, q0, pos = gr.work_offset
+        i, j = pos % W_OUT, pos // W_OUT
+        x_view = gr.load(x[n0:, :, i * stride:, j * stride:], shape=(TN, SZ), mapping=x_map)
+        f_view = gr.load(f[q0:, :, :, :], shape=(SZ, TNF), mapping=f_map)
+        acc = gr.zeros(shape=(x_view.shape[0], f_view.shape[1]), dtype=out.dtype)
+        for step in range(steps):
+            k0 = step * KB
+            acc += np.dot(gr.vload(x_view[:, k0:], shape=(TN, KB)),
+                          gr.vload(f_view[k0:, :], shape=(KB, TNF)))
+        gr.store(out[n0:, q0:, i:, j:], acc, mapping=out_map)
+
+    return conv

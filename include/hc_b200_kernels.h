@@ -120,6 +120,38 @@ HC_B200_API int hcPairwiseDistance(HcContext c, const void *a, const void *b,
                                    long long D, long long lda, long long ldb,
                                    long long ldo, int dtype);
 
+/* Gathered tile product: what work-groups compute that load their operand tiles
+ * with group.load(view, shape, mapping=...), multiply them and write the result
+ * with group.store(view, tile, mapping=...)
+ * (python/hckernel/kernel_api.py:297-336; the implicit-GEMM convolution of
+ * python/hckernel/tests/test_examples.py:203-252).  For every work-group g
+ *   A[a,k] = x[xOrigin(g) + xMap(a,k)],  B[k,b] = f[fOrigin(g) + fMap(k,b)]
+ *   out[oOrigin(g) + oMap(a,b)] = sum_k A[a,k] * B[k,b]
+ * where an operand element whose mapped index falls outside its array reads as
+ * zero and a result element whose mapped index falls outside `out` is dropped.
+ * The mappings arrive as tables in device memory, evaluated by the caller:
+ *   map      int32 [tile elements][4]  mapped index relative to the tile origin
+ *   lin      int32 [tile elements]     sum_d map[d] * stride[d]
+ *   origins  int32 [groups][4]         tile origin of every work-group (>= 0)
+ * with tile elements in row-major order of the tile ([TM,K], [K,TN], [TM,TN]);
+ * `map` and `origins` must be 16-byte aligned.  Arrays of rank below 4 are
+ * padded with shape 1, stride 0 and zeros in the tables.  lo/hi are the
+ * smallest/largest value of each column of `map`.  Distinct (group, element)
+ * pairs must not map to the same element of `out`.  HC_F32 or HC_F64. */
+typedef struct HcMappedOperand {
+  void *base;           /* device: element [0,0,0,0] of the array */
+  const int *map;       /* device */
+  const int *lin;       /* device */
+  const int *origins;   /* device */
+  int shape[4];
+  long long stride[4];  /* in elements */
+  int lo[4];
+  int hi[4];
+} HcMappedOperand;
+HC_B200_API int hcMappedGemm(HcContext c, const HcMappedOperand *x,
+                             const HcMappedOperand *f, const HcMappedOperand *out,
+                             long long groups, int TM, int TN, int K, int dtype);
+
 /* C[M,N] = A[M,K] @ B[K,N] on the CUDA cores; HC_F32, HC_F64, or HC_BF16
  * (bf16 in and out, fp32 accumulation)
  * (python/hckernel/tests/test_examples.py:74-165). */

@@ -222,8 +222,13 @@ def test_affine_offsets():
     assert (g0 * 4) * 2 == g0 * 8
     assert (g0 + g1 - g0) == g1
     assert int(Affine(7) // 2) == 3 and int(Affine(7) % 4) == 3
-    with pytest.raises(UnsupportedKernel):
-        _ = g0 * g1
+    # Products, quotients and remainders of group offsets leave the affine
+    # family: no whole-array kernel takes such a tile origin (tests/
+    # test_mapped_cpu.py covers where they are accepted).
+    with pytest.raises(UnsupportedKernel, match="not affine"):
+        _ = (g0 * g1).const
+    with pytest.raises(UnsupportedKernel, match="not affine"):
+        _ = (g0 % 3).coefs
     with pytest.raises(UnsupportedKernel):
         int(g0)
 
