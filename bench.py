@@ -44,7 +44,13 @@ SHAPES = {
     "gemm_f32": (256, 256, 256),
     "gemm_bf16": (8192, 8192, 8192),
     "gemm_w8a16": (4096, 8192, 8192),
+    # Implicit-GEMM convolution through index mappings, fp32: images [N, C, H, W],
+    # filters [NF, C, HF, WF], stride (a ResNet-style 3x3 layer; not one of the
+    # five benchmark configurations, measured as the next kernel family).
+    "conv": (32, 64, 56, 56, 64, 3, 3, 1),
 }
+# Tile sizes (TN images x TNF filters per work-group, K block) the conv is run with.
+CONV_TILES = (32, 64, 16)
 
 # Reduced shapes for profiler captures (--small): the streaming kernels still
 # move more than the 126 MB L2 holds, but a launch lasts tens of microseconds.
@@ -54,9 +60,15 @@ SMALL_SHAPES = {
     "gemm_f32": (256, 256, 256),
     "gemm_bf16": (2048, 2048, 2048),
     "gemm_w8a16": (1024, 2048, 2048),
+    "conv": (8, 64, 56, 56, 64, 3, 3, 1),
 }
 
+# fp32 FMA rate of the CUDA cores, nominal (no measured figure exists for it):
+# 148 SMs x 128 lanes x 2 flop x 1.965 GHz.
+FP32_NOMINAL_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
+
 METRIC = {
+    "conv": "conv_implicit_gemm_f32_throughput",
     "softmax": "softmax_rows_f32_algorithmic_bandwidth",
     "reduce": "reduce_rows_f32_algorithmic_bandwidth",
     "gemm_f32": "gemm_f32_tiled_throughput",
@@ -64,12 +76,24 @@ METRIC = {
     "gemm_w8a16": "gemm_w8a16_throughput",
 }
 DTYPE = {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32", "gemm_bf16": "bf16",
-         "gemm_w8a16": "bf16"}
+         "gemm_w8a16": "bf16", "conv": "f32"}
+
+
+def conv_shapes(s):
+    """x, f and out shapes of the conv workload tuple."""
+    n, c, h, w, nf, hf, wf, stride = s
+    return ((n, c, h, w), (nf, c, hf, wf),
+            (n, nf, (h - hf) // stride + 1, (w - wf) // stride + 1))
 
 
 def algorithmic(name):
     """(bytes, flops, bound) one launch of the workload must move / compute."""
     s = SHAPES[name]
+    if name == "conv":
+        xs, fs, os_ = conv_shapes(s)
+        size = lambda shape: shape[0] * shape[1] * shape[2] * shape[3]  # noqa: E731
+        return ((size(xs) + size(fs) + size(os_)) * 4,
+                2 * size(os_) * fs[1] * fs[2] * fs[3], "fp32")
     if name == "softmax":
         m, n = s
         return 2 * m * n * 4, 0, "hbm"
@@ -109,6 +133,7 @@ NCU_TRAFFIC = {
     "gemm_bf16": None,
     "gemm_w8a16": None,
     "gemm_f32": None,
+    "conv": None,
 }
 
 
@@ -238,6 +263,17 @@ def cpu_sample(name, threads, repeats):
 
         def one_pass():
             oracle.gemm_bf16(a, b, out, (256, 256))
+    elif name == "conv":
+        xs, fs, os_ = conv_shapes(s)
+        images = min(xs[0], 4)
+        x, f = oracle.make_conv_inputs((images,) + xs[1:], fs, "float32")
+        out = np.zeros((images,) + os_[1:], np.float32)
+        scale = images / xs[0]
+        tn, tnf, kb = min(CONV_TILES[0], images), CONV_TILES[1], CONV_TILES[2]
+        what = f"{images} of {xs[0]} images, groups of {tn} images x {tnf} filters, KB={kb}"
+
+        def one_pass():
+            oracle.conv_implicit_gemm(x, f, out, s[7], tn, tnf, kb)
     else:
         rows = min(s[0], 256)
         a, w, sc = oracle.make_inputs("gemm_w8a16", shape=(rows, s[1], s[2]))
@@ -341,6 +377,11 @@ def run_gpu(args):
         if name == "reduce":
             x = torch.rand(*s, device=dev, generator=g) * 20 - 10
             return [x], [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
+        if name == "conv":
+            xs, fs, os_ = conv_shapes(s)
+            x = torch.randn(*xs, device=dev, generator=g)
+            f = torch.randn(*fs, device=dev, generator=g)
+            return [x, f], [torch.zeros(*os_, device=dev)]
         m, n, k = s
         if name == "gemm_f32":
             a = torch.rand(m, k, device=dev, generator=g) * 2 - 1
@@ -355,6 +396,18 @@ def run_gpu(args):
         sc = torch.rand(n, device=dev, generator=g) * 0.019 + 0.001
         return [a, w, sc], [torch.empty(m, n, device=dev, dtype=torch.bfloat16)]
 
+    conv_cache = []
+
+    def conv_kernel():
+        if not conv_cache:
+            from hc_b200.hckernel.kernel import sym
+            from hc_b200.workloads import make_conv
+
+            tn, tnf, kb = CONV_TILES
+            conv_cache.append(make_conv(SHAPES["conv"][7], desc).parametrize(
+                {sym.TN: tn, sym.TNF: tnf, sym.KB: kb}))
+        return conv_cache[0]
+
     def direct_call(name, ins, outs):
         """The C++ dispatcher entry of the workload (no Python front door)."""
         if name == "softmax":
@@ -363,6 +416,12 @@ def run_gpu(args):
             return lambda: native.reduce_rows(ctx, ins[0], outs[0], outs[1])
         if name in ("gemm_f32", "gemm_bf16"):
             return lambda: native.gemm(ctx, ins[0], ins[1], outs[0])
+        if name == "conv":
+            # The index tables belong to the launch plan; made once, outside the timing.
+            spec = conv_kernel().plan_for((ins[0], ins[1], outs[0])).roles["spec"]
+            tx, tf, to = spec.device_tables((ins[0], ins[1], outs[0]))
+            return lambda: native.mapped_gemm(ctx, ins[0], tx, ins[1], tf, outs[0], to,
+                                              spec.groups, spec.tm, spec.tn, spec.k)
         n, k = ins[1].shape[1], ins[1].shape[0]
         ws = torch.empty(native.w8a16_workspace_bytes(n, k), dtype=torch.uint8, device=dev)
         return lambda: native.gemm_w8a16(ctx, ins[0], ins[1], ins[2], outs[0], ws)
@@ -377,6 +436,8 @@ def run_gpu(args):
             return lambda: kernels.dot(ins[0], ins[1], outs[0], (64, 64))
         if name == "gemm_bf16":
             return lambda: kernels.dot_fullk(ins[0], ins[1], outs[0], (256, 256))
+        if name == "conv":
+            return lambda: conv_kernel()(ins[0], ins[1], outs[0])
         return lambda: kernels.dequant_dot(ins[0], ins[1], ins[2], outs[0], (256, 256))
 
     def roofline(name, per_step_ms):
@@ -387,6 +448,10 @@ def run_gpu(args):
                          "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name],
                          "peak_source": peaks["source"]}
         ach = flops / per_step_ms / 1e9
+        if bound == "fp32":
+            return ach, {"bound": "fp32 CUDA cores", "achieved": ach, "peak": FP32_NOMINAL_TFLOPS,
+                         "unit": "TFLOP/s", "frac": ach / FP32_NOMINAL_TFLOPS,
+                         "traffic": NCU_TRAFFIC[name], "peak_source": "nominal"}
         return ach, {"bound": "tensor" if bound == "tensor" else "latency", "achieved": ach,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": ach / peaks["bf16_tflops"],
@@ -452,7 +517,7 @@ def run_gpu(args):
         extras = {}
         if name == "softmax" and not args.no_extras:
             for other, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
-                                 ("gemm_f32", 500)):
+                                 ("gemm_f32", 500), ("conv", 50)):
                 # Each kernel is timed alone: let the board's power state settle
                 # after the previous one (a dense GEMM runs into the 1 kW cap and
                 # would hand lower clocks to whatever is measured right after it).
@@ -467,8 +532,10 @@ def run_gpu(args):
             "dtype": DTYPE[name], "data": "synthetic",
             "config": {"workload": describe(name),
                        "sharding": "independent shards, no collective in the timed path",
-                       "l2": "inputs and outputs larger than L2 (no flush needed)"
-                       if name != "gemm_f32" else "operands fit in L2 (latency-bound case)"},
+                       "l2": {"gemm_f32": "operands fit in L2 (latency-bound case)",
+                              "conv": "operands (50 MB) fit in L2; the kernel is bound by the "
+                                      "CUDA cores, not by memory"}.get(
+                                  name, "inputs and outputs larger than L2 (no flush needed)")},
             "roofline": head["roofline"], "gpu_launches": head["launches"],
             "kernel_status": head["status"], "clocks": sampler.summary(), "e2e": e2e,
         }

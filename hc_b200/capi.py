@@ -46,6 +46,8 @@ class HcMappedOperand(C.Structure):
         ("stride", _ll * 4),
         ("lo", C.c_int * 4),
         ("hi", C.c_int * 4),
+        ("transposed", C.c_int),
+        ("reserved", C.c_int),
     ]
 
 

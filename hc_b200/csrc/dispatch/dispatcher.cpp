@@ -200,7 +200,8 @@ void pairwiseDistance(Context &ctx, py::handle a, py::handle b, py::handle out) 
 
 // One operand of the gathered tile product: the array (any rank up to 4, any
 // non-negative strides) and its tables (map int32 [E,4], lin int32 [E],
-// origins int32 [G,4], lo and hi as 4 ints each).
+// origins int32 [G,4], lo and hi as 4 ints each, whether map/lin are in
+// transposed tile order).
 HcMappedOperand mappedOperand(const Context &ctx, py::handle array, py::handle tables,
                               const char *name, long long elems, long long groups,
                               ElemKind *kind) {
@@ -230,8 +231,10 @@ HcMappedOperand mappedOperand(const Context &ctx, py::handle array, py::handle t
     op.stride[d] = a.strides[d];
   }
   auto t = py::cast<py::tuple>(tables);
-  if (t.size() != 5)
-    throw py::value_error(std::string(name) + ": tables must be (map, lin, origins, lo, hi)");
+  if (t.size() != 6)
+    throw py::value_error(std::string(name) +
+                          ": tables must be (map, lin, origins, lo, hi, transposed)");
+  op.transposed = py::cast<bool>(t[5]) ? 1 : 0;
   const std::string nm(name);
   ArrayArg map = deviceArray(ctx, t[0], (nm + " map").c_str(), 2);
   ArrayArg lin = deviceArray(ctx, t[1], (nm + " lin").c_str(), 1);

@@ -22,9 +22,17 @@
 // linear offsets; an edge group also reads the 16-byte index and compares it
 // with what is left of the array from its origin.
 //
-// 256 threads as 16 x 16, each owning an MT x MT block of the result with a
+// Gathers are only as fast as they are coalesced, and which neighbours in a
+// tile are neighbours in memory depends on the mapping (the filter tile of the
+// convolution is contiguous along K, not along its columns).  So each operand
+// table comes in the order the host found best (row-major or transposed) and
+// consecutive threads take consecutive table entries.
+//
+// 256 threads as 16 x 16, each owning an MY x MX block of the result with a
 // stride of 16 between its rows and columns; the operands pass through shared
-// memory in K chunks of 16.  Tiles larger than 16*MT are walked in pieces.
+// memory in K chunks of 16, the next chunk being fetched into registers while
+// the current one is multiplied.  Tiles larger than 16*MY x 16*MX are walked
+// in pieces.
 #include "mapped_params.h"
 
 #include <stdint.h>
@@ -69,14 +77,26 @@ template <typename T>
 __device__ __forceinline__ T fetch(const HcMappedOperandDev &op, const GroupView &v, int idx) {
   if (!inside(op, v, idx))
     return T(0);
-  return static_cast<const T *>(op.base)[v.base + op.lin[idx]];
+  return __ldg(static_cast<const T *>(op.base) + v.base + __ldg(op.lin + idx));
 }
 
-template <typename T, int MT>
+// Element `e` of a [rows x KC] chunk in table order: k fastest when the table
+// has k as its fastest index, the row (or column) of the tile otherwise.
+__device__ __forceinline__ void chunkElement(int e, int span, bool kFastest, int &r, int &kk) {
+  if (kFastest) {
+    kk = e % KC;
+    r = e / KC;
+  } else {
+    r = e % span;
+    kk = e / span;
+  }
+}
+
+template <typename T, int MY, int MX>
 __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
-  constexpr int S = 16 * MT;
-  __shared__ T sA[KC][S + 1]; // [k][row]
-  __shared__ T sB[KC][S + 1]; // [k][column]
+  constexpr int SY = 16 * MY, SX = 16 * MX;
+  __shared__ T sA[KC][SY + 1]; // [k][row]
+  __shared__ T sB[KC][SX + 1]; // [k][column]
   __shared__ GroupView views[3];
 
   const int tid = threadIdx.x;
@@ -86,55 +106,86 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
   __syncthreads();
   const int ty = tid >> 4, tx = tid & 15;
   const int TM = p.TM, TN = p.TN, K = p.K;
+  // x natural order is [a][k] (k fastest); f natural order is [k][b].
+  const bool xKFast = !p.x.transposed, fKFast = p.f.transposed != 0;
 
-  for (int m0 = 0; m0 < TM; m0 += S)
-    for (int n0 = 0; n0 < TN; n0 += S) {
-      T acc[MT][MT];
+  for (int m0 = 0; m0 < TM; m0 += SY)
+    for (int n0 = 0; n0 < TN; n0 += SX) {
+      T acc[MY][MX];
 #pragma unroll
-      for (int i = 0; i < MT; ++i)
+      for (int i = 0; i < MY; ++i)
 #pragma unroll
-        for (int j = 0; j < MT; ++j)
+        for (int j = 0; j < MX; ++j)
           acc[i][j] = T(0);
 
-      for (int k0 = 0; k0 < K; k0 += KC) {
-        // A: consecutive threads take consecutive k of one row (the table and,
-        // for patch gathers, the data are contiguous that way).
-        for (int e = tid; e < S * KC; e += THREADS) {
-          const int kk = e % KC, aa = e / KC;
+      T ra[MY], rb[MX]; // this thread's share of the chunk in flight
+      auto fetchChunk = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < MY; ++i) {
+          int aa, kk;
+          chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
           const int a = m0 + aa, k = k0 + kk;
-          sA[kk][aa] = (a < TM && k < K) ? fetch<T>(p.x, views[0], a * K + k) : T(0);
+          ra[i] = (a < TM && k < K)
+                      ? fetch<T>(p.x, views[0], xKFast ? a * K + k : k * TM + a)
+                      : T(0);
         }
-        // B: consecutive threads take consecutive columns of one k.
-        for (int e = tid; e < S * KC; e += THREADS) {
-          const int bb = e % S, kk = e / S;
+#pragma unroll
+        for (int j = 0; j < MX; ++j) {
+          int bb, kk;
+          chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
           const int b = n0 + bb, k = k0 + kk;
-          sB[kk][bb] = (b < TN && k < K) ? fetch<T>(p.f, views[1], k * TN + b) : T(0);
+          rb[j] = (b < TN && k < K)
+                      ? fetch<T>(p.f, views[1], fKFast ? b * K + k : k * TN + b)
+                      : T(0);
         }
+      };
+      auto stageChunk = [&]() {
+#pragma unroll
+        for (int i = 0; i < MY; ++i) {
+          int aa, kk;
+          chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
+          sA[kk][aa] = ra[i];
+        }
+#pragma unroll
+        for (int j = 0; j < MX; ++j) {
+          int bb, kk;
+          chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
+          sB[kk][bb] = rb[j];
+        }
+      };
+
+      if (K > 0)
+        fetchChunk(0);
+      for (int k0 = 0; k0 < K; k0 += KC) {
+        stageChunk();
         __syncthreads();
+        if (k0 + KC < K)
+          fetchChunk(k0 + KC);
 #pragma unroll
         for (int kk = 0; kk < KC; ++kk) {
-          T av[MT], bv[MT];
+          T av[MY], bv[MX];
 #pragma unroll
-          for (int i = 0; i < MT; ++i) {
+          for (int i = 0; i < MY; ++i)
             av[i] = sA[kk][ty + 16 * i];
-            bv[i] = sB[kk][tx + 16 * i];
-          }
 #pragma unroll
-          for (int i = 0; i < MT; ++i)
+          for (int j = 0; j < MX; ++j)
+            bv[j] = sB[kk][tx + 16 * j];
 #pragma unroll
-            for (int j = 0; j < MT; ++j)
+          for (int i = 0; i < MY; ++i)
+#pragma unroll
+            for (int j = 0; j < MX; ++j)
               acc[i][j] += av[i] * bv[j];
         }
         __syncthreads();
       }
 
 #pragma unroll
-      for (int i = 0; i < MT; ++i) {
+      for (int i = 0; i < MY; ++i) {
         const int a = m0 + ty + 16 * i;
         if (a >= TM)
           continue;
 #pragma unroll
-        for (int j = 0; j < MT; ++j) {
+        for (int j = 0; j < MX; ++j) {
           const int b = n0 + tx + 16 * j;
           if (b >= TN)
             continue;
@@ -148,15 +199,21 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 } // namespace
 
-#define HC_MAPPED_KERNEL(name, T, MT)                                                   \
+#define HC_MAPPED_KERNEL(T, tname, MY, MX)                                              \
   extern "C" __global__ void __launch_bounds__(THREADS)                                 \
-      name(const __grid_constant__ HcMappedGemmParams p) {                              \
-    mappedGemm<T, MT>(p);                                                               \
+      hc_mapped_gemm_##tname##_m##MY##n##MX(const __grid_constant__ HcMappedGemmParams p) { \
+    mappedGemm<T, MY, MX>(p);                                                           \
   }
+#define HC_MAPPED_KERNELS(T, tname)                                                     \
+  HC_MAPPED_KERNEL(T, tname, 1, 1)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 1, 2)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 1, 4)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 2, 1)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 2, 2)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 2, 4)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 4, 1)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 4, 2)                                                      \
+  HC_MAPPED_KERNEL(T, tname, 4, 4)
 
-HC_MAPPED_KERNEL(hc_mapped_gemm_f32_t1, float, 1)
-HC_MAPPED_KERNEL(hc_mapped_gemm_f32_t2, float, 2)
-HC_MAPPED_KERNEL(hc_mapped_gemm_f32_t4, float, 4)
-HC_MAPPED_KERNEL(hc_mapped_gemm_f64_t1, double, 1)
-HC_MAPPED_KERNEL(hc_mapped_gemm_f64_t2, double, 2)
-HC_MAPPED_KERNEL(hc_mapped_gemm_f64_t4, double, 4)
+HC_MAPPED_KERNELS(float, f32)
+HC_MAPPED_KERNELS(double, f64)

@@ -15,9 +15,15 @@ struct HcMappedOperandDev {
   int64_t stride[4]; // in elements
   int32_t lo[4];     // smallest relative index per dimension over the tile
   int32_t hi[4];     // largest relative index per dimension over the tile
+  // Order of the tile elements in `map` and `lin`: 0 = row-major of the tile as
+  // the kernel body declares it, 1 = transposed.  The kernel walks an operand
+  // in table order, so the host picks the order in which neighbouring elements
+  // are neighbours in memory.
+  int32_t transposed;
+  int32_t reserved;
 };
 
 struct HcMappedGemmParams {
-  HcMappedOperandDev x, f, out; // tiles [TM, K], [K, TN], [TM, TN], row-major
+  HcMappedOperandDev x, f, out; // tiles [TM, K], [K, TN], [TM, TN]
   int32_t TM, TN, K;
 };

@@ -73,12 +73,24 @@ const KernelEntry kKernelTable[] = {
     {"hc_selftest_wait_timeout", "selftest"},
     {"hc_pairwise_distance_f32", "pairwise_distance"},
     {"hc_pairwise_distance_f64", "pairwise_distance"},
-    {"hc_mapped_gemm_f32_t1", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_t2", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_t4", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_t1", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_t2", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_t4", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m1n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m1n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m1n4", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m2n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m2n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m2n4", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m4n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m4n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f32_m4n4", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m1n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m1n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m1n4", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m2n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m2n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m2n4", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m4n1", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m4n2", "mapped_gemm"},
+    {"hc_mapped_gemm_f64_m4n4", "mapped_gemm"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f32_async", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
@@ -544,7 +556,9 @@ static_assert(sizeof(HcMappedOperand) == sizeof(HcMappedOperandDev) &&
                   offsetof(HcMappedOperand, shape) == offsetof(HcMappedOperandDev, shape) &&
                   offsetof(HcMappedOperand, stride) == offsetof(HcMappedOperandDev, stride) &&
                   offsetof(HcMappedOperand, lo) == offsetof(HcMappedOperandDev, lo) &&
-                  offsetof(HcMappedOperand, hi) == offsetof(HcMappedOperandDev, hi),
+                  offsetof(HcMappedOperand, hi) == offsetof(HcMappedOperandDev, hi) &&
+                  offsetof(HcMappedOperand, transposed) ==
+                      offsetof(HcMappedOperandDev, transposed),
               "public operand description and kernel parameter block differ");
 
 int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f,
@@ -588,13 +602,14 @@ int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f
   p.TM = TM;
   p.TN = TN;
   p.K = K;
-  // Smallest 16*MT square that holds the tile, up to 64; larger tiles are
-  // walked in 64 x 64 pieces by the kernel.
-  const int side = std::max(TM, TN);
-  const char *variant = side <= 16 ? "t1" : side <= 32 ? "t2" : "t4";
+  if (out->transposed)
+    return c->fail("hcMappedGemm: the tables of out must be in row-major order");
+  // Smallest (16*MY) x (16*MX) piece that holds the tile, up to 64 x 64; larger
+  // tiles are walked in pieces by the kernel.
+  auto perThread = [](int extent) { return extent <= 16 ? 1 : extent <= 32 ? 2 : 4; };
   char name[48];
-  std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_%s", dtype == HC_F32 ? "f32" : "f64",
-                variant);
+  std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_m%dn%d", dtype == HC_F32 ? "f32" : "f64",
+                perThread(TM), perThread(TN));
   void *args[] = {&p};
   return c->launch(name, size_t(groups), 1, 1, 256, args, 1, 0);
 }

@@ -51,6 +51,15 @@ def _identity(*index):
     return index
 
 
+def _neighbour_distance(offsets, axis, sector):
+    """Mean distance in memory, capped at one 32-byte sector, between tile
+    elements adjacent along ``axis`` - how well a warp that walks the tile along
+    that axis coalesces."""
+    if offsets.shape[axis] < 2:
+        return float(sector)
+    return float(np.minimum(np.abs(np.diff(offsets, axis=axis)), sector).mean())
+
+
 def _source(tile, what):
     """(base tile, offsets) of a dot operand: a gathered or loaded tile, whole
     or seen through ``vload(tile[a:, b:], shape)``."""
@@ -222,8 +231,8 @@ class MappedSpec:
         return self._host
 
     def device_tables(self, tensors):
-        """(map, lin, origins, lo, hi) per operand, on the device of ``tensors``
-        (the x, f, out call arguments) and for their strides."""
+        """(map, lin, origins, lo, hi, transposed) per operand, on the device of
+        ``tensors`` (the x, f, out call arguments) and for their strides."""
         import torch
 
         key = (str(tensors[0].device),) + tuple(tuple(t.stride()) for t in tensors)
@@ -238,11 +247,24 @@ class MappedSpec:
                     raise UnsupportedKernel(f"{op.name}: tile offsets leave the 32-bit range")
                 lo = mp.min(axis=0) if mp.size else np.zeros(4, np.int64)
                 hi = mp.max(axis=0) if mp.size else np.zeros(4, np.int64)
+                # The kernel gives consecutive table entries to consecutive
+                # threads: store an operand tile transposed when its columns,
+                # not its rows, are what lies together in memory.
+                rows, cols = op.tile_shape
+                transposed = False
+                if role != "out" and mp.size:
+                    sector = max(1, 32 // t.element_size())
+                    grid = lin.reshape(rows, cols)
+                    transposed = (_neighbour_distance(grid, 0, sector)
+                                  < _neighbour_distance(grid, 1, sector))
+                if transposed:
+                    mp = mp.reshape(rows, cols, 4).transpose(1, 0, 2).reshape(-1, 4)
+                    lin = lin.reshape(rows, cols).T.reshape(-1)
 
                 def dev(a):
                     return torch.from_numpy(np.ascontiguousarray(a.astype(np.int32))).to(t.device)
 
                 tables.append((dev(mp), dev(lin), dev(org), [int(v) for v in lo],
-                               [int(v) for v in hi]))
+                               [int(v) for v in hi], bool(transposed)))
             self._device[key] = tables
         return tables

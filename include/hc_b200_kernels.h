@@ -133,11 +133,15 @@ HC_B200_API int hcPairwiseDistance(HcContext c, const void *a, const void *b,
  *   map      int32 [tile elements][4]  mapped index relative to the tile origin
  *   lin      int32 [tile elements]     sum_d map[d] * stride[d]
  *   origins  int32 [groups][4]         tile origin of every work-group (>= 0)
- * with tile elements in row-major order of the tile ([TM,K], [K,TN], [TM,TN]);
+ * with tile elements in row-major order of the tile ([TM,K], [K,TN], [TM,TN])
+ * or, for x and f, transposed ([K,TM], [TN,K]) when `transposed` is set: the
+ * kernel hands consecutive table entries to consecutive threads, so the caller
+ * picks the order in which neighbouring entries are neighbours in memory.
  * `map` and `origins` must be 16-byte aligned.  Arrays of rank below 4 are
  * padded with shape 1, stride 0 and zeros in the tables.  lo/hi are the
  * smallest/largest value of each column of `map`.  Distinct (group, element)
- * pairs must not map to the same element of `out`.  HC_F32 or HC_F64. */
+ * pairs must not map to the same element of `out`, and `out` must not overlap
+ * x or f.  HC_F32 or HC_F64. */
 typedef struct HcMappedOperand {
   void *base;           /* device: element [0,0,0,0] of the array */
   const int *map;       /* device */
@@ -147,6 +151,8 @@ typedef struct HcMappedOperand {
   long long stride[4];  /* in elements */
   int lo[4];
   int hi[4];
+  int transposed;       /* order of map/lin; must be 0 for out */
+  int reserved;         /* 0 */
 } HcMappedOperand;
 HC_B200_API int hcMappedGemm(HcContext c, const HcMappedOperand *x,
                              const HcMappedOperand *f, const HcMappedOperand *out,

@@ -138,6 +138,25 @@ def test_mapped_gemm_through_the_c_abi(hc):
     expect[1:] = (x.T @ f)[: m - 1]
     np.testing.assert_allclose(d_out.cpu().numpy(), expect, rtol=1e-12, atol=1e-12)
 
+    # The same product with the operand tables in transposed tile order.
+    d_out.fill_(-1.0)
+    flipped = []
+    for arr, (mp, org), (rows, cols) in ((d_x, (x_map, x_org), (tm, k)),
+                                        (d_f, (f_map, f_org), (k, n + 2))):
+        stride = np.array([arr.stride(d) if d < arr.dim() else 0 for d in range(4)])
+        mp_t = mp.reshape(rows, cols, 4).transpose(1, 0, 2).reshape(-1, 4)
+        flipped.append((i32(mp_t), i32(mp_t @ stride), i32(org)))
+    ops_t = [_operand(arr, *t) for arr, t in zip((d_x, d_f), flipped)]
+    for op in ops_t:
+        op.transposed = 1
+    hc.mapped_gemm(ops_t[0], ops_t[1], ops[2], groups, tm, n + 2, k, capi.HC_F64)
+    finish(hc)
+    np.testing.assert_allclose(d_out.cpu().numpy(), expect, rtol=1e-12, atol=1e-12)
+    ops[2].transposed = 1
+    with pytest.raises(RuntimeError, match="row-major"):
+        hc.mapped_gemm(ops[0], ops[1], ops[2], groups, tm, n + 2, k, capi.HC_F64)
+    ops[2].transposed = 0
+
     # Argument errors come back as error codes with a message, not as faults.
     with pytest.raises(RuntimeError, match="unsupported dtype"):
         hc.mapped_gemm(ops[0], ops[1], ops[2], groups, tm, n + 2, k, capi.HC_BF16)
@@ -146,4 +165,4 @@ def test_mapped_gemm_through_the_c_abi(hc):
     with pytest.raises(RuntimeError, match="not 16-byte aligned"):
         hc.mapped_gemm(ops[0], ops[1], bad, groups, tm, n + 2, k, capi.HC_F64)
     hc.mapped_gemm(ops[0], ops[1], ops[2], 0, tm, n + 2, k, capi.HC_F64)  # no groups: no-op
-    assert ctypes.sizeof(capi.HcMappedOperand) == 112
+    assert ctypes.sizeof(capi.HcMappedOperand) == 120

@@ -82,6 +82,27 @@ def test_fractional_output_extent_truncates_like_the_reference():
     assert out_origins.tolist() == [[0, 0, 0, 0], [0, 0, 1, 0]]
 
 
+def test_table_order_follows_memory_order():
+    """Consecutive threads take consecutive table entries, so an operand tile is
+    stored transposed when its columns are what lies together in memory: the
+    filter tile [K, TNF] of the convolution is contiguous along K."""
+    import torch
+
+    x, f, out = torch.zeros(4, 3, 8, 8), torch.zeros(16, 3, 3, 3), torch.zeros(4, 16, 6, 6)
+    spec = make_conv(1).plan_for((x, f, out)).roles["spec"]
+    tx, tf, to = spec.device_tables((x, f, out))
+    assert (tx[5], tf[5], to[5]) == (False, True, False)
+    natural_map, _ = spec.host_tables()["f"]
+    k, tnf = spec.k, spec.tn
+    assert np.array_equal(tf[0].numpy().reshape(tnf, k, 4),
+                          natural_map.reshape(k, tnf, 4).transpose(1, 0, 2))
+    # lin = map . strides, in the same order as map.
+    stride = np.array(f.stride())
+    assert np.array_equal(tf[1].numpy(), tf[0].numpy() @ stride)
+    assert tf[3] == [0, 0, 0, 0] and tf[4] == [tnf - 1, 2, 2, 2]
+    assert spec.device_tables((x, f, out)) is spec.device_tables((x, f, out))  # cached
+
+
 def test_index_expressions():
     g = tuple(Affine(0, {d: 1}) for d in range(3))
     gids = np.indices((2, 3, 4)).reshape(3, -1)
