@@ -60,7 +60,7 @@ SMALL_SHAPES = {
     "gemm_f32": (256, 256, 256),
     "gemm_bf16": (2048, 2048, 2048),
     "gemm_w8a16": (1024, 2048, 2048),
-    "conv": (8, 64, 56, 56, 64, 3, 3, 1),
+    "conv": (32, 64, 30, 30, 64, 3, 3, 1),
 }
 
 # fp32 FMA rate of the CUDA cores, nominal (no measured figure exists for it):

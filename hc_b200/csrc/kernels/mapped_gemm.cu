@@ -28,11 +28,13 @@
 // table comes in the order the host found best (row-major or transposed) and
 // consecutive threads take consecutive table entries.
 //
-// 256 threads as 16 x 16, each owning an MY x MX block of the result with a
-// stride of 16 between its rows and columns; the operands pass through shared
-// memory in K chunks of 16, the next chunk being fetched into registers while
-// the current one is multiplied.  Tiles larger than 16*MY x 16*MX are walked
-// in pieces.
+// 256 threads as 16 x 16, each owning MY adjacent rows and MX adjacent columns
+// of the result, so that one 8- or 16-byte shared-memory load brings all of a
+// thread's rows (columns) for one k.  The operands pass through shared memory
+// in K chunks of 16 ([k][row] and [k][column], 4-element groups XOR-swizzled
+// with k so that a warp that stages 16 consecutive k of two rows spreads over
+// the banks); the next chunk is fetched into registers while the current one
+// is multiplied.  Tiles larger than 16*MY x 16*MX are walked in pieces.
 #include "mapped_params.h"
 
 #include <stdint.h>
@@ -92,11 +94,34 @@ __device__ __forceinline__ void chunkElement(int e, int span, bool kFastest, int
   }
 }
 
+// Position of element `c` in row `kk` of a staged chunk: groups of four
+// elements are XOR-ed with k.  Aligned runs of 1, 2 or 4 elements stay whole.
+template <int SPAN>
+__device__ __forceinline__ int swizzled(int kk, int c) {
+  constexpr int groups = SPAN / 4; // 4, 8 or 16 groups per row
+  return c ^ ((kk & (groups < 8 ? groups - 1 : 7)) << 2);
+}
+
+// N adjacent elements from shared memory with the widest loads that fit.
+template <typename T, int N>
+__device__ __forceinline__ void loadRun(const T *src, T (&dst)[N]) {
+  constexpr int bytes = N * int(sizeof(T));
+  if constexpr (bytes % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < bytes / 16; ++i)
+      reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+  } else if constexpr (bytes == 8) {
+    *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(src);
+  } else {
+    dst[0] = src[0];
+  }
+}
+
 template <typename T, int MY, int MX>
 __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
   constexpr int SY = 16 * MY, SX = 16 * MX;
-  __shared__ T sA[KC][SY + 1]; // [k][row]
-  __shared__ T sB[KC][SX + 1]; // [k][column]
+  __shared__ __align__(16) T sA[KC][SY]; // [k][row], swizzled
+  __shared__ __align__(16) T sB[KC][SX]; // [k][column], swizzled
   __shared__ GroupView views[3];
 
   const int tid = threadIdx.x;
@@ -144,13 +169,13 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
         for (int i = 0; i < MY; ++i) {
           int aa, kk;
           chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
-          sA[kk][aa] = ra[i];
+          sA[kk][swizzled<SY>(kk, aa)] = ra[i];
         }
 #pragma unroll
         for (int j = 0; j < MX; ++j) {
           int bb, kk;
           chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
-          sB[kk][bb] = rb[j];
+          sB[kk][swizzled<SX>(kk, bb)] = rb[j];
         }
       };
 
@@ -163,13 +188,10 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
           fetchChunk(k0 + KC);
 #pragma unroll
         for (int kk = 0; kk < KC; ++kk) {
-          T av[MY], bv[MX];
-#pragma unroll
-          for (int i = 0; i < MY; ++i)
-            av[i] = sA[kk][ty + 16 * i];
-#pragma unroll
-          for (int j = 0; j < MX; ++j)
-            bv[j] = sB[kk][tx + 16 * j];
+          alignas(16) T av[MY];
+          alignas(16) T bv[MX];
+          loadRun<T, MY>(&sA[kk][swizzled<SY>(kk, ty * MY)], av);
+          loadRun<T, MX>(&sB[kk][swizzled<SX>(kk, tx * MX)], bv);
 #pragma unroll
           for (int i = 0; i < MY; ++i)
 #pragma unroll
@@ -181,12 +203,12 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 #pragma unroll
       for (int i = 0; i < MY; ++i) {
-        const int a = m0 + ty + 16 * i;
+        const int a = m0 + ty * MY + i;
         if (a >= TM)
           continue;
 #pragma unroll
         for (int j = 0; j < MX; ++j) {
-          const int b = n0 + tx + 16 * j;
+          const int b = n0 + tx * MX + j;
           if (b >= TN)
             continue;
           const int idx = a * TN + b;
@@ -199,8 +221,12 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 } // namespace
 
+// Gathers hide their latency behind other CTAs: cap the registers so that four
+// CTAs fit on an SM (three or two where the accumulators alone take 64 or 128
+// bytes per thread).
 #define HC_MAPPED_KERNEL(T, tname, MY, MX)                                              \
-  extern "C" __global__ void __launch_bounds__(THREADS)                                 \
+  extern "C" __global__ void __launch_bounds__(                                         \
+      THREADS, MY * MX * sizeof(T) >= 128 ? 2 : MY * MX * sizeof(T) >= 64 ? 3 : 4)      \
       hc_mapped_gemm_##tname##_m##MY##n##MX(const __grid_constant__ HcMappedGemmParams p) { \
     mappedGemm<T, MY, MX>(p);                                                           \
   }
