@@ -28,20 +28,31 @@
 // table comes in the order the host found best (row-major or transposed) and
 // consecutive threads take consecutive table entries.
 //
-// 256 threads as 16 x 16, each owning MY adjacent rows and MX adjacent columns
-// of the result, so that one 8- or 16-byte shared-memory load brings all of a
-// thread's rows (columns) for one k.  The operands pass through shared memory
-// in K chunks of 16 ([k][row] and [k][column], 4-element groups XOR-swizzled
-// with k so that a warp that stages 16 consecutive k of two rows spreads over
-// the banks); the next chunk is fetched into registers while the current one
-// is multiplied.  Tiles larger than 16*MY x 16*MX are walked in pieces.
+// A gather is two dependent loads (offset, then element), both usually served
+// by L2.  To keep that latency off the multiply loop the operands travel as
+// 4- or 8-byte cp.async copies straight into a three-stage ring of K chunks
+// in shared memory (a copy with source size 0 writes the zero of an element
+// outside its array), and the offsets a chunk needs are loaded into registers
+// one chunk before its copies are issued.
+//
+// TY x TX threads (8 or 16 each way), each owning MY adjacent rows and MX
+// adjacent columns of the result (1, 2 or 4), so that one 8- or 16-byte
+// shared-memory load brings all of a thread's rows (columns) for one k.  A
+// chunk is [k][row] and [k][column] with 4-element groups XOR-swizzled with k,
+// so that the copies of a warp spread over the banks.  Tiles larger than
+// TY*MY x TX*MX are walked in pieces.
+//
+// What bounds it: every work-group gathers both of its operand tiles and
+// their offset tables again, so for tiles of a few thousand elements the
+// traffic from L2 into the SMs, not the FMA pipe, sets the pace (measured on
+// a 32 x 64 x 576 tile: about 0.8 MB per group for 2.4 MFLOP).
 #include "mapped_params.h"
 
 #include <stdint.h>
 
 namespace {
 
-constexpr int KC = 16, THREADS = 256;
+constexpr int KC = 16;
 
 struct GroupView {
   long long base; // linear offset of the tile origin
@@ -75,15 +86,9 @@ __device__ __forceinline__ bool inside(const HcMappedOperandDev &op, const Group
          r.z < v.lim[2] && r.w >= 0 && r.w < v.lim[3];
 }
 
-template <typename T>
-__device__ __forceinline__ T fetch(const HcMappedOperandDev &op, const GroupView &v, int idx) {
-  if (!inside(op, v, idx))
-    return T(0);
-  return __ldg(static_cast<const T *>(op.base) + v.base + __ldg(op.lin + idx));
-}
-
-// Element `e` of a [rows x KC] chunk in table order: k fastest when the table
-// has k as its fastest index, the row (or column) of the tile otherwise.
+// Which element of a [rows x KC] chunk thread-slot `e` carries: in table
+// order, so a warp takes all 16 k of two adjacent rows where the table has k
+// as its fastest index, and 32 adjacent rows of one k otherwise.
 __device__ __forceinline__ void chunkElement(int e, int span, bool kFastest, int &r, int &kk) {
   if (kFastest) {
     kk = e % KC;
@@ -94,34 +99,94 @@ __device__ __forceinline__ void chunkElement(int e, int span, bool kFastest, int
   }
 }
 
-// Position of element `c` in row `kk` of a staged chunk: groups of four
-// elements are XOR-ed with k.  Aligned runs of 1, 2 or 4 elements stay whole.
+// Position of element `c` in row `kk` of a staged chunk.  The group of four
+// that `c` is in is XOR-ed with k (8 phases), and the two pairs inside a group
+// change places for k >= 8, so that the 32 copies of a warp (16 k of two
+// adjacent elements) land in 32 different banks.  Aligned runs of one or two
+// elements stay whole; a run of four comes back with its halves exchanged for
+// k >= 8 (loadRun puts them right).
 template <int SPAN>
 __device__ __forceinline__ int swizzled(int kk, int c) {
-  constexpr int groups = SPAN / 4; // 4, 8 or 16 groups per row
-  return c ^ ((kk & (groups < 8 ? groups - 1 : 7)) << 2);
+  constexpr int groups = SPAN / 4; // 2, 4, 8 or 16 groups per row
+  return c ^ (((kk & (groups < 8 ? groups - 1 : 7)) << 2) | (((kk >> 3) & 1) << 1));
 }
 
-// N adjacent elements from shared memory with the widest loads that fit.
-template <typename T, int N>
-__device__ __forceinline__ void loadRun(const T *src, T (&dst)[N]) {
+// The N adjacent elements that start at (unswizzled) position `c` of row `kk`.
+template <typename T, int N, int SPAN>
+__device__ __forceinline__ void loadRun(const T (&row)[SPAN], int kk, int c, T (&dst)[N]) {
   constexpr int bytes = N * int(sizeof(T));
-  if constexpr (bytes % 16 == 0) {
+  if constexpr (N == 4) {
+    const T *src = &row[swizzled<SPAN>(kk, c) & ~3];
+    alignas(16) T raw[4];
 #pragma unroll
     for (int i = 0; i < bytes / 16; ++i)
-      reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+      reinterpret_cast<uint4 *>(raw)[i] = reinterpret_cast<const uint4 *>(src)[i];
+    const bool exchanged = (kk & 8) != 0;
+    dst[0] = exchanged ? raw[2] : raw[0];
+    dst[1] = exchanged ? raw[3] : raw[1];
+    dst[2] = exchanged ? raw[0] : raw[2];
+    dst[3] = exchanged ? raw[1] : raw[3];
+  } else if constexpr (bytes == 16) {
+    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&row[swizzled<SPAN>(kk, c)]);
   } else if constexpr (bytes == 8) {
-    *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(src);
+    *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(&row[swizzled<SPAN>(kk, c)]);
   } else {
-    dst[0] = src[0];
+    dst[0] = row[swizzled<SPAN>(kk, c)];
   }
 }
 
-template <typename T, int MY, int MX>
+// One element, global -> shared, asynchronously; `valid` false writes zero and
+// reads nothing.
+template <typename T>
+__device__ __forceinline__ void copyAsync(T *dstShared, const T *src, bool valid) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(dstShared));
+  const int bytes = valid ? int(sizeof(T)) : 0;
+  if constexpr (sizeof(T) == 4)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                 : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void commitCopies() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void waitCopies() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// How one side of the CTA's piece of the tile is split: `SPAN` rows (columns)
+// as `threads` threads with `each` adjacent rows (columns) apiece.
+template <int SPAN>
+struct Side {
+  static constexpr int threads = SPAN >= 32 ? 16 : 8;
+  static constexpr int each = SPAN / threads; // 1, 2, 2, 4 for 8, 16, 32, 64
+};
+
+template <int SY, int SX>
+__host__ __device__ constexpr int threadsOf() {
+  return Side<SY>::threads * Side<SX>::threads;
+}
+
+// CTAs per SM the register allocation should leave room for (occupancy is what
+// hides the gathers): 40 registers of addressing, the copy offsets and one and
+// a half times the accumulators per thread.
+template <typename T, int SY, int SX>
+__host__ __device__ constexpr int residentCtas() {
+  constexpr int MY = Side<SY>::each, MX = Side<SX>::each, NT = threadsOf<SY, SX>();
+  constexpr int regs = 40 + MY * MX * int(sizeof(T) / 4) * 3 / 2 + (SY + SX) * KC / NT;
+  constexpr int fit = 65536 / (NT * regs);
+  return fit < 1 ? 1 : fit > 8 ? 8 : fit;
+}
+
+template <typename T, int SY, int SX>
 __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
-  constexpr int SY = 16 * MY, SX = 16 * MX;
-  __shared__ __align__(16) T sA[KC][SY]; // [k][row], swizzled
-  __shared__ __align__(16) T sB[KC][SX]; // [k][column], swizzled
+  constexpr int MY = Side<SY>::each, MX = Side<SX>::each;
+  constexpr int TX = Side<SX>::threads, THREADS = threadsOf<SY, SX>();
+  constexpr int NA = SY * KC / THREADS, NB = SX * KC / THREADS; // copies per thread and chunk
+  // Three stages, two where three would pass the 48 KB of static shared memory.
+  constexpr int STAGES = 3 * KC * (SY + SX) * int(sizeof(T)) > 47 * 1024 ? 2 : 3;
+  __shared__ __align__(16) T sA[STAGES][KC][SY]; // [stage][k][row], swizzled
+  __shared__ __align__(16) T sB[STAGES][KC][SX]; // [stage][k][column], swizzled
   __shared__ GroupView views[3];
 
   const int tid = threadIdx.x;
@@ -129,10 +194,13 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
   if (tid < 3)
     openView(tid == 0 ? p.x : tid == 1 ? p.f : p.out, g, views[tid]);
   __syncthreads();
-  const int ty = tid >> 4, tx = tid & 15;
+  const int ty = tid / TX, tx = tid % TX;
   const int TM = p.TM, TN = p.TN, K = p.K;
   // x natural order is [a][k] (k fastest); f natural order is [k][b].
   const bool xKFast = !p.x.transposed, fKFast = p.f.transposed != 0;
+  const T *xArray = static_cast<const T *>(p.x.base), *xBase = xArray + views[0].base;
+  const T *fArray = static_cast<const T *>(p.f.base), *fBase = fArray + views[1].base;
+  const int chunks = (K + KC - 1) / KC;
 
   for (int m0 = 0; m0 < TM; m0 += SY)
     for (int n0 = 0; n0 < TN; n0 += SX) {
@@ -143,63 +211,79 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
         for (int j = 0; j < MX; ++j)
           acc[i][j] = T(0);
 
-      T ra[MY], rb[MX]; // this thread's share of the chunk in flight
-      auto fetchChunk = [&](int k0) {
+      // Offsets of this thread's elements of one chunk; negative = reads as zero.
+      int offA[NA], offB[NB];
+      auto loadOffsets = [&](int chunk) {
+        const int k0 = chunk * KC;
 #pragma unroll
-        for (int i = 0; i < MY; ++i) {
+        for (int i = 0; i < NA; ++i) {
           int aa, kk;
           chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
           const int a = m0 + aa, k = k0 + kk;
-          ra[i] = (a < TM && k < K)
-                      ? fetch<T>(p.x, views[0], xKFast ? a * K + k : k * TM + a)
-                      : T(0);
+          const int idx = xKFast ? a * K + k : k * TM + a;
+          offA[i] = (chunk < chunks && a < TM && k < K && inside(p.x, views[0], idx))
+                        ? __ldg(p.x.lin + idx)
+                        : -1;
         }
 #pragma unroll
-        for (int j = 0; j < MX; ++j) {
+        for (int j = 0; j < NB; ++j) {
           int bb, kk;
           chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
           const int b = n0 + bb, k = k0 + kk;
-          rb[j] = (b < TN && k < K)
-                      ? fetch<T>(p.f, views[1], fKFast ? b * K + k : k * TN + b)
-                      : T(0);
+          const int idx = fKFast ? b * K + k : k * TN + b;
+          offB[j] = (chunk < chunks && b < TN && k < K && inside(p.f, views[1], idx))
+                        ? __ldg(p.f.lin + idx)
+                        : -1;
         }
       };
-      auto stageChunk = [&]() {
+      // Mapped offsets are never negative for an element inside its array
+      // (origins and in-range relative indices are >= 0, strides are >= 0).
+      auto issueCopies = [&](int stage) {
 #pragma unroll
-        for (int i = 0; i < MY; ++i) {
+        for (int i = 0; i < NA; ++i) {
           int aa, kk;
           chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
-          sA[kk][swizzled<SY>(kk, aa)] = ra[i];
+          const bool valid = offA[i] >= 0;
+          copyAsync(&sA[stage][kk][swizzled<SY>(kk, aa)], valid ? xBase + offA[i] : xArray, valid);
         }
 #pragma unroll
-        for (int j = 0; j < MX; ++j) {
+        for (int j = 0; j < NB; ++j) {
           int bb, kk;
           chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
-          sB[kk][swizzled<SX>(kk, bb)] = rb[j];
+          const bool valid = offB[j] >= 0;
+          copyAsync(&sB[stage][kk][swizzled<SX>(kk, bb)], valid ? fBase + offB[j] : fArray, valid);
         }
+        commitCopies();
       };
 
-      if (K > 0)
-        fetchChunk(0);
-      for (int k0 = 0; k0 < K; k0 += KC) {
-        stageChunk();
-        __syncthreads();
-        if (k0 + KC < K)
-          fetchChunk(k0 + KC);
+      __syncthreads(); // the previous piece is done with the ring
+      // Fill the first STAGES-1 stages; keep the offsets of the next chunk ready.
+      loadOffsets(0);
+#pragma unroll
+      for (int s = 0; s < STAGES - 1; ++s) {
+        issueCopies(s); // chunks past the end copy zeros
+        loadOffsets(s + 1);
+      }
+      for (int c = 0; c < chunks; ++c) {
+        waitCopies<STAGES - 2>(); // chunk c has landed (this thread's part)
+        __syncthreads();          // ... everyone's part; and chunk c-1 is no longer read
+        issueCopies((c + STAGES - 1) % STAGES);
+        loadOffsets(c + STAGES);
+        const int stage = c % STAGES;
 #pragma unroll
         for (int kk = 0; kk < KC; ++kk) {
           alignas(16) T av[MY];
           alignas(16) T bv[MX];
-          loadRun<T, MY>(&sA[kk][swizzled<SY>(kk, ty * MY)], av);
-          loadRun<T, MX>(&sB[kk][swizzled<SX>(kk, tx * MX)], bv);
+          loadRun<T, MY, SY>(sA[stage][kk], kk, ty * MY, av);
+          loadRun<T, MX, SX>(sB[stage][kk], kk, tx * MX, bv);
 #pragma unroll
           for (int i = 0; i < MY; ++i)
 #pragma unroll
             for (int j = 0; j < MX; ++j)
               acc[i][j] += av[i] * bv[j];
         }
-        __syncthreads();
       }
+      waitCopies<0>();
 
 #pragma unroll
       for (int i = 0; i < MY; ++i) {
@@ -221,25 +305,24 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 } // namespace
 
-// Gathers hide their latency behind other CTAs: cap the registers so that four
-// CTAs fit on an SM (three or two where the accumulators alone take 64 or 128
-// bytes per thread).
-#define HC_MAPPED_KERNEL(T, tname, MY, MX)                                              \
-  extern "C" __global__ void __launch_bounds__(                                         \
-      THREADS, MY * MX * sizeof(T) >= 128 ? 2 : MY * MX * sizeof(T) >= 64 ? 3 : 4)      \
-      hc_mapped_gemm_##tname##_m##MY##n##MX(const __grid_constant__ HcMappedGemmParams p) { \
-    mappedGemm<T, MY, MX>(p);                                                           \
+// One kernel per piece shape SY x SX (8, 16, 32 or 64 each way); the launcher
+// picks the smallest piece that holds the tile.
+#define HC_MAPPED_KERNEL(T, tname, SY, SX)                                              \
+  extern "C" __global__ void                                                            \
+      __launch_bounds__(threadsOf<SY, SX>(), residentCtas<T, SY, SX>())                 \
+          hc_mapped_gemm_##tname##_##SY##x##SX(const __grid_constant__ HcMappedGemmParams p) { \
+    mappedGemm<T, SY, SX>(p);                                                           \
   }
+#define HC_MAPPED_ROW(T, tname, SY)                                                     \
+  HC_MAPPED_KERNEL(T, tname, SY, 8)                                                     \
+  HC_MAPPED_KERNEL(T, tname, SY, 16)                                                    \
+  HC_MAPPED_KERNEL(T, tname, SY, 32)                                                    \
+  HC_MAPPED_KERNEL(T, tname, SY, 64)
 #define HC_MAPPED_KERNELS(T, tname)                                                     \
-  HC_MAPPED_KERNEL(T, tname, 1, 1)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 1, 2)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 1, 4)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 2, 1)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 2, 2)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 2, 4)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 4, 1)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 4, 2)                                                      \
-  HC_MAPPED_KERNEL(T, tname, 4, 4)
+  HC_MAPPED_ROW(T, tname, 8)                                                            \
+  HC_MAPPED_ROW(T, tname, 16)                                                           \
+  HC_MAPPED_ROW(T, tname, 32)                                                           \
+  HC_MAPPED_ROW(T, tname, 64)
 
 HC_MAPPED_KERNELS(float, f32)
 HC_MAPPED_KERNELS(double, f64)

@@ -73,24 +73,8 @@ const KernelEntry kKernelTable[] = {
     {"hc_selftest_wait_timeout", "selftest"},
     {"hc_pairwise_distance_f32", "pairwise_distance"},
     {"hc_pairwise_distance_f64", "pairwise_distance"},
-    {"hc_mapped_gemm_f32_m1n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m1n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m1n4", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m2n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m2n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m2n4", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m4n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m4n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f32_m4n4", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m1n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m1n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m1n4", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m2n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m2n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m2n4", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m4n1", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m4n2", "mapped_gemm"},
-    {"hc_mapped_gemm_f64_m4n4", "mapped_gemm"},
+    // hc_mapped_gemm_{f32,f64}_{8,16,32,64}x{8,16,32,64}: one per piece shape.
+    {"hc_mapped_gemm_", "mapped_gemm"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f32_async", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
@@ -102,6 +86,18 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_bf16_umma_pair_scaled", "gemm_bf16_umma"},
     {"hc_dequant_w8_bf16", "dequant_w8"},
 };
+
+// Image that defines `kernel`; a table entry ending in '_' stands for every
+// kernel whose name starts with it.
+const char *imageOfKernel(const char *kernel) {
+  for (const auto &e : kKernelTable) {
+    const size_t n = std::strlen(e.kernel);
+    if (n && e.kernel[n - 1] == '_' ? std::strncmp(e.kernel, kernel, n) == 0
+                                    : std::strcmp(e.kernel, kernel) == 0)
+      return e.image;
+  }
+  return nullptr;
+}
 
 int findImage(const char *name) {
   for (int i = 0; i < hc_b200_image_count; ++i)
@@ -167,10 +163,7 @@ struct HcContextImpl {
     auto it = kernels.find(name);
     if (it != kernels.end())
       return it->second;
-    const char *imageName = nullptr;
-    for (const auto &e : kKernelTable)
-      if (std::strcmp(e.kernel, name) == 0)
-        imageName = e.image;
+    const char *imageName = imageOfKernel(name);
     int idx = imageName ? findImage(imageName) : -1;
     if (idx < 0) {
       fail("Unknown kernel: %s", name);
@@ -244,10 +237,8 @@ const void *hcImageData(int index, size_t *lenRet) {
 int hcImageOfKernel(const char *kernelName) {
   if (!kernelName)
     return -1;
-  for (const auto &e : kKernelTable)
-    if (std::strcmp(e.kernel, kernelName) == 0)
-      return findImage(e.image);
-  return -1;
+  const char *image = imageOfKernel(kernelName);
+  return image ? findImage(image) : -1;
 }
 
 HcContext hcCreateContext(const char *deviceDesc, OlErrorCallback errCallback,
@@ -604,14 +595,17 @@ int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f
   p.K = K;
   if (out->transposed)
     return c->fail("hcMappedGemm: the tables of out must be in row-major order");
-  // Smallest (16*MY) x (16*MX) piece that holds the tile, up to 64 x 64; larger
-  // tiles are walked in pieces by the kernel.
-  auto perThread = [](int extent) { return extent <= 16 ? 1 : extent <= 32 ? 2 : 4; };
+  // Smallest piece (8, 16, 32 or 64 each way) that holds the tile; larger tiles
+  // are walked in 64-wide pieces by the kernel.  A side of 32 or 64 is worked
+  // on by 16 threads, a shorter one by 8 (mapped_gemm.cu: Side).
+  auto side = [](int extent) { return extent <= 8 ? 8 : extent <= 16 ? 16 : extent <= 32 ? 32 : 64; };
+  const int sy = side(TM), sx = side(TN);
+  const int threads = (sy >= 32 ? 16 : 8) * (sx >= 32 ? 16 : 8);
   char name[48];
-  std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_m%dn%d", dtype == HC_F32 ? "f32" : "f64",
-                perThread(TM), perThread(TN));
+  std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_%dx%d", dtype == HC_F32 ? "f32" : "f64", sy,
+                sx);
   void *args[] = {&p};
-  return c->launch(name, size_t(groups), 1, 1, 256, args, 1, 0);
+  return c->launch(name, size_t(groups), 1, 1, size_t(threads), args, 1, 0);
 }
 
 // ---- GEMMs ----------------------------------------------------------------------
