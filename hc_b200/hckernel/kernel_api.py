@@ -10,7 +10,8 @@ calls on tiles build an expression graph, ``group.store`` appends to the
 group's list of stores.  ``hckernel.kernel`` then recognises the recorded
 graph as one of the precompiled kernel families (copy, row softmax, last-axis
 reductions, GEMM, weight-only dequant GEMM) and launches that kernel on the
-whole arrays.  Nothing is computed on the host.
+whole arrays - or, for tile products gathered through index mappings, one CTA
+per work-group.  Nothing is computed on the host.
 
 Semantics the recording keeps from the reference:
 

@@ -17,6 +17,9 @@ What is restated, and from where (paths are relative to the reference tree):
 * ``group.store`` - the tile clipped to the destination view; with a masked
   source only the valid elements are written
   (python/hckernel/kernel_api.py:318-342);
+* ``group.load`` / ``group.store`` through an index mapping - element-wise
+  gather and scatter with out-of-range indices masked or dropped
+  (python/hckernel/kernel_api.py:303-310, 319-336);
 * tile allocators ``zeros``/``full`` (python/hckernel/kernel_api.py:347-369,
   433-434);
 * masked reductions that ignore padding (numpy.ma behaviour reached through
