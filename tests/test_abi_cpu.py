@@ -204,6 +204,15 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
         assert blob == (NATIVE / f"{name}.cubin").read_bytes()
         symbols[name] = _elf_symbols(blob)
     for kernel, image in table:
+        if kernel.endswith("_"):
+            # A prefix entry: the family of the gathered tile product, one kernel
+            # per element type and piece shape.
+            family = {s for s in symbols[image] if s.startswith(kernel)}
+            assert family == {f"{kernel}{t}_{sy}x{sx}" for t in ("f32", "f64")
+                              for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)}
+            for member in family:
+                assert lib.hcImageName(lib.hcImageOfKernel(member.encode())).decode() == image
+            continue
         assert kernel in symbols[image], (kernel, image)
         assert lib.hcImageOfKernel(kernel.encode()) >= 0
     assert lib.hcImageOfKernel(b"no_such_kernel") == -1
