@@ -13,7 +13,11 @@ actually differ on this backend:
   defaults when they are valid and otherwise the first valid combination;
 * the native variants of the recognised kernel family - one CTA or a CTA pair
   per GEMM tile, register or bulk-copy softmax, plain or cp.async fp32 GEMM -
-  do differ, and are timed with CUDA events on the stream the kernels run on.
+  do differ, and are timed with CUDA events on the stream the kernels run on;
+* tile products gathered through index mappings (the implicit-GEMM
+  convolution) are the exception to the first point: they run one CTA per
+  work-group exactly as the body tiles the problem, so for them the symbolic
+  tunables are searched and timed, which is what the RFC meant them for.
 
 The result is a :class:`TunedParams`: a ``{symbol: value}`` mapping accepted by
 ``kernel.parametrize`` that also carries the chosen native options.
@@ -93,6 +97,46 @@ def _time_call(kernel, args, options, repeats):
     return start.elapsed_time(stop) / repeats
 
 
+def _spread_of(tunable):
+    """The default, the largest value and the powers of two among a tunable's
+    values - a coarse grid that still spans its range."""
+    values = set(tunable.vals)
+    picks = {tunable.default, max(values)}
+    power = 1
+    while power <= max(values):
+        if power in values:
+            picks.add(power)
+        power *= 2
+    return sorted(picks)
+
+
+def _tune_mapped_tiles(kernel, args, defaults, repeats, limit):
+    """Tile products gathered through mappings run one CTA per work-group, so
+    here the symbolic tunables (the tile sizes of the body) are what decides the
+    speed: every combination of a coarse grid of their values is recorded, and
+    each distinct launch (tile sizes and group counts; tunables that only
+    restructure the body's K loop give the same launch) is timed once."""
+    tunables = _tunable_list(kernel.tunables)
+    timings, timed, best = {}, {}, (dict(defaults), None)
+    combos = itertools.islice(itertools.product(*(_spread_of(t) for t in tunables)), limit)
+    for combo in itertools.chain([tuple(defaults[t.sym] for t in tunables)], combos):
+        symbols = dict(zip((t.sym for t in tunables), combo))
+        try:
+            spec = kernel.parametrize(symbols).plan_for(args).roles.get("spec")
+            if spec is None:
+                continue
+            launch = (spec.tm, spec.tn, spec.k, spec.counts)
+            if launch not in timed:
+                timed[launch] = _time_call(kernel.parametrize(symbols), args, {}, repeats)
+                timings[json.dumps({str(k): int(v) for k, v in symbols.items()},
+                                   sort_keys=True)] = timed[launch]
+        except (UnsupportedKernel, ValueError, RuntimeError):
+            continue  # a combination the front door or the launcher refuses
+        if best[1] is None or timed[launch] < best[1]:
+            best = (symbols, timed[launch])
+    return TunedParams(best[0], {}, timings)
+
+
 def autotune(kernel, *args, repeats=5, max_symbol_sets=256):
     """Tuned parameters of ``kernel`` for arguments shaped like ``args``.
 
@@ -110,6 +154,8 @@ def autotune(kernel, *args, repeats=5, max_symbol_sets=256):
         raise UnsupportedKernel(
             f"{kernel.func.__name__}: no combination of tunables gives a supported kernel")
     symbols, plan = chosen
+    if plan.family == "mapped_gemm":
+        return _tune_mapped_tiles(kernel, args, symbols, repeats, max_symbol_sets)
     timings, best = {}, ({}, None)
     for options in _VARIANTS.get(plan.family, [{}]):
         try:

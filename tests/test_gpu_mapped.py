@@ -90,6 +90,33 @@ def test_non_contiguous_arguments():
     assert torch.equal(d_out.contiguous(), d_out2)  # one plan, tables per stride set
 
 
+def test_autotune_searches_the_tile_sizes():
+    """For this family the symbolic tunables decide the launch, so autotune
+    times a grid of them (docs/langref.md:471-586 of the reference describes the
+    API; the reference does not implement it)."""
+    from hc_b200.hckernel.autotune import autotune
+
+    x_shape, f_shape = (16, 8, 20, 20), (32, 8, 3, 3)
+    x, f = oracle.make_conv_inputs(x_shape, f_shape, "float32")
+    out_shape = oracle.conv_out_shape(x_shape, f_shape, 1)
+    d_x, d_f = torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda()
+    d_out = torch.zeros(out_shape, device="cuda")
+    conv = make_conv(1)
+    tuned = autotune(conv, d_x, d_f, d_out, repeats=3)
+    assert set(tuned) == {sym.TN, sym.TNF, sym.KB}
+    # Tile sizes were really compared (KB only restructures the body's K loop
+    # and is not timed separately), and the fastest launch was taken.
+    assert len(tuned.timings) >= 9
+    import json
+    best = json.dumps({str(k): int(v) for k, v in tuned.items()}, sort_keys=True)
+    assert tuned.timings[best] == min(tuned.timings.values())
+    d_out.zero_()
+    conv.parametrize(tuned)(d_x, d_f, d_out)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(d_out.cpu().numpy(), oracle.conv_direct(x, f, 1),
+                               rtol=1e-4, atol=1e-4)
+
+
 def _operand(array, table, lin, origins):
     op = capi.HcMappedOperand()
     op.base = array.data_ptr()

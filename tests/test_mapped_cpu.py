@@ -103,6 +103,14 @@ def test_table_order_follows_memory_order():
     assert spec.device_tables((x, f, out)) is spec.device_tables((x, f, out))  # cached
 
 
+def test_autotune_grid_of_a_tunable():
+    from hc_b200.hckernel.autotune import _spread_of
+
+    assert _spread_of(TunableParam(sym.TN, 8, range(1, 64))) == [1, 2, 4, 8, 16, 32, 63]
+    assert _spread_of(TunableParam(sym.KB, 16, range(8, 128))) == [8, 16, 32, 64, 127]
+    assert _spread_of(TunableParam(sym.V, 3, [3, 5, 6])) == [3, 6]
+
+
 def test_index_expressions():
     g = tuple(Affine(0, {d: 1}) for d in range(3))
     gids = np.indices((2, 3, 4)).reshape(3, -1)
