@@ -47,7 +47,7 @@ class HcMappedOperand(C.Structure):
         ("lo", C.c_int * 4),
         ("hi", C.c_int * 4),
         ("transposed", C.c_int),
-        ("reserved", C.c_int),
+        ("sharedRun", C.c_int),
     ]
 
 

@@ -231,10 +231,11 @@ HcMappedOperand mappedOperand(const Context &ctx, py::handle array, py::handle t
     op.stride[d] = a.strides[d];
   }
   auto t = py::cast<py::tuple>(tables);
-  if (t.size() != 6)
+  if (t.size() != 7)
     throw py::value_error(std::string(name) +
-                          ": tables must be (map, lin, origins, lo, hi, transposed)");
+                          ": tables must be (map, lin, origins, lo, hi, transposed, shared_run)");
   op.transposed = py::cast<bool>(t[5]) ? 1 : 0;
+  op.sharedRun = py::cast<int>(t[6]);
   const std::string nm(name);
   ArrayArg map = deviceArray(ctx, t[0], (nm + " map").c_str(), 2);
   ArrayArg lin = deviceArray(ctx, t[1], (nm + " lin").c_str(), 1);

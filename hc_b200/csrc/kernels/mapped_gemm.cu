@@ -42,10 +42,16 @@
 // so that the copies of a warp spread over the banks.  Tiles larger than
 // TY*MY x TX*MX are walked in pieces.
 //
-// What bounds it: every work-group gathers both of its operand tiles and
-// their offset tables again, so for tiles of a few thousand elements the
-// traffic from L2 into the SMs, not the FMA pipe, sets the pace (measured on
-// a 32 x 64 x 576 tile: about 0.8 MB per group for 2.4 MFLOP).
+// Work-groups whose f tile is the same (consecutive output positions of the
+// convolution) are stacked: one CTA takes up to eight of them, as long as the
+// stacked rows fit one 64-row piece, gathers the f tile once and multiplies it
+// with the rows of all of them.  The result of every group is what it would be
+// alone (same sum order); the stack only shares the B side.
+//
+// What bounds it: with tiles of a few thousand elements a thread owns few
+// results, so the shared-memory side of the L1 pipe (one or two wavefronts per
+// 8- or 16-byte load of a quarter warp), not the FMA pipe, sets the pace;
+// larger tiles and stacks move the balance towards the FMA pipe.
 #include "mapped_params.h"
 
 #include <stdint.h>
@@ -53,6 +59,7 @@
 namespace {
 
 constexpr int KC = 16;
+constexpr int kMaxStack = 8; // work-groups one CTA may stack (the launcher asks for <= 8)
 
 struct GroupView {
   long long base; // linear offset of the tile origin
@@ -173,7 +180,8 @@ __host__ __device__ constexpr int threadsOf() {
 template <typename T, int SY, int SX>
 __host__ __device__ constexpr int residentCtas() {
   constexpr int MY = Side<SY>::each, MX = Side<SX>::each, NT = threadsOf<SY, SX>();
-  constexpr int regs = 40 + MY * MX * int(sizeof(T) / 4) * 3 / 2 + (SY + SX) * KC / NT;
+  constexpr int regs =
+      40 + MY * MX * int(sizeof(T) / 4) * 3 / 2 + (SY + SX) * KC / NT + 2 * SY * KC / NT;
   constexpr int fit = 65536 / (NT * regs);
   return fit < 1 ? 1 : fit > 8 ? 8 : fit;
 }
@@ -187,22 +195,37 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
   constexpr int STAGES = 3 * KC * (SY + SX) * int(sizeof(T)) > 47 * 1024 ? 2 : 3;
   __shared__ __align__(16) T sA[STAGES][KC][SY]; // [stage][k][row], swizzled
   __shared__ __align__(16) T sB[STAGES][KC][SX]; // [stage][k][column], swizzled
-  __shared__ GroupView views[3];
+  // A CTA takes `stack` consecutive work-groups that share their f tile and
+  // computes them as one product with stack * TM rows.
+  __shared__ GroupView xViews[kMaxStack], outViews[kMaxStack], fView;
 
   const int tid = threadIdx.x;
-  const long long g = blockIdx.x;
-  if (tid < 3)
-    openView(tid == 0 ? p.x : tid == 1 ? p.f : p.out, g, views[tid]);
+  const int TM = p.TM, TN = p.TN, K = p.K, stack = p.stack;
+  const long long g0 = (long long)blockIdx.x * stack;
+  if (tid < 2 * stack + 1) {
+    const int which = tid % 2, j = tid / 2; // (x, out) of stacked group j; the last one: f
+    const long long g = g0 + j;
+    if (tid == 2 * stack) {
+      openView(p.f, g0, fView);
+    } else if (g < p.groups) {
+      openView(which == 0 ? p.x : p.out, g, which == 0 ? xViews[j] : outViews[j]);
+    } else { // past the last work-group: nothing is inside
+      GroupView &v = which == 0 ? xViews[j] : outViews[j];
+      v.base = 0;
+      v.interior = 0;
+      v.lim[0] = v.lim[1] = v.lim[2] = v.lim[3] = 0;
+    }
+  }
   __syncthreads();
   const int ty = tid / TX, tx = tid % TX;
-  const int TM = p.TM, TN = p.TN, K = p.K;
+  const int rows = stack * TM;
   // x natural order is [a][k] (k fastest); f natural order is [k][b].
   const bool xKFast = !p.x.transposed, fKFast = p.f.transposed != 0;
-  const T *xArray = static_cast<const T *>(p.x.base), *xBase = xArray + views[0].base;
-  const T *fArray = static_cast<const T *>(p.f.base), *fBase = fArray + views[1].base;
+  const T *xArray = static_cast<const T *>(p.x.base);
+  const T *fArray = static_cast<const T *>(p.f.base), *fBase = fArray + fView.base;
   const int chunks = (K + KC - 1) / KC;
 
-  for (int m0 = 0; m0 < TM; m0 += SY)
+  for (int m0 = 0; m0 < rows; m0 += SY)
     for (int n0 = 0; n0 < TN; n0 += SX) {
       T acc[MY][MX];
 #pragma unroll
@@ -211,6 +234,17 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
         for (int j = 0; j < MX; ++j)
           acc[i][j] = T(0);
 
+      // Which stacked group and which row of its tile each of this thread's A
+      // elements belongs to (the same for every chunk).
+      int groupOfA[NA], rowOfA[NA];
+#pragma unroll
+      for (int i = 0; i < NA; ++i) {
+        int aa, kk;
+        chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
+        const int row = m0 + aa;
+        groupOfA[i] = row < rows ? row / TM : -1;
+        rowOfA[i] = row % TM;
+      }
       // Offsets of this thread's elements of one chunk; negative = reads as zero.
       int offA[NA], offB[NB];
       auto loadOffsets = [&](int chunk) {
@@ -219,9 +253,10 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
         for (int i = 0; i < NA; ++i) {
           int aa, kk;
           chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
-          const int a = m0 + aa, k = k0 + kk;
+          const int a = rowOfA[i], k = k0 + kk;
           const int idx = xKFast ? a * K + k : k * TM + a;
-          offA[i] = (chunk < chunks && a < TM && k < K && inside(p.x, views[0], idx))
+          offA[i] = (chunk < chunks && groupOfA[i] >= 0 && k < K &&
+                     inside(p.x, xViews[groupOfA[i]], idx))
                         ? __ldg(p.x.lin + idx)
                         : -1;
         }
@@ -231,7 +266,7 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
           chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
           const int b = n0 + bb, k = k0 + kk;
           const int idx = fKFast ? b * K + k : k * TN + b;
-          offB[j] = (chunk < chunks && b < TN && k < K && inside(p.f, views[1], idx))
+          offB[j] = (chunk < chunks && b < TN && k < K && inside(p.f, fView, idx))
                         ? __ldg(p.f.lin + idx)
                         : -1;
         }
@@ -244,7 +279,8 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
           int aa, kk;
           chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
           const bool valid = offA[i] >= 0;
-          copyAsync(&sA[stage][kk][swizzled<SY>(kk, aa)], valid ? xBase + offA[i] : xArray, valid);
+          copyAsync(&sA[stage][kk][swizzled<SY>(kk, aa)],
+                    valid ? xArray + xViews[groupOfA[i]].base + offA[i] : xArray, valid);
         }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
@@ -287,17 +323,19 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 #pragma unroll
       for (int i = 0; i < MY; ++i) {
-        const int a = m0 + ty * MY + i;
-        if (a >= TM)
+        const int row = m0 + ty * MY + i;
+        if (row >= rows)
           continue;
+        const GroupView &view = outViews[row / TM];
+        const int a = row % TM;
 #pragma unroll
         for (int j = 0; j < MX; ++j) {
           const int b = n0 + tx * MX + j;
           if (b >= TN)
             continue;
           const int idx = a * TN + b;
-          if (inside(p.out, views[2], idx))
-            static_cast<T *>(p.out.base)[views[2].base + p.out.lin[idx]] = acc[i][j];
+          if (inside(p.out, view, idx))
+            static_cast<T *>(p.out.base)[view.base + p.out.lin[idx]] = acc[i][j];
         }
       }
     }

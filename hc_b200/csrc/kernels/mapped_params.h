@@ -20,10 +20,15 @@ struct HcMappedOperandDev {
   // in table order, so the host picks the order in which neighbouring elements
   // are neighbours in memory.
   int32_t transposed;
-  int32_t reserved;
+  // Work-groups g with equal g / sharedRun have the same tile origin in this
+  // array (0 or 1: nothing known).  Read for f only: such groups multiply
+  // against one and the same B tile, so one CTA can take several of them.
+  int32_t sharedRun;
 };
 
 struct HcMappedGemmParams {
   HcMappedOperandDev x, f, out; // tiles [TM, K], [K, TN], [TM, TN]
   int32_t TM, TN, K;
+  int32_t stack;  // consecutive work-groups one CTA computes, stacked along the rows
+  int64_t groups; // work-groups in all
 };

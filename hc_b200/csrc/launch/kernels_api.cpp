@@ -136,6 +136,7 @@ struct HcContextImpl {
   long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
   long long tiledVariant = 0;
   long long reduceVariant = 0;
+  long long mappedStack = 0;
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
@@ -362,6 +363,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
   }
   if (std::strcmp(name, "tiled_variant") == 0 && value >= 0 && value <= 1) {
     c->tiledVariant = value; // 1: never use the cp.async pipelined fp32 kernel
+    return 0;
+  }
+  if (std::strcmp(name, "mapped_stack") == 0 && value >= 0 && value <= 1) {
+    c->mappedStack = value; // 1: one work-group per CTA even where groups share a tile
     return 0;
   }
   return c->fail("Invalid option: %s = %lld", name, value);
@@ -599,13 +604,22 @@ int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f
   // are walked in 64-wide pieces by the kernel.  A side of 32 or 64 is worked
   // on by 16 threads, a shorter one by 8 (mapped_gemm.cu: Side).
   auto side = [](int extent) { return extent <= 8 ? 8 : extent <= 16 ? 16 : extent <= 32 ? 32 : 64; };
-  const int sy = side(TM), sx = side(TN);
+  // Work-groups that share their f tile are stacked along the rows of one CTA:
+  // the largest power of two that the caller vouches for (f->sharedRun), that
+  // the kernel holds (8) and that keeps the stacked rows within one 64-row piece.
+  int stack = 1;
+  while (stack * 2 <= 8 && stack * 2 <= f->sharedRun && f->sharedRun % (stack * 2) == 0 &&
+         (long long)stack * 2 * TM <= 64 && c->mappedStack != 1)
+    stack *= 2;
+  p.stack = stack;
+  p.groups = groups;
+  const int sy = side(stack * TM), sx = side(TN);
   const int threads = (sy >= 32 ? 16 : 8) * (sx >= 32 ? 16 : 8);
   char name[48];
   std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_%dx%d", dtype == HC_F32 ? "f32" : "f64", sy,
                 sx);
   void *args[] = {&p};
-  return c->launch(name, size_t(groups), 1, 1, size_t(threads), args, 1, 0);
+  return c->launch(name, size_t(ceilDiv(groups, stack)), 1, 1, size_t(threads), args, 1, 0);
 }
 
 // ---- GEMMs ----------------------------------------------------------------------

@@ -51,6 +51,22 @@ def _identity(*index):
     return index
 
 
+def _shared_run(origins):
+    """Largest n in (8, 4, 2) such that work-groups g with equal ``g // n`` all
+    have the same tile origin, else 1.  Groups of such a run read one and the
+    same tile, so the kernel lets one CTA compute several of them against it."""
+    groups = origins.shape[0]
+    for n in (8, 4, 2):
+        if groups < n:
+            continue
+        whole = groups // n * n
+        runs = origins[:whole].reshape(-1, n, origins.shape[1])
+        tail = origins[whole:]
+        if (runs == runs[:, :1]).all() and (tail == tail[:1]).all():
+            return n
+    return 1
+
+
 def _neighbour_distance(offsets, axis, sector):
     """Mean distance in memory, capped at one 32-byte sector, between tile
     elements adjacent along ``axis`` - how well a warp that walks the tile along
@@ -231,8 +247,8 @@ class MappedSpec:
         return self._host
 
     def device_tables(self, tensors):
-        """(map, lin, origins, lo, hi, transposed) per operand, on the device of
-        ``tensors`` (the x, f, out call arguments) and for their strides."""
+        """(map, lin, origins, lo, hi, transposed, shared_run) per operand, on the
+        device of ``tensors`` (the x, f, out call arguments) and for their strides."""
         import torch
 
         key = (str(tensors[0].device),) + tuple(tuple(t.stride()) for t in tensors)
@@ -265,6 +281,6 @@ class MappedSpec:
                     return torch.from_numpy(np.ascontiguousarray(a.astype(np.int32))).to(t.device)
 
                 tables.append((dev(mp), dev(lin), dev(org), [int(v) for v in lo],
-                               [int(v) for v in hi], bool(transposed)))
+                               [int(v) for v in hi], bool(transposed), _shared_run(org)))
             self._device[key] = tables
         return tables

@@ -83,7 +83,9 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
                                       int observedRet[2]);
 
 /* Tuning and test switches.  "gemm_variant": 0 = automatic, 1 = one CTA per
- * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel. */
+ * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel.  "mapped_stack":
+ * 0 = hcMappedGemm stacks work-groups that share their f tile, 1 = one
+ * work-group per CTA. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* ---- workloads -------------------------------------------------------------
@@ -152,7 +154,10 @@ typedef struct HcMappedOperand {
   int lo[4];
   int hi[4];
   int transposed;       /* order of map/lin; must be 0 for out */
-  int reserved;         /* 0 */
+  int sharedRun;        /* n > 1: work-groups g with equal g / n have the same
+                           origin in this array (read for f only: such groups
+                           use one f tile, so one CTA computes several of them
+                           against it); 0 or 1: nothing known */
 } HcMappedOperand;
 HC_B200_API int hcMappedGemm(HcContext c, const HcMappedOperand *x,
                              const HcMappedOperand *f, const HcMappedOperand *out,

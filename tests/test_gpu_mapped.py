@@ -58,6 +58,29 @@ def test_conv_larger_cases_match_the_oracle(dtype, tiles):
     np.testing.assert_allclose(out, oracle.conv_direct(x, f, stride), rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("tiles", [(8, 8, 16), (5, 24, 16), (16, 64, 16), (32, 64, 16)])
+def test_stacked_groups_give_what_single_groups_give(tiles):
+    """Consecutive output positions share their filter tile, so one CTA computes
+    up to eight of them (fewer for taller tiles); bit for bit the result must be
+    what one CTA per work-group produces."""
+    from hc_b200.hckernel.autotune import TunedParams
+
+    x_shape, f_shape = (19, 5, 11, 11), (40, 5, 3, 3)
+    x, f = oracle.make_conv_inputs(x_shape, f_shape, "float32", seed=12)
+    out_shape = oracle.conv_out_shape(x_shape, f_shape, 1)
+    tn, tnf, kb = tiles
+    conv = make_conv(1).parametrize({sym.TN: tn, sym.TNF: tnf, sym.KB: kb})
+    d_x, d_f = torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda()
+    stacked = torch.full(out_shape, -3.0, device="cuda")
+    single = torch.full(out_shape, -3.0, device="cuda")
+    conv(d_x, d_f, stacked)
+    conv.parametrize(TunedParams({}, {"mapped_stack": 1}))(d_x, d_f, single)
+    torch.cuda.synchronize()
+    assert torch.equal(stacked, single)
+    np.testing.assert_allclose(stacked.cpu().numpy(), oracle.conv_direct(x, f, 1),
+                               rtol=1e-4, atol=1e-4)
+
+
 def test_elements_no_group_writes_stay_untouched():
     # A 5x8 image: positions run over W_OUT on the H axis (test_examples.py:
     # 237-240), so output columns 4..6 are never written - by the reference or here.
@@ -179,6 +202,15 @@ def test_mapped_gemm_through_the_c_abi(hc):
     hc.mapped_gemm(ops_t[0], ops_t[1], ops[2], groups, tm, n + 2, k, capi.HC_F64)
     finish(hc)
     np.testing.assert_allclose(d_out.cpu().numpy(), expect, rtol=1e-12, atol=1e-12)
+    # All three groups read the same f tile: tell the kernel, which then computes
+    # two groups per CTA (and the odd last one alone) - same result.
+    for run in (2, 8):
+        d_out.fill_(-1.0)
+        ops[1].sharedRun = run
+        hc.mapped_gemm(ops[0], ops[1], ops[2], groups, tm, n + 2, k, capi.HC_F64)
+        finish(hc)
+        np.testing.assert_allclose(d_out.cpu().numpy(), expect, rtol=1e-12, atol=1e-12)
+    ops[1].sharedRun = 0
     ops[2].transposed = 1
     with pytest.raises(RuntimeError, match="row-major"):
         hc.mapped_gemm(ops[0], ops[1], ops[2], groups, tm, n + 2, k, capi.HC_F64)

@@ -92,6 +92,9 @@ def test_table_order_follows_memory_order():
     spec = make_conv(1).plan_for((x, f, out)).roles["spec"]
     tx, tf, to = spec.device_tables((x, f, out))
     assert (tx[5], tf[5], to[5]) == (False, True, False)
+    # 1 x 2 x 36 work-groups: the 36 positions of one filter block share their f
+    # tile; aligned runs of 8 would straddle the two blocks, runs of 4 do not.
+    assert spec.counts == (1, 2, 36) and (tx[6], tf[6], to[6]) == (1, 4, 1)
     natural_map, _ = spec.host_tables()["f"]
     k, tnf = spec.k, spec.tn
     assert np.array_equal(tf[0].numpy().reshape(tnf, k, 4),
@@ -101,6 +104,19 @@ def test_table_order_follows_memory_order():
     assert np.array_equal(tf[1].numpy(), tf[0].numpy() @ stride)
     assert tf[3] == [0, 0, 0, 0] and tf[4] == [tnf - 1, 2, 2, 2]
     assert spec.device_tables((x, f, out)) is spec.device_tables((x, f, out))  # cached
+
+
+def test_shared_runs_of_tile_origins():
+    from hc_b200.hckernel.mapped import _shared_run
+
+    same = np.zeros((20, 4), np.int64)
+    assert _shared_run(same) == 8            # 20 = 2 runs of 8 + a tail of 4, all equal
+    blocks = np.repeat(np.arange(5), 4)[:, None] * np.ones((1, 4), np.int64)
+    assert _shared_run(blocks) == 4          # origins change every 4 groups
+    assert _shared_run(blocks[:18]) == 4     # a short last run is fine
+    assert _shared_run(blocks[2:]) == 2      # shifted by 2: aligned runs of 4 would mix blocks
+    assert _shared_run(np.arange(12)[:, None] * np.ones((1, 4), np.int64)) == 1
+    assert _shared_run(same[:1]) == 1
 
 
 def test_autotune_grid_of_a_tunable():
