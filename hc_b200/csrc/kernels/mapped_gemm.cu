@@ -234,60 +234,61 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
         for (int j = 0; j < MX; ++j)
           acc[i][j] = T(0);
 
-      // Which stacked group and which row of its tile each of this thread's A
-      // elements belongs to (the same for every chunk).
-      int groupOfA[NA], rowOfA[NA];
+      // What stays the same from chunk to chunk for each of this thread's
+      // elements: where it lands in a stage, its table index in chunk 0 (the
+      // index advances by a fixed step per chunk) and, for A, the stacked
+      // group its row belongs to (-1: a row or column past the tile).
+      int landA[NA], landB[NB], tableA[NA], tableB[NB], groupOfA[NA];
 #pragma unroll
       for (int i = 0; i < NA; ++i) {
         int aa, kk;
         chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
-        const int row = m0 + aa;
+        const int row = m0 + aa, a = row % TM;
+        landA[i] = kk * SY + swizzled<SY>(kk, aa);
+        tableA[i] = xKFast ? a * K + kk : kk * TM + a;
         groupOfA[i] = row < rows ? row / TM : -1;
-        rowOfA[i] = row % TM;
       }
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        int bb, kk;
+        chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
+        const int b = n0 + bb;
+        landB[j] = kk * SX + swizzled<SX>(kk, bb);
+        tableB[j] = b < TN ? (fKFast ? b * K + kk : kk * TN + b) : -1;
+      }
+      const int stepA = xKFast ? KC : KC * TM, stepB = fKFast ? KC : KC * TN;
       // Offsets of this thread's elements of one chunk; negative = reads as zero.
       int offA[NA], offB[NB];
       auto loadOffsets = [&](int chunk) {
         const int k0 = chunk * KC;
 #pragma unroll
         for (int i = 0; i < NA; ++i) {
-          int aa, kk;
-          chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
-          const int a = rowOfA[i], k = k0 + kk;
-          const int idx = xKFast ? a * K + k : k * TM + a;
-          offA[i] = (chunk < chunks && groupOfA[i] >= 0 && k < K &&
-                     inside(p.x, xViews[groupOfA[i]], idx))
+          const int k = k0 + landA[i] / SY, idx = tableA[i] + chunk * stepA;
+          offA[i] = (groupOfA[i] >= 0 && k < K && inside(p.x, xViews[groupOfA[i]], idx))
                         ? __ldg(p.x.lin + idx)
                         : -1;
         }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-          int bb, kk;
-          chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
-          const int b = n0 + bb, k = k0 + kk;
-          const int idx = fKFast ? b * K + k : k * TN + b;
-          offB[j] = (chunk < chunks && b < TN && k < K && inside(p.f, fView, idx))
-                        ? __ldg(p.f.lin + idx)
-                        : -1;
+          const int k = k0 + landB[j] / SX, idx = tableB[j] + chunk * stepB;
+          offB[j] = (tableB[j] >= 0 && k < K && inside(p.f, fView, idx)) ? __ldg(p.f.lin + idx)
+                                                                          : -1;
         }
       };
       // Mapped offsets are never negative for an element inside its array
       // (origins and in-range relative indices are >= 0, strides are >= 0).
       auto issueCopies = [&](int stage) {
+        T *stageA = &sA[stage][0][0], *stageB = &sB[stage][0][0];
 #pragma unroll
         for (int i = 0; i < NA; ++i) {
-          int aa, kk;
-          chunkElement(tid + i * THREADS, SY, xKFast, aa, kk);
           const bool valid = offA[i] >= 0;
-          copyAsync(&sA[stage][kk][swizzled<SY>(kk, aa)],
+          copyAsync(stageA + landA[i],
                     valid ? xArray + xViews[groupOfA[i]].base + offA[i] : xArray, valid);
         }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-          int bb, kk;
-          chunkElement(tid + j * THREADS, SX, fKFast, bb, kk);
           const bool valid = offB[j] >= 0;
-          copyAsync(&sB[stage][kk][swizzled<SX>(kk, bb)], valid ? fBase + offB[j] : fArray, valid);
+          copyAsync(stageB + landB[j], valid ? fBase + offB[j] : fArray, valid);
         }
         commitCopies();
       };
