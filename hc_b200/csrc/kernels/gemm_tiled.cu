@@ -16,8 +16,11 @@
 // kernels: bf16 inputs with fp32 accumulation and bf16 output, and bf16 x int8
 // with a per-output-column fp32 scale applied to the accumulator before
 // rounding (the weight-only dequant GEMM).
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -161,12 +164,13 @@ __device__ __forceinline__ void cpAsync16(void *smemDst, const void *gmemSrc,
                : "memory");
 }
 
-__device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
-                                              const float *__restrict__ b,
-                                              float *__restrict__ c, long long M,
-                                              long long N, long long K,
-                                              long long lda, long long ldb,
-                                              long long ldc, AsyncStage *stages) {
+// acc += A[m0.., kBegin:K] @ B[kBegin:K, n0..] for this thread's 4 x 4 block
+// (kBegin a multiple of 4, K the end of the range this CTA sums over).
+__device__ __forceinline__ void gemmTileAsyncRange(const float *__restrict__ a,
+                                                   const float *__restrict__ b, long long M,
+                                                   long long N, long long kBegin, long long K,
+                                                   long long lda, long long ldb,
+                                                   AsyncStage *stages, float (&acc)[4][4]) {
   const int tid = threadIdx.x;
   const long long m0 = (long long)blockIdx.y * TM;
   const long long n0 = (long long)blockIdx.x * TN;
@@ -197,12 +201,11 @@ __device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
   };
 
   const int ty = tid >> 4, tx = tid & 15;
-  float acc[4][4] = {};
-  const long long kBlocks = (K + AK - 1) / AK;
+  const long long kBlocks = K > kBegin ? (K - kBegin + AK - 1) / AK : 0;
   // Prologue: fill the pipeline (empty commits keep the group count uniform).
   for (int s = 0; s < ASTAGES - 1; ++s) {
     if (s < kBlocks)
-      issue(s, (long long)s * AK);
+      issue(s, kBegin + (long long)s * AK);
     else
       asm volatile("cp.async.commit_group;" ::: "memory");
   }
@@ -211,7 +214,7 @@ __device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
     __syncthreads(); // block kb has landed; block kb-1's buffer is free
     const long long next = kb + ASTAGES - 1;
     if (next < kBlocks)
-      issue(int(next % ASTAGES), next * AK);
+      issue(int(next % ASTAGES), kBegin + next * AK);
     else
       asm volatile("cp.async.commit_group;" ::: "memory");
     const AsyncStage &st = stages[kb % ASTAGES];
@@ -230,6 +233,18 @@ __device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
           acc[i][j] = fmaf(av[i], bb[j], acc[i][j]);
     }
   }
+}
+
+__device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
+                                              const float *__restrict__ b,
+                                              float *__restrict__ c, long long M,
+                                              long long N, long long K,
+                                              long long lda, long long ldb,
+                                              long long ldc, AsyncStage *stages) {
+  float acc[4][4] = {};
+  gemmTileAsyncRange(a, b, M, N, 0, K, lda, ldb, stages, acc);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const long long m0 = (long long)blockIdx.y * TM, n0 = (long long)blockIdx.x * TN;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const long long gm = m0 + ty * 4 + i;
@@ -244,6 +259,65 @@ __device__ __forceinline__ void gemmTileAsync(const float *__restrict__ a,
   }
 }
 
+// ---- split-K over a thread-block cluster --------------------------------------------
+// A problem with few output tiles (the 256^3 case has 16) leaves most SMs
+// idle and is paced by the K loop of one CTA.  Here a cluster of four CTAs
+// shares one tile: each sums a quarter of K (rounded to whole K blocks), parks
+// its 64 x 64 partial result in its own shared memory, and after a cluster
+// barrier each CTA adds up a quarter of the rows - reading the three other
+// partials through distributed shared memory, always in rank order, so the
+// result does not depend on timing - and stores them.
+constexpr int SPLIT = 4;
+constexpr int P_PITCH = TN + 4; // floats per row of a parked partial tile
+
+__device__ __forceinline__ void gemmTileSplitK(const float *__restrict__ a,
+                                               const float *__restrict__ b,
+                                               float *__restrict__ c, long long M,
+                                               long long N, long long K, long long lda,
+                                               long long ldb, long long ldc,
+                                               AsyncStage *stages) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = int(cluster.block_rank());
+  const long long perRank = ((K + SPLIT - 1) / SPLIT + AK - 1) / AK * AK;
+  const long long kBegin = rank * perRank;
+  const long long kEnd = kBegin + perRank < K ? kBegin + perRank : K;
+  float acc[4][4] = {};
+  gemmTileAsyncRange(a, b, M, N, kBegin, kEnd, lda, ldb, stages, acc);
+
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads(); // every thread is done with the stages: reuse them for the partial
+  float *partial = reinterpret_cast<float *>(stages);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4 *>(&partial[(ty * 4 + i) * P_PITCH + tx * 4]) =
+        make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+  cluster.sync();
+
+  // This CTA's quarter of the rows: 16 rows x 64 columns, one float4 per thread.
+  const int row = rank * (TM / SPLIT) + (tid >> 4), col = (tid & 15) << 2;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < SPLIT; ++r) {
+    const float *peer = cluster.map_shared_rank(partial, r);
+    const float4 v = *reinterpret_cast<const float4 *>(&peer[row * P_PITCH + col]);
+    sum.x += v.x;
+    sum.y += v.y;
+    sum.z += v.z;
+    sum.w += v.w;
+  }
+  const long long gm = (long long)blockIdx.y * TM + row;
+  const long long gn = (long long)blockIdx.x * TN + col;
+  if (gm < M) {
+    const float out[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (gn + j < N)
+        c[gm * ldc + gn + j] = out[j];
+  }
+  cluster.sync(); // nobody leaves while a peer may still read its partial
+}
+
 } // namespace
 
 extern "C" __global__ void __launch_bounds__(THREADS)
@@ -253,6 +327,15 @@ extern "C" __global__ void __launch_bounds__(THREADS)
   extern __shared__ __align__(16) unsigned char asyncSmem[];
   gemmTileAsync(a, b, c, M, N, K, lda, ldb, ldc,
                 reinterpret_cast<AsyncStage *>(asyncSmem));
+}
+
+extern "C" __global__ void __cluster_dims__(1, 1, SPLIT) __launch_bounds__(THREADS)
+    hc_gemm_tiled_f32_splitk(const float *a, const float *b, float *c,
+                             long long M, long long N, long long K,
+                             long long lda, long long ldb, long long ldc) {
+  extern __shared__ __align__(16) unsigned char splitSmem[];
+  gemmTileSplitK(a, b, c, M, N, K, lda, ldb, ldc,
+                 reinterpret_cast<AsyncStage *>(splitSmem));
 }
 
 extern "C" __global__ void __launch_bounds__(THREADS)

@@ -77,6 +77,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_mapped_gemm_", "mapped_gemm"},
     {"hc_gemm_tiled_f32", "gemm_tiled"},
     {"hc_gemm_tiled_f32_async", "gemm_tiled"},
+    {"hc_gemm_tiled_f32_splitk", "gemm_tiled"},
     {"hc_gemm_tiled_f64", "gemm_tiled"},
     {"hc_gemm_tiled_bf16", "gemm_tiled"},
     {"hc_gemm_tiled_w8a16", "gemm_tiled"},
@@ -361,8 +362,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->reduceVariant = value; // 1: persistent grid for the warp-per-row kernel
     return 0;
   }
-  if (std::strcmp(name, "tiled_variant") == 0 && value >= 0 && value <= 1) {
-    c->tiledVariant = value; // 1: never use the cp.async pipelined fp32 kernel
+  if (std::strcmp(name, "tiled_variant") == 0 && value >= 0 && value <= 2) {
+    // 1: never use the cp.async pipelined fp32 kernel; 2: use it, but never
+    // split K over a cluster.
+    c->tiledVariant = value;
     return 0;
   }
   if (std::strcmp(name, "mapped_stack") == 0 && value >= 0 && value <= 1) {
@@ -655,10 +658,18 @@ int hcGemmTiled(HcContext c, const void *a, const void *b, void *out,
   // fp32 operands that 16-byte cp.async can fetch take the pipelined variant
   // (3 stages of a 64x36 A block and a 32x68 B block of floats).
   if (dtype == HC_F32 && K > 0 && c->tiledVariant != 1 && lda % 4 == 0 &&
-      ldb % 4 == 0 && aligned(a, 16) && aligned(b, 16))
+      ldb % 4 == 0 && aligned(a, 16) && aligned(b, 16)) {
+    const size_t smem = 3 * (64 * 36 + 32 * 68) * sizeof(float);
+    const long long tiles = ceilDiv(N, 64) * ceilDiv(M, 64);
+    // Few tiles and a K loop worth splitting: a cluster of four CTAs per tile,
+    // each summing a quarter of K (gemm_tiled.cu), as long as the clusters of
+    // all tiles can be resident at once.
+    if (c->tiledVariant != 2 && c->ccMajor >= 9 && K >= 4 * 32 && tiles * 4 <= c->smCount)
+      return c->launch("hc_gemm_tiled_f32_splitk", size_t(ceilDiv(N, 64)),
+                       size_t(ceilDiv(M, 64)), 4, 256, args, 9, smem);
     return c->launch("hc_gemm_tiled_f32_async", size_t(ceilDiv(N, 64)),
-                     size_t(ceilDiv(M, 64)), 1, 256, args, 9,
-                     3 * (64 * 36 + 32 * 68) * sizeof(float));
+                     size_t(ceilDiv(M, 64)), 1, 256, args, 9, smem);
+  }
   return c->launch(name, size_t(ceilDiv(N, 64)), size_t(ceilDiv(M, 64)), 1, 256,
                    args, 9, 0);
 }

@@ -31,7 +31,8 @@ from .kernel_api import TunableParam, UnsupportedKernel
 
 # Native options worth trying, per recognised family.
 _VARIANTS = {
-    "gemm": [{"gemm_variant": 1}, {"gemm_variant": 2}, {"tiled_variant": 1}, {}],
+    "gemm": [{"gemm_variant": 1}, {"gemm_variant": 2}, {"tiled_variant": 1}, {"tiled_variant": 2},
+             {}],
     "gemm_w8a16": [{"gemm_variant": 1}, {"gemm_variant": 2}],
     "softmax_rows": [{"softmax_variant": 1}, {"softmax_variant": 2}],
 }

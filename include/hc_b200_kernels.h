@@ -83,7 +83,9 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
                                       int observedRet[2]);
 
 /* Tuning and test switches.  "gemm_variant": 0 = automatic, 1 = one CTA per
- * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel.  "mapped_stack":
+ * tile, 2 = CTA pair per tile, 3 = CUDA-core tiled kernel.  "tiled_variant"
+ * (fp32 hcGemmTiled): 0 = automatic, 1 = no cp.async pipeline, 2 = pipeline
+ * but no split of K over a cluster.  "mapped_stack":
  * 0 = hcMappedGemm stacks work-groups that share their f tile, 1 = one
  * work-group per CTA. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);

@@ -253,9 +253,12 @@ def test_gemm_tiled_f32_shapes(hc, shape):
     _gemm_f32_check(a, b, d_c.cpu().numpy(), expect)
 
 
-@pytest.mark.parametrize("variant", [0, 1])  # 0: cp.async pipeline when legal, 1: never
+# 0: cp.async pipeline when legal, K split over a four-CTA cluster when there are
+# few tiles and K >= 128; 1: neither; 2: the pipeline without the split.
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("shape", [(256, 256, 256), (70, 44, 36), (130, 68, 100), (64, 64, 4),
-                                   (1, 4, 8), (200, 260, 1028)])
+                                   (1, 4, 8), (200, 260, 1028), (64, 64, 128), (65, 124, 132),
+                                   (300, 380, 516), (37, 8, 4100), (64, 64, 160)])
 def test_gemm_tiled_f32_pipelined_and_plain_agree(hc, variant, shape):
     m, n, k = shape
     rng = np.random.default_rng(m + n + k)
