@@ -475,9 +475,10 @@ def run_gpu(args):
         h_ins = [t.cpu().pin_memory() for t in ins]
         h_outs = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
 
-        if name in ("softmax", "reduce"):
-            # Row-wise workloads have a host-buffer entry point that streams row
-            # chunks through the GPU (upload, kernel and download overlapped).
+        if name in ("softmax", "reduce", "gemm_bf16"):
+            # Row-wise workloads (and the rows of A in a GEMM) have a host-buffer
+            # entry point that streams row chunks through the GPU (upload,
+            # kernel and download overlapped).
             from hc_b200 import host as hc_host
 
             del ins, outs  # the pipeline brings its own device slots
@@ -486,8 +487,10 @@ def run_gpu(args):
                 with torch.cuda.stream(stream):
                     if name == "softmax":
                         hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
-                    else:
+                    elif name == "reduce":
                         hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
+                    else:
+                        hc_host.gemm_host(h_ins[0], h_ins[1], h_outs[0], desc)
         else:
             call = public_call(name, ins, outs)
 

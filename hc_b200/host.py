@@ -150,6 +150,41 @@ def reduce_rows_host(x_host, sum_host, max_host, device="cuda:0", chunk_rows=Non
         [x_host], [sum_host, max_host])
 
 
+_resident = {}
+
+
+def gemm_host(a_host, b_host, out_host, device="cuda:0", chunk_rows=None, group_shape=(256, 256)):
+    """``out = a @ b`` for host matrices a [M, K], b [K, N], out [M, N] (one
+    dtype: bfloat16, float32 or float64).  ``b`` is uploaded whole, then row
+    blocks of ``a`` stream through: upload of block i+1, product of block i and
+    download of block i-1 overlap.  Row blocks of a product are independent; in
+    bfloat16 the result is bit for bit that of one launch on the whole
+    matrices, in float32 the CUDA-core kernel may split K differently for a row
+    block than for the whole matrix, so low-order bits can differ."""
+    if (a_host.dim() != 2 or b_host.dim() != 2 or a_host.shape[1] != b_host.shape[0]
+            or tuple(out_host.shape) != (a_host.shape[0], b_host.shape[1])):
+        raise ValueError("gemm_host: expected a [M, K], b [K, N], out [M, N]")
+    if not a_host.dtype == b_host.dtype == out_host.dtype:
+        raise ValueError("gemm_host: a, b and out must have one dtype")
+    k = _kernels(device)
+    pipe = _pipeline(device, chunk_rows or _default_chunk_rows(a_host))
+    # One device copy of b per (device, shape, dtype), refilled on every call.
+    key = (device, tuple(b_host.shape), b_host.dtype)
+    b_dev = _resident.get(key)
+    if b_dev is None:
+        b_dev = _resident[key] = torch.empty(b_host.shape, dtype=b_host.dtype, device=pipe.dev)
+    caller = torch.cuda.current_stream(pipe.dev)
+    # The kernels of an earlier call may still read b on the kernel stream.
+    pipe.s_up.wait_stream(caller)
+    pipe.s_up.wait_stream(pipe.s_kernel)
+    with torch.cuda.stream(pipe.s_up):
+        b_dev.copy_(b_host, non_blocking=True)
+    # The row uploads follow b on the upload stream, and every kernel waits for
+    # its row upload, so b is in place before the first product starts.
+    pipe.run(lambda ins, outs: k.dot_fullk(ins[0], b_dev, outs[0], group_shape),
+             [a_host], [out_host])
+
+
 def synchronize(device="cuda:0"):
     """Block until everything queued by the host entry points has finished."""
     torch.cuda.synchronize(torch.device("cuda", get_context(device).ordinal))

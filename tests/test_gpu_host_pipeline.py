@@ -36,6 +36,33 @@ def test_softmax_rows_host_equals_single_launch(pinned, rows, cols, chunk):
     assert np.all(np.abs(hy.numpy() - expect) <= 1e-6 + 1e-5 * np.abs(expect))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gemm_host_equals_single_launch(dtype):
+    m, k, n = 600, 256, 384
+    a, b = oracle.make_inputs("gemm_bf16", shape=(m, n, k))  # bf16-exact float32 values
+    ha, hb = torch.from_numpy(a).to(dtype).pin_memory(), torch.from_numpy(b).to(dtype).pin_memory()
+    hc_out = torch.zeros((m, n), dtype=dtype).pin_memory()
+    kernels = make_kernels("cuda:0")
+    d_out = torch.zeros((m, n), dtype=dtype, device="cuda")
+    kernels.dot_fullk(ha.cuda(), hb.cuda(), d_out, (256, 256))
+    for _ in range(2):  # the second call reuses the resident copy of b and the slots
+        hc_out.zero_()
+        hc_host.gemm_host(ha, hb, hc_out, "cuda:0", chunk_rows=250)
+        hc_host.synchronize("cuda:0")
+        if dtype == torch.bfloat16:
+            assert torch.equal(hc_out, d_out.cpu())  # same tcgen05 kernel, same sum order
+        else:
+            # A row block has few tiles, so its K loop may be split over a cluster
+            # where the whole matrix is not: equal up to summation order.
+            assert torch.allclose(hc_out, d_out.cpu(), rtol=1e-5, atol=1e-6)
+    expect = a.astype(np.float64) @ b.astype(np.float64)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert np.all(np.abs(hc_out.double().numpy() - expect)
+                  <= tol * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)) + 1e-30)
+    with pytest.raises(ValueError, match="expected a"):
+        hc_host.gemm_host(ha, hb[:10], hc_out, "cuda:0")
+
+
 def test_reduce_rows_host_matches_oracle():
     rows, cols = 3000, 1024
     (x,) = oracle.make_inputs("reduce", shape=(rows, cols))
