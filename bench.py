@@ -130,7 +130,8 @@ NCU_TRAFFIC = {
     "softmax": 848.4e6,
     # profiles/reduce_rows_warp_f32_16384x8192.md: (536.89 + 3.88) MB for a quarter of the rows.
     "reduce": 2163.1e6,
-    "gemm_bf16": None,
+    # profiles/gemm_bf16_umma_pair_2048.md, full-size section: 1418.1 MB read + 128.5 MB written.
+    "gemm_bf16": 1546.6e6,
     "gemm_w8a16": None,
     "gemm_f32": None,
     "conv": None,
