@@ -583,10 +583,12 @@ int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f
   const HcMappedOperand *ops[3] = {x, f, out};
   const char *names[3] = {"x", "f", "out"};
   for (int i = 0; i < 3; ++i) {
-    const bool used = i == 2 || K > 0; // with K == 0 the operands are never read
-    if (!used)
-      continue;
-    if (!ops[i]->base || !ops[i]->map || !ops[i]->lin || !ops[i]->origins)
+    // The tile origins are read for every operand; with K == 0 the elements and
+    // the element tables of x and f are not (their tiles are empty).
+    const bool elementsUsed = i == 2 || K > 0;
+    if (!ops[i]->origins)
+      return c->fail("hcMappedGemm: null origins table in %s", names[i]);
+    if (elementsUsed && (!ops[i]->base || !ops[i]->map || !ops[i]->lin))
       return c->fail("hcMappedGemm: null buffer or table in %s", names[i]);
     if (!aligned(ops[i]->map, 16) || !aligned(ops[i]->origins, 16))
       return c->fail("hcMappedGemm: tables of %s are not 16-byte aligned", names[i]);

@@ -224,4 +224,18 @@ def test_mapped_gemm_through_the_c_abi(hc):
     with pytest.raises(RuntimeError, match="not 16-byte aligned"):
         hc.mapped_gemm(ops[0], ops[1], bad, groups, tm, n + 2, k, capi.HC_F64)
     hc.mapped_gemm(ops[0], ops[1], ops[2], 0, tm, n + 2, k, capi.HC_F64)  # no groups: no-op
+    # K == 0: empty operand tiles (their element tables may be absent), the
+    # products are empty sums, so every mapped output element becomes zero.
+    d_out.fill_(-1.0)
+    empty_x, empty_f = _operand(d_x, *tables[0]), _operand(d_f, *tables[1])
+    for op in (empty_x, empty_f):
+        op.map, op.lin = None, None
+    hc.mapped_gemm(empty_x, empty_f, ops[2], groups, tm, n + 2, 0, capi.HC_F64)
+    finish(hc)
+    zeros = np.full((m, n), -1.0)
+    zeros[1:] = 0.0
+    assert np.array_equal(d_out.cpu().numpy(), zeros)
+    empty_x.origins = None
+    with pytest.raises(RuntimeError, match="null origins"):
+        hc.mapped_gemm(empty_x, empty_f, ops[2], groups, tm, n + 2, 0, capi.HC_F64)
     assert ctypes.sizeof(capi.HcMappedOperand) == 120
