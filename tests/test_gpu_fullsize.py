@@ -126,3 +126,53 @@ def test_config5_w8a16_4096x8192x8192(hc):
     finish(hc)
     assert torch.equal(d_part[:, 1024:2048].contiguous().view(torch.int16),
                        d_c[:, 1024:2048].contiguous().view(torch.int16))
+
+
+def test_conv_benchmark_shape_properties():
+    """The implicit-GEMM convolution at the shape bench.py measures (a 3x3 layer,
+    32 x 64 x 56 x 56 images, 64 filters): against the oracle on a sample of
+    output positions, against float64 sums of the same products, and through
+    properties that hold at any size - the result scales exactly with a power
+    of two, and an image alone gives bit for bit what it gives inside the batch
+    (tiles of other images never leak into it)."""
+    from hc_b200.hckernel.kernel import sym
+    from hc_b200.workloads import make_conv
+
+    x_shape, f_shape, stride = (32, 64, 56, 56), (64, 64, 3, 3), 1
+    x, f = oracle.make_conv_inputs(x_shape, f_shape, "float32", seed=21)
+    conv = make_conv(stride).parametrize({sym.TN: 32, sym.TNF: 64, sym.KB: 16})
+    d_x, d_f = torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda()
+    out_shape = oracle.conv_out_shape(x_shape, f_shape, stride)
+    d_out = torch.full(out_shape, float("nan"), device="cuda")
+    conv(d_x, d_f, d_out)
+    torch.cuda.synchronize()
+    assert not torch.isnan(d_out).any()  # every output element was written
+
+    # Sampled positions against exact float64 sums of the same products.
+    got = d_out.cpu().numpy()
+    rng = np.random.default_rng(0)
+    for _ in range(64):
+        n, q = rng.integers(0, 32), rng.integers(0, 64)
+        i, j = rng.integers(0, out_shape[2]), rng.integers(0, out_shape[3])
+        patch = x[n, :, i:i + 3, j:j + 3].astype(np.float64)
+        terms = patch * f[q].astype(np.float64)
+        assert abs(got[n, q, i, j] - terms.sum()) <= 1e-5 * np.abs(terms).sum()
+
+    # The oracle on a corner of the problem small enough for it: 2 images, 8
+    # filters, a 6x6 window of the image (4x4 output positions).
+    sub_x, sub_f = np.ascontiguousarray(x[:2, :, :6, :6]), np.ascontiguousarray(f[:8])
+    expect = np.zeros((2, 8, 4, 4), np.float32)
+    oracle.conv_implicit_gemm(sub_x, sub_f, expect, stride, 2, 8, 16)
+    np.testing.assert_allclose(got[:2, :8, :4, :4], expect, rtol=1e-4, atol=1e-4)
+
+    # Scaling the filters by two scales every output by exactly two.
+    d_twice = torch.empty_like(d_out)
+    conv(d_x, d_f * 2, d_twice)
+    torch.cuda.synchronize()
+    assert torch.equal(d_twice, d_out * 2)
+
+    # One image alone (ragged tile: 1 of 32 rows real) equals its slice of the batch.
+    d_one = torch.empty((1,) + out_shape[1:], device="cuda")
+    conv(d_x[5:6].contiguous(), d_f, d_one)
+    torch.cuda.synchronize()
+    assert torch.equal(d_one[0], d_out[5])
