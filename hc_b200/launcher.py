@@ -117,6 +117,13 @@ class ShardedLauncher:
         if w_shard.shape[1]:
             self.kernels.dequant_dot(a_full, w_shard, scale_shard, out_shard, group)
 
+    def conv_images(self, conv, x_shard, f_full, out_shard):
+        """Batch-sharded convolution: this rank's images against the replicated
+        filters; ``conv`` is a kernel from :func:`hc_b200.workloads.make_conv`.
+        Output images are independent, so ``gather_rows`` assembles the result."""
+        if x_shard.shape[0]:
+            conv(x_shard, f_full, out_shard)
+
     # -- the one collective: gather the output ------------------------------------------
     def gather_rows(self, shard, full):
         """All-gather row shards (``partition`` order) into ``full`` on every rank."""

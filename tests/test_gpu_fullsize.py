@@ -1,4 +1,5 @@
-"""Full-size parity: the five benchmark configurations at their real shapes.
+"""Full-size parity: the five benchmark configurations at their real shapes
+(and the convolution at the shape bench.py measures it on).
 
 The CPU oracle cannot redo 10^12 flops in a test, so each configuration is
 checked (a) against the oracle on a sample of rows, computed from the same

@@ -88,6 +88,22 @@ def _worker(rank, world, port, results):
         mag = np.abs(a) @ (np.abs(w.astype(np.float32)) * s)
         ok["dequant_cols"] = bool(np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect) + 1e-4 * mag))
 
+        from hc_b200.workloads import make_conv
+
+        x_shape, f_shape = (11, 4, 9, 9), (12, 4, 3, 3)  # 6 + 5 images
+        x, f = oracle.make_conv_inputs(x_shape, f_shape, "float32")
+        out_shape = oracle.conv_out_shape(x_shape, f_shape, 1)
+        span = L.rows(x_shape[0])
+        x_s = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        f_d = torch.from_numpy(f).to(dev)  # replicated
+        o_s = torch.zeros((span.size,) + out_shape[1:], device=dev)
+        L.conv_images(make_conv(1, f"cuda:{rank}"), x_s, f_d, o_s)
+        o_full = torch.empty(out_shape, device=dev)
+        L.gather_rows(o_s, o_full)
+        expect = np.zeros(out_shape, np.float32)
+        oracle.conv_implicit_gemm(x, f, expect, 1)
+        ok["conv_images"] = bool(np.allclose(o_full.cpu().numpy(), expect, rtol=1e-5, atol=1e-5))
+
         ok["status"] = get_context(f"cuda:{rank}").kernel_status() == 0
         results[rank] = ok
     finally:
