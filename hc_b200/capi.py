@@ -51,6 +51,23 @@ class HcMappedOperand(C.Structure):
     ]
 
 
+class HcMapProgram(C.Structure):
+    """include/hc_b200_kernels.h: the arrays and the program of hcMapElements."""
+
+    _fields_ = [
+        ("inputs", _vp * 4),
+        ("inPitch", _ll * 4),
+        ("out", _vp),
+        ("outPitch", _ll),
+        ("rows", _ll),
+        ("cols", _ll),
+        ("nInputs", C.c_int),
+        ("nInstr", C.c_int),
+        ("code", C.c_uint * 32),
+        ("consts", C.c_double * 8),
+    ]
+
+
 # name -> (restype, argtypes), exactly as declared in include/offload_api.h
 OL_PROTOTYPES = {
     "olCreateDevice": (_vp, [C.c_char_p, OlErrorCallback, _vp]),
@@ -116,6 +133,7 @@ KERNELS_PROTOTYPES = {
     "hcPairwiseDistance": (
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]
     ),
+    "hcMapElements": (C.c_int, [_vp, C.POINTER(HcMapProgram), C.c_int]),
     "hcMappedGemm": (
         C.c_int,
         [_vp, C.POINTER(HcMappedOperand), C.POINTER(HcMappedOperand),
@@ -284,6 +302,10 @@ class Context:
             self.lib.hcPairwiseDistance(self.handle, a, b, out, m, n, d, lda, ldb, ldo, dtype),
             "hcPairwiseDistance",
         )
+
+    def map_elements(self, program, dtype=HC_F32):
+        """``program``: :class:`HcMapProgram`."""
+        self._check(self.lib.hcMapElements(self.handle, C.byref(program), dtype), "hcMapElements")
 
     def mapped_gemm(self, x, f, out, groups, tm, tn, k, dtype=HC_F32):
         """``x``, ``f``, ``out``: :class:`HcMappedOperand`."""

@@ -198,6 +198,49 @@ void pairwiseDistance(Context &ctx, py::handle a, py::handle b, py::handle out) 
             "pairwise_distance");
 }
 
+// Element-wise expression over matrices (or vectors) of one shape and type:
+// `inputs` a list of up to four arrays, `code` and `consts` the program
+// (include/hc_b200_kernels.h: HcMapProgram).
+void mapElements(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
+                 const std::vector<double> &consts) {
+  auto ins = py::cast<py::list>(inputs);
+  if (ins.size() > 4)
+    throw py::value_error("map_elements: at most 4 input arrays");
+  if (code.empty() || code.size() > 32 || consts.size() > 8)
+    throw py::value_error("map_elements: 1..32 instructions and at most 8 constants");
+  ArrayArg o;
+  try {
+    o = hc::arrayFromPython(out);
+  } catch (const std::exception &e) {
+    throw py::type_error(std::string("out: ") + e.what());
+  }
+  const int rank = o.rank();
+  if (rank != 1 && rank != 2)
+    throw py::value_error("map_elements: vectors or matrices expected");
+  ArrayArg O = deviceArray(ctx, out, "out", rank);
+  HcMapProgram p{};
+  auto rows = [&](const ArrayArg &a) { return rank == 2 ? a.shape[0] : 1; };
+  auto cols = [&](const ArrayArg &a) { return a.shape[rank - 1]; };
+  auto rowPitch = [&](const ArrayArg &a) { return rank == 2 ? pitch(a) : a.shape[0]; };
+  p.out = O.data;
+  p.outPitch = rowPitch(O);
+  p.rows = rows(O);
+  p.cols = cols(O);
+  p.nInputs = int(ins.size());
+  for (int k = 0; k < p.nInputs; ++k) {
+    const std::string name = "input " + std::to_string(k);
+    ArrayArg a = deviceArray(ctx, ins[k], name.c_str(), rank);
+    sameKind(a, O, name.c_str(), "out");
+    sameShape(a, O, name.c_str(), "out");
+    p.in[k] = a.data;
+    p.inPitch[k] = rowPitch(a);
+  }
+  p.nInstr = int(code.size());
+  std::copy(code.begin(), code.end(), p.code);
+  std::copy(consts.begin(), consts.end(), p.consts);
+  ctx.check(hcMapElements(ctx.get(), &p, floatDType(O, "out")), "map_elements");
+}
+
 // One operand of the gathered tile product: the array (any rank up to 4, any
 // non-negative strides) and its tables (map int32 [E,4], lin int32 [E],
 // origins int32 [G,4], lo and hi as 4 ints each, whether map/lin are in
@@ -368,6 +411,8 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
   m.def("pairwise_distance", &pairwiseDistance, py::arg("ctx"), py::arg("a"), py::arg("b"),
         py::arg("out"));
+  m.def("map_elements", &mapElements, py::arg("ctx"), py::arg("inputs"), py::arg("out"),
+        py::arg("code"), py::arg("consts"));
   m.def("mapped_gemm", &mappedGemm, py::arg("ctx"), py::arg("x"), py::arg("x_tables"),
         py::arg("f"), py::arg("f_tables"), py::arg("out"), py::arg("out_tables"),
         py::arg("groups"), py::arg("tm"), py::arg("tn"), py::arg("k"));

@@ -1,0 +1,43 @@
+// Parameter block of the element-wise expression kernel (map_elements.cu),
+// shared by the kernel and by the host code that fills it.
+#pragma once
+
+#include <stdint.h>
+
+// The expression is a program for a one-accumulator machine with three
+// temporaries.  An instruction is `op | (src << 8)`; binary operations combine
+// the accumulator with the operand `src` names.
+enum HcMapOp : uint32_t {
+  HC_MAP_LOAD = 0,  // acc = v
+  HC_MAP_ADD = 1,   // acc = acc + v
+  HC_MAP_SUB = 2,   // acc = acc - v
+  HC_MAP_RSUB = 3,  // acc = v - acc
+  HC_MAP_MUL = 4,   // acc = acc * v
+  HC_MAP_DIV = 5,   // acc = acc / v
+  HC_MAP_RDIV = 6,  // acc = v / acc
+  HC_MAP_MAX = 7,   // acc = max(acc, v), NaN if either is NaN
+  HC_MAP_MIN = 8,   // acc = min(acc, v), NaN if either is NaN
+  HC_MAP_NEG = 9,   // acc = -acc
+  HC_MAP_ABS = 10,  // acc = |acc|
+  HC_MAP_EXP = 11,  // acc = exp(acc)
+  HC_MAP_SQRT = 12, // acc = sqrt(acc)
+  HC_MAP_SAVE0 = 13, // t0 = acc
+  HC_MAP_SAVE1 = 14, // t1 = acc
+  HC_MAP_SAVE2 = 15, // t2 = acc
+  HC_MAP_OP_COUNT = 16
+};
+
+// Operand names: inputs 0..3, temporaries t0..t2, constants 0..7.
+constexpr uint32_t HC_MAP_SRC_INPUT = 0, HC_MAP_SRC_TEMP = 4, HC_MAP_SRC_CONST = 8;
+constexpr int HC_MAP_MAX_INPUTS = 4, HC_MAP_MAX_CONSTS = 8, HC_MAP_MAX_INSTR = 32;
+
+struct HcMapProgramDev {
+  const void *in[HC_MAP_MAX_INPUTS];
+  int64_t inPitch[HC_MAP_MAX_INPUTS]; // in elements
+  void *out;
+  int64_t outPitch;
+  int64_t rows, cols;
+  int32_t nInputs, nInstr;
+  uint32_t code[HC_MAP_MAX_INSTR];
+  double consts[HC_MAP_MAX_CONSTS];
+};

@@ -9,6 +9,7 @@
 // entry point that validates its arguments and chooses a kernel variant.
 #include "hc_b200_kernels.h"
 
+#include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
 
 #include <cuda.h> // CUtensorMap (type only; no driver call is made here)
@@ -48,6 +49,10 @@ struct KernelEntry {
 // Which image defines which kernel.
 const KernelEntry kKernelTable[] = {
     {"hc_copy2d", "copy2d"},
+    {"hc_map_elements_f32_v4", "map_elements"},
+    {"hc_map_elements_f32_v1", "map_elements"},
+    {"hc_map_elements_f64_v2", "map_elements"},
+    {"hc_map_elements_f64_v1", "map_elements"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
     {"hc_softmax_rows_f32_w4", "softmax_rows"},
@@ -409,6 +414,95 @@ int hcCopy2D(HcContext c, const void *src, void *dst, long long rows,
   long long gy = std::min<long long>(rows, std::max<long long>(1, c->smCount * 8 / gx));
   void *args[] = {&src, &dst, &rows, &rowBytes, &sp, &dp, &packet};
   return c->launch("hc_copy2d", size_t(gx), size_t(gy), 1, 256, args, 7, 0);
+}
+
+// ---- element-wise expressions -------------------------------------------------------
+static_assert(sizeof(HcMapProgram) == sizeof(HcMapProgramDev) &&
+                  offsetof(HcMapProgram, out) == offsetof(HcMapProgramDev, out) &&
+                  offsetof(HcMapProgram, rows) == offsetof(HcMapProgramDev, rows) &&
+                  offsetof(HcMapProgram, nInputs) == offsetof(HcMapProgramDev, nInputs) &&
+                  offsetof(HcMapProgram, code) == offsetof(HcMapProgramDev, code) &&
+                  offsetof(HcMapProgram, consts) == offsetof(HcMapProgramDev, consts),
+              "public program description and kernel parameter block differ");
+
+int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcMapElements: unsupported dtype %d", dtype);
+  if (!program)
+    return c->fail("hcMapElements: null program");
+  HcMapProgramDev p;
+  std::memcpy(&p, program, sizeof p);
+  if (p.nInputs < 0 || p.nInputs > HC_MAP_MAX_INPUTS || p.nInstr < 1 ||
+      p.nInstr > HC_MAP_MAX_INSTR)
+    return c->fail("hcMapElements: %d inputs, %d instructions (at most %d and 1..%d)", p.nInputs,
+                   p.nInstr, HC_MAP_MAX_INPUTS, HC_MAP_MAX_INSTR);
+  // Check the program before it reaches the GPU: known operations, operands
+  // that exist, temporaries written before they are read, and a first
+  // instruction that sets the accumulator.
+  bool saved[3] = {false, false, false};
+  for (int pc = 0; pc < p.nInstr; ++pc) {
+    const uint32_t op = p.code[pc] & 0xffu, src = p.code[pc] >> 8;
+    if (op >= HC_MAP_OP_COUNT)
+      return c->fail("hcMapElements: unknown operation %u at instruction %d", op, pc);
+    if (pc == 0 && op != HC_MAP_LOAD)
+      return c->fail("hcMapElements: the first instruction must load the accumulator");
+    if (op <= HC_MAP_MIN) {
+      const bool input = src < uint32_t(p.nInputs);
+      const bool temp = src >= HC_MAP_SRC_TEMP && src < HC_MAP_SRC_TEMP + 3 &&
+                        saved[src - HC_MAP_SRC_TEMP];
+      const bool constant =
+          src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + HC_MAP_MAX_CONSTS;
+      if (!input && !temp && !constant)
+        return c->fail("hcMapElements: instruction %d reads operand %u, which does not exist "
+                       "or is not written yet",
+                       pc, src);
+    }
+    if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
+      saved[op - HC_MAP_SAVE0] = true;
+  }
+  if (p.rows < 0 || p.cols < 0 || p.outPitch < p.cols)
+    return c->fail("hcMapElements: invalid shape %lld x %lld", (long long)p.rows,
+                   (long long)p.cols);
+  for (int k = 0; k < p.nInputs; ++k)
+    if (p.inPitch[k] < p.cols)
+      return c->fail("hcMapElements: pitch of input %d is shorter than a row", k);
+  if (p.rows == 0 || p.cols == 0)
+    return 0;
+  if (!p.out)
+    return c->fail("hcMapElements: null output");
+  for (int k = 0; k < p.nInputs; ++k)
+    if (!p.in[k])
+      return c->fail("hcMapElements: null input %d", k);
+  const int elem = dtype == HC_F32 ? 4 : 8;
+  // Contiguous matrices are one long row.
+  bool flat = p.outPitch == p.cols;
+  for (int k = 0; k < p.nInputs; ++k)
+    flat = flat && p.inPitch[k] == p.cols;
+  if (flat) {
+    p.cols *= p.rows;
+    p.rows = 1;
+    p.outPitch = p.cols;
+    for (int k = 0; k < p.nInputs; ++k)
+      p.inPitch[k] = p.cols;
+  }
+  // 16-byte packets when every base, pitch and the row length allow it.
+  const int perPacket = 16 / elem;
+  bool wide = p.cols % perPacket == 0 && aligned(p.out, 16) &&
+              (p.rows == 1 || p.outPitch % perPacket == 0);
+  for (int k = 0; k < p.nInputs; ++k)
+    wide = wide && aligned(p.in[k], 16) && (p.rows == 1 || p.inPitch[k] % perPacket == 0);
+  const int v = wide ? perPacket : 1;
+  char name[40];
+  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d", dtype == HC_F32 ? "f32" : "f64", v);
+  const long long perRow = p.cols / v;
+  // One CTA per 512 packets of a row (two per thread); rows beyond 65535 and
+  // very long rows are walked by the kernel's strides.
+  long long gx = std::min<long long>(ceilDiv(perRow, 512), 1 << 20);
+  long long gy = std::min<long long>(p.rows, 65535);
+  void *args[] = {&p};
+  return c->launch(name, size_t(gx), size_t(gy), 1, 256, args, 1, 0);
 }
 
 // ---- softmax --------------------------------------------------------------------

@@ -1,0 +1,142 @@
+"""Element-wise kernel bodies: tiles loaded at one origin, combined element by
+element, stored at the same origin::
+
+    x, y = gr.work_offset
+    a_t = gr.load(a[x:, y:], shape=gr.shape)
+    b_t = gr.load(b[x:, y:], shape=gr.shape)
+    gr.store(out[x:, y:], np.maximum(a_t * 2.0 - b_t, 0.0))
+
+The reference compiles such a body to GPU code (its copy kernels are the
+degenerate case, python/hckernel/tests/test_e2e.py:57-136; tile arithmetic is
+python/hckernel/kernel_api.py:136-211).  There is no compiler here, so the
+recorded expression is translated into a short program for the one-accumulator
+machine that ``csrc/kernels/map_elements.cu`` interprets - three temporaries,
+up to four input arrays, eight constants, 32 instructions - and one launch on
+the whole arrays computes what all work-groups would.
+
+Translation: the right operand of a binary operation is taken straight from an
+input, a constant or a temporary whenever it is a leaf; when only the left one
+is a leaf the operation is emitted in its reversed form (``v - acc``,
+``v / acc``); when neither is, the right subtree is evaluated first and parked
+in a temporary.  An expression that needs more than three temporaries at once
+or more than 32 instructions is refused.
+"""
+
+from .kernel_api import Tile, UnsupportedKernel
+
+LOAD, ADD, SUB, RSUB, MUL, DIV, RDIV, MAX, MIN, NEG, ABS, EXP, SQRT, SAVE0 = range(14)
+SRC_TEMP, SRC_CONST = 4, 8
+MAX_INPUTS, MAX_CONSTS, MAX_INSTR, TEMPS = 4, 8, 32, 3
+
+_BINARY = {"add": (ADD, ADD), "sub": (SUB, RSUB), "mul": (MUL, MUL), "div": (DIV, RDIV),
+           "maximum": (MAX, MAX), "minimum": (MIN, MIN)}
+_UNARY = {"neg": NEG, "abs": ABS, "exp": EXP, "sqrt": SQRT}
+
+
+class MapProgram:
+    """The translated expression: which loads feed it (``inputs``, Tile nodes),
+    the instructions and the constants."""
+
+    def __init__(self, shape):
+        self.shape = tuple(shape)
+        self.inputs, self.code, self.consts = [], [], []
+        self._free = list(range(TEMPS))
+
+    def _leaf(self, node):
+        """Operand name of a leaf, or None for an inner node."""
+        if node.op == "load":
+            if node.shape != self.shape:
+                raise UnsupportedKernel(
+                    f"element-wise kernel: a tile of shape {node.shape} in an expression of shape "
+                    f"{self.shape} (broadcasting between tiles is not supported)")
+            for i, seen in enumerate(self.inputs):
+                if seen.key() == node.key():
+                    return i
+            if len(self.inputs) == MAX_INPUTS:
+                raise UnsupportedKernel(f"element-wise kernel: more than {MAX_INPUTS} input tiles")
+            self.inputs.append(node)
+            return len(self.inputs) - 1
+        if node.op in ("const", "alloc"):
+            value = float(node.args[0])
+            for i, seen in enumerate(self.consts):
+                # Bit-for-bit the same constant (so that 0.0 and -0.0 stay apart).
+                if seen == value and str(seen) == str(value):
+                    return SRC_CONST + i
+            if len(self.consts) == MAX_CONSTS:
+                raise UnsupportedKernel(f"element-wise kernel: more than {MAX_CONSTS} constants")
+            self.consts.append(value)
+            return SRC_CONST + len(self.consts) - 1
+        return None
+
+    def _emit(self, op, src=0):
+        if len(self.code) == MAX_INSTR:
+            raise UnsupportedKernel(f"element-wise kernel: more than {MAX_INSTR} operations")
+        self.code.append(op | (src << 8))
+
+    def evaluate(self, node):
+        """Append the instructions that leave the value of ``node`` in the accumulator."""
+        if not isinstance(node, Tile):
+            raise UnsupportedKernel(f"element-wise kernel: operand {node!r}")
+        src = self._leaf(node)
+        if src is not None:
+            self._emit(LOAD, src)
+        elif node.op in _UNARY:
+            self.evaluate(node.args[0])
+            self._emit(_UNARY[node.op])
+        elif node.op == "astype" and node.dtype == node.args[0].dtype:
+            self.evaluate(node.args[0])
+        elif node.op in _BINARY:
+            forward, reverse = _BINARY[node.op]
+            left, right = node.args
+            right_src = self._leaf(right)
+            if right_src is not None:
+                self.evaluate(left)
+                self._emit(forward, right_src)
+                return
+            left_src = self._leaf(left)
+            if left_src is not None:
+                self.evaluate(right)
+                self._emit(reverse, left_src)
+                return
+            self.evaluate(right)
+            if not self._free:
+                raise UnsupportedKernel("element-wise kernel: the expression needs more than "
+                                        f"{TEMPS} intermediate values at once")
+            temp = self._free.pop(0)
+            self._emit(SAVE0 + temp)
+            self.evaluate(left)
+            self._emit(forward, SRC_TEMP + temp)
+            self._free.insert(0, temp)
+        else:
+            raise UnsupportedKernel(
+                f"element-wise kernel: operation '{node.op}' has no element-wise form")
+
+
+def match_map(stores, counts, covers):
+    """``(program, destination view)`` when the single store of a body is an
+    element-wise expression of tiles loaded where it is stored, else None.
+    ``covers`` is the coverage check shared with the other families."""
+    if len(stores) != 1:
+        return None
+    dst, expr = stores[0]
+    if expr.op not in _BINARY and expr.op not in _UNARY and expr.op not in ("alloc", "astype"):
+        return None
+    if dst.buffer.ndim not in (1, 2) or len(expr.shape) != dst.buffer.ndim:
+        raise UnsupportedKernel("element-wise kernels are supported for vectors and matrices")
+    if dst.buffer.dtype not in ("float32", "float64"):
+        raise UnsupportedKernel(
+            f"element-wise kernels compute in float32 or float64, not {dst.buffer.dtype}")
+    program = MapProgram(expr.shape)
+    program.evaluate(expr)
+    for tile in program.inputs:
+        view = tile.args[0]
+        if view.buffer.shape != dst.buffer.shape or view.buffer.dtype != dst.buffer.dtype:
+            raise UnsupportedKernel(
+                f"element-wise kernel: {view.buffer.name} and {dst.buffer.name} differ in shape or "
+                f"element type")
+        if tuple(view.origin) != tuple(dst.origin):
+            raise UnsupportedKernel(
+                f"element-wise kernel: {view.buffer.name} is loaded at another origin than "
+                f"{dst.buffer.name} is stored")
+    covers(dst.origin, expr.shape, dst.buffer.shape, counts, "element-wise kernel")
+    return program, dst

@@ -37,6 +37,7 @@ import sympy
 
 from . import settings
 from .kernel_api import *  # noqa: F401,F403  (the reference re-exports kernel_api)
+from .elementwise import match_map
 from .mapped import match_mapped
 from .kernel_api import (
     Affine,
@@ -565,6 +566,12 @@ class KernelDispatcher:
                 plan = matcher(recorder.stores, counts)
                 if plan is not None:
                     return plan
+            found = match_map(recorder.stores, counts, _covers)
+            if found is not None:
+                program, dst = found
+                return _Plan("map_elements", out=dst.buffer.index,
+                             inputs=[tile.args[0].buffer.index for tile in program.inputs],
+                             code=list(program.code), consts=list(program.consts))
         raise UnsupportedKernel(
             f"{self.func.__name__}: the body matches none of the precompiled kernel families "
             f"(copy, row softmax, last-axis sum/max, whole-array sum, pairwise distance, GEMM, "
@@ -612,6 +619,9 @@ class KernelDispatcher:
             native.reduce_all(ctx, args[r["a"]], args[r["result"]])
         elif plan.family == "pairwise_distance":
             native.pairwise_distance(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
+        elif plan.family == "map_elements":
+            native.map_elements(ctx, [args[i] for i in r["inputs"]], args[r["out"]], r["code"],
+                                r["consts"])
         elif plan.family == "mapped_gemm":
             spec = r["spec"]
             x, f, out = args[r["x"]], args[r["f"]], args[r["out"]]

@@ -505,6 +505,18 @@ class Tile:
     def __truediv__(self, o): return self._binary("div", o)
     def __rtruediv__(self, o): return self._binary("div", o, True)
     def __matmul__(self, o): return _dot(self, o)
+    def __neg__(self): return self._unary("neg")
+    def __abs__(self): return self._unary("abs")
+
+    def _unary(self, op):
+        return Tile(op, (self,), self.shape, self.dtype)
+
+    def __pow__(self, exponent):
+        if exponent == 2:
+            return self * self
+        if exponent == 0.5:
+            return self._unary("sqrt")
+        raise UnsupportedKernel(f"tile ** {exponent!r}: only squares and square roots")
     # `acc += x` rebinds the name to the new node, like any immutable value.
     def __iadd__(self, o): return self._binary("add", o)
     def __isub__(self, o): return self._binary("sub", o)
@@ -575,10 +587,12 @@ class Tile:
         if method != "__call__" or kwargs.get("out") is not None:
             raise UnsupportedKernel(f"np.{ufunc.__name__}.{method} on a tile")
         names = {"add": "add", "subtract": "sub", "multiply": "mul", "true_divide": "div",
-                 "divide": "div"}
-        if ufunc.__name__ == "exp":
+                 "divide": "div", "maximum": "maximum", "minimum": "minimum"}
+        unary = {"exp": "exp", "sqrt": "sqrt", "absolute": "abs", "fabs": "abs",
+                 "negative": "neg"}
+        if ufunc.__name__ in unary:
             (x,) = inputs
-            return Tile("exp", (x,), x.shape, x.dtype)
+            return x._unary(unary[ufunc.__name__])
         if ufunc.__name__ in names:
             a, b = (Tile._wrap(v) for v in inputs)
             return a._binary(names[ufunc.__name__], b)

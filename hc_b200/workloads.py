@@ -91,6 +91,52 @@ def make_kernels(device="cuda:0"):
                                  dot_fullk=dot_fullk, dequant_dot=dequant_dot, device=device)
 
 
+def make_elementwise(fn, inputs=1, rank=2, group_shape=None, device="cuda:0"):
+    """An element-wise kernel ``k(a[, b[, c]], out)``: every work-group loads one
+    tile per input at its offset, stores ``fn`` of them at the same offset.
+    ``fn`` is written with operators and NumPy calls (``np.maximum``, ``np.exp``,
+    ``np.sqrt``, ``np.abs`` ...) on tiles, as in the reference's tile arithmetic
+    (python/hckernel/kernel_api.py:136-211)."""
+    target = dict(backend="nvvm", device=device)
+    W, H = sym.W, sym.H
+    if rank == 1:
+        if inputs != 1:
+            raise ValueError("vector kernels take one input here")
+
+        @kernel(work_shape=W, group_shape=group_shape and group_shape[0], **target)
+        def map1(gr: CurrentGroup, a: Buffer[W, DT], out: Buffer[W, DT]):
+            x = gr.work_offset[0]
+            gr.store(out[x:], fn(gr.load(a[x:], shape=gr.shape[0])))
+
+        return map1
+    if inputs == 1:
+        @kernel(work_shape=(W, H), group_shape=group_shape, **target)
+        def map2(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+            x, y = gr.work_offset
+            gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape)))
+
+        return map2
+    if inputs == 2:
+        @kernel(work_shape=(W, H), group_shape=group_shape, **target)
+        def map3(gr: CurrentGroup, a: Buffer[W, H, DT], b: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+            x, y = gr.work_offset
+            gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape),
+                                     gr.load(b[x:, y:], shape=gr.shape)))
+
+        return map3
+    if inputs == 3:
+        @kernel(work_shape=(W, H), group_shape=group_shape, **target)
+        def map4(gr: CurrentGroup, a: Buffer[W, H, DT], b: Buffer[W, H, DT], c: Buffer[W, H, DT],
+                 out: Buffer[W, H, DT]):
+            x, y = gr.work_offset
+            gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape),
+                                     gr.load(b[x:, y:], shape=gr.shape),
+                                     gr.load(c[x:, y:], shape=gr.shape)))
+
+        return map4
+    raise ValueError("one to three inputs")
+
+
 def make_conv(stride=1, device="cuda:0"):
     """The convolution written as an implicit GEMM, as in the reference's
     example (python/hckernel/tests/test_examples.py:203-252): ``conv(x, f, out)``

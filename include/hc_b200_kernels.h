@@ -97,6 +97,33 @@ HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
                          long long rows, long long cols, long long srcPitch,
                          long long dstPitch, int elemBytes);
 
+/* Element-wise expression: out[r,c] = f(in0[r,c], ..., in3[r,c]) over
+ * rows x cols matrices, HC_F32 or HC_F64 (all arrays one type).  What
+ * work-groups compute that load tiles at one origin, combine them element by
+ * element and store the result there - the reference's copy kernels
+ * (python/hckernel/tests/test_e2e.py:57-136) with tile arithmetic
+ * (python/hckernel/kernel_api.py:136-211) in between.  The reference compiles
+ * such a body; here f is data: a program for a machine with one accumulator and
+ * three temporaries.  An instruction is `op | (src << 8)`:
+ *   op   0 load  1 add  2 sub  3 rsub (v - acc)  4 mul  5 div  6 rdiv (v / acc)
+ *        7 max  8 min  9 neg  10 abs  11 exp  12 sqrt  13..15 save to t0..t2
+ *   src  0..3 input arrays, 4..6 temporaries t0..t2, 8..15 consts[0..7]
+ * max and min give NaN when either operand is NaN (NumPy's maximum/minimum);
+ * operations are never contracted into FMAs.  The value of the accumulator
+ * after the last instruction is stored.  Pitches are in elements. */
+typedef struct HcMapProgram {
+  const void *in[4];      /* device */
+  long long inPitch[4];
+  void *out;              /* device */
+  long long outPitch;
+  long long rows, cols;
+  int nInputs;            /* 0..4 */
+  int nInstr;             /* 1..32 */
+  unsigned code[32];
+  double consts[8];
+} HcMapProgram;
+HC_B200_API int hcMapElements(HcContext c, const HcMapProgram *program, int dtype);
+
 /* Row softmax over the last axis, HC_F32 or HC_F64
  * (python/hckernel/tests/test_examples.py:304-321). */
 HC_B200_API int hcSoftmaxRows(HcContext c, const void *x, void *y,

@@ -93,6 +93,54 @@ def load_tile(view: np.ndarray, shape) -> Tile:
     return Tile(data, valid)
 
 
+class ArithmeticTile:
+    """A tile as the reference's arithmetic sees it: a thin wrapper around a
+    ``numpy.ma`` array (python/hckernel/kernel_api.py:106-211).
+
+    Operators go to ``numpy.ma`` and give a wrapped tile again (:136-148,
+    :157-211; there are no reflected operators, so ``1.0 + tile`` is an error
+    there and here).  NumPy functions reach the masked array through
+    ``__array__`` (:150-151) and return a bare masked array, which ``store``
+    then treats as a plain array (:338-342).  Consequences kept on purpose:
+    a Python float operand becomes a float64 array inside ``numpy.ma``, so
+    ``tile_f32 * 2.0`` continues in float64 until it is stored.
+    """
+
+    def __init__(self, masked):
+        self.ma = masked
+
+    def __array__(self, dtype=None, copy=None):
+        return self.ma if dtype is None else self.ma.astype(dtype)
+
+    def _binary(self, other, op):
+        return ArithmeticTile(op(self.ma, other.ma if isinstance(other, ArithmeticTile) else other))
+
+    def __add__(self, other): return self._binary(other, np.ma.add)
+    def __sub__(self, other): return self._binary(other, np.ma.subtract)
+    def __mul__(self, other): return self._binary(other, np.ma.multiply)
+    def __truediv__(self, other): return self._binary(other, np.ma.true_divide)
+    def __neg__(self): return ArithmeticTile(-self.ma)
+    def __abs__(self): return ArithmeticTile(abs(self.ma))
+
+    def __getattr__(self, name):
+        return getattr(self.ma, name)
+
+
+def arithmetic_tile(tile: Tile) -> ArithmeticTile:
+    return ArithmeticTile(np.ma.masked_array(tile.data, mask=~tile.valid))
+
+
+def store_result(dst_view: np.ndarray, result) -> None:
+    """``group.store`` of whatever tile arithmetic produced: a wrapped tile
+    writes its unmasked elements only, anything else is assigned as it is
+    (python/hckernel/kernel_api.py:338-342)."""
+    if isinstance(result, ArithmeticTile):
+        mask = np.ma.getmaskarray(result.ma)
+        store_tile(dst_view, Tile(np.asarray(result.ma.data), ~mask))
+    else:
+        store_tile(dst_view, np.asarray(np.ma.getdata(result)))
+
+
 def alloc_tile(shape, dtype, fill=0) -> Tile:
     """``group.zeros/ones/full``: every element valid
     (python/hckernel/kernel_api.py:347-369, 433-434)."""

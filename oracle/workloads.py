@@ -18,6 +18,8 @@ import numpy as np
 
 from .hcsim import (
     alloc_tile,
+    arithmetic_tile,
+    store_result,
     ceil_div,
     iter_groups,
     load_tile,
@@ -208,6 +210,54 @@ def pairwise_distance(a, b, out, group_shape=(8, 8), mi: int = 1, ni: int = 1) -
         b_tile = load_tile(b[n0:, :], (n_block, d))
         diff = a_tile.data[:, None, :] - b_tile.data[None, :, :]
         store_tile(out[m0:, n0:], np.linalg.norm(diff, axis=2))
+
+
+# ---- element-wise bodies ------------------------------------------------------------
+def elementwise(fn, inputs, out, group_shape) -> None:
+    """A body that loads one tile per input at the group's offset, combines
+    them element by element with ``fn`` and stores the result at the same offset
+    (the reference's copy kernels with arithmetic in between:
+    python/hckernel/tests/test_e2e.py:57-136, tile arithmetic
+    python/hckernel/kernel_api.py:136-211).
+
+    The reference's tiles are ``numpy.ma`` arrays (kernel_api.py:106-155), and
+    that is kept here because it is visible in the results: ``numpy.ma``
+    turns a Python float operand into a float64 array, so ``tile_f32 + 1.0`` is
+    computed and carried on in float64 and only rounded to float32 when it is
+    stored (plain NumPy would stay in float32), and its division masks the
+    elements whose divisor is zero, which the masked store then leaves
+    unwritten.  The padding of edge tiles is masked from the start and dropped
+    by the store."""
+    group_shape = tuple(np.atleast_1d(group_shape).tolist())
+    for _, offset in iter_groups(out.shape, group_shape):
+        window = tuple(slice(o, None) for o in offset)
+        tiles = [arithmetic_tile(load_tile(a[window], group_shape)) for a in inputs]
+        with np.errstate(all="ignore"):
+            store_result(out[window], fn(*tiles))
+
+
+def elementwise_cases():
+    """``(name, fn, number of inputs, shape, dtype, group shape)`` of the
+    element-wise vectors stored under ``tests/golden``.  Every ``fn`` is written
+    with NumPy calls and operators only, so the same function object runs on
+    the reference simulator's tiles, on NumPy arrays and on recorded tiles."""
+    return [
+        ("map_relu_axpby_f32", lambda a, b: np.maximum(a * 2.0 - b, 0.0), 2, (111, 813), "float32",
+         (4, 16)),
+        ("map_mixed_f64",
+         lambda a, b: (a + b) / (np.sqrt(np.abs(a)) + 1.5) - np.minimum(a, b) * (-b),
+         2, (70, 45), "float64", (8, 8)),
+        ("map_gauss_f32", lambda a: np.exp(-(a * a)), 1, (33, 130), "float32", (16, 32)),
+        ("map_vector_f32", lambda a: a * a + 1.0, 1, (1000,), "float32", (64,)),
+        # (the reference's tiles have no reflected operators: `c * c + 1.0`, not `1.0 + c * c`)
+        ("map_three_inputs_f32", lambda a, b, c: (a - b) * (b - c) / (c * c + 1.0), 3, (64, 256),
+         "float32", (8, 64)),
+    ]
+
+
+def make_elementwise_inputs(count, shape, dtype, seed: int = 7):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal(shape).astype(dtype) for _ in range(count)]
 
 
 # ---- implicit-GEMM convolution (gathers through index mappings) ---------------------

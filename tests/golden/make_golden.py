@@ -202,6 +202,44 @@ def ref_conv(stride):
     return conv
 
 
+def ref_map(fn, count, rank, group):
+    """An element-wise body in the reference's DSL: one tile per input loaded at
+    the group's offset, ``fn`` of them stored at the same offset."""
+    W, H = sym.W, sym.H
+    if rank == 1:
+        @kernel(work_shape=W, group_shape=group[0])
+        def k1(gr: CurrentGroup, a: Buffer[W, DT], out: Buffer[W, DT]):
+            x = gr.work_offset[0]
+            gr.store(out[x:], fn(gr.load(a[x:], shape=gr.shape[0])))
+
+        return k1
+    if count == 1:
+        @kernel(work_shape=(W, H), group_shape=group)
+        def k2(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+            x, y = gr.work_offset
+            gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape)))
+
+        return k2
+    if count == 2:
+        @kernel(work_shape=(W, H), group_shape=group)
+        def k3(gr: CurrentGroup, a: Buffer[W, H, DT], b: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+            x, y = gr.work_offset
+            gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape),
+                                     gr.load(b[x:, y:], shape=gr.shape)))
+
+        return k3
+
+    @kernel(work_shape=(W, H), group_shape=group)
+    def k4(gr: CurrentGroup, a: Buffer[W, H, DT], b: Buffer[W, H, DT], c: Buffer[W, H, DT],
+           out: Buffer[W, H, DT]):
+        x, y = gr.work_offset
+        gr.store(out[x:, y:], fn(gr.load(a[x:, y:], shape=gr.shape),
+                                 gr.load(b[x:, y:], shape=gr.shape),
+                                 gr.load(c[x:, y:], shape=gr.shape)))
+
+    return k4
+
+
 def ref_copy():
     W, H = sym.W, sym.H
 
@@ -377,6 +415,21 @@ def main():
         if square and (x_shape[2] - f_shape[2]) % stride == 0:
             np.testing.assert_allclose(r, oracle.conv_direct(x, f, stride),
                                        rtol=1e-4 if dtype == "float32" else 1e-10, atol=1e-5)
+        out[name] = r
+
+    # 6. Element-wise bodies (tile arithmetic between a load and a store).
+    for name, fn, count, shape, dtype, group in oracle.elementwise_cases():
+        inputs = oracle.make_elementwise_inputs(count, shape, dtype)
+        r = np.zeros(shape, dtype)
+        with np.errstate(all="ignore"):
+            ref_map(fn, count, len(shape), group)(*inputs, r)
+        o = np.zeros(shape, dtype)
+        oracle.elementwise(fn, inputs, o, group)
+        same(name, r, o)
+        # Plain NumPy on whole arrays agrees up to the last bit or two: the
+        # reference's tiles carry Python-float operands on in float64 where
+        # NumPy arrays stay in float32.
+        np.testing.assert_allclose(r, fn(*inputs), rtol=3e-7 if dtype == "float32" else 0)
         out[name] = r
 
     np.savez_compressed(HERE / "reference_outputs.npz", **out)

@@ -1,0 +1,138 @@
+"""Element-wise bodies on CPU: the oracle against the reference simulator's
+outputs (bit for bit), and the front door - the recorded expression must be
+translated into a program for the accumulator machine of
+csrc/kernels/map_elements.cu that, run here in NumPy, gives exactly what NumPy
+gives for the same expression.  No kernel is launched."""
+
+import numpy as np
+import pytest
+
+from hc_b200.hckernel import elementwise as ew
+from hc_b200.hckernel.kernel import *  # noqa: F401,F403
+from hc_b200.hckernel.kernel import UnsupportedKernel
+from hc_b200.workloads import make_elementwise
+from oracle import workloads as oracle
+
+CASES = oracle.elementwise_cases()
+
+
+class FakeTensor:
+    def __init__(self, shape, dtype="float32"):
+        self.shape, self.dtype = tuple(shape), dtype
+
+
+F = FakeTensor
+
+
+def run_program(code, consts, inputs, dtype):
+    """The machine of map_elements.cu, one NumPy operation per instruction."""
+    dtype = np.dtype(dtype).type
+    acc, temps = None, [None, None, None]
+    with np.errstate(all="ignore"):
+        for ins in code:
+            op, src = ins & 0xFF, ins >> 8
+            if op <= ew.MIN:
+                v = (inputs[src] if src < 4 else temps[src - 4] if src < 8
+                     else dtype(consts[src - 8]))
+            if op == ew.LOAD:
+                acc = v if isinstance(v, np.ndarray) else np.full(inputs[0].shape, v, dtype)
+            elif op == ew.ADD: acc = acc + v
+            elif op == ew.SUB: acc = acc - v
+            elif op == ew.RSUB: acc = v - acc
+            elif op == ew.MUL: acc = acc * v
+            elif op == ew.DIV: acc = acc / v
+            elif op == ew.RDIV: acc = v / acc
+            elif op == ew.MAX: acc = np.maximum(acc, v)
+            elif op == ew.MIN: acc = np.minimum(acc, v)
+            elif op == ew.NEG: acc = -acc
+            elif op == ew.ABS: acc = np.abs(acc)
+            elif op == ew.EXP: acc = np.exp(acc)
+            elif op == ew.SQRT: acc = np.sqrt(acc)
+            else: temps[op - ew.SAVE0] = acc
+            assert acc.dtype == dtype
+    return acc
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c[0])
+def test_oracle_matches_the_reference_simulator(golden, case):
+    name, fn, count, shape, dtype, group = case
+    inputs = oracle.make_elementwise_inputs(count, shape, dtype)
+    out = np.zeros(shape, dtype)
+    oracle.elementwise(fn, inputs, out, group)
+    assert np.array_equal(out, golden[name])
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c[0])
+def test_recorded_expression_becomes_an_equivalent_program(golden, case):
+    name, fn, count, shape, dtype, group = case
+    k = make_elementwise(fn, count, len(shape), group)
+    plan = k.plan_for(tuple(F(shape, dtype) for _ in range(count + 1)))
+    assert plan.family == "map_elements"
+    # Program input k is call argument inputs[k] (numbered in order of first use).
+    assert sorted(plan.roles["inputs"]) == list(range(count)) and plan.roles["out"] == count
+    inputs = oracle.make_elementwise_inputs(count, shape, dtype)
+    got = run_program(plan.roles["code"], plan.roles["consts"],
+                      [inputs[i] for i in plan.roles["inputs"]], dtype)
+    with np.errstate(all="ignore"):
+        assert np.array_equal(got, fn(*inputs))  # the same IEEE operations, one by one
+    # ... and the reference's result up to its float64 detours (see oracle.elementwise).
+    np.testing.assert_allclose(got, golden[name], rtol=3e-7 if dtype == "float32" else 0)
+
+
+def test_translation_details():
+    a = make_elementwise(lambda t: (t + 1.0) * (t - 1.0) / ((t * t + 2.0) * (t + 3.0)), 1, 2, (4, 16))
+    plan = a.plan_for((F((8, 32)), F((8, 32))))
+    code, consts = plan.roles["code"], plan.roles["consts"]
+    assert consts == [3.0, 2.0, 1.0]  # in order of first use: right operands are evaluated first
+    ops = [c & 0xFF for c in code]
+    # Three products/quotients of two inner nodes each park one value; at most
+    # two are parked at once, so t2 is never needed.
+    assert (ops.count(ew.SAVE0), ops.count(ew.SAVE0 + 1), ops.count(ew.SAVE0 + 2)) == (2, 1, 0)
+    x = np.linspace(-2, 2, 256, dtype=np.float32).reshape(8, 32)
+    want = (x + np.float32(1)) * (x - np.float32(1)) / ((x * x + np.float32(2)) * (x + np.float32(3)))
+    assert np.array_equal(run_program(code, consts, [x], "float32"), want)
+    # Reversed forms: constant on the left of a non-commutative operation.
+    b = make_elementwise(lambda t: 1.0 / (2.0 - t * t), 1, 2, (4, 16))
+    code = b.plan_for((F((8, 32)), F((8, 32)))).roles["code"]
+    assert [c & 0xFF for c in code] == [ew.LOAD, ew.MUL, ew.RSUB, ew.RDIV]
+    # The same tile used twice is one input; squares and roots through **.
+    c = make_elementwise(lambda s, t: (s * s + t * t) ** 0.5, 2, 2, (4, 16))
+    plan = c.plan_for((F((8, 32)), F((8, 32)), F((8, 32))))
+    assert sorted(plan.roles["inputs"]) == [0, 1] and (plan.roles["code"][-1] & 0xFF) == ew.SQRT
+    # A constant tile: no inputs at all.
+    fill = make_elementwise(lambda t: t * 0.0 + 7.0, 1, 2, (4, 16))
+    assert fill.plan_for((F((8, 32)), F((8, 32)))).roles["inputs"] == [0]
+
+
+def test_bodies_outside_the_element_wise_family():
+    W, H, DT = sym.W, sym.H, typename.DT
+    target = dict(backend="nvvm", device="cuda:0")
+    with pytest.raises(UnsupportedKernel, match="np.tanh"):
+        make_elementwise(np.tanh, 1, 2, (4, 16)).plan_for((F((8, 32)), F((8, 32))))
+    with pytest.raises(UnsupportedKernel, match="float32 or float64"):
+        make_elementwise(lambda t: t + 1, 1, 2, (4, 16)).plan_for(
+            (F((8, 32), "int32"), F((8, 32), "int32")))
+
+    @kernel(work_shape=(W, H), group_shape=(4, 16), **target)
+    def shifted(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        x, y = gr.work_offset
+        gr.store(out[x:, y:], gr.load(a[x:, y + 1:], shape=gr.shape) * 2.0)
+
+    with pytest.raises(UnsupportedKernel, match="another origin"):
+        shifted.plan_for((F((8, 32)), F((8, 32))))
+
+    @kernel(work_shape=(W, H), group_shape=(4, 16), **target)
+    def row_broadcast(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        x, y = gr.work_offset
+        t = gr.load(a[x:, y:], shape=gr.shape)
+        gr.store(out[x:, y:], t - gr.load(a[x:, y:], shape=(gr.shape[0], 1)))
+
+    with pytest.raises(UnsupportedKernel, match="broadcasting between tiles"):
+        row_broadcast.plan_for((F((8, 32)), F((8, 32))))
+
+    def deep(t):  # needs four values parked at once
+        p = lambda u, v: (u + v) * (u - v)  # noqa: E731
+        return p(p(p(p(t, t * 2.0), p(t, t * 3.0)), p(p(t, t * 4.0), p(t, t * 5.0))), t)
+
+    with pytest.raises(UnsupportedKernel, match="more than|intermediate"):
+        make_elementwise(deep, 1, 2, (4, 16)).plan_for((F((8, 32)), F((8, 32))))

@@ -197,8 +197,17 @@ def test_bodies_outside_the_families_are_refused():
         t = gr.load(a[m0:, :], shape=(gr.shape[0], N))
         gr.store(out[m0:, :], t * t)
 
+    # Element-wise arithmetic is a family of its own (tests/test_elementwise_cpu.py).
+    assert squares.plan_for((F((32, 64)), F((32, 64)), 8)).family == "map_elements"
+
+    @kernel(work_shape=M, group_shape=GM, **TARGET)
+    def column_sums(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[N, DT], gshape: GM):
+        m0 = gr.work_offset[0]
+        t = gr.load(a[m0:, :], shape=(gr.shape[0], N))
+        gr.store(out, t.sum(axis=0))
+
     with pytest.raises(UnsupportedKernel, match="matches none"):
-        squares.plan_for((F((32, 64)), F((32, 64)), 8))
+        column_sums.plan_for((F((32, 64)), F((64,)), 8))
 
     @kernel(work_shape=M, group_shape=GM, **TARGET)
     def with_workitems(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):

@@ -1,0 +1,128 @@
+"""GPU parity of element-wise bodies: through the ``@kernel`` front door against
+the outputs of the reference simulator (tests/golden) and against NumPy, and
+hcMapElements called directly through the C-ABI.
+
+Tolerances: + - * / sqrt, max, min, abs and negation are single correctly
+rounded IEEE operations in the array's type, never contracted, so against
+NumPy on the same arrays the result is bit-exact; ``exp`` is within 4 ulp
+(expf is accurate to 2 ulp, NumPy's own exp to about 1).
+Against the reference simulator float32 results may differ in the last bits
+where the reference carries a Python-float operand on in float64
+(oracle.elementwise explains): 3e-7 relative."""
+
+import numpy as np
+import pytest
+import torch
+
+from hc_b200 import capi
+from hc_b200.hckernel import elementwise as ew
+from hc_b200.workloads import make_elementwise
+from oracle import workloads as oracle
+from tests.gpu_util import finish
+
+pytestmark = pytest.mark.gpu
+
+CASES = oracle.elementwise_cases()
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c[0])
+def test_element_wise_bodies_match_reference_and_numpy(golden, case):
+    name, fn, count, shape, dtype, group = case
+    inputs = oracle.make_elementwise_inputs(count, shape, dtype)
+    k = make_elementwise(fn, count, len(shape), group)
+    d_in = [torch.from_numpy(a).cuda() for a in inputs]
+    d_out = torch.full(shape, float("nan"), dtype=d_in[0].dtype, device="cuda")
+    k(*d_in, d_out)
+    torch.cuda.synchronize()
+    got = d_out.cpu().numpy()
+    with np.errstate(all="ignore"):
+        want = fn(*inputs)
+    if "gauss" in name:
+        np.testing.assert_array_max_ulp(got, want, maxulp=4)
+    else:
+        assert np.array_equal(got, want)
+    np.testing.assert_allclose(got, golden[name], rtol=3e-7 if dtype == "float32" else 2e-16)
+
+
+@pytest.mark.parametrize("shape,pitch", [((37, 101), 101), ((64, 256), 260), ((5, 8), 12),
+                                         ((1, 1), 1), ((300, 4), 4)])
+def test_unaligned_and_pitched_matrices(shape, pitch):
+    """Rows that are not multiples of 16 bytes, views with a pitch, tiny arrays."""
+    rng = np.random.default_rng(shape[0] * 1000 + shape[1])
+    a = rng.standard_normal(shape).astype(np.float32)
+    b = rng.standard_normal(shape).astype(np.float32)
+    k = make_elementwise(lambda s, t: np.minimum(s, t) / (np.abs(t) + 0.5), 2, 2, (8, 32))
+    store = torch.zeros((3, shape[0], pitch), device="cuda")
+    d_a, d_b, d_out = (store[i, :, : shape[1]] for i in range(3))
+    d_a.copy_(torch.from_numpy(a))
+    d_b.copy_(torch.from_numpy(b))
+    k(d_a, d_b, d_out)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_out.cpu().numpy(), np.minimum(a, b) / (np.abs(b) + np.float32(0.5)))
+    if pitch > shape[1]:  # the gap between rows is not touched
+        assert float(store[2, :, shape[1]:].abs().max()) == 0.0
+
+
+def test_nan_and_signed_zero_semantics():
+    """NumPy's maximum/minimum propagate NaN; abs and negation handle -0.0."""
+    a = np.array([[np.nan, 1.0, -0.0, 0.0, -2.0, np.inf, 3.0, np.nan]], np.float32)
+    b = np.array([[1.0, np.nan, 0.0, -0.0, 5.0, -np.inf, 3.0, np.nan]], np.float32)
+    for fn in (lambda s, t: np.maximum(s, t), lambda s, t: np.minimum(s, t),
+               lambda s, t: np.abs(s) - (-t)):
+        k = make_elementwise(fn, 2, 2, (1, 8))
+        d_out = torch.zeros((1, 8), device="cuda")
+        k(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), d_out)
+        torch.cuda.synchronize()
+        with np.errstate(all="ignore"):
+            want = fn(a, b)
+        got = d_out.cpu().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = ~np.isnan(want)
+        assert np.array_equal(got[ok], want[ok])
+        assert np.array_equal(np.signbit(got[ok]), np.signbit(want[ok]))
+
+
+def test_map_elements_through_the_c_abi(hc):
+    rng = np.random.default_rng(5)
+    rows, cols = 19, 40
+    a, b = rng.standard_normal((rows, cols)), rng.standard_normal((rows, cols))
+    d_a, d_b = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    d_out = torch.zeros((rows, cols), dtype=torch.float64, device="cuda")
+    p = capi.HcMapProgram()
+    p.inputs[0], p.inputs[1] = d_a.data_ptr(), d_b.data_ptr()
+    p.inPitch[0] = p.inPitch[1] = p.outPitch = cols
+    p.out, p.rows, p.cols, p.nInputs = d_out.data_ptr(), rows, cols, 2
+    # sqrt(a*a + b*b) * 0.5: load a; mul a; save t0; load b; mul b; add t0; sqrt; mul c0
+    program = [ew.LOAD | 0 << 8, ew.MUL | 0 << 8, ew.SAVE0, ew.LOAD | 1 << 8, ew.MUL | 1 << 8,
+               ew.ADD | (ew.SRC_TEMP + 0) << 8, ew.SQRT, ew.MUL | (ew.SRC_CONST + 0) << 8]
+    p.nInstr = len(program)
+    for i, ins in enumerate(program):
+        p.code[i] = ins
+    p.consts[0] = 0.5
+    hc.map_elements(p, capi.HC_F64)
+    finish(hc)
+    assert np.array_equal(d_out.cpu().numpy(), np.sqrt(b * b + a * a) * 0.5)
+
+    # Malformed programs are refused with a message before anything is launched.
+    p.code[5] = ew.ADD | (ew.SRC_TEMP + 1) << 8       # t1 was never written
+    with pytest.raises(RuntimeError, match="not written yet"):
+        hc.map_elements(p, capi.HC_F64)
+    p.code[5] = 99                                    # unknown operation
+    with pytest.raises(RuntimeError, match="unknown operation"):
+        hc.map_elements(p, capi.HC_F64)
+    p.code[5] = ew.ADD | 3 << 8                       # input 3 of 2
+    with pytest.raises(RuntimeError, match="does not exist"):
+        hc.map_elements(p, capi.HC_F64)
+    p.code[5] = ew.ADD | (ew.SRC_TEMP + 0) << 8
+    p.code[0] = ew.ADD | 0 << 8                       # accumulator read before it is set
+    with pytest.raises(RuntimeError, match="first instruction"):
+        hc.map_elements(p, capi.HC_F64)
+    p.code[0] = ew.LOAD | 0 << 8
+    p.nInstr = 0
+    with pytest.raises(RuntimeError, match="instructions"):
+        hc.map_elements(p, capi.HC_F64)
+    p.nInstr = len(program)
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        hc.map_elements(p, capi.HC_BF16)
+    p.rows = 0
+    hc.map_elements(p, capi.HC_F64)                   # empty: nothing to do
