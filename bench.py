@@ -48,6 +48,9 @@ SHAPES = {
     # filters [NF, C, HF, WF], stride (a ResNet-style 3x3 layer; not one of the
     # five benchmark configurations, measured as the next kernel family).
     "conv": (32, 64, 56, 56, 64, 3, 3, 1),
+    # Element-wise body out = max(2a - b, 0) on fp32 matrices (three 512 MiB
+    # arrays; likewise measured as a further kernel family).
+    "map": (32768, 4096),
 }
 # Tile sizes (TN images x TNF filters per work-group, K block) the conv is run with.
 CONV_TILES = (32, 64, 16)
@@ -61,6 +64,7 @@ SMALL_SHAPES = {
     "gemm_bf16": (2048, 2048, 2048),
     "gemm_w8a16": (1024, 2048, 2048),
     "conv": (32, 64, 30, 30, 64, 3, 3, 1),
+    "map": (8192, 4096),
 }
 
 # fp32 FMA rate of the CUDA cores, nominal (no measured figure exists for it):
@@ -69,6 +73,7 @@ FP32_NOMINAL_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 METRIC = {
     "conv": "conv_implicit_gemm_f32_throughput",
+    "map": "elementwise_relu_axpby_f32_algorithmic_bandwidth",
     "softmax": "softmax_rows_f32_algorithmic_bandwidth",
     "reduce": "reduce_rows_f32_algorithmic_bandwidth",
     "gemm_f32": "gemm_f32_tiled_throughput",
@@ -76,7 +81,14 @@ METRIC = {
     "gemm_w8a16": "gemm_w8a16_throughput",
 }
 DTYPE = {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32", "gemm_bf16": "bf16",
-         "gemm_w8a16": "bf16", "conv": "f32"}
+         "gemm_w8a16": "bf16", "conv": "f32", "map": "f32"}
+
+
+def relu_axpby(a, b):
+    """The element-wise body of the ``map`` workload."""
+    import numpy as np
+
+    return np.maximum(a * 2.0 - b, 0.0)
 
 
 def conv_shapes(s):
@@ -97,6 +109,9 @@ def algorithmic(name):
     if name == "softmax":
         m, n = s
         return 2 * m * n * 4, 0, "hbm"
+    if name == "map":
+        m, n = s
+        return 3 * m * n * 4, 0, "hbm"
     if name == "reduce":
         m, n = s
         return m * n * 4 + 2 * m * 4, 0, "hbm"
@@ -135,6 +150,7 @@ NCU_TRAFFIC = {
     "gemm_w8a16": None,
     "gemm_f32": None,
     "conv": None,
+    "map": None,
 }
 
 
@@ -264,6 +280,17 @@ def cpu_sample(name, threads, repeats):
 
         def one_pass():
             oracle.gemm_bf16(a, b, out, (256, 256))
+    elif name == "map":
+        rows = min(s[0], 8192 if threads > 1 else 2048)
+        a, b = oracle.make_elementwise_inputs(2, (rows, s[1]), "float32")
+        out = np.empty_like(a)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows, groups of 256 rows"
+
+        def one_pass():
+            oracle.run_row_groups_parallel(
+                lambda r0, r1: oracle.elementwise(relu_axpby, [a[r0:r1], b[r0:r1]], out[r0:r1],
+                                                  (256, s[1])), rows, 256, threads)
     elif name == "conv":
         xs, fs, os_ = conv_shapes(s)
         images = min(xs[0], 4)
@@ -378,6 +405,10 @@ def run_gpu(args):
         if name == "reduce":
             x = torch.rand(*s, device=dev, generator=g) * 20 - 10
             return [x], [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
+        if name == "map":
+            a = torch.randn(*s, device=dev, generator=g)
+            b = torch.randn(*s, device=dev, generator=g)
+            return [a, b], [torch.empty_like(a)]
         if name == "conv":
             xs, fs, os_ = conv_shapes(s)
             x = torch.randn(*xs, device=dev, generator=g)
@@ -409,6 +440,15 @@ def run_gpu(args):
                 {sym.TN: tn, sym.TNF: tnf, sym.KB: kb}))
         return conv_cache[0]
 
+    map_cache = []
+
+    def map_kernel():
+        if not map_cache:
+            from hc_b200.workloads import make_elementwise
+
+            map_cache.append(make_elementwise(relu_axpby, 2, 2, (4, 256), desc))
+        return map_cache[0]
+
     def direct_call(name, ins, outs):
         """The C++ dispatcher entry of the workload (no Python front door)."""
         if name == "softmax":
@@ -417,6 +457,10 @@ def run_gpu(args):
             return lambda: native.reduce_rows(ctx, ins[0], outs[0], outs[1])
         if name in ("gemm_f32", "gemm_bf16"):
             return lambda: native.gemm(ctx, ins[0], ins[1], outs[0])
+        if name == "map":
+            roles = map_kernel().plan_for((ins[0], ins[1], outs[0])).roles
+            arrays = [ins[i] for i in roles["inputs"]]
+            return lambda: native.map_elements(ctx, arrays, outs[0], roles["code"], roles["consts"])
         if name == "conv":
             # The index tables belong to the launch plan; made once, outside the timing.
             spec = conv_kernel().plan_for((ins[0], ins[1], outs[0])).roles["spec"]
@@ -439,6 +483,8 @@ def run_gpu(args):
             return lambda: kernels.dot_fullk(ins[0], ins[1], outs[0], (256, 256))
         if name == "conv":
             return lambda: conv_kernel()(ins[0], ins[1], outs[0])
+        if name == "map":
+            return lambda: map_kernel()(ins[0], ins[1], outs[0])
         return lambda: kernels.dequant_dot(ins[0], ins[1], ins[2], outs[0], (256, 256))
 
     def roofline(name, per_step_ms):
@@ -521,7 +567,7 @@ def run_gpu(args):
         extras = {}
         if name == "softmax" and not args.no_extras:
             for other, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
-                                 ("gemm_f32", 500), ("conv", 50)):
+                                 ("gemm_f32", 500), ("conv", 50), ("map", 200)):
                 # Each kernel is timed alone: let the board's power state settle
                 # after the previous one (a dense GEMM runs into the 1 kW cap and
                 # would hand lower clocks to whatever is measured right after it).

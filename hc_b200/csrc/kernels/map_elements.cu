@@ -60,89 +60,119 @@ __device__ __forceinline__ void storePacket(T *p, const Packet<T, V> &value) {
     __stcs(p, value.v[0]);
 }
 
-template <typename T, int V>
-__device__ __forceinline__ Packet<T, V> evaluate(const HcMapProgramDev &p,
-                                                 const Packet<T, V> (&x)[HC_MAP_MAX_INPUTS]) {
-  Packet<T, V> acc, t0, t1, t2;
+// Runs the program on all W elements this thread holds at once: one decode
+// and one (uniform) branch per instruction, then W independent operations.
+// The inputs and the accumulator live in registers; the temporaries, which few
+// expressions need, in this thread's column of a shared-memory array, so that
+// registers stay free for loads in flight (occupancy is what a streaming
+// kernel lives on).
+template <typename T, int W, int NIN>
+__device__ __forceinline__ void evaluate(const HcMapProgramDev &p, const T (&x)[NIN][W],
+                                         T (&acc)[W], T (&temps)[3][W][THREADS]) {
+  const int lane = threadIdx.x;
 #pragma unroll
-  for (int i = 0; i < V; ++i)
-    acc.v[i] = t0.v[i] = t1.v[i] = t2.v[i] = T(0);
+  for (int i = 0; i < W; ++i)
+    acc[i] = T(0);
+#define HC_MAP_EACH(expr)                                                               \
+  _Pragma("unroll") for (int i = 0; i < W; ++i) {                                       \
+    const T a = acc[i], b = v[i];                                                       \
+    (void)b;                                                                            \
+    acc[i] = (expr);                                                                    \
+  }                                                                                     \
+  break
+#define HC_MAP_TAKE(from)                                                               \
+  _Pragma("unroll") for (int i = 0; i < W; ++i) v[i] = from;                            \
+  break
   for (int pc = 0; pc < p.nInstr; ++pc) {
     const uint32_t ins = p.code[pc], op = ins & 0xffu, src = ins >> 8;
-    Packet<T, V> v = acc; // operand of the binary operations
+    T v[W]; // operand of the binary operations
+#pragma unroll
+    for (int i = 0; i < W; ++i)
+      v[i] = T(0);
     if (op <= HC_MAP_MIN) {
       if (src >= HC_MAP_SRC_CONST) {
         const T c = T(p.consts[src - HC_MAP_SRC_CONST]);
 #pragma unroll
-        for (int i = 0; i < V; ++i)
-          v.v[i] = c;
+        for (int i = 0; i < W; ++i)
+          v[i] = c;
       } else {
-        switch (src) { // named registers only: no indexed (local-memory) access
-        case 0: v = x[0]; break;
-        case 1: v = x[1]; break;
-        case 2: v = x[2]; break;
-        case 3: v = x[3]; break;
-        case 4: v = t0; break;
-        case 5: v = t1; break;
-        default: v = t2; break;
+        // Named registers only: an indexed access would go to local memory.
+        switch (src) {
+        case 0: HC_MAP_TAKE(x[0][i]);
+        case 1: if constexpr (NIN > 1) { HC_MAP_TAKE(x[1][i]); } break;
+        case 2: if constexpr (NIN > 2) { HC_MAP_TAKE(x[2][i]); } break;
+        case 3: if constexpr (NIN > 3) { HC_MAP_TAKE(x[3][i]); } break;
+        case 4: HC_MAP_TAKE(temps[0][i][lane]);
+        case 5: HC_MAP_TAKE(temps[1][i][lane]);
+        default: HC_MAP_TAKE(temps[2][i][lane]);
         }
       }
     }
+    switch (op) {
+    case HC_MAP_LOAD: HC_MAP_EACH(b);
+    case HC_MAP_ADD: HC_MAP_EACH(a + b);
+    case HC_MAP_SUB: HC_MAP_EACH(a - b);
+    case HC_MAP_RSUB: HC_MAP_EACH(b - a);
+    case HC_MAP_MUL: HC_MAP_EACH(a * b);
+    case HC_MAP_DIV: HC_MAP_EACH(a / b);
+    case HC_MAP_RDIV: HC_MAP_EACH(b / a);
+    case HC_MAP_MAX: HC_MAP_EACH(maxOf(a, b));
+    case HC_MAP_MIN: HC_MAP_EACH(minOf(a, b));
+    case HC_MAP_NEG: HC_MAP_EACH(-a);
+    case HC_MAP_ABS: HC_MAP_EACH(a < T(0) ? -a : (a == T(0) ? T(0) : a));
+    case HC_MAP_EXP: HC_MAP_EACH(expOf(a));
+    case HC_MAP_SQRT: HC_MAP_EACH(sqrt(a));
+    default: { // HC_MAP_SAVE0..2: park the accumulator
+      const int t = int(op) - int(HC_MAP_SAVE0);
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      const T a = acc.v[i], b = v.v[i];
-      T r = a;
-      switch (op) {
-      case HC_MAP_LOAD: r = b; break;
-      case HC_MAP_ADD: r = a + b; break;
-      case HC_MAP_SUB: r = a - b; break;
-      case HC_MAP_RSUB: r = b - a; break;
-      case HC_MAP_MUL: r = a * b; break;
-      case HC_MAP_DIV: r = a / b; break;
-      case HC_MAP_RDIV: r = b / a; break;
-      case HC_MAP_MAX: r = maxOf(a, b); break;
-      case HC_MAP_MIN: r = minOf(a, b); break;
-      case HC_MAP_NEG: r = -a; break;
-      case HC_MAP_ABS: r = a < T(0) ? -a : (a == T(0) ? T(0) : a); break;
-      case HC_MAP_EXP: r = expOf(a); break;
-      case HC_MAP_SQRT: r = sqrt(a); break;
-      default: break; // the SAVE operations leave the accumulator alone
-      }
-      acc.v[i] = r;
+      for (int i = 0; i < W; ++i)
+        temps[t][i][lane] = acc[i];
+      break;
     }
-    if (op == HC_MAP_SAVE0)
-      t0 = acc;
-    else if (op == HC_MAP_SAVE1)
-      t1 = acc;
-    else if (op == HC_MAP_SAVE2)
-      t2 = acc;
+    }
   }
-  return acc;
+#undef HC_MAP_EACH
+#undef HC_MAP_TAKE
 }
 
-template <typename T, int V>
+template <typename T, int V, int NIN>
 __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
+  constexpr int W = V * UNROLL;
+  __shared__ T temps[3][W][THREADS];
   const long long perRow = p.cols / V;
   for (long long r = blockIdx.y; r < p.rows; r += gridDim.y) {
     const long long first = ((long long)blockIdx.x * UNROLL) * THREADS + threadIdx.x;
     for (long long base = first; base < perRow;
          base += (long long)gridDim.x * UNROLL * THREADS) {
       // All loads of the UNROLL packets are issued before any arithmetic.
-      Packet<T, V> x[UNROLL][HC_MAP_MAX_INPUTS];
+      T x[NIN][W];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const long long i = base + (long long)u * THREADS;
+      for (int k = 0; k < NIN; ++k)
 #pragma unroll
-        for (int k = 0; k < HC_MAP_MAX_INPUTS; ++k)
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = base + (long long)u * THREADS;
+          Packet<T, V> packet;
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            packet.v[e] = T(0);
           if (k < p.nInputs && i < perRow)
-            x[u][k] = loadPacket<T, V>(static_cast<const T *>(p.in[k]) + r * p.inPitch[k] + i * V);
-      }
+            packet = loadPacket<T, V>(static_cast<const T *>(p.in[k]) + r * p.inPitch[k] + i * V);
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            x[k][u * V + e] = packet.v[e];
+        }
+      T result[W];
+      evaluate<T, W, NIN>(p, x, result, temps);
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const long long i = base + (long long)u * THREADS;
-        if (i < perRow)
-          storePacket<T, V>(static_cast<T *>(p.out) + r * p.outPitch + i * V,
-                            evaluate<T, V>(p, x[u]));
+        if (i < perRow) {
+          Packet<T, V> packet;
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            packet.v[e] = result[u * V + e];
+          storePacket<T, V>(static_cast<T *>(p.out) + r * p.outPitch + i * V, packet);
+        }
       }
     }
   }
@@ -150,13 +180,20 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
 
 } // namespace
 
-#define HC_MAP_KERNEL(name, T, V)                                                       \
-  extern "C" __global__ void __launch_bounds__(THREADS)                                 \
-      name(const __grid_constant__ HcMapProgramDev p) {                                 \
-    mapRows<T, V>(p);                                                                   \
+// One kernel per element type, packet width and number of input arrays (a
+// program without inputs runs on the one-input kernel and loads nothing).
+#define HC_MAP_KERNEL(tname, T, V, NIN)                                                 \
+  extern "C" __global__ void __launch_bounds__(THREADS, 4)                              \
+      hc_map_elements_##tname##_v##V##_n##NIN(const __grid_constant__ HcMapProgramDev p) { \
+    mapRows<T, V, NIN>(p);                                                              \
   }
+#define HC_MAP_KERNELS(tname, T, V)                                                     \
+  HC_MAP_KERNEL(tname, T, V, 1)                                                         \
+  HC_MAP_KERNEL(tname, T, V, 2)                                                         \
+  HC_MAP_KERNEL(tname, T, V, 3)                                                         \
+  HC_MAP_KERNEL(tname, T, V, 4)
 
-HC_MAP_KERNEL(hc_map_elements_f32_v4, float, 4)
-HC_MAP_KERNEL(hc_map_elements_f32_v1, float, 1)
-HC_MAP_KERNEL(hc_map_elements_f64_v2, double, 2)
-HC_MAP_KERNEL(hc_map_elements_f64_v1, double, 1)
+HC_MAP_KERNELS(f32, float, 4)
+HC_MAP_KERNELS(f32, float, 1)
+HC_MAP_KERNELS(f64, double, 2)
+HC_MAP_KERNELS(f64, double, 1)

@@ -49,10 +49,9 @@ struct KernelEntry {
 // Which image defines which kernel.
 const KernelEntry kKernelTable[] = {
     {"hc_copy2d", "copy2d"},
-    {"hc_map_elements_f32_v4", "map_elements"},
-    {"hc_map_elements_f32_v1", "map_elements"},
-    {"hc_map_elements_f64_v2", "map_elements"},
-    {"hc_map_elements_f64_v1", "map_elements"},
+    // hc_map_elements_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1..4}: element type, packet
+    // width and number of input arrays.
+    {"hc_map_elements_", "map_elements"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
     {"hc_softmax_rows_f32_w4", "softmax_rows"},
@@ -495,7 +494,8 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
     wide = wide && aligned(p.in[k], 16) && (p.rows == 1 || p.inPitch[k] % perPacket == 0);
   const int v = wide ? perPacket : 1;
   char name[40];
-  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d", dtype == HC_F32 ? "f32" : "f64", v);
+  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
+                v, std::max(1, p.nInputs));
   const long long perRow = p.cols / v;
   // One CTA per 512 packets of a row (two per thread); rows beyond 65535 and
   // very long rows are walked by the kernel's strides.

@@ -205,11 +205,18 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
         symbols[name] = _elf_symbols(blob)
     for kernel, image in table:
         if kernel.endswith("_"):
-            # A prefix entry: the family of the gathered tile product, one kernel
-            # per element type and piece shape.
+            # A prefix entry stands for a family: the gathered tile product has
+            # one kernel per element type and piece shape, the element-wise
+            # interpreter one per element type, packet width and input count.
             family = {s for s in symbols[image] if s.startswith(kernel)}
-            assert family == {f"{kernel}{t}_{sy}x{sx}" for t in ("f32", "f64")
-                              for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)}
+            expected = {
+                "hc_mapped_gemm_": {f"{kernel}{t}_{sy}x{sx}" for t in ("f32", "f64")
+                                    for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)},
+                "hc_map_elements_": {f"{kernel}{tv}_n{n}" for tv in ("f32_v4", "f32_v1", "f64_v2",
+                                                                     "f64_v1")
+                                     for n in (1, 2, 3, 4)},
+            }[kernel]
+            assert family == expected
             for member in family:
                 assert lib.hcImageName(lib.hcImageOfKernel(member.encode())).decode() == image
             continue
