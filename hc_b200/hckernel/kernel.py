@@ -575,7 +575,7 @@ class KernelDispatcher:
         raise UnsupportedKernel(
             f"{self.func.__name__}: the body matches none of the precompiled kernel families "
             f"(copy, row softmax, last-axis sum/max, whole-array sum, pairwise distance, GEMM, "
-            f"tile products gathered through mappings, "
+            f"tile products gathered through mappings, element-wise tile arithmetic, "
             f"int8 dequant GEMM)"
         )
 
