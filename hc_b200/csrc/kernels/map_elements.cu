@@ -85,10 +85,7 @@ __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, const T (&x)[
   break
   for (int pc = 0; pc < p.nInstr; ++pc) {
     const uint32_t ins = p.code[pc], op = ins & 0xffu, src = ins >> 8;
-    T v[W]; // operand of the binary operations
-#pragma unroll
-    for (int i = 0; i < W; ++i)
-      v[i] = T(0);
+    T v[W]; // operand of the binary operations (the unary ones never read it)
     if (op <= HC_MAP_MIN) {
       if (src >= HC_MAP_SRC_CONST) {
         const T c = T(p.consts[src - HC_MAP_SRC_CONST]);
