@@ -66,9 +66,14 @@ __device__ __forceinline__ void storePacket(T *p, const Packet<T, V> &value) {
 // expressions need, in this thread's column of a shared-memory array, so that
 // registers stay free for loads in flight (occupancy is what a streaming
 // kernel lives on).
-template <typename T, int W, int NIN>
+//
+// `row` and `packet` say where the elements sit (element i is in packet
+// `packet + (i / V) * THREADS`, at position i % V of it): programs written at
+// work-item level use the indices themselves as operands.
+template <typename T, int W, int V, int NIN, bool INDEXED>
 __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, const T (&x)[NIN][W],
-                                         T (&acc)[W], T (&temps)[3][W][THREADS]) {
+                                         T (&acc)[W], T (&temps)[3][W][THREADS], long long row,
+                                         long long packet) {
   const int lane = threadIdx.x;
 #pragma unroll
   for (int i = 0; i < W; ++i)
@@ -87,7 +92,13 @@ __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, const T (&x)[
     const uint32_t ins = p.code[pc], op = ins & 0xffu, src = ins >> 8;
     T v[W]; // operand of the binary operations (the unary ones never read it)
     if (op <= HC_MAP_MIN) {
-      if (src >= HC_MAP_SRC_CONST) {
+      if (INDEXED && src >= HC_MAP_SRC_ROW) {
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          v[i] = src == HC_MAP_SRC_ROW
+                     ? T(row)
+                     : T((packet + (long long)(i / V) * THREADS) * V + i % V);
+      } else if (src >= HC_MAP_SRC_CONST) {
         const T c = T(p.consts[src - HC_MAP_SRC_CONST]);
 #pragma unroll
         for (int i = 0; i < W; ++i)
@@ -132,7 +143,7 @@ __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, const T (&x)[
 #undef HC_MAP_TAKE
 }
 
-template <typename T, int V, int NIN>
+template <typename T, int V, int NIN, bool INDEXED>
 __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
   constexpr int W = V * UNROLL;
   __shared__ T temps[3][W][THREADS];
@@ -159,7 +170,7 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
             x[k][u * V + e] = packet.v[e];
         }
       T result[W];
-      evaluate<T, W, NIN>(p, x, result, temps);
+      evaluate<T, W, V, NIN, INDEXED>(p, x, result, temps, r, base);
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const long long i = base + (long long)u * THREADS;
@@ -178,11 +189,17 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
 } // namespace
 
 // One kernel per element type, packet width and number of input arrays (a
-// program without inputs runs on the one-input kernel and loads nothing).
+// program without inputs runs on the one-input kernel and loads nothing), and
+// a twin of each (suffix `i`) for programs that use the element indices, so
+// that the streaming kernels do not carry the index bookkeeping.
 #define HC_MAP_KERNEL(tname, T, V, NIN)                                                 \
   extern "C" __global__ void __launch_bounds__(THREADS, 4)                              \
       hc_map_elements_##tname##_v##V##_n##NIN(const __grid_constant__ HcMapProgramDev p) { \
-    mapRows<T, V, NIN>(p);                                                              \
+    mapRows<T, V, NIN, false>(p);                                                       \
+  }                                                                                     \
+  extern "C" __global__ void __launch_bounds__(THREADS, 4)                              \
+      hc_map_elements_##tname##_v##V##_n##NIN##i(const __grid_constant__ HcMapProgramDev p) { \
+    mapRows<T, V, NIN, true>(p);                                                        \
   }
 #define HC_MAP_KERNELS(tname, T, V)                                                     \
   HC_MAP_KERNEL(tname, T, V, 1)                                                         \

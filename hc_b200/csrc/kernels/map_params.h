@@ -27,8 +27,10 @@ enum HcMapOp : uint32_t {
   HC_MAP_OP_COUNT = 16
 };
 
-// Operand names: inputs 0..3, temporaries t0..t2, constants 0..7.
+// Operand names: inputs 0..3, temporaries t0..t2, constants 0..7, and the row
+// and column index of the element itself (as a value of the element type).
 constexpr uint32_t HC_MAP_SRC_INPUT = 0, HC_MAP_SRC_TEMP = 4, HC_MAP_SRC_CONST = 8;
+constexpr uint32_t HC_MAP_SRC_ROW = 16, HC_MAP_SRC_COL = 17;
 constexpr int HC_MAP_MAX_INPUTS = 4, HC_MAP_MAX_CONSTS = 8, HC_MAP_MAX_INSTR = 32;
 
 struct HcMapProgramDev {

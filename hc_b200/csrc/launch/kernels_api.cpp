@@ -49,8 +49,8 @@ struct KernelEntry {
 // Which image defines which kernel.
 const KernelEntry kKernelTable[] = {
     {"hc_copy2d", "copy2d"},
-    // hc_map_elements_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1..4}: element type, packet
-    // width and number of input arrays.
+    // hc_map_elements_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1..4}[i]: element type, packet
+    // width, number of input arrays, and whether element indices are operands.
     {"hc_map_elements_", "map_elements"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
@@ -441,6 +441,7 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   // that exist, temporaries written before they are read, and a first
   // instruction that sets the accumulator.
   bool saved[3] = {false, false, false};
+  bool usesIndices = false;
   for (int pc = 0; pc < p.nInstr; ++pc) {
     const uint32_t op = p.code[pc] & 0xffu, src = p.code[pc] >> 8;
     if (op >= HC_MAP_OP_COUNT)
@@ -453,7 +454,9 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
                         saved[src - HC_MAP_SRC_TEMP];
       const bool constant =
           src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + HC_MAP_MAX_CONSTS;
-      if (!input && !temp && !constant)
+      const bool index = src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL;
+      usesIndices = usesIndices || index;
+      if (!input && !temp && !constant && !index)
         return c->fail("hcMapElements: instruction %d reads operand %u, which does not exist "
                        "or is not written yet",
                        pc, src);
@@ -475,8 +478,9 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
     if (!p.in[k])
       return c->fail("hcMapElements: null input %d", k);
   const int elem = dtype == HC_F32 ? 4 : 8;
-  // Contiguous matrices are one long row.
-  bool flat = p.outPitch == p.cols;
+  // Contiguous matrices are one long row (unless the program asks where an
+  // element is).
+  bool flat = p.outPitch == p.cols && !usesIndices;
   for (int k = 0; k < p.nInputs; ++k)
     flat = flat && p.inPitch[k] == p.cols;
   if (flat) {
@@ -494,8 +498,8 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
     wide = wide && aligned(p.in[k], 16) && (p.rows == 1 || p.inPitch[k] % perPacket == 0);
   const int v = wide ? perPacket : 1;
   char name[40];
-  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
-                v, std::max(1, p.nInputs));
+  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s", dtype == HC_F32 ? "f32" : "f64",
+                v, std::max(1, p.nInputs), usesIndices ? "i" : "");
   const long long perRow = p.cols / v;
   // One CTA per 512 packets of a row (two per thread); rows beyond 65535 and
   // very long rows are walked by the kernel's strides.

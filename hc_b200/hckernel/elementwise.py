@@ -37,10 +37,11 @@ class MapProgram:
     """The translated expression: which loads feed it (``inputs``, Tile nodes),
     the instructions and the constants."""
 
-    def __init__(self, shape):
+    def __init__(self, shape, index_sources=None):
         self.shape = tuple(shape)
         self.inputs, self.code, self.consts = [], [], []
         self._free = list(range(TEMPS))
+        self.index_sources = index_sources  # work axis -> operand name (work-item level only)
 
     def _leaf(self, node):
         """Operand name of a leaf, or None for an inner node."""
@@ -56,6 +57,19 @@ class MapProgram:
                 raise UnsupportedKernel(f"element-wise kernel: more than {MAX_INPUTS} input tiles")
             self.inputs.append(node)
             return len(self.inputs) - 1
+        if node.op == "item_load":  # `buf[gid]` at work-item level
+            for i, seen in enumerate(self.inputs):
+                if seen.op == "item_load" and seen.args[0] is node.args[0] \
+                        and seen.attrs["axes"] == node.attrs["axes"]:
+                    return i
+            if len(self.inputs) == MAX_INPUTS:
+                raise UnsupportedKernel(f"element-wise kernel: more than {MAX_INPUTS} input arrays")
+            self.inputs.append(node)
+            return len(self.inputs) - 1
+        if node.op == "index":  # the work-item's own index as a value
+            if self.index_sources is None:
+                raise UnsupportedKernel("a work-item index outside a work-item function")
+            return self.index_sources[node.attrs["axis"]]
         if node.op in ("const", "alloc"):
             value = float(node.args[0])
             for i, seen in enumerate(self.consts):
@@ -129,6 +143,8 @@ def match_map(stores, counts, covers):
     program = MapProgram(expr.shape)
     program.evaluate(expr)
     for tile in program.inputs:
+        if tile.op != "load":
+            raise UnsupportedKernel("element-wise kernel: work-item reads inside a tile expression")
         view = tile.args[0]
         if view.buffer.shape != dst.buffer.shape or view.buffer.dtype != dst.buffer.dtype:
             raise UnsupportedKernel(
@@ -139,4 +155,56 @@ def match_map(stores, counts, covers):
                 f"element-wise kernel: {view.buffer.name} is loaded at another origin than "
                 f"{dst.buffer.name} is stored")
     covers(dst.origin, expr.shape, dst.buffer.shape, counts, "element-wise kernel")
+    return program, dst
+
+
+SRC_ROW, SRC_COL = 16, 17
+
+
+def match_items(item_stores, guards, work_shape):
+    """``(program, destination buffer)`` for a body written at work-item level
+    (``@group.workitems``; reference python/hckernel/kernel_api.py:395-414, its
+    tests python/hckernel/tests/test_kernel_sim.py:381-412)::
+
+        gid = wi.global_id()[:2]
+        if gid[0] < arr.shape[0] and gid[1] < arr.shape[1]:
+            arr[gid] = gid[0] * arr.shape[1] + gid[1]
+
+    Every work-item writes the element of one array that its own global id
+    names, computed from its index and from the same element of other arrays -
+    an element-wise program whose operands include the row and column index.
+    The launch covers whole arrays, so the conditions taken must be implied by
+    the array bounds and the work shape must reach every element."""
+    what = "work-item kernel"
+    if len(item_stores) != 1:
+        raise UnsupportedKernel(f"{what}: exactly one element store per work-item is supported")
+    dst, axes, expr = item_stores[0]
+    rank = dst.ndim
+    if rank not in (1, 2) or axes != tuple(range(rank)):
+        raise UnsupportedKernel(
+            f"{what}: the store must be {dst.name}[global_id] with one index per dimension, in "
+            f"order, of a vector or matrix")
+    if dst.dtype not in ("float32", "float64"):
+        raise UnsupportedKernel(f"{what}: float32 or float64 arrays, not {dst.dtype}")
+    for axis, bound in guards:
+        if axis >= rank or bound < dst.shape[axis]:
+            raise UnsupportedKernel(
+                f"{what}: the condition index{axis} < {bound} is not implied by the shape "
+                f"{list(dst.shape)} of {dst.name}; only bounds guards can be honoured")
+    for d in range(rank):
+        if work_shape[d] < dst.shape[d]:
+            raise UnsupportedKernel(
+                f"{what}: the work shape stops at {work_shape[d]} of {dst.shape[d]} in dimension {d}")
+    # Rows and columns of the kernel: a vector is one row.
+    sources = {0: SRC_COL} if rank == 1 else {0: SRC_ROW, 1: SRC_COL}
+    program = MapProgram((), sources)
+    program.evaluate(expr)
+    for tile in program.inputs:
+        src = tile.args[0]
+        if tile.op != "item_load":
+            raise UnsupportedKernel(f"{what}: tile loads cannot be mixed into a work-item function")
+        if tile.attrs["axes"] != axes or src.shape != dst.shape or src.dtype != dst.dtype:
+            raise UnsupportedKernel(
+                f"{what}: {src.name} must be read at the work-item's own index and match "
+                f"{dst.name} in shape and element type")
     return program, dst

@@ -37,7 +37,7 @@ import sympy
 
 from . import settings
 from .kernel_api import *  # noqa: F401,F403  (the reference re-exports kernel_api)
-from .elementwise import match_map
+from .elementwise import match_items, match_map
 from .mapped import match_mapped
 from .kernel_api import (
     Affine,
@@ -548,6 +548,13 @@ class KernelDispatcher:
             else:
                 stand_ins.append(a)
         body(recorder, *stand_ins)
+        if recorder.item_stores:
+            if recorder.stores or recorder.atomics or recorder.scatters:
+                raise UnsupportedKernel("kernels that mix work-item stores with tile stores")
+            program, dst = match_items(recorder.item_stores, recorder.guards, work)
+            return _Plan("map_elements", out=dst.index,
+                         inputs=[tile.args[0].index for tile in program.inputs],
+                         code=list(program.code), consts=list(program.consts))
         if not recorder.stores and not recorder.atomics and not recorder.scatters:
             raise UnsupportedKernel(f"{self.func.__name__}: the kernel stores nothing")
         if recorder.scatters:

@@ -376,7 +376,19 @@ class BufferRef:
             if len(index) != self.ndim or any(not 0 <= i < s for i, s in zip(index, self.shape)):
                 raise IndexError(f"{self.name}{list(index)} is out of range")
             return ElementRef(self, index)
+        axes = self._item_axes(key)
+        if axes is not None:  # `buf[gid]` read inside a work-item function
+            return Tile("item_load", (self,), (), self.dtype, axes=axes)
         return BufferView(self, self._origin(key))
+
+    @staticmethod
+    def _item_axes(key):
+        """The work axes of ``buf[gid]`` / ``buf[i, j]`` written at work-item
+        level, or None when ``key`` is anything else."""
+        keys = key if isinstance(key, tuple) else (key,)
+        if keys and all(isinstance(k, WorkIndex) for k in keys):
+            return tuple(k.axis for k in keys)
+        return None
 
     def __setitem__(self, key, value):
         # `buf[i] += tile` arrives here after ElementRef.__iadd__.
@@ -384,6 +396,12 @@ class BufferRef:
             if self.recorder is None:
                 raise UnsupportedKernel("element update outside a kernel body")
             self.recorder.atomics.append(value)
+            return
+        axes = self._item_axes(key)
+        if axes is not None:  # `buf[gid] = value` inside a work-item function
+            if self.recorder is None:
+                raise UnsupportedKernel("element store outside a kernel body")
+            self.recorder.item_stores.append((self, axes, Tile._wrap(value)))
             return
         raise UnsupportedKernel(f"direct assignment into {self.name}; use group.store")
 
@@ -486,6 +504,8 @@ class Tile:
     def _wrap(value):
         if isinstance(value, Tile):
             return value
+        if isinstance(value, WorkIndex):
+            return value.tile()
         if isinstance(value, (int, float, np.integer, np.floating)):
             return Tile("const", (float(value),), (), "scalar")
         raise UnsupportedKernel(f"operand {value!r} is not a tile or a number")
@@ -636,13 +656,71 @@ class CurrentSubGroup:
         return self._subgroup_id
 
 
+class Guard:
+    """``gid < bound`` inside a work-item function.  ``if`` asks for its truth:
+    the recording takes the branch (the function is recorded for the work-items
+    that pass) and notes the bound, which must turn out to be an array bound -
+    the only kind of condition a launch over whole arrays can honour."""
+
+    def __init__(self, axis, bound, recorder):
+        self.axis, self.bound, self.recorder = axis, bound, recorder
+
+    def __bool__(self):
+        self.recorder.guards.append((self.axis, self.bound))
+        return True
+
+
+class WorkIndex:
+    """One component of ``global_id()`` while a work-item function is recorded:
+    it stands for every work-item along that axis at once.  It indexes buffers
+    (``buf[gid]``), takes part in arithmetic as the index value, and compares
+    against a bound in a guarding ``if``."""
+
+    def __init__(self, axis, recorder):
+        self.axis, self.recorder = axis, recorder
+
+    def tile(self):
+        return Tile("index", (), (), "scalar", axis=self.axis)
+
+    def __lt__(self, bound):
+        return Guard(self.axis, int(Affine.of(bound)), self.recorder)
+
+    def __le__(self, bound):
+        return Guard(self.axis, int(Affine.of(bound)) + 1, self.recorder)
+
+    def _refuse(self, *_):
+        raise UnsupportedKernel("a work-item index can only be compared as `index < bound`")
+
+    __gt__ = __ge__ = __eq__ = __ne__ = _refuse
+    __hash__ = object.__hash__
+
+    def __index__(self):
+        raise UnsupportedKernel("a work-item index has no single value while the kernel is recorded")
+
+    __int__ = __index__
+
+    def __add__(self, o): return self.tile() + o
+    def __radd__(self, o): return o + self.tile()
+    def __sub__(self, o): return self.tile() - o
+    def __rsub__(self, o): return o - self.tile()
+    def __mul__(self, o): return self.tile() * o
+    def __rmul__(self, o): return o * self.tile()
+    def __truediv__(self, o): return self.tile() / o
+    def __rtruediv__(self, o): return o / self.tile()
+    def __neg__(self): return -self.tile()
+
+
 class CurrentWorkitem:
-    """Importable for source compatibility (reference: kernel_api.py:243-252)."""
+    """The work-item a ``@group.workitems`` function sees (reference:
+    kernel_api.py:243-252), recording instead of iterating."""
 
     def __init__(self, lid, gid):
         self._local_id, self._global_id = lid, gid
 
     def local_id(self):
+        if self._local_id is None:
+            raise UnsupportedKernel("work-item functions are recorded for the whole launch: only "
+                                    "global_id() is available, not local_id()")
         return self._local_id
 
     def global_id(self):
@@ -660,6 +738,8 @@ class CurrentGroup:
         self.stores = []
         self.scatters = []  # stores through a mapping: (view, tile, mapping)
         self.atomics = []
+        self.item_stores = []  # `buf[gid] = value` at work-item level: (buffer, axes, tile)
+        self.guards = []       # `gid < bound` conditions taken at work-item level: (axis, bound)
 
     @property
     def id(self):
@@ -739,7 +819,17 @@ class CurrentGroup:
         raise UnsupportedKernel("group.subgroups is not supported by the precompiled kernels")
 
     def workitems(self, func):
-        raise UnsupportedKernel("group.workitems is not supported by the precompiled kernels")
+        """Work-item scope (reference kernel_api.py:395-414, which runs ``func``
+        once per work-item).  Here ``func`` is recorded once, with a
+        :class:`WorkIndex` per axis standing for all work-items: what it may do
+        is what every work-item can do independently - read ``buf[gid]``,
+        compute, write ``buf[gid]`` under a bounds guard."""
+
+        def run():
+            ids = tuple(WorkIndex(d, self) for d in range(len(self._group_shape)))
+            func(CurrentWorkitem(None, ids))
+
+        return run
 
     def barrier(self):
         raise UnsupportedKernel("group.barrier is not supported by the precompiled kernels")

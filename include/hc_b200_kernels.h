@@ -107,7 +107,10 @@ HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
  * three temporaries.  An instruction is `op | (src << 8)`:
  *   op   0 load  1 add  2 sub  3 rsub (v - acc)  4 mul  5 div  6 rdiv (v / acc)
  *        7 max  8 min  9 neg  10 abs  11 exp  12 sqrt  13..15 save to t0..t2
- *   src  0..3 input arrays, 4..6 temporaries t0..t2, 8..15 consts[0..7]
+ *   src  0..3 input arrays, 4..6 temporaries t0..t2, 8..15 consts[0..7],
+ *        16 / 17 the row / column index of the element, as a value (what a body
+ *        written at work-item level gets from global_id(),
+ *        python/hckernel/kernel_api.py:243-252, 395-414)
  * max and min give NaN when either operand is NaN (NumPy's maximum/minimum);
  * operations are never contracted into FMAs.  The value of the accumulator
  * after the last instruction is stored.  Pitches are in elements. */

@@ -24,18 +24,23 @@ class FakeTensor:
 F = FakeTensor
 
 
-def run_program(code, consts, inputs, dtype):
+def run_program(code, consts, inputs, dtype, shape=None):
     """The machine of map_elements.cu, one NumPy operation per instruction."""
     dtype = np.dtype(dtype).type
+    shape = inputs[0].shape if shape is None else shape
     acc, temps = None, [None, None, None]
     with np.errstate(all="ignore"):
         for ins in code:
             op, src = ins & 0xFF, ins >> 8
             if op <= ew.MIN:
-                v = (inputs[src] if src < 4 else temps[src - 4] if src < 8
-                     else dtype(consts[src - 8]))
+                if src >= ew.SRC_ROW:  # the element's own row / column index
+                    rows, cols = np.indices(np.atleast_2d(np.empty(shape)).shape)
+                    v = (rows if src == ew.SRC_ROW else cols).reshape(shape).astype(dtype)
+                else:
+                    v = (inputs[src] if src < 4 else temps[src - 4] if src < 8
+                         else dtype(consts[src - 8]))
             if op == ew.LOAD:
-                acc = v if isinstance(v, np.ndarray) else np.full(inputs[0].shape, v, dtype)
+                acc = v if isinstance(v, np.ndarray) else np.full(shape, v, dtype)
             elif op == ew.ADD: acc = acc + v
             elif op == ew.SUB: acc = acc - v
             elif op == ew.RSUB: acc = v - acc
@@ -136,3 +141,105 @@ def test_bodies_outside_the_element_wise_family():
 
     with pytest.raises(UnsupportedKernel, match="more than|intermediate"):
         make_elementwise(deep, 1, 2, (4, 16)).plan_for((F((8, 32)), F((8, 32))))
+
+
+def test_work_item_bodies_of_the_reference_tests():
+    """python/hckernel/tests/test_kernel_sim.py:381-412, bodies unchanged: every
+    work-item writes its own (linearised) global id under a bounds guard."""
+    G, G1, G2, DT = sym.G, sym.G1, sym.G2, typename.DT
+    target = dict(backend="nvvm", device="cuda:0")
+
+    @kernel(work_shape=G, **target)
+    def dims1(gr: CurrentGroup, arr: Buffer[G, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            gid = wi.global_id()[0]
+            if gid < arr.shape[0]:
+                arr[gid] = gid
+
+        inner()
+
+    plan = dims1.plan_for((F((12,), "float64"),))
+    assert (plan.family, plan.roles["inputs"], plan.roles["out"]) == ("map_elements", [], 0)
+    got = run_program(plan.roles["code"], plan.roles["consts"], [], "float64", (12,))
+    assert np.array_equal(got, np.arange(12))
+
+    @kernel(work_shape=(G1, G2), **target)
+    def dims2(gr: CurrentGroup, arr: Buffer[G1, G2, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            gid = wi.global_id()[:2]
+            if gid[0] < arr.shape[0] and gid[1] < arr.shape[1]:
+                arr[gid] = gid[0] * arr.shape[1] + gid[1]
+
+        inner()
+
+    plan = dims2.plan_for((F((12, 5), "float64"),))
+    got = run_program(plan.roles["code"], plan.roles["consts"], [], "float64", (12, 5))
+    assert np.array_equal(got, np.arange(60).reshape(12, 5))
+
+
+def test_work_item_bodies_with_reads_and_their_limits():
+    W, H, DT = sym.W, sym.H, typename.DT
+    target = dict(backend="nvvm", device="cuda:0")
+
+    def item_kernel(body, work=(W, H)):
+        @kernel(work_shape=work, **target)
+        def k(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+            @gr.workitems
+            def inner(wi: CurrentWorkitem):
+                body(wi.global_id(), a, out)
+
+            inner()
+
+        return k
+
+    def scaled(gid, a, out):
+        i, j = gid
+        if i < out.shape[0] and j < out.shape[1]:
+            out[i, j] = a[i, j] * 2.0 + j
+
+    plan = item_kernel(scaled).plan_for((F((6, 9)), F((6, 9))))
+    assert (plan.roles["inputs"], plan.roles["out"]) == ([0], 1)
+    a = np.arange(54, dtype=np.float32).reshape(6, 9)
+    got = run_program(plan.roles["code"], plan.roles["consts"], [a], "float32")
+    assert np.array_equal(got, a * 2 + np.arange(9, dtype=np.float32))
+
+    def half(gid, a, out):  # a condition that is not a bounds guard
+        if gid[0] < 3:
+            out[gid] = a[gid]
+
+    with pytest.raises(UnsupportedKernel, match="not implied by the shape"):
+        item_kernel(half).plan_for((F((6, 9)), F((6, 9))))
+
+    def transposed(gid, a, out):
+        out[gid[1], gid[0]] = a[gid]
+
+    with pytest.raises(UnsupportedKernel, match="one index per dimension, in order"):
+        item_kernel(transposed).plan_for((F((6, 6)), F((6, 6))))
+
+    def shifted_read(gid, a, out):
+        out[gid] = a[gid[1], gid[0]]
+
+    with pytest.raises(UnsupportedKernel, match="own index"):
+        item_kernel(shifted_read).plan_for((F((6, 6)), F((6, 6))))
+
+    def plain(gid, a, out):
+        out[gid] = a[gid] + 1.0
+
+    with pytest.raises(UnsupportedKernel, match="work shape stops"):
+        item_kernel(plain, work=(W, 4)).plan_for((F((6, 9)), F((6, 9))))
+
+    def local(gid, a, out):
+        out[gid] = a[gid]
+
+    @kernel(work_shape=(W, H), **target)
+    def uses_local_id(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            out[wi.local_id()] = a[wi.local_id()]
+
+        inner()
+
+    with pytest.raises(UnsupportedKernel, match="local_id"):
+        uses_local_id.plan_for((F((6, 9)), F((6, 9))))

@@ -126,3 +126,70 @@ def test_map_elements_through_the_c_abi(hc):
         hc.map_elements(p, capi.HC_BF16)
     p.rows = 0
     hc.map_elements(p, capi.HC_F64)                   # empty: nothing to do
+
+
+def test_work_item_kernels_of_the_reference_tests():
+    """python/hckernel/tests/test_kernel_sim.py:381-412 (test_buffer_dims1/2) with
+    the bodies unchanged: each work-item writes its own linearised global id."""
+    from hc_b200.hckernel.kernel import (Buffer, CurrentGroup, CurrentWorkitem, kernel, sym,
+                                         typename)
+
+    G, G1, G2, DT = sym.G, sym.G1, sym.G2, typename.DT
+    target = dict(backend="nvvm", device="cuda:0")
+
+    @kernel(work_shape=G, **target)
+    def dims1(gr: CurrentGroup, arr: Buffer[G, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            gid = wi.global_id()[0]
+            if gid < arr.shape[0]:
+                arr[gid] = gid
+
+        inner()
+
+    src = torch.zeros(12, dtype=torch.float64, device="cuda")
+    dims1(src)
+    torch.cuda.synchronize()
+    assert np.array_equal(src.cpu().numpy(), np.arange(12))
+
+    @kernel(work_shape=(G1, G2), **target)
+    def dims2(gr: CurrentGroup, arr: Buffer[G1, G2, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            gid = wi.global_id()[:2]
+            if gid[0] < arr.shape[0] and gid[1] < arr.shape[1]:
+                arr[gid] = gid[0] * arr.shape[1] + gid[1]
+
+        inner()
+
+    for shape, dtype in (((12, 5), torch.float64), ((300, 1000), torch.float32)):
+        src = torch.zeros(shape, dtype=dtype, device="cuda")
+        dims2(src)
+        torch.cuda.synchronize()
+        assert np.array_equal(src.cpu().numpy(), np.arange(shape[0] * shape[1]).reshape(shape))
+
+
+def test_work_item_kernel_with_reads():
+    from hc_b200.hckernel.kernel import (Buffer, CurrentGroup, CurrentWorkitem, kernel, sym,
+                                         typename)
+
+    W, H, DT = sym.W, sym.H, typename.DT
+
+    @kernel(work_shape=(W, H), backend="nvvm", device="cuda:0")
+    def k(gr: CurrentGroup, a: Buffer[W, H, DT], b: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        @gr.workitems
+        def inner(wi: CurrentWorkitem):
+            i, j = wi.global_id()
+            if i < out.shape[0] and j < out.shape[1]:
+                out[i, j] = (a[i, j] - b[i, j]) * (i + 1.0) + j
+
+        inner()
+
+    rng = np.random.default_rng(9)
+    a, b = (rng.standard_normal((37, 130)).astype(np.float32) for _ in range(2))
+    d_out = torch.full((37, 130), float("nan"), device="cuda")
+    k(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), d_out)
+    torch.cuda.synchronize()
+    rows = np.arange(37, dtype=np.float32)[:, None]
+    cols = np.arange(130, dtype=np.float32)[None, :]
+    assert np.array_equal(d_out.cpu().numpy(), (a - b) * (rows + np.float32(1)) + cols)
