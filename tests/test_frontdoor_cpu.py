@@ -210,11 +210,18 @@ def test_bodies_outside_the_families_are_refused():
         column_sums.plan_for((F((32, 64)), F((64,)), 8))
 
     @kernel(work_shape=M, group_shape=GM, **TARGET)
-    def with_workitems(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
-        gr.workitems(lambda wi: None)
+    def with_subgroups(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
+        gr.subgroups(lambda sg: None)
 
-    with pytest.raises(UnsupportedKernel, match="workitems"):
-        with_workitems.plan_for((F((32, 64)), F((32, 64)), 8))
+    with pytest.raises(UnsupportedKernel, match="group.subgroups is not supported"):
+        with_subgroups.plan_for((F((32, 64)), F((32, 64)), 8))
+
+    @kernel(work_shape=M, group_shape=GM, **TARGET)
+    def with_barrier(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
+        gr.barrier()
+
+    with pytest.raises(UnsupportedKernel, match="group.barrier is not supported"):
+        with_barrier.plan_for((F((32, 64)), F((32, 64)), 8))
 
 
 def test_default_group_shape_follows_the_launch_heuristic():
