@@ -28,7 +28,10 @@ Semantics the recording keeps from the reference:
   ``view[m.func(*index)]`` or zero when that falls outside ``view``
   (kernel_api.py:303-310); ``group.store(view, tile, mapping=m)`` scatters the
   same way and drops what falls outside (kernel_api.py:319-336).  The recording
-  keeps the mapping object; the launch plan evaluates it into index tables.
+  keeps the mapping object; the launch plan evaluates it into index tables;
+* ``@group.workitems`` (kernel_api.py:395-414): the function is recorded once
+  with a :class:`WorkIndex` per axis in place of ``global_id()``; reads and one
+  guarded write of the work-item's own element become an element-wise program.
 """
 
 import fractions

@@ -255,6 +255,46 @@ def elementwise_cases():
     ]
 
 
+def random_expression(rng, inputs: int, depth: int):
+    """A random element-wise function of ``inputs`` arrays as ``(fn, text)``:
+    a tree of + - * /, maximum, minimum, abs, negation and sqrt(abs(.)) over the
+    inputs and a few constants, at most ``depth`` levels deep.  Divisors are
+    kept away from zero (``abs(.) + 0.5``).  Used to test the translation of
+    recorded expressions against NumPy on the same arrays."""
+    names = "abcd"[:inputs]
+
+    def build(level):
+        if level == 0 or rng.random() < 0.2:
+            if rng.random() < 0.75:
+                return str(rng.choice(list(names)))
+            return repr(float(rng.choice([0.5, 1.0, 2.0, -1.5, 3.0])))
+        kind = rng.integers(0, 9)
+        x = build(level - 1)
+        if kind == 6:
+            return f"np.abs({x})"
+        if kind == 7:
+            return f"(-({x}))"
+        if kind == 8:
+            return f"np.sqrt(np.abs({x}))"
+        y = build(level - 1)
+        if kind == 3:
+            return f"(({x}) / (np.abs({y}) + 0.5))"
+        if kind == 4:
+            return f"np.maximum({x}, {y})"
+        if kind == 5:
+            return f"np.minimum({x}, {y})"
+        return f"(({x}) {'+-*'[kind]} ({y}))"
+
+    import re
+
+    while True:
+        text = build(depth)
+        if re.search(rf"\b[{names}]\b", text):  # at least one array takes part
+            break
+    fn = eval(f"lambda {', '.join(names)}: {text}", {"np": np})  # noqa: S307 (own text)
+    return fn, text
+
+
 def make_elementwise_inputs(count, shape, dtype, seed: int = 7):
     rng = np.random.default_rng(seed)
     return [rng.standard_normal(shape).astype(dtype) for _ in range(count)]

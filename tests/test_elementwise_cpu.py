@@ -84,6 +84,33 @@ def test_recorded_expression_becomes_an_equivalent_program(golden, case):
     np.testing.assert_allclose(got, golden[name], rtol=3e-7 if dtype == "float32" else 0)
 
 
+def test_random_expressions_translate_exactly():
+    """200 random expression trees: the program, run one NumPy operation per
+    instruction, must give bit for bit what NumPy gives for the expression
+    (float64, where NumPy's scalar promotion rules cannot interfere)."""
+    rng = np.random.default_rng(2024)
+    translated = 0
+    for _ in range(200):
+        count = int(rng.integers(1, 4))
+        fn, text = oracle.random_expression(rng, count, int(rng.integers(1, 5)))
+        k = make_elementwise(fn, count, 2, (4, 16))
+        try:
+            plan = k.plan_for(tuple(F((8, 32), "float64") for _ in range(count + 1)))
+        except UnsupportedKernel as e:  # too many values parked at once, too long
+            assert "more than" in str(e), text
+            continue
+        if plan.family == "copy2d":  # the expression was a bare input
+            continue
+        translated += 1
+        inputs = oracle.make_elementwise_inputs(count, (8, 32), "float64", seed=translated)
+        got = run_program(plan.roles["code"], plan.roles["consts"],
+                          [inputs[i] for i in plan.roles["inputs"]], "float64", (8, 32))
+        with np.errstate(all="ignore"):
+            want = np.broadcast_to(fn(*inputs), (8, 32))
+        assert np.array_equal(got, want, equal_nan=True), text
+    assert translated > 120
+
+
 def test_translation_details():
     a = make_elementwise(lambda t: (t + 1.0) * (t - 1.0) / ((t * t + 2.0) * (t + 3.0)), 1, 2, (4, 16))
     plan = a.plan_for((F((8, 32)), F((8, 32))))
