@@ -150,7 +150,9 @@ NCU_TRAFFIC = {
     "gemm_w8a16": None,
     "gemm_f32": None,
     "conv": None,
-    "map": None,
+    # profiles/map_elements_f32_v4_n2_8192x4096.md: (268.49 + 97.94) MB for a quarter of the
+    # rows, scaled by 4 (the part of the output still in L2 at kernel end is not counted).
+    "map": 1465.7e6,
 }
 
 
