@@ -32,6 +32,7 @@ INCLUDE = ROOT.parent / "include"
 KERNEL_SOURCES = [
     "copy2d",
     "map_elements",
+    "row_program",
     "softmax_rows",
     "reduce_rows",
     "reduce_all",

@@ -134,6 +134,7 @@ KERNELS_PROTOTYPES = {
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]
     ),
     "hcMapElements": (C.c_int, [_vp, C.POINTER(HcMapProgram), C.c_int]),
+    "hcRowProgram": (C.c_int, [_vp, C.POINTER(HcMapProgram), C.c_int]),
     "hcMappedGemm": (
         C.c_int,
         [_vp, C.POINTER(HcMappedOperand), C.POINTER(HcMappedOperand),
@@ -306,6 +307,10 @@ class Context:
     def map_elements(self, program, dtype=HC_F32):
         """``program``: :class:`HcMapProgram`."""
         self._check(self.lib.hcMapElements(self.handle, C.byref(program), dtype), "hcMapElements")
+
+    def row_program(self, program, dtype=HC_F32):
+        """``program``: :class:`HcMapProgram` with row reductions."""
+        self._check(self.lib.hcRowProgram(self.handle, C.byref(program), dtype), "hcRowProgram")
 
     def mapped_gemm(self, x, f, out, groups, tm, tn, k, dtype=HC_F32):
         """``x``, ``f``, ``out``: :class:`HcMappedOperand`."""

@@ -201,8 +201,8 @@ void pairwiseDistance(Context &ctx, py::handle a, py::handle b, py::handle out) 
 // Element-wise expression over matrices (or vectors) of one shape and type:
 // `inputs` a list of up to four arrays, `code` and `consts` the program
 // (include/hc_b200_kernels.h: HcMapProgram).
-void mapElements(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
-                 const std::vector<double> &consts) {
+void runProgram(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
+                const std::vector<double> &consts, bool rowProgram) {
   auto ins = py::cast<py::list>(inputs);
   if (ins.size() > 4)
     throw py::value_error("map_elements: at most 4 input arrays");
@@ -238,7 +238,24 @@ void mapElements(Context &ctx, py::handle inputs, py::handle out, const std::vec
   p.nInstr = int(code.size());
   std::copy(code.begin(), code.end(), p.code);
   std::copy(consts.begin(), consts.end(), p.consts);
-  ctx.check(hcMapElements(ctx.get(), &p, floatDType(O, "out")), "map_elements");
+  if (rowProgram) {
+    if (rank != 2)
+      throw py::value_error("row_program: matrices expected");
+    ctx.check(hcRowProgram(ctx.get(), &p, floatDType(O, "out")), "row_program");
+  } else {
+    ctx.check(hcMapElements(ctx.get(), &p, floatDType(O, "out")), "map_elements");
+  }
+}
+
+void mapElements(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
+                 const std::vector<double> &consts) {
+  runProgram(ctx, inputs, out, code, consts, false);
+}
+
+// Row program (hcRowProgram): like map_elements, with reductions along the rows.
+void rowProgram(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
+                const std::vector<double> &consts) {
+  runProgram(ctx, inputs, out, code, consts, true);
 }
 
 // One operand of the gathered tile product: the array (any rank up to 4, any
@@ -412,6 +429,8 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("pairwise_distance", &pairwiseDistance, py::arg("ctx"), py::arg("a"), py::arg("b"),
         py::arg("out"));
   m.def("map_elements", &mapElements, py::arg("ctx"), py::arg("inputs"), py::arg("out"),
+        py::arg("code"), py::arg("consts"));
+  m.def("row_program", &rowProgram, py::arg("ctx"), py::arg("inputs"), py::arg("out"),
         py::arg("code"), py::arg("consts"));
   m.def("mapped_gemm", &mappedGemm, py::arg("ctx"), py::arg("x"), py::arg("x_tables"),
         py::arg("f"), py::arg("f_tables"), py::arg("out"), py::arg("out_tables"),

@@ -24,13 +24,21 @@ enum HcMapOp : uint32_t {
   HC_MAP_SAVE0 = 13, // t0 = acc
   HC_MAP_SAVE1 = 14, // t1 = acc
   HC_MAP_SAVE2 = 15, // t2 = acc
-  HC_MAP_OP_COUNT = 16
+  HC_MAP_LOG = 16,   // acc = log(acc)
+  // Row programs only (row_program.cu): end a pass over the row by reducing the
+  // accumulator along it into row scalar s[src].
+  HC_MAP_RSUM = 17,
+  HC_MAP_RMAX = 18,
+  HC_MAP_OP_COUNT = 19
 };
 
 // Operand names: inputs 0..3, temporaries t0..t2, constants 0..7, and the row
 // and column index of the element itself (as a value of the element type).
 constexpr uint32_t HC_MAP_SRC_INPUT = 0, HC_MAP_SRC_TEMP = 4, HC_MAP_SRC_CONST = 8;
 constexpr uint32_t HC_MAP_SRC_ROW = 16, HC_MAP_SRC_COL = 17;
+// Row programs only: the row scalars s0..s3 that earlier passes reduced.
+constexpr uint32_t HC_MAP_SRC_SCALAR = 20;
+constexpr int HC_MAP_MAX_SCALARS = 4;
 constexpr int HC_MAP_MAX_INPUTS = 4, HC_MAP_MAX_CONSTS = 8, HC_MAP_MAX_INSTR = 32;
 
 struct HcMapProgramDev {

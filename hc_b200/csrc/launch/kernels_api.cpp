@@ -52,6 +52,8 @@ const KernelEntry kKernelTable[] = {
     // hc_map_elements_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1..4}[i]: element type, packet
     // width, number of input arrays, and whether element indices are operands.
     {"hc_map_elements_", "map_elements"},
+    // hc_row_program_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1,2}
+    {"hc_row_program_", "row_program"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
     {"hc_softmax_rows_f32_w4", "softmax_rows"},
@@ -424,6 +426,62 @@ static_assert(sizeof(HcMapProgram) == sizeof(HcMapProgramDev) &&
                   offsetof(HcMapProgram, consts) == offsetof(HcMapProgramDev, consts),
               "public program description and kernel parameter block differ");
 
+// Checks a program before it reaches the GPU: known operations, operands that
+// exist, temporaries and row scalars written before they are read, an
+// accumulator that is loaded before it is used.  `rowProgram`: reductions and
+// row scalars are allowed (and a last pass that stores is required); element
+// indices are not.
+static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &p,
+                           bool rowProgram, bool *usesIndices) {
+  bool saved[3] = {false, false, false};
+  bool reduced[HC_MAP_MAX_SCALARS] = {false, false, false, false};
+  bool passStart = true;
+  for (int pc = 0; pc < p.nInstr; ++pc) {
+    const uint32_t op = p.code[pc] & 0xffu, src = p.code[pc] >> 8;
+    if (op >= HC_MAP_OP_COUNT)
+      return c->fail("%s: unknown operation %u at instruction %d", who, op, pc);
+    if (passStart && op != HC_MAP_LOAD)
+      return c->fail(pc == 0 ? "%s: the first instruction must load the accumulator"
+                             : "%s: the instruction after a reduction must load the accumulator",
+                     who);
+    passStart = false;
+    if (op <= HC_MAP_MIN) {
+      const bool input = src < uint32_t(p.nInputs);
+      const bool temp = src >= HC_MAP_SRC_TEMP && src < HC_MAP_SRC_TEMP + 3 &&
+                        saved[src - HC_MAP_SRC_TEMP];
+      const bool constant =
+          src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + uint32_t(HC_MAP_MAX_CONSTS);
+      const bool index = !rowProgram && (src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL);
+      const bool scalar = rowProgram && src >= HC_MAP_SRC_SCALAR &&
+                          src < HC_MAP_SRC_SCALAR + uint32_t(HC_MAP_MAX_SCALARS) &&
+                          reduced[src - HC_MAP_SRC_SCALAR];
+      *usesIndices = *usesIndices || index;
+      if (!input && !temp && !constant && !index && !scalar)
+        return c->fail("%s: instruction %d reads operand %u, which does not exist "
+                       "or is not written yet",
+                       who, pc, src);
+    }
+    if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
+      saved[op - HC_MAP_SAVE0] = true;
+    if (op == HC_MAP_RSUM || op == HC_MAP_RMAX) {
+      if (!rowProgram)
+        return c->fail("%s: row reductions belong to hcRowProgram (instruction %d)", who, pc);
+      if (src >= uint32_t(HC_MAP_MAX_SCALARS))
+        return c->fail("%s: instruction %d reduces into row scalar %u of %d", who, pc, src,
+                       HC_MAP_MAX_SCALARS);
+      if (pc == p.nInstr - 1)
+        return c->fail("%s: the program ends in a reduction; a last pass must compute what is "
+                       "stored",
+                       who);
+      reduced[src] = true;
+      passStart = true;
+      // Temporaries do not outlive a pass (every pass walks the row again).
+      saved[0] = saved[1] = saved[2] = false;
+    }
+  }
+  return 0;
+}
+
 int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   if (!c)
     return 1;
@@ -437,33 +495,9 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
       p.nInstr > HC_MAP_MAX_INSTR)
     return c->fail("hcMapElements: %d inputs, %d instructions (at most %d and 1..%d)", p.nInputs,
                    p.nInstr, HC_MAP_MAX_INPUTS, HC_MAP_MAX_INSTR);
-  // Check the program before it reaches the GPU: known operations, operands
-  // that exist, temporaries written before they are read, and a first
-  // instruction that sets the accumulator.
-  bool saved[3] = {false, false, false};
   bool usesIndices = false;
-  for (int pc = 0; pc < p.nInstr; ++pc) {
-    const uint32_t op = p.code[pc] & 0xffu, src = p.code[pc] >> 8;
-    if (op >= HC_MAP_OP_COUNT)
-      return c->fail("hcMapElements: unknown operation %u at instruction %d", op, pc);
-    if (pc == 0 && op != HC_MAP_LOAD)
-      return c->fail("hcMapElements: the first instruction must load the accumulator");
-    if (op <= HC_MAP_MIN) {
-      const bool input = src < uint32_t(p.nInputs);
-      const bool temp = src >= HC_MAP_SRC_TEMP && src < HC_MAP_SRC_TEMP + 3 &&
-                        saved[src - HC_MAP_SRC_TEMP];
-      const bool constant =
-          src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + HC_MAP_MAX_CONSTS;
-      const bool index = src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL;
-      usesIndices = usesIndices || index;
-      if (!input && !temp && !constant && !index)
-        return c->fail("hcMapElements: instruction %d reads operand %u, which does not exist "
-                       "or is not written yet",
-                       pc, src);
-    }
-    if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
-      saved[op - HC_MAP_SAVE0] = true;
-  }
+  if (checkMapProgram(c, "hcMapElements", p, false, &usesIndices))
+    return 1;
   if (p.rows < 0 || p.cols < 0 || p.outPitch < p.cols)
     return c->fail("hcMapElements: invalid shape %lld x %lld", (long long)p.rows,
                    (long long)p.cols);
@@ -507,6 +541,48 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   long long gy = std::min<long long>(p.rows, 65535);
   void *args[] = {&p};
   return c->launch(name, size_t(gx), size_t(gy), 1, 256, args, 1, 0);
+}
+
+int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("hcRowProgram: unsupported dtype %d", dtype);
+  if (!program)
+    return c->fail("hcRowProgram: null program");
+  HcMapProgramDev p;
+  std::memcpy(&p, program, sizeof p);
+  if (p.nInputs < 1 || p.nInputs > 2 || p.nInstr < 1 || p.nInstr > HC_MAP_MAX_INSTR)
+    return c->fail("hcRowProgram: %d inputs, %d instructions (1..2 and 1..%d)", p.nInputs,
+                   p.nInstr, HC_MAP_MAX_INSTR);
+  bool usesIndices = false;
+  if (checkMapProgram(c, "hcRowProgram", p, true, &usesIndices))
+    return 1;
+  if (p.rows < 0 || p.cols < 0 || p.outPitch < p.cols)
+    return c->fail("hcRowProgram: invalid shape %lld x %lld", (long long)p.rows,
+                   (long long)p.cols);
+  for (int k = 0; k < p.nInputs; ++k)
+    if (p.inPitch[k] < p.cols)
+      return c->fail("hcRowProgram: pitch of input %d is shorter than a row", k);
+  if (p.rows == 0 || p.cols == 0)
+    return 0;
+  if (!p.out)
+    return c->fail("hcRowProgram: null output");
+  for (int k = 0; k < p.nInputs; ++k)
+    if (!p.in[k])
+      return c->fail("hcRowProgram: null input %d", k);
+  if (ceilDiv(p.rows, 8) > 0x7fffffffLL)
+    return c->fail("hcRowProgram: %lld rows exceed one launch", (long long)p.rows);
+  const int perPacket = 16 / (dtype == HC_F32 ? 4 : 8);
+  bool wide = p.cols % perPacket == 0 && aligned(p.out, 16) && p.outPitch % perPacket == 0;
+  for (int k = 0; k < p.nInputs; ++k)
+    wide = wide && aligned(p.in[k], 16) && p.inPitch[k] % perPacket == 0;
+  char name[40];
+  std::snprintf(name, sizeof name, "hc_row_program_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
+                wide ? perPacket : 1, p.nInputs);
+  void *args[] = {&p};
+  // One warp per row, eight rows per CTA.
+  return c->launch(name, size_t(ceilDiv(p.rows, 8)), 1, 1, 256, args, 1, 0);
 }
 
 // ---- softmax --------------------------------------------------------------------

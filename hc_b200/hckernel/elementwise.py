@@ -25,12 +25,14 @@ or more than 32 instructions is refused.
 from .kernel_api import Tile, UnsupportedKernel
 
 LOAD, ADD, SUB, RSUB, MUL, DIV, RDIV, MAX, MIN, NEG, ABS, EXP, SQRT, SAVE0 = range(14)
-SRC_TEMP, SRC_CONST = 4, 8
-MAX_INPUTS, MAX_CONSTS, MAX_INSTR, TEMPS = 4, 8, 32, 3
+LOG, RSUM, RMAX = 16, 17, 18
+SRC_TEMP, SRC_CONST, SRC_SCALAR = 4, 8, 20
+MAX_INPUTS, MAX_CONSTS, MAX_INSTR, TEMPS, MAX_SCALARS = 4, 8, 32, 3, 4
 
 _BINARY = {"add": (ADD, ADD), "sub": (SUB, RSUB), "mul": (MUL, MUL), "div": (DIV, RDIV),
            "maximum": (MAX, MAX), "minimum": (MIN, MIN)}
-_UNARY = {"neg": NEG, "abs": ABS, "exp": EXP, "sqrt": SQRT}
+_UNARY = {"neg": NEG, "abs": ABS, "exp": EXP, "sqrt": SQRT, "log": LOG}
+_ROW_REDUCTIONS = {"sum": RSUM, "max": RMAX}
 
 
 class MapProgram:
@@ -42,9 +44,16 @@ class MapProgram:
         self.inputs, self.code, self.consts = [], [], []
         self._free = list(range(TEMPS))
         self.index_sources = index_sources  # work axis -> operand name (work-item level only)
+        self.scalars = []  # row programs: the reductions already computed, in scalar order
 
     def _leaf(self, node):
         """Operand name of a leaf, or None for an inner node."""
+        if node.op in _ROW_REDUCTIONS:  # a value an earlier pass of a row program reduced
+            for i, seen in enumerate(self.scalars):
+                if seen.key() == node.key():
+                    return SRC_SCALAR + i
+            raise UnsupportedKernel(
+                f"element-wise kernel: operation '{node.op}' has no element-wise form")
         if node.op == "load":
             if node.shape != self.shape:
                 raise UnsupportedKernel(
@@ -155,6 +164,68 @@ def match_map(stores, counts, covers):
                 f"element-wise kernel: {view.buffer.name} is loaded at another origin than "
                 f"{dst.buffer.name} is stored")
     covers(dst.origin, expr.shape, dst.buffer.shape, counts, "element-wise kernel")
+    return program, dst
+
+
+def match_rows(stores, counts, covers):
+    """``(program, destination view)`` when the single store of a body is an
+    expression of whole-row tiles that reduces along the rows (``sum`` / ``max``
+    / ``mean`` with ``axis=1, keepdims=True``) and uses the reduced values
+    again - the reference's softmax body (python/hckernel/tests/
+    test_examples.py:312-321) and its relatives; None when nothing is reduced.
+
+    The program is cut into passes: one per distinct reduction, in dependency
+    order (the argument of a reduction may use earlier reductions), each ending
+    in the instruction that reduces the accumulator into a row scalar; a last
+    pass computes the stored value with the scalars as operands."""
+    if len(stores) != 1:
+        return None
+    dst, expr = stores[0]
+    reductions = []
+
+    def collect(node):  # post-order: what a reduction depends on comes first
+        for arg in node.args:
+            if isinstance(arg, Tile):
+                collect(arg)
+        if node.op in _ROW_REDUCTIONS and not any(r.key() == node.key() for r in reductions):
+            reductions.append(node)
+
+    collect(expr)
+    if not reductions or expr.op in _ROW_REDUCTIONS:
+        return None
+    what = "row kernel"
+    if dst.buffer.ndim != 2 or len(expr.shape) != 2:
+        raise UnsupportedKernel(f"{what}: matrices expected")
+    if dst.buffer.dtype not in ("float32", "float64"):
+        raise UnsupportedKernel(f"{what}: float32 or float64, not {dst.buffer.dtype}")
+    if len(reductions) > MAX_SCALARS:
+        raise UnsupportedKernel(f"{what}: more than {MAX_SCALARS} different row reductions")
+    if expr.shape[1] != dst.buffer.shape[1]:
+        raise UnsupportedKernel(f"{what}: tiles must hold whole rows")
+    program = MapProgram(expr.shape)
+    for i, node in enumerate(reductions):
+        if node.attrs != {"axis": 1, "keepdims": True} or node.args[0].shape != expr.shape:
+            raise UnsupportedKernel(
+                f"{what}: reductions must be over whole rows with axis=1, keepdims=True")
+        program.evaluate(node.args[0])
+        program._emit(_ROW_REDUCTIONS[node.op], i)
+        program.scalars.append(node)
+        program._free = list(range(TEMPS))  # temporaries do not outlive a pass
+    program.evaluate(expr)
+    if len(program.inputs) > 2 or not program.inputs:
+        raise UnsupportedKernel(f"{what}: one or two input matrices")
+    for tile in program.inputs:
+        if tile.op != "load":
+            raise UnsupportedKernel(f"{what}: work-item reads inside a tile expression")
+        view = tile.args[0]
+        if view.buffer.shape != dst.buffer.shape or view.buffer.dtype != dst.buffer.dtype:
+            raise UnsupportedKernel(
+                f"{what}: {view.buffer.name} and {dst.buffer.name} differ in shape or element type")
+        if tuple(view.origin) != tuple(dst.origin):
+            raise UnsupportedKernel(
+                f"{what}: {view.buffer.name} is loaded at another origin than {dst.buffer.name} "
+                f"is stored")
+    covers(dst.origin, expr.shape, dst.buffer.shape, counts, what)
     return program, dst
 
 

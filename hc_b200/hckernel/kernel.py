@@ -37,7 +37,7 @@ import sympy
 
 from . import settings
 from .kernel_api import *  # noqa: F401,F403  (the reference re-exports kernel_api)
-from .elementwise import match_items, match_map
+from .elementwise import match_items, match_map, match_rows
 from .mapped import match_mapped
 from .kernel_api import (
     Affine,
@@ -573,6 +573,12 @@ class KernelDispatcher:
                 plan = matcher(recorder.stores, counts)
                 if plan is not None:
                     return plan
+            found = match_rows(recorder.stores, counts, _covers)
+            if found is not None:
+                program, dst = found
+                return _Plan("row_program", out=dst.buffer.index,
+                             inputs=[tile.args[0].buffer.index for tile in program.inputs],
+                             code=list(program.code), consts=list(program.consts))
             found = match_map(recorder.stores, counts, _covers)
             if found is not None:
                 program, dst = found
@@ -629,6 +635,9 @@ class KernelDispatcher:
         elif plan.family == "map_elements":
             native.map_elements(ctx, [args[i] for i in r["inputs"]], args[r["out"]], r["code"],
                                 r["consts"])
+        elif plan.family == "row_program":
+            native.row_program(ctx, [args[i] for i in r["inputs"]], args[r["out"]], r["code"],
+                               r["consts"])
         elif plan.family == "mapped_gemm":
             spec = r["spec"]
             x, f, out = args[r["x"]], args[r["f"]], args[r["out"]]

@@ -561,6 +561,10 @@ class Tile:
     def max(self, axis=None, keepdims=False, **_):
         return self._reduce("max", axis, keepdims)
 
+    def mean(self, axis=None, keepdims=False, **_):
+        count = self.size if axis is None else self.shape[axis % self.ndim]
+        return self._reduce("sum", axis, keepdims) / float(count)
+
     def astype(self, dtype, **_):
         return Tile("astype", (self,), self.shape, dtype_name(dtype))
 
@@ -612,7 +616,7 @@ class Tile:
         names = {"add": "add", "subtract": "sub", "multiply": "mul", "true_divide": "div",
                  "divide": "div", "maximum": "maximum", "minimum": "minimum"}
         unary = {"exp": "exp", "sqrt": "sqrt", "absolute": "abs", "fabs": "abs",
-                 "negative": "neg"}
+                 "negative": "neg", "log": "log"}
         if ufunc.__name__ in unary:
             (x,) = inputs
             return x._unary(unary[ufunc.__name__])
@@ -628,6 +632,8 @@ class Tile:
             return args[0].sum(*args[1:], **kwargs)
         if func in (np.max, np.amax):
             return args[0].max(*args[1:], **kwargs)
+        if func is np.mean:
+            return args[0].mean(*args[1:], **kwargs)
         if func is np.linalg.norm:
             extra = {k: v for k, v in kwargs.items() if k != "axis" and v is not None and v is not False}
             if len(args) != 1 or extra or not isinstance(kwargs.get("axis"), int):

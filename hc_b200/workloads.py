@@ -137,6 +137,33 @@ def make_elementwise(fn, inputs=1, rank=2, group_shape=None, device="cuda:0"):
     raise ValueError("one to three inputs")
 
 
+def make_rowwise(fn, inputs=1, device="cuda:0"):
+    """A row kernel ``k(a[, b], out, group_rows)``: every work-group loads whole
+    rows of each input, stores ``fn`` of them.  ``fn`` may reduce along the rows
+    (``.sum/.max/.mean(axis=1, keepdims=True)``) and use the reduced values
+    again, like the reference's softmax body
+    (python/hckernel/tests/test_examples.py:312-321)."""
+    target = dict(backend="nvvm", device=device)
+    M, N, GM = sym.M, sym.N, sym.GM
+    if inputs == 1:
+        @kernel(work_shape=M, group_shape=GM, **target)
+        def rows1(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
+            m0 = gr.work_offset[0]
+            gr.store(out[m0:, :], fn(gr.load(a[m0:, :], shape=(gr.shape[0], N))))
+
+        return rows1
+    if inputs == 2:
+        @kernel(work_shape=M, group_shape=GM, **target)
+        def rows2(gr: CurrentGroup, a: Buffer[M, N, DT], b: Buffer[M, N, DT], out: Buffer[M, N, DT],
+                  gshape: GM):
+            m0 = gr.work_offset[0]
+            gr.store(out[m0:, :], fn(gr.load(a[m0:, :], shape=(gr.shape[0], N)),
+                                     gr.load(b[m0:, :], shape=(gr.shape[0], N))))
+
+        return rows2
+    raise ValueError("one or two inputs")
+
+
 def make_conv(stride=1, device="cuda:0"):
     """The convolution written as an implicit GEMM, as in the reference's
     example (python/hckernel/tests/test_examples.py:203-252): ``conv(x, f, out)``

@@ -107,6 +107,7 @@ HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
  * three temporaries.  An instruction is `op | (src << 8)`:
  *   op   0 load  1 add  2 sub  3 rsub (v - acc)  4 mul  5 div  6 rdiv (v / acc)
  *        7 max  8 min  9 neg  10 abs  11 exp  12 sqrt  13..15 save to t0..t2
+ *        16 log
  *   src  0..3 input arrays, 4..6 temporaries t0..t2, 8..15 consts[0..7],
  *        16 / 17 the row / column index of the element, as a value (what a body
  *        written at work-item level gets from global_id(),
@@ -126,6 +127,20 @@ typedef struct HcMapProgram {
   double consts[8];
 } HcMapProgram;
 HC_B200_API int hcMapElements(HcContext c, const HcMapProgram *program, int dtype);
+
+/* Row program: out[r,:] = f(in0[r,:], in1[r,:]) where f may reduce along the
+ * row and use the reduced values again - the reference's row softmax
+ * (python/hckernel/tests/test_examples.py:312-321) generalised to any such
+ * expression (centring, normalising, scaling rows by their own statistics).
+ * Same program structure as hcMapElements (1 or 2 inputs, op 16 = log), with
+ *   op   17 rsum / 18 rmax: end a pass over the row, reduce the accumulator
+ *        along it into row scalar s[src], src 0..3 (max gives NaN if the row
+ *        holds one); the next instruction must be a load
+ *   src  20..23 the row scalars s0..s3, once reduced
+ * The program must end with a pass that is not a reduction: its accumulator is
+ * stored.  Temporaries do not carry over from one pass to the next; element
+ * indices (src 16/17) are not available. */
+HC_B200_API int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype);
 
 /* Row softmax over the last axis, HC_F32 or HC_F64
  * (python/hckernel/tests/test_examples.py:304-321). */

@@ -255,6 +255,50 @@ def elementwise_cases():
     ]
 
 
+def rowwise(fn, inputs, out, group_rows: int = 8) -> None:
+    """A body that loads ``group_rows`` whole rows per input, computes ``fn`` of
+    them - which may reduce along the rows and use the reduced values again, as
+    the reference's softmax does (python/hckernel/tests/test_examples.py:
+    312-321) - and stores the rows.  Same tile arithmetic as
+    :func:`elementwise`; reductions reach ``numpy.ma`` through the tile wrapper
+    (python/hckernel/kernel_api.py:150-151) and ignore the padding rows."""
+    cols = out.shape[1]
+    for _, (m0,) in iter_groups(out.shape[0], group_rows):
+        tiles = [arithmetic_tile(load_tile(a[m0:, :], (group_rows, cols))) for a in inputs]
+        with np.errstate(all="ignore"):
+            store_result(out[m0:, :], fn(*tiles))
+
+
+def rowwise_cases():
+    """``(name, fn, number of inputs, shape, dtype, rows per group)`` of the row
+    bodies stored under ``tests/golden``; every ``fn`` runs unchanged on the
+    reference simulator's tiles, on NumPy arrays and on recorded tiles."""
+    def centre(t):
+        return t - t.mean(axis=1, keepdims=True)
+
+    def l2_normalise(t):
+        return t / np.sqrt((t * t).sum(axis=1, keepdims=True))
+
+    def log_softmax(t):
+        shifted = t - t.max(axis=1, keepdims=True)
+        return shifted - np.log(np.exp(shifted).sum(axis=1, keepdims=True))
+
+    def softmax_temperature(t):
+        e = np.exp((t - t.max(axis=1, keepdims=True)) * 0.5)
+        return e / e.sum(axis=1, keepdims=True)
+
+    def scaled_difference(a, b):
+        return (a - b) / np.maximum(np.abs(a).max(axis=1, keepdims=True), 1.0)
+
+    return [
+        ("rows_centre_f32", centre, 1, (37, 300), "float32", 8),
+        ("rows_l2_normalise_f64", l2_normalise, 1, (30, 25), "float64", 8),
+        ("rows_log_softmax_f32", log_softmax, 1, (48, 1024), "float32", 16),
+        ("rows_softmax_temperature_f32", softmax_temperature, 1, (19, 130), "float32", 4),
+        ("rows_scaled_difference_f32", scaled_difference, 2, (64, 512), "float32", 32),
+    ]
+
+
 def random_expression(rng, inputs: int, depth: int):
     """A random element-wise function of ``inputs`` arrays as ``(fn, text)``:
     a tree of + - * /, maximum, minimum, abs, negation and sqrt(abs(.)) over the

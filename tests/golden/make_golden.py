@@ -240,6 +240,27 @@ def ref_map(fn, count, rank, group):
     return k4
 
 
+def ref_rows(fn, count):
+    """A row body in the reference's DSL: whole rows loaded, ``fn`` stored."""
+    M, N, GM = sym.M, sym.N, sym.GM
+    if count == 1:
+        @kernel(work_shape=M, group_shape=GM)
+        def r1(gr: CurrentGroup, a: Buffer[M, N, DT], out: Buffer[M, N, DT], gshape: GM):
+            m0 = gr.work_offset[0]
+            gr.store(out[m0:, :], fn(gr.load(a[m0:, :], shape=(gr.shape[0], N))))
+
+        return r1
+
+    @kernel(work_shape=M, group_shape=GM)
+    def r2(gr: CurrentGroup, a: Buffer[M, N, DT], b: Buffer[M, N, DT], out: Buffer[M, N, DT],
+           gshape: GM):
+        m0 = gr.work_offset[0]
+        gr.store(out[m0:, :], fn(gr.load(a[m0:, :], shape=(gr.shape[0], N)),
+                                 gr.load(b[m0:, :], shape=(gr.shape[0], N))))
+
+    return r2
+
+
 def ref_copy():
     W, H = sym.W, sym.H
 
@@ -430,6 +451,19 @@ def main():
         # reference's tiles carry Python-float operands on in float64 where
         # NumPy arrays stay in float32.
         np.testing.assert_allclose(r, fn(*inputs), rtol=3e-7 if dtype == "float32" else 0)
+        out[name] = r
+
+    # 7. Row bodies: reductions along the rows used again in the same expression.
+    for name, fn, count, shape, dtype, group_rows in oracle.rowwise_cases():
+        inputs = oracle.make_elementwise_inputs(count, shape, dtype, seed=8)
+        r = np.zeros(shape, dtype)
+        with np.errstate(all="ignore"):
+            ref_rows(fn, count)(*inputs, r, group_rows)
+        o = np.zeros(shape, dtype)
+        oracle.rowwise(fn, inputs, o, group_rows)
+        same(name, r, o)
+        np.testing.assert_allclose(r, fn(*inputs), rtol=2e-6 if dtype == "float32" else 1e-14,
+                                   atol=1e-6 if dtype == "float32" else 0)
         out[name] = r
 
     np.savez_compressed(HERE / "reference_outputs.npz", **out)

@@ -28,12 +28,19 @@ def run_program(code, consts, inputs, dtype, shape=None):
     """The machine of map_elements.cu, one NumPy operation per instruction."""
     dtype = np.dtype(dtype).type
     shape = inputs[0].shape if shape is None else shape
-    acc, temps = None, [None, None, None]
+    acc, temps, scalars = None, [None, None, None], [None] * 4
     with np.errstate(all="ignore"):
         for ins in code:
             op, src = ins & 0xFF, ins >> 8
+            if op in (ew.RSUM, ew.RMAX):  # row programs: reduce along the rows, end the pass
+                reduce = np.sum if op == ew.RSUM else np.max
+                scalars[src] = reduce(acc, axis=1, keepdims=True).astype(dtype)
+                acc, temps = None, [None, None, None]
+                continue
             if op <= ew.MIN:
-                if src >= ew.SRC_ROW:  # the element's own row / column index
+                if src >= ew.SRC_SCALAR:
+                    v = np.broadcast_to(scalars[src - ew.SRC_SCALAR], shape)
+                elif src >= ew.SRC_ROW:  # the element's own row / column index
                     rows, cols = np.indices(np.atleast_2d(np.empty(shape)).shape)
                     v = (rows if src == ew.SRC_ROW else cols).reshape(shape).astype(dtype)
                 else:
@@ -53,6 +60,7 @@ def run_program(code, consts, inputs, dtype, shape=None):
             elif op == ew.ABS: acc = np.abs(acc)
             elif op == ew.EXP: acc = np.exp(acc)
             elif op == ew.SQRT: acc = np.sqrt(acc)
+            elif op == ew.LOG: acc = np.log(acc)
             else: temps[op - ew.SAVE0] = acc
             assert acc.dtype == dtype
     return acc

@@ -1,0 +1,125 @@
+"""GPU parity of row bodies (reductions along the rows used again in the same
+expression): through the ``@kernel`` front door against the outputs of the
+reference simulator (tests/golden) and against NumPy, and hcRowProgram called
+directly through the C-ABI.
+
+Tolerances: a row sum is a running value per lane plus a shuffle tree, NumPy's
+is pairwise, and exp/log are within a few ulp, so float32 results agree to
+2e-6 relative (1e-6 absolute near zero), float64 to 1e-13; row max is exact."""
+
+import numpy as np
+import pytest
+import torch
+
+from hc_b200 import capi
+from hc_b200.hckernel import elementwise as ew
+from hc_b200.workloads import make_rowwise
+from oracle import workloads as oracle
+from tests.gpu_util import finish
+
+pytestmark = pytest.mark.gpu
+
+CASES = oracle.rowwise_cases()
+TOL = {"float32": dict(rtol=2e-6, atol=1e-6), "float64": dict(rtol=1e-13, atol=1e-15)}
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c[0])
+def test_row_bodies_match_reference_and_numpy(golden, case):
+    name, fn, count, shape, dtype, group_rows = case
+    inputs = oracle.make_elementwise_inputs(count, shape, dtype, seed=8)
+    k = make_rowwise(fn, count)
+    d_in = [torch.from_numpy(a).cuda() for a in inputs]
+    d_out = torch.full(shape, float("nan"), dtype=d_in[0].dtype, device="cuda")
+    k(*d_in, d_out, group_rows)
+    torch.cuda.synchronize()
+    got = d_out.cpu().numpy()
+    with np.errstate(all="ignore"):
+        np.testing.assert_allclose(got, fn(*inputs), **TOL[dtype])
+    np.testing.assert_allclose(got, golden[name], **TOL[dtype])
+
+
+@pytest.mark.parametrize("shape,pitch", [((33, 4096), 4096), ((7, 1001), 1001), ((300, 36), 40),
+                                         ((1, 1), 1), ((9, 8), 8)])
+def test_rows_of_many_lengths_and_pitches(shape, pitch):
+    """Long rows, rows that are not multiples of 16 bytes, pitched views, fewer
+    rows than a CTA holds."""
+    rng = np.random.default_rng(shape[0] * 7 + shape[1])
+    a = rng.standard_normal(shape).astype(np.float32)
+    k = make_rowwise(lambda t: (t - t.mean(axis=1, keepdims=True))
+                     / np.sqrt((t * t).sum(axis=1, keepdims=True) + 1.0))
+    store = torch.zeros((2, shape[0], pitch), device="cuda")
+    d_a, d_out = store[0, :, : shape[1]], store[1, :, : shape[1]]
+    d_a.copy_(torch.from_numpy(a))
+    k(d_a, d_out, 16)
+    torch.cuda.synchronize()
+    a64 = a.astype(np.float64)
+    want = (a64 - a64.mean(axis=1, keepdims=True)) / np.sqrt((a64 * a64).sum(axis=1, keepdims=True) + 1)
+    np.testing.assert_allclose(d_out.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    if pitch > shape[1]:
+        assert float(store[1, :, shape[1]:].abs().max()) == 0.0
+
+
+def test_row_max_propagates_nan_like_numpy():
+    a = np.array([[1.0, np.nan, 3.0, 0.0], [1.0, 2.0, 3.0, 4.0]], np.float32)
+    k = make_rowwise(lambda t: t - t.max(axis=1, keepdims=True))
+    d_out = torch.zeros((2, 4), device="cuda")
+    k(torch.from_numpy(a).cuda(), d_out, 2)
+    torch.cuda.synchronize()
+    got = d_out.cpu().numpy()
+    assert np.all(np.isnan(got[0])) and np.array_equal(got[1], [-3.0, -2.0, -1.0, 0.0])
+
+
+def test_row_program_through_the_c_abi(hc):
+    """Variance-normalise rows in float64: s0 = sum(x); s1 = sum((x - s0/N)^2);
+    out = (x - s0/N) / sqrt(s1/N)."""
+    rng = np.random.default_rng(4)
+    rows, cols = 21, 50
+    x = rng.standard_normal((rows, cols))
+    d_x = torch.from_numpy(x).cuda()
+    d_out = torch.zeros((rows, cols), dtype=torch.float64, device="cuda")
+    p = capi.HcMapProgram()
+    p.inputs[0], p.inPitch[0], p.outPitch = d_x.data_ptr(), cols, cols
+    p.out, p.rows, p.cols, p.nInputs = d_out.data_ptr(), rows, cols, 1
+    c0, s0, s1, t0 = ew.SRC_CONST, ew.SRC_SCALAR, ew.SRC_SCALAR + 1, ew.SRC_TEMP
+    program = [
+        ew.LOAD | 0 << 8, ew.RSUM | 0 << 8,                                   # s0 = sum(x)
+        ew.LOAD | s0 << 8, ew.MUL | c0 << 8, ew.RSUB | 0 << 8,                # x - s0/N
+        ew.SAVE0, ew.MUL | t0 << 8, ew.RSUM | 1 << 8,                         # s1 = sum(d*d)
+        ew.LOAD | s1 << 8, ew.MUL | c0 << 8, ew.SQRT, ew.SAVE0,               # t0 = sqrt(s1/N)
+        ew.LOAD | s0 << 8, ew.MUL | c0 << 8, ew.RSUB | 0 << 8, ew.DIV | t0 << 8,
+    ]
+    p.nInstr = len(program)
+    for i, ins in enumerate(program):
+        p.code[i] = ins
+    p.consts[0] = 1.0 / cols
+    hc.row_program(p, capi.HC_F64)
+    finish(hc)
+    mean = x.sum(axis=1, keepdims=True) * (1.0 / cols)
+    want = (x - mean) / np.sqrt(((x - mean) ** 2).sum(axis=1, keepdims=True) * (1.0 / cols))
+    np.testing.assert_allclose(d_out.cpu().numpy(), want, rtol=1e-13)
+
+    # Malformed programs are refused before anything is launched.
+    p.code[len(program) - 1] = ew.RSUM | 2 << 8
+    with pytest.raises(RuntimeError, match="ends in a reduction"):
+        hc.row_program(p, capi.HC_F64)
+    p.code[len(program) - 1] = ew.DIV | t0 << 8
+    p.code[2] = ew.ADD | s0 << 8
+    with pytest.raises(RuntimeError, match="after a reduction must load"):
+        hc.row_program(p, capi.HC_F64)
+    p.code[2] = ew.LOAD | (ew.SRC_SCALAR + 3) << 8
+    with pytest.raises(RuntimeError, match="not written yet"):
+        hc.row_program(p, capi.HC_F64)
+    p.code[2] = ew.LOAD | s0 << 8
+    p.code[6] = ew.MUL | (t0 + 1) << 8
+    with pytest.raises(RuntimeError, match="not written yet"):
+        hc.row_program(p, capi.HC_F64)
+    p.code[6] = ew.MUL | t0 << 8
+    p.code[1] = ew.RSUM | 7 << 8
+    with pytest.raises(RuntimeError, match="row scalar 7"):
+        hc.row_program(p, capi.HC_F64)
+    p.code[1] = ew.RSUM | 0 << 8
+    with pytest.raises(RuntimeError, match="row reductions belong to hcRowProgram"):
+        hc.map_elements(p, capi.HC_F64)
+    p.nInputs = 3
+    with pytest.raises(RuntimeError, match="inputs"):
+        hc.row_program(p, capi.HC_F64)
