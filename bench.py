@@ -51,6 +51,9 @@ SHAPES = {
     # Element-wise body out = max(2a - b, 0) on fp32 matrices (three 512 MiB
     # arrays; likewise measured as a further kernel family).
     "map": (32768, 4096),
+    # Row body with reductions used again (log-softmax), interpreted as a
+    # three-pass row program; same shape as the softmax configuration.
+    "rows": (32768, 4096),
 }
 # Tile sizes (TN images x TNF filters per work-group, K block) the conv is run with.
 CONV_TILES = (32, 64, 16)
@@ -65,6 +68,7 @@ SMALL_SHAPES = {
     "gemm_w8a16": (1024, 2048, 2048),
     "conv": (32, 64, 30, 30, 64, 3, 3, 1),
     "map": (8192, 4096),
+    "rows": (8192, 4096),
 }
 
 # fp32 FMA rate of the CUDA cores, nominal (no measured figure exists for it):
@@ -74,6 +78,7 @@ FP32_NOMINAL_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 METRIC = {
     "conv": "conv_implicit_gemm_f32_throughput",
     "map": "elementwise_relu_axpby_f32_algorithmic_bandwidth",
+    "rows": "row_program_log_softmax_f32_algorithmic_bandwidth",
     "softmax": "softmax_rows_f32_algorithmic_bandwidth",
     "reduce": "reduce_rows_f32_algorithmic_bandwidth",
     "gemm_f32": "gemm_f32_tiled_throughput",
@@ -81,7 +86,7 @@ METRIC = {
     "gemm_w8a16": "gemm_w8a16_throughput",
 }
 DTYPE = {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32", "gemm_bf16": "bf16",
-         "gemm_w8a16": "bf16", "conv": "f32", "map": "f32"}
+         "gemm_w8a16": "bf16", "conv": "f32", "map": "f32", "rows": "f32"}
 
 
 def relu_axpby(a, b):
@@ -89,6 +94,14 @@ def relu_axpby(a, b):
     import numpy as np
 
     return np.maximum(a * 2.0 - b, 0.0)
+
+
+def log_softmax(t):
+    """The row body of the ``rows`` workload."""
+    import numpy as np
+
+    shifted = t - t.max(axis=1, keepdims=True)
+    return shifted - np.log(np.exp(shifted).sum(axis=1, keepdims=True))
 
 
 def conv_shapes(s):
@@ -106,7 +119,7 @@ def algorithmic(name):
         size = lambda shape: shape[0] * shape[1] * shape[2] * shape[3]  # noqa: E731
         return ((size(xs) + size(fs) + size(os_)) * 4,
                 2 * size(os_) * fs[1] * fs[2] * fs[3], "fp32")
-    if name == "softmax":
+    if name in ("softmax", "rows"):
         m, n = s
         return 2 * m * n * 4, 0, "hbm"
     if name == "map":
@@ -153,6 +166,7 @@ NCU_TRAFFIC = {
     # profiles/map_elements_f32_v4_n2_8192x4096.md: (268.49 + 97.94) MB for a quarter of the
     # rows, scaled by 4 (the part of the output still in L2 at kernel end is not counted).
     "map": 1465.7e6,
+    "rows": None,
 }
 
 
@@ -282,6 +296,17 @@ def cpu_sample(name, threads, repeats):
 
         def one_pass():
             oracle.gemm_bf16(a, b, out, (256, 256))
+    elif name == "rows":
+        rows = min(s[0], 8192 if threads > 1 else 2048)
+        (x,) = oracle.make_inputs("softmax", shape=(rows, s[1]))
+        out = np.empty_like(x)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows, groups of 256 rows"
+
+        def one_pass():
+            oracle.run_row_groups_parallel(
+                lambda r0, r1: oracle.rowwise(log_softmax, [x[r0:r1]], out[r0:r1], 256),
+                rows, 256, threads)
     elif name == "map":
         rows = min(s[0], 8192 if threads > 1 else 2048)
         a, b = oracle.make_elementwise_inputs(2, (rows, s[1]), "float32")
@@ -401,7 +426,7 @@ def run_gpu(args):
         """Device-resident synthetic inputs and outputs of one workload."""
         g = torch.Generator(device=dev).manual_seed(1000 + rank)
         s = SHAPES[name]
-        if name == "softmax":
+        if name in ("softmax", "rows"):
             x = torch.randn(*s, device=dev, generator=g)
             return [x], [torch.empty_like(x)]
         if name == "reduce":
@@ -442,6 +467,15 @@ def run_gpu(args):
                 {sym.TN: tn, sym.TNF: tnf, sym.KB: kb}))
         return conv_cache[0]
 
+    rows_cache = []
+
+    def rows_kernel():
+        if not rows_cache:
+            from hc_b200.workloads import make_rowwise
+
+            rows_cache.append(make_rowwise(log_softmax, 1, desc))
+        return rows_cache[0]
+
     map_cache = []
 
     def map_kernel():
@@ -463,6 +497,10 @@ def run_gpu(args):
             roles = map_kernel().plan_for((ins[0], ins[1], outs[0])).roles
             arrays = [ins[i] for i in roles["inputs"]]
             return lambda: native.map_elements(ctx, arrays, outs[0], roles["code"], roles["consts"])
+        if name == "rows":
+            roles = rows_kernel().plan_for((ins[0], outs[0], 256)).roles
+            return lambda: native.row_program(ctx, [ins[0]], outs[0], roles["code"],
+                                              roles["consts"])
         if name == "conv":
             # The index tables belong to the launch plan; made once, outside the timing.
             spec = conv_kernel().plan_for((ins[0], ins[1], outs[0])).roles["spec"]
@@ -487,6 +525,8 @@ def run_gpu(args):
             return lambda: conv_kernel()(ins[0], ins[1], outs[0])
         if name == "map":
             return lambda: map_kernel()(ins[0], ins[1], outs[0])
+        if name == "rows":
+            return lambda: rows_kernel()(ins[0], outs[0], 256)
         return lambda: kernels.dequant_dot(ins[0], ins[1], ins[2], outs[0], (256, 256))
 
     def roofline(name, per_step_ms):
@@ -569,7 +609,7 @@ def run_gpu(args):
         extras = {}
         if name == "softmax" and not args.no_extras:
             for other, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
-                                 ("gemm_f32", 500), ("conv", 50), ("map", 200)):
+                                 ("gemm_f32", 500), ("conv", 50), ("map", 200), ("rows", 200)):
                 # Each kernel is timed alone: let the board's power state settle
                 # after the previous one (a dense GEMM runs into the 1 kW cap and
                 # would hand lower clocks to whatever is measured right after it).

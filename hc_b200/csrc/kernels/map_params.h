@@ -29,8 +29,15 @@ enum HcMapOp : uint32_t {
   // accumulator along it into row scalar s[src].
   HC_MAP_RSUM = 17,
   HC_MAP_RMAX = 18,
-  HC_MAP_OP_COUNT = 19
+  // Row programs only, in the uniform prologue of a pass: s[src] = acc.
+  HC_MAP_SET = 19,
+  HC_MAP_OP_COUNT = 20
 };
+// Row programs only: an instruction with this bit set in its operation byte is
+// uniform - it works on one value per row (operands: constants and row
+// scalars) and runs once, before the pass walks the row.  A pass may begin
+// with such instructions; they end in HC_MAP_SET.
+constexpr uint32_t HC_MAP_UNIFORM = 0x80;
 
 // Operand names: inputs 0..3, temporaries t0..t2, constants 0..7, and the row
 // and column index of the element itself (as a value of the element type).

@@ -50,6 +50,47 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
 
   int pc = 0;
   while (pc < p.nInstr) {
+    // Uniform prologue: expressions of row scalars and constants only (the
+    // log of a sum, a mean from a sum ...) are computed once per row here,
+    // not once per element in the walk below.
+    T one = T(0);
+    for (; pc < p.nInstr && (p.code[pc] & HC_MAP_UNIFORM); ++pc) {
+      const uint32_t op = p.code[pc] & 0x7fu, src = p.code[pc] >> 8;
+      T b = T(0);
+      if (op <= HC_MAP_MIN) {
+        if (src >= HC_MAP_SRC_SCALAR) {
+          const uint32_t k = src - HC_MAP_SRC_SCALAR;
+          b = k == 0 ? scalars[0] : k == 1 ? scalars[1] : k == 2 ? scalars[2] : scalars[3];
+        } else {
+          b = T(p.consts[src - HC_MAP_SRC_CONST]);
+        }
+      }
+      switch (op) {
+      case HC_MAP_LOAD: one = b; break;
+      case HC_MAP_ADD: one = one + b; break;
+      case HC_MAP_SUB: one = one - b; break;
+      case HC_MAP_RSUB: one = b - one; break;
+      case HC_MAP_MUL: one = one * b; break;
+      case HC_MAP_DIV: one = one / b; break;
+      case HC_MAP_RDIV: one = b / one; break;
+      case HC_MAP_MAX: one = maxOf(one, b); break;
+      case HC_MAP_MIN: one = minOf(one, b); break;
+      case HC_MAP_NEG: one = -one; break;
+      case HC_MAP_ABS: one = one < T(0) ? -one : (one == T(0) ? T(0) : one); break;
+      case HC_MAP_EXP: one = expOf(one); break;
+      case HC_MAP_SQRT: one = sqrt(one); break;
+      case HC_MAP_LOG: one = logOf(one); break;
+      case HC_MAP_SET:
+        switch (src) {
+        case 0: scalars[0] = one; break;
+        case 1: scalars[1] = one; break;
+        case 2: scalars[2] = one; break;
+        default: scalars[3] = one; break;
+        }
+        break;
+      default: break;
+      }
+    }
     // The pass runs to the next reduction instruction or to the end.
     int end = pc;
     uint32_t reduction = 0, target = 0;

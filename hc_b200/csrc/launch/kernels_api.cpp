@@ -436,9 +436,50 @@ static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &
   bool saved[3] = {false, false, false};
   bool reduced[HC_MAP_MAX_SCALARS] = {false, false, false, false};
   bool passStart = true;
+  bool uniformLoaded = false; // inside a uniform prologue: its accumulator holds a value
   for (int pc = 0; pc < p.nInstr; ++pc) {
-    const uint32_t op = p.code[pc] & 0xffu, src = p.code[pc] >> 8;
-    if (op >= HC_MAP_OP_COUNT)
+    const uint32_t src = p.code[pc] >> 8;
+    uint32_t op = p.code[pc] & 0xffu;
+    if (op & HC_MAP_UNIFORM) {
+      // One value per row, computed before the pass walks the row.
+      op &= 0x7fu;
+      if (!rowProgram)
+        return c->fail("%s: uniform instructions belong to hcRowProgram (instruction %d)", who,
+                       pc);
+      if (!passStart)
+        return c->fail("%s: uniform instruction %d is not at the start of a pass", who, pc);
+      if (pc == p.nInstr - 1)
+        return c->fail("%s: the program ends in a uniform instruction; a last pass must compute "
+                       "what is stored",
+                       who);
+      const bool arithmetic = op <= HC_MAP_SQRT || op == HC_MAP_LOG;
+      if (!arithmetic && op != HC_MAP_SET)
+        return c->fail("%s: operation %u cannot be uniform (instruction %d)", who, op, pc);
+      if (op != HC_MAP_LOAD && !uniformLoaded)
+        return c->fail("%s: uniform instruction %d uses an accumulator that holds nothing", who,
+                       pc);
+      if (op <= HC_MAP_MIN) {
+        const bool constant =
+            src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + uint32_t(HC_MAP_MAX_CONSTS);
+        const bool scalar = src >= HC_MAP_SRC_SCALAR &&
+                            src < HC_MAP_SRC_SCALAR + uint32_t(HC_MAP_MAX_SCALARS) &&
+                            reduced[src - HC_MAP_SRC_SCALAR];
+        if (!constant && !scalar)
+          return c->fail("%s: uniform instruction %d reads operand %u; only constants and row "
+                         "scalars that are already set can be read there",
+                         who, pc, src);
+      }
+      uniformLoaded = true;
+      if (op == HC_MAP_SET) {
+        if (src >= uint32_t(HC_MAP_MAX_SCALARS))
+          return c->fail("%s: instruction %d sets row scalar %u of %d", who, pc, src,
+                         HC_MAP_MAX_SCALARS);
+        reduced[src] = true;
+        uniformLoaded = false;
+      }
+      continue;
+    }
+    if (op >= HC_MAP_OP_COUNT || op == HC_MAP_SET)
       return c->fail("%s: unknown operation %u at instruction %d", who, op, pc);
     if (passStart && op != HC_MAP_LOAD)
       return c->fail(pc == 0 ? "%s: the first instruction must load the accumulator"

@@ -25,7 +25,8 @@ or more than 32 instructions is refused.
 from .kernel_api import Tile, UnsupportedKernel
 
 LOAD, ADD, SUB, RSUB, MUL, DIV, RDIV, MAX, MIN, NEG, ABS, EXP, SQRT, SAVE0 = range(14)
-LOG, RSUM, RMAX = 16, 17, 18
+LOG, RSUM, RMAX, SET = 16, 17, 18, 19
+UNIFORM = 0x80  # flag in the operation byte: one value per row, computed before the walk
 SRC_TEMP, SRC_CONST, SRC_SCALAR = 4, 8, 20
 MAX_INPUTS, MAX_CONSTS, MAX_INSTR, TEMPS, MAX_SCALARS = 4, 8, 32, 3, 4
 
@@ -45,9 +46,88 @@ class MapProgram:
         self._free = list(range(TEMPS))
         self.index_sources = index_sources  # work axis -> operand name (work-item level only)
         self.scalars = []  # row programs: the reductions already computed, in scalar order
+        # Row programs: expressions of row scalars and constants only are computed
+        # once per row, in a uniform prologue of the pass that first needs them,
+        # and kept in a row scalar of their own.
+        self.row_mode = False
+        self.reserved_scalars = 0   # scalars 0..n-1 belong to the reductions
+        self.hoisted = []           # uniform nodes that got a scalar, in order
+        self._prologue = []         # uniform instructions of the pass being written
+        self._pass_start = 0
+
+    # -- row programs: passes and uniform prologues ---------------------------------------
+    def begin_pass(self):
+        self._pass_start, self._prologue = len(self.code), []
+        self._free = list(range(TEMPS))  # temporaries do not outlive a pass
+
+    def end_pass(self):
+        if len(self.code) + len(self._prologue) > MAX_INSTR:
+            raise UnsupportedKernel(f"element-wise kernel: more than {MAX_INSTR} operations")
+        self.code[self._pass_start:self._pass_start] = self._prologue
+        self._prologue = []
+
+    def _scalar_of(self, node):
+        for i, seen in enumerate(self.scalars):
+            if seen.key() == node.key():
+                return SRC_SCALAR + i
+        for i, seen in enumerate(self.hoisted):
+            if seen.key() == node.key():
+                return SRC_SCALAR + self.reserved_scalars + i
+        return None
+
+    def _is_uniform(self, node):
+        if not isinstance(node, Tile):
+            return False
+        if node.op in ("const", "alloc") or self._scalar_of(node) is not None:
+            return True
+        if node.op in _UNARY or node.op in _BINARY:
+            return all(self._is_uniform(a) for a in node.args)
+        return False
+
+    def _uniform_chain(self, node):
+        """Instructions that compute a uniform expression in the one-value
+        accumulator of the prologue (which has no temporaries), or None."""
+        src = self._scalar_of(node)
+        if src is None and node.op in ("const", "alloc"):
+            src = self._leaf(node)
+        if src is not None:
+            return [LOAD | (src << 8)]
+        if node.op in _UNARY:
+            inner = self._uniform_chain(node.args[0])
+            return None if inner is None else inner + [_UNARY[node.op]]
+        forward, reverse = _BINARY[node.op]
+        left, right = node.args
+        for operand, other, op in ((right, left, forward), (left, right, reverse)):
+            src = self._scalar_of(operand)
+            if src is None and operand.op in ("const", "alloc"):
+                src = self._leaf(operand)
+            if src is not None:
+                inner = self._uniform_chain(other)
+                return None if inner is None else inner + [op | (src << 8)]
+        return None
+
+    def _hoist(self, node):
+        """Row scalar that holds the uniform expression ``node``, computing it in
+        the prologue of the current pass on first use; None if it cannot be."""
+        known = self._scalar_of(node)
+        if known is not None:
+            return known
+        index = self.reserved_scalars + len(self.hoisted)
+        if index >= MAX_SCALARS:
+            return None
+        chain = self._uniform_chain(node)
+        if chain is None:
+            return None
+        self._prologue += [ins | UNIFORM for ins in chain] + [SET | UNIFORM | (index << 8)]
+        self.hoisted.append(node)
+        return SRC_SCALAR + index
 
     def _leaf(self, node):
         """Operand name of a leaf, or None for an inner node."""
+        if self.row_mode and (node.op in _UNARY or node.op in _BINARY) and self._is_uniform(node):
+            hoisted = self._hoist(node)
+            if hoisted is not None:
+                return hoisted
         if node.op in _ROW_REDUCTIONS:  # a value an earlier pass of a row program reduced
             for i, seen in enumerate(self.scalars):
                 if seen.key() == node.key():
@@ -203,15 +283,19 @@ def match_rows(stores, counts, covers):
     if expr.shape[1] != dst.buffer.shape[1]:
         raise UnsupportedKernel(f"{what}: tiles must hold whole rows")
     program = MapProgram(expr.shape)
+    program.row_mode, program.reserved_scalars = True, len(reductions)
     for i, node in enumerate(reductions):
         if node.attrs != {"axis": 1, "keepdims": True} or node.args[0].shape != expr.shape:
             raise UnsupportedKernel(
                 f"{what}: reductions must be over whole rows with axis=1, keepdims=True")
+        program.begin_pass()
         program.evaluate(node.args[0])
         program._emit(_ROW_REDUCTIONS[node.op], i)
+        program.end_pass()
         program.scalars.append(node)
-        program._free = list(range(TEMPS))  # temporaries do not outlive a pass
+    program.begin_pass()
     program.evaluate(expr)
+    program.end_pass()
     if len(program.inputs) > 2 or not program.inputs:
         raise UnsupportedKernel(f"{what}: one or two input matrices")
     for tile in program.inputs:

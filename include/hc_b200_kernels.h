@@ -136,7 +136,11 @@ HC_B200_API int hcMapElements(HcContext c, const HcMapProgram *program, int dtyp
  *   op   17 rsum / 18 rmax: end a pass over the row, reduce the accumulator
  *        along it into row scalar s[src], src 0..3 (max gives NaN if the row
  *        holds one); the next instruction must be a load
- *   src  20..23 the row scalars s0..s3, once reduced
+ *   src  20..23 the row scalars s0..s3, once reduced or set
+ * A pass may open with uniform instructions - operation byte | 0x80 - that work
+ * on one value per row (operands: constants and row scalars) and run once per
+ * row instead of once per element; such a sequence starts with a load and ends
+ * with op 19 set: s[src] = that value (the log of a sum, a mean from a sum).
  * The program must end with a pass that is not a reduction: its accumulator is
  * stored.  Temporaries do not carry over from one pass to the next; element
  * indices (src 16/17) are not available. */

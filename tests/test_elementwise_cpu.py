@@ -28,10 +28,26 @@ def run_program(code, consts, inputs, dtype, shape=None):
     """The machine of map_elements.cu, one NumPy operation per instruction."""
     dtype = np.dtype(dtype).type
     shape = inputs[0].shape if shape is None else shape
-    acc, temps, scalars = None, [None, None, None], [None] * 4
+    acc, temps, scalars, one = None, [None, None, None], [None] * 4, None
     with np.errstate(all="ignore"):
         for ins in code:
             op, src = ins & 0xFF, ins >> 8
+            if op & ew.UNIFORM:  # row programs: one value per row, before the pass walks it
+                op &= 0x7F
+                if op <= ew.MIN:
+                    b = scalars[src - ew.SRC_SCALAR] if src >= ew.SRC_SCALAR \
+                        else dtype(consts[src - ew.SRC_CONST])
+                if op == ew.SET:
+                    scalars[src] = np.broadcast_to(one, (shape[0], 1)).astype(dtype)
+                else:
+                    one = {ew.LOAD: lambda: b, ew.ADD: lambda: one + b, ew.SUB: lambda: one - b,
+                           ew.RSUB: lambda: b - one, ew.MUL: lambda: one * b,
+                           ew.DIV: lambda: one / b, ew.RDIV: lambda: b / one,
+                           ew.MAX: lambda: np.maximum(one, b), ew.MIN: lambda: np.minimum(one, b),
+                           ew.NEG: lambda: -one, ew.ABS: lambda: np.abs(one),
+                           ew.EXP: lambda: np.exp(one), ew.SQRT: lambda: np.sqrt(one),
+                           ew.LOG: lambda: np.log(one)}[op]()
+                continue
             if op in (ew.RSUM, ew.RMAX):  # row programs: reduce along the rows, end the pass
                 reduce = np.sum if op == ew.RSUM else np.max
                 scalars[src] = reduce(acc, axis=1, keepdims=True).astype(dtype)

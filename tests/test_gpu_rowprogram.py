@@ -98,6 +98,40 @@ def test_row_program_through_the_c_abi(hc):
     want = (x - mean) / np.sqrt(((x - mean) ** 2).sum(axis=1, keepdims=True) * (1.0 / cols))
     np.testing.assert_allclose(d_out.cpu().numpy(), want, rtol=1e-13)
 
+    # The same with the per-row values computed once per row, in uniform prologues:
+    # s2 = s0/N before the second pass, s3 = sqrt(s1/N) before the third.
+    u = ew.UNIFORM
+    uniform = [
+        ew.LOAD | 0 << 8, ew.RSUM | 0 << 8,
+        ew.LOAD | u | s0 << 8, ew.MUL | u | c0 << 8, ew.SET | u | 2 << 8,
+        ew.LOAD | 0 << 8, ew.SUB | (ew.SRC_SCALAR + 2) << 8, ew.SAVE0, ew.MUL | t0 << 8,
+        ew.RSUM | 1 << 8,
+        ew.LOAD | u | s1 << 8, ew.MUL | u | c0 << 8, ew.SQRT | u, ew.SET | u | 3 << 8,
+        ew.LOAD | 0 << 8, ew.SUB | (ew.SRC_SCALAR + 2) << 8, ew.DIV | (ew.SRC_SCALAR + 3) << 8,
+    ]
+    q = capi.HcMapProgram()
+    q.inputs[0], q.inPitch[0], q.outPitch = d_x.data_ptr(), cols, cols
+    d_out2 = torch.zeros_like(d_out)
+    q.out, q.rows, q.cols, q.nInputs, q.nInstr = d_out2.data_ptr(), rows, cols, 1, len(uniform)
+    for i, ins in enumerate(uniform):
+        q.code[i] = ins
+    q.consts[0] = 1.0 / cols
+    hc.row_program(q, capi.HC_F64)
+    finish(hc)
+    assert torch.equal(d_out2, d_out)  # the same operations on the same values
+    q.code[5] = ew.LOAD | u | s0 << 8  # a uniform instruction in the middle of a pass
+    q.code[4] = ew.LOAD | 0 << 8
+    with pytest.raises(RuntimeError, match="not at the start of a pass"):
+        hc.row_program(q, capi.HC_F64)
+    q.code[4], q.code[5] = ew.SET | u | 2 << 8, ew.LOAD | 0 << 8
+    q.code[2] = ew.LOAD | u | 0 << 8  # an array as a uniform operand
+    with pytest.raises(RuntimeError, match="only constants and row scalars"):
+        hc.row_program(q, capi.HC_F64)
+    q.code[2] = ew.LOAD | u | s0 << 8
+    q.code[0] = ew.LOAD | u | c0 << 8  # hcMapElements knows no uniform instructions
+    with pytest.raises(RuntimeError, match="uniform instructions belong to hcRowProgram"):
+        hc.map_elements(q, capi.HC_F64)
+
     # Malformed programs are refused before anything is launched.
     p.code[len(program) - 1] = ew.RSUM | 2 << 8
     with pytest.raises(RuntimeError, match="ends in a reduction"):

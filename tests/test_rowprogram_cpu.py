@@ -56,8 +56,12 @@ def test_pass_structure_of_log_softmax():
     assert ops[:2] == [(ew.LOAD, 0), (ew.RMAX, 0)]
     second = ops[2:ops.index((ew.RSUM, 1)) + 1]
     assert second == [(ew.LOAD, 0), (ew.SUB, ew.SRC_SCALAR + 0), (ew.EXP, 0), (ew.RSUM, 1)]
+    # The last pass opens with a uniform prologue - log(s1) once per row, kept in
+    # s2 - and then walks the row with three cheap instructions.
     last = ops[ops.index((ew.RSUM, 1)) + 1:]
-    assert (ew.LOG, 0) in last and last[0][0] == ew.LOAD
+    u = ew.UNIFORM
+    assert last == [(ew.LOAD | u, ew.SRC_SCALAR + 1), (ew.LOG | u, 0), (ew.SET | u, 2),
+                    (ew.LOAD, 0), (ew.SUB, ew.SRC_SCALAR + 0), (ew.SUB, ew.SRC_SCALAR + 2)]
     # The same reduction written twice is computed once.
     twice = make_rowwise(lambda t: (t - t.max(axis=1, keepdims=True))
                          / (t.max(axis=1, keepdims=True) + 2.0))
