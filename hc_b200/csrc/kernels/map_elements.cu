@@ -31,9 +31,18 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
   const T noScalars[4] = {T(0), T(0), T(0), T(0)};
   const long long perRow = p.cols / V;
   for (long long r = blockIdx.y; r < p.rows; r += gridDim.y) {
+    const T *rowIn[NIN];
+#pragma unroll
+    for (int k = 0; k < NIN; ++k) {
+      const int kk = k < p.nInputs ? k : 0; // a program without inputs loads input 0's slot
+      rowIn[k] = static_cast<const T *>(p.in[kk]) + r * p.inPitch[kk];
+    }
+    T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
     const long long first = ((long long)blockIdx.x * UNROLL) * THREADS + threadIdx.x;
     for (long long base = first; base < perRow;
          base += (long long)gridDim.x * UNROLL * THREADS) {
+      // Every packet of this step lies inside the row (the same for the whole CTA)?
+      const bool whole = base - threadIdx.x + (long long)UNROLL * THREADS <= perRow;
       // All loads of the UNROLL packets are issued before any arithmetic.
       T x[NIN][W];
 #pragma unroll
@@ -42,11 +51,13 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
         for (int u = 0; u < UNROLL; ++u) {
           const long long i = base + (long long)u * THREADS;
           Packet<T, V> packet;
+          if (k < p.nInputs && (whole || i < perRow)) {
+            packet = loadPacket<T, V>(rowIn[k] + i * V);
+          } else {
 #pragma unroll
-          for (int e = 0; e < V; ++e)
-            packet.v[e] = T(0);
-          if (k < p.nInputs && i < perRow)
-            packet = loadPacket<T, V>(static_cast<const T *>(p.in[k]) + r * p.inPitch[k] + i * V);
+            for (int e = 0; e < V; ++e)
+              packet.v[e] = T(0);
+          }
 #pragma unroll
           for (int e = 0; e < V; ++e)
             x[k][u * V + e] = packet.v[e];
@@ -57,12 +68,12 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const long long i = base + (long long)u * THREADS;
-        if (i < perRow) {
+        if (whole || i < perRow) {
           Packet<T, V> packet;
 #pragma unroll
           for (int e = 0; e < V; ++e)
             packet.v[e] = result[u * V + e];
-          storePacket<T, V>(static_cast<T *>(p.out) + r * p.outPitch + i * V, packet);
+          storePacket<T, V>(rowOut + i * V, packet);
         }
       }
     }

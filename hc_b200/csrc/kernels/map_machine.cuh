@@ -53,10 +53,39 @@ __device__ __forceinline__ void storePacket(T *p, const Packet<T, V> &value) {
     __stcs(p, value.v[0]);
 }
 
+// The binary operations of the machine on W accumulators; `operand(i)` names
+// the second operand of element i (a register, a uniform value or an
+// expression of the element's position), so that no operand is copied before
+// it is used.
+template <typename T, int W, typename F>
+__device__ __forceinline__ void binary(uint32_t op, T (&acc)[W], F operand) {
+#define HC_MAP_EACH(expr)                                                               \
+  _Pragma("unroll") for (int i = 0; i < W; ++i) {                                       \
+    const T a = acc[i], b = operand(i);                                                 \
+    (void)a;                                                                            \
+    acc[i] = (expr);                                                                    \
+  }                                                                                     \
+  break
+  switch (op) {
+  case HC_MAP_LOAD: HC_MAP_EACH(b);
+  case HC_MAP_ADD: HC_MAP_EACH(a + b);
+  case HC_MAP_SUB: HC_MAP_EACH(a - b);
+  case HC_MAP_RSUB: HC_MAP_EACH(b - a);
+  case HC_MAP_MUL: HC_MAP_EACH(a * b);
+  case HC_MAP_DIV: HC_MAP_EACH(a / b);
+  case HC_MAP_RDIV: HC_MAP_EACH(b / a);
+  case HC_MAP_MAX: HC_MAP_EACH(maxOf(a, b));
+  default: HC_MAP_EACH(minOf(a, b));
+  }
+#undef HC_MAP_EACH
+}
+
 // Runs instructions [pcBegin, pcEnd) of the program on W elements.  The
 // inputs and the accumulator live in registers; the temporaries, which few
 // expressions need, in this thread's column of a shared-memory array, so that
-// registers stay free for loads in flight.
+// registers stay free for loads in flight.  The first instruction of a range
+// is always a load of the accumulator (the host refuses other programs), so
+// `acc` needs no initial value.
 //
 // INDEXED: `row` and `packet` say where the elements sit (element i is in
 // packet `packet + (i / V) * STRIDE`, at position i % V of it) - programs
@@ -68,64 +97,51 @@ __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, int pcBegin, 
                                          T (&temps)[3][W][THREADS], long long row,
                                          long long packet, const T (&scalars)[4]) {
   const int lane = threadIdx.x;
-#pragma unroll
-  for (int i = 0; i < W; ++i)
-    acc[i] = T(0);
 #define HC_MAP_EACH(expr)                                                               \
   _Pragma("unroll") for (int i = 0; i < W; ++i) {                                       \
-    const T a = acc[i], b = v[i];                                                       \
-    (void)b;                                                                            \
+    const T a = acc[i];                                                                 \
     acc[i] = (expr);                                                                    \
   }                                                                                     \
   break
-#define HC_MAP_TAKE(from)                                                               \
-  _Pragma("unroll") for (int i = 0; i < W; ++i) v[i] = from;                            \
-  break
   for (int pc = pcBegin; pc < pcEnd; ++pc) {
     const uint32_t ins = p.code[pc], op = ins & 0xffu, src = ins >> 8;
-    T v[W]; // operand of the binary operations (the unary ones never read it)
     if (op <= HC_MAP_MIN) {
-      if (ROWS && src >= HC_MAP_SRC_SCALAR) {
-        switch (src - HC_MAP_SRC_SCALAR) {
-        case 0: HC_MAP_TAKE(scalars[0]);
-        case 1: HC_MAP_TAKE(scalars[1]);
-        case 2: HC_MAP_TAKE(scalars[2]);
-        default: HC_MAP_TAKE(scalars[3]);
+      if (src >= HC_MAP_SRC_CONST) {
+        // One value for all elements: a constant, a row scalar, the row index.
+        if (INDEXED && src == HC_MAP_SRC_COL) {
+          binary<T, W>(op, acc, [&](int i) {
+            return T((packet + (long long)(i / V) * STRIDE) * V + i % V);
+          });
+          continue;
         }
-      } else if (INDEXED && src >= HC_MAP_SRC_ROW) {
+        T one;
+        if (ROWS && src >= HC_MAP_SRC_SCALAR) {
+          const uint32_t k = src - HC_MAP_SRC_SCALAR;
+          one = k == 0 ? scalars[0] : k == 1 ? scalars[1] : k == 2 ? scalars[2] : scalars[3];
+        } else if (INDEXED && src == HC_MAP_SRC_ROW) {
+          one = T(row);
+        } else {
+          one = T(p.consts[src - HC_MAP_SRC_CONST]);
+        }
+        binary<T, W>(op, acc, [&](int) { return one; });
+      } else if (src >= HC_MAP_SRC_TEMP) {
+        T v[W]; // shared memory may be indexed by the operand number, registers not
 #pragma unroll
         for (int i = 0; i < W; ++i)
-          v[i] = src == HC_MAP_SRC_ROW
-                     ? T(row)
-                     : T((packet + (long long)(i / V) * STRIDE) * V + i % V);
-      } else if (src >= HC_MAP_SRC_CONST) {
-        const T c = T(p.consts[src - HC_MAP_SRC_CONST]);
-#pragma unroll
-        for (int i = 0; i < W; ++i)
-          v[i] = c;
+          v[i] = temps[src - HC_MAP_SRC_TEMP][i][lane];
+        binary<T, W>(op, acc, [&](int i) { return v[i]; });
       } else {
         // Named registers only: an indexed access would go to local memory.
         switch (src) {
-        case 0: HC_MAP_TAKE(x[0][i]);
-        case 1: if constexpr (NIN > 1) { HC_MAP_TAKE(x[1][i]); } break;
-        case 2: if constexpr (NIN > 2) { HC_MAP_TAKE(x[2][i]); } break;
-        case 3: if constexpr (NIN > 3) { HC_MAP_TAKE(x[3][i]); } break;
-        case 4: HC_MAP_TAKE(temps[0][i][lane]);
-        case 5: HC_MAP_TAKE(temps[1][i][lane]);
-        default: HC_MAP_TAKE(temps[2][i][lane]);
+        case 0: binary<T, W>(op, acc, [&](int i) { return x[0][i]; }); break;
+        case 1: if constexpr (NIN > 1) binary<T, W>(op, acc, [&](int i) { return x[1][i]; }); break;
+        case 2: if constexpr (NIN > 2) binary<T, W>(op, acc, [&](int i) { return x[2][i]; }); break;
+        default: if constexpr (NIN > 3) binary<T, W>(op, acc, [&](int i) { return x[3][i]; }); break;
         }
       }
+      continue;
     }
     switch (op) {
-    case HC_MAP_LOAD: HC_MAP_EACH(b);
-    case HC_MAP_ADD: HC_MAP_EACH(a + b);
-    case HC_MAP_SUB: HC_MAP_EACH(a - b);
-    case HC_MAP_RSUB: HC_MAP_EACH(b - a);
-    case HC_MAP_MUL: HC_MAP_EACH(a * b);
-    case HC_MAP_DIV: HC_MAP_EACH(a / b);
-    case HC_MAP_RDIV: HC_MAP_EACH(b / a);
-    case HC_MAP_MAX: HC_MAP_EACH(maxOf(a, b));
-    case HC_MAP_MIN: HC_MAP_EACH(minOf(a, b));
     case HC_MAP_NEG: HC_MAP_EACH(-a);
     case HC_MAP_ABS: HC_MAP_EACH(a < T(0) ? -a : (a == T(0) ? T(0) : a));
     case HC_MAP_EXP: HC_MAP_EACH(expOf(a));
@@ -133,19 +149,16 @@ __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, int pcBegin, 
     case HC_MAP_LOG: HC_MAP_EACH(logOf(a));
     case HC_MAP_SAVE0:
     case HC_MAP_SAVE1:
-    case HC_MAP_SAVE2: { // park the accumulator
-      const int t = int(op) - int(HC_MAP_SAVE0);
+    case HC_MAP_SAVE2: // park the accumulator
 #pragma unroll
       for (int i = 0; i < W; ++i)
-        temps[t][i][lane] = acc[i];
+        temps[op - HC_MAP_SAVE0][i][lane] = acc[i];
       break;
-    }
     default: // the row reductions end a pass and are handled by the caller
       break;
     }
   }
 #undef HC_MAP_EACH
-#undef HC_MAP_TAKE
 }
 
 } // namespace hcmap

@@ -37,6 +37,15 @@ template <typename T> __device__ __forceinline__ T lowest();
 template <> __device__ __forceinline__ float lowest<float>() { return -INFINITY; }
 template <> __device__ __forceinline__ double lowest<double>() { return -INFINITY; }
 
+// The larger of two values, NaN if either is NaN (what NumPy's max along an
+// axis gives); one instruction for float.
+__device__ __forceinline__ float maxNan(float a, float b) {
+  float out;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
+  return out;
+}
+__device__ __forceinline__ double maxNan(double a, double b) { return maxOf(a, b); }
+
 template <typename T, int V, int NIN>
 __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
   constexpr int W = V * UNROLL;
@@ -45,7 +54,12 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
   const long long r = (long long)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5);
   if (r >= p.rows)
     return; // whole warps leave; nothing below synchronises the CTA
-  const long long perRow = p.cols / V;
+  const int perRow = int(p.cols / V); // the host refuses rows of 2^31 packets and more
+  const T *rowIn[NIN];
+#pragma unroll
+  for (int k = 0; k < NIN; ++k)
+    rowIn[k] = static_cast<const T *>(p.in[k < p.nInputs ? k : 0]) + r * p.inPitch[k < p.nInputs ? k : 0];
+  T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
   T scalars[4] = {T(0), T(0), T(0), T(0)};
 
   int pc = 0;
@@ -103,22 +117,26 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
       }
     }
     const bool last = end >= p.nInstr;
-    T running = reduction == HC_MAP_RMAX ? lowest<T>() : T(0);
+    const bool takeMax = reduction == HC_MAP_RMAX;
+    T running = takeMax ? lowest<T>() : T(0);
 
-    for (long long base = lane; base < perRow; base += 32 * UNROLL) {
+    for (int base = lane; base < perRow; base += 32 * UNROLL) {
+      // Every packet of this step lies inside the row (the same for all lanes)?
+      const bool whole = base - lane + 32 * UNROLL <= perRow;
       T x[NIN][W];
 #pragma unroll
       for (int k = 0; k < NIN; ++k)
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-          const long long i = base + (long long)u * 32;
+          const int i = base + u * 32;
           Packet<T, V> packet;
-#pragma unroll
-          for (int e = 0; e < V; ++e)
-            packet.v[e] = T(0);
-          if (k < p.nInputs && i < perRow) {
-            const T *src = static_cast<const T *>(p.in[k]) + r * p.inPitch[k] + i * V;
+          if (whole || i < perRow) {
+            const T *src = rowIn[k] + (long long)i * V;
             packet = last ? loadPacket<T, V>(src) : loadPacketKept<T, V>(src);
+          } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              packet.v[e] = T(0);
           }
 #pragma unroll
           for (int e = 0; e < V; ++e)
@@ -126,23 +144,34 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
         }
       T value[W];
       evaluate<T, W, V, NIN, false, true, 32>(p, pc, end, x, value, temps, r, base, scalars);
+      if (last) {
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const long long i = base + (long long)u * 32;
-        if (i >= perRow)
-          continue;
-        if (last) {
-          Packet<T, V> packet;
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = base + u * 32;
+          if (whole || i < perRow) {
+            Packet<T, V> packet;
 #pragma unroll
-          for (int e = 0; e < V; ++e)
-            packet.v[e] = value[u * V + e];
-          storePacket<T, V>(static_cast<T *>(p.out) + r * p.outPitch + i * V, packet);
-        } else {
-#pragma unroll
-          for (int e = 0; e < V; ++e)
-            running = reduction == HC_MAP_RMAX ? maxOf(running, value[u * V + e])
-                                               : running + value[u * V + e];
+            for (int e = 0; e < V; ++e)
+              packet.v[e] = value[u * V + e];
+            storePacket<T, V>(rowOut + (long long)i * V, packet);
+          }
         }
+      } else if (takeMax) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+          if (whole || base + u * 32 < perRow) {
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              running = maxNan(running, value[u * V + e]);
+          }
+      } else {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+          if (whole || base + u * 32 < perRow) {
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              running = running + value[u * V + e];
+          }
       }
     }
     if (last)
@@ -150,7 +179,7 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
       const T other = __shfl_xor_sync(0xffffffffu, running, offset);
-      running = reduction == HC_MAP_RMAX ? maxOf(running, other) : running + other;
+      running = takeMax ? maxNan(running, other) : running + other;
     }
     switch (target) { // named registers, no indexed access
     case 0: scalars[0] = running; break;

@@ -614,6 +614,8 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
       return c->fail("hcRowProgram: null input %d", k);
   if (ceilDiv(p.rows, 8) > 0x7fffffffLL)
     return c->fail("hcRowProgram: %lld rows exceed one launch", (long long)p.rows);
+  if (p.cols > 0x7fffff00LL) // the kernel counts the packets of a row in an int
+    return c->fail("hcRowProgram: rows of %lld elements are too long", (long long)p.cols);
   const int perPacket = 16 / (dtype == HC_F32 ? 4 : 8);
   bool wide = p.cols % perPacket == 0 && aligned(p.out, 16) && p.outPitch % perPacket == 0;
   for (int k = 0; k < p.nInputs; ++k)
