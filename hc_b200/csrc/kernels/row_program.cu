@@ -46,6 +46,71 @@ __device__ __forceinline__ float maxNan(float a, float b) {
 }
 __device__ __forceinline__ double maxNan(double a, double b) { return maxOf(a, b); }
 
+// Uniform prologue of a pass: expressions of row scalars and constants only
+// (the log of a sum, a mean from a sum ...) are computed once per row here, not
+// once per element in the walk that follows.  Returns the first instruction
+// of the walk.
+template <typename T>
+__device__ __forceinline__ int uniformPrologue(const HcMapProgramDev &p, int pc, T (&scalars)[4]) {
+  T one = T(0);
+  for (; pc < p.nInstr && (p.code[pc] & HC_MAP_UNIFORM); ++pc) {
+    const uint32_t op = p.code[pc] & 0x7fu, src = p.code[pc] >> 8;
+    T b = T(0);
+    if (op <= HC_MAP_MIN) {
+      if (src >= HC_MAP_SRC_SCALAR) {
+        const uint32_t k = src - HC_MAP_SRC_SCALAR;
+        b = k == 0 ? scalars[0] : k == 1 ? scalars[1] : k == 2 ? scalars[2] : scalars[3];
+      } else {
+        b = T(p.consts[src - HC_MAP_SRC_CONST]);
+      }
+    }
+    switch (op) {
+    case HC_MAP_LOAD: one = b; break;
+    case HC_MAP_ADD: one = one + b; break;
+    case HC_MAP_SUB: one = one - b; break;
+    case HC_MAP_RSUB: one = b - one; break;
+    case HC_MAP_MUL: one = one * b; break;
+    case HC_MAP_DIV: one = one / b; break;
+    case HC_MAP_RDIV: one = b / one; break;
+    case HC_MAP_MAX: one = maxOf(one, b); break;
+    case HC_MAP_MIN: one = minOf(one, b); break;
+    case HC_MAP_NEG: one = -one; break;
+    case HC_MAP_ABS: one = one < T(0) ? -one : (one == T(0) ? T(0) : one); break;
+    case HC_MAP_EXP: one = expOf(one); break;
+    case HC_MAP_SQRT: one = sqrt(one); break;
+    case HC_MAP_LOG: one = logOf(one); break;
+    case HC_MAP_SET:
+      switch (src) {
+      case 0: scalars[0] = one; break;
+      case 1: scalars[1] = one; break;
+      case 2: scalars[2] = one; break;
+      default: scalars[3] = one; break;
+      }
+      break;
+    default: break;
+    }
+  }
+  return pc;
+}
+
+// Where the pass that starts at `pc` ends: at the next reduction instruction
+// (returned through `reduction` and `target`) or at the end of the program.
+__device__ __forceinline__ int passEnd(const HcMapProgramDev &p, int pc, uint32_t &reduction,
+                                       uint32_t &target) {
+  reduction = 0;
+  target = 0;
+  int end = pc;
+  for (; end < p.nInstr; ++end) {
+    const uint32_t op = p.code[end] & 0xffu;
+    if (op == HC_MAP_RSUM || op == HC_MAP_RMAX) {
+      reduction = op;
+      target = p.code[end] >> 8;
+      break;
+    }
+  }
+  return end;
+}
+
 template <typename T, int V, int NIN>
 __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
   constexpr int W = V * UNROLL;
@@ -64,58 +129,9 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
 
   int pc = 0;
   while (pc < p.nInstr) {
-    // Uniform prologue: expressions of row scalars and constants only (the
-    // log of a sum, a mean from a sum ...) are computed once per row here,
-    // not once per element in the walk below.
-    T one = T(0);
-    for (; pc < p.nInstr && (p.code[pc] & HC_MAP_UNIFORM); ++pc) {
-      const uint32_t op = p.code[pc] & 0x7fu, src = p.code[pc] >> 8;
-      T b = T(0);
-      if (op <= HC_MAP_MIN) {
-        if (src >= HC_MAP_SRC_SCALAR) {
-          const uint32_t k = src - HC_MAP_SRC_SCALAR;
-          b = k == 0 ? scalars[0] : k == 1 ? scalars[1] : k == 2 ? scalars[2] : scalars[3];
-        } else {
-          b = T(p.consts[src - HC_MAP_SRC_CONST]);
-        }
-      }
-      switch (op) {
-      case HC_MAP_LOAD: one = b; break;
-      case HC_MAP_ADD: one = one + b; break;
-      case HC_MAP_SUB: one = one - b; break;
-      case HC_MAP_RSUB: one = b - one; break;
-      case HC_MAP_MUL: one = one * b; break;
-      case HC_MAP_DIV: one = one / b; break;
-      case HC_MAP_RDIV: one = b / one; break;
-      case HC_MAP_MAX: one = maxOf(one, b); break;
-      case HC_MAP_MIN: one = minOf(one, b); break;
-      case HC_MAP_NEG: one = -one; break;
-      case HC_MAP_ABS: one = one < T(0) ? -one : (one == T(0) ? T(0) : one); break;
-      case HC_MAP_EXP: one = expOf(one); break;
-      case HC_MAP_SQRT: one = sqrt(one); break;
-      case HC_MAP_LOG: one = logOf(one); break;
-      case HC_MAP_SET:
-        switch (src) {
-        case 0: scalars[0] = one; break;
-        case 1: scalars[1] = one; break;
-        case 2: scalars[2] = one; break;
-        default: scalars[3] = one; break;
-        }
-        break;
-      default: break;
-      }
-    }
-    // The pass runs to the next reduction instruction or to the end.
-    int end = pc;
-    uint32_t reduction = 0, target = 0;
-    for (; end < p.nInstr; ++end) {
-      const uint32_t op = p.code[end] & 0xffu;
-      if (op == HC_MAP_RSUM || op == HC_MAP_RMAX) {
-        reduction = op;
-        target = p.code[end] >> 8;
-        break;
-      }
-    }
+    pc = uniformPrologue<T>(p, pc, scalars);
+    uint32_t reduction, target;
+    const int end = passEnd(p, pc, reduction, target);
     const bool last = end >= p.nInstr;
     const bool takeMax = reduction == HC_MAP_RMAX;
     T running = takeMax ? lowest<T>() : T(0);
@@ -191,6 +207,116 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
   }
 }
 
+// Rows of up to P * 256 packets, held in registers: one CTA per row, thread t
+// owns packets t, t + 256, ... of the row.  The row is read from HBM once, with
+// streaming loads; every pass works on the registers, so the later passes issue
+// no loads and no address arithmetic, and an instruction is decoded once for
+// P packets.  A reduction is a running value per thread, a shuffle tree per
+// warp and the eight warp results added (or compared) in warp order by every
+// thread, so all threads hold the same row scalar.
+//
+// Dynamic shared memory: 256 bytes for the warp results (four slots of eight
+// values, so that one barrier per reduction is enough), then as many of the
+// three temporaries as the program saves to.
+template <typename T, int V, int P, int NIN>
+__device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
+  constexpr int W = V * P;
+  extern __shared__ __align__(16) unsigned char raw[];
+  T(*const partial)[THREADS / 32] = reinterpret_cast<T(*)[THREADS / 32]>(raw);
+  T(&temps)[3][W][THREADS] = *reinterpret_cast<T(*)[3][W][THREADS]>(raw + 256);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long r = blockIdx.x;
+  const int perRow = int(p.cols / V);
+
+  T x[NIN][W];
+#pragma unroll
+  for (int k = 0; k < NIN; ++k)
+#pragma unroll
+    for (int u = 0; u < P; ++u) {
+      const int i = threadIdx.x + u * THREADS;
+      Packet<T, V> packet;
+      if (k < p.nInputs && i < perRow) {
+        packet = loadPacket<T, V>(static_cast<const T *>(p.in[k]) + r * p.inPitch[k] +
+                                  (long long)i * V);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+          packet.v[e] = T(0);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e)
+        x[k][u * V + e] = packet.v[e];
+    }
+
+  T scalars[4] = {T(0), T(0), T(0), T(0)};
+  int pc = 0, reductions = 0;
+  while (pc < p.nInstr) { // the same trip count for every thread of the CTA
+    pc = uniformPrologue<T>(p, pc, scalars);
+    uint32_t reduction, target;
+    const int end = passEnd(p, pc, reduction, target);
+    T value[W];
+    evaluate<T, W, V, NIN, false, true, THREADS>(p, pc, end, x, value, temps, r, threadIdx.x,
+                                                 scalars);
+    if (end >= p.nInstr) {
+      T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
+#pragma unroll
+      for (int u = 0; u < P; ++u) {
+        const int i = threadIdx.x + u * THREADS;
+        if (i < perRow) {
+          Packet<T, V> packet;
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            packet.v[e] = value[u * V + e];
+          storePacket<T, V>(rowOut + (long long)i * V, packet);
+        }
+      }
+      break;
+    }
+    const bool takeMax = reduction == HC_MAP_RMAX;
+    T running = takeMax ? lowest<T>() : T(0);
+    if (takeMax) {
+#pragma unroll
+      for (int u = 0; u < P; ++u)
+        if (threadIdx.x + u * THREADS < perRow) {
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            running = maxNan(running, value[u * V + e]);
+        }
+    } else {
+#pragma unroll
+      for (int u = 0; u < P; ++u)
+        if (threadIdx.x + u * THREADS < perRow) {
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            running = running + value[u * V + e];
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const T other = __shfl_xor_sync(0xffffffffu, running, offset);
+      running = takeMax ? maxNan(running, other) : running + other;
+    }
+    // Slot n is written again only after three more barriers, long after its
+    // last reader has passed the next one.
+    T *const slot = partial[reductions & 3];
+    ++reductions;
+    if (lane == 0)
+      slot[warp] = running;
+    __syncthreads();
+    T whole = slot[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; ++w)
+      whole = takeMax ? maxNan(whole, slot[w]) : whole + slot[w];
+    switch (target) {
+    case 0: scalars[0] = whole; break;
+    case 1: scalars[1] = whole; break;
+    case 2: scalars[2] = whole; break;
+    default: scalars[3] = whole; break;
+    }
+    pc = end + 1;
+  }
+}
+
 } // namespace
 
 #define HC_ROW_KERNEL(tname, T, V, NIN)                                                 \
@@ -206,3 +332,19 @@ HC_ROW_KERNELS(f32, float, 4)
 HC_ROW_KERNELS(f32, float, 1)
 HC_ROW_KERNELS(f64, double, 2)
 HC_ROW_KERNELS(f64, double, 1)
+
+// Held-row kernels: rows of up to 512 (p2) or 1024 (p4) 16-byte packets.
+#define HC_ROW_HELD_KERNEL(tname, T, V, P, NIN)                                         \
+  extern "C" __global__ void __launch_bounds__(THREADS, (NIN == 1 ? 4 : 3) - (sizeof(T) == 8)) \
+      hc_row_program_held_##tname##_v##V##_p##P##_n##NIN(                               \
+          const __grid_constant__ HcMapProgramDev p) {                                  \
+    rowProgramHeld<T, V, P, NIN>(p);                                                    \
+  }
+#define HC_ROW_HELD_KERNELS(tname, T, V)                                                \
+  HC_ROW_HELD_KERNEL(tname, T, V, 2, 1)                                                 \
+  HC_ROW_HELD_KERNEL(tname, T, V, 2, 2)                                                 \
+  HC_ROW_HELD_KERNEL(tname, T, V, 4, 1)                                                 \
+  HC_ROW_HELD_KERNEL(tname, T, V, 4, 2)
+
+HC_ROW_HELD_KERNELS(f32, float, 4)
+HC_ROW_HELD_KERNELS(f64, double, 2)

@@ -52,7 +52,8 @@ const KernelEntry kKernelTable[] = {
     // hc_map_elements_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1..4}[i]: element type, packet
     // width, number of input arrays, and whether element indices are operands.
     {"hc_map_elements_", "map_elements"},
-    // hc_row_program_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1,2}
+    // hc_row_program_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1,2} (a warp walks the row) and
+    // hc_row_program_held_{f32_v4,f64_v2}_p{2,4}_n{1,2} (a CTA holds the row).
     {"hc_row_program_", "row_program"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
@@ -144,6 +145,7 @@ struct HcContextImpl {
   long long tiledVariant = 0;
   long long reduceVariant = 0;
   long long mappedStack = 0;
+  long long rowVariant = 0;
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
@@ -376,6 +378,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
   }
   if (std::strcmp(name, "mapped_stack") == 0 && value >= 0 && value <= 1) {
     c->mappedStack = value; // 1: one work-group per CTA even where groups share a tile
+    return 0;
+  }
+  if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 1) {
+    c->rowVariant = value; // 1: warp-per-row kernel even for rows a CTA could hold
     return 0;
   }
   return c->fail("Invalid option: %s = %lld", name, value);
@@ -620,10 +626,28 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
   bool wide = p.cols % perPacket == 0 && aligned(p.out, 16) && p.outPitch % perPacket == 0;
   for (int k = 0; k < p.nInputs; ++k)
     wide = wide && aligned(p.in[k], 16) && p.inPitch[k] % perPacket == 0;
-  char name[40];
+  char name[48];
+  void *args[] = {&p};
+  // Rows of 257..1024 packets are held in the registers of one CTA per row
+  // (2 or 4 packets per thread); shorter ones would leave most of a CTA idle,
+  // longer ones do not fit.
+  const long long packets = p.cols / perPacket;
+  if (wide && packets > 256 && packets <= 1024 && c->rowVariant != 1 &&
+      p.rows <= 0x7fffffffLL) {
+    const int held = packets > 512 ? 4 : 2;
+    int temps = 0; // the temporaries the program saves to, t0 first
+    for (int pc = 0; pc < p.nInstr; ++pc) {
+      const uint32_t op = p.code[pc] & 0xffu;
+      if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
+        temps = std::max(temps, int(op - HC_MAP_SAVE0) + 1);
+    }
+    std::snprintf(name, sizeof name, "hc_row_program_held_%s_v%d_p%d_n%d",
+                  dtype == HC_F32 ? "f32" : "f64", perPacket, held, p.nInputs);
+    const size_t smem = 256 + size_t(temps) * held * 16 * 256;
+    return c->launch(name, size_t(p.rows), 1, 1, 256, args, 1, smem);
+  }
   std::snprintf(name, sizeof name, "hc_row_program_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
                 wide ? perPacket : 1, p.nInputs);
-  void *args[] = {&p};
   // One warp per row, eight rows per CTA.
   return c->launch(name, size_t(ceilDiv(p.rows, 8)), 1, 1, 256, args, 1, 0);
 }

@@ -87,7 +87,9 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * (fp32 hcGemmTiled): 0 = automatic, 1 = no cp.async pipeline, 2 = pipeline
  * but no split of K over a cluster.  "mapped_stack":
  * 0 = hcMappedGemm stacks work-groups that share their f tile, 1 = one
- * work-group per CTA. */
+ * work-group per CTA.  "row_variant": 0 = hcRowProgram holds rows of 257..1024
+ * 16-byte packets in the registers of one CTA per row, 1 = always one warp per
+ * row that walks the row once per pass. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* ---- workloads -------------------------------------------------------------

@@ -217,7 +217,9 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
                                      for n in (1, 2, 3, 4) for i in ("", "i")},
                 "hc_row_program_": {f"{kernel}{tv}_n{n}" for tv in ("f32_v4", "f32_v1", "f64_v2",
                                                                     "f64_v1")
-                                    for n in (1, 2)},
+                                    for n in (1, 2)}
+                | {f"{kernel}held_{tv}_p{held}_n{n}" for tv in ("f32_v4", "f64_v2")
+                   for held in (2, 4) for n in (1, 2)},
             }[kernel]
             assert family == expected
             for member in family:

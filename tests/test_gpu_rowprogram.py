@@ -69,6 +69,95 @@ def test_row_max_propagates_nan_like_numpy():
     assert np.all(np.isnan(got[0])) and np.array_equal(got[1], [-3.0, -2.0, -1.0, 0.0])
 
 
+def _program(code, consts, d_in, d_out, pitch_in=None, pitch_out=None):
+    p = capi.HcMapProgram()
+    rows, cols = d_out.shape
+    p.inputs[0], p.inPitch[0] = d_in.data_ptr(), pitch_in or cols
+    p.out, p.outPitch, p.rows, p.cols, p.nInputs = d_out.data_ptr(), pitch_out or cols, rows, cols, 1
+    p.nInstr = len(code)
+    for i, ins in enumerate(code):
+        p.code[i] = ins
+    for i, value in enumerate(consts):
+        p.consts[i] = value
+    return p
+
+
+@pytest.mark.parametrize("variant", [0, 1], ids=["held", "walked"])
+@pytest.mark.parametrize("dtype,cols", [("float32", 4096), ("float32", 4092), ("float32", 2048),
+                                        ("float32", 1028), ("float32", 1024), ("float64", 2048),
+                                        ("float64", 1030), ("float64", 514), ("float64", 512)])
+def test_rows_held_in_registers_and_rows_walked_agree(hc, variant, dtype, cols):
+    """Rows of 257..1024 16-byte packets take the kernel that holds the row in the
+    registers of a CTA, others (and all rows under row_variant 1) the warp that
+    walks the row once per pass.  Two programs: log-softmax (max, sum, a uniform
+    prologue), and a variance normalisation that parks values in all three
+    temporaries (more than 48 KB of dynamic shared memory at four packets per
+    thread)."""
+    rows = 19
+    rng = np.random.default_rng(cols)
+    x = rng.standard_normal((rows, cols)).astype(dtype)
+    x[3, 5] = 9.0
+    d_x = torch.from_numpy(x).cuda()
+    d_out = torch.full((rows, cols), float("nan"), dtype=d_x.dtype, device="cuda")
+    kind = capi.HC_F32 if dtype == "float32" else capi.HC_F64
+    u, c0, s0, t0 = ew.UNIFORM, ew.SRC_CONST, ew.SRC_SCALAR, ew.SRC_TEMP
+    tol = dict(rtol=3e-6, atol=2e-6) if dtype == "float32" else dict(rtol=1e-13, atol=1e-14)
+    x64 = x.astype(np.float64)
+    hc.set_option("row_variant", variant)
+    try:
+        log_softmax = [
+            ew.LOAD | 0 << 8, ew.RMAX | 0 << 8,
+            ew.LOAD | 0 << 8, ew.SUB | s0 << 8, ew.EXP, ew.RSUM | 1 << 8,
+            ew.LOAD | u | (s0 + 1) << 8, ew.LOG | u, ew.SET | u | 2 << 8,
+            ew.LOAD | 0 << 8, ew.SUB | s0 << 8, ew.SUB | (s0 + 2) << 8,
+        ]
+        hc.row_program(_program(log_softmax, [], d_x, d_out), kind)
+        finish(hc)
+        shifted = x64 - x64.max(axis=1, keepdims=True)
+        want = shifted - np.log(np.exp(shifted).sum(axis=1, keepdims=True))
+        np.testing.assert_allclose(d_out.cpu().numpy(), want, **tol)
+
+        # d = x - mean; t0 = d; t1 = d*d; t2 = |d|; out = t0 / sqrt(sum(t1)/N) + t2 * 0
+        normalise = [
+            ew.LOAD | 0 << 8, ew.RSUM | 0 << 8,
+            ew.LOAD | u | s0 << 8, ew.MUL | u | c0 << 8, ew.SET | u | 1 << 8,
+            ew.LOAD | 0 << 8, ew.SUB | (s0 + 1) << 8, ew.SAVE0, ew.MUL | t0 << 8, ew.RSUM | 2 << 8,
+            ew.LOAD | u | (s0 + 2) << 8, ew.MUL | u | c0 << 8, ew.SQRT | u, ew.SET | u | 3 << 8,
+            ew.LOAD | 0 << 8, ew.SUB | (s0 + 1) << 8, ew.SAVE0, ew.MUL | t0 << 8, ew.SAVE0 + 1,
+            ew.LOAD | t0 << 8, ew.ABS, ew.SAVE0 + 2,
+            ew.MUL | (c0 + 1) << 8, ew.SAVE0 + 2,
+            ew.LOAD | t0 << 8, ew.DIV | (s0 + 3) << 8, ew.ADD | (t0 + 2) << 8,
+        ]
+        d_out.fill_(float("nan"))
+        hc.row_program(_program(normalise, [1.0 / cols, 0.0], d_x, d_out), kind)
+        finish(hc)
+        d = x64 - x64.mean(axis=1, keepdims=True)
+        want = d / np.sqrt((d * d).sum(axis=1, keepdims=True) / cols)
+        np.testing.assert_allclose(d_out.cpu().numpy(), want, **tol)
+    finally:
+        hc.set_option("row_variant", 0)
+
+
+def test_held_rows_respect_pitches(hc):
+    """Pitched input and output (multiples of 16 bytes) with the held-row kernel:
+    nothing outside the rows is written."""
+    rows, cols, pitch = 11, 2044, 2052
+    rng = np.random.default_rng(2)
+    store = torch.zeros((2, rows, pitch), device="cuda")
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    store[0, :, :cols].copy_(torch.from_numpy(x))
+    d_out = store[1, :, :cols]
+    centre = [ew.LOAD | 0 << 8, ew.RSUM | 0 << 8,
+              ew.LOAD | ew.UNIFORM | ew.SRC_SCALAR << 8, ew.MUL | ew.UNIFORM | ew.SRC_CONST << 8,
+              ew.SET | ew.UNIFORM | 1 << 8,
+              ew.LOAD | 0 << 8, ew.SUB | (ew.SRC_SCALAR + 1) << 8]
+    hc.row_program(_program(centre, [1.0 / cols], store[0], d_out, pitch, pitch), capi.HC_F32)
+    finish(hc)
+    want = x.astype(np.float64) - x.astype(np.float64).mean(axis=1, keepdims=True)
+    np.testing.assert_allclose(d_out.cpu().numpy(), want, rtol=3e-6, atol=2e-6)
+    assert float(store[1, :, cols:].abs().max()) == 0.0
+
+
 def test_row_program_through_the_c_abi(hc):
     """Variance-normalise rows in float64: s0 = sum(x); s1 = sum((x - s0/N)^2);
     out = (x - s0/N) / sqrt(s1/N)."""
