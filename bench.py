@@ -166,9 +166,9 @@ NCU_TRAFFIC = {
     # profiles/map_elements_f32_v4_n2_8192x4096.md: (268.49 + 97.94) MB for a quarter of the
     # rows, scaled by 4 (the part of the output still in L2 at kernel end is not counted).
     "map": 1465.7e6,
-    # profiles/row_program_f32_v4_n1_8192x4096.md: (139.94 + 79.57) MB for a quarter of the
-    # rows, scaled by 4 (later passes are served by L2; written rows still in L2 not counted).
-    "rows": 878.0e6,
+    # profiles/row_program_f32_log_softmax_8192x4096.md (held rows): (134.33 + 84.75) MB for a
+    # quarter of the rows, scaled by 4 (written rows still in L2 at kernel end not counted).
+    "rows": 876.3e6,
 }
 
 

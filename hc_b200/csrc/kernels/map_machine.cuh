@@ -91,10 +91,11 @@ __device__ __forceinline__ void binary(uint32_t op, T (&acc)[W], F operand) {
 // packet `packet + (i / V) * STRIDE`, at position i % V of it) - programs
 // written at work-item level use the indices themselves as operands.
 // ROWS: `scalars` are the values earlier passes of a row program reduced.
-template <typename T, int W, int V, int NIN, bool INDEXED, bool ROWS, int STRIDE>
+template <typename T, int W, int V, int NIN, bool INDEXED, bool ROWS, int STRIDE,
+          int COLUMNS = THREADS>
 __device__ __forceinline__ void evaluate(const HcMapProgramDev &p, int pcBegin, int pcEnd,
                                          const T (&x)[NIN][W], T (&acc)[W],
-                                         T (&temps)[3][W][THREADS], long long row,
+                                         T (&temps)[3][W][COLUMNS], long long row,
                                          long long packet, const T (&scalars)[4]) {
   const int lane = threadIdx.x;
 #define HC_MAP_EACH(expr)                                                               \

@@ -218,12 +218,12 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
 // Dynamic shared memory: 256 bytes for the warp results (four slots of eight
 // values, so that one barrier per reduction is enough), then as many of the
 // three temporaries as the program saves to.
-template <typename T, int V, int P, int NIN>
+template <typename T, int V, int P, int NIN, int NT>
 __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
   constexpr int W = V * P;
   extern __shared__ __align__(16) unsigned char raw[];
-  T(*const partial)[THREADS / 32] = reinterpret_cast<T(*)[THREADS / 32]>(raw);
-  T(&temps)[3][W][THREADS] = *reinterpret_cast<T(*)[3][W][THREADS]>(raw + 256);
+  T(*const partial)[NT / 32] = reinterpret_cast<T(*)[NT / 32]>(raw);
+  T(&temps)[3][W][NT] = *reinterpret_cast<T(*)[3][W][NT]>(raw + 256);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long r = blockIdx.x;
   const int perRow = int(p.cols / V);
@@ -233,7 +233,7 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
   for (int k = 0; k < NIN; ++k)
 #pragma unroll
     for (int u = 0; u < P; ++u) {
-      const int i = threadIdx.x + u * THREADS;
+      const int i = threadIdx.x + u * NT;
       Packet<T, V> packet;
       if (k < p.nInputs && i < perRow) {
         packet = loadPacket<T, V>(static_cast<const T *>(p.in[k]) + r * p.inPitch[k] +
@@ -255,13 +255,13 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
     uint32_t reduction, target;
     const int end = passEnd(p, pc, reduction, target);
     T value[W];
-    evaluate<T, W, V, NIN, false, true, THREADS>(p, pc, end, x, value, temps, r, threadIdx.x,
+    evaluate<T, W, V, NIN, false, true, NT, NT>(p, pc, end, x, value, temps, r, threadIdx.x,
                                                  scalars);
     if (end >= p.nInstr) {
       T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
 #pragma unroll
       for (int u = 0; u < P; ++u) {
-        const int i = threadIdx.x + u * THREADS;
+        const int i = threadIdx.x + u * NT;
         if (i < perRow) {
           Packet<T, V> packet;
 #pragma unroll
@@ -277,7 +277,7 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
     if (takeMax) {
 #pragma unroll
       for (int u = 0; u < P; ++u)
-        if (threadIdx.x + u * THREADS < perRow) {
+        if (threadIdx.x + u * NT < perRow) {
 #pragma unroll
           for (int e = 0; e < V; ++e)
             running = maxNan(running, value[u * V + e]);
@@ -285,16 +285,20 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
     } else {
 #pragma unroll
       for (int u = 0; u < P; ++u)
-        if (threadIdx.x + u * THREADS < perRow) {
+        if (threadIdx.x + u * NT < perRow) {
 #pragma unroll
           for (int e = 0; e < V; ++e)
             running = running + value[u * V + e];
         }
     }
+    if (takeMax) {
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const T other = __shfl_xor_sync(0xffffffffu, running, offset);
-      running = takeMax ? maxNan(running, other) : running + other;
+      for (int offset = 16; offset > 0; offset >>= 1)
+        running = maxNan(running, __shfl_xor_sync(0xffffffffu, running, offset));
+    } else {
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1)
+        running = running + __shfl_xor_sync(0xffffffffu, running, offset);
     }
     // Slot n is written again only after three more barriers, long after its
     // last reader has passed the next one.
@@ -304,9 +308,15 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
       slot[warp] = running;
     __syncthreads();
     T whole = slot[0];
+    if (takeMax) {
 #pragma unroll
-    for (int w = 1; w < THREADS / 32; ++w)
-      whole = takeMax ? maxNan(whole, slot[w]) : whole + slot[w];
+      for (int w = 1; w < NT / 32; ++w)
+        whole = maxNan(whole, slot[w]);
+    } else {
+#pragma unroll
+      for (int w = 1; w < NT / 32; ++w)
+        whole = whole + slot[w];
+    }
     switch (target) {
     case 0: scalars[0] = whole; break;
     case 1: scalars[1] = whole; break;
@@ -333,18 +343,32 @@ HC_ROW_KERNELS(f32, float, 1)
 HC_ROW_KERNELS(f64, double, 2)
 HC_ROW_KERNELS(f64, double, 1)
 
-// Held-row kernels: rows of up to 512 (p2) or 1024 (p4) 16-byte packets.
-#define HC_ROW_HELD_KERNEL(tname, T, V, P, NIN)                                         \
-  extern "C" __global__ void __launch_bounds__(THREADS, (NIN == 1 ? 4 : 3) - (sizeof(T) == 8)) \
-      hc_row_program_held_##tname##_v##V##_p##P##_n##NIN(                               \
+// Held-row kernels.  Eight packets per thread on 64, 96 or 128 threads (rows
+// of up to 512, 768, 1024 packets): the fewer threads share a row, the fewer
+// decode each instruction, and the more elements each decode serves.  Four
+// packets per thread on 256 threads is the alternative for rows of 513..1024
+// packets with twice the resident warps.  The last argument is the number of
+// CTAs per SM the register budget is set for.
+#define HC_ROW_HELD_KERNEL(tname, T, V, P, NT, NIN, CTAS)                               \
+  extern "C" __global__ void __launch_bounds__(NT, CTAS)                                \
+      hc_row_program_held_##tname##_v##V##_p##P##_t##NT##_n##NIN(                       \
           const __grid_constant__ HcMapProgramDev p) {                                  \
-    rowProgramHeld<T, V, P, NIN>(p);                                                    \
+    rowProgramHeld<T, V, P, NIN, NT>(p);                                                \
   }
-#define HC_ROW_HELD_KERNELS(tname, T, V)                                                \
-  HC_ROW_HELD_KERNEL(tname, T, V, 2, 1)                                                 \
-  HC_ROW_HELD_KERNEL(tname, T, V, 2, 2)                                                 \
-  HC_ROW_HELD_KERNEL(tname, T, V, 4, 1)                                                 \
-  HC_ROW_HELD_KERNEL(tname, T, V, 4, 2)
 
-HC_ROW_HELD_KERNELS(f32, float, 4)
-HC_ROW_HELD_KERNELS(f64, double, 2)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 128, 1, 4)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 96, 1, 5)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 64, 1, 8)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 128, 2, 3)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 96, 2, 4)
+HC_ROW_HELD_KERNEL(f32, float, 4, 8, 64, 2, 6)
+HC_ROW_HELD_KERNEL(f32, float, 4, 4, 256, 1, 4)
+HC_ROW_HELD_KERNEL(f32, float, 4, 4, 256, 2, 3)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 128, 1, 3)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 96, 1, 4)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 64, 1, 6)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 128, 2, 2)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 96, 2, 3)
+HC_ROW_HELD_KERNEL(f64, double, 2, 8, 64, 2, 4)
+HC_ROW_HELD_KERNEL(f64, double, 2, 4, 256, 1, 3)
+HC_ROW_HELD_KERNEL(f64, double, 2, 4, 256, 2, 2)

@@ -123,6 +123,10 @@ bool aligned(const void *p, size_t a) {
 // Geometry of the tensor-core GEMM kernels (gemm_bf16_umma.cu).
 constexpr int kUmmaBM = 128, kUmmaBN = 256, kUmmaBK = 64;
 constexpr int kUmmaThreads = 192;
+
+// hcRowProgram holds a row in a CTA's registers when the row fills at least
+// this share of the CTA's packet slots.
+constexpr int kRowHeldFillPercent = 85;
 constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
                                   512 /*barriers*/;
 
@@ -380,8 +384,8 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->mappedStack = value; // 1: one work-group per CTA even where groups share a tile
     return 0;
   }
-  if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 1) {
-    c->rowVariant = value; // 1: warp-per-row kernel even for rows a CTA could hold
+  if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 3) {
+    c->rowVariant = value; // see hcRowProgram
     return 0;
   }
   return c->fail("Invalid option: %s = %lld", name, value);
@@ -628,23 +632,36 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
     wide = wide && aligned(p.in[k], 16) && p.inPitch[k] % perPacket == 0;
   char name[48];
   void *args[] = {&p};
-  // Rows of 257..1024 packets are held in the registers of one CTA per row
-  // (2 or 4 packets per thread); shorter ones would leave most of a CTA idle,
-  // longer ones do not fit.
+  // Rows of 257..1024 packets can be held in the registers of one CTA per row:
+  // eight packets per thread on 64, 96 or 128 threads.  That pays when the row
+  // fills most of the CTA's slots; otherwise a warp that walks the row is
+  // faster.  row_variant 1 never holds, 2 holds rows beyond 512 packets on 256
+  // threads with four packets each, 3 holds whatever the fill.
   const long long packets = p.cols / perPacket;
-  if (wide && packets > 256 && packets <= 1024 && c->rowVariant != 1 &&
-      p.rows <= 0x7fffffffLL) {
-    const int held = packets > 512 ? 4 : 2;
-    int temps = 0; // the temporaries the program saves to, t0 first
-    for (int pc = 0; pc < p.nInstr; ++pc) {
-      const uint32_t op = p.code[pc] & 0xffu;
-      if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
-        temps = std::max(temps, int(op - HC_MAP_SAVE0) + 1);
+  if (wide && packets > 256 && packets <= 1024 && c->rowVariant != 1) {
+    int held = 8;
+    size_t threads = packets > 768 ? 128 : packets > 512 ? 96 : 64;
+    if (c->rowVariant == 2 && packets > 512) {
+      held = 4;
+      threads = 256;
     }
-    std::snprintf(name, sizeof name, "hc_row_program_held_%s_v%d_p%d_n%d",
-                  dtype == HC_F32 ? "f32" : "f64", perPacket, held, p.nInputs);
-    const size_t smem = 256 + size_t(temps) * held * 16 * 256;
-    return c->launch(name, size_t(p.rows), 1, 1, 256, args, 1, smem);
+    // Measured with a log-softmax program on 512 MB: float rows that fill their
+    // CTA run at 3.6-4.0 TB/s held against 3.1-3.3 TB/s walked, and fall behind
+    // below about 85 % fill; double rows gain nothing (2.2 TB/s either way).
+    const bool filled = dtype == HC_F32 &&
+                        packets * 100 >= (long long)(held * threads) * kRowHeldFillPercent;
+    if (filled || c->rowVariant >= 2) {
+      int temps = 0; // the temporaries the program saves to, t0 first
+      for (int pc = 0; pc < p.nInstr; ++pc) {
+        const uint32_t op = p.code[pc] & 0xffu;
+        if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
+          temps = std::max(temps, int(op - HC_MAP_SAVE0) + 1);
+      }
+      std::snprintf(name, sizeof name, "hc_row_program_held_%s_v%d_p%d_t%d_n%d",
+                    dtype == HC_F32 ? "f32" : "f64", perPacket, held, int(threads), p.nInputs);
+      const size_t smem = 256 + size_t(temps) * held * 16 * threads;
+      return c->launch(name, size_t(p.rows), 1, 1, threads, args, 1, smem);
+    }
   }
   std::snprintf(name, sizeof name, "hc_row_program_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
                 wide ? perPacket : 1, p.nInputs);

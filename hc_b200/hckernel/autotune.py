@@ -35,6 +35,8 @@ _VARIANTS = {
              {}],
     "gemm_w8a16": [{"gemm_variant": 1}, {"gemm_variant": 2}],
     "softmax_rows": [{"softmax_variant": 1}, {"softmax_variant": 2}],
+    # a warp walks the row / a CTA holds it (on 256 threads; on as few as fit)
+    "row_program": [{"row_variant": 1}, {"row_variant": 2}, {"row_variant": 3}],
 }
 
 

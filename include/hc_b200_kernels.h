@@ -87,9 +87,12 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * (fp32 hcGemmTiled): 0 = automatic, 1 = no cp.async pipeline, 2 = pipeline
  * but no split of K over a cluster.  "mapped_stack":
  * 0 = hcMappedGemm stacks work-groups that share their f tile, 1 = one
- * work-group per CTA.  "row_variant": 0 = hcRowProgram holds rows of 257..1024
- * 16-byte packets in the registers of one CTA per row, 1 = always one warp per
- * row that walks the row once per pass. */
+ * work-group per CTA.  "row_variant" (hcRowProgram): 0 = float rows of 257..1024
+ * 16-byte packets that fill at least 85 % of a CTA's slots are held in the
+ * registers of one CTA per row (eight packets per thread on 64, 96 or 128
+ * threads), 1 = always one warp per row that walks the row once per pass,
+ * 2 = as 3, with 256 threads and four packets each beyond 512 packets,
+ * 3 = hold such rows whatever the fill. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* ---- workloads -------------------------------------------------------------

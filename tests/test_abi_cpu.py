@@ -218,8 +218,8 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
                 "hc_row_program_": {f"{kernel}{tv}_n{n}" for tv in ("f32_v4", "f32_v1", "f64_v2",
                                                                     "f64_v1")
                                     for n in (1, 2)}
-                | {f"{kernel}held_{tv}_p{held}_n{n}" for tv in ("f32_v4", "f64_v2")
-                   for held in (2, 4) for n in (1, 2)},
+                | {f"{kernel}held_{tv}_p{held}_t{threads}_n{n}" for tv in ("f32_v4", "f64_v2")
+                   for held, threads in ((8, 64), (8, 96), (8, 128), (4, 256)) for n in (1, 2)},
             }[kernel]
             assert family == expected
             for member in family:

@@ -233,6 +233,19 @@ def test_autotune_picks_a_variant_and_keeps_results_right(k, tmp_path):
     expect = np.zeros_like(x)
     oracle.softmax_rows(x, expect, 64)
     assert np.all(np.abs(d_y.cpu().numpy() - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+
+    # A row body: a warp that walks the row against a CTA that holds it.
+    from hc_b200.workloads import make_rowwise
+
+    centre = make_rowwise(lambda t: t - t.mean(axis=1, keepdims=True))
+    d_y.fill_(float("nan"))
+    tparams = autotune(centre, d_x, d_y, 64, repeats=3)
+    assert tparams.options.get("row_variant") in (1, 2, 3) and len(tparams.timings) == 3
+    centre.parametrize(tparams)(d_x, d_y, 64)
+    torch.cuda.synchronize()
+    x64 = x.astype(np.float64)
+    np.testing.assert_allclose(d_y.cpu().numpy(), x64 - x64.mean(axis=1, keepdims=True),
+                               rtol=2e-6, atol=1e-6)
     assert get_context(DEVICE).kernel_status() == 0
 
 

@@ -82,17 +82,19 @@ def _program(code, consts, d_in, d_out, pitch_in=None, pitch_out=None):
     return p
 
 
-@pytest.mark.parametrize("variant", [0, 1], ids=["held", "walked"])
+@pytest.mark.parametrize("variant", [0, 3, 2, 1], ids=["auto", "held", "held256", "walked"])
 @pytest.mark.parametrize("dtype,cols", [("float32", 4096), ("float32", 4092), ("float32", 2048),
                                         ("float32", 1028), ("float32", 1024), ("float64", 2048),
                                         ("float64", 1030), ("float64", 514), ("float64", 512)])
 def test_rows_held_in_registers_and_rows_walked_agree(hc, variant, dtype, cols):
-    """Rows of 257..1024 16-byte packets take the kernel that holds the row in the
-    registers of a CTA, others (and all rows under row_variant 1) the warp that
-    walks the row once per pass.  Two programs: log-softmax (max, sum, a uniform
-    prologue), and a variance normalisation that parks values in all three
-    temporaries (more than 48 KB of dynamic shared memory at four packets per
-    thread)."""
+    """Rows of 257..1024 16-byte packets that fill most of a CTA's slots take the
+    kernel that holds the row in registers (eight packets per thread on 64, 96 or
+    128 threads; row_variant 3 holds whatever the fill, 2 uses 256 threads with
+    four packets each beyond 512 packets), others (and all rows under row_variant
+    1) the warp that walks the row once per pass.  Two programs: log-softmax (max,
+    sum, a uniform prologue), and a variance normalisation that parks values in
+    all three temporaries (more than 48 KB of dynamic shared memory for rows
+    beyond 768 packets)."""
     rows = 19
     rng = np.random.default_rng(cols)
     x = rng.standard_normal((rows, cols)).astype(dtype)
@@ -136,6 +138,29 @@ def test_rows_held_in_registers_and_rows_walked_agree(hc, variant, dtype, cols):
         np.testing.assert_allclose(d_out.cpu().numpy(), want, **tol)
     finally:
         hc.set_option("row_variant", 0)
+
+
+@pytest.mark.parametrize("dtype,cols", [("float32", 4096), ("float32", 1540), ("float64", 1030)])
+def test_more_rows_than_resident_ctas(hc, dtype, cols):
+    """Several waves of CTAs of the held-row kernel: every row must come out as
+    its own centred self."""
+    rows = 1900
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(dtype) + np.arange(rows, dtype=dtype)[:, None]
+    d_x = torch.from_numpy(x).cuda()
+    d_out = torch.full((rows, cols), float("nan"), dtype=d_x.dtype, device="cuda")
+    centre = [ew.LOAD | 0 << 8, ew.RSUM | 0 << 8,
+              ew.LOAD | ew.UNIFORM | ew.SRC_SCALAR << 8, ew.MUL | ew.UNIFORM | ew.SRC_CONST << 8,
+              ew.SET | ew.UNIFORM | 1 << 8,
+              ew.LOAD | 0 << 8, ew.SUB | (ew.SRC_SCALAR + 1) << 8]
+    hc.row_program(_program(centre, [1.0 / cols], d_x, d_out),
+                   capi.HC_F32 if dtype == "float32" else capi.HC_F64)
+    finish(hc)
+    x64 = x.astype(np.float64)
+    # Row r lies around the value r, so a row taken from the wrong buffer is off
+    # by at least 1; the float32 mean of 4096 values near 1900 is good to ~5e-4.
+    tol = dict(rtol=0, atol=2e-3) if dtype == "float32" else dict(rtol=0, atol=1e-10)
+    np.testing.assert_allclose(d_out.cpu().numpy(), x64 - x64.mean(axis=1, keepdims=True), **tol)
 
 
 def test_held_rows_respect_pitches(hc):
