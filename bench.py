@@ -556,6 +556,18 @@ def run_gpu(args):
         torch.cuda.synchronize(dev)
         ms, launches = timed(fn, steps, warmup)
         ach, roof = roofline(name, ms / steps)
+        # Spread of single steps, each between its own pair of events (after the
+        # timed region, so the figures above are untouched).
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                  for _ in range(min(steps, 50))]
+        for e0, e1 in events:
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+        stream.synchronize()
+        each = sorted(e0.elapsed_time(e1) for e0, e1 in events)
+        roof["step_ms"] = {"min": each[0], "median": statistics.median(each),
+                           "steps": len(each)}
         return {"ms_per_step": ms / steps, "steps": steps, "launches": launches,
                 "status": ctx.kernel_status(), "value": ach * world, "unit": roof["unit"],
                 "roofline": roof}
