@@ -12,6 +12,7 @@ arithmetic, and a final round-to-nearest-even to bf16.
 
 from __future__ import annotations
 
+import re
 from concurrent.futures import ThreadPoolExecutor
 
 import numpy as np
@@ -329,12 +330,66 @@ def random_expression(rng, inputs: int, depth: int):
             return f"np.minimum({x}, {y})"
         return f"(({x}) {'+-*'[kind]} ({y}))"
 
-    import re
-
     while True:
         text = build(depth)
         if re.search(rf"\b[{names}]\b", text):  # at least one array takes part
             break
+    fn = eval(f"lambda {', '.join(names)}: {text}", {"np": np})  # noqa: S307 (own text)
+    return fn, text
+
+
+def random_row_expression(rng, inputs: int):
+    """A random row body of ``inputs`` matrices as ``(fn, text)``: one or two
+    reductions along the rows (sum, max, mean of a random element-wise
+    expression; the second may use the first) and a final element-wise
+    expression of the matrices and the reduced values.  Magnitudes stay tame:
+    divisors are ``abs(.) + 0.5``, exponentials are of ``-abs(.)``.  Used to test
+    the translation of recorded row bodies against NumPy on the same arrays."""
+    names = list("ab"[:inputs])
+
+    def build(level, leaves):
+        if level == 0 or rng.random() < 0.25:
+            if rng.random() < 0.8:
+                return str(rng.choice(leaves))
+            return repr(float(rng.choice([0.5, 1.0, 2.0, -1.5, 0.25])))
+        kind = rng.integers(0, 9)
+        x = build(level - 1, leaves)
+        if kind == 5:
+            return f"np.abs({x})"
+        if kind == 6:
+            return f"np.exp(-np.abs({x}))"
+        if kind == 7:
+            return f"np.sqrt(np.abs({x}) + 1.0)"
+        y = build(level - 1, leaves)
+        if kind == 3:
+            return f"(({x}) / (np.abs({y}) + 0.5))"
+        if kind == 4:
+            return f"np.maximum({x}, {y})"
+        if kind == 8:
+            return f"np.minimum({x}, {y})"
+        return f"(({x}) {'+-*'[kind]} ({y}))"
+
+    def with_array(level, leaves):
+        while True:
+            text = build(level, leaves)
+            if re.search(rf"\b[{''.join(names)}]\b", text):  # a matrix takes part
+                return text
+
+    def reduced(text):
+        how = str(rng.choice(["sum", "max", "mean"]))
+        return f"(({text}).{how}(axis=1, keepdims=True))"
+
+    # Reduced values travel as the placeholders R0, R1 until the end, so that
+    # "a matrix takes part" is asked of each expression's own leaves.
+    scalars = {"R0": reduced(with_array(int(rng.integers(0, 3)), names))}
+    if rng.random() < 0.5:
+        scalars["R1"] = reduced(with_array(int(rng.integers(1, 3)), names + ["R0"]))
+    text = with_array(int(rng.integers(1, 3)), names + list(scalars))
+    if not any(s in text for s in scalars):  # the body must use a reduction
+        text = f"(({text}) - {list(scalars)[-1]})"
+    for name in ("R1", "R0"):
+        if name in scalars:
+            text = text.replace(name, scalars[name])
     fn = eval(f"lambda {', '.join(names)}: {text}", {"np": np})  # noqa: S307 (own text)
     return fn, text
 

@@ -271,3 +271,36 @@ def test_row_program_through_the_c_abi(hc):
     p.nInputs = 3
     with pytest.raises(RuntimeError, match="inputs"):
         hc.row_program(p, capi.HC_F64)
+
+
+@pytest.mark.parametrize("cols", [4096, 3072, 2048, 1000, 777])
+def test_random_row_bodies_against_numpy(cols):
+    """Random row bodies through the front door on rows that are held by 128, 96
+    and 64 threads, on walked rows and on rows that are no multiple of 16 bytes.
+    The float32 kernel must be as close to the float64 value of the expression
+    as NumPy's own float32 evaluation is, up to a small factor (sum orders and
+    a few ulp in exp differ; anything structural is off by far more)."""
+    rng = np.random.default_rng(cols)
+    rows, done = 21, 0
+    while done < 12:
+        count = int(rng.integers(1, 3))
+        fn, text = oracle.random_row_expression(rng, count)
+        k = make_rowwise(fn, count)
+        inputs = oracle.make_elementwise_inputs(count, (rows, cols), "float32", seed=done + cols)
+        d_in = [torch.from_numpy(a).cuda() for a in inputs]
+        d_out = torch.full((rows, cols), float("nan"), device="cuda")
+        try:
+            k(*d_in, d_out, 8)
+        except Exception as e:  # noqa: BLE001 - too long for the machine: not this test's subject
+            assert "more than" in str(e), text
+            continue
+        torch.cuda.synchronize()
+        done += 1
+        got = d_out.cpu().numpy().astype(np.float64)
+        with np.errstate(all="ignore"):
+            single = fn(*inputs).astype(np.float64)
+            truth = fn(*[a.astype(np.float64) for a in inputs])
+        scale = np.abs(truth).max(axis=1, keepdims=True) + 1e-30
+        ours = (np.abs(got - truth) / scale).max()
+        numpys = (np.abs(single - truth) / scale).max()
+        assert ours <= 8 * numpys + 2e-6, (text, ours, numpys)

@@ -96,3 +96,29 @@ def test_row_bodies_outside_the_family():
     with pytest.raises(UnsupportedKernel, match="float32 or float64"):
         make_rowwise(lambda t: t - t.max(axis=1, keepdims=True)).plan_for(
             (F((8, 16), "int32"), F((8, 16), "int32"), 8))
+
+
+def test_random_row_bodies_translate():
+    """150 random row bodies (one or two reductions, the second possibly of an
+    expression of the first): the multi-pass program, run one NumPy operation
+    per instruction in float64, must agree with NumPy on the expression."""
+    rng = np.random.default_rng(77)
+    translated = 0
+    for _ in range(150):
+        count = int(rng.integers(1, 3))
+        fn, text = oracle.random_row_expression(rng, count)
+        k = make_rowwise(fn, count)
+        try:
+            plan = k.plan_for(tuple(F((8, 32), "float64") for _ in range(count + 1)) + (4,))
+        except UnsupportedKernel as e:  # too many values parked at once, too long
+            assert "more than" in str(e), text
+            continue
+        assert plan.family == "row_program", text
+        translated += 1
+        inputs = oracle.make_elementwise_inputs(count, (8, 32), "float64", seed=translated)
+        got = run_program(plan.roles["code"], plan.roles["consts"],
+                          [inputs[i] for i in plan.roles["inputs"]], "float64", (8, 32))
+        with np.errstate(all="ignore"):
+            want = fn(*inputs)
+        np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-13, err_msg=text)
+    assert translated > 100
