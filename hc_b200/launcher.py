@@ -124,6 +124,17 @@ class ShardedLauncher:
         if x_shard.shape[0]:
             conv(x_shard, f_full, out_shard)
 
+    def rows_body(self, body, in_shards, out_shard, group_rows: int = 256):
+        """Row-sharded element-wise or row body: ``body`` is a kernel from
+        :func:`hc_b200.workloads.make_rowwise` (called with the rows per group) or
+        :func:`hc_b200.workloads.make_elementwise` (``group_rows=None``); rows are
+        independent, so ``gather_rows`` assembles the result."""
+        if out_shard.shape[0]:
+            if group_rows is None:
+                body(*in_shards, out_shard)
+            else:
+                body(*in_shards, out_shard, group_rows)
+
     # -- the one collective: gather the output ------------------------------------------
     def gather_rows(self, shard, full):
         """All-gather row shards (``partition`` order) into ``full`` on every rank."""

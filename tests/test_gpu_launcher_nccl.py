@@ -104,6 +104,28 @@ def _worker(rank, world, port, results):
         oracle.conv_implicit_gemm(x, f, expect, 1)
         ok["conv_images"] = bool(np.allclose(o_full.cpu().numpy(), expect, rtol=1e-5, atol=1e-5))
 
+        # Row bodies and element-wise bodies shard by rows like the softmax.
+        from hc_b200.workloads import make_elementwise, make_rowwise
+
+        rows = 301  # 151 + 150 rows of 4096: held in registers by the row-program kernel
+        (x,) = oracle.make_elementwise_inputs(1, (rows, 4096), "float32", seed=5)
+        span = L.rows(rows)
+        xs = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        ys = torch.full_like(xs, float("nan"))
+        centre = make_rowwise(lambda t: t - t.mean(axis=1, keepdims=True), 1, f"cuda:{rank}")
+        L.rows_body(centre, [xs], ys, 64)
+        full = torch.empty(rows, 4096, device=dev)
+        L.gather_rows(ys, full)
+        x64 = x.astype(np.float64)
+        ok["rows_body"] = bool(np.allclose(full.cpu().numpy(), x64 - x64.mean(axis=1, keepdims=True),
+                                           rtol=2e-6, atol=1e-6))
+        relu = make_elementwise(lambda t: np.maximum(t * 2.0 - 1.0, 0.0), 1, 2, (4, 256),
+                                f"cuda:{rank}")
+        L.rows_body(relu, [xs], ys, None)
+        L.gather_rows(ys, full)
+        ok["map_body"] = bool(np.array_equal(full.cpu().numpy(),
+                                             np.maximum(x * np.float32(2) - np.float32(1), 0)))
+
         ok["status"] = get_context(f"cuda:{rank}").kernel_status() == 0
         results[rank] = ok
     finally:

@@ -117,6 +117,35 @@ def _worker(rank, world, port, rows, results):
         expect = np.zeros((24, n), np.float32)
         oracle.gemm_w8a16(a, w, s, expect, (8, 16))
         ok["dequant_cols"] = np.array_equal(o_full.numpy(), expect)
+
+        # A row body (rows centred on their mean) and an element-wise body, sharded
+        # by rows; the stand-ins run the oracle's tile arithmetic.
+        def centre(t):
+            return t - t.mean(axis=1, keepdims=True)
+
+        def centre_body(x_t, out_t, gm):
+            o = np.zeros(tuple(out_t.shape), np.float32)
+            oracle.rowwise(centre, [x_t.numpy()], o, gm)
+            out_t.copy_(torch.from_numpy(o))
+
+        def double_body(x_t, out_t):
+            o = np.zeros(tuple(out_t.shape), np.float32)
+            oracle.elementwise(lambda t: t * 2.0, [x_t.numpy()], o, (4, 16))
+            out_t.copy_(torch.from_numpy(o))
+
+        (x,) = oracle.make_elementwise_inputs(1, (rows, 40), "float32", seed=3)
+        span = L.rows(rows)
+        xs = torch.from_numpy(x[span.begin:span.end].copy())
+        ys = torch.empty_like(xs)
+        L.rows_body(centre_body, [xs], ys, 8)
+        full = torch.empty(rows, 40)
+        L.gather_rows(ys, full)
+        expect = np.zeros_like(x)
+        oracle.rowwise(centre, [x], expect, 8)
+        ok["rows_body"] = np.array_equal(full.numpy(), expect)
+        L.rows_body(double_body, [xs], ys, None)
+        L.gather_rows(ys, full)
+        ok["map_body"] = np.array_equal(full.numpy(), x * 2)
         results[rank] = ok
     finally:
         dist.destroy_process_group()
