@@ -638,7 +638,8 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
   // faster.  row_variant 1 never holds, 2 holds rows beyond 512 packets on 256
   // threads with four packets each, 3 holds whatever the fill.
   const long long packets = p.cols / perPacket;
-  if (wide && packets > 256 && packets <= 1024 && c->rowVariant != 1) {
+  if (wide && packets > 256 && packets <= 1024 && c->rowVariant != 1 &&
+      p.rows <= 0x7fffffffLL /* one CTA per row */) {
     int held = 8;
     size_t threads = packets > 768 ? 128 : packets > 512 ? 96 : 64;
     if (c->rowVariant == 2 && packets > 512) {
