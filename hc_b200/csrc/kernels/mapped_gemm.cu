@@ -36,15 +36,16 @@
 // one chunk before its copies are issued.
 //
 // TY x TX threads (8 or 16 each way), each owning MY adjacent rows and MX
-// adjacent columns of the result (1, 2 or 4), so that one 8- or 16-byte
-// shared-memory load brings all of a thread's rows (columns) for one k.  A
+// adjacent columns of the result (1, 2, 4, or 8 rows in the 128-row pieces), so
+// that one or two 8- or 16-byte shared-memory loads bring all of a thread's
+// rows (columns) for one k.  A
 // chunk is [k][row] and [k][column] with 4-element groups XOR-swizzled with k,
 // so that the copies of a warp spread over the banks.  Tiles larger than
 // TY*MY x TX*MX are walked in pieces.
 //
 // Work-groups whose f tile is the same (consecutive output positions of the
 // convolution) are stacked: one CTA takes up to eight of them, as long as the
-// stacked rows fit one 64-row piece, gathers the f tile once and multiplies it
+// stacked rows fit one piece (128 rows for float, 64 for double), gathers the f tile once and multiplies it
 // with the rows of all of them.  The result of every group is what it would be
 // alone (same sum order); the stack only shares the B side.
 //
@@ -122,7 +123,16 @@ __device__ __forceinline__ int swizzled(int kk, int c) {
 template <typename T, int N, int SPAN>
 __device__ __forceinline__ void loadRun(const T (&row)[SPAN], int kk, int c, T (&dst)[N]) {
   constexpr int bytes = N * int(sizeof(T));
-  if constexpr (N == 4) {
+  if constexpr (N == 8) { // two runs of four
+    T low[4], high[4];
+    loadRun<T, 4, SPAN>(row, kk, c, low);
+    loadRun<T, 4, SPAN>(row, kk, c + 4, high);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dst[i] = low[i];
+      dst[4 + i] = high[i];
+    }
+  } else if constexpr (N == 4) {
     const T *src = &row[swizzled<SPAN>(kk, c) & ~3];
     alignas(16) T raw[4];
 #pragma unroll
@@ -166,7 +176,7 @@ __device__ __forceinline__ void waitCopies() {
 template <int SPAN>
 struct Side {
   static constexpr int threads = SPAN >= 32 ? 16 : 8;
-  static constexpr int each = SPAN / threads; // 1, 2, 2, 4 for 8, 16, 32, 64
+  static constexpr int each = SPAN / threads; // 1, 2, 2, 4, 8 for 8, 16, 32, 64, 128
 };
 
 template <int SY, int SX>
@@ -344,8 +354,8 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 } // namespace
 
-// One kernel per piece shape SY x SX (8, 16, 32 or 64 each way); the launcher
-// picks the smallest piece that holds the tile.
+// One kernel per piece shape SY x SX (8, 16, 32 or 64 each way, and 128 rows
+// for float); the launcher picks the smallest piece that holds the tile.
 #define HC_MAPPED_KERNEL(T, tname, SY, SX)                                              \
   extern "C" __global__ void                                                            \
       __launch_bounds__(threadsOf<SY, SX>(), residentCtas<T, SY, SX>())                 \
@@ -365,3 +375,10 @@ __device__ __forceinline__ void mappedGemm(const HcMappedGemmParams &p) {
 
 HC_MAPPED_KERNELS(float, f32)
 HC_MAPPED_KERNELS(double, f64)
+// Tall pieces for stacks of work-groups (float only: three stages of a
+// 128-row piece of doubles would not fit the static shared memory): a thread
+// owns 8 rows, so a k costs three 16-byte shared loads for 32 products where
+// the 64-row piece needs two for 16.  Only with 16 threads across: on 8 the
+// copies per thread would double.
+HC_MAPPED_KERNEL(float, f32, 128, 32)
+HC_MAPPED_KERNEL(float, f32, 128, 64)

@@ -380,8 +380,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->tiledVariant = value;
     return 0;
   }
-  if (std::strcmp(name, "mapped_stack") == 0 && value >= 0 && value <= 1) {
-    c->mappedStack = value; // 1: one work-group per CTA even where groups share a tile
+  if (std::strcmp(name, "mapped_stack") == 0 && value >= 0 && value <= 2) {
+    // 1: one work-group per CTA even where groups share a tile; 2: stacks of at
+    // most 64 rows.
+    c->mappedStack = value;
     return 0;
   }
   if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 3) {
@@ -865,19 +867,22 @@ int hcMappedGemm(HcContext c, const HcMappedOperand *x, const HcMappedOperand *f
   if (out->transposed)
     return c->fail("hcMappedGemm: the tables of out must be in row-major order");
   // Smallest piece (8, 16, 32 or 64 each way) that holds the tile; larger tiles
-  // are walked in 64-wide pieces by the kernel.  A side of 32 or 64 is worked
+  // are walked in 64-wide pieces by the kernel.  A side of 32 or more is worked
   // on by 16 threads, a shorter one by 8 (mapped_gemm.cu: Side).
   auto side = [](int extent) { return extent <= 8 ? 8 : extent <= 16 ? 16 : extent <= 32 ? 32 : 64; };
   // Work-groups that share their f tile are stacked along the rows of one CTA:
   // the largest power of two that the caller vouches for (f->sharedRun), that
-  // the kernel holds (8) and that keeps the stacked rows within one 64-row piece.
+  // the kernel holds (8) and that keeps the stacked rows within one piece: 128
+  // rows for float tiles of more than 16 columns (mapped_stack 2: 64), else 64.
+  const int sx = side(TN);
+  const int tallest = dtype == HC_F32 && sx >= 32 && c->mappedStack != 2 ? 128 : 64;
   int stack = 1;
   while (stack * 2 <= 8 && stack * 2 <= f->sharedRun && f->sharedRun % (stack * 2) == 0 &&
-         (long long)stack * 2 * TM <= 64 && c->mappedStack != 1)
+         (long long)stack * 2 * TM <= tallest && c->mappedStack != 1)
     stack *= 2;
   p.stack = stack;
   p.groups = groups;
-  const int sy = side(stack * TM), sx = side(TN);
+  const int sy = stack * TM > 64 && tallest == 128 ? 128 : side(stack * TM);
   const int threads = (sy >= 32 ? 16 : 8) * (sx >= 32 ? 16 : 8);
   char name[48];
   std::snprintf(name, sizeof name, "hc_mapped_gemm_%s_%dx%d", dtype == HC_F32 ? "f32" : "f64", sy,

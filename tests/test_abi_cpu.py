@@ -211,7 +211,8 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
             family = {s for s in symbols[image] if s.startswith(kernel)}
             expected = {
                 "hc_mapped_gemm_": {f"{kernel}{t}_{sy}x{sx}" for t in ("f32", "f64")
-                                    for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)},
+                                    for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)}
+                | {f"{kernel}f32_128x32", f"{kernel}f32_128x64"},
                 "hc_map_elements_": {f"{kernel}{tv}_n{n}{i}" for tv in ("f32_v4", "f32_v1", "f64_v2",
                                                                         "f64_v1")
                                      for n in (1, 2, 3, 4) for i in ("", "i")},

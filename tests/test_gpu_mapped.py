@@ -77,6 +77,11 @@ def test_stacked_groups_give_what_single_groups_give(tiles):
     conv.parametrize(TunedParams({}, {"mapped_stack": 1}))(d_x, d_f, single)
     torch.cuda.synchronize()
     assert torch.equal(stacked, single)
+    # Stacks kept within 64 rows (the float default goes up to 128-row pieces).
+    short = torch.full(out_shape, -3.0, device="cuda")
+    conv.parametrize(TunedParams({}, {"mapped_stack": 2}))(d_x, d_f, short)
+    torch.cuda.synchronize()
+    assert torch.equal(short, single)
     np.testing.assert_allclose(stacked.cpu().numpy(), oracle.conv_direct(x, f, 1),
                                rtol=1e-4, atol=1e-4)
 
