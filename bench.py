@@ -578,7 +578,7 @@ def run_gpu(args):
         h_ins = [t.cpu().pin_memory() for t in ins]
         h_outs = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
 
-        if name in ("softmax", "reduce", "gemm_bf16"):
+        if name in ("softmax", "reduce", "gemm_bf16", "map", "rows"):
             # Row-wise workloads (and the rows of A in a GEMM) have a host-buffer
             # entry point that streams row chunks through the GPU (upload,
             # kernel and download overlapped).
@@ -592,6 +592,10 @@ def run_gpu(args):
                         hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
                     elif name == "reduce":
                         hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
+                    elif name == "map":
+                        hc_host.rows_body_host(map_kernel(), h_ins, h_outs[0], desc, group_rows=None)
+                    elif name == "rows":
+                        hc_host.rows_body_host(rows_kernel(), h_ins, h_outs[0], desc)
                     else:
                         hc_host.gemm_host(h_ins[0], h_ins[1], h_outs[0], desc)
         else:

@@ -150,6 +150,27 @@ def reduce_rows_host(x_host, sum_host, max_host, device="cuda:0", chunk_rows=Non
         [x_host], [sum_host, max_host])
 
 
+def rows_body_host(body, in_hosts, out_host, device="cuda:0", chunk_rows=None, group_rows=256):
+    """An element-wise or row body on host matrices: ``body`` is a kernel from
+    :func:`hc_b200.workloads.make_rowwise` (called as ``body(*ins, out,
+    group_rows)``) or :func:`hc_b200.workloads.make_elementwise`
+    (``group_rows=None``: ``body(*ins, out)``) made for ``device``; the inputs
+    and ``out`` are [M, N] of one dtype.  Rows are independent in both, so row
+    chunks stream through the GPU as in :func:`softmax_rows_host`."""
+    in_hosts = list(in_hosts)
+    if not in_hosts or any(t.shape != out_host.shape or t.dtype != out_host.dtype
+                           for t in in_hosts) or out_host.dim() != 2:
+        raise ValueError("rows_body_host: inputs and out must be matrices of one shape and dtype")
+
+    def launch(ins, outs):
+        if group_rows is None:
+            body(*ins, outs[0])
+        else:
+            body(*ins, outs[0], group_rows)
+
+    _pipeline(device, chunk_rows or _default_chunk_rows(out_host)).run(launch, in_hosts, [out_host])
+
+
 _resident = {}
 
 

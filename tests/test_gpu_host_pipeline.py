@@ -75,3 +75,34 @@ def test_reduce_rows_host_matches_oracle():
     assert np.all(np.abs(hs.numpy() - exact) <= 1e-5 * np.abs(x).astype(np.float64).sum(axis=1))
     with pytest.raises(ValueError, match="expected x"):
         hc_host.reduce_rows_host(hx, hs[:10], hm, "cuda:0")
+
+
+def test_rows_body_host_equals_single_launch():
+    """A row body (rows centred and scaled by their own statistics) and an
+    element-wise body on host matrices, in ragged row chunks: bit for bit what one
+    launch on the whole matrix gives."""
+    from hc_b200.workloads import make_elementwise, make_rowwise
+
+    rows, cols = 777, 2048
+    a, b = oracle.make_elementwise_inputs(2, (rows, cols), "float32", seed=21)
+    ha, hb = torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()
+    hy = torch.full((rows, cols), float("nan")).pin_memory()
+    body = make_rowwise(lambda t: (t - t.mean(axis=1, keepdims=True))
+                        / np.sqrt((t * t).sum(axis=1, keepdims=True) + 1.0))
+    hc_host.rows_body_host(body, [ha], hy, "cuda:0", chunk_rows=200, group_rows=64)
+    hc_host.synchronize("cuda:0")
+    d_y = torch.empty(rows, cols, device="cuda")
+    body(ha.cuda(), d_y, 64)
+    torch.cuda.synchronize()
+    assert torch.equal(hy, d_y.cpu())
+    a64 = a.astype(np.float64)
+    want = (a64 - a64.mean(axis=1, keepdims=True)) / np.sqrt((a64 * a64).sum(axis=1, keepdims=True) + 1)
+    np.testing.assert_allclose(hy.numpy(), want, rtol=1e-5, atol=1e-6)
+
+    relu = make_elementwise(lambda s, t: np.maximum(s * 2.0 - t, 0.0), 2, 2, (4, 256))
+    hy.fill_(float("nan"))
+    hc_host.rows_body_host(relu, [ha, hb], hy, "cuda:0", chunk_rows=333, group_rows=None)
+    hc_host.synchronize("cuda:0")
+    assert np.array_equal(hy.numpy(), np.maximum(a * np.float32(2) - b, 0))
+    with pytest.raises(ValueError, match="one shape and dtype"):
+        hc_host.rows_body_host(relu, [ha, hb[:10]], hy, "cuda:0", group_rows=None)
