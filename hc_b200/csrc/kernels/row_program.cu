@@ -21,7 +21,10 @@ namespace {
 
 using namespace hcmap;
 
-constexpr int UNROLL = 2;
+// Packets per lane and decode of the walking kernel.  Four (three CTAs per SM
+// for float) measured 3.8 TB/s on a log-softmax of 4096-column rows where two
+// (four CTAs per SM) gave 3.1: the decode is shared by twice the elements.
+constexpr int UNROLL = 4;
 
 template <typename T, int V>
 __device__ __forceinline__ Packet<T, V> loadPacketKept(const T *p) {
@@ -330,7 +333,7 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
 } // namespace
 
 #define HC_ROW_KERNEL(tname, T, V, NIN)                                                 \
-  extern "C" __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 3 : 4)         \
+  extern "C" __global__ void __launch_bounds__(THREADS, sizeof(T) == 8 ? 2 : 3)         \
       hc_row_program_##tname##_v##V##_n##NIN(const __grid_constant__ HcMapProgramDev p) { \
     rowProgram<T, V, NIN>(p);                                                           \
   }

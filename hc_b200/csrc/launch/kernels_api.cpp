@@ -53,7 +53,8 @@ const KernelEntry kKernelTable[] = {
     // width, number of input arrays, and whether element indices are operands.
     {"hc_map_elements_", "map_elements"},
     // hc_row_program_{f32_v4,f32_v1,f64_v2,f64_v1}_n{1,2} (a warp walks the row) and
-    // hc_row_program_held_{f32_v4,f64_v2}_p{2,4}_n{1,2} (a CTA holds the row).
+    // hc_row_program_held_{f32_v4,f64_v2}_p{8_t64,8_t96,8_t128,4_t256}_n{1,2} (a CTA
+    // holds the row: packets per thread, threads).
     {"hc_row_program_", "row_program"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
@@ -123,12 +124,12 @@ bool aligned(const void *p, size_t a) {
 // Geometry of the tensor-core GEMM kernels (gemm_bf16_umma.cu).
 constexpr int kUmmaBM = 128, kUmmaBN = 256, kUmmaBK = 64;
 constexpr int kUmmaThreads = 192;
+constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
+                                  512 /*barriers*/;
 
 // hcRowProgram holds a row in a CTA's registers when the row fills at least
 // this share of the CTA's packet slots.
-constexpr int kRowHeldFillPercent = 85;
-constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
-                                  512 /*barriers*/;
+constexpr int kRowHeldFillPercent = 90;
 
 } // namespace
 
@@ -648,10 +649,11 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
       held = 4;
       threads = 256;
     }
-    // Measured with a log-softmax program on 512 MB: float rows that fill their
-    // CTA run at 3.6-4.0 TB/s held against 3.1-3.3 TB/s walked, and fall behind
-    // below about 85 % fill; double rows gain nothing (2.2 TB/s either way).
-    const bool filled = dtype == HC_F32 &&
+    // Measured with a log-softmax program on 512 MB: float rows that fill a CTA
+    // of 64 or 128 threads run at 3.8-4.0 TB/s held against 3.65-3.8 TB/s walked
+    // and fall behind below about 90 % fill; on 96 threads (3.6 against 3.7 TB/s)
+    // and for doubles (2.2 against 2.4 TB/s) walking is faster throughout.
+    const bool filled = dtype == HC_F32 && threads != 96 &&
                         packets * 100 >= (long long)(held * threads) * kRowHeldFillPercent;
     if (filled || c->rowVariant >= 2) {
       int temps = 0; // the temporaries the program saves to, t0 first

@@ -89,7 +89,7 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * 0 = hcMappedGemm stacks work-groups that share their f tile (up to 128 rows
  * of float tiles wider than 16 columns, else 64), 1 = one work-group per CTA,
  * 2 = stacks of at most 64 rows.  "row_variant" (hcRowProgram): 0 = float rows of 257..1024
- * 16-byte packets that fill at least 85 % of a CTA's slots are held in the
+ * 16-byte packets that fill at least 90 % of a CTA of 64 or 128 threads are held in the
  * registers of one CTA per row (eight packets per thread on 64, 96 or 128
  * threads), 1 = always one warp per row that walks the row once per pass,
  * 2 = as 3, with 256 threads and four packets each beyond 512 packets,
