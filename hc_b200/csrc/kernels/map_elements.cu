@@ -22,10 +22,11 @@ namespace {
 
 using namespace hcmap;
 
-constexpr int UNROLL = 2;
-
 template <typename T, int V, int NIN, bool INDEXED>
 __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
+  // Packets per thread and decode: four with one or two inputs (three CTAs per
+  // SM), two beyond (the inputs of four packets would not fit the registers).
+  constexpr int UNROLL = NIN <= 2 ? 4 : 2;
   constexpr int W = V * UNROLL;
   __shared__ T temps[3][W][THREADS];
   const T noScalars[4] = {T(0), T(0), T(0), T(0)};
@@ -87,11 +88,11 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
 // a twin of each (suffix `i`) for programs that use the element indices, so
 // that the streaming kernels do not carry the index bookkeeping.
 #define HC_MAP_KERNEL(tname, T, V, NIN)                                                 \
-  extern "C" __global__ void __launch_bounds__(THREADS, 4)                              \
+  extern "C" __global__ void __launch_bounds__(THREADS, NIN <= 2 ? 3 : 4)                              \
       hc_map_elements_##tname##_v##V##_n##NIN(const __grid_constant__ HcMapProgramDev p) { \
     mapRows<T, V, NIN, false>(p);                                                       \
   }                                                                                     \
-  extern "C" __global__ void __launch_bounds__(THREADS, 4)                              \
+  extern "C" __global__ void __launch_bounds__(THREADS, NIN <= 2 ? 3 : 4)                              \
       hc_map_elements_##tname##_v##V##_n##NIN##i(const __grid_constant__ HcMapProgramDev p) { \
     mapRows<T, V, NIN, true>(p);                                                        \
   }

@@ -589,9 +589,11 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s", dtype == HC_F32 ? "f32" : "f64",
                 v, std::max(1, p.nInputs), usesIndices ? "i" : "");
   const long long perRow = p.cols / v;
-  // One CTA per 512 packets of a row (two per thread); rows beyond 65535 and
-  // very long rows are walked by the kernel's strides.
-  long long gx = std::min<long long>(ceilDiv(perRow, 512), 1 << 20);
+  // One CTA per 1024 packets of a row (four per thread; 512 and two with three
+  // or four inputs - map_elements.cu); rows beyond 65535 and very long rows are
+  // walked by the kernel's strides.
+  const long long perCta = p.nInputs <= 2 ? 1024 : 512;
+  long long gx = std::min<long long>(ceilDiv(perRow, perCta), 1 << 20);
   long long gy = std::min<long long>(p.rows, 65535);
   void *args[] = {&p};
   return c->launch(name, size_t(gx), size_t(gy), 1, 256, args, 1, 0);
