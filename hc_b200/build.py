@@ -110,13 +110,14 @@ def build_cubins(verbose=False, force=False):
 
 
 def _write_images_asm(cubins, path: Path):
-    """Assembly that embeds each cubin and a name/begin/end table."""
+    """Assembly that embeds each cubin and a name/begin/end table.  The cubins
+    are named by file name only; the assembler finds them through ``-I``."""
     lines = ['.section .rodata', '.balign 16']
     for i, c in enumerate(cubins):
         lines += [
             f"hc_img_name_{i}: .asciz \"{c.stem}\"",
             ".balign 16",
-            f"hc_img_begin_{i}: .incbin \"{c}\"",
+            f"hc_img_begin_{i}: .incbin \"{c.name}\"",
             f"hc_img_end_{i}:",
             ".balign 16",
         ]
@@ -168,7 +169,7 @@ def build_libs(verbose=False, force=False):
         static_obj = OUT / "w8a16_static.o"
         _run([cuda / "bin" / "nvcc", *NVCC_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "-cudart", "static", *inc, "-c", "-o", static_obj, static_src], verbose)
-        _run([cxx, *CXX_FLAGS, *inc, "-o", kernels, srcs[0], asm, static_obj,
+        _run([cxx, *CXX_FLAGS, *inc, "-I", OUT, "-o", kernels, srcs[0], asm, static_obj,
               "-L", OUT, "-lhc-gpu-runtime-loader", "-L", cuda / "lib64", "-lcudart_static",
               "-lrt", "-lpthread", "-ldl"], verbose)
 

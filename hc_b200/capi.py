@@ -27,6 +27,7 @@ OLX_DEVICE_CC_MAJOR = 2
 OLX_DEVICE_CC_MINOR = 3
 OLX_DEVICE_L2_BYTES = 4
 OLX_DEVICE_MAX_SMEM_OPTIN = 5
+OLX_DEVICE_ORDINAL = 6
 
 _sz = C.c_size_t
 _vp = C.c_void_p
@@ -101,6 +102,16 @@ OLX_PROTOTYPES = {
         C.c_int,
         [_vp, _vp, C.c_uint, _sz, C.c_uint, C.POINTER(C.c_int)],
     ),
+    "olxDeviceContextEnter": (C.c_int, [_vp]),
+    "olxDeviceContextLeave": (C.c_int, [_vp]),
+    "olxPointerDevice": (C.c_int, [_vp, _vp, C.POINTER(C.c_int)]),
+    "olxCreateEvent": (_vp, [_vp]),
+    "olxReleaseEvent": (None, [_vp, _vp]),
+    "olxRecordEvent": (C.c_int, [_vp, _vp]),
+    "olxQueueWaitEvent": (C.c_int, [_vp, _vp]),
+    "olxEventElapsedMs": (C.c_int, [_vp, _vp, _vp, C.POINTER(C.c_float)]),
+    "olxHostRegister": (C.c_int, [_vp, _vp, _sz]),
+    "olxHostUnregister": (C.c_int, [_vp, _vp]),
 }
 LOADER_EXTRA_PROTOTYPES = {
     "setGPULoaderSearchPaths": (None, [C.POINTER(C.c_char_p), _sz]),

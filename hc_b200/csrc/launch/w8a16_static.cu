@@ -19,8 +19,9 @@
 // ordering between them) would convert into the same bytes and race.  Calls
 // issued on one context are ordered by its queue and are safe.
 //
-// The first call on a device does set-up work - it asks the CUDA runtime for
-// the device address of the array and makes sure the kernel images are loaded
+// The first call on a device does set-up work - with the context's own CUDA
+// context made current it asks the CUDA runtime for the device address of the
+// array, and it makes sure the kernel images are loaded
 // - and should therefore be made before any stream capture is started on the
 // context's stream.  After that the entry point calls no cudaMalloc, cudaFree
 // or any other allocating routine: it looks up a cached pointer and launches.
@@ -44,27 +45,29 @@ static __device__ __align__(256) unsigned char hcW8A16Scratch[kScratchBytes];
 std::mutex setupLock;
 void *scratchOnDevice[kMaxDevices]; // device address of the array, per ordinal
 
-// Device address of the scratch array on `device`, resolved once per device
-// with that device current.  Returns nullptr and fills `why` on failure.
-void *scratchAddress(int device, char *why, size_t whyLen) {
+// Device address of the scratch array on the context's GPU, resolved once per
+// GPU.  The context's own primary context is made current for the look-up (a
+// push and a pop through the backend), so the calling thread's device is never
+// changed and no other GPU is touched.  Returns nullptr and fills `why` on
+// failure.
+void *scratchAddress(HcContext c, int ordinal, char *why, size_t whyLen) {
   std::lock_guard<std::mutex> lock(setupLock);
-  if (scratchOnDevice[device])
-    return scratchOnDevice[device];
-  int previous = -1;
-  cudaError_t rc = cudaGetDevice(&previous);
-  if (rc == cudaSuccess)
-    rc = cudaSetDevice(device);
+  if (scratchOnDevice[ordinal])
+    return scratchOnDevice[ordinal];
+  OlDevice dev = hcContextDevice(c);
+  if (olxDeviceContextEnter(dev)) {
+    snprintf(why, whyLen, "hcGemmW8A16Static: could not make the context's device current");
+    return nullptr;
+  }
   void *ptr = nullptr;
-  if (rc == cudaSuccess)
-    rc = cudaGetSymbolAddress(&ptr, hcW8A16Scratch);
-  if (previous >= 0 && previous != device)
-    cudaSetDevice(previous);
+  const cudaError_t rc = cudaGetSymbolAddress(&ptr, hcW8A16Scratch);
+  olxDeviceContextLeave(dev);
   if (rc != cudaSuccess || !ptr) {
     snprintf(why, whyLen, "cudaGetSymbolAddress for the static scratch failed: %s",
              cudaGetErrorString(rc));
     return nullptr;
   }
-  scratchOnDevice[device] = ptr;
+  scratchOnDevice[ordinal] = ptr;
   return ptr;
 }
 
@@ -91,14 +94,25 @@ int hcGemmW8A16Static(HcContext c, const void *a, const void *w,
   }
   if (M <= 0 || N <= 0 || K <= 0) // nothing to convert; let the common path validate
     return hcGemmW8A16(c, a, w, scale, out, nullptr, 0, M, N, K, lda, ldw, ldc);
-  // The array belongs to the GPU that holds the output.
-  cudaPointerAttributes attr;
-  if (cudaPointerGetAttributes(&attr, out) != cudaSuccess ||
-      attr.type != cudaMemoryTypeDevice || attr.device < 0 || attr.device >= kMaxDevices) {
-    cudaGetLastError();
+  // The scratch is the array of the context's GPU, and `out` must live there
+  // too: a context never launches against another GPU's copy of the array.
+  OlDevice dev = hcContextDevice(c);
+  long long ordinal = -1;
+  if (olxDeviceAttribute(dev, OLX_DEVICE_ORDINAL, &ordinal) || ordinal < 0 ||
+      ordinal >= kMaxDevices)
+    return hcReportError(c, "hcGemmW8A16Static: the context's device has no usable ordinal");
+  int owner = -1;
+  if (olxPointerDevice(dev, out, &owner))
+    return 1;
+  if (owner < 0)
     return hcReportError(c, "hcGemmW8A16Static: `out` is not a device pointer");
+  if (owner != int(ordinal)) {
+    snprintf(why, sizeof(why),
+             "hcGemmW8A16Static: `out` lives on cuda:%d but the context drives cuda:%lld",
+             owner, ordinal);
+    return hcReportError(c, why);
   }
-  void *scratch = scratchAddress(attr.device, why, sizeof(why));
+  void *scratch = scratchAddress(c, int(ordinal), why, sizeof(why));
   if (!scratch)
     return hcReportError(c, why);
   return hcGemmW8A16(c, a, w, scale, out, scratch, kScratchBytes, M, N, K, lda, ldw, ldc);

@@ -92,6 +92,16 @@ struct Backend {
   decltype(&olxDeviceAttribute) DeviceAttribute = nullptr;
   decltype(&olxEncodeTensorMap2D) EncodeTensorMap2D = nullptr;
   decltype(&olxMaxActiveClusters) MaxActiveClusters = nullptr;
+  decltype(&olxDeviceContextEnter) DeviceContextEnter = nullptr;
+  decltype(&olxDeviceContextLeave) DeviceContextLeave = nullptr;
+  decltype(&olxPointerDevice) PointerDevice = nullptr;
+  decltype(&olxCreateEvent) CreateEvent = nullptr;
+  decltype(&olxReleaseEvent) ReleaseEvent = nullptr;
+  decltype(&olxRecordEvent) RecordEvent = nullptr;
+  decltype(&olxQueueWaitEvent) QueueWaitEvent = nullptr;
+  decltype(&olxEventElapsedMs) EventElapsedMs = nullptr;
+  decltype(&olxHostRegister) HostRegister = nullptr;
+  decltype(&olxHostUnregister) HostUnregister = nullptr;
 };
 
 struct Reporter {
@@ -162,6 +172,16 @@ std::unique_ptr<Backend> openBackend(const std::string &path,
   HC_BIND_OPT(DeviceAttribute);
   HC_BIND_OPT(EncodeTensorMap2D);
   HC_BIND_OPT(MaxActiveClusters);
+  HC_BIND_OPT(DeviceContextEnter);
+  HC_BIND_OPT(DeviceContextLeave);
+  HC_BIND_OPT(PointerDevice);
+  HC_BIND_OPT(CreateEvent);
+  HC_BIND_OPT(ReleaseEvent);
+  HC_BIND_OPT(RecordEvent);
+  HC_BIND_OPT(QueueWaitEvent);
+  HC_BIND_OPT(EventElapsedMs);
+  HC_BIND_OPT(HostRegister);
+  HC_BIND_OPT(HostUnregister);
 #undef HC_BIND_OPT
   return b;
 }
@@ -445,6 +465,88 @@ int olxMaxActiveClusters(OlQueue q, OlKernel k, unsigned blockThreads,
   return fn ? fn(queue->inner, kernel->inner, blockThreads, sharedMemSize,
                  clusterSize, clustersRet)
             : missing(queue->device, "olxMaxActiveClusters");
+}
+
+int olxDeviceContextEnter(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->DeviceContextEnter;
+  return fn ? fn(dev->inner) : missing(dev, "olxDeviceContextEnter");
+}
+
+int olxDeviceContextLeave(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->DeviceContextLeave;
+  return fn ? fn(dev->inner) : missing(dev, "olxDeviceContextLeave");
+}
+
+int olxPointerDevice(OlDevice d, const void *ptr, int *ordinalRet) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->PointerDevice;
+  return fn ? fn(dev->inner, ptr, ordinalRet) : missing(dev, "olxPointerDevice");
+}
+
+OlxEvent olxCreateEvent(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return nullptr;
+  auto fn = dev->api->CreateEvent;
+  if (!fn) {
+    missing(dev, "olxCreateEvent");
+    return nullptr;
+  }
+  return fn(dev->inner);
+}
+
+void olxReleaseEvent(OlDevice d, OlxEvent ev) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (dev && dev->api->ReleaseEvent)
+    dev->api->ReleaseEvent(dev->inner, ev);
+}
+
+int olxRecordEvent(OlQueue q, OlxEvent ev) noexcept {
+  auto *queue = static_cast<QueueHandle *>(q);
+  if (!queue)
+    return 1;
+  auto fn = queue->device->api->RecordEvent;
+  return fn ? fn(queue->inner, ev) : missing(queue->device, "olxRecordEvent");
+}
+
+int olxQueueWaitEvent(OlQueue q, OlxEvent ev) noexcept {
+  auto *queue = static_cast<QueueHandle *>(q);
+  if (!queue)
+    return 1;
+  auto fn = queue->device->api->QueueWaitEvent;
+  return fn ? fn(queue->inner, ev) : missing(queue->device, "olxQueueWaitEvent");
+}
+
+int olxEventElapsedMs(OlDevice d, OlxEvent from, OlxEvent to, float *msRet) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->EventElapsedMs;
+  return fn ? fn(dev->inner, from, to, msRet) : missing(dev, "olxEventElapsedMs");
+}
+
+int olxHostRegister(OlDevice d, void *ptr, size_t size) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->HostRegister;
+  return fn ? fn(dev->inner, ptr, size) : missing(dev, "olxHostRegister");
+}
+
+int olxHostUnregister(OlDevice d, void *ptr) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->HostUnregister;
+  return fn ? fn(dev->inner, ptr) : missing(dev, "olxHostUnregister");
 }
 
 } // extern "C"

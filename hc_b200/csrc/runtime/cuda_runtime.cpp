@@ -449,6 +449,9 @@ int olxDeviceAttribute(OlDevice d, int what, long long *valueRet) noexcept {
   case OLX_DEVICE_MAX_SMEM_OPTIN:
     attr = CU_DEVICE_ATTRIBUTE_MAX_SHARED_MEMORY_PER_BLOCK_OPTIN;
     break;
+  case OLX_DEVICE_ORDINAL:
+    *valueRet = dev->ordinal;
+    return 0;
   default:
     dev->report(OlSeverity::Error, "Invalid device attribute: %d", what);
     return 1;
@@ -561,6 +564,126 @@ int olxEncodeTensorMap2D(OlDevice d, void *mapOut, int elemKind,
                          : CU_TENSOR_MAP_SWIZZLE_NONE,
           CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+}
+
+int olxDeviceContextEnter(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev)
+    return 1;
+  return dev->check("cuCtxPushCurrent",
+                    DriverApi::get().CtxPushCurrent(dev->context));
+}
+
+int olxDeviceContextLeave(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev)
+    return 1;
+  return dev->check("cuCtxPopCurrent", DriverApi::get().CtxPopCurrent(nullptr));
+}
+
+int olxPointerDevice(OlDevice d, const void *ptr, int *ordinalRet) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !ordinalRet)
+    return 1;
+  *ordinalRet = -1;
+  if (!ptr)
+    return 0;
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  const DriverApi &cu = DriverApi::get();
+  const auto address = reinterpret_cast<CUdeviceptr>(ptr);
+  unsigned memoryType = 0;
+  // A pointer the driver has never seen is not an error here: it is host memory.
+  if (cu.PointerGetAttribute(&memoryType, CU_POINTER_ATTRIBUTE_MEMORY_TYPE,
+                             address) != CUDA_SUCCESS ||
+      memoryType != CU_MEMORYTYPE_DEVICE)
+    return 0;
+  int ordinal = -1;
+  if (dev->check("cuPointerGetAttribute",
+                 cu.PointerGetAttribute(&ordinal, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL,
+                                        address)))
+    return 1;
+  *ordinalRet = ordinal;
+  return 0;
+}
+
+OlxEvent olxCreateEvent(OlDevice d) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev)
+    return nullptr;
+  ContextScope scope(dev);
+  if (!scope)
+    return nullptr;
+  CUevent ev = nullptr;
+  if (dev->check("cuEventCreate", DriverApi::get().EventCreate(&ev, CU_EVENT_DEFAULT)))
+    return nullptr;
+  return ev;
+}
+
+void olxReleaseEvent(OlDevice d, OlxEvent ev) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !ev)
+    return;
+  ContextScope scope(dev);
+  if (scope)
+    dev->check("cuEventDestroy", DriverApi::get().EventDestroy(static_cast<CUevent>(ev)));
+}
+
+int olxRecordEvent(OlQueue queue, OlxEvent ev) noexcept {
+  auto *q = static_cast<QueueState *>(queue);
+  if (!q || !ev)
+    return 1;
+  ContextScope scope(q->device);
+  if (!scope)
+    return 1;
+  return q->device->check(
+      "cuEventRecord", DriverApi::get().EventRecord(static_cast<CUevent>(ev), q->stream));
+}
+
+int olxQueueWaitEvent(OlQueue queue, OlxEvent ev) noexcept {
+  auto *q = static_cast<QueueState *>(queue);
+  if (!q || !ev)
+    return 1;
+  ContextScope scope(q->device);
+  if (!scope)
+    return 1;
+  return q->device->check(
+      "cuStreamWaitEvent",
+      DriverApi::get().StreamWaitEvent(q->stream, static_cast<CUevent>(ev), 0));
+}
+
+int olxEventElapsedMs(OlDevice d, OlxEvent from, OlxEvent to, float *msRet) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !from || !to || !msRet)
+    return 1;
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  return dev->check("cuEventElapsedTime",
+                    DriverApi::get().EventElapsedTime(msRet, static_cast<CUevent>(from),
+                                                      static_cast<CUevent>(to)));
+}
+
+int olxHostRegister(OlDevice d, void *ptr, size_t size) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !ptr || size == 0)
+    return 1;
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  return dev->check("cuMemHostRegister",
+                    DriverApi::get().MemHostRegister(ptr, size, CU_MEMHOSTREGISTER_PORTABLE));
+}
+
+int olxHostUnregister(OlDevice d, void *ptr) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !ptr)
+    return 1;
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  return dev->check("cuMemHostUnregister", DriverApi::get().MemHostUnregister(ptr));
 }
 
 } // extern "C"

@@ -50,6 +50,14 @@ struct DriverApi {
 
   CUresult (*OccupancyMaxActiveClusters)(int *, CUfunction,
                                          const CUlaunchConfig *) = nullptr;
+  CUresult (*PointerGetAttribute)(void *, CUpointer_attribute, CUdeviceptr) = nullptr;
+  CUresult (*EventCreate)(CUevent *, unsigned) = nullptr;
+  CUresult (*EventDestroy)(CUevent) = nullptr;
+  CUresult (*EventRecord)(CUevent, CUstream) = nullptr;
+  CUresult (*EventElapsedTime)(float *, CUevent, CUevent) = nullptr;
+  CUresult (*StreamWaitEvent)(CUstream, CUevent, unsigned) = nullptr;
+  CUresult (*MemHostRegister)(void *, size_t, unsigned) = nullptr;
+  CUresult (*MemHostUnregister)(void *) = nullptr;
 
   bool ok = false;
   std::string error;
@@ -109,7 +117,15 @@ private:
          bind(MemsetD8Async, "cuMemsetD8Async") &&
          bind(LaunchKernel, "cuLaunchKernel") &&
          bind(TensorMapEncodeTiled, "cuTensorMapEncodeTiled") &&
-         bind(OccupancyMaxActiveClusters, "cuOccupancyMaxActiveClusters");
+         bind(OccupancyMaxActiveClusters, "cuOccupancyMaxActiveClusters") &&
+         bind(PointerGetAttribute, "cuPointerGetAttribute") &&
+         bind(EventCreate, "cuEventCreate") &&
+         bind(EventDestroy, "cuEventDestroy_v2") &&
+         bind(EventRecord, "cuEventRecord") &&
+         bind(EventElapsedTime, "cuEventElapsedTime") &&
+         bind(StreamWaitEvent, "cuStreamWaitEvent") &&
+         bind(MemHostRegister, "cuMemHostRegister_v2") &&
+         bind(MemHostUnregister, "cuMemHostUnregister");
   }
 };
 

@@ -115,6 +115,7 @@ OFFLOAD_API_EXPORT int olxMemsetD8(OlQueue q, void *dst, int value,
 #define OLX_DEVICE_CC_MINOR 3
 #define OLX_DEVICE_L2_BYTES 4
 #define OLX_DEVICE_MAX_SMEM_OPTIN 5
+#define OLX_DEVICE_ORDINAL 6 /* the N of the "cuda:N" the device was created from */
 OFFLOAD_API_EXPORT int olxDeviceAttribute(OlDevice dev, int what,
                                           long long *valueRet) HC_NOEXCEPT;
 
@@ -137,6 +138,40 @@ OFFLOAD_API_EXPORT int olxMaxActiveClusters(OlQueue q, OlKernel k,
                                             size_t sharedMemSize,
                                             unsigned clusterSize,
                                             int *clustersRet) HC_NOEXCEPT;
+
+/* Makes the device's primary context current on the calling thread until the
+ * matching olxDeviceContextLeave (a push and a pop of the driver's context
+ * stack; the thread's previous context, if any, is current again afterwards).
+ * For code that must call another CUDA library on this device without
+ * changing the thread's device.  Returns 0 on success. */
+OFFLOAD_API_EXPORT int olxDeviceContextEnter(OlDevice dev) HC_NOEXCEPT;
+OFFLOAD_API_EXPORT int olxDeviceContextLeave(OlDevice dev) HC_NOEXCEPT;
+
+/* Which GPU owns the memory `ptr` points into: *ordinalRet is its ordinal, or
+ * -1 when `ptr` is not device memory (host memory, unknown to the driver).
+ * Returns 0 on success. */
+OFFLOAD_API_EXPORT int olxPointerDevice(OlDevice dev, const void *ptr,
+                                        int *ordinalRet) HC_NOEXCEPT;
+
+/* Events order work between queues of one device without blocking the host:
+ * olxRecordEvent marks a point in a queue, olxQueueWaitEvent makes everything
+ * submitted to a queue afterwards wait for that point.  The reference needs
+ * none because it synchronises the host after every launch
+ * (python/cpp/py-runtime/src/GpuRuntime.cpp:67). */
+typedef void *OlxEvent;
+OFFLOAD_API_EXPORT OlxEvent olxCreateEvent(OlDevice dev) HC_NOEXCEPT;
+OFFLOAD_API_EXPORT void olxReleaseEvent(OlDevice dev, OlxEvent ev) HC_NOEXCEPT;
+OFFLOAD_API_EXPORT int olxRecordEvent(OlQueue q, OlxEvent ev) HC_NOEXCEPT;
+OFFLOAD_API_EXPORT int olxQueueWaitEvent(OlQueue q, OlxEvent ev) HC_NOEXCEPT;
+/* Milliseconds between two recorded events that have both completed. */
+OFFLOAD_API_EXPORT int olxEventElapsedMs(OlDevice dev, OlxEvent from, OlxEvent to,
+                                         float *msRet) HC_NOEXCEPT;
+
+/* Page-locks (pins) an existing host range so that copies to and from it run
+ * asynchronously at full link speed, and undoes it.  Returns 0 on success. */
+OFFLOAD_API_EXPORT int olxHostRegister(OlDevice dev, void *ptr,
+                                       size_t size) HC_NOEXCEPT;
+OFFLOAD_API_EXPORT int olxHostUnregister(OlDevice dev, void *ptr) HC_NOEXCEPT;
 
 #ifdef __cplusplus
 }

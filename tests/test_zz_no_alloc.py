@@ -60,6 +60,58 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     try:
         _both_ways(hc, (256, 512, 1024), 0)
         _both_ways(hc, (192, 272, 520), 7)  # smaller, ragged N: reuses the same scratch
+        _both_ways(hc, (160, 264, 520), 3)  # N not a multiple of 16: padded scratch pitch
+    finally:
+        hc.close()
+
+
+def test_static_scratch_takes_the_largest_admitted_weights():
+    """4096 x 4096 weights need exactly the 32 MiB the scratch holds."""
+    hc = capi.Context("cuda:0")
+    try:
+        assert hc.gemm_w8a16_workspace_bytes(4096, 4096) == hc.lib.hcGemmW8A16StaticMaxBytes()
+        _both_ways(hc, (64, 4096, 4096), 1)
+    finally:
+        hc.close()
+
+
+def test_static_scratch_calls_after_the_first_allocate_nothing():
+    """What the entry point is for: once the first call on a device has done its
+    set-up, a call changes neither the free device memory nor torch's pool."""
+    hc = capi.Context("cuda:0")
+    try:
+        m, n, k = 128, 512, 512
+        a, w, s = oracle.make_inputs("gemm_w8a16", shape=(m, n, k))
+        d_a, d_w, d_s = dev_bf16(a), dev(w), dev(s)
+        out = empty_like_dev((m, n), torch.bfloat16)
+
+        def call():
+            hc.gemm_w8a16_static(d_a.data_ptr(), d_w.data_ptr(), d_s.data_ptr(), out.data_ptr(),
+                                 m, n, k, k, n, n)
+            finish(hc)
+
+        call()  # set-up: symbol address, kernel images
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.cuda.memory_reserved() == reserved_before
+    finally:
+        hc.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_static_scratch_refuses_an_output_on_another_gpu():
+    hc = capi.Context("cuda:0")
+    try:
+        here = torch.empty(256 * 512, dtype=torch.bfloat16, device="cuda:0")
+        there = torch.empty(128 * 256, dtype=torch.bfloat16, device="cuda:1")
+        with pytest.raises(capi.HcError, match="lives on cuda:1 but the context drives cuda:0"):
+            hc.gemm_w8a16_static(here.data_ptr(), here.data_ptr(), here.data_ptr(),
+                                 there.data_ptr(), 128, 256, 512, 512, 256, 256)
     finally:
         hc.close()
 
