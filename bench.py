@@ -21,9 +21,14 @@ default headline the other four are measured too and reported under
              row-wise workloads through the host-buffer entry points
              (``hc_b200.host``: row chunks with upload, ``@kernel`` call and
              download overlapped), the GEMMs as copy, ``@kernel`` call, copy.
-* scaling is weak: every rank runs the full single-GPU workload on its own
-  rows (shards are independent, so no collective is in the timed path);
-  ``value`` is the sum over ranks divided by the slowest rank's time.
+* with several GPUs the scaling is strong: the fixed full-size problem is
+  sharded (rows of the softmax, of the reductions and of the row bodies, M of
+  the bf16 GEMM, N of the dequant GEMM), every rank runs the kernels on its
+  share and the timed step ends with the NCCL all-gather that leaves the whole
+  output on every GPU; ``phases`` times the kernels and the collective apart,
+  and the gathered output is compared with the single-GPU output and with the
+  CPU oracle inside the run.  ``--replicas`` runs independent replicas instead
+  (weak scaling, no collective).
 """
 
 import argparse
@@ -376,13 +381,30 @@ def run_reference(args):
 
 
 # ---- GPU arm ----------------------------------------------------------------------------
+# Sharding of each workload across ranks (strong scaling: the problem is the
+# fixed full-size one, a rank works on its share, every rank ends with the whole
+# output).  "rows": the rows of the output (softmax, reductions, row and
+# element-wise bodies; M of the bf16 GEMM with B replicated); "cols": N of the
+# dequant GEMM with A replicated; "replicas": too small to shard.
+SHARDING = {"softmax": "rows", "rows": "rows", "map": "rows", "reduce": "rows",
+            "gemm_bf16": "rows", "gemm_w8a16": "cols", "gemm_f32": "replicas",
+            "conv": "replicas"}
+
+# Row bands per workload at N > 1 (launcher.BandPlan): the all-gather of band b
+# overlaps the kernel of band b + 1.
+DEFAULT_BANDS = {"softmax": 8, "rows": 8, "map": 8, "reduce": 1, "gemm_bf16": 2}
+# Which inputs of a row-sharded workload are split by rows (the others are replicated).
+ROW_INPUTS = {"softmax": (0,), "rows": (0,), "map": (0, 1), "reduce": (0,), "gemm_bf16": (0,)}
+
+
 def run_gpu(args):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     from hc_b200._native import _dispatcher as native
     from hc_b200.hckernel.kernel import get_context
-    from hc_b200.launcher import init_process_group
+    from hc_b200.launcher import BandPlan, ShardedLauncher, init_process_group, partition
     from hc_b200.workloads import make_kernels
 
     rank, world, local = init_process_group()
@@ -395,6 +417,8 @@ def run_gpu(args):
     ctx = get_context(desc)
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
     peaks = load_peaks()
+    launcher = ShardedLauncher(kernels, rank, world)
+    sharded = world > 1 and not args.replicas
 
     def barrier():
         ctx.synchronize()
@@ -410,54 +434,88 @@ def run_gpu(args):
         return float(t.item())
 
     def timed(fn, steps, warmup):
-        """ms for `steps` calls of fn on the context's stream (max over ranks)
-        and the number of kernel launches they issued."""
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        before = ctx.launch_count
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        barrier()
+        """ms for `steps` calls of fn queued from the context's stream (max over
+        ranks) and the number of kernel launches they issued."""
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            before = ctx.launch_count
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
         return max_over_ranks(e0.elapsed_time(e1)), ctx.launch_count - before
 
-    def device_inputs(name):
-        """Device-resident synthetic inputs and outputs of one workload."""
-        g = torch.Generator(device=dev).manual_seed(1000 + rank)
-        s = SHAPES[name]
-        if name in ("softmax", "rows"):
-            x = torch.randn(*s, device=dev, generator=g)
-            return [x], [torch.empty_like(x)]
-        if name == "reduce":
-            x = torch.rand(*s, device=dev, generator=g) * 20 - 10
-            return [x], [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
-        if name == "map":
-            a = torch.randn(*s, device=dev, generator=g)
-            b = torch.randn(*s, device=dev, generator=g)
-            return [a, b], [torch.empty_like(a)]
-        if name == "conv":
-            xs, fs, os_ = conv_shapes(s)
-            x = torch.randn(*xs, device=dev, generator=g)
-            f = torch.randn(*fs, device=dev, generator=g)
-            return [x, f], [torch.zeros(*os_, device=dev)]
-        m, n, k = s
-        if name == "gemm_f32":
-            a = torch.rand(m, k, device=dev, generator=g) * 2 - 1
-            b = torch.rand(k, n, device=dev, generator=g) * 2 - 1
-            return [a, b], [torch.empty(m, n, device=dev)]
-        if name == "gemm_bf16":
-            a = (torch.randn(m, k, device=dev, generator=g) * 0.02).bfloat16()
-            b = (torch.randn(k, n, device=dev, generator=g) * 0.02).bfloat16()
-            return [a, b], [torch.empty(m, n, device=dev, dtype=torch.bfloat16)]
-        a = torch.randn(m, k, device=dev, generator=g).bfloat16()
-        w = torch.randint(-127, 128, (k, n), device=dev, generator=g, dtype=torch.int8)
-        sc = torch.rand(n, device=dev, generator=g) * 0.019 + 0.001
-        return [a, w, sc], [torch.empty(m, n, device=dev, dtype=torch.bfloat16)]
+    def timed_regions(fn, steps, warmup, min_seconds=0.2, max_regions=64):
+        """Regions of exactly `steps` steps, repeated until they cover
+        `min_seconds`; returns per-step ms of every region and the launches of one."""
+        per_step, launches, total = [], 0, 0.0
+        while not per_step or (total < min_seconds * 1e3 and len(per_step) < max_regions):
+            ms, launches = timed(fn, steps, warmup if not per_step else 0)
+            per_step.append(ms / steps)
+            total += ms
+        return per_step, launches
 
-    conv_cache = []
+    # ---- inputs: the seeded arrays of the benchmark configurations ---------------
+    def to_device(array, bf16=False):
+        t = torch.from_numpy(np.ascontiguousarray(array)).to(dev)
+        return t.bfloat16() if bf16 else t
+
+    inputs_cache = {}
+
+    def baseline_inputs(name):
+        if name not in inputs_cache:
+            inputs_cache.clear()  # one workload's arrays at a time
+            inputs_cache[name] = draw_inputs(name)
+        return inputs_cache[name]
+
+    def draw_inputs(name):
+        """(host arrays on rank 0 or None, device tensors on every rank, what they
+        are).  Rank 0 draws them with the configuration's own generator and seed
+        and the other ranks receive them over NCCL, so every GPU works on the
+        arrays the parity tests use; workloads outside the five configurations
+        draw on the device."""
+        s = SHAPES[name]
+        config = {"softmax": "softmax", "rows": "softmax", "reduce": "reduce",
+                  "gemm_f32": "gemm_f32", "gemm_bf16": "gemm_bf16",
+                  "gemm_w8a16": "gemm_w8a16"}.get(name)
+        if config is None:
+            g = torch.Generator(device=dev).manual_seed(1000)
+            if name == "map":
+                return None, [torch.randn(*s, device=dev, generator=g) for _ in range(2)], \
+                    "torch.randn on the device, seed 1000"
+            xs, fs, _ = conv_shapes(s)
+            return None, [torch.randn(*xs, device=dev, generator=g),
+                          torch.randn(*fs, device=dev, generator=g)], \
+                "torch.randn on the device, seed 1000"
+        kinds = {"gemm_bf16": (True, True), "gemm_w8a16": (True, False, False)}.get(
+            name, (False,) * 3)
+        host, tensors = None, []
+        if rank == 0:
+            from oracle import workloads as oracle
+
+            host = oracle.make_inputs(config, shape=s)
+            tensors = [to_device(a, bf) for a, bf in zip(host, kinds)]
+        if world > 1:
+            shapes = {"softmax": [s], "rows": [s], "reduce": [s],
+                      "gemm_f32": [(s[0], s[2]), (s[2], s[1])],
+                      "gemm_bf16": [(s[0], s[2]), (s[2], s[1])],
+                      "gemm_w8a16": [(s[0], s[2]), (s[2], s[1]), (s[1],)]}[name]
+            dtypes = {"gemm_bf16": [torch.bfloat16] * 2,
+                      "gemm_w8a16": [torch.bfloat16, torch.int8, torch.float32]}.get(
+                          name, [torch.float32] * 2)
+            if rank != 0:
+                tensors = [torch.empty(sh, dtype=dt, device=dev) for sh, dt in zip(shapes, dtypes)]
+            for t in tensors:
+                dist.broadcast(t, src=0)
+        seed = {"gemm_f32": 0, "softmax": 1, "rows": 1, "reduce": 2, "gemm_bf16": 3,
+                "gemm_w8a16": 4}[name]
+        return host, tensors, f"numpy default_rng({seed}) arrays of the configuration, uploaded"
+
+    conv_cache, rows_cache, map_cache = [], [], []
 
     def conv_kernel():
         if not conv_cache:
@@ -469,16 +527,12 @@ def run_gpu(args):
                 {sym.TN: tn, sym.TNF: tnf, sym.KB: kb}))
         return conv_cache[0]
 
-    rows_cache = []
-
     def rows_kernel():
         if not rows_cache:
             from hc_b200.workloads import make_rowwise
 
             rows_cache.append(make_rowwise(log_softmax, 1, desc))
         return rows_cache[0]
-
-    map_cache = []
 
     def map_kernel():
         if not map_cache:
@@ -487,31 +541,51 @@ def run_gpu(args):
             map_cache.append(make_elementwise(relu_axpby, 2, 2, (4, 256), desc))
         return map_cache[0]
 
-    def direct_call(name, ins, outs):
-        """The C++ dispatcher entry of the workload (no Python front door)."""
-        if name == "softmax":
-            return lambda: native.softmax_rows(ctx, ins[0], outs[0])
+    def output_like(name, ins):
+        s = SHAPES[name]
+        if name in ("softmax", "rows", "map"):
+            return [torch.empty(s, device=dev)]
         if name == "reduce":
-            return lambda: native.reduce_rows(ctx, ins[0], outs[0], outs[1])
+            return [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
+        if name == "conv":
+            return [torch.zeros(*conv_shapes(s)[2], device=dev)]
+        dtype = torch.float32 if name == "gemm_f32" else torch.bfloat16
+        return [torch.empty(s[0], s[1], device=dev, dtype=dtype)]
+
+    def row_call(name, ins, outs):
+        """The C++ dispatcher entry of a workload on row views (no Python front
+        door): returns fn(in_views, out_views)."""
+        if name == "softmax":
+            return lambda i, o: native.softmax_rows(ctx, i[0], o[0])
+        if name == "reduce":
+            return lambda i, o: native.reduce_rows(ctx, i[0], o[0], o[1])
         if name in ("gemm_f32", "gemm_bf16"):
-            return lambda: native.gemm(ctx, ins[0], ins[1], outs[0])
+            return lambda i, o: native.gemm(ctx, i[0], i[1], o[0])
         if name == "map":
             roles = map_kernel().plan_for((ins[0], ins[1], outs[0])).roles
-            arrays = [ins[i] for i in roles["inputs"]]
-            return lambda: native.map_elements(ctx, arrays, outs[0], roles["code"], roles["consts"])
+            order = roles["inputs"]
+            return lambda i, o: native.map_elements(ctx, [i[k] for k in order], o[0],
+                                                    roles["code"], roles["consts"])
         if name == "rows":
             roles = rows_kernel().plan_for((ins[0], outs[0], 256)).roles
-            return lambda: native.row_program(ctx, [ins[0]], outs[0], roles["code"],
-                                              roles["consts"])
+            return lambda i, o: native.row_program(ctx, [i[0]], o[0], roles["code"],
+                                                   roles["consts"])
         if name == "conv":
             # The index tables belong to the launch plan; made once, outside the timing.
             spec = conv_kernel().plan_for((ins[0], ins[1], outs[0])).roles["spec"]
             tx, tf, to = spec.device_tables((ins[0], ins[1], outs[0]))
-            return lambda: native.mapped_gemm(ctx, ins[0], tx, ins[1], tf, outs[0], to,
-                                              spec.groups, spec.tm, spec.tn, spec.k)
-        n, k = ins[1].shape[1], ins[1].shape[0]
-        ws = torch.empty(native.w8a16_workspace_bytes(n, k), dtype=torch.uint8, device=dev)
-        return lambda: native.gemm_w8a16(ctx, ins[0], ins[1], ins[2], outs[0], ws)
+            return lambda i, o: native.mapped_gemm(ctx, i[0], tx, i[1], tf, o[0], to,
+                                                   spec.groups, spec.tm, spec.tn, spec.k)
+        spaces = {}
+
+        def w8a16(i, o):
+            n, k = i[1].shape[1], i[1].shape[0]
+            ws = spaces.get((n, k))
+            if ws is None:
+                ws = spaces[(n, k)] = torch.empty(native.w8a16_workspace_bytes(n, k),
+                                                  dtype=torch.uint8, device=dev)
+            native.gemm_w8a16(ctx, i[0], i[1], i[2], o[0], ws)
+        return w8a16
 
     def public_call(name, ins, outs):
         """The same workload through the @kernel call surface."""
@@ -531,8 +605,11 @@ def run_gpu(args):
             return lambda: rows_kernel()(ins[0], outs[0], 256)
         return lambda: kernels.dequant_dot(ins[0], ins[1], ins[2], outs[0], (256, 256))
 
-    def roofline(name, per_step_ms):
+    def roofline(name, per_step_ms, share=1.0):
+        """Throughput of `share` x the full problem done in `per_step_ms`, and the
+        roofline record that goes with it."""
         nbytes, flops, bound = algorithmic(name)
+        nbytes, flops = nbytes * share, flops * share
         if bound == "hbm":
             ach = nbytes / per_step_ms / 1e6
             return ach, {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -549,34 +626,241 @@ def run_gpu(args):
                      "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
                      "traffic": NCU_TRAFFIC[name], "peak_source": peaks["source"]}
 
-    def measure(name, steps, warmup):
+    # ---- in-run parity: sampled rows of the output against the CPU oracle -----------
+    def oracle_rows(name, host, rows):
+        """Expected output rows `rows` (float64 where the bound needs it) and the
+        per-element error bound, computed on rank 0 from the host arrays."""
+        from oracle import workloads as oracle
+
+        if name == "softmax":
+            expect = np.zeros((len(rows), host[0].shape[1]), np.float32)
+            oracle.softmax_rows(host[0][rows], expect, 32)
+            return [expect], [1e-6 + 1e-5 * np.abs(expect)]
+        if name == "rows":
+            expect = np.zeros((len(rows), host[0].shape[1]), np.float32)
+            oracle.rowwise(log_softmax, [host[0][rows]], expect, 32)
+            return [expect], [1e-5 + 1e-5 * np.abs(expect)]
+        if name == "reduce":
+            x = host[0][rows]
+            exact = x.astype(np.float64).sum(axis=1)
+            return [exact, x.max(axis=1).astype(np.float64)], \
+                [1e-5 * np.abs(x).astype(np.float64).sum(axis=1), np.zeros(len(rows))]
+        if name == "gemm_bf16":
+            a, b = host
+            expect = np.zeros((len(rows), b.shape[1]), np.float32)
+            oracle.gemm_bf16(a[rows], b, expect, (256, 256))
+            return [expect], [1e-2 * np.abs(expect) + 1e-4 * (np.abs(a[rows]) @ np.abs(b))]
+        if name == "gemm_w8a16":
+            a, w, sc = host
+            expect = np.zeros((len(rows), w.shape[1]), np.float32)
+            oracle.gemm_w8a16(a[rows], w, sc, expect, (256, 256))
+            mag = np.abs(a[rows]) @ (np.abs(w.astype(np.float32)) * sc)
+            return [expect], [1e-2 * np.abs(expect) + 1e-4 * mag]
+        if name == "gemm_f32":
+            a, b = host
+            expect = a[rows].astype(np.float64) @ b.astype(np.float64)
+            return [expect], [1e-5 * (np.abs(a[rows]).astype(np.float64)
+                                      @ np.abs(b).astype(np.float64))]
+        raise ValueError(name)
+
+    def verify(name, host, outs, samples=96):
+        """Every rank compares sampled rows of its own copy of the output with the
+        oracle's rows (computed once, on rank 0, and sent round)."""
+        if name in ("map", "conv"):
+            return None  # no host arrays: these are covered by the GPU test-suite only
+        m = outs[0].shape[0]
+        rows = np.unique(np.r_[0:8, m - 8:m,
+                               np.random.default_rng(11).integers(0, m, samples)]).astype(np.int64)
+        expect = bound = None
+        if rank == 0:
+            expect, bound = oracle_rows(name, host, rows)
+        if world > 1:
+            box = [expect, bound]
+            dist.broadcast_object_list(box, src=0)
+            expect, bound = box
+        index = torch.from_numpy(rows).to(dev)
+        worst = 0.0
+        for out, e, b in zip(outs, expect, bound):
+            got = out[index].double().cpu().numpy()
+            err = np.abs(got - e.astype(np.float64))
+            if not np.all(err <= b):
+                raise AssertionError(f"{name}: rank {rank}: output differs from the oracle on "
+                                     f"{int((err > b).sum())} sampled elements")
+            scale = np.maximum(b, 1e-300)
+            worst = max(worst, float((err / scale).max())) if b.any() else worst
+        return {"rows_checked": int(len(rows)), "worst_error_over_bound": worst, "ok": True}
+
+    # ---- one workload -----------------------------------------------------------------
+    def measure(name, steps, warmup, regions=True):
         """Device-resident throughput of one workload; returns a result dict."""
-        ins, outs = device_inputs(name)
-        fn = direct_call(name, ins, outs)
+        host, ins, data = baseline_inputs(name)
+        full_outs = output_like(name, ins)
+        call = row_call(name, ins, full_outs)
+        mode = SHARDING[name] if sharded else "single"
+        phases = parity_note = None
+
+        single = lambda: call(ins, full_outs)  # noqa: E731  the whole problem on this GPU
+        if mode in ("single", "replicas"):
+            step = single
+            units = float(world)  # replicas: every rank does the whole problem
+        elif mode == "rows":
+            m = full_outs[0].shape[0]
+            want = args.bands or DEFAULT_BANDS[name]
+            bands = max(1, want)
+            while bands > 1 and m % (bands * world):
+                bands //= 2
+            plan = BandPlan(m, world, bands)
+            # Inputs whose first dimension is the row dimension are sharded; the
+            # others (B of the GEMM) are replicated.
+            shard_in = [plan.take_shard(t, rank).contiguous() if k in ROW_INPUTS[name] else t
+                        for k, t in enumerate(ins)]
+            sharded_outs = [torch.empty_like(t) for t in full_outs]
+            if name == "reduce":
+                # One in-place all-gather for both vectors: rank r writes its sums and
+                # maxima into pair[r, 0] and pair[r, 1]; two small copies lay them out.
+                share = m // world
+                pair = torch.empty(world, 2, share, device=dev)
+
+                def compute(band, loc, out_block):
+                    call([shard_in[0][loc.begin:loc.end]], [pair[rank, 0], pair[rank, 1]])
+
+                def gather():
+                    dist.all_gather_into_tensor(pair.view(world * 2, share), pair[rank])
+                    native.copy2d(ctx, pair[:, 0], sharded_outs[0].view(world, share))
+                    native.copy2d(ctx, pair[:, 1], sharded_outs[1].view(world, share))
+
+                def step(do_compute=True, do_gather=True):
+                    if do_compute:
+                        compute(0, plan.local(0, rank), None)
+                    if do_gather:
+                        gather()
+                gathered = 2 * 4 * m * (world - 1) // world
+            else:
+                def compute(band, loc, out_block):
+                    views = [t[loc.begin:loc.end] if k in ROW_INPUTS[name] else t
+                             for k, t in enumerate(shard_in)]
+                    call(views, [out_block])
+
+                def step(do_compute=True, do_gather=True):
+                    if do_compute:
+                        launcher.run_rows_pipelined(compute, sharded_outs[0], plan, do_gather)
+                    else:
+                        pending = [launcher.gather_band(sharded_outs[0], plan, b, async_op=True)
+                                   for b in range(plan.bands)]
+                        for work in pending:
+                            work.wait()
+                out = sharded_outs[0]
+                gathered = out.numel() * out.element_size() * (world - 1) // world
+            units = 1.0
+            collective = (f"ncclAllGather (torch all_gather_into_tensor, in place), "
+                          f"{plan.bands} row band(s), each queued behind its kernel")
+        else:  # "cols": N of the dequant GEMM
+            a, w, sc = ins
+            n = w.shape[1]
+            span = partition(n, world, rank, align=16)
+            if n % (16 * world):
+                raise SystemExit("column shards must be equal multiples of 16")
+            w_s = w[:, span.begin:span.end]
+            sc_s = sc[span.begin:span.end].contiguous()
+            out_s = torch.empty(a.shape[0], span.size, device=dev, dtype=torch.bfloat16)
+            staging = torch.empty(world, a.shape[0], span.size, device=dev, dtype=torch.bfloat16)
+            sharded_outs = [torch.empty_like(full_outs[0])]
+
+            def step(do_compute=True, do_gather=True):
+                if do_compute:
+                    call([a, w_s, sc_s], [out_s])
+                if do_gather:
+                    launcher.gather_cols_even(out_s, staging, sharded_outs[0],
+                                              lambda src, dst: native.copy2d(ctx, src, dst))
+            units = 1.0
+            gathered = out_s.numel() * 2 * (world - 1)
+            collective = ("ncclAllGather of [M, N/g] column blocks into [g, M, N/g], then g "
+                          "strided copies (hc_copy2d) into [M, N]")
+
         torch.cuda.synchronize(dev)
-        ms, launches = timed(fn, steps, warmup)
-        ach, roof = roofline(name, ms / steps)
+        if regions:
+            per_step, launches = timed_regions(step, steps, warmup)
+        else:
+            ms, launches = timed(step, steps, warmup)
+            per_step = [ms / steps]
+        ms_per_step = statistics.median(per_step)
+        value, roof = roofline(name, ms_per_step, units)
+        if mode == "replicas":
+            roof = roofline(name, ms_per_step)[1]  # the kernel on one GPU
+        result = {"ms_per_step": ms_per_step, "steps": steps, "launches": launches,
+                  "regions": {"count": len(per_step), "min_ms_per_step": min(per_step),
+                              "median_ms_per_step": ms_per_step},
+                  "data": data}
+        if mode in ("rows", "cols"):
+            # Phases, each timed alone: the kernels of the shard, the collective, and
+            # (above) the step that overlaps them; and the whole problem on one GPU.
+            k_ms, _ = timed(lambda: step(True, False), steps, 2)
+            g_ms, _ = timed(lambda: step(False, True), steps, 2)
+            one_ms, _ = timed(single, max(3, steps // 2), 2)
+            k_ms, g_ms, one_ms = k_ms / steps, g_ms / steps, one_ms / max(3, steps // 2)
+            phases = {"kernel_ms": k_ms, "gather_ms": g_ms, "total_ms": ms_per_step,
+                      "single_gpu_ms": one_ms, "kernel_speedup": one_ms / k_ms,
+                      "total_speedup": one_ms / ms_per_step,
+                      "gather_bytes_in_per_rank": gathered,
+                      "gather_gbs_in_per_rank": gathered / g_ms / 1e6,
+                      "nvlink_peak_gbs_per_direction": 900, "collective": collective}
+            # The roofline is the kernel's: this GPU's share of the problem in the
+            # time its kernels take when nothing else runs.
+            roof = roofline(name, k_ms, 1.0 / world)[1]
+            roof["of"] = "the kernel phase of one GPU (its 1/%d share of the problem)" % world
+            # Sharded == single GPU, bit for bit, on every rank.
+            step()
+            single()
+            barrier()
+            for a_t, b_t in zip(sharded_outs, full_outs):
+                if not torch.equal(a_t, b_t):
+                    raise AssertionError(f"{name}: rank {rank}: gathered output differs from the "
+                                         f"single-GPU output")
+            parity_note = "gathered == single-GPU output bit for bit on every rank"
+            outs_to_check = sharded_outs
+        else:
+            single()
+            barrier()
+            outs_to_check = full_outs
+        parity = verify(name, host, outs_to_check)
+        if parity and parity_note:
+            parity["sharded"] = parity_note
         # Spread of single steps, each between its own pair of events (after the
-        # timed region, so the figures above are untouched).
+        # timed regions, so the figures above are untouched).
         events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                   for _ in range(min(steps, 50))]
-        for e0, e1 in events:
-            e0.record(stream)
-            fn()
-            e1.record(stream)
-        stream.synchronize()
+        with torch.cuda.stream(stream):
+            for e0, e1 in events:
+                e0.record(stream)
+                step()
+                e1.record(stream)
+            stream.synchronize()
         each = sorted(e0.elapsed_time(e1) for e0, e1 in events)
-        roof["step_ms"] = {"min": each[0], "median": statistics.median(each),
-                           "steps": len(each)}
-        return {"ms_per_step": ms / steps, "steps": steps, "launches": launches,
-                "status": ctx.kernel_status(), "value": ach * world, "unit": roof["unit"],
-                "roofline": roof}
+        roof["step_ms"] = {"min": each[0], "median": statistics.median(each), "steps": len(each)}
+        result.update({"status": ctx.kernel_status(), "value": value, "unit": roof["unit"],
+                       "roofline": roof, "sharding": mode})
+        if phases:
+            result["phases"] = phases
+        if parity:
+            result["parity"] = parity
+        return result
 
     def measure_e2e(name, steps, warmup):
-        """Host buffers in, host buffers out, through the public call surface."""
-        ins, outs = device_inputs(name)
+        """Host buffers in, host buffers out, through the public call surface; with
+        several ranks every rank streams its own rows of the problem."""
+        _, ins, _ = baseline_inputs(name)
+        outs = output_like(name, ins)
+        share = 1.0
+        if sharded and SHARDING[name] == "rows":
+            m = outs[0].shape[0]
+            span = partition(m, world, rank)
+            ins = [t[span.begin:span.end] if k in ROW_INPUTS[name] else t
+                   for k, t in enumerate(ins)]
+            outs = [t[span.begin:span.end] for t in outs]
+        else:
+            share = float(world) if world > 1 else 1.0
         h_ins = [t.cpu().pin_memory() for t in ins]
-        h_outs = [torch.empty_like(t, device="cpu").pin_memory() for t in outs]
+        h_outs = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
 
         if name in ("softmax", "reduce", "gemm_bf16", "map", "rows"):
             # Row-wise workloads (and the rows of A in a GEMM) have a host-buffer
@@ -587,37 +871,41 @@ def run_gpu(args):
             del ins, outs  # the pipeline brings its own device slots
 
             def step():
-                with torch.cuda.stream(stream):
-                    if name == "softmax":
-                        hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
-                    elif name == "reduce":
-                        hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
-                    elif name == "map":
-                        hc_host.rows_body_host(map_kernel(), h_ins, h_outs[0], desc, group_rows=None)
-                    elif name == "rows":
-                        hc_host.rows_body_host(rows_kernel(), h_ins, h_outs[0], desc)
-                    else:
-                        hc_host.gemm_host(h_ins[0], h_ins[1], h_outs[0], desc)
+                if name == "softmax":
+                    hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
+                elif name == "reduce":
+                    hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
+                elif name == "map":
+                    hc_host.rows_body_host(map_kernel(), h_ins, h_outs[0], desc, group_rows=None)
+                elif name == "rows":
+                    hc_host.rows_body_host(rows_kernel(), h_ins, h_outs[0], desc)
+                else:
+                    hc_host.gemm_host(h_ins[0], h_ins[1], h_outs[0], desc)
         else:
             call = public_call(name, ins, outs)
 
             def step():
-                with torch.cuda.stream(stream):
-                    for d, h in zip(ins, h_ins):
-                        d.copy_(h, non_blocking=True)
-                    call()
-                    for h, d in zip(h_outs, outs):
-                        h.copy_(d, non_blocking=True)
+                for d, h in zip(ins, h_ins):
+                    d.copy_(h, non_blocking=True)
+                call()
+                for h, d in zip(h_outs, outs):
+                    h.copy_(d, non_blocking=True)
 
         ms, _ = timed(step, steps, warmup)
         if name == "softmax":  # the result really came back
             sums = h_outs[0][:64].sum(dim=1)
             assert torch.allclose(sums, torch.ones_like(sums), atol=1e-4), "softmax rows != 1"
-        ach, roof = roofline(name, ms / steps)
-        return {"value": ach * world, "unit": roof["unit"],
-                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in h_ins),
-                "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in h_outs),
-                "ms_per_step": ms / steps, "steps": steps}
+        ach, roof = roofline(name, ms / steps, share)
+        up = sum(t.numel() * t.element_size() for t in h_ins)
+        down = sum(t.numel() * t.element_size() for t in h_outs)
+        if world > 1:
+            t = torch.tensor([up, down], dtype=torch.float64, device=dev)
+            dist.all_reduce(t)
+            up, down = int(t[0].item()), int(t[1].item())
+        return {"value": ach, "unit": roof["unit"], "h2d_bytes_per_step": up,
+                "d2h_bytes_per_step": down, "ms_per_step": ms / steps, "steps": steps,
+                "what": "every rank streams its rows from pinned host memory and back"
+                if world > 1 else "pinned host memory in, pinned host memory out"}
 
     name = args.workload
     sampler = ClockSampler(local)
@@ -626,8 +914,11 @@ def run_gpu(args):
         e2e = measure_e2e(name, max(3, min(args.steps, 20)), 3)
         extras = {}
         if name == "softmax" and not args.no_extras:
-            for other, steps in (("reduce", 200), ("gemm_bf16", 50), ("gemm_w8a16", 50),
-                                 ("gemm_f32", 500), ("conv", 50), ("map", 200), ("rows", 200)):
+            others = [("reduce", 100), ("gemm_bf16", 50), ("gemm_w8a16", 50), ("gemm_f32", 500)]
+            if not sharded:
+                others += [("conv", 50)]
+            others += [("map", 100), ("rows", 100)]
+            for other, steps in others:
                 # Each kernel is timed alone: let the board's power state settle
                 # after the previous one (a dense GEMM runs into the 1 kW cap and
                 # would hand lower clocks to whatever is measured right after it).
@@ -635,29 +926,49 @@ def run_gpu(args):
                 extras[other] = measure(other, steps, 5)
 
     if rank == 0:
+        mode = SHARDING[name] if sharded else ("replicas" if world > 1 else "single GPU")
         line = {
             "metric": METRIC[name], "value": head["value"], "unit": head["unit"], "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": DTYPE[name], "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if sharded else "weak",
+            "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic: " + head["data"],
             "config": {"workload": describe(name),
-                       "sharding": "independent shards, no collective in the timed path",
+                       "sharding": {"rows": "rows of the fixed full-size problem split over the "
+                                            "ranks in row bands; the output all-gather (NCCL) is "
+                                            "inside the timed step",
+                                    "cols": "output columns split over the ranks, all-gather inside "
+                                            "the timed step",
+                                    "replicas": "independent replicas, no collective",
+                                    "single GPU": "one GPU"}[mode],
                        "l2": {"gemm_f32": "operands fit in L2 (latency-bound case)",
                               "conv": "operands (50 MB) fit in L2; the kernel is bound by the "
                                       "CUDA cores, not by memory"}.get(
                                   name, "inputs and outputs larger than L2 (no flush needed)")},
             "roofline": head["roofline"], "gpu_launches": head["launches"],
-            "kernel_status": head["status"], "clocks": sampler.summary(), "e2e": e2e,
+            "kernel_status": head["status"], "regions": head["regions"],
+            "clocks": sampler.summary(), "e2e": e2e,
         }
+        for key in ("phases", "parity"):
+            if key in head:
+                line[key] = head[key]
         if args.small:
             line["config"]["small"] = "reduced shape for profiling; not a benchmark result"
         if extras:
-            line["workloads"] = extras
+            # Short figures first (they survive a truncated record), details after.
+            line["summary"] = {k: {"value": round(v["value"], 1), "unit": v["unit"],
+                                   "frac": round(v["roofline"]["frac"], 3),
+                                   "ms": round(v["ms_per_step"], 4),
+                                   **({"kernel_speedup": round(v["phases"]["kernel_speedup"], 2),
+                                       "total_speedup": round(v["phases"]["total_speedup"], 2)}
+                                      if "phases" in v else {})}
+                               for k, v in extras.items()}
         if world == 1 and not args.no_cpu_baseline:
             value, dt, what = cpu_sample(name, 1, 3)
             line["cpu_baseline"] = {"value": value, "unit": unit_of(name), "cores": 1,
                                     "kind": "port",
                                     "sample": f"{what}; NumPy oracle, single thread, 3 passes"}
+        if extras:
+            line["workloads"] = extras
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -673,6 +984,11 @@ def main():
     ap.add_argument("--workload", default="softmax", choices=sorted(SHAPES))
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--replicas", action="store_true",
+                    help="with several GPUs: every rank runs the whole problem on its own "
+                         "(weak scaling, no collective) instead of sharding the fixed problem")
+    ap.add_argument("--bands", type=int, default=0,
+                    help="row bands of the sharded run (0: the workload's default)")
     ap.add_argument("--small", action="store_true",
                     help="reduced shapes, for profiler captures; not a benchmark result")
     args = ap.parse_args()

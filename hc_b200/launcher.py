@@ -56,6 +56,52 @@ def partition(n: int, world: int, rank: int, align: int = 1) -> Span:
     return Span(min(n, begin_block * align), min(n, end_block * align))
 
 
+class BandPlan:
+    """Block-cyclic partition of ``m`` rows: the rows are cut into ``bands``
+    consecutive bands and every band is split over the ranks, so a rank owns
+    one block of rows per band.
+
+    With one band this is the plain contiguous partition.  With several, the
+    all-gather of band ``b`` (whose blocks, in rank order, are exactly the rows
+    of the band, so it lands in place in the full output) can run on the
+    communication stream while the kernel computes band ``b + 1``: the output
+    all-gather, which moves far more bytes than a shard's kernel takes time for,
+    hides behind the computation instead of following it."""
+
+    def __init__(self, m: int, world: int, bands: int = 1, align: int = 1):
+        if bands <= 0:
+            raise ValueError("bands must be positive")
+        self.m, self.world, self.bands = m, world, bands
+        self.band_spans = [partition(m, bands, b, align) for b in range(bands)]
+        self.blocks = []  # [band][rank] -> Span of absolute rows
+        for band in self.band_spans:
+            inner = [partition(band.size, world, r, align) for r in range(world)]
+            self.blocks.append([Span(band.begin + s.begin, band.begin + s.end) for s in inner])
+
+    def block(self, band: int, rank: int) -> Span:
+        """Absolute rows of ``rank``'s block in ``band``."""
+        return self.blocks[band][rank]
+
+    def local(self, band: int, rank: int) -> Span:
+        """The same block as rows of the rank's compact shard (its blocks of all
+        bands, in band order)."""
+        begin = sum(self.blocks[b][rank].size for b in range(band))
+        return Span(begin, begin + self.blocks[band][rank].size)
+
+    def shard_rows(self, rank: int) -> int:
+        return sum(self.blocks[b][rank].size for b in range(self.bands))
+
+    def even(self, band: int) -> bool:
+        return len({s.size for s in self.blocks[band]}) == 1
+
+    def take_shard(self, full, rank: int):
+        """Rank ``rank``'s compact shard of a tensor whose first dimension is the
+        row dimension (a copy unless there is one band)."""
+        parts = [full[self.blocks[b][rank].begin:self.blocks[b][rank].end]
+                 for b in range(self.bands)]
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+
+
 def init_process_group(backend: str | None = None):
     """Join the job described by the torchrun environment; returns
     ``(rank, world, local_rank)``.  With no ``WORLD_SIZE`` in the environment
@@ -155,6 +201,73 @@ class ShardedLauncher:
         dist.all_gather(parts, padded, group=self.group)
         for s, part in zip(spans, parts):
             full[s.begin : s.end] = part[: s.size]
+        return full
+
+    def gather_band(self, full, plan: BandPlan, band: int, async_op: bool = False):
+        """All-gather one band of ``full`` in place: this rank's block of the band
+        is already written at its rows of ``full``; afterwards every rank holds
+        the whole band.  Even blocks take one ``all_gather_into_tensor`` whose
+        input is the rank's own slice of the output (NCCL's in-place form, no
+        staging copy) and, with ``async_op``, return the work handle to wait on;
+        ragged bands are gathered padded, synchronously."""
+        if self.world == 1:
+            return None
+        span = plan.band_spans[band]
+        mine = plan.block(band, self.rank)
+        if plan.even(band) and full.is_contiguous():
+            return dist.all_gather_into_tensor(full[span.begin:span.end],
+                                               full[mine.begin:mine.end], group=self.group,
+                                               async_op=async_op)
+        widest = max(s.size for s in plan.blocks[band])
+        padded = full.new_zeros((widest,) + tuple(full.shape[1:]))
+        padded[: mine.size] = full[mine.begin:mine.end]
+        parts = [torch.empty_like(padded) for _ in range(self.world)]
+        dist.all_gather(parts, padded, group=self.group)
+        for s, part in zip(plan.blocks[band], parts):
+            full[s.begin:s.end] = part[: s.size]
+        return None
+
+    def run_rows_pipelined(self, compute, full, plan: BandPlan, gather: bool = True):
+        """The sharded step of a row-partitioned workload: for every band,
+        ``compute(band, local_span, out_block)`` runs this rank's kernel on its
+        block (``local_span``: rows of the compact input shard; ``out_block``: the
+        block's rows of ``full``, written in place) and the band's all-gather is
+        queued behind it without waiting, so it overlaps the next band's
+        kernel.  Returns when everything is queued and the current stream has
+        been made to wait for the gathers."""
+        pending = []
+        for band in range(plan.bands):
+            mine = plan.block(band, self.rank)
+            if mine.size:
+                compute(band, plan.local(band, self.rank), full[mine.begin:mine.end])
+            if gather:
+                work = self.gather_band(full, plan, band, async_op=True)
+                if work is not None:
+                    pending.append(work)
+        for work in pending:
+            work.wait()
+        return full
+
+    def gather_cols_even(self, shard, staging, full, place=None):
+        """All-gather equal column shards without allocating: ``shard`` [M, n]
+        is gathered into ``staging`` [world, M, n] (one ``all_gather_into_tensor``)
+        and block r is then placed into columns ``[r*n, (r+1)*n)`` of ``full``
+        by ``place(src_block, dst_view)`` (default: a strided tensor copy)."""
+        if self.world == 1:
+            if full.data_ptr() != shard.data_ptr():
+                full.copy_(shard)
+            return full
+        n = shard.shape[1]
+        if tuple(staging.shape) != (self.world,) + tuple(shard.shape) or \
+                full.shape[1] != n * self.world:
+            raise ValueError("gather_cols_even: staging must be [world, M, n] and full [M, world*n]")
+        dist.all_gather_into_tensor(staging.view(-1, n), shard, group=self.group)
+        for r in range(self.world):
+            dst = full[:, r * n:(r + 1) * n]
+            if place is None:
+                dst.copy_(staging[r])
+            else:
+                place(staging[r], dst)
         return full
 
     def gather_cols(self, shard, full):

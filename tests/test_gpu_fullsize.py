@@ -15,6 +15,8 @@ seeded inputs, and (b) through properties that do not depend on size:
   multi-GPU launcher's sharded output equal to the single-GPU output.
 """
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -47,11 +49,16 @@ def test_config2_softmax_32768x4096(hc):
     assert torch.all((sums - 1).abs() < 1e-5)
     assert float(d_y.min()) >= 0.0 and float(d_y.max()) <= 1.0
     assert torch.equal(d_y.argmax(dim=1), d_x.argmax(dim=1))
-    rows = np.r_[0:64, 16000:16064, m - 64:m]
-    expect = np.zeros((len(rows), n), np.float32)
-    oracle.softmax_rows(x[rows], expect, 32)
-    got = d_y[torch.from_numpy(rows).cuda()].cpu().numpy()
-    assert np.all(np.abs(got - expect) <= 1e-6 + 1e-5 * np.abs(expect))
+    # Every one of the 32768 rows against the oracle (groups of 256 rows spread
+    # over the host threads; the tiling is the oracle's own).
+    expect = np.empty((m, n), np.float32)
+    oracle.run_row_groups_parallel(
+        lambda r0, r1: oracle.softmax_rows(x[r0:r1], expect[r0:r1], 256), m, 256,
+        len(os.sched_getaffinity(0)))
+    got = d_y.cpu().numpy()
+    for r0 in range(0, m, 4096):  # in blocks, to keep the temporaries small
+        e, g = expect[r0:r0 + 4096], got[r0:r0 + 4096]
+        assert np.all(np.abs(g - e) <= 1e-6 + 1e-5 * np.abs(e))
 
 
 def test_config3_row_sum_and_max_65536x8192(hc):
@@ -63,10 +70,18 @@ def test_config3_row_sum_and_max_65536x8192(hc):
     finish(hc)
     got_s, got_m = d_s.cpu().numpy(), d_m.cpu().numpy()
     assert np.array_equal(got_m, x.max(axis=1))  # bit-exact on every row
-    rows = np.r_[0:256, 40000:40256, m - 256:m]
-    exact = x[rows].astype(np.float64).sum(axis=1)
+    # Every one of the 65536 row sums against the float64 sum of the row.
+    for r0 in range(0, m, 4096):
+        block = x[r0:r0 + 4096].astype(np.float64)
+        exact, bound = block.sum(axis=1), 1e-5 * np.abs(block).sum(axis=1)
+        assert np.all(np.abs(got_s[r0:r0 + 4096] - exact) <= bound)
+    # And the oracle's own sums (float32, NumPy's pairwise order) within the same bound.
+    rows = np.r_[0:1024, 40000:41024, m - 1024:m]
+    so, mo = np.zeros(len(rows), np.float32), np.zeros(len(rows), np.float32)
+    oracle.reduce_rows(x[rows], so, mo, 256)
     bound = 1e-5 * np.abs(x[rows]).astype(np.float64).sum(axis=1)
-    assert np.all(np.abs(got_s[rows] - exact) <= bound)
+    assert np.all(np.abs(got_s[rows].astype(np.float64) - so) <= 2 * bound)
+    assert np.array_equal(got_m[rows], mo)
     d_x.mul_(2.0)
     d_s2 = empty_like_dev((m,), torch.float32)
     hc.reduce_rows(d_x.data_ptr(), d_s2.data_ptr(), 0, m, n, n)
@@ -85,8 +100,11 @@ def test_config4_bf16_gemm_8192(hc):
     d_c = empty_like_dev((m, n), torch.bfloat16)
     hc.gemm_bf16(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), m, n, k, k, n, n)
     finish(hc)
-    rows = np.r_[0:32, 4000:4032, m - 32:m]
-    expect = oracle.round_to_bf16(a[rows] @ b)  # the oracle's full-K GEMM on these rows
+    # 1280 rows (five whole 256-row groups spread over the matrix, so every row
+    # position inside a tile is covered) against the oracle's full-K GEMM.
+    rows = np.r_[0:256, 1792:2048, 4000:4256, 6100:6356, m - 256:m]
+    expect = np.zeros((len(rows), n), np.float32)
+    oracle.gemm_bf16(a[rows], b, expect, (256, 256))
     got = host_bf16(d_c[torch.from_numpy(rows).cuda()])
     assert _bf16_close(got, expect, np.abs(a[rows]) @ np.abs(b))
 
@@ -115,8 +133,10 @@ def test_config5_w8a16_4096x8192x8192(hc):
     hc.gemm_w8a16(d_a.data_ptr(), d_w.data_ptr(), d_s.data_ptr(), d_c.data_ptr(), ws.data_ptr(),
                   ws_bytes, m, n, k, k, n, n)
     finish(hc)
-    rows = np.r_[0:16, 2000:2016, m - 16:m]
-    expect = oracle.round_to_bf16((a[rows] @ w.astype(np.float32)) * s)
+    # 768 rows (three whole 256-row groups) against the oracle.
+    rows = np.r_[0:256, 2000:2256, m - 256:m]
+    expect = np.zeros((len(rows), n), np.float32)
+    oracle.gemm_w8a16(a[rows], w, s, expect, (256, 256))
     got = host_bf16(d_c[torch.from_numpy(rows).cuda()])
     assert _bf16_close(got, expect, np.abs(a[rows]) @ (np.abs(w.astype(np.float32)) * s))
 

@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from hc_b200.launcher import ShardedLauncher, Span, partition
+from hc_b200.launcher import BandPlan, ShardedLauncher, Span, partition
 from oracle import workloads as oracle
 
 
@@ -36,6 +36,29 @@ def test_partition_properties():
         partition(10, 0, 0)
     with pytest.raises(ValueError):
         partition(10, 2, 2)
+
+
+def test_band_plan_covers_every_row_once():
+    for m in (0, 5, 64, 37, 32768):
+        for world in (1, 2, 8):
+            for bands in (1, 2, 8):
+                plan = BandPlan(m, world, bands)
+                seen = np.zeros(m, int)
+                for r in range(world):
+                    at = 0
+                    for b in range(bands):
+                        blk, loc = plan.block(b, r), plan.local(b, r)
+                        seen[blk.begin:blk.end] += 1
+                        assert (loc.begin, loc.size) == (at, blk.size)
+                        at += blk.size
+                    assert plan.shard_rows(r) == at
+                assert np.all(seen == 1)
+                # Blocks of a band are consecutive in rank order: gathered in that
+                # order they are the band itself.
+                for b in range(bands):
+                    assert plan.blocks[b][0].begin == plan.band_spans[b].begin
+                    assert plan.blocks[b][-1].end == plan.band_spans[b].end
+    assert BandPlan(32768, 8, 8).block(3, 5) == Span(3 * 4096 + 5 * 512, 3 * 4096 + 6 * 512)
 
 
 def _oracle_kernels():
@@ -146,6 +169,37 @@ def _worker(rank, world, port, rows, results):
         L.rows_body(double_body, [xs], ys, None)
         L.gather_rows(ys, full)
         ok["map_body"] = np.array_equal(full.numpy(), x * 2)
+
+        # Row bands: every band is computed in place in the full output and
+        # gathered behind its kernel; ragged bands take the padded path.
+        for bands in (1, 2, 4):
+            plan = BandPlan(rows, world, bands)
+            (x,) = oracle.make_inputs("softmax", shape=(rows, 96))
+            shard = plan.take_shard(torch.from_numpy(x), rank).contiguous()
+            assert shard.shape[0] == plan.shard_rows(rank)
+            full = torch.full((rows, 96), float("nan"))
+
+            def compute(band, loc, out_block, shard=shard):
+                L.softmax(shard[loc.begin:loc.end], out_block, 8)
+
+            L.run_rows_pipelined(compute, full, plan)
+            expect = np.zeros_like(x)
+            oracle.softmax_rows(x, expect, 8)
+            ok[f"bands{bands}"] = np.array_equal(full.numpy(), expect)
+
+        if True:
+            n = 64  # equal column shards of 32
+            a, w, s = oracle.make_inputs("gemm_w8a16", shape=(24, n, 32))
+            cs = L.cols(n)
+            o_s = torch.empty(24, cs.size)
+            L.dequant_gemm_cols(torch.from_numpy(a), torch.from_numpy(w)[:, cs.begin:cs.end],
+                                torch.from_numpy(s[cs.begin:cs.end].copy()), o_s, (8, 16))
+            staging = torch.empty(world, 24, cs.size)
+            o_full = torch.empty(24, n)
+            L.gather_cols_even(o_s, staging, o_full)
+            expect = np.zeros((24, n), np.float32)
+            oracle.gemm_w8a16(a, w, s, expect, (8, 16))
+            ok["cols_even"] = np.array_equal(o_full.numpy(), expect)
         results[rank] = ok
     finally:
         dist.destroy_process_group()
