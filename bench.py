@@ -156,24 +156,21 @@ def describe(name):
 
 
 # dram bytes per launch from the ncu captures summarised under profiles/ (None
-# where no capture scales to the full-size launch).
+# where there is no capture of the full-size launch).  The streaming bodies were
+# captured at full size, one launch each (profiles/dram_traffic_full_size_streaming_bodies.md);
+# the part of the output still in L2 when the kernel ends is not in the figure.
 NCU_TRAFFIC = {
-    # profiles/softmax_rows_f32_w32_8192x4096.md: (134.25 + 77.85) MB for a quarter of
-    # the rows, scaled by 4 (the part of Y still in L2 at kernel end is not counted).
-    "softmax": 848.4e6,
-    # profiles/reduce_rows_warp_f32_16384x8192.md: (536.89 + 3.88) MB for a quarter of the rows.
+    "softmax": 536906496 + 481441280,
+    # profiles/reduce_rows_warp_f32_16384x8192.md: (536.89 + 3.88) MB for a quarter of the
+    # rows; the read traffic grows with the rows, so four times that.
     "reduce": 2163.1e6,
     # profiles/gemm_bf16_umma_pair_2048.md, full-size section: 1418.1 MB read + 128.5 MB written.
     "gemm_bf16": 1546.6e6,
     "gemm_w8a16": None,
     "gemm_f32": None,
     "conv": None,
-    # profiles/map_elements_f32_v4_n2_8192x4096.md: (268.49 + 97.94) MB for a quarter of the
-    # rows, scaled by 4 (the part of the output still in L2 at kernel end is not counted).
-    "map": 1465.7e6,
-    # profiles/row_program_f32_log_softmax_8192x4096.md (held rows): (134.33 + 84.75) MB for a
-    # quarter of the rows, scaled by 4 (written rows still in L2 at kernel end not counted).
-    "rows": 876.3e6,
+    "map": 1073761280 + 495959040,
+    "rows": 536891392 + 481583104,
 }
 
 
@@ -392,7 +389,9 @@ SHARDING = {"softmax": "rows", "rows": "rows", "map": "rows", "reduce": "rows",
 
 # Row bands per workload at N > 1 (launcher.BandPlan): the all-gather of band b
 # overlaps the kernel of band b + 1.
-DEFAULT_BANDS = {"softmax": 8, "rows": 8, "map": 8, "reduce": 1, "gemm_bf16": 2}
+# The HBM-bound bodies take 8 / N bands: their shard's kernel is short against the
+# gather, so more bands only add launches.
+DEFAULT_BANDS = {"softmax": 0, "rows": 0, "map": 0, "reduce": 1, "gemm_bf16": 2}
 # Which inputs of a row-sharded workload are split by rows (the others are replicated).
 ROW_INPUTS = {"softmax": (0,), "rows": (0,), "map": (0, 1), "reduce": (0,), "gemm_bf16": (0,)}
 
@@ -500,10 +499,12 @@ def run_gpu(args):
             host = oracle.make_inputs(config, shape=s)
             tensors = [to_device(a, bf) for a, bf in zip(host, kinds)]
         if world > 1:
-            shapes = {"softmax": [s], "rows": [s], "reduce": [s],
-                      "gemm_f32": [(s[0], s[2]), (s[2], s[1])],
-                      "gemm_bf16": [(s[0], s[2]), (s[2], s[1])],
-                      "gemm_w8a16": [(s[0], s[2]), (s[2], s[1]), (s[1],)]}[name]
+            if len(s) == 2:
+                shapes = [s]
+            elif name == "gemm_w8a16":
+                shapes = [(s[0], s[2]), (s[2], s[1]), (s[1],)]
+            else:
+                shapes = [(s[0], s[2]), (s[2], s[1])]
             dtypes = {"gemm_bf16": [torch.bfloat16] * 2,
                       "gemm_w8a16": [torch.bfloat16, torch.int8, torch.float32]}.get(
                           name, [torch.float32] * 2)
@@ -705,7 +706,7 @@ def run_gpu(args):
             units = float(world)  # replicas: every rank does the whole problem
         elif mode == "rows":
             m = full_outs[0].shape[0]
-            want = args.bands or DEFAULT_BANDS[name]
+            want = args.bands or DEFAULT_BANDS[name] or max(1, 8 // world)
             bands = max(1, want)
             while bands > 1 and m % (bands * world):
                 bands //= 2

@@ -33,6 +33,8 @@ KERNEL_SOURCES = [
     "copy2d",
     "map_elements",
     "row_program",
+    "map_fused",
+    "row_fused",
     "softmax_rows",
     "reduce_rows",
     "reduce_all",
@@ -157,7 +159,8 @@ def build_libs(verbose=False, force=False):
     kernels = OUT / "libhc-b200-kernels.so"
     srcs = [CSRC / "launch" / "kernels_api.cpp", INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h",
-            CSRC / "kernels" / "map_params.h", loader, *cubins]
+            CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h", loader,
+            *cubins]
     static_src = CSRC / "launch" / "w8a16_static.cu"
     srcs.append(static_src)
     if force or _stale(kernels, srcs):

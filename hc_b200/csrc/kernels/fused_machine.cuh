@@ -1,0 +1,173 @@
+// The accumulator machine of map_machine.cuh with the program known at compile
+// time: every instruction word is a template constant, so a program becomes
+// straight-line code on registers - no decoding, no operand selection, no
+// copies between the accumulator and the inputs.  The operations are the same,
+// in the same order, each rounded on its own (the *_rn intrinsics are never
+// contracted into fused multiply-adds), so a precompiled program gives bit for
+// bit what the interpreter gives for the same instruction words.
+//
+// A program type P provides `nin`, `n` and `code[n]` (fused_programs.h).
+#pragma once
+
+#include "map_machine.cuh"
+
+namespace hcfused {
+
+template <typename T> struct Arith;
+template <> struct Arith<float> {
+  static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+  static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+  static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+  static __device__ __forceinline__ float div(float a, float b) { return __fdiv_rn(a, b); }
+  static __device__ __forceinline__ float sqrt(float a) { return __fsqrt_rn(a); }
+  static __device__ __forceinline__ float exp(float a) { return expf(a); }
+  static __device__ __forceinline__ float log(float a) { return logf(a); }
+  // NaN if either operand is NaN (NumPy's maximum / minimum), one instruction.
+  static __device__ __forceinline__ float max(float a, float b) {
+    float out;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
+    return out;
+  }
+  static __device__ __forceinline__ float min(float a, float b) {
+    float out;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
+    return out;
+  }
+};
+template <> struct Arith<double> {
+  static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
+  static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
+  static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+  static __device__ __forceinline__ double div(double a, double b) { return __ddiv_rn(a, b); }
+  static __device__ __forceinline__ double sqrt(double a) { return __dsqrt_rn(a); }
+  static __device__ __forceinline__ double exp(double a) { return ::exp(a); }
+  static __device__ __forceinline__ double log(double a) { return ::log(a); }
+  static __device__ __forceinline__ double max(double a, double b) { return hcmap::maxOf(a, b); }
+  static __device__ __forceinline__ double min(double a, double b) { return hcmap::minOf(a, b); }
+};
+
+template <typename T, uint32_t OP> __device__ __forceinline__ T binaryOp(T a, T b) {
+  if constexpr (OP == HC_MAP_LOAD) return b;
+  else if constexpr (OP == HC_MAP_ADD) return Arith<T>::add(a, b);
+  else if constexpr (OP == HC_MAP_SUB) return Arith<T>::sub(a, b);
+  else if constexpr (OP == HC_MAP_RSUB) return Arith<T>::sub(b, a);
+  else if constexpr (OP == HC_MAP_MUL) return Arith<T>::mul(a, b);
+  else if constexpr (OP == HC_MAP_DIV) return Arith<T>::div(a, b);
+  else if constexpr (OP == HC_MAP_RDIV) return Arith<T>::div(b, a);
+  else if constexpr (OP == HC_MAP_MAX) return Arith<T>::max(a, b);
+  else return Arith<T>::min(a, b);
+}
+
+template <typename T, uint32_t OP> __device__ __forceinline__ T unaryOp(T a) {
+  if constexpr (OP == HC_MAP_NEG) return -a;
+  // As the interpreter writes it: -0 becomes +0, a NaN keeps its bits.
+  else if constexpr (OP == HC_MAP_ABS) return a < T(0) ? -a : (a == T(0) ? T(0) : a);
+  else if constexpr (OP == HC_MAP_EXP) return Arith<T>::exp(a);
+  else if constexpr (OP == HC_MAP_SQRT) return Arith<T>::sqrt(a);
+  else return Arith<T>::log(a);
+}
+
+// What a thread holds while it runs a program on W elements.
+template <typename T, int W, int NIN> struct Frame {
+  T x[NIN][W];  // the inputs
+  T t[3][W];    // the temporaries (only those a program saves to become registers)
+  T s[4];       // row scalars
+};
+
+// First instruction at or after `pc` that is not part of a uniform prologue.
+template <typename P> __host__ __device__ constexpr int afterUniform(int pc) {
+  while (pc < P::n && (P::code[pc] & HC_MAP_UNIFORM))
+    ++pc;
+  return pc;
+}
+// Where the pass that starts at `pc` ends: at its reduction instruction, or at
+// the end of the program.
+template <typename P> __host__ __device__ constexpr int passEnd(int pc) {
+  while (pc < P::n && (P::code[pc] & 0xffu) != HC_MAP_RSUM && (P::code[pc] & 0xffu) != HC_MAP_RMAX)
+    ++pc;
+  return pc;
+}
+template <typename P> __host__ __device__ constexpr bool usesIndices() {
+  for (int pc = 0; pc < P::n; ++pc) {
+    const uint32_t op = P::code[pc] & 0xffu, src = P::code[pc] >> 8;
+    if (op <= HC_MAP_MIN && (src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL))
+      return true;
+  }
+  return false;
+}
+
+// Instructions [PC, END) on the W elements of a thread.  `row` / `packet` say
+// where they sit (element i is in packet `packet + (i / V) * STRIDE`, position
+// i % V), for programs that use the element indices.
+template <typename T, int W, int V, int NIN, typename P, int PC, int END, int STRIDE>
+__device__ __forceinline__ void run(const HcMapProgramDev &p, Frame<T, W, NIN> &f, T (&acc)[W],
+                                    long long row, long long packet) {
+  if constexpr (PC < END) {
+    constexpr uint32_t ins = P::code[PC], op = ins & 0xffu, src = ins >> 8;
+    if constexpr (op <= HC_MAP_MIN) {
+      if constexpr (src >= HC_MAP_SRC_SCALAR) {
+        const T one = f.s[src - HC_MAP_SRC_SCALAR];
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i], one);
+      } else if constexpr (src == HC_MAP_SRC_COL) {
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i],
+                                   T((packet + (long long)(i / V) * STRIDE) * V + i % V));
+      } else if constexpr (src == HC_MAP_SRC_ROW) {
+        const T one = T(row);
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i], one);
+      } else if constexpr (src >= HC_MAP_SRC_CONST) {
+        const T one = T(p.consts[src - HC_MAP_SRC_CONST]);
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i], one);
+      } else if constexpr (src >= HC_MAP_SRC_TEMP) {
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
+      } else {
+        static_assert(src < uint32_t(NIN), "the program reads an input the kernel does not load");
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          acc[i] = binaryOp<T, op>(acc[i], f.x[src][i]);
+      }
+    } else if constexpr (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2) {
+#pragma unroll
+      for (int i = 0; i < W; ++i)
+        f.t[op - HC_MAP_SAVE0][i] = acc[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; ++i)
+        acc[i] = unaryOp<T, op>(acc[i]);
+    }
+    run<T, W, V, NIN, P, PC + 1, END, STRIDE>(p, f, acc, row, packet);
+  }
+}
+
+// The uniform prologue that starts at PC: one value per row, from constants
+// and row scalars, ending in `set` instructions that write row scalars.
+template <typename T, typename P, int PC>
+__device__ __forceinline__ void runUniform(const HcMapProgramDev &p, T (&s)[4], T one) {
+  if constexpr (PC < P::n && (P::code[PC < P::n ? PC : 0] & HC_MAP_UNIFORM) != 0) {
+    constexpr uint32_t ins = P::code[PC], op = ins & 0x7fu, src = ins >> 8;
+    if constexpr (op == HC_MAP_SET) {
+      s[src] = one;
+    } else if constexpr (op <= HC_MAP_MIN) {
+      T b;
+      if constexpr (src >= HC_MAP_SRC_SCALAR)
+        b = s[src - HC_MAP_SRC_SCALAR];
+      else
+        b = T(p.consts[src - HC_MAP_SRC_CONST]);
+      one = binaryOp<T, op>(one, b);
+    } else {
+      one = unaryOp<T, op>(one);
+    }
+    runUniform<T, P, PC + 1>(p, s, one);
+  }
+}
+
+} // namespace hcfused

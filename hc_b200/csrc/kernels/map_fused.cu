@@ -1,0 +1,91 @@
+// Element-wise bodies compiled ahead of time: the bodies listed in
+// fused_programs.h (scale-and-shift, rectifiers, differences, a Horner
+// polynomial ... - tile arithmetic between a load and a store at one origin,
+// python/hckernel/kernel_api.py:136-211) as straight-line kernels.
+//
+// Same launch shape and element order as the interpreting kernel of
+// map_elements.cu; every instruction of the program is a template constant
+// (fused_machine.cuh), so a thread loads its packets, runs the arithmetic and
+// stores, with nothing in between.  Results are bit for bit the interpreter's.
+#include "fused_machine.cuh"
+#include "fused_programs.h"
+
+namespace {
+
+using namespace hcmap;
+using namespace hcfused;
+
+template <typename T, int V, typename P>
+__device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
+  constexpr int NIN = P::nin;
+  // Packets per thread and step, as in map_elements.cu.
+  constexpr int UNROLL = NIN <= 2 ? 4 : 2;
+  constexpr int W = V * UNROLL;
+  const long long perRow = p.cols / V;
+  for (long long r = blockIdx.y; r < p.rows; r += gridDim.y) {
+    const T *rowIn[NIN];
+#pragma unroll
+    for (int k = 0; k < NIN; ++k)
+      rowIn[k] = static_cast<const T *>(p.in[k]) + r * p.inPitch[k];
+    T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
+    const long long first = ((long long)blockIdx.x * UNROLL) * THREADS + threadIdx.x;
+    for (long long base = first; base < perRow;
+         base += (long long)gridDim.x * UNROLL * THREADS) {
+      // Every packet of this step lies inside the row (the same for the whole CTA)?
+      const bool whole = base - threadIdx.x + (long long)UNROLL * THREADS <= perRow;
+      Frame<T, W, NIN> f;
+#pragma unroll
+      for (int k = 0; k < NIN; ++k)
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = base + (long long)u * THREADS;
+          Packet<T, V> packet;
+          if (whole || i < perRow) {
+            packet = loadPacket<T, V>(rowIn[k] + i * V);
+          } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              packet.v[e] = T(0);
+          }
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            f.x[k][u * V + e] = packet.v[e];
+        }
+      T result[W];
+      run<T, W, V, NIN, P, 0, P::n, THREADS>(p, f, result, r, base);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = base + (long long)u * THREADS;
+        if (whole || i < perRow) {
+          Packet<T, V> packet;
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            packet.v[e] = result[u * V + e];
+          storePacket<T, V>(rowOut + i * V, packet);
+        }
+      }
+    }
+  }
+}
+
+} // namespace
+
+#define HC_MAP_FUSED(body)                                                                       \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f32_v4(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<float, 4, hcfused::map_##body>(p);                                                  \
+  }                                                                                              \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f32_v1(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<float, 1, hcfused::map_##body>(p);                                                  \
+  }                                                                                              \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f64_v2(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<double, 2, hcfused::map_##body>(p);                                                 \
+  }                                                                                              \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f64_v1(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<double, 1, hcfused::map_##body>(p);                                                 \
+  }
+
+HC_FUSED_MAP_LIST(HC_MAP_FUSED)

@@ -23,12 +23,13 @@ template <typename T> __device__ __forceinline__ T logOf(T v);
 template <> __device__ __forceinline__ float logOf<float>(float v) { return logf(v); }
 template <> __device__ __forceinline__ double logOf<double>(double v) { return log(v); }
 
-// NumPy's maximum/minimum: NaN if either operand is NaN.
+// NumPy's maximum/minimum: NaN if either operand is NaN, the first operand on
+// a tie (which matters for +0 against -0 only).
 template <typename T> __device__ __forceinline__ T maxOf(T a, T b) {
-  return (a > b || a != a) ? a : b;
+  return (a >= b || a != a) ? a : b;
 }
 template <typename T> __device__ __forceinline__ T minOf(T a, T b) {
-  return (a < b || a != a) ? a : b;
+  return (a <= b || a != a) ? a : b;
 }
 
 template <typename T, int V> struct Packet { T v[V]; };
@@ -52,6 +53,31 @@ __device__ __forceinline__ void storePacket(T *p, const Packet<T, V> &value) {
   else
     __stcs(p, value.v[0]);
 }
+
+// A load that leaves the line in the caches (a later pass of a row program
+// reads the row again), where loadPacket streams.
+template <typename T, int V>
+__device__ __forceinline__ Packet<T, V> loadPacketKept(const T *p) {
+  Packet<T, V> out;
+  if constexpr (V * sizeof(T) == 16)
+    *reinterpret_cast<float4 *>(out.v) = *reinterpret_cast<const float4 *>(p);
+  else
+    out.v[0] = *p;
+  return out;
+}
+
+template <typename T> __device__ __forceinline__ T lowest();
+template <> __device__ __forceinline__ float lowest<float>() { return -INFINITY; }
+template <> __device__ __forceinline__ double lowest<double>() { return -INFINITY; }
+
+// The larger of two values, NaN if either is NaN (what NumPy's max along an
+// axis gives); one instruction for float.
+__device__ __forceinline__ float maxNan(float a, float b) {
+  float out;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
+  return out;
+}
+__device__ __forceinline__ double maxNan(double a, double b) { return maxOf(a, b); }
 
 // The binary operations of the machine on W accumulators; `operand(i)` names
 // the second operand of element i (a register, a uniform value or an

@@ -26,29 +26,6 @@ using namespace hcmap;
 // (four CTAs per SM) gave 3.1: the decode is shared by twice the elements.
 constexpr int UNROLL = 4;
 
-template <typename T, int V>
-__device__ __forceinline__ Packet<T, V> loadPacketKept(const T *p) {
-  Packet<T, V> out;
-  if constexpr (V * sizeof(T) == 16)
-    *reinterpret_cast<float4 *>(out.v) = *reinterpret_cast<const float4 *>(p);
-  else
-    out.v[0] = *p;
-  return out;
-}
-
-template <typename T> __device__ __forceinline__ T lowest();
-template <> __device__ __forceinline__ float lowest<float>() { return -INFINITY; }
-template <> __device__ __forceinline__ double lowest<double>() { return -INFINITY; }
-
-// The larger of two values, NaN if either is NaN (what NumPy's max along an
-// axis gives); one instruction for float.
-__device__ __forceinline__ float maxNan(float a, float b) {
-  float out;
-  asm("max.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
-  return out;
-}
-__device__ __forceinline__ double maxNan(double a, double b) { return maxOf(a, b); }
-
 // Uniform prologue of a pass: expressions of row scalars and constants only
 // (the log of a sum, a mean from a sum ...) are computed once per row here, not
 // once per element in the walk that follows.  Returns the first instruction

@@ -9,6 +9,7 @@
 // entry point that validates its arguments and chooses a kernel variant.
 #include "hc_b200_kernels.h"
 
+#include "../kernels/fused_programs.h"
 #include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
 
@@ -56,6 +57,11 @@ const KernelEntry kKernelTable[] = {
     // hc_row_program_held_{f32_v4,f64_v2}_p{8_t64,8_t96,8_t128,4_t256}_n{1,2} (a CTA
     // holds the row: packets per thread, threads).
     {"hc_row_program_", "row_program"},
+    // hc_row_fused_<body>_{f32_held_t64,f32_held_t128,f32_v4,f32_v1,f64_v2,f64_v1} and
+    // hc_map_fused_<body>_{f32_v4,f32_v1,f64_v2,f64_v1}: the bodies of
+    // fused_programs.h compiled ahead of time.
+    {"hc_row_fused_", "row_fused"},
+    {"hc_map_fused_", "map_fused"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
     {"hc_softmax_rows_f32_w2", "softmax_rows"},
     {"hc_softmax_rows_f32_w4", "softmax_rows"},
@@ -127,6 +133,32 @@ constexpr int kUmmaThreads = 192;
 constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
                                   512 /*barriers*/;
 
+// Programs that exist as precompiled straight-line kernels (fused_programs.h).
+struct FusedProgram {
+  const char *name;
+  int nin, n;
+  const uint32_t *code;
+};
+#define HC_FUSED_ENTRY(body)                                                             \
+  {#body, hcfused::row_##body::nin, hcfused::row_##body::n, hcfused::row_##body::code},
+const FusedProgram kFusedRows[] = {HC_FUSED_ROW_LIST(HC_FUSED_ENTRY)};
+#undef HC_FUSED_ENTRY
+#define HC_FUSED_ENTRY(body)                                                             \
+  {#body, hcfused::map_##body::nin, hcfused::map_##body::n, hcfused::map_##body::code},
+const FusedProgram kFusedMaps[] = {HC_FUSED_MAP_LIST(HC_FUSED_ENTRY)};
+#undef HC_FUSED_ENTRY
+
+// Name of the precompiled body whose instruction words are exactly those of
+// `p` (constants are operands and not compared), or nullptr.
+template <size_t N>
+const char *matchFused(const FusedProgram (&table)[N], const HcMapProgramDev &p) {
+  for (const FusedProgram &f : table)
+    if (f.nin == p.nInputs && f.n == p.nInstr &&
+        std::equal(f.code, f.code + f.n, p.code))
+      return f.name;
+  return nullptr;
+}
+
 // hcRowProgram holds a row in a CTA's registers when the row fills at least
 // this share of the CTA's packet slots.
 constexpr int kRowHeldFillPercent = 90;
@@ -151,6 +183,7 @@ struct HcContextImpl {
   long long reduceVariant = 0;
   long long mappedStack = 0;
   long long rowVariant = 0;
+  long long fusedVariant = 0; // 1: never use the precompiled bodies
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
@@ -387,6 +420,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->mappedStack = value;
     return 0;
   }
+  if (std::strcmp(name, "fused") == 0 && value >= 0 && value <= 1) {
+    c->fusedVariant = value; // 1: interpret every program, precompiled or not
+    return 0;
+  }
   if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 3) {
     c->rowVariant = value; // see hcRowProgram
     return 0;
@@ -585,9 +622,17 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   for (int k = 0; k < p.nInputs; ++k)
     wide = wide && aligned(p.in[k], 16) && (p.rows == 1 || p.inPitch[k] % perPacket == 0);
   const int v = wide ? perPacket : 1;
-  char name[40];
-  std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s", dtype == HC_F32 ? "f32" : "f64",
-                v, std::max(1, p.nInputs), usesIndices ? "i" : "");
+  char name[64];
+  // A body that was compiled ahead of time runs as straight-line code; any
+  // other program is interpreted.
+  const char *fused = c->fusedVariant == 1 ? nullptr : matchFused(kFusedMaps, p);
+  if (fused)
+    std::snprintf(name, sizeof name, "hc_map_fused_%s_%s_v%d", fused,
+                  dtype == HC_F32 ? "f32" : "f64", v);
+  else
+    std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s",
+                  dtype == HC_F32 ? "f32" : "f64", v, std::max(1, p.nInputs),
+                  usesIndices ? "i" : "");
   const long long perRow = p.cols / v;
   // One CTA per 1024 packets of a row (four per thread; 512 and two with three
   // or four inputs - map_elements.cu); rows beyond 65535 and very long rows are
@@ -635,8 +680,10 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
   bool wide = p.cols % perPacket == 0 && aligned(p.out, 16) && p.outPitch % perPacket == 0;
   for (int k = 0; k < p.nInputs; ++k)
     wide = wide && aligned(p.in[k], 16) && p.inPitch[k] % perPacket == 0;
-  char name[48];
+  char name[64];
   void *args[] = {&p};
+  const char *fused =
+      c->fusedVariant == 1 || c->rowVariant >= 2 ? nullptr : matchFused(kFusedRows, p);
   // Rows of 257..1024 packets can be held in the registers of one CTA per row:
   // eight packets per thread on 64, 96 or 128 threads.  That pays when the row
   // fills most of the CTA's slots; otherwise a warp that walks the row is
@@ -657,6 +704,10 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
     // and for doubles (2.2 against 2.4 TB/s) walking is faster throughout.
     const bool filled = dtype == HC_F32 && threads != 96 &&
                         packets * 100 >= (long long)(held * threads) * kRowHeldFillPercent;
+    if (filled && fused) {
+      std::snprintf(name, sizeof name, "hc_row_fused_%s_f32_held_t%d", fused, int(threads));
+      return c->launch(name, size_t(p.rows), 1, 1, threads, args, 1, 0);
+    }
     if (filled || c->rowVariant >= 2) {
       int temps = 0; // the temporaries the program saves to, t0 first
       for (int pc = 0; pc < p.nInstr; ++pc) {
@@ -670,8 +721,12 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
       return c->launch(name, size_t(p.rows), 1, 1, threads, args, 1, smem);
     }
   }
-  std::snprintf(name, sizeof name, "hc_row_program_%s_v%d_n%d", dtype == HC_F32 ? "f32" : "f64",
-                wide ? perPacket : 1, p.nInputs);
+  if (fused)
+    std::snprintf(name, sizeof name, "hc_row_fused_%s_%s_v%d", fused,
+                  dtype == HC_F32 ? "f32" : "f64", wide ? perPacket : 1);
+  else
+    std::snprintf(name, sizeof name, "hc_row_program_%s_v%d_n%d",
+                  dtype == HC_F32 ? "f32" : "f64", wide ? perPacket : 1, p.nInputs);
   // One warp per row, eight rows per CTA.
   return c->launch(name, size_t(ceilDiv(p.rows, 8)), 1, 1, 256, args, 1, 0);
 }
