@@ -863,27 +863,36 @@ def run_gpu(args):
         h_ins = [t.cpu().pin_memory() for t in ins]
         h_outs = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
 
-        if name in ("softmax", "reduce", "gemm_bf16", "map", "rows"):
-            # Row-wise workloads (and the rows of A in a GEMM) have a host-buffer
-            # entry point that streams row chunks through the GPU (upload,
-            # kernel and download overlapped).
-            from hc_b200 import host as hc_host
-
-            del ins, outs  # the pipeline brings its own device slots
+        if name in ("softmax", "reduce", "gemm_bf16"):
+            # The host-buffer entry points of the C-ABI (hcSoftmaxRowsHost,
+            # hcReduceRowsHost, hcGemmBf16Host): row chunks stream through the GPU,
+            # upload, kernel and download overlapped, all in the C++ library.
+            dev_copies = (ins, outs)  # kept for the link-only measurement below
 
             def step():
                 if name == "softmax":
-                    hc_host.softmax_rows_host(h_ins[0], h_outs[0], desc)
+                    native.softmax_rows_host(ctx, h_ins[0], h_outs[0])
                 elif name == "reduce":
-                    hc_host.reduce_rows_host(h_ins[0], h_outs[0], h_outs[1], desc)
-                elif name == "map":
-                    hc_host.rows_body_host(map_kernel(), h_ins, h_outs[0], desc, group_rows=None)
-                elif name == "rows":
-                    hc_host.rows_body_host(rows_kernel(), h_ins, h_outs[0], desc)
+                    native.reduce_rows_host(ctx, h_ins[0], h_outs[0], h_outs[1])
                 else:
-                    hc_host.gemm_host(h_ins[0], h_ins[1], h_outs[0], desc)
+                    native.gemm_bf16_host(ctx, h_ins[0], h_ins[1], h_outs[0])
+            via = "C-ABI host-buffer entry point (libhc-b200-kernels.so)"
+        elif name in ("map", "rows"):
+            # Recorded bodies stream the same way through hc_b200.host (the chunk
+            # pipeline around the @kernel call).
+            from hc_b200 import host as hc_host
+
+            dev_copies = (ins, outs)
+
+            def step():
+                if name == "map":
+                    hc_host.rows_body_host(map_kernel(), h_ins, h_outs[0], desc, group_rows=None)
+                else:
+                    hc_host.rows_body_host(rows_kernel(), h_ins, h_outs[0], desc)
+            via = "hc_b200.host chunk pipeline around the @kernel call"
         else:
             call = public_call(name, ins, outs)
+            dev_copies = (ins, outs)
 
             def step():
                 for d, h in zip(ins, h_ins):
@@ -891,6 +900,7 @@ def run_gpu(args):
                 call()
                 for h, d in zip(h_outs, outs):
                     h.copy_(d, non_blocking=True)
+            via = "copy, @kernel call, copy"
 
         ms, _ = timed(step, steps, warmup)
         if name == "softmax":  # the result really came back
@@ -903,8 +913,24 @@ def run_gpu(args):
             t = torch.tensor([up, down], dtype=torch.float64, device=dev)
             dist.all_reduce(t)
             up, down = int(t[0].item()), int(t[1].item())
+        # What the link alone allows: the same bytes up and down at once on two
+        # streams, nothing computed (every rank at the same time).
+        side = torch.cuda.Stream(dev)
+
+        def link_only():
+            side.wait_stream(torch.cuda.current_stream(dev))
+            for d, h in zip(dev_copies[0], h_ins):
+                d.copy_(h, non_blocking=True)
+            with torch.cuda.stream(side):
+                for h, d in zip(h_outs, dev_copies[1]):
+                    h.copy_(d, non_blocking=True)
+            torch.cuda.current_stream(dev).wait_stream(side)
+
+        link_ms, _ = timed(link_only, max(3, steps // 2), 1)
+        link_ms /= max(3, steps // 2)
         return {"value": ach, "unit": roof["unit"], "h2d_bytes_per_step": up,
                 "d2h_bytes_per_step": down, "ms_per_step": ms / steps, "steps": steps,
+                "via": via, "link_only_ms_per_step": link_ms,
                 "what": "every rank streams its rows from pinned host memory and back"
                 if world > 1 else "pinned host memory in, pinned host memory out"}
 

@@ -157,7 +157,9 @@ def build_libs(verbose=False, force=False):
         _run([cxx, *CXX_FLAGS, *inc, "-o", loader, srcs[0], "-ldl"], verbose)
 
     kernels = OUT / "libhc-b200-kernels.so"
-    srcs = [CSRC / "launch" / "kernels_api.cpp", INCLUDE / "hc_b200_kernels.h",
+    host_src = CSRC / "launch" / "host_api.cpp"
+    srcs = [CSRC / "launch" / "kernels_api.cpp", host_src, CSRC / "launch" / "context.hpp",
+            INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h",
             CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h", loader,
             *cubins]
@@ -172,7 +174,7 @@ def build_libs(verbose=False, force=False):
         static_obj = OUT / "w8a16_static.o"
         _run([cuda / "bin" / "nvcc", *NVCC_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "-cudart", "static", *inc, "-c", "-o", static_obj, static_src], verbose)
-        _run([cxx, *CXX_FLAGS, *inc, "-I", OUT, "-o", kernels, srcs[0], asm, static_obj,
+        _run([cxx, *CXX_FLAGS, *inc, "-I", OUT, "-o", kernels, srcs[0], host_src, asm, static_obj,
               "-L", OUT, "-lhc-gpu-runtime-loader", "-L", cuda / "lib64", "-lcudart_static",
               "-lrt", "-lpthread", "-ldl"], verbose)
 

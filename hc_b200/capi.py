@@ -105,7 +105,7 @@ OLX_PROTOTYPES = {
     "olxDeviceContextEnter": (C.c_int, [_vp]),
     "olxDeviceContextLeave": (C.c_int, [_vp]),
     "olxPointerDevice": (C.c_int, [_vp, _vp, C.POINTER(C.c_int)]),
-    "olxCreateEvent": (_vp, [_vp]),
+    "olxCreateEvent": (_vp, [_vp, C.c_int]),
     "olxReleaseEvent": (None, [_vp, _vp]),
     "olxRecordEvent": (C.c_int, [_vp, _vp]),
     "olxQueueWaitEvent": (C.c_int, [_vp, _vp]),
@@ -162,6 +162,11 @@ KERNELS_PROTOTYPES = {
     "hcGemmW8A16StaticMaxBytes": (_sz, []),
     "hcGemmW8A16Static": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
     "hcReportError": (C.c_int, [_vp, C.c_char_p]),
+    "hcHostPin": (C.c_int, [_vp, _vp, _sz]),
+    "hcHostUnpin": (C.c_int, [_vp, _vp]),
+    "hcSoftmaxRowsHost": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
+    "hcReduceRowsHost": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),
+    "hcGemmBf16Host": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
 }
 # include/hc_python_runtime.h
 PYRUNTIME_PROTOTYPES = {
@@ -357,6 +362,31 @@ class Context:
         self._check(
             self.lib.hcGemmW8A16Static(self.handle, a, w, scale, out, m, n, k, lda, ldw, ldc),
             "hcGemmW8A16Static",
+        )
+
+    def host_pin(self, ptr, nbytes):
+        self._check(self.lib.hcHostPin(self.handle, ptr, nbytes), "hcHostPin")
+
+    def host_unpin(self, ptr):
+        self._check(self.lib.hcHostUnpin(self.handle, ptr), "hcHostUnpin")
+
+    def softmax_rows_host(self, x, y, rows, cols, x_pitch, y_pitch, dtype=HC_F32):
+        """``x``, ``y``: HOST addresses."""
+        self._check(
+            self.lib.hcSoftmaxRowsHost(self.handle, x, y, rows, cols, x_pitch, y_pitch, dtype),
+            "hcSoftmaxRowsHost",
+        )
+
+    def reduce_rows_host(self, x, sum_out, max_out, rows, cols, pitch, dtype=HC_F32):
+        self._check(
+            self.lib.hcReduceRowsHost(self.handle, x, sum_out, max_out, rows, cols, pitch, dtype),
+            "hcReduceRowsHost",
+        )
+
+    def gemm_bf16_host(self, a, b, c, m, n, k, lda, ldb, ldc):
+        self._check(
+            self.lib.hcGemmBf16Host(self.handle, a, b, c, m, n, k, lda, ldb, ldc),
+            "hcGemmBf16Host",
         )
 
     def dequant_w8(self, w, out, rows, cols, w_pitch, out_pitch):

@@ -168,6 +168,80 @@ void reduceRows(Context &ctx, py::handle x, py::object sumOut, py::object maxOut
             "reduce_rows");
 }
 
+// ---- host buffers (hcSoftmaxRowsHost, hcReduceRowsHost, hcGemmBf16Host) ---------------
+// A host array (a NumPy array or a CPU tensor; page-locked memory makes the
+// copies overlap), rows contiguous.
+ArrayArg hostArray(py::handle obj, const char *name, int rank) {
+  ArrayArg a;
+  try {
+    a = hc::arrayFromPython(obj);
+  } catch (const std::exception &e) {
+    throw py::type_error(std::string(name) + ": " + e.what());
+  }
+  if (a.onDevice)
+    throw py::value_error(std::string(name) + ": expected host memory, got a CUDA tensor");
+  if (a.rank() != rank)
+    throw py::value_error(std::string(name) + ": expected rank " + std::to_string(rank) +
+                          ", got " + std::to_string(a.rank()));
+  if (!a.rowMajor())
+    throw py::value_error(std::string(name) + ": rows must be contiguous (last stride 1)");
+  for (auto s : a.strides)
+    if (s < 0)
+      throw py::value_error(std::string(name) + ": negative strides are not supported");
+  return a;
+}
+
+void softmaxRowsHost(Context &ctx, py::handle x, py::handle y) {
+  ArrayArg a = hostArray(x, "x", 2), b = hostArray(y, "out", 2);
+  sameKind(a, b, "x", "out");
+  sameShape(a, b, "x", "out");
+  const int dtype = floatDType(a, "x");
+  int rc;
+  {
+    py::gil_scoped_release release; // the call waits for the GPU
+    rc = hcSoftmaxRowsHost(ctx.get(), a.data, b.data, a.shape[0], a.shape[1], pitch(a), pitch(b),
+                           dtype);
+  }
+  ctx.check(rc, "softmax_rows_host");
+}
+
+void reduceRowsHost(Context &ctx, py::handle x, py::object sumOut, py::object maxOut) {
+  ArrayArg a = hostArray(x, "x", 2);
+  const int dtype = floatDType(a, "x");
+  auto output = [&](py::object &o, const char *name) -> void * {
+    if (o.is_none())
+      return nullptr;
+    ArrayArg r = hostArray(o, name, 1);
+    sameKind(a, r, "x", name);
+    if (r.shape[0] != a.shape[0] || (r.shape[0] > 1 && r.strides[0] != 1))
+      throw py::value_error(std::string(name) + ": expected " + std::to_string(a.shape[0]) +
+                            " contiguous elements");
+    return r.data;
+  };
+  void *sp = output(sumOut, "sum_out"), *mp = output(maxOut, "max_out");
+  int rc;
+  {
+    py::gil_scoped_release release;
+    rc = hcReduceRowsHost(ctx.get(), a.data, sp, mp, a.shape[0], a.shape[1], pitch(a), dtype);
+  }
+  ctx.check(rc, "reduce_rows_host");
+}
+
+void gemmBf16Host(Context &ctx, py::handle a, py::handle b, py::handle out) {
+  ArrayArg A = hostArray(a, "a", 2), B = hostArray(b, "b", 2), O = hostArray(out, "out", 2);
+  if (A.kind != ElemKind::BF16 || B.kind != ElemKind::BF16 || O.kind != ElemKind::BF16)
+    throw py::type_error("gemm_bf16_host: bfloat16 matrices expected");
+  if (A.shape[1] != B.shape[0] || O.shape[0] != A.shape[0] || O.shape[1] != B.shape[1])
+    throw py::value_error("gemm_bf16_host: shapes do not form [M,K] @ [K,N] -> [M,N]");
+  int rc;
+  {
+    py::gil_scoped_release release;
+    rc = hcGemmBf16Host(ctx.get(), A.data, B.data, O.data, A.shape[0], B.shape[1], A.shape[1],
+                        pitch(A), pitch(B), pitch(O));
+  }
+  ctx.check(rc, "gemm_bf16_host");
+}
+
 void reduceAll(Context &ctx, py::handle a, py::handle result) {
   ArrayArg A = deviceArray(ctx, a, "a", 1), R = deviceArray(ctx, result, "result", 1);
   if (A.shape[0] > 1 && A.strides[0] != 1)
@@ -243,7 +317,10 @@ void runProgram(Context &ctx, py::handle inputs, py::handle out, const std::vect
       throw py::value_error("row_program: matrices expected");
     ctx.check(hcRowProgram(ctx.get(), &p, floatDType(O, "out")), "row_program");
   } else {
-    ctx.check(hcMapElements(ctx.get(), &p, floatDType(O, "out")), "map_elements");
+    const int dtype = O.kind == ElemKind::I32   ? HC_I32
+                      : O.kind == ElemKind::I64 ? HC_I64
+                                                : floatDType(O, "out");
+    ctx.check(hcMapElements(ctx.get(), &p, dtype), "map_elements");
   }
 }
 
@@ -426,6 +503,11 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("reduce_rows", &reduceRows, py::arg("ctx"), py::arg("x"),
         py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
   m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
+  m.def("softmax_rows_host", &softmaxRowsHost, py::arg("ctx"), py::arg("x"), py::arg("out"));
+  m.def("reduce_rows_host", &reduceRowsHost, py::arg("ctx"), py::arg("x"),
+        py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
+  m.def("gemm_bf16_host", &gemmBf16Host, py::arg("ctx"), py::arg("a"), py::arg("b"),
+        py::arg("out"));
   m.def("pairwise_distance", &pairwiseDistance, py::arg("ctx"), py::arg("a"), py::arg("b"),
         py::arg("out"));
   m.def("map_elements", &mapElements, py::arg("ctx"), py::arg("inputs"), py::arg("out"),

@@ -22,17 +22,9 @@ template <> struct Arith<float> {
   static __device__ __forceinline__ float sqrt(float a) { return __fsqrt_rn(a); }
   static __device__ __forceinline__ float exp(float a) { return expf(a); }
   static __device__ __forceinline__ float log(float a) { return logf(a); }
-  // NaN if either operand is NaN (NumPy's maximum / minimum), one instruction.
-  static __device__ __forceinline__ float max(float a, float b) {
-    float out;
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
-    return out;
-  }
-  static __device__ __forceinline__ float min(float a, float b) {
-    float out;
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(out) : "f"(a), "f"(b));
-    return out;
-  }
+  // As the interpreter: NaN if either operand is NaN, the first operand on a tie.
+  static __device__ __forceinline__ float max(float a, float b) { return hcmap::maxOf(a, b); }
+  static __device__ __forceinline__ float min(float a, float b) { return hcmap::minOf(a, b); }
 };
 template <> struct Arith<double> {
   static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
@@ -72,7 +64,20 @@ template <typename T, int W, int NIN> struct Frame {
   T x[NIN][W];  // the inputs
   T t[3][W];    // the temporaries (only those a program saves to become registers)
   T s[4];       // row scalars
+  uint32_t ok = ~0u;                   // validity bits of the accumulator's elements
+  uint32_t okT[3] = {~0u, ~0u, ~0u};   // ... and of the parked values
 };
+
+// Clears the validity bit of the elements whose division numpy.ma would mask
+// (map_machine.cuh: Num<T>::divides); MASKED is false for row programs, which do
+// not track validity, and then nothing is generated.
+template <typename T, uint32_t OP, bool MASKED>
+__device__ __forceinline__ void noteDivision(uint32_t &ok, int i, T a, T b) {
+  if constexpr (MASKED && (OP == HC_MAP_DIV || OP == HC_MAP_RDIV)) {
+    if (!(OP == HC_MAP_DIV ? hcmap::Num<T>::divides(a, b) : hcmap::Num<T>::divides(b, a)))
+      ok &= ~(1u << i);
+  }
+}
 
 // First instruction at or after `pc` that is not part of a uniform prologue.
 template <typename P> __host__ __device__ constexpr int afterUniform(int pc) {
@@ -99,52 +104,73 @@ template <typename P> __host__ __device__ constexpr bool usesIndices() {
 // Instructions [PC, END) on the W elements of a thread.  `row` / `packet` say
 // where they sit (element i is in packet `packet + (i / V) * STRIDE`, position
 // i % V), for programs that use the element indices.
-template <typename T, int W, int V, int NIN, typename P, int PC, int END, int STRIDE>
+template <typename T, int W, int V, int NIN, typename P, int PC, int END, int STRIDE,
+          bool MASKED = false>
 __device__ __forceinline__ void run(const HcMapProgramDev &p, Frame<T, W, NIN> &f, T (&acc)[W],
                                     long long row, long long packet) {
   if constexpr (PC < END) {
     constexpr uint32_t ins = P::code[PC], op = ins & 0xffu, src = ins >> 8;
+    static_assert(op < HC_MAP_FLOORDIV, "only the operations up to `set` are compiled ahead");
+    if constexpr (MASKED && op == HC_MAP_LOAD)
+      f.ok = ~0u; // a fresh value (a parked one brings its own bits, below)
     if constexpr (op <= HC_MAP_MIN) {
       if constexpr (src >= HC_MAP_SRC_SCALAR) {
         const T one = f.s[src - HC_MAP_SRC_SCALAR];
 #pragma unroll
-        for (int i = 0; i < W; ++i)
+        for (int i = 0; i < W; ++i) {
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
           acc[i] = binaryOp<T, op>(acc[i], one);
+        }
       } else if constexpr (src == HC_MAP_SRC_COL) {
 #pragma unroll
-        for (int i = 0; i < W; ++i)
-          acc[i] = binaryOp<T, op>(acc[i],
-                                   T((packet + (long long)(i / V) * STRIDE) * V + i % V));
+        for (int i = 0; i < W; ++i) {
+          const T col = T((packet + (long long)(i / V) * STRIDE) * V + i % V);
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], col);
+          acc[i] = binaryOp<T, op>(acc[i], col);
+        }
       } else if constexpr (src == HC_MAP_SRC_ROW) {
         const T one = T(row);
 #pragma unroll
-        for (int i = 0; i < W; ++i)
+        for (int i = 0; i < W; ++i) {
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
           acc[i] = binaryOp<T, op>(acc[i], one);
+        }
       } else if constexpr (src >= HC_MAP_SRC_CONST) {
         const T one = T(p.consts[src - HC_MAP_SRC_CONST]);
 #pragma unroll
-        for (int i = 0; i < W; ++i)
+        for (int i = 0; i < W; ++i) {
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
           acc[i] = binaryOp<T, op>(acc[i], one);
+        }
       } else if constexpr (src >= HC_MAP_SRC_TEMP) {
+        if constexpr (MASKED)
+          f.ok = op == HC_MAP_LOAD ? f.okT[src - HC_MAP_SRC_TEMP]
+                                   : f.ok & f.okT[src - HC_MAP_SRC_TEMP];
 #pragma unroll
-        for (int i = 0; i < W; ++i)
+        for (int i = 0; i < W; ++i) {
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
           acc[i] = binaryOp<T, op>(acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
+        }
       } else {
         static_assert(src < uint32_t(NIN), "the program reads an input the kernel does not load");
 #pragma unroll
-        for (int i = 0; i < W; ++i)
+        for (int i = 0; i < W; ++i) {
+          noteDivision<T, op, MASKED>(f.ok, i, acc[i], f.x[src][i]);
           acc[i] = binaryOp<T, op>(acc[i], f.x[src][i]);
+        }
       }
     } else if constexpr (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2) {
 #pragma unroll
       for (int i = 0; i < W; ++i)
         f.t[op - HC_MAP_SAVE0][i] = acc[i];
+      if constexpr (MASKED)
+        f.okT[op - HC_MAP_SAVE0] = f.ok;
     } else {
 #pragma unroll
       for (int i = 0; i < W; ++i)
         acc[i] = unaryOp<T, op>(acc[i]);
     }
-    run<T, W, V, NIN, P, PC + 1, END, STRIDE>(p, f, acc, row, packet);
+    run<T, W, V, NIN, P, PC + 1, END, STRIDE, MASKED>(p, f, acc, row, packet);
   }
 }
 

@@ -1,6 +1,10 @@
 // Element-wise expression kernel: out[r, c] = f(in0[r, c], ..., in3[r, c]) for
-// rows x cols matrices (row-major, own pitches), f a composition of + - * /,
-// max, min, neg, abs, exp, log, sqrt and constants.
+// rows x cols matrices (row-major, own pitches) of float32, float64, int32 or
+// int64, f a composition of the reference's tile operators (+ - * / // % **,
+// comparisons, & | ^ << >> ~, neg, abs: python/hckernel/kernel_api.py:157-176),
+// max, min, exp, log, sqrt and constants.  Elements that the arithmetic masks -
+// a zero divisor, a power that is not finite - are not stored, like the
+// reference's masked store (kernel_api.py:338-340).
 //
 // This is the GPU form of work-groups that load tiles at one origin, combine
 // them element by element and store the result at the same origin - the shape
@@ -22,7 +26,10 @@ namespace {
 
 using namespace hcmap;
 
-template <typename T, int V, int NIN, bool INDEXED>
+// EXTENDED: the kernel for programs that divide (/ // %), raise to a power,
+// compare, use bitwise operators or work on integers - it tracks which elements
+// stay valid and stores only those.  The basic kernel carries none of that.
+template <typename T, int V, int NIN, bool INDEXED, bool EXTENDED>
 __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
   // Packets per thread and decode: four with one or two inputs (three CTAs per
   // SM), two beyond (the inputs of four packets would not fit the registers).
@@ -64,17 +71,23 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
             x[k][u * V + e] = packet.v[e];
         }
       T result[W];
-      evaluate<T, W, V, NIN, INDEXED, false, THREADS>(p, 0, p.nInstr, x, result, temps, r, base,
-                                                      noScalars);
+      uint32_t ok = ~0u;
+      uint64_t parkedOk = ~0ull;
+      evaluate<T, W, V, NIN, INDEXED, false, THREADS, THREADS, EXTENDED>(
+          p, 0, p.nInstr, x, result, temps, r, base, noScalars, ok, parkedOk);
+      if constexpr (EXTENDED) {
+        storeValid<T, V, UNROLL, THREADS>(rowOut, result, ok, base, perRow, whole);
+      } else {
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const long long i = base + (long long)u * THREADS;
-        if (whole || i < perRow) {
-          Packet<T, V> packet;
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = base + (long long)u * THREADS;
+          if (whole || i < perRow) {
+            Packet<T, V> packet;
 #pragma unroll
-          for (int e = 0; e < V; ++e)
-            packet.v[e] = result[u * V + e];
-          storePacket<T, V>(rowOut + i * V, packet);
+            for (int e = 0; e < V; ++e)
+              packet.v[e] = result[u * V + e];
+            storePacket<T, V>(rowOut + i * V, packet);
+          }
         }
       }
     }
@@ -84,25 +97,37 @@ __device__ __forceinline__ void mapRows(const HcMapProgramDev &p) {
 } // namespace
 
 // One kernel per element type, packet width and number of input arrays (a
-// program without inputs runs on the one-input kernel and loads nothing), and
-// a twin of each (suffix `i`) for programs that use the element indices, so
-// that the streaming kernels do not carry the index bookkeeping.
-#define HC_MAP_KERNEL(tname, T, V, NIN)                                                 \
-  extern "C" __global__ void __launch_bounds__(THREADS, NIN <= 2 ? 3 : 4)                              \
-      hc_map_elements_##tname##_v##V##_n##NIN(const __grid_constant__ HcMapProgramDev p) { \
-    mapRows<T, V, NIN, false>(p);                                                       \
-  }                                                                                     \
-  extern "C" __global__ void __launch_bounds__(THREADS, NIN <= 2 ? 3 : 4)                              \
-      hc_map_elements_##tname##_v##V##_n##NIN##i(const __grid_constant__ HcMapProgramDev p) { \
-    mapRows<T, V, NIN, true>(p);                                                        \
+// program without inputs runs on the one-input kernel and loads nothing), a
+// twin of each (suffix `i`) for programs that use the element indices, so that
+// the streaming kernels do not carry the index bookkeeping, and of each of
+// those the extended form (suffix `x`).  Integer arrays have extended kernels
+// only.
+// (The extended kernels get the registers of two CTAs per SM: the out-of-line
+// operations would otherwise spill around their calls.)
+#define HC_MAP_KERNEL_FORM(tname, T, V, NIN, suffix, INDEXED, EXTENDED)                 \
+  extern "C" __global__ void __launch_bounds__(THREADS, EXTENDED ? 2 : NIN <= 2 ? 3 : 4) \
+      hc_map_elements_##tname##_v##V##_n##NIN##suffix(                                  \
+          const __grid_constant__ HcMapProgramDev p) {                                  \
+    mapRows<T, V, NIN, INDEXED, EXTENDED>(p);                                           \
   }
-#define HC_MAP_KERNELS(tname, T, V)                                                     \
-  HC_MAP_KERNEL(tname, T, V, 1)                                                         \
-  HC_MAP_KERNEL(tname, T, V, 2)                                                         \
-  HC_MAP_KERNEL(tname, T, V, 3)                                                         \
-  HC_MAP_KERNEL(tname, T, V, 4)
+#define HC_MAP_BASIC(tname, T, V, NIN)                                                  \
+  HC_MAP_KERNEL_FORM(tname, T, V, NIN, , false, false)                                  \
+  HC_MAP_KERNEL_FORM(tname, T, V, NIN, i, true, false)
+#define HC_MAP_EXTENDED(tname, T, V, NIN)                                               \
+  HC_MAP_KERNEL_FORM(tname, T, V, NIN, x, false, true)                                  \
+  HC_MAP_KERNEL_FORM(tname, T, V, NIN, ix, true, true)
+#define HC_MAP_EACH_NIN(FORM, tname, T, V)                                              \
+  FORM(tname, T, V, 1) FORM(tname, T, V, 2) FORM(tname, T, V, 3) FORM(tname, T, V, 4)
 
-HC_MAP_KERNELS(f32, float, 4)
-HC_MAP_KERNELS(f32, float, 1)
-HC_MAP_KERNELS(f64, double, 2)
-HC_MAP_KERNELS(f64, double, 1)
+HC_MAP_EACH_NIN(HC_MAP_BASIC, f32, float, 4)
+HC_MAP_EACH_NIN(HC_MAP_BASIC, f32, float, 1)
+HC_MAP_EACH_NIN(HC_MAP_BASIC, f64, double, 2)
+HC_MAP_EACH_NIN(HC_MAP_BASIC, f64, double, 1)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, f32, float, 4)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, f32, float, 1)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, f64, double, 2)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, f64, double, 1)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, i32, int32_t, 4)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, i32, int32_t, 1)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, i64, int64_t, 2)
+HC_MAP_EACH_NIN(HC_MAP_EXTENDED, i64, int64_t, 1)

@@ -52,18 +52,10 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
             f.x[k][u * V + e] = packet.v[e];
         }
       T result[W];
-      run<T, W, V, NIN, P, 0, P::n, THREADS>(p, f, result, r, base);
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const long long i = base + (long long)u * THREADS;
-        if (whole || i < perRow) {
-          Packet<T, V> packet;
-#pragma unroll
-          for (int e = 0; e < V; ++e)
-            packet.v[e] = result[u * V + e];
-          storePacket<T, V>(rowOut + i * V, packet);
-        }
-      }
+      run<T, W, V, NIN, P, 0, P::n, THREADS, true>(p, f, result, r, base);
+      // Elements whose divisor was zero are left unwritten (a program without
+      // divisions keeps all bits set and the test folds away).
+      storeValid<T, V, UNROLL, THREADS>(rowOut, result, f.ok, base, perRow, whole);
     }
   }
 }
@@ -71,7 +63,7 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
 } // namespace
 
 #define HC_MAP_FUSED(body)                                                                       \
-  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f32_v4(            \
+  extern "C" __global__ void __launch_bounds__(THREADS, 3) hc_map_fused_##body##_f32_v4(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     mapFused<float, 4, hcfused::map_##body>(p);                                                  \
   }                                                                                              \

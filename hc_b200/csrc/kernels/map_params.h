@@ -31,8 +31,40 @@ enum HcMapOp : uint32_t {
   HC_MAP_RMAX = 18,
   // Row programs only, in the uniform prologue of a pass: s[src] = acc.
   HC_MAP_SET = 19,
-  HC_MAP_OP_COUNT = 20
+  // The rest of the tile operator table (element-wise kernel only).  The
+  // division-like operations mark the element invalid where NumPy's masked
+  // arrays mask it - a zero divisor; a power that is not finite - and an
+  // invalid element is not stored, like the reference's masked store.
+  HC_MAP_FLOORDIV = 20,  // acc = floor(acc / v), NumPy's floor_divide
+  HC_MAP_RFLOORDIV = 21, // acc = floor(v / acc)
+  HC_MAP_MOD = 22,       // acc = acc mod v, sign of the divisor (NumPy's remainder)
+  HC_MAP_RMOD = 23,      // acc = v mod acc
+  HC_MAP_POW = 24,       // acc = acc ** v
+  HC_MAP_RPOW = 25,      // acc = v ** acc
+  HC_MAP_LT = 26,        // acc = acc < v ? 1 : 0, and likewise:
+  HC_MAP_LE = 27,
+  HC_MAP_EQ = 28,
+  HC_MAP_NE = 29,
+  HC_MAP_GE = 30,
+  HC_MAP_GT = 31,
+  HC_MAP_AND = 32,       // integers: bitwise; floats: logical on zero / nonzero
+  HC_MAP_OR = 33,
+  HC_MAP_XOR = 34,
+  HC_MAP_SHL = 35,       // integers only: acc << v
+  HC_MAP_SHR = 36,       // acc >> v (arithmetic)
+  HC_MAP_RSHL = 37,      // v << acc
+  HC_MAP_RSHR = 38,      // v >> acc
+  HC_MAP_INV = 39,       // integers: ~acc; floats (truth values): acc == 0 ? 1 : 0
+  HC_MAP_OP_COUNT = 40
 };
+// Does `op` combine the accumulator with an operand (as opposed to changing
+// the accumulator alone, saving it or ending a pass)?
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+constexpr bool hcMapIsBinary(uint32_t op) {
+  return op <= HC_MAP_MIN || (op >= HC_MAP_FLOORDIV && op <= HC_MAP_RSHR);
+}
 // Row programs only: an instruction with this bit set in its operation byte is
 // uniform - it works on one value per row (operands: constants and row
 // scalars) and runs once, before the pass walks the row.  A pass may begin

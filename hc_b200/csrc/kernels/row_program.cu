@@ -139,7 +139,10 @@ __device__ __forceinline__ void rowProgram(const HcMapProgramDev &p) {
             x[k][u * V + e] = packet.v[e];
         }
       T value[W];
-      evaluate<T, W, V, NIN, false, true, 32>(p, pc, end, x, value, temps, r, base, scalars);
+      uint32_t ok = ~0u; // row programs do not track validity
+      uint64_t parkedOk = ~0ull;
+      evaluate<T, W, V, NIN, false, true, 32>(p, pc, end, x, value, temps, r, base, scalars, ok,
+                                              parkedOk);
       if (last) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -235,8 +238,10 @@ __device__ __forceinline__ void rowProgramHeld(const HcMapProgramDev &p) {
     uint32_t reduction, target;
     const int end = passEnd(p, pc, reduction, target);
     T value[W];
+    uint32_t ok = ~0u; // row programs do not track validity
+    uint64_t parkedOk = ~0ull;
     evaluate<T, W, V, NIN, false, true, NT, NT>(p, pc, end, x, value, temps, r, threadIdx.x,
-                                                 scalars);
+                                                 scalars, ok, parkedOk);
     if (end >= p.nInstr) {
       T *const rowOut = static_cast<T *>(p.out) + r * p.outPitch;
 #pragma unroll

@@ -1,0 +1,65 @@
+// The context behind an HcContext handle, shared by the translation units of
+// libhc-b200-kernels.so.
+#pragma once
+
+#include "hc_b200_kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+struct HcContextImpl {
+  OlErrorCallback callback = nullptr;
+  void *callbackCtx = nullptr;
+  OlDevice device = nullptr;
+  OlQueue queue = nullptr;
+  std::vector<OlModule> modules; // one slot per image, loaded on first use
+  std::map<std::string, OlKernel> kernels;
+  int *statusWord = nullptr; // device
+  std::string lastError;
+  long long launches = 0;
+  long long smCount = 0;
+  long long ccMajor = 0;
+  long long gemmVariant = 0;
+  long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
+  long long tiledVariant = 0;
+  long long reduceVariant = 0;
+  long long mappedStack = 0;
+  long long rowVariant = 0;
+  long long fusedVariant = 0; // 1: never use the precompiled bodies
+  long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
+
+  int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
+    char text[320];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(text, sizeof(text), fmt, ap);
+    va_end(ap);
+    lastError = text;
+    if (callback)
+      callback(callbackCtx, OlSeverity::Error, text);
+    return 1;
+  }
+
+  // ol* failures arrive here through the loader/backend callback.
+  static void onBackendMessage(void *self, OlSeverity sev, const char *desc) {
+    auto *c = static_cast<HcContextImpl *>(self);
+    if (sev == OlSeverity::Error)
+      c->lastError = desc ? desc : "";
+    if (c->callback)
+      c->callback(c->callbackCtx, sev, desc);
+  }
+
+  // The kernel `name` from the embedded images (loaded on first use), or null.
+  OlKernel kernel(const char *name);
+  // Launches `name` with a one-dimensional block on the context's queue.
+  int launch(const char *name, size_t gx, size_t gy, size_t gz, size_t threads, void **args,
+             size_t nArgs, size_t smem);
+  // Scratch of the host-buffer entry points (host_api.cpp), released with the context.
+  struct HostPipeline *hostPipeline = nullptr;
+};
+
+// Frees what the host-buffer entry points keep in a context (host_api.cpp).
+void hcReleaseHostPipeline(HcContextImpl *c);

@@ -7,7 +7,7 @@
 // python/cpp/py-runtime/src/GpuRuntime.cpp:26-69 executes it).  Here the blobs
 // are fixed, so the sequence is ordinary C++ and each workload gets a typed
 // entry point that validates its arguments and chooses a kernel variant.
-#include "hc_b200_kernels.h"
+#include "context.hpp"
 
 #include "../kernels/fused_programs.h"
 #include "../kernels/map_params.h"
@@ -165,89 +165,46 @@ constexpr int kRowHeldFillPercent = 90;
 
 } // namespace
 
-struct HcContextImpl {
-  OlErrorCallback callback = nullptr;
-  void *callbackCtx = nullptr;
-  OlDevice device = nullptr;
-  OlQueue queue = nullptr;
-  std::vector<OlModule> modules; // one slot per image, loaded on first use
-  std::map<std::string, OlKernel> kernels;
-  int *statusWord = nullptr; // device
-  std::string lastError;
-  long long launches = 0;
-  long long smCount = 0;
-  long long ccMajor = 0;
-  long long gemmVariant = 0;
-  long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
-  long long tiledVariant = 0;
-  long long reduceVariant = 0;
-  long long mappedStack = 0;
-  long long rowVariant = 0;
-  long long fusedVariant = 0; // 1: never use the precompiled bodies
-  long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
-
-  int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
-    char text[320];
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(text, sizeof(text), fmt, ap);
-    va_end(ap);
-    lastError = text;
-    if (callback)
-      callback(callbackCtx, OlSeverity::Error, text);
-    return 1;
+OlKernel HcContextImpl::kernel(const char *name) {
+  auto it = kernels.find(name);
+  if (it != kernels.end())
+    return it->second;
+  const char *imageName = imageOfKernel(name);
+  int idx = imageName ? findImage(imageName) : -1;
+  if (idx < 0) {
+    fail("Unknown kernel: %s", name);
+    return nullptr;
   }
-
-  // ol* failures arrive here through the loader/backend callback.
-  static void onBackendMessage(void *self, OlSeverity sev, const char *desc) {
-    auto *c = static_cast<HcContextImpl *>(self);
-    if (sev == OlSeverity::Error)
-      c->lastError = desc ? desc : "";
-    if (c->callback)
-      c->callback(c->callbackCtx, sev, desc);
-  }
-
-  OlKernel kernel(const char *name) {
-    auto it = kernels.find(name);
-    if (it != kernels.end())
-      return it->second;
-    const char *imageName = imageOfKernel(name);
-    int idx = imageName ? findImage(imageName) : -1;
-    if (idx < 0) {
-      fail("Unknown kernel: %s", name);
-      return nullptr;
-    }
+  if (!modules[idx]) {
+    const HcImage &img = hc_b200_images[idx];
+    modules[idx] = olCreateModule(device, img.begin, size_t(img.end - img.begin));
     if (!modules[idx]) {
-      const HcImage &img = hc_b200_images[idx];
-      modules[idx] = olCreateModule(device, img.begin, size_t(img.end - img.begin));
-      if (!modules[idx]) {
-        fail("olCreateModule failed for image %s: %s", img.name,
-             lastError.c_str());
-        return nullptr;
-      }
-    }
-    OlKernel k = olGetKernel(modules[idx], name);
-    if (!k) {
-      fail("olGetKernel failed for %s: %s", name, lastError.c_str());
+      fail("olCreateModule failed for image %s: %s", img.name,
+           lastError.c_str());
       return nullptr;
     }
-    kernels[name] = k;
-    return k;
   }
+  OlKernel k = olGetKernel(modules[idx], name);
+  if (!k) {
+    fail("olGetKernel failed for %s: %s", name, lastError.c_str());
+    return nullptr;
+  }
+  kernels[name] = k;
+  return k;
+}
 
-  int launch(const char *name, size_t gx, size_t gy, size_t gz, size_t threads,
-             void **args, size_t nArgs, size_t smem) {
-    OlKernel k = kernel(name);
-    if (!k)
-      return 1;
-    const size_t grid[3] = {gx, gy, gz};
-    const size_t block[3] = {threads, 1, 1};
-    if (olLaunchKernel(queue, k, grid, block, 3, args, nArgs, smem))
-      return fail("olLaunchKernel failed for %s: %s", name, lastError.c_str());
-    ++launches;
-    return 0;
-  }
-};
+int HcContextImpl::launch(const char *name, size_t gx, size_t gy, size_t gz, size_t threads,
+                        void **args, size_t nArgs, size_t smem) {
+  OlKernel k = kernel(name);
+  if (!k)
+    return 1;
+  const size_t grid[3] = {gx, gy, gz};
+  const size_t block[3] = {threads, 1, 1};
+  if (olLaunchKernel(queue, k, grid, block, 3, args, nArgs, smem))
+    return fail("olLaunchKernel failed for %s: %s", name, lastError.c_str());
+  ++launches;
+  return 0;
+}
 
 namespace {
 
@@ -331,6 +288,7 @@ void hcReleaseContext(HcContext c) {
   for (OlModule m : c->modules)
     if (m)
       olReleaseModule(m);
+  hcReleaseHostPipeline(c);
   if (c->statusWord)
     olDeallocDevice(c->queue, c->statusWord);
   if (c->queue)
@@ -482,7 +440,7 @@ static_assert(sizeof(HcMapProgram) == sizeof(HcMapProgramDev) &&
 // row scalars are allowed (and a last pass that stores is required); element
 // indices are not.
 static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &p,
-                           bool rowProgram, bool *usesIndices) {
+                           bool rowProgram, bool *usesIndices, bool integer = false) {
   bool saved[3] = {false, false, false};
   bool reduced[HC_MAP_MAX_SCALARS] = {false, false, false, false};
   bool passStart = true;
@@ -531,12 +489,20 @@ static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &
     }
     if (op >= HC_MAP_OP_COUNT || op == HC_MAP_SET)
       return c->fail("%s: unknown operation %u at instruction %d", who, op, pc);
+    if (rowProgram && op >= HC_MAP_FLOORDIV)
+      return c->fail("%s: operation %u (instruction %d) belongs to hcMapElements", who, op, pc);
+    if (integer && (op == HC_MAP_DIV || op == HC_MAP_RDIV || op == HC_MAP_EXP ||
+                    op == HC_MAP_SQRT || op == HC_MAP_LOG || op == HC_MAP_RPOW))
+      return c->fail("%s: operation %u (instruction %d) is not defined on integer arrays", who,
+                     op, pc);
+    if (!integer && op >= HC_MAP_SHL && op <= HC_MAP_RSHR)
+      return c->fail("%s: shifts (instruction %d) are defined on integer arrays only", who, pc);
     if (passStart && op != HC_MAP_LOAD)
       return c->fail(pc == 0 ? "%s: the first instruction must load the accumulator"
                              : "%s: the instruction after a reduction must load the accumulator",
                      who);
     passStart = false;
-    if (op <= HC_MAP_MIN) {
+    if (hcMapIsBinary(op)) {
       const bool input = src < uint32_t(p.nInputs);
       const bool temp = src >= HC_MAP_SRC_TEMP && src < HC_MAP_SRC_TEMP + 3 &&
                         saved[src - HC_MAP_SRC_TEMP];
@@ -551,6 +517,18 @@ static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &
         return c->fail("%s: instruction %d reads operand %u, which does not exist "
                        "or is not written yet",
                        who, pc, src);
+      if (integer && constant) {
+        const double value = p.consts[src - HC_MAP_SRC_CONST];
+        if (value != double((long long)value) || value < -9.2e18 || value > 9.2e18)
+          return c->fail("%s: constant %g (instruction %d) is not an integer", who, value, pc);
+        if (op == HC_MAP_POW && value < 0)
+          return c->fail("%s: integers to negative integer powers are not allowed "
+                         "(instruction %d)",
+                         who, pc);
+      }
+      if (integer && op == HC_MAP_POW && !constant)
+        return c->fail("%s: integer arrays take constant exponents only (instruction %d)", who,
+                       pc);
     }
     if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
       saved[op - HC_MAP_SAVE0] = true;
@@ -576,8 +554,9 @@ static int checkMapProgram(HcContext c, const char *who, const HcMapProgramDev &
 int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   if (!c)
     return 1;
-  if (dtype != HC_F32 && dtype != HC_F64)
+  if (dtype != HC_F32 && dtype != HC_F64 && dtype != HC_I32 && dtype != HC_I64)
     return c->fail("hcMapElements: unsupported dtype %d", dtype);
+  const bool integer = dtype == HC_I32 || dtype == HC_I64;
   if (!program)
     return c->fail("hcMapElements: null program");
   HcMapProgramDev p;
@@ -587,7 +566,7 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
     return c->fail("hcMapElements: %d inputs, %d instructions (at most %d and 1..%d)", p.nInputs,
                    p.nInstr, HC_MAP_MAX_INPUTS, HC_MAP_MAX_INSTR);
   bool usesIndices = false;
-  if (checkMapProgram(c, "hcMapElements", p, false, &usesIndices))
+  if (checkMapProgram(c, "hcMapElements", p, false, &usesIndices, integer))
     return 1;
   if (p.rows < 0 || p.cols < 0 || p.outPitch < p.cols)
     return c->fail("hcMapElements: invalid shape %lld x %lld", (long long)p.rows,
@@ -602,7 +581,11 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   for (int k = 0; k < p.nInputs; ++k)
     if (!p.in[k])
       return c->fail("hcMapElements: null input %d", k);
-  const int elem = dtype == HC_F32 ? 4 : 8;
+  const int elem = dtype == HC_F32 || dtype == HC_I32 ? 4 : 8;
+  const char *tname = dtype == HC_F32   ? "f32"
+                      : dtype == HC_F64 ? "f64"
+                      : dtype == HC_I32 ? "i32"
+                                        : "i64";
   // Contiguous matrices are one long row (unless the program asks where an
   // element is).
   bool flat = p.outPitch == p.cols && !usesIndices;
@@ -625,14 +608,21 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   char name[64];
   // A body that was compiled ahead of time runs as straight-line code; any
   // other program is interpreted.
-  const char *fused = c->fusedVariant == 1 ? nullptr : matchFused(kFusedMaps, p);
+  const char *fused =
+      c->fusedVariant == 1 || integer ? nullptr : matchFused(kFusedMaps, p);
   if (fused)
-    std::snprintf(name, sizeof name, "hc_map_fused_%s_%s_v%d", fused,
-                  dtype == HC_F32 ? "f32" : "f64", v);
-  else
-    std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s",
-                  dtype == HC_F32 ? "f32" : "f64", v, std::max(1, p.nInputs),
-                  usesIndices ? "i" : "");
+    std::snprintf(name, sizeof name, "hc_map_fused_%s_%s_v%d", fused, tname, v);
+  else {
+    // Programs that divide, compare, use the later operators or work on integers
+    // take the extended kernel, which tracks the validity of every element.
+    bool extended = integer;
+    for (int pc = 0; pc < p.nInstr; ++pc) {
+      const uint32_t op = p.code[pc] & 0xffu;
+      extended = extended || op == HC_MAP_DIV || op == HC_MAP_RDIV || op >= HC_MAP_FLOORDIV;
+    }
+    std::snprintf(name, sizeof name, "hc_map_elements_%s_v%d_n%d%s%s", tname, v,
+                  std::max(1, p.nInputs), usesIndices ? "i" : "", extended ? "x" : "");
+  }
   const long long perRow = p.cols / v;
   // One CTA per 1024 packets of a row (four per thread; 512 and two with three
   // or four inputs - map_elements.cu); rows beyond 65535 and very long rows are

@@ -491,7 +491,7 @@ int olxPointerDevice(OlDevice d, const void *ptr, int *ordinalRet) noexcept {
   return fn ? fn(dev->inner, ptr, ordinalRet) : missing(dev, "olxPointerDevice");
 }
 
-OlxEvent olxCreateEvent(OlDevice d) noexcept {
+OlxEvent olxCreateEvent(OlDevice d, int timing) noexcept {
   auto *dev = static_cast<DeviceHandle *>(d);
   if (!dev)
     return nullptr;
@@ -500,7 +500,7 @@ OlxEvent olxCreateEvent(OlDevice d) noexcept {
     missing(dev, "olxCreateEvent");
     return nullptr;
   }
-  return fn(dev->inner);
+  return fn(dev->inner, timing);
 }
 
 void olxReleaseEvent(OlDevice d, OlxEvent ev) noexcept {

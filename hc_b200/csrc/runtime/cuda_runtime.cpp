@@ -608,7 +608,7 @@ int olxPointerDevice(OlDevice d, const void *ptr, int *ordinalRet) noexcept {
   return 0;
 }
 
-OlxEvent olxCreateEvent(OlDevice d) noexcept {
+OlxEvent olxCreateEvent(OlDevice d, int timing) noexcept {
   auto *dev = static_cast<DeviceState *>(d);
   if (!dev)
     return nullptr;
@@ -616,7 +616,8 @@ OlxEvent olxCreateEvent(OlDevice d) noexcept {
   if (!scope)
     return nullptr;
   CUevent ev = nullptr;
-  if (dev->check("cuEventCreate", DriverApi::get().EventCreate(&ev, CU_EVENT_DEFAULT)))
+  if (dev->check("cuEventCreate", DriverApi::get().EventCreate(
+                                      &ev, timing ? CU_EVENT_DEFAULT : CU_EVENT_DISABLE_TIMING)))
     return nullptr;
   return ev;
 }

@@ -26,13 +26,64 @@ from .kernel_api import Tile, UnsupportedKernel
 
 LOAD, ADD, SUB, RSUB, MUL, DIV, RDIV, MAX, MIN, NEG, ABS, EXP, SQRT, SAVE0 = range(14)
 LOG, RSUM, RMAX, SET = 16, 17, 18, 19
+# The rest of the reference's tile operator table (element-wise bodies only).
+(FLOORDIV, RFLOORDIV, MOD, RMOD, POW, RPOW, LT, LE, EQ, NE, GE, GT, AND, OR, XOR, SHL, SHR, RSHL,
+ RSHR, INV) = range(20, 40)
 UNIFORM = 0x80  # flag in the operation byte: one value per row, computed before the walk
 SRC_TEMP, SRC_CONST, SRC_SCALAR = 4, 8, 20
 MAX_INPUTS, MAX_CONSTS, MAX_INSTR, TEMPS, MAX_SCALARS = 4, 8, 32, 3, 4
 
+# operation -> (acc OP v, v OP acc)
 _BINARY = {"add": (ADD, ADD), "sub": (SUB, RSUB), "mul": (MUL, MUL), "div": (DIV, RDIV),
-           "maximum": (MAX, MAX), "minimum": (MIN, MIN)}
-_UNARY = {"neg": NEG, "abs": ABS, "exp": EXP, "sqrt": SQRT, "log": LOG}
+           "maximum": (MAX, MAX), "minimum": (MIN, MIN),
+           "floordiv": (FLOORDIV, RFLOORDIV), "mod": (MOD, RMOD), "pow": (POW, RPOW),
+           "lt": (LT, GT), "le": (LE, GE), "eq": (EQ, EQ), "ne": (NE, NE), "ge": (GE, LE),
+           "gt": (GT, LT), "and": (AND, AND), "or": (OR, OR), "xor": (XOR, XOR),
+           "lshift": (SHL, RSHL), "rshift": (SHR, RSHR)}
+_UNARY = {"neg": NEG, "abs": ABS, "exp": EXP, "sqrt": SQRT, "log": LOG, "invert": INV}
+_FLOAT_ONLY = ("div", "exp", "sqrt", "log")
+_INTEGER_ONLY = ("lshift", "rshift")
+_LOGICAL = ("and", "or", "xor", "invert")
+
+
+def check_types(expr, dtype, what):
+    """Refuses what the element type of the arrays has no operation for, with
+    NumPy's reasons: integers have no true division (its result is a float
+    array), exp, sqrt or log here, floats no shifts and no bitwise operators
+    except on truth values (the results of comparisons)."""
+    integer = dtype.startswith("int")
+    seen = set()
+
+    def walk(node):
+        if not isinstance(node, Tile) or id(node) in seen:
+            return
+        seen.add(id(node))
+        for arg in node.args:
+            walk(arg)
+        if integer and node.op in _FLOAT_ONLY:
+            raise UnsupportedKernel(
+                f"{what}: '{node.op}' on {dtype} tiles gives floating-point values; compute in a "
+                f"float array")
+        if integer and node.op == "const" and float(node.args[0]) != int(node.args[0]):
+            raise UnsupportedKernel(
+                f"{what}: the constant {node.args[0]!r} turns {dtype} tiles into floating-point "
+                f"values; compute in a float array")
+        if integer and node.op == "pow":
+            exponent = node.args[1]
+            if not (isinstance(exponent, Tile) and exponent.op == "const"):
+                raise UnsupportedKernel(f"{what}: {dtype} tiles take constant exponents only")
+            if float(exponent.args[0]) < 0:
+                raise ValueError("Integers to negative integer powers are not allowed.")
+        if not integer and node.op in _INTEGER_ONLY:
+            raise TypeError(f"{what}: shifts are not supported for {dtype} tiles")
+        if not integer and node.op in _LOGICAL:
+            operands = [a for a in node.args if isinstance(a, Tile) and a.op != "const"]
+            if any(a.dtype != "bool" for a in operands):
+                raise TypeError(
+                    f"{what}: '{node.op}' is not supported for {dtype} tiles (only for truth "
+                    f"values, the results of comparisons)")
+
+    walk(expr)
 _ROW_REDUCTIONS = {"sum": RSUM, "max": RMAX}
 
 
@@ -183,6 +234,11 @@ class MapProgram:
         src = self._leaf(node)
         if src is not None:
             self._emit(LOAD, src)
+        elif node.op == "invert" and node.args[0].dtype == "bool":
+            # NumPy's ~ on truth values is "not": 1 where the value is 0 (the
+            # machine's own `inv` is the bitwise one on integer arrays).
+            self.evaluate(node.args[0])
+            self._emit(EQ, self._leaf(Tile("const", (0.0,), (), "scalar")))
         elif node.op in _UNARY:
             self.evaluate(node.args[0])
             self._emit(_UNARY[node.op])
@@ -226,9 +282,11 @@ def match_map(stores, counts, covers):
         return None
     if dst.buffer.ndim not in (1, 2) or len(expr.shape) != dst.buffer.ndim:
         raise UnsupportedKernel("element-wise kernels are supported for vectors and matrices")
-    if dst.buffer.dtype not in ("float32", "float64"):
+    if dst.buffer.dtype not in ("float32", "float64", "int32", "int64"):
         raise UnsupportedKernel(
-            f"element-wise kernels compute in float32 or float64, not {dst.buffer.dtype}")
+            f"element-wise kernels compute in float32, float64, int32 or int64, not "
+            f"{dst.buffer.dtype}")
+    check_types(expr, dst.buffer.dtype, "element-wise kernel")
     program = MapProgram(expr.shape)
     program.evaluate(expr)
     for tile in program.inputs:
@@ -296,6 +354,10 @@ def match_rows(stores, counts, covers):
     program.begin_pass()
     program.evaluate(expr)
     program.end_pass()
+    if any((ins & 0x7F) >= FLOORDIV for ins in program.code):
+        raise UnsupportedKernel(
+            f"{what}: // % ** comparisons and bitwise operators are supported in element-wise "
+            f"bodies only, not together with row reductions")
     if len(program.inputs) > 2 or not program.inputs:
         raise UnsupportedKernel(f"{what}: one or two input matrices")
     for tile in program.inputs:
@@ -339,8 +401,10 @@ def match_items(item_stores, guards, work_shape):
         raise UnsupportedKernel(
             f"{what}: the store must be {dst.name}[global_id] with one index per dimension, in "
             f"order, of a vector or matrix")
-    if dst.dtype not in ("float32", "float64"):
-        raise UnsupportedKernel(f"{what}: float32 or float64 arrays, not {dst.dtype}")
+    if dst.dtype not in ("float32", "float64", "int32", "int64"):
+        raise UnsupportedKernel(
+            f"{what}: float32, float64, int32 or int64 arrays, not {dst.dtype}")
+    check_types(expr, dst.dtype, what)
     for axis, bound in guards:
         if axis >= rank or bound < dst.shape[axis]:
             raise UnsupportedKernel(

@@ -465,6 +465,9 @@ def _broadcast(a, b):
     return tuple(out)
 
 
+_COMPARISONS = ("lt", "le", "eq", "ne", "ge", "gt")
+
+
 class Tile:
     """A node of the recorded expression graph.
 
@@ -516,7 +519,22 @@ class Tile:
     def _binary(self, op, other, swapped=False):
         o = Tile._wrap(other)
         lhs, rhs = (o, self) if swapped else (self, o)
-        dtype = lhs.dtype if lhs.dtype != "scalar" else rhs.dtype
+        kinds = [d for d in (lhs.dtype, rhs.dtype) if d != "scalar"]
+        if kinds == ["bool", "bool"]:
+            # Truth values among themselves, as NumPy treats bool arrays.
+            if op in ("add", "or", "maximum"):
+                op = "or"
+            elif op in ("mul", "and", "minimum"):
+                op = "and"
+            elif op not in _COMPARISONS and op != "xor":
+                raise TypeError(f"numpy boolean {op} is not supported; use & | ^ on truth values")
+            dtype = "bool"
+        else:
+            # A truth value (0 / 1) takes the type of what it is combined with.
+            others = [d for d in kinds if d != "bool"]
+            dtype = others[0] if others else (kinds[0] if kinds else "scalar")
+        if op in _COMPARISONS:
+            dtype = "bool"
         return Tile(op, (lhs, rhs), _broadcast(lhs.shape, rhs.shape), dtype)
 
     def __add__(self, o): return self._binary("add", o)
@@ -535,11 +553,49 @@ class Tile:
         return Tile(op, (self,), self.shape, self.dtype)
 
     def __pow__(self, exponent):
-        if exponent == 2:
+        # NumPy computes squares as products and ** 0.5 as a square root.
+        if isinstance(exponent, (int, float)) and exponent == 2:
             return self * self
-        if exponent == 0.5:
+        if isinstance(exponent, (int, float)) and exponent == 0.5:
             return self._unary("sqrt")
-        raise UnsupportedKernel(f"tile ** {exponent!r}: only squares and square roots")
+        return self._binary("pow", exponent)
+
+    def __rpow__(self, base): return self._binary("pow", base, True)
+
+    # The rest of the reference's operator table (kernel_api.py:157-176).
+    # Comparisons give truth values (0 / 1 in the element type once they meet
+    # arithmetic); & | ^ are bitwise on integer tiles and logical on truth values.
+    def __floordiv__(self, o): return self._binary("floordiv", o)
+    def __rfloordiv__(self, o): return self._binary("floordiv", o, True)
+    def __mod__(self, o): return self._binary("mod", o)
+    def __rmod__(self, o): return self._binary("mod", o, True)
+    def __lt__(self, o): return self._binary("lt", o)
+    def __le__(self, o): return self._binary("le", o)
+    def __eq__(self, o): return self._binary("eq", o)
+    def __ne__(self, o): return self._binary("ne", o)
+    def __ge__(self, o): return self._binary("ge", o)
+    def __gt__(self, o): return self._binary("gt", o)
+    def __and__(self, o): return self._binary("and", o)
+    def __rand__(self, o): return self._binary("and", o, True)
+    def __or__(self, o): return self._binary("or", o)
+    def __ror__(self, o): return self._binary("or", o, True)
+    def __xor__(self, o): return self._binary("xor", o)
+    def __rxor__(self, o): return self._binary("xor", o, True)
+    def __lshift__(self, o): return self._binary("lshift", o)
+    def __rlshift__(self, o): return self._binary("lshift", o, True)
+    def __rshift__(self, o): return self._binary("rshift", o)
+    def __rrshift__(self, o): return self._binary("rshift", o, True)
+    def __invert__(self): return self._unary("invert")
+    __hash__ = object.__hash__  # (nodes are compared through key(), never with ==)
+
+    def __bool__(self):
+        # `not tile`, `if tile:` - NumPy's answer for arrays (the reference's
+        # operator.not_ entry fails the same way on a tile of several elements).
+        raise ValueError("The truth value of a tile with more than one element is ambiguous")
+
+    def __ifloordiv__(self, o): return self._binary("floordiv", o)
+    def __imod__(self, o): return self._binary("mod", o)
+    def __itruediv__(self, o): return self._binary("div", o)
     # `acc += x` rebinds the name to the new node, like any immutable value.
     def __iadd__(self, o): return self._binary("add", o)
     def __isub__(self, o): return self._binary("sub", o)
@@ -614,9 +670,16 @@ class Tile:
         if method != "__call__" or kwargs.get("out") is not None:
             raise UnsupportedKernel(f"np.{ufunc.__name__}.{method} on a tile")
         names = {"add": "add", "subtract": "sub", "multiply": "mul", "true_divide": "div",
-                 "divide": "div", "maximum": "maximum", "minimum": "minimum"}
+                 "divide": "div", "maximum": "maximum", "minimum": "minimum",
+                 "floor_divide": "floordiv", "remainder": "mod", "mod": "mod", "power": "pow",
+                 "less": "lt", "less_equal": "le", "equal": "eq", "not_equal": "ne",
+                 "greater_equal": "ge", "greater": "gt", "bitwise_and": "and",
+                 "bitwise_or": "or", "bitwise_xor": "xor", "logical_and": "and",
+                 "logical_or": "or", "logical_xor": "xor", "left_shift": "lshift",
+                 "right_shift": "rshift"}
         unary = {"exp": "exp", "sqrt": "sqrt", "absolute": "abs", "fabs": "abs",
-                 "negative": "neg", "log": "log"}
+                 "negative": "neg", "log": "log", "invert": "invert", "bitwise_not": "invert",
+                 "logical_not": "invert"}
         if ufunc.__name__ in unary:
             (x,) = inputs
             return x._unary(unary[ufunc.__name__])

@@ -93,7 +93,9 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * registers of one CTA per row (eight packets per thread on 64, 96 or 128
  * threads), 1 = always one warp per row that walks the row once per pass,
  * 2 = as 3, with 256 threads and four packets each beyond 512 packets,
- * 3 = hold such rows whatever the fill. */
+ * 3 = hold such rows whatever the fill.  "fused": 0 = programs that match a body
+ * compiled ahead of time run as straight-line kernels, 1 = every program is
+ * interpreted. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* ---- workloads -------------------------------------------------------------
@@ -104,7 +106,7 @@ HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
                          long long dstPitch, int elemBytes);
 
 /* Element-wise expression: out[r,c] = f(in0[r,c], ..., in3[r,c]) over
- * rows x cols matrices, HC_F32 or HC_F64 (all arrays one type).  What
+ * rows x cols matrices, HC_F32, HC_F64, HC_I32 or HC_I64 (all arrays one type).  What
  * work-groups compute that load tiles at one origin, combine them element by
  * element and store the result there - the reference's copy kernels
  * (python/hckernel/tests/test_e2e.py:57-136) with tile arithmetic
@@ -114,13 +116,30 @@ HC_B200_API int hcCopy2D(HcContext c, const void *src, void *dst,
  *   op   0 load  1 add  2 sub  3 rsub (v - acc)  4 mul  5 div  6 rdiv (v / acc)
  *        7 max  8 min  9 neg  10 abs  11 exp  12 sqrt  13..15 save to t0..t2
  *        16 log
+ *        the rest of the reference's tile operator table
+ *        (python/hckernel/kernel_api.py:157-176), hcMapElements only:
+ *        20 floordiv  21 rfloordiv (v // acc)  22 mod  23 rmod  24 pow  25 rpow
+ *        26 lt  27 le  28 eq  29 ne  30 ge  31 gt   (acc = acc OP v ? 1 : 0)
+ *        32 and  33 or  34 xor   (integers: bitwise; floats: logical on zero / nonzero)
+ *        35 shl  36 shr  37 rshl (v << acc)  38 rshr   (integers only)
+ *        39 inv   (integers: ~acc; floats: acc == 0 ? 1 : 0)
  *   src  0..3 input arrays, 4..6 temporaries t0..t2, 8..15 consts[0..7],
  *        16 / 17 the row / column index of the element, as a value (what a body
  *        written at work-item level gets from global_id(),
  *        python/hckernel/kernel_api.py:243-252, 395-414)
  * max and min give NaN when either operand is NaN (NumPy's maximum/minimum);
- * operations are never contracted into FMAs.  The value of the accumulator
- * after the last instruction is stored.  Pitches are in elements. */
+ * operations are never contracted into FMAs; integer arithmetic wraps; floor
+ * division and remainder follow NumPy's (Python's sign conventions).  Integer
+ * arrays take no division, exp, sqrt or log, integral constants only, and
+ * constant non-negative exponents.  The value of the accumulator after the last
+ * instruction is stored - except where the arithmetic made it invalid the way
+ * NumPy's masked arrays mask an element (the reference's tiles are numpy.ma
+ * arrays): a zero divisor of / // %, a power that is not finite.  Such elements
+ * of `out` are left as they were, like the reference's masked store
+ * (python/hckernel/kernel_api.py:338-340).  A program that matches one of the
+ * bodies compiled ahead of time (hc_b200/csrc/kernels/fused_programs.h) runs as
+ * a straight-line kernel, any other is interpreted; the results are the same
+ * bit for bit.  Pitches are in elements. */
 typedef struct HcMapProgram {
   const void *in[4];      /* device */
   long long inPitch[4];
@@ -266,6 +285,35 @@ HC_B200_API int hcGemmW8A16Static(HcContext c, const void *a, const void *w,
                                   const float *scale, void *out, long long M,
                                   long long N, long long K, long long lda,
                                   long long ldw, long long ldc);
+
+/* ---- host buffers ------------------------------------------------------------
+ * The row-wise workloads and the bf16 GEMM on matrices that live in HOST
+ * memory: every pointer below is a host pointer.  The matrix is cut into row
+ * chunks of about 16 MiB that stream through the GPU on three queues of the
+ * context's device (upload of chunk i+1, kernel on chunk i, download of chunk
+ * i-1 overlap; device slots are allocated on first use and kept by the
+ * context), so a call costs little more than moving the data over the link
+ * once each way.  Only whole rows reach the kernels: results are bit for bit
+ * those of the device entry points.  A call returns when the result is in host
+ * memory.  The copies overlap only for page-locked memory: lock a range once
+ * with hcHostPin (and release it with hcHostUnpin); pageable memory works but
+ * serialises the three stages.  No counterpart in the reference, whose runtime
+ * sees device pointers only and synchronises after every launch
+ * (python/cpp/py-runtime/src/GpuRuntime.cpp:60-69). */
+HC_B200_API int hcHostPin(HcContext c, void *ptr, size_t bytes);
+HC_B200_API int hcHostUnpin(HcContext c, void *ptr);
+HC_B200_API int hcSoftmaxRowsHost(HcContext c, const void *xHost, void *yHost,
+                                  long long rows, long long cols, long long xPitch,
+                                  long long yPitch, int dtype);
+/* Either output may be NULL. */
+HC_B200_API int hcReduceRowsHost(HcContext c, const void *xHost, void *sumHost,
+                                 void *maxHost, long long rows, long long cols,
+                                 long long pitch, int dtype);
+/* c = a @ b in bf16 with fp32 accumulation: b [K, N] is uploaded whole, row
+ * blocks of a [M, K] stream through, row blocks of c [M, N] come back. */
+HC_B200_API int hcGemmBf16Host(HcContext c, const void *aHost, const void *bHost,
+                               void *cHost, long long M, long long N, long long K,
+                               long long lda, long long ldb, long long ldc);
 
 /* Records `text` as the context's last error, reports it through the
  * context's callback and returns 1.  For code layered on this library. */

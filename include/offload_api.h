@@ -159,7 +159,9 @@ OFFLOAD_API_EXPORT int olxPointerDevice(OlDevice dev, const void *ptr,
  * none because it synchronises the host after every launch
  * (python/cpp/py-runtime/src/GpuRuntime.cpp:67). */
 typedef void *OlxEvent;
-OFFLOAD_API_EXPORT OlxEvent olxCreateEvent(OlDevice dev) HC_NOEXCEPT;
+/* `timing` 0 makes an event that only orders work (cheaper); nonzero one that
+ * olxEventElapsedMs can read. */
+OFFLOAD_API_EXPORT OlxEvent olxCreateEvent(OlDevice dev, int timing) HC_NOEXCEPT;
 OFFLOAD_API_EXPORT void olxReleaseEvent(OlDevice dev, OlxEvent ev) HC_NOEXCEPT;
 OFFLOAD_API_EXPORT int olxRecordEvent(OlQueue q, OlxEvent ev) HC_NOEXCEPT;
 OFFLOAD_API_EXPORT int olxQueueWaitEvent(OlQueue q, OlxEvent ev) HC_NOEXCEPT;

@@ -42,6 +42,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from itertools import product
 
+import operator
+
 import numpy as np
 
 
@@ -121,6 +123,27 @@ class ArithmeticTile:
     def __truediv__(self, other): return self._binary(other, np.ma.true_divide)
     def __neg__(self): return ArithmeticTile(-self.ma)
     def __abs__(self): return ArithmeticTile(abs(self.ma))
+
+    # The rest of the reference's operator table (kernel_api.py:157-176): the
+    # Python operator applied to the masked arrays.  Division-like operators
+    # mask the elements whose divisor is zero, ``**`` those whose result is not
+    # finite (numpy.ma's domains); the masked store then leaves them unwritten.
+    def __floordiv__(self, other): return self._binary(other, operator.floordiv)
+    def __mod__(self, other): return self._binary(other, operator.mod)
+    def __pow__(self, other): return self._binary(other, operator.pow)
+    def __lt__(self, other): return self._binary(other, operator.lt)
+    def __le__(self, other): return self._binary(other, operator.le)
+    def __eq__(self, other): return self._binary(other, operator.eq)
+    def __ne__(self, other): return self._binary(other, operator.ne)
+    def __ge__(self, other): return self._binary(other, operator.ge)
+    def __gt__(self, other): return self._binary(other, operator.gt)
+    def __and__(self, other): return self._binary(other, operator.and_)
+    def __or__(self, other): return self._binary(other, operator.or_)
+    def __xor__(self, other): return self._binary(other, operator.xor)
+    def __lshift__(self, other): return self._binary(other, operator.lshift)
+    def __rshift__(self, other): return self._binary(other, operator.rshift)
+    def __invert__(self): return ArithmeticTile(~self.ma)
+    __hash__ = None
 
     def __getattr__(self, name):
         return getattr(self.ma, name)

@@ -256,6 +256,53 @@ def elementwise_cases():
     ]
 
 
+def operator_cases():
+    """``(name, fn, input arrays, group shape)`` of the vectors under
+    ``tests/golden`` that pin the rest of the reference's tile operator table
+    (python/hckernel/kernel_api.py:157-176) and its masked store (:338-340):
+    floor division, remainder and division with zero divisors (those elements
+    stay unwritten), ``**`` with results that are not finite (likewise),
+    comparisons used as 0/1 factors, and integer tiles.  Every case runs on the
+    reference simulator; outputs start as -77 so that unwritten elements show.
+
+    Not in the list because the reference simulator itself fails on them
+    (``AssertionError`` from its mask helper when numpy.ma returns ``nomask``,
+    ``TypeError`` for ``~``): a comparison or ``& | ^ << >>`` stored directly,
+    ``tile ** tile`` and integer ``**``."""
+    rng = np.random.default_rng(12)
+
+    def floats(shape, dtype):
+        a = rng.standard_normal(shape).astype(dtype) * 4
+        b = np.round(rng.standard_normal(shape) * 1.5).astype(dtype)  # whole numbers, many zeros
+        a[0, :3] = [0.0, -0.0, 5.0]
+        b[0, :3] = [0.0, 0.0, -0.0]
+        return a, b
+
+    def ints(shape, dtype):
+        a = rng.integers(-50, 50, shape).astype(dtype)
+        b = rng.integers(-4, 5, shape).astype(dtype)  # one in nine is zero
+        return a, b
+
+    af, bf = floats((37, 53), "float32")
+    ad, bd = floats((20, 33), "float64")
+    ai, bi = ints((41, 29), "int32")
+    al, bl = ints((18, 70), "int64")
+    return [
+        ("ops_floordiv_f32", lambda a, b: a // b, (af, bf), (8, 16)),
+        ("ops_mod_f32", lambda a, b: a % b, (af, bf), (8, 16)),
+        ("ops_div_zero_f32", lambda a, b: a / b, (af, bf), (8, 16)),
+        ("ops_floordiv_mod_f64", lambda a, b: (a // b) * b + a % b, (ad, bd), (4, 8)),
+        ("ops_pow_f32", lambda a, b: a ** 2.5 + b, (af, bf), (8, 16)),
+        ("ops_compare_f32", lambda a, b: (a < b) * a + (a >= b) * b, (af, bf), (8, 16)),
+        ("ops_equal_f64", lambda a, b: (a == b) * 3.0 + (a != b) * a - (a > b) * (a <= 0.5),
+         (np.round(ad), bd), (4, 8)),
+        ("ops_arith_i32", lambda a, b: a * 3 - b + a // b, (ai, bi), (8, 8)),
+        ("ops_mod_abs_i32", lambda a, b: a % b - abs(-a), (ai, bi), (8, 8)),
+        ("ops_compare_i32", lambda a, b: (a <= b) * a + (a > b) * b, (ai, bi), (8, 8)),
+        ("ops_arith_i64", lambda a, b: a * a - b // 7 + a % 5, (al, bl), (4, 32)),
+    ]
+
+
 def rowwise(fn, inputs, out, group_rows: int = 8) -> None:
     """A body that loads ``group_rows`` whole rows per input, computes ``fn`` of
     them - which may reduce along the rows and use the reduced values again, as

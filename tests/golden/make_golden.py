@@ -453,6 +453,19 @@ def main():
         np.testing.assert_allclose(r, fn(*inputs), rtol=3e-7 if dtype == "float32" else 0)
         out[name] = r
 
+    # 6b. The rest of the tile operator table and the masked store: elements the
+    #     arithmetic masks (zero divisors, results that are not finite) stay -77.
+    for name, fn, inputs, group in oracle.operator_cases():
+        shape, dtype = inputs[0].shape, inputs[0].dtype
+        r = np.full(shape, -77, dtype)
+        with np.errstate(all="ignore"):
+            ref_map(fn, len(inputs), 2, group)(*inputs, r)
+        o = np.full(shape, -77, dtype)
+        oracle.elementwise(fn, list(inputs), o, group)
+        same(name, r, o)
+        assert (r == -77).any() or "compare" in name or "equal" in name or "i64" in name, name
+        out[name] = r
+
     # 7. Row bodies: reductions along the rows used again in the same expression.
     for name, fn, count, shape, dtype, group_rows in oracle.rowwise_cases():
         inputs = oracle.make_elementwise_inputs(count, shape, dtype, seed=8)

@@ -19,6 +19,7 @@ from pathlib import Path
 import pytest
 
 from hc_b200 import capi
+from hc_b200.hckernel import precompiled
 
 REPO = Path(__file__).resolve().parent.parent
 NATIVE = REPO / "hc_b200" / "_native"
@@ -213,14 +214,25 @@ def test_images_are_sm100a_cubins_holding_every_listed_kernel():
                 "hc_mapped_gemm_": {f"{kernel}{t}_{sy}x{sx}" for t in ("f32", "f64")
                                     for sy in (8, 16, 32, 64) for sx in (8, 16, 32, 64)}
                 | {f"{kernel}f32_128x32", f"{kernel}f32_128x64"},
-                "hc_map_elements_": {f"{kernel}{tv}_n{n}{i}" for tv in ("f32_v4", "f32_v1", "f64_v2",
-                                                                        "f64_v1")
-                                     for n in (1, 2, 3, 4) for i in ("", "i")},
+                # Basic kernels for floats; extended ones (suffix x: the whole operator
+                # table, validity of every element) for floats and integers.
+                "hc_map_elements_": {f"{kernel}{tv}_n{n}{i}{x}"
+                                     for tv, forms in (("f32_v4", ("", "x")), ("f32_v1", ("", "x")),
+                                                       ("f64_v2", ("", "x")), ("f64_v1", ("", "x")),
+                                                       ("i32_v4", ("x",)), ("i32_v1", ("x",)),
+                                                       ("i64_v2", ("x",)), ("i64_v1", ("x",)))
+                                     for n in (1, 2, 3, 4) for i in ("", "i") for x in forms},
                 "hc_row_program_": {f"{kernel}{tv}_n{n}" for tv in ("f32_v4", "f32_v1", "f64_v2",
                                                                     "f64_v1")
                                     for n in (1, 2)}
                 | {f"{kernel}held_{tv}_p{held}_t{threads}_n{n}" for tv in ("f32_v4", "f64_v2")
                    for held, threads in ((8, 64), (8, 96), (8, 128), (4, 256)) for n in (1, 2)},
+                # One kernel per body compiled ahead of time and kernel form.
+                "hc_row_fused_": {f"{kernel}{body}_{form}" for body, _, _ in precompiled.ROW_BODIES
+                                  for form in ("f32_held_t64", "f32_held_t128", "f32_v4", "f32_v1",
+                                               "f64_v2", "f64_v1")},
+                "hc_map_fused_": {f"{kernel}{body}_{form}" for body, _, _ in precompiled.MAP_BODIES
+                                  for form in ("f32_v4", "f32_v1", "f64_v2", "f64_v1")},
             }[kernel]
             assert family == expected
             for member in family:

@@ -24,11 +24,48 @@ class FakeTensor:
 F = FakeTensor
 
 
-def run_program(code, consts, inputs, dtype, shape=None):
-    """The machine of map_elements.cu, one NumPy operation per instruction."""
+def _divides(a, b):
+    """Where numpy.ma does not mask a / b, a // b, a % b (its _DomainSafeDivide)."""
+    a, b = np.broadcast_arrays(np.asarray(a), np.asarray(b))
+    if a.dtype.kind == "f":
+        return ~(np.abs(a.astype(np.float64)) * np.finfo(np.float64).tiny
+                 >= np.abs(b.astype(np.float64)))
+    return b != 0
+
+
+def run_program(code, consts, inputs, dtype, shape=None, valid_out=None):
+    """The machine of map_elements.cu, one NumPy operation per instruction.
+    ``valid_out`` (a list) receives the validity of the result's elements: what
+    the kernel stores and what it leaves untouched."""
     dtype = np.dtype(dtype).type
     shape = inputs[0].shape if shape is None else shape
     acc, temps, scalars, one = None, [None, None, None], [None] * 4, None
+    ok, temps_ok = np.ones(shape, bool), [None, None, None]
+    truth = lambda cond: cond.astype(dtype)  # noqa: E731
+    if np.dtype(dtype).kind == "f":
+        bits = {ew.AND: lambda a, b: truth((a != 0) & (b != 0)),
+                ew.OR: lambda a, b: truth((a != 0) | (b != 0)),
+                ew.XOR: lambda a, b: truth((a != 0) ^ (b != 0))}
+    else:
+        bits = {ew.AND: np.bitwise_and, ew.OR: np.bitwise_or, ew.XOR: np.bitwise_xor}
+    extended = {
+        ew.FLOORDIV: lambda a, b: (np.floor_divide(a, b), _divides(a, b)),
+        ew.RFLOORDIV: lambda a, b: (np.floor_divide(b, a), _divides(b, a)),
+        ew.MOD: lambda a, b: (np.remainder(a, b), _divides(a, b)),
+        ew.RMOD: lambda a, b: (np.remainder(b, a), _divides(b, a)),
+        ew.POW: lambda a, b: (np.power(a, b), None),
+        ew.RPOW: lambda a, b: (np.power(b, a), None),
+        ew.LT: lambda a, b: (truth(a < b), True), ew.LE: lambda a, b: (truth(a <= b), True),
+        ew.EQ: lambda a, b: (truth(a == b), True), ew.NE: lambda a, b: (truth(a != b), True),
+        ew.GE: lambda a, b: (truth(a >= b), True), ew.GT: lambda a, b: (truth(a > b), True),
+        ew.AND: lambda a, b: (bits[ew.AND](a, b), True),
+        ew.OR: lambda a, b: (bits[ew.OR](a, b), True),
+        ew.XOR: lambda a, b: (bits[ew.XOR](a, b), True),
+        ew.SHL: lambda a, b: (np.left_shift(a, b), True),
+        ew.SHR: lambda a, b: (np.right_shift(a, b), True),
+        ew.RSHL: lambda a, b: (np.left_shift(b, a), True),
+        ew.RSHR: lambda a, b: (np.right_shift(b, a), True),
+    }
     with np.errstate(all="ignore"):
         for ins in code:
             op, src = ins & 0xFF, ins >> 8
@@ -53,7 +90,10 @@ def run_program(code, consts, inputs, dtype, shape=None):
                 scalars[src] = reduce(acc, axis=1, keepdims=True).astype(dtype)
                 acc, temps = None, [None, None, None]
                 continue
-            if op <= ew.MIN:
+            v_ok = True
+            if op <= ew.MIN or ew.FLOORDIV <= op <= ew.RSHR:
+                if 4 <= src < 8:
+                    v_ok = temps_ok[src - 4]
                 if src >= ew.SRC_SCALAR:
                     v = np.broadcast_to(scalars[src - ew.SRC_SCALAR], shape)
                 elif src >= ew.SRC_ROW:  # the element's own row / column index
@@ -64,21 +104,32 @@ def run_program(code, consts, inputs, dtype, shape=None):
                          else dtype(consts[src - 8]))
             if op == ew.LOAD:
                 acc = v if isinstance(v, np.ndarray) else np.full(shape, v, dtype)
-            elif op == ew.ADD: acc = acc + v
-            elif op == ew.SUB: acc = acc - v
-            elif op == ew.RSUB: acc = v - acc
-            elif op == ew.MUL: acc = acc * v
-            elif op == ew.DIV: acc = acc / v
-            elif op == ew.RDIV: acc = v / acc
-            elif op == ew.MAX: acc = np.maximum(acc, v)
-            elif op == ew.MIN: acc = np.minimum(acc, v)
+                ok = np.ones(shape, bool) & v_ok
+            elif op in extended:
+                ok = ok & v_ok
+                acc, fine = extended[op](acc, v)
+                acc = acc.astype(dtype)
+                ok = ok & (np.isfinite(acc) if fine is None else fine)
+            elif op == ew.INV:
+                acc = truth(acc == 0) if np.dtype(dtype).kind == "f" else ~acc
+            elif op == ew.ADD: acc, ok = acc + v, ok & v_ok
+            elif op == ew.SUB: acc, ok = acc - v, ok & v_ok
+            elif op == ew.RSUB: acc, ok = v - acc, ok & v_ok
+            elif op == ew.MUL: acc, ok = acc * v, ok & v_ok
+            elif op == ew.DIV: acc, ok = (acc / v).astype(dtype), ok & v_ok & _divides(acc, v)
+            elif op == ew.RDIV: acc, ok = (v / acc).astype(dtype), ok & v_ok & _divides(v, acc)
+            elif op == ew.MAX: acc, ok = np.maximum(acc, v), ok & v_ok
+            elif op == ew.MIN: acc, ok = np.minimum(acc, v), ok & v_ok
             elif op == ew.NEG: acc = -acc
             elif op == ew.ABS: acc = np.abs(acc)
             elif op == ew.EXP: acc = np.exp(acc)
             elif op == ew.SQRT: acc = np.sqrt(acc)
             elif op == ew.LOG: acc = np.log(acc)
-            else: temps[op - ew.SAVE0] = acc
+            else:
+                temps[op - ew.SAVE0], temps_ok[op - ew.SAVE0] = acc, ok
             assert acc.dtype == dtype
+    if valid_out is not None:
+        valid_out.append(ok)
     return acc
 
 
@@ -165,9 +216,9 @@ def test_bodies_outside_the_element_wise_family():
     target = dict(backend="nvvm", device="cuda:0")
     with pytest.raises(UnsupportedKernel, match="np.tanh"):
         make_elementwise(np.tanh, 1, 2, (4, 16)).plan_for((F((8, 32)), F((8, 32))))
-    with pytest.raises(UnsupportedKernel, match="float32 or float64"):
+    with pytest.raises(UnsupportedKernel, match="int32 or int64, not int16"):
         make_elementwise(lambda t: t + 1, 1, 2, (4, 16)).plan_for(
-            (F((8, 32), "int32"), F((8, 32), "int32")))
+            (F((8, 32), "int16"), F((8, 32), "int16")))
 
     @kernel(work_shape=(W, H), group_shape=(4, 16), **target)
     def shifted(gr: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
@@ -294,3 +345,75 @@ def test_work_item_bodies_with_reads_and_their_limits():
 
     with pytest.raises(UnsupportedKernel, match="local_id"):
         uses_local_id.plan_for((F((6, 9)), F((6, 9))))
+
+
+OPERATOR_CASES = oracle.operator_cases()
+
+
+@pytest.mark.parametrize("case", OPERATOR_CASES, ids=lambda c: c[0])
+def test_operator_table_oracle_matches_the_reference_simulator(golden, case):
+    """// % / with zero divisors, ** with results that are not finite, comparisons
+    as 0/1 factors, integer tiles: the oracle against the outputs of the
+    reference simulator, bit for bit, unwritten elements (-77) included."""
+    name, fn, inputs, group = case
+    out = np.full(inputs[0].shape, -77, inputs[0].dtype)
+    oracle.elementwise(fn, list(inputs), out, group)
+    assert np.array_equal(out, golden[name])
+
+
+@pytest.mark.parametrize("case", OPERATOR_CASES, ids=lambda c: c[0])
+def test_operator_table_translates_to_an_equivalent_program(golden, case):
+    """The recorded body as a program, run one NumPy operation per instruction:
+    the elements it marks valid are the ones the reference wrote, with the
+    reference's values (bit for bit for everything but **, whose float32 power
+    the reference computes through float64)."""
+    name, fn, inputs, group = case
+    dtype = inputs[0].dtype.name
+    k = make_elementwise(fn, len(inputs), 2, group)
+    plan = k.plan_for(tuple(F(a.shape, dtype) for a in inputs) + (F(inputs[0].shape, dtype),))
+    assert plan.family == "map_elements"
+    valid = []
+    with np.errstate(all="ignore"):
+        got = run_program(plan.roles["code"], plan.roles["consts"],
+                          [inputs[i] for i in plan.roles["inputs"]], dtype, valid_out=valid)
+    out = np.where(valid[0], got, np.asarray(-77, got.dtype))
+    want = golden[name]
+    if "pow" in name:
+        assert np.array_equal(out == -77, want == -77)
+        np.testing.assert_allclose(out, want, rtol=1e-6)
+    else:
+        assert np.array_equal(out, want)
+
+
+def test_operator_table_refusals_follow_numpy():
+    shape = (8, 32)
+    ints = (F(shape, "int32"), F(shape, "int32"), F(shape, "int32"))
+    floats = (F(shape), F(shape), F(shape))
+    two = lambda fn: make_elementwise(fn, 2, 2, (4, 16))  # noqa: E731
+    with pytest.raises(UnsupportedKernel, match="floating-point values"):
+        two(lambda a, b: a / b).plan_for(ints)
+    with pytest.raises(UnsupportedKernel, match="floating-point values"):
+        two(lambda a, b: a * 2.5 + b).plan_for(ints)
+    with pytest.raises(UnsupportedKernel, match="constant exponents"):
+        two(lambda a, b: a ** b).plan_for(ints)
+    with pytest.raises(ValueError, match="negative integer powers"):
+        two(lambda a, b: a ** -1 + b).plan_for(ints)
+    with pytest.raises(TypeError, match="shifts are not supported"):
+        two(lambda a, b: a << b).plan_for(floats)
+    with pytest.raises(TypeError, match="only for truth values"):
+        two(lambda a, b: a & b).plan_for(floats)
+    with pytest.raises(ValueError, match="truth value of a tile"):
+        two(lambda a, b: (not a) + b).plan_for(floats)
+    # What NumPy allows: logical operators on the results of comparisons, stored
+    # as 0 / 1; shifts and bitwise operators on integer tiles.
+    plan = two(lambda a, b: ((a < b) & (b > 0.0)) | ~(a >= 1.0)).plan_for(floats)
+    rng = np.random.default_rng(4)
+    a, b = rng.standard_normal(shape).astype("float32"), rng.standard_normal(shape).astype("float32")
+    got = run_program(plan.roles["code"], plan.roles["consts"],
+                      [(a, b)[i] for i in plan.roles["inputs"]], "float32")
+    assert np.array_equal(got, (((a < b) & (b > 0)) | ~(a >= 1)).astype("float32"))
+    plan = two(lambda a, b: ((a << 3) ^ (b >> 1)) & ~a | (a % 7 == 3)).plan_for(ints)
+    a, b = rng.integers(-99, 99, shape, dtype="int32"), rng.integers(-99, 99, shape, dtype="int32")
+    got = run_program(plan.roles["code"], plan.roles["consts"],
+                      [(a, b)[i] for i in plan.roles["inputs"]], "int32")
+    assert np.array_equal(got, ((a << 3) ^ (b >> 1)) & ~a | (a % 7 == 3))

@@ -219,3 +219,97 @@ def test_work_item_kernel_with_reads():
     rows = np.arange(37, dtype=np.float32)[:, None]
     cols = np.arange(130, dtype=np.float32)[None, :]
     assert np.array_equal(d_out.cpu().numpy(), (a - b) * (rows + np.float32(1)) + cols)
+
+
+OPERATOR_CASES = oracle.operator_cases()
+
+
+@pytest.mark.parametrize("fused", [0, 1], ids=["precompiled-or-interpreted", "interpreted"])
+@pytest.mark.parametrize("case", OPERATOR_CASES, ids=lambda c: c[0])
+def test_operator_table_and_masked_store_match_the_reference(golden, case, fused):
+    """The rest of the reference's tile operator table (// % ** comparisons,
+    integer tiles) and its masked store: elements whose divisor is zero, or whose
+    power is not finite, keep what the output held (-77 here), everything else is
+    bit for bit the reference simulator's output - except ``**``, where the
+    reference computes a float32 power through float64 and powf is within a few
+    ulp (1e-6 relative)."""
+    from hc_b200.hckernel.kernel import get_context
+
+    name, fn, inputs, group = case
+    k = make_elementwise(fn, len(inputs), 2, group)
+    d_in = [torch.from_numpy(a).cuda() for a in inputs]
+    d_out = torch.full(inputs[0].shape, -77, dtype=d_in[0].dtype, device="cuda")
+    ctx = get_context("cuda:0")
+    ctx.set_option("fused", fused)
+    try:
+        k(*d_in, d_out)
+    finally:
+        ctx.set_option("fused", 0)
+    torch.cuda.synchronize()
+    got, want = d_out.cpu().numpy(), golden[name]
+    if "pow" in name:
+        assert np.array_equal(got == -77, want == -77)
+        np.testing.assert_allclose(got, want, rtol=1e-6)
+    else:
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", ["int32", "int64", "float32", "float64"])
+def test_every_operator_against_numpy(dtype):
+    """Each operator of the table on its own, on ragged and pitched arrays (both
+    the 16-byte packet kernels and the single-element ones), against NumPy on the
+    same arrays; zero divisors keep the output's old value."""
+    rng = np.random.default_rng(31)
+    integer = dtype.startswith("int")
+    for shape, pitch in (((33, 64), 64), ((17, 101), 104), ((5, 7), 7)):
+        if integer:
+            a = rng.integers(-40, 40, shape).astype(dtype)
+            b = rng.integers(-5, 6, shape).astype(dtype)
+        else:
+            a = (rng.standard_normal(shape) * 3).astype(dtype)
+            b = np.round(rng.standard_normal(shape) * 2).astype(dtype)
+        bodies = {
+            "floordiv": (lambda s, t: s // t, True), "mod": (lambda s, t: s % t, True),
+            "lt": (lambda s, t: (s < t) * 1, False), "le": (lambda s, t: (s <= t) * 1, False),
+            "eq": (lambda s, t: (s == t) * 1, False), "ne": (lambda s, t: (s != t) * 1, False),
+            "ge": (lambda s, t: (s >= t) * 1, False), "gt": (lambda s, t: (s > t) * 1, False),
+            "logic": (lambda s, t: ((s < t) & (t > 0)) | ((s > 1) ^ (t < 1)), False),
+            "not": (lambda s, t: ~(s < t) * s, False),
+            "neg_abs": (lambda s, t: abs(-s) - t, False),
+            "max_min": (lambda s, t: np.maximum(s, t) - np.minimum(s, t), False),
+        }
+        if integer:
+            bodies.update({
+                "bits": (lambda s, t: (s & t) | (s ^ 21), False),
+                "shifts": (lambda s, t: (s << 3) + (s >> 2) + (t << 1), False),
+                "inv": (lambda s, t: ~s - t, False),
+                "pow3": (lambda s, t: s ** 3 + t, False),
+                "rfloordiv": (lambda s, t: 1000 // t, True),
+                "rmod": (lambda s, t: 1000 % t, True),
+            })
+        else:
+            bodies.update({
+                "div": (lambda s, t: s / t, True),
+                "pow": (lambda s, t: np.abs(s) ** 1.5 + t, False),
+                "rdiv": (lambda s, t: 2.0 / t, True),
+            })
+        for name, (fn, divides) in bodies.items():
+            k = make_elementwise(fn, 2, 2, (4, 16))
+            store = torch.full((3, shape[0], pitch), -77, dtype=torch.from_numpy(a).dtype,
+                               device="cuda")
+            d_a, d_b, d_out = (store[i, :, : shape[1]] for i in range(3))
+            d_a.copy_(torch.from_numpy(a))
+            d_b.copy_(torch.from_numpy(b))
+            k(d_a, d_b, d_out)
+            torch.cuda.synchronize()
+            got = d_out.cpu().numpy()
+            with np.errstate(all="ignore"):
+                want = np.asarray(fn(a, b)).astype(dtype)
+            if divides:
+                want = np.where(b == 0, np.asarray(-77, dtype), want)
+            if name == "pow":
+                np.testing.assert_allclose(got, want, rtol=2e-6 if dtype == "float32" else 1e-14)
+            else:
+                assert np.array_equal(got, want), (name, shape, dtype)
+            if pitch > shape[1]:
+                assert (store[2, :, shape[1]:] == -77).all()
