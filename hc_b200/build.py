@@ -33,6 +33,7 @@ KERNEL_SOURCES = [
     "copy2d",
     "map_elements",
     "row_program",
+    "work_items",
     "map_fused",
     "row_fused",
     "softmax_rows",
@@ -161,7 +162,8 @@ def build_libs(verbose=False, force=False):
     srcs = [CSRC / "launch" / "kernels_api.cpp", host_src, CSRC / "launch" / "context.hpp",
             INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h",
-            CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h", loader,
+            CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h",
+            CSRC / "kernels" / "items_params.h", loader,
             *cubins]
     static_src = CSRC / "launch" / "w8a16_static.cu"
     srcs.append(static_src)

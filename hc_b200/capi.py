@@ -69,6 +69,33 @@ class HcMapProgram(C.Structure):
     ]
 
 
+class HcItemProgram(C.Structure):
+    """include/hc_b200_kernels.h: the arrays and the program of hcWorkItems."""
+
+    _fields_ = [
+        ("inputs", _vp * 4),
+        ("inPitch", _ll * 4),
+        ("inRow", C.c_int * 4),
+        ("inCol", C.c_int * 4),
+        ("out", _vp),
+        ("outPitch", _ll),
+        ("rows", _ll),
+        ("cols", _ll),
+        ("groupRows", C.c_int),
+        ("groupCols", C.c_int),
+        ("nInputs", C.c_int),
+        ("nInstr", C.c_int),
+        ("code", C.c_uint * 48),
+        ("consts", C.c_double * 8),
+        ("guardLo", (_ll * 2) * 2),
+        ("guardHi", (_ll * 2) * 2),
+        ("tileScale", (C.c_int * 2) * 4),
+        ("tileOffset", (C.c_int * 2) * 4),
+        ("tileMod", (C.c_int * 2) * 4),
+        ("tileFill", C.c_double),
+    ]
+
+
 # name -> (restype, argtypes), exactly as declared in include/offload_api.h
 OL_PROTOTYPES = {
     "olCreateDevice": (_vp, [C.c_char_p, OlErrorCallback, _vp]),
@@ -146,6 +173,7 @@ KERNELS_PROTOTYPES = {
     ),
     "hcMapElements": (C.c_int, [_vp, C.POINTER(HcMapProgram), C.c_int]),
     "hcRowProgram": (C.c_int, [_vp, C.POINTER(HcMapProgram), C.c_int]),
+    "hcWorkItems": (C.c_int, [_vp, C.POINTER(HcItemProgram), C.c_int]),
     "hcMappedGemm": (
         C.c_int,
         [_vp, C.POINTER(HcMappedOperand), C.POINTER(HcMappedOperand),
@@ -323,6 +351,10 @@ class Context:
     def map_elements(self, program, dtype=HC_F32):
         """``program``: :class:`HcMapProgram`."""
         self._check(self.lib.hcMapElements(self.handle, C.byref(program), dtype), "hcMapElements")
+
+    def work_items(self, program, dtype=HC_F32):
+        """``program``: :class:`HcItemProgram`."""
+        self._check(self.lib.hcWorkItems(self.handle, C.byref(program), dtype), "hcWorkItems")
 
     def row_program(self, program, dtype=HC_F32):
         """``program``: :class:`HcMapProgram` with row reductions."""

@@ -16,6 +16,8 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
+#include <array>
 #include <charconv>
 #include <memory>
 #include <string>
@@ -329,6 +331,74 @@ void mapElements(Context &ctx, py::handle inputs, py::handle out, const std::vec
   runProgram(ctx, inputs, out, code, consts, false);
 }
 
+// Work-item program (hcWorkItems): `inputs` arrays of the shape of `out`, each
+// read at the work-item's global id plus `offsets[k]` = (row, column); `group`
+// the work-group shape (rows, columns); `guards` one (lo row, hi row, lo column,
+// hi column) per phase; `tiles` the reads of the group's tile as (row scale, row
+// offset, row wrap, column scale, column offset, column wrap).
+void workItems(Context &ctx, py::handle inputs, const std::vector<std::pair<int, int>> &offsets,
+               py::handle out, std::pair<int, int> group, const std::vector<unsigned> &code,
+               const std::vector<double> &consts,
+               const std::vector<std::array<long long, 4>> &guards,
+               const std::vector<std::array<int, 6>> &tiles, double tileFill) {
+  auto ins = py::cast<py::list>(inputs);
+  if (ins.size() > 4 || offsets.size() != ins.size())
+    throw py::value_error("work_items: at most 4 input arrays, one offset pair each");
+  if (code.empty() || code.size() > 48 || consts.size() > 8 || guards.empty() ||
+      guards.size() > 2 || tiles.size() > 4)
+    throw py::value_error("work_items: 1..48 instructions, at most 8 constants, 1..2 guards and "
+                          "at most 4 tile reads");
+  ArrayArg o;
+  try {
+    o = hc::arrayFromPython(out);
+  } catch (const std::exception &e) {
+    throw py::type_error(std::string("out: ") + e.what());
+  }
+  const int rank = o.rank();
+  if (rank != 1 && rank != 2)
+    throw py::value_error("work_items: vectors or matrices expected");
+  ArrayArg O = deviceArray(ctx, out, "out", rank);
+  HcItemProgram p{};
+  auto rowPitch = [&](const ArrayArg &a) { return rank == 2 ? pitch(a) : a.shape[0]; };
+  p.out = O.data;
+  p.outPitch = rowPitch(O);
+  p.rows = rank == 2 ? O.shape[0] : 1;
+  p.cols = O.shape[rank - 1];
+  p.groupRows = group.first;
+  p.groupCols = group.second;
+  p.nInputs = int(ins.size());
+  for (int k = 0; k < p.nInputs; ++k) {
+    const std::string name = "input " + std::to_string(k);
+    ArrayArg a = deviceArray(ctx, ins[k], name.c_str(), rank);
+    sameKind(a, O, name.c_str(), "out");
+    sameShape(a, O, name.c_str(), "out");
+    p.in[k] = a.data;
+    p.inPitch[k] = rowPitch(a);
+    p.inRow[k] = offsets[k].first;
+    p.inCol[k] = offsets[k].second;
+  }
+  p.nInstr = int(code.size());
+  std::copy(code.begin(), code.end(), p.code);
+  std::copy(consts.begin(), consts.end(), p.consts);
+  for (size_t ph = 0; ph < 2; ++ph) {
+    const auto &g = guards[std::min(ph, guards.size() - 1)];
+    p.guardLo[ph][0] = g[0];
+    p.guardHi[ph][0] = g[1];
+    p.guardLo[ph][1] = g[2];
+    p.guardHi[ph][1] = g[3];
+  }
+  for (size_t k = 0; k < tiles.size(); ++k) {
+    p.tileScale[k][0] = tiles[k][0];
+    p.tileOffset[k][0] = tiles[k][1];
+    p.tileMod[k][0] = tiles[k][2];
+    p.tileScale[k][1] = tiles[k][3];
+    p.tileOffset[k][1] = tiles[k][4];
+    p.tileMod[k][1] = tiles[k][5];
+  }
+  p.tileFill = tileFill;
+  ctx.check(hcWorkItems(ctx.get(), &p, floatDType(O, "out")), "work_items");
+}
+
 // Row program (hcRowProgram): like map_elements, with reductions along the rows.
 void rowProgram(Context &ctx, py::handle inputs, py::handle out, const std::vector<unsigned> &code,
                 const std::vector<double> &consts) {
@@ -512,6 +582,9 @@ PYBIND11_MODULE(_dispatcher, m) {
         py::arg("out"));
   m.def("map_elements", &mapElements, py::arg("ctx"), py::arg("inputs"), py::arg("out"),
         py::arg("code"), py::arg("consts"));
+  m.def("work_items", &workItems, py::arg("ctx"), py::arg("inputs"), py::arg("offsets"),
+        py::arg("out"), py::arg("group"), py::arg("code"), py::arg("consts"), py::arg("guards"),
+        py::arg("tiles"), py::arg("tile_fill") = 0.0);
   m.def("row_program", &rowProgram, py::arg("ctx"), py::arg("inputs"), py::arg("out"),
         py::arg("code"), py::arg("consts"));
   m.def("mapped_gemm", &mappedGemm, py::arg("ctx"), py::arg("x"), py::arg("x_tables"),

@@ -10,6 +10,7 @@
 #include "context.hpp"
 
 #include "../kernels/fused_programs.h"
+#include "../kernels/items_params.h"
 #include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
 
@@ -60,6 +61,8 @@ const KernelEntry kKernelTable[] = {
     // hc_row_fused_<body>_{f32_held_t64,f32_held_t128,f32_v4,f32_v1,f64_v2,f64_v1} and
     // hc_map_fused_<body>_{f32_v4,f32_v1,f64_v2,f64_v1}: the bodies of
     // fused_programs.h compiled ahead of time.
+    {"hc_work_items_f32", "work_items"},
+    {"hc_work_items_f64", "work_items"},
     {"hc_row_fused_", "row_fused"},
     {"hc_map_fused_", "map_fused"},
     {"hc_softmax_rows_f32_w1", "softmax_rows"},
@@ -719,6 +722,128 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
                   dtype == HC_F32 ? "f32" : "f64", wide ? perPacket : 1, p.nInputs);
   // One warp per row, eight rows per CTA.
   return c->launch(name, size_t(ceilDiv(p.rows, 8)), 1, 1, 256, args, 1, 0);
+}
+
+// ---- work-item programs ---------------------------------------------------------------
+static_assert(sizeof(HcItemProgram) == sizeof(HcItemProgramDev) &&
+                  offsetof(HcItemProgram, out) == offsetof(HcItemProgramDev, out) &&
+                  offsetof(HcItemProgram, groupRows) == offsetof(HcItemProgramDev, groupRows) &&
+                  offsetof(HcItemProgram, code) == offsetof(HcItemProgramDev, code) &&
+                  offsetof(HcItemProgram, guardLo) == offsetof(HcItemProgramDev, guardLo) &&
+                  offsetof(HcItemProgram, tileScale) == offsetof(HcItemProgramDev, tileScale) &&
+                  offsetof(HcItemProgram, tileFill) == offsetof(HcItemProgramDev, tileFill),
+              "public work-item program and kernel parameter block differ");
+
+int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype) {
+  if (!c)
+    return 1;
+  const char *who = "hcWorkItems";
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return c->fail("%s: unsupported dtype %d", who, dtype);
+  if (!program)
+    return c->fail("%s: null program", who);
+  HcItemProgramDev p;
+  std::memcpy(&p, program, sizeof p);
+  if (p.nInputs < 0 || p.nInputs > HC_MAP_MAX_INPUTS || p.nInstr < 1 ||
+      p.nInstr > HC_ITEM_MAX_INSTR)
+    return c->fail("%s: %d inputs, %d instructions (at most %d and 1..%d)", who, p.nInputs,
+                   p.nInstr, HC_MAP_MAX_INPUTS, HC_ITEM_MAX_INSTR);
+  if (p.rows < 0 || p.cols < 0 || p.outPitch < p.cols)
+    return c->fail("%s: invalid shape %lld x %lld", who, (long long)p.rows, (long long)p.cols);
+  if (p.groupRows < 1 || p.groupCols < 1 || (long long)p.groupRows * p.groupCols > 1024)
+    return c->fail("%s: a work-group of %d x %d work-items (1..1024 in all)", who, p.groupRows,
+                   p.groupCols);
+  // Guards never reach beyond the arrays.
+  for (int ph = 0; ph < HC_ITEM_MAX_PHASES; ++ph) {
+    p.guardLo[ph][0] = std::max<long long>(p.guardLo[ph][0], 0);
+    p.guardLo[ph][1] = std::max<long long>(p.guardLo[ph][1], 0);
+    p.guardHi[ph][0] = std::min<long long>(p.guardHi[ph][0], p.rows);
+    p.guardHi[ph][1] = std::min<long long>(p.guardHi[ph][1], p.cols);
+  }
+  int phase = 0;
+  bool loaded = false, stores = false;
+  bool saved[3] = {false, false, false};
+  for (int pc = 0; pc < p.nInstr; ++pc) {
+    const uint32_t op = p.code[pc] & 0xffu, src = (p.code[pc] >> 8) & 0xffu;
+    if (op == HC_ITEM_BARRIER) {
+      if (++phase >= HC_ITEM_MAX_PHASES)
+        return c->fail("%s: more than one barrier (instruction %d)", who, pc);
+      loaded = false;
+      continue;
+    }
+    if (op == HC_ITEM_STORE_TILE || op == HC_ITEM_STORE_OUT) {
+      if (!loaded)
+        return c->fail("%s: instruction %d stores an accumulator that holds nothing", who, pc);
+      stores = stores || op == HC_ITEM_STORE_OUT;
+      continue;
+    }
+    if (op >= HC_MAP_OP_COUNT || op == HC_MAP_RSUM || op == HC_MAP_RMAX || op == HC_MAP_SET ||
+        (op >= HC_MAP_SHL && op <= HC_MAP_RSHR))
+      return c->fail("%s: unknown operation %u at instruction %d", who, op, pc);
+    if (op != HC_MAP_LOAD && !loaded)
+      return c->fail("%s: instruction %d uses an accumulator that holds nothing", who, pc);
+    if (hcMapIsBinary(op)) {
+      const bool input = src < uint32_t(p.nInputs);
+      const bool temp =
+          src >= HC_MAP_SRC_TEMP && src < HC_MAP_SRC_TEMP + 3 && saved[src - HC_MAP_SRC_TEMP];
+      const bool constant =
+          src >= HC_MAP_SRC_CONST && src < HC_MAP_SRC_CONST + uint32_t(HC_MAP_MAX_CONSTS);
+      const bool index = src >= HC_MAP_SRC_ROW && src <= HC_ITEM_SRC_LOCAL_COL;
+      const bool tile =
+          src >= HC_ITEM_SRC_TILE && src < HC_ITEM_SRC_TILE + uint32_t(HC_ITEM_MAX_TILE_READS);
+      if (!input && !temp && !constant && !index && !tile)
+        return c->fail("%s: instruction %d reads operand %u, which does not exist or is not "
+                       "written yet",
+                       who, pc, src);
+      if (input) {
+        // Every work-item that passes the phase's guard must find its element.
+        if (!p.in[src])
+          return c->fail("%s: null input %u", who, src);
+        if (p.inPitch[src] < p.cols)
+          return c->fail("%s: pitch of input %u is shorter than a row", who, src);
+        const bool empty = p.guardLo[phase][0] >= p.guardHi[phase][0] ||
+                           p.guardLo[phase][1] >= p.guardHi[phase][1];
+        if (!empty && (p.guardLo[phase][0] + p.inRow[src] < 0 ||
+                       p.guardHi[phase][0] + p.inRow[src] > p.rows ||
+                       p.guardLo[phase][1] + p.inCol[src] < 0 ||
+                       p.guardHi[phase][1] + p.inCol[src] > p.cols))
+          return c->fail("%s: input %u read at offset (%d, %d) leaves the array for work-items "
+                         "that pass the guard of phase %d",
+                         who, src, p.inRow[src], p.inCol[src], phase);
+      }
+      if (tile) {
+        const int k = int(src - HC_ITEM_SRC_TILE);
+        const int extent[2] = {p.groupRows, p.groupCols};
+        for (int a = 0; a < 2; ++a) {
+          if (p.tileMod[k][a] < 0 || p.tileMod[k][a] > extent[a])
+            return c->fail("%s: tile read %d wraps at %d, beyond the group", who, k,
+                           p.tileMod[k][a]);
+          if (p.tileMod[k][a] == 0) {
+            const long long first = p.tileOffset[k][a];
+            const long long last = (long long)p.tileScale[k][a] * (extent[a] - 1) + first;
+            if (std::min(first, last) < 0 || std::max(first, last) >= extent[a])
+              return c->fail("%s: tile read %d leaves the group's tile", who, k);
+          }
+        }
+      }
+    }
+    if (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2)
+      saved[op - HC_MAP_SAVE0] = true;
+    loaded = true;
+  }
+  if (!stores)
+    return c->fail("%s: the program stores nothing", who);
+  if (p.rows == 0 || p.cols == 0)
+    return 0;
+  if (!p.out)
+    return c->fail("%s: null output", who);
+  const long long groups = ceilDiv(p.rows, p.groupRows) * ceilDiv(p.cols, p.groupCols);
+  if (groups > 0x7fffffffLL)
+    return c->fail("%s: %lld work-groups exceed one launch", who, groups);
+  const size_t threads = size_t(p.groupRows) * size_t(p.groupCols);
+  void *args[] = {&p};
+  return c->launch(dtype == HC_F32 ? "hc_work_items_f32" : "hc_work_items_f64", size_t(groups),
+                   1, 1, threads, args, 1, threads * (dtype == HC_F32 ? 4 : 8));
 }
 
 // ---- softmax --------------------------------------------------------------------

@@ -547,10 +547,30 @@ class KernelDispatcher:
                 stand_ins.append(BufferRef(i, name, a.shape, a.dtype, recorder))
             else:
                 stand_ins.append(a)
-        body(recorder, *stand_ins)
-        if recorder.item_stores:
+        from . import kernel_api as _api
+
+        _api._RECORDING.append(recorder)
+        try:
+            body(recorder, *stand_ins)
+        finally:
+            _api._RECORDING.pop()
+        if recorder.item_events:
             if recorder.stores or recorder.atomics or recorder.scatters:
                 raise UnsupportedKernel("kernels that mix work-item stores with tile stores")
+            from . import workitems
+
+            found = workitems.match_item_pairwise(recorder)
+            if found is not None:
+                a, b, out = found
+                return _Plan("pairwise_distance", a=a.index, b=b.index, out=out.index)
+            if workitems.needs_work_items(recorder):
+                program, dst, group2, guards, fill = workitems.match_work_items(recorder, work,
+                                                                                group)
+                return _Plan("work_items", out=dst.index,
+                             inputs=[buffer.index for buffer, _ in program.slots],
+                             offsets=[offsets for _, offsets in program.slots],
+                             group=group2, code=list(program.code), consts=list(program.consts),
+                             guards=guards, tiles=list(program.tile_reads), tile_fill=fill)
             program, dst = match_items(recorder.item_stores, recorder.guards, work)
             return _Plan("map_elements", out=dst.index,
                          inputs=[tile.args[0].index for tile in program.inputs],
@@ -635,6 +655,10 @@ class KernelDispatcher:
         elif plan.family == "map_elements":
             native.map_elements(ctx, [args[i] for i in r["inputs"]], args[r["out"]], r["code"],
                                 r["consts"])
+        elif plan.family == "work_items":
+            native.work_items(ctx, [args[i] for i in r["inputs"]], r["offsets"], args[r["out"]],
+                              r["group"], r["code"], r["consts"], r["guards"], r["tiles"],
+                              r["tile_fill"])
         elif plan.family == "row_program":
             native.row_program(ctx, [args[i] for i in r["inputs"]], args[r["out"]], r["code"],
                                r["consts"])

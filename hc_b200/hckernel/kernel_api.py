@@ -379,19 +379,31 @@ class BufferRef:
             if len(index) != self.ndim or any(not 0 <= i < s for i, s in zip(index, self.shape)):
                 raise IndexError(f"{self.name}{list(index)} is out of range")
             return ElementRef(self, index)
-        axes = self._item_axes(key)
-        if axes is not None:  # `buf[gid]` read inside a work-item function
-            return Tile("item_load", (self,), (), self.dtype, axes=axes)
+        item = self._item_axes(key)
+        if item is not None:  # `buf[gid]`, `buf[i, j + 1]`, `buf[i]` (a row) at work-item level
+            axes, offsets = item
+            if len(axes) > self.ndim:
+                raise IndexError(f"too many indices for {self.name}")
+            attrs = {"axes": axes}
+            if any(offsets):
+                attrs["offsets"] = offsets
+            return Tile("item_load", (self,), self.shape[len(axes):], self.dtype, **attrs)
         return BufferView(self, self._origin(key))
 
     @staticmethod
     def _item_axes(key):
-        """The work axes of ``buf[gid]`` / ``buf[i, j]`` written at work-item
-        level, or None when ``key`` is anything else."""
+        """``(work axes, offsets)`` of ``buf[gid]`` / ``buf[i, j]`` / ``buf[i, j + 1]``
+        written at work-item level - every index the work-item's global id along
+        some axis plus a constant - or None when ``key`` is anything else."""
         keys = key if isinstance(key, tuple) else (key,)
-        if keys and all(isinstance(k, WorkIndex) for k in keys):
-            return tuple(k.axis for k in keys)
-        return None
+        axes, offsets = [], []
+        for k in keys:
+            form = index_form(k)
+            if form is None or form[0] != "global" or form[2] != 1 or form[4]:
+                return None
+            axes.append(form[1])
+            offsets.append(form[3])
+        return (tuple(axes), tuple(offsets)) if keys else None
 
     def __setitem__(self, key, value):
         # `buf[i] += tile` arrives here after ElementRef.__iadd__.
@@ -400,11 +412,16 @@ class BufferRef:
                 raise UnsupportedKernel("element update outside a kernel body")
             self.recorder.atomics.append(value)
             return
-        axes = self._item_axes(key)
-        if axes is not None:  # `buf[gid] = value` inside a work-item function
+        item = self._item_axes(key)
+        if item is not None:  # `buf[gid] = value` inside a work-item function
             if self.recorder is None:
                 raise UnsupportedKernel("element store outside a kernel body")
+            axes, offsets = item
+            if any(offsets):
+                raise UnsupportedKernel(
+                    f"{self.name}[...] = value: a work-item may write its own element only")
             self.recorder.item_stores.append((self, axes, Tile._wrap(value)))
+            self.recorder.item_events.append(("out", self, axes, Tile._wrap(value)))
             return
         raise UnsupportedKernel(f"direct assignment into {self.name}; use group.store")
 
@@ -466,6 +483,51 @@ def _broadcast(a, b):
 
 
 _COMPARISONS = ("lt", "le", "eq", "ne", "ge", "gt")
+
+# The work-group whose body is being recorded (conditions on work-item indices
+# are noted there when an `if` asks for their truth).
+_RECORDING = []
+
+
+def index_form(value):
+    """``(kind, axis, scale, offset, wrap)`` when ``value`` is a work-item index
+    (``kind`` "global" or "local") times a constant plus a constant, optionally
+    modulo a constant - ``lid``, ``gid + 1``, ``n - 1 - lid``, ``(lid + 3) % 8`` -
+    else None."""
+    if isinstance(value, WorkIndex):
+        return (value.kind, value.axis, 1, 0, 0)
+    if not isinstance(value, Tile):
+        return None
+    if value.op == "index":
+        return (value.attrs.get("kind", "global"), value.attrs["axis"], 1, 0, 0)
+
+    def number(node):
+        if isinstance(node, Tile) and node.op == "const" and float(node.args[0]) == int(node.args[0]):
+            return int(node.args[0])
+        return None
+
+    if value.op == "neg":
+        inner = index_form(value.args[0])
+        return inner and not inner[4] and (inner[0], inner[1], -inner[2], -inner[3], 0)
+    if value.op in ("add", "sub", "mul", "mod") and len(value.args) == 2:
+        left, right = value.args
+        a, b = index_form(left), index_form(right)
+        ca, cb = number(left), number(right)
+        if value.op == "add" and a and cb is not None and not a[4]:
+            return (a[0], a[1], a[2], a[3] + cb, 0)
+        if value.op == "add" and b and ca is not None and not b[4]:
+            return (b[0], b[1], b[2], b[3] + ca, 0)
+        if value.op == "sub" and a and cb is not None and not a[4]:
+            return (a[0], a[1], a[2], a[3] - cb, 0)
+        if value.op == "sub" and b and ca is not None and not b[4]:
+            return (b[0], b[1], -b[2], ca - b[3], 0)
+        if value.op == "mul" and a and cb is not None and not a[4]:
+            return (a[0], a[1], a[2] * cb, a[3] * cb, 0)
+        if value.op == "mul" and b and ca is not None and not b[4]:
+            return (b[0], b[1], b[2] * ca, b[3] * ca, 0)
+        if value.op == "mod" and a and cb is not None and cb > 0 and not a[4]:
+            return (a[0], a[1], a[2], a[3], cb)
+    return None
 
 
 class Tile:
@@ -589,6 +651,21 @@ class Tile:
     __hash__ = object.__hash__  # (nodes are compared through key(), never with ==)
 
     def __bool__(self):
+        # A condition on a work-item index (`if gid + 1 < n:`): the recording
+        # takes the branch and notes the range of indices that pass.
+        if self.op in _COMPARISONS and _RECORDING:
+            left, right = self.args
+            for index, other, op in ((index_form(left), right, self.op),
+                                     (index_form(right), left,
+                                      {"lt": "gt", "le": "ge", "gt": "lt", "ge": "le"}.get(self.op))):
+                if (index and op and isinstance(other, Tile) and other.op == "const"
+                        and index[0] == "global" and index[2] in (1, -1) and not index[4]):
+                    _RECORDING[-1].note_guard(index[1], index[2], index[3], op,
+                                              float(other.args[0]))
+                    return True
+            raise UnsupportedKernel(
+                "a condition inside a work-item function must compare the work-item's global "
+                "index (plus a constant) with a number")
         # `not tile`, `if tile:` - NumPy's answer for arrays (the reference's
         # operator.not_ entry fails the same way on a tile of several elements).
         raise ValueError("The truth value of a tile with more than one element is ambiguous")
@@ -705,6 +782,47 @@ class Tile:
         raise UnsupportedKernel(f"np.{func.__name__} on a tile")
 
 
+class GroupTile(Tile):
+    """A tile allocated by the group (``group.zeros`` and friends).  At group
+    level it is a constant tile like any other; inside a work-item function it is
+    the group's shared storage: ``tile[lid] = value`` before a barrier,
+    ``tile.data[n - 1 - lid]`` (or ``tile[...]``) after it."""
+
+    def __init__(self, fill, shape, dtype, recorder):
+        super().__init__("alloc", (fill,), shape, dtype)
+        self.recorder = recorder
+
+    @property
+    def data(self):
+        return self
+
+    @staticmethod
+    def _local_forms(key):
+        keys = key if isinstance(key, tuple) else (key,)
+        forms = [index_form(k) for k in keys]
+        if keys and all(f is not None and f[0] == "local" for f in forms):
+            return tuple(forms)
+        return None
+
+    def __setitem__(self, key, value):
+        forms = self._local_forms(key)
+        if forms is None or not self.recorder.in_workitems:
+            raise UnsupportedKernel("a group tile is written as tile[local_id] inside a "
+                                    "work-item function")
+        if len(forms) != self.ndim or any(f != ("local", d, 1, 0, 0) for d, f in enumerate(forms)):
+            raise UnsupportedKernel("a work-item writes the group tile at its own local id only")
+        self.recorder.item_events.append(("tile", self, forms, Tile._wrap(value)))
+
+    def __getitem__(self, key):
+        forms = self._local_forms(key)
+        if forms is not None:
+            if len(forms) != self.ndim:
+                raise IndexError("a group tile is read with one index per dimension")
+            return Tile("tile_read", (self,), (), self.dtype,
+                        index=tuple((f[1], f[2], f[3], f[4]) for f in forms))
+        return super().__getitem__(key)
+
+
 def _dot(a, b):
     a, b = Tile._wrap(a), Tile._wrap(b)
     if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[0]:
@@ -739,6 +857,7 @@ class Guard:
 
     def __bool__(self):
         self.recorder.guards.append((self.axis, self.bound))
+        self.recorder.note_guard(self.axis, 1, 0, "lt", float(self.bound))
         return True
 
 
@@ -748,23 +867,31 @@ class WorkIndex:
     (``buf[gid]``), takes part in arithmetic as the index value, and compares
     against a bound in a guarding ``if``."""
 
-    def __init__(self, axis, recorder):
-        self.axis, self.recorder = axis, recorder
+    def __init__(self, axis, recorder, kind="global"):
+        self.axis, self.recorder, self.kind = axis, recorder, kind
 
     def tile(self):
+        if self.kind == "local":
+            return Tile("index", (), (), "scalar", axis=self.axis, kind="local")
         return Tile("index", (), (), "scalar", axis=self.axis)
 
     def __lt__(self, bound):
+        if self.kind != "global":
+            return self.tile() < bound
         return Guard(self.axis, int(Affine.of(bound)), self.recorder)
 
     def __le__(self, bound):
+        if self.kind != "global":
+            return self.tile() <= bound
         return Guard(self.axis, int(Affine.of(bound)) + 1, self.recorder)
 
-    def _refuse(self, *_):
-        raise UnsupportedKernel("a work-item index can only be compared as `index < bound`")
-
-    __gt__ = __ge__ = __eq__ = __ne__ = _refuse
+    def __gt__(self, bound): return self.tile() > bound
+    def __ge__(self, bound): return self.tile() >= bound
+    def __eq__(self, other): return self.tile() == other
+    def __ne__(self, other): return self.tile() != other
     __hash__ = object.__hash__
+    def __mod__(self, o): return self.tile() % o
+    def __floordiv__(self, o): return self.tile() // o
 
     def __index__(self):
         raise UnsupportedKernel("a work-item index has no single value while the kernel is recorded")
@@ -790,9 +917,6 @@ class CurrentWorkitem:
         self._local_id, self._global_id = lid, gid
 
     def local_id(self):
-        if self._local_id is None:
-            raise UnsupportedKernel("work-item functions are recorded for the whole launch: only "
-                                    "global_id() is available, not local_id()")
         return self._local_id
 
     def global_id(self):
@@ -812,6 +936,35 @@ class CurrentGroup:
         self.atomics = []
         self.item_stores = []  # `buf[gid] = value` at work-item level: (buffer, axes, tile)
         self.guards = []       # `gid < bound` conditions taken at work-item level: (axis, bound)
+        # Everything a work-item function does, in order: ("out", buffer, axes, value),
+        # ("tile", group tile, local index forms, value), ("barrier",); and per phase
+        # (the stretch before / after a barrier) the index ranges its conditions allow:
+        # phase -> axis -> [lo, hi).
+        self.item_events = []
+        self.item_ranges = [{}]
+        self.in_workitems = False
+
+    def note_guard(self, axis, scale, offset, op, bound):
+        """``scale * gid[axis] + offset  OP  bound`` was taken as true."""
+        lo, hi = self.item_ranges[-1].get(axis, (-(1 << 62), 1 << 62))
+        if scale < 0:  # -gid + offset OP bound  <=>  gid  OP'  offset - bound
+            op = {"lt": "gt", "le": "ge", "gt": "lt", "ge": "le"}.get(op, op)
+            bound = offset - bound
+        else:
+            bound = bound - offset
+        import math
+
+        if op == "lt":
+            hi = min(hi, math.ceil(bound))
+        elif op == "le":
+            hi = min(hi, math.floor(bound) + 1)
+        elif op == "gt":
+            lo = max(lo, math.floor(bound) + 1)
+        elif op == "ge":
+            lo = max(lo, math.ceil(bound))
+        else:
+            raise UnsupportedKernel("work-item indices can be compared with < <= > >= only")
+        self.item_ranges[-1][axis] = (lo, hi)
 
     @property
     def id(self):
@@ -870,7 +1023,7 @@ class CurrentGroup:
 
     # -- allocators ---------------------------------------------------------------
     def _alloc(self, shape, dtype, fill):
-        return Tile("alloc", (float(fill),), _shape_tuple(shape), dtype_name(dtype))
+        return GroupTile(float(fill), _shape_tuple(shape), dtype_name(dtype), self)
 
     def empty(self, shape, dtype): return self._alloc(shape, dtype, 0)
     def zeros(self, shape, dtype): return self._alloc(shape, dtype, 0)
@@ -898,13 +1051,28 @@ class CurrentGroup:
         compute, write ``buf[gid]`` under a bounds guard."""
 
         def run():
-            ids = tuple(WorkIndex(d, self) for d in range(len(self._group_shape)))
-            func(CurrentWorkitem(None, ids))
+            dims = range(len(self._group_shape))
+            gids = tuple(WorkIndex(d, self) for d in dims)
+            lids = tuple(WorkIndex(d, self, "local") for d in dims)
+            self.in_workitems = True
+            try:
+                func(CurrentWorkitem(lids, gids))
+            finally:
+                self.in_workitems = False
 
         return run
 
     def barrier(self):
-        raise UnsupportedKernel("group.barrier is not supported by the precompiled kernels")
+        """``group.barrier()`` inside a work-item function (reference
+        kernel_api.py:416-431): every work-item of the group arrives before any
+        goes on.  Splits the function into two phases; values cross it through a
+        tile of the group (``group.zeros(...)`` written at ``tile[lid]``)."""
+        if not self.in_workitems:
+            return  # at group level nothing runs concurrently: nothing to wait for
+        if any(e[0] == "barrier" for e in self.item_events):
+            raise UnsupportedKernel("more than one group.barrier() in a work-item function")
+        self.item_events.append(("barrier",))
+        self.item_ranges.append({})
 
 
 class CurrentGroup1(CurrentGroup):

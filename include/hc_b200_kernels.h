@@ -171,6 +171,43 @@ HC_B200_API int hcMapElements(HcContext c, const HcMapProgram *program, int dtyp
  * indices (src 16/17) are not available. */
 HC_B200_API int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype);
 
+/* Work-item program: a body written at work-item level
+ * (CurrentGroup.workitems, python/hckernel/kernel_api.py:395-414) that an
+ * element-wise pass cannot express - it uses the work-item's local id, reads a
+ * neighbour's element, or has two phases separated by group.barrier()
+ * (kernel_api.py:416-431) that exchange values through a tile of the work-group.
+ * One thread per work-item, one CTA per work-group of groupRows x groupCols
+ * (at most 1024 work-items), the tile in shared memory.  The program uses the
+ * operations of hcMapElements on single values (no validity tracking: a zero
+ * divisor gives the IEEE result), with an instruction `op | (src << 8)` and
+ *   op   64 store to the group's tile at the work-item's local id
+ *        65 barrier   66 store to out at the work-item's global id
+ *   src  0..3 input k at (row + inRow[k], col + inCol[k]), 4..6 temporaries,
+ *        8..15 constants, 16 / 17 global row / column, 18 / 19 local row / column,
+ *        24..27 the tile at local index (tileScale * local id + tileOffset) mod
+ *        tileMod per axis (tileMod 0: no wrap), table entry src - 24
+ * A work-item takes part in phase p (0 before the barrier, 1 after it) only if
+ * guardLo[p] <= global id < guardHi[p] on both axes - the `if gid < n` of the
+ * body; all arrays are rows x cols (rows = 1 for one-dimensional work) and the
+ * guards are cut to that.  HC_F32 or HC_F64. */
+typedef struct HcItemProgram {
+  const void *in[4];      /* device */
+  long long inPitch[4];
+  int inRow[4], inCol[4];
+  void *out;              /* device */
+  long long outPitch;
+  long long rows, cols;
+  int groupRows, groupCols;
+  int nInputs;            /* 0..4 */
+  int nInstr;             /* 1..48 */
+  unsigned code[48];
+  double consts[8];
+  long long guardLo[2][2], guardHi[2][2]; /* [phase][0 rows, 1 columns] */
+  int tileScale[4][2], tileOffset[4][2], tileMod[4][2];
+  double tileFill;        /* the tile's content before the first store */
+} HcItemProgram;
+HC_B200_API int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype);
+
 /* Row softmax over the last axis, HC_F32 or HC_F64
  * (python/hckernel/tests/test_examples.py:304-321). */
 HC_B200_API int hcSoftmaxRows(HcContext c, const void *x, void *y,

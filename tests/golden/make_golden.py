@@ -13,9 +13,9 @@ NumPy oracle (``oracle/``) on the same inputs and refuses to write anything if
 the two disagree, so a committed fixture always means "reference == oracle on
 this case".  The tests never import the reference; they only read the files.
 
-``greenlet`` is imported unconditionally by the reference's ``kernel_api`` but
-is only needed by its work-item scopes, which none of these kernels use; a
-placeholder module is registered when the package is absent.
+``greenlet`` is imported unconditionally by the reference's ``kernel_api`` and
+drives its work-item scopes; when the package is absent ``greenlet_shim.py``
+(one thread per task, one baton) stands in for it.
 """
 
 
@@ -36,9 +36,12 @@ sys.path.insert(0, str(REFERENCE / "python"))
 try:
     import greenlet  # noqa: F401
 except ImportError:
-    stub = types.ModuleType("greenlet")
-    stub.greenlet = type("greenlet", (), {})
-    sys.modules["greenlet"] = stub
+    # Work-item scopes and group.barrier() need real task switching
+    # (greenlet_shim.py explains).
+    sys.path.insert(0, str(HERE))
+    import greenlet_shim
+
+    sys.modules["greenlet"] = greenlet_shim
 
 from hckernel.kernel_sim import (  # noqa: E402  (the reference)
     Buffer,
@@ -465,6 +468,24 @@ def main():
         same(name, r, o)
         assert (r == -77).any() or "compare" in name or "equal" in name or "i64" in name, name
         out[name] = r
+
+    # 6c. Work-item bodies: the work-item form of the pairwise distance
+    #     (docs/langref.md:47-63), neighbour reads, local ids, and two phases
+    #     separated by group.barrier() that exchange values through a group tile.
+    import hckernel.kernel_sim as ref_sim
+
+    ns = types.SimpleNamespace(kernel=ref_sim.kernel, sym=sym, CurrentGroup=CurrentGroup,
+                               Buffer=Buffer, DT=DT, target={})
+    from oracle import workitems as oracle_items
+
+    for case in oracle_items.work_item_cases():
+        shape, dtype = case["out"]
+        r = np.full(shape, -77, dtype)
+        case["make"](ns)(*case["inputs"], r)
+        o = np.full(shape, -77, dtype)
+        case["oracle"](case["inputs"], o)
+        same(case["name"], r, o)
+        out[case["name"]] = r
 
     # 7. Row bodies: reductions along the rows used again in the same expression.
     for name, fn, count, shape, dtype, group_rows in oracle.rowwise_cases():
