@@ -59,6 +59,9 @@ SHAPES = {
     # Row body with reductions used again (log-softmax), interpreted as a
     # three-pass row program; same shape as the softmax configuration.
     "rows": (32768, 4096),
+    # float32 GEMM large enough for the tensor cores (three tf32 products per
+    # product); not one of the five configurations.
+    "gemm_f32_tensor": (4096, 4096, 4096),
 }
 # Tile sizes (TN images x TNF filters per work-group, K block) the conv is run with.
 CONV_TILES = (32, 64, 16)
@@ -74,7 +77,12 @@ SMALL_SHAPES = {
     "conv": (32, 64, 30, 30, 64, 3, 3, 1),
     "map": (8192, 4096),
     "rows": (8192, 4096),
+    "gemm_f32_tensor": (2048, 2048, 2048),
 }
+
+# Dense tf32 rate of the tensor cores, nominal (no measured figure exists); a
+# float32 product costs three tf32 products.
+TF32_NOMINAL_TFLOPS = 1125.0
 
 # fp32 FMA rate of the CUDA cores, nominal (no measured figure exists for it):
 # 148 SMs x 128 lanes x 2 flop x 1.965 GHz.
@@ -89,9 +97,11 @@ METRIC = {
     "gemm_f32": "gemm_f32_tiled_throughput",
     "gemm_bf16": "gemm_bf16_throughput",
     "gemm_w8a16": "gemm_w8a16_throughput",
+    "gemm_f32_tensor": "gemm_f32_3xtf32_throughput",
 }
 DTYPE = {"softmax": "f32", "reduce": "f32", "gemm_f32": "f32", "gemm_bf16": "bf16",
-         "gemm_w8a16": "bf16", "conv": "f32", "map": "f32", "rows": "f32"}
+         "gemm_w8a16": "bf16", "conv": "f32", "map": "f32", "rows": "f32",
+         "gemm_f32_tensor": "f32 (3 x tf32)"}
 
 
 def relu_axpby(a, b):
@@ -138,6 +148,8 @@ def algorithmic(name):
         return 3 * m * n * 4, 2 * m * n * k, "latency"
     if name == "gemm_bf16":
         return (m * k + k * n + m * n) * 2, 2 * m * n * k, "tensor"
+    if name == "gemm_f32_tensor":
+        return (m * k + k * n + m * n) * 4, 2 * m * n * k, "tf32x3"
     return m * k * 2 + k * n + n * 4 + m * n * 2, 2 * m * n * k, "tensor"
 
 
@@ -168,6 +180,7 @@ NCU_TRAFFIC = {
     "gemm_bf16": 1546.6e6,
     "gemm_w8a16": None,
     "gemm_f32": None,
+    "gemm_f32_tensor": None,
     "conv": None,
     "map": 1073761280 + 495959040,
     "rows": 536891392 + 481583104,
@@ -291,6 +304,15 @@ def cpu_sample(name, threads, repeats):
 
         def one_pass():
             oracle.gemm_kblocked(a, b, out, (64, 64), kb=16)
+    elif name == "gemm_f32_tensor":
+        rows = min(s[0], 512)
+        a, b = oracle.make_inputs("gemm_f32", shape=(rows, s[1], s[2]))
+        out = np.zeros((rows, s[1]), np.float32)
+        scale = rows / s[0]
+        what = f"{rows} of {s[0]} rows of A against the full B, 256x256 groups, full K"
+
+        def one_pass():
+            oracle.gemm_fullk(a, b, out, (256, 256))
     elif name == "gemm_bf16":
         rows = min(s[0], 512)
         a, b = oracle.make_inputs("gemm_bf16", shape=(rows, s[1], s[2]))
@@ -383,7 +405,7 @@ def run_reference(args):
 # output).  "rows": the rows of the output (softmax, reductions, row and
 # element-wise bodies; M of the bf16 GEMM with B replicated); "cols": N of the
 # dequant GEMM with A replicated; "replicas": too small to shard.
-SHARDING = {"softmax": "rows", "rows": "rows", "map": "rows", "reduce": "rows",
+SHARDING = {"gemm_f32_tensor": "replicas", "softmax": "rows", "rows": "rows", "map": "rows", "reduce": "rows",
             "gemm_bf16": "rows", "gemm_w8a16": "cols", "gemm_f32": "replicas",
             "conv": "replicas"}
 
@@ -486,6 +508,10 @@ def run_gpu(args):
             if name == "map":
                 return None, [torch.randn(*s, device=dev, generator=g) for _ in range(2)], \
                     "torch.randn on the device, seed 1000"
+            if name == "gemm_f32_tensor":
+                return None, [torch.rand(s[0], s[2], device=dev, generator=g) * 2 - 1,
+                              torch.rand(s[2], s[1], device=dev, generator=g) * 2 - 1], \
+                    "torch.rand on the device, seed 1000"
             xs, fs, _ = conv_shapes(s)
             return None, [torch.randn(*xs, device=dev, generator=g),
                           torch.randn(*fs, device=dev, generator=g)], \
@@ -550,7 +576,7 @@ def run_gpu(args):
             return [torch.empty(s[0], device=dev), torch.empty(s[0], device=dev)]
         if name == "conv":
             return [torch.zeros(*conv_shapes(s)[2], device=dev)]
-        dtype = torch.float32 if name == "gemm_f32" else torch.bfloat16
+        dtype = torch.float32 if name in ("gemm_f32", "gemm_f32_tensor") else torch.bfloat16
         return [torch.empty(s[0], s[1], device=dev, dtype=dtype)]
 
     def row_call(name, ins, outs):
@@ -562,6 +588,12 @@ def run_gpu(args):
             return lambda i, o: native.reduce_rows(ctx, i[0], o[0], o[1])
         if name in ("gemm_f32", "gemm_bf16"):
             return lambda i, o: native.gemm(ctx, i[0], i[1], o[0])
+        if name == "gemm_f32_tensor":
+            s3 = SHAPES[name]
+            need = native.gemm_f32_workspace_bytes(s3[0], s3[1], s3[2])
+            raw = torch.empty(need + 1024, dtype=torch.uint8, device=dev)
+            ws = raw[(-raw.data_ptr()) % 1024:][:need]
+            return lambda i, o: native.gemm(ctx, i[0], i[1], o[0], ws)
         if name == "map":
             roles = map_kernel().plan_for((ins[0], ins[1], outs[0])).roles
             order = roles["inputs"]
@@ -596,7 +628,7 @@ def run_gpu(args):
             return lambda: kernels.reduce_rows(ins[0], outs[0], outs[1], 256)
         if name == "gemm_f32":
             return lambda: kernels.dot(ins[0], ins[1], outs[0], (64, 64))
-        if name == "gemm_bf16":
+        if name in ("gemm_bf16", "gemm_f32_tensor"):
             return lambda: kernels.dot_fullk(ins[0], ins[1], outs[0], (256, 256))
         if name == "conv":
             return lambda: conv_kernel()(ins[0], ins[1], outs[0])
@@ -617,6 +649,12 @@ def run_gpu(args):
                          "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name],
                          "peak_source": peaks["source"]}
         ach = flops / per_step_ms / 1e9
+        if bound == "tf32x3":
+            peak = TF32_NOMINAL_TFLOPS / 3
+            return ach, {"bound": "tensor (three tf32 products per float32 product)",
+                         "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                         "traffic": NCU_TRAFFIC[name], "peak_source": "nominal tf32 / 3",
+                         "cuda_core_peak": FP32_NOMINAL_TFLOPS}
         if bound == "fp32":
             return ach, {"bound": "fp32 CUDA cores", "achieved": ach, "peak": FP32_NOMINAL_TFLOPS,
                          "unit": "TFLOP/s", "frac": ach / FP32_NOMINAL_TFLOPS,
@@ -667,7 +705,7 @@ def run_gpu(args):
     def verify(name, host, outs, samples=96):
         """Every rank compares sampled rows of its own copy of the output with the
         oracle's rows (computed once, on rank 0, and sent round)."""
-        if name in ("map", "conv"):
+        if name in ("map", "conv", "gemm_f32_tensor"):
             return None  # no host arrays: these are covered by the GPU test-suite only
         m = outs[0].shape[0]
         rows = np.unique(np.r_[0:8, m - 8:m,
@@ -941,7 +979,8 @@ def run_gpu(args):
         e2e = measure_e2e(name, max(3, min(args.steps, 20)), 3)
         extras = {}
         if name == "softmax" and not args.no_extras:
-            others = [("reduce", 100), ("gemm_bf16", 50), ("gemm_w8a16", 50), ("gemm_f32", 500)]
+            others = [("reduce", 100), ("gemm_bf16", 50), ("gemm_w8a16", 50), ("gemm_f32", 500),
+                      ("gemm_f32_tensor", 20)]
             if not sharded:
                 others += [("conv", 50)]
             others += [("map", 100), ("rows", 100)]

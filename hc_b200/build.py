@@ -43,6 +43,7 @@ KERNEL_SOURCES = [
     "mapped_gemm",
     "gemm_tiled",
     "gemm_bf16_umma",
+    "gemm_f32_umma",
     "dequant_w8",
     "selftest",
 ]

@@ -181,6 +181,10 @@ KERNELS_PROTOTYPES = {
     ),
     "hcGemmTiled": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]),
     "hcGemmBf16": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll]),
+    "hcGemmF32TensorWorkspaceBytes": (_sz, [_ll, _ll, _ll]),
+    "hcGemmF32Tensor": (
+        C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll]
+    ),
     "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
     "hcGemmW8A16": (
         C.c_int,
@@ -372,6 +376,13 @@ class Context:
         self._check(
             self.lib.hcGemmTiled(self.handle, a, b, c, m, n, k, lda, ldb, ldc, dtype),
             "hcGemmTiled",
+        )
+
+    def gemm_f32_tensor(self, a, b, c, workspace, workspace_bytes, m, n, k, lda, ldb, ldc):
+        self._check(
+            self.lib.hcGemmF32Tensor(self.handle, a, b, c, workspace, workspace_bytes, m, n, k,
+                                     lda, ldb, ldc),
+            "hcGemmF32Tensor",
         )
 
     def gemm_bf16(self, a, b, c, m, n, k, lda, ldb, ldc):

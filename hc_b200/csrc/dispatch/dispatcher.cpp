@@ -487,7 +487,13 @@ void mappedGemm(Context &ctx, py::handle x, py::handle xTables, py::handle f,
             "mapped_gemm");
 }
 
-void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
+size_t gemmF32WorkspaceBytes(long long m, long long n, long long k) {
+  return hcGemmF32TensorWorkspaceBytes(m, n, k);
+}
+
+// `workspace` (a uint8 device buffer of gemm_f32_workspace_bytes) sends a
+// float32 product to the tensor cores (hcGemmF32Tensor).
+void gemm(Context &ctx, py::handle a, py::handle b, py::handle out, py::object workspace) {
   ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2),
            C = deviceArray(ctx, out, "out", 2);
   sameKind(A, B, "a", "b");
@@ -499,6 +505,14 @@ void gemm(Context &ctx, py::handle a, py::handle b, py::handle out) {
     ctx.check(hcGemmBf16(ctx.get(), A.data, B.data, C.data, M, N, K, pitch(A), pitch(B),
                          pitch(C)),
               "gemm (bf16)");
+    return;
+  }
+  if (A.kind == ElemKind::F32 && !workspace.is_none()) {
+    ArrayArg ws = deviceArray(ctx, workspace, "workspace", 1);
+    ctx.check(hcGemmF32Tensor(ctx.get(), A.data, B.data, C.data, ws.data,
+                              size_t(ws.shape[0]) * size_t(ws.itemsize), M, N, K, pitch(A),
+                              pitch(B), pitch(C)),
+              "gemm (float32, tensor cores)");
     return;
   }
   ctx.check(hcGemmTiled(ctx.get(), A.data, B.data, C.data, M, N, K, pitch(A), pitch(B),
@@ -590,7 +604,10 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("mapped_gemm", &mappedGemm, py::arg("ctx"), py::arg("x"), py::arg("x_tables"),
         py::arg("f"), py::arg("f_tables"), py::arg("out"), py::arg("out_tables"),
         py::arg("groups"), py::arg("tm"), py::arg("tn"), py::arg("k"));
-  m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"));
+  m.def("gemm", &gemm, py::arg("ctx"), py::arg("a"), py::arg("b"), py::arg("out"),
+        py::arg("workspace") = py::none());
+  m.def("gemm_f32_workspace_bytes", &gemmF32WorkspaceBytes, py::arg("m"), py::arg("n"),
+        py::arg("k"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());
   m.def("w8a16_workspace_bytes", &w8a16WorkspaceBytes, py::arg("n"), py::arg("k"));

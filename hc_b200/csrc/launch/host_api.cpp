@@ -15,9 +15,11 @@
 //
 // PCIe is full duplex and the copy engines run beside the SMs, so upload,
 // kernel and download overlap; two device slots per direction keep all three
-// busy.  Only whole rows are handed to the kernels, so the result is bit for
-// bit that of one launch on the whole matrix.  The calls return when the result
-// is in host memory.  Copies are asynchronous (and overlap) only for page-locked
+// busy.  Only whole rows are handed to the kernels, so the result is that of
+// one launch on the whole matrix - bit for bit for the softmax, the row maxima
+// and the GEMM; a row sum may differ in its last bits when a chunk has so few
+// rows that hcReduceRows takes its other kernel (a CTA per row instead of a warp
+// per row).  The calls return when the result is in host memory.  Copies are asynchronous (and overlap) only for page-locked
 // host memory: hcHostPin / hcHostUnpin lock an existing range.
 #include "context.hpp"
 
@@ -157,6 +159,9 @@ int streamRows(HcContextImpl *c, long long rows, long long chunkRows, const Stre
   if (!p)
     return 1;
   chunkRows = std::max<long long>(1, std::min(chunkRows, rows));
+  // Equal chunks rather than full ones and a short tail.
+  const long long chunks = (rows + chunkRows - 1) / chunkRows;
+  chunkRows = (rows + chunks - 1) / chunks;
   for (int s = 0; s < 2; ++s) {
     for (int k = 0; k < nIn; ++k)
       if (reserve(c, p->in[s][k], size_t(chunkRows) * size_t(ins[k].rowBytes)))

@@ -103,6 +103,9 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_bf16_umma_pair", "gemm_bf16_umma"},
     {"hc_gemm_bf16_umma_pair_scaled", "gemm_bf16_umma"},
     {"hc_dequant_w8_bf16", "dequant_w8"},
+    {"hc_split_tf32", "gemm_f32_umma"},
+    {"hc_split_tf32_t", "gemm_f32_umma"},
+    {"hc_gemm_f32_umma", "gemm_f32_umma"},
 };
 
 // Image that defines `kernel`; a table entry ending in '_' stands for every
@@ -1177,6 +1180,73 @@ int hcGemmBf16(HcContext c, const void *a, const void *b, void *out,
   // per 128 x 256 tile; it needs at least two row blocks to be worth a cluster.
   const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > kUmmaBM);
   return launchUmma(c, a, b, nullptr, out, M, N, K, lda, ldb, ldc, pair);
+}
+
+// ---- fp32 GEMM on the tensor cores (three tf32 products per fp32 product) ----------
+static long long f32Pitch(long long K) { return roundUp(K, 4); }
+
+size_t hcGemmF32TensorWorkspaceBytes(long long M, long long N, long long K) {
+  if (M <= 0 || N <= 0 || K <= 0)
+    return 0;
+  // hi and lo parts of A [M, Kp] and of B transposed [N, Kp], each 1 KiB aligned.
+  const size_t a = size_t(roundUp(M * f32Pitch(K) * 4, 1024));
+  const size_t b = size_t(roundUp(N * f32Pitch(K) * 4, 1024));
+  return 2 * a + 2 * b;
+}
+
+int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *workspace,
+                    size_t workspaceBytes, long long M, long long N, long long K,
+                    long long lda, long long ldb, long long ldc) {
+  if (!c)
+    return 1;
+  if (checkGemmShape(c, "hcGemmF32Tensor", a, b, out, M, N, K, lda, ldb, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  // Without tcgen05, or with nothing to sum, the CUDA-core kernel does it.
+  if (c->ccMajor != 10 || K == 0 || c->gemmVariant == 3)
+    return hcGemmTiled(c, a, b, out, M, N, K, lda, ldb, ldc, HC_F32);
+  const size_t need = hcGemmF32TensorWorkspaceBytes(M, N, K);
+  if (!workspace || workspaceBytes < need || !aligned(workspace, 1024))
+    return c->fail("hcGemmF32Tensor: workspace of %zu bytes (1 KiB aligned) needed, got %zu",
+                   need, workspaceBytes);
+  const long long kp = f32Pitch(K);
+  const size_t aBytes = size_t(roundUp(M * kp * 4, 1024)), bBytes = size_t(roundUp(N * kp * 4, 1024));
+  auto *base = static_cast<unsigned char *>(workspace);
+  float *aHi = reinterpret_cast<float *>(base), *aLo = reinterpret_cast<float *>(base + aBytes);
+  float *bHi = reinterpret_cast<float *>(base + 2 * aBytes);
+  float *bLo = reinterpret_cast<float *>(base + 2 * aBytes + bBytes);
+  {
+    long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(kp, 256), 64));
+    long long gy = std::max<long long>(1, std::min<long long>(M, 65535));
+    void *args[] = {&a, &aHi, &aLo, &M, &K, &lda, (void *)&kp};
+    if (c->launch("hc_split_tf32", size_t(gx), size_t(gy), 1, 256, args, 7, 0))
+      return 1;
+  }
+  {
+    const long long tiles = ceilDiv(N, 32) * ceilDiv(kp, 32);
+    long long grid = std::max<long long>(1, std::min<long long>(tiles, c->smCount * 16));
+    void *args[] = {&b, &bHi, &bLo, &K, &N, &ldb, (void *)&kp};
+    if (c->launch("hc_split_tf32_t", size_t(grid), 1, 1, 256, args, 7, 0))
+      return 1;
+  }
+  alignas(64) CUtensorMap maps[4];
+  const void *parts[4] = {aHi, aLo, bHi, bLo};
+  for (int i = 0; i < 4; ++i) {
+    const bool isA = i < 2;
+    if (olxEncodeTensorMap2D(c->device, &maps[i], /*f32*/ 1, parts[i], size_t(isA ? M : N),
+                             size_t(kp), size_t(kp) * 4, isA ? 128 : 256, 32, 128))
+      return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
+  }
+  int tilesM = int(ceilDiv(M, 128)), tilesN = int(ceilDiv(N, 256));
+  int bandM = 16;
+  int vecStore = aligned(out, 16) && ldc % 4 == 0;
+  const long long tiles = (long long)tilesM * tilesN;
+  const long long grid = std::min<long long>(tiles, c->smCount);
+  const size_t smem = 2 * 96 * 1024 /*stages*/ + 1024 /*align*/ + 256 /*barriers*/;
+  void *args[] = {&maps[0], &maps[1], &maps[2], &maps[3], &out,    &M,        &N,
+                  &K,       &ldc,     &tilesM,  &tilesN,  &bandM, &vecStore, &c->statusWord};
+  return c->launch("hc_gemm_f32_umma", size_t(grid), 1, 1, 192, args, 14, smem);
 }
 
 size_t hcGemmW8A16WorkspaceBytes(long long N, long long K) {

@@ -668,7 +668,18 @@ class KernelDispatcher:
             tx, tf, to = spec.device_tables((x, f, out))
             native.mapped_gemm(ctx, x, tx, f, tf, out, to, spec.groups, spec.tm, spec.tn, spec.k)
         elif plan.family == "gemm":
-            native.gemm(ctx, args[r["a"]], args[r["b"]], args[r["out"]])
+            a, b = args[r["a"]], args[r["b"]]
+            m, k, n = a.shape[0], a.shape[1], b.shape[1]
+            # float32 products of at least 1024 each way go to the tensor cores
+            # (three tf32 products per product); smaller ones stay on the CUDA
+            # cores, where the launch is what they cost.
+            if (dtype_name(a.dtype) == "float32" and min(m, n, k) >= _F32_TENSOR_MIN
+                    and settings.GEMM_VARIANT != 3):
+                if workspace is None:
+                    workspace = _f32_workspace_for(self.device, a, m, n, k)
+                native.gemm(ctx, a, b, args[r["out"]], workspace)
+            else:
+                native.gemm(ctx, a, b, args[r["out"]])
         elif plan.family == "gemm_w8a16":
             a, w = args[r["a"]], args[r["w"]]
             if workspace is None:
@@ -717,6 +728,22 @@ class _StreamFence:
 
 
 _workspaces = {}
+_F32_TENSOR_MIN = 1024
+
+
+def _f32_workspace_for(device, a, m, n, k):
+    """Scratch for the split operands of a float32 product on the tensor cores,
+    kept per (device, M, N, K)."""
+    import torch
+    from .._native import _dispatcher as native
+
+    need = native.gemm_f32_workspace_bytes(m, n, k)
+    key = (device, "f32", m, n, k)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need:
+        buf = _workspaces[key] = torch.empty(need + 1024, dtype=torch.uint8, device=a.device)
+    offset = (-buf.data_ptr()) % 1024  # the entry point wants 1 KiB alignment
+    return buf[offset:offset + need]
 
 
 def _workspace_for(device, w):

@@ -284,6 +284,22 @@ HC_B200_API int hcGemmTiled(HcContext c, const void *a, const void *b, void *cOu
                             long long lda, long long ldb, long long ldc,
                             int dtype);
 
+/* float32 GEMM on the tensor cores: C[M,N] = A[M,K] @ B[K,N], float32 in and
+ * out, for the same dot kernels as hcGemmTiled
+ * (python/hckernel/tests/test_examples.py:74-165) at sizes where the CUDA cores
+ * are the limit.  Every operand is split into two tf32 numbers and three tf32
+ * products per product accumulate in fp32 (tcgen05.mma.kind::tf32), which keeps
+ * the result within about 3e-7 * sum|a||b| of the exact one - float32 class,
+ * where a single tf32 product would lose three digits.  `workspace` must hold
+ * hcGemmF32TensorWorkspaceBytes(M, N, K) bytes of device memory, 1 KiB aligned
+ * (the split operands); it is written by every call.  On a device without
+ * tcgen05, or with "gemm_variant" 3, the call runs hcGemmTiled instead. */
+HC_B200_API size_t hcGemmF32TensorWorkspaceBytes(long long M, long long N, long long K);
+HC_B200_API int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *cOut,
+                                void *workspace, size_t workspaceBytes, long long M,
+                                long long N, long long K, long long lda, long long ldb,
+                                long long ldc);
+
 /* bf16 GEMM with fp32 accumulation on the tensor cores (tcgen05); falls back
  * to the bf16 tiled kernel for layouts TMA cannot describe (a pitch that is
  * not a multiple of 8 elements or a base that is not 16-byte aligned). */
@@ -330,9 +346,10 @@ HC_B200_API int hcGemmW8A16Static(HcContext c, const void *a, const void *w,
  * context's device (upload of chunk i+1, kernel on chunk i, download of chunk
  * i-1 overlap; device slots are allocated on first use and kept by the
  * context), so a call costs little more than moving the data over the link
- * once each way.  Only whole rows reach the kernels: results are bit for bit
- * those of the device entry points.  A call returns when the result is in host
- * memory.  The copies overlap only for page-locked memory: lock a range once
+ * once each way.  Only whole rows reach the kernels: results are those of the
+ * device entry points, bit for bit except that a row sum may differ in its last
+ * bits when a chunk is short enough for hcReduceRows to take its other kernel.
+ * A call returns when the result is in host memory.  The copies overlap only for page-locked memory: lock a range once
  * with hcHostPin (and release it with hcHostUnpin); pageable memory works but
  * serialises the three stages.  No counterpart in the reference, whose runtime
  * sees device pointers only and synchronises after every launch

@@ -308,7 +308,10 @@ def test_every_operator_against_numpy(dtype):
             if divides:
                 want = np.where(b == 0, np.asarray(-77, dtype), want)
             if name == "pow":
-                np.testing.assert_allclose(got, want, rtol=2e-6 if dtype == "float32" else 1e-14)
+                # (powf is within a few ulp; the added tile may cancel most of the power)
+                tol = dict(rtol=2e-6, atol=2e-6) if dtype == "float32" else dict(rtol=1e-14,
+                                                                                 atol=1e-14)
+                np.testing.assert_allclose(got, want, **tol)
             else:
                 assert np.array_equal(got, want), (name, shape, dtype)
             if pitch > shape[1]:

@@ -86,7 +86,11 @@ def test_reduce_rows_host(hc):
     d_s, d_m = empty_like_dev((rows,), torch.float32), empty_like_dev((rows,), torch.float32)
     hc.reduce_rows(dev(x).data_ptr(), d_s.data_ptr(), d_m.data_ptr(), rows, cols, cols)
     finish(hc)
-    assert np.array_equal(hs, d_s.cpu().numpy())
+    # (A chunk may take the other reduction kernel than the whole matrix does: same
+    # sums up to the order of the additions.)
+    assert np.all(np.abs(hs - d_s.cpu().numpy())
+                  <= 1e-6 * np.abs(x).astype(np.float64).sum(axis=1))
+    assert np.array_equal(hm, d_m.cpu().numpy())
 
 
 @pytest.mark.parametrize("m,n,k", [(600, 384, 256), (2500, 512, 4096), (100, 72, 40)])
