@@ -414,6 +414,14 @@ SHARDING = {"gemm_f32_tensor": "replicas", "softmax": "rows", "rows": "rows", "m
 # The HBM-bound bodies take 8 / N bands: their shard's kernel is short against the
 # gather, so more bands only add launches.
 DEFAULT_BANDS = {"softmax": 0, "rows": 0, "map": 0, "reduce": 1, "gemm_bf16": 2}
+# Workloads whose kernel does the output all-gather itself by default (the *_peers
+# entry points: stores into every rank's buffer over NVLink); the others gather with
+# NCCL.  The GEMMs have such kernels too (`--gather fused-all` uses them), but their
+# epilogue writes 64-byte pieces per lane, which NVLink moves at a sixth of the rate
+# of the softmax's 512-byte rows, and the stalled epilogue holds the tensor cores
+# back: on 2 GPUs 0.61 ms against 0.55 ms with NCCL's gather behind the kernel.
+FUSED_GATHER = ("softmax", "reduce")
+FUSED_GATHER_ALL = ("softmax", "reduce", "gemm_bf16", "gemm_w8a16")
 # Which inputs of a row-sharded workload are split by rows (the others are replicated).
 ROW_INPUTS = {"softmax": (0,), "rows": (0,), "map": (0, 1), "reduce": (0,), "gemm_bf16": (0,)}
 
@@ -425,7 +433,8 @@ def run_gpu(args):
 
     from hc_b200._native import _dispatcher as native
     from hc_b200.hckernel.kernel import get_context
-    from hc_b200.launcher import BandPlan, ShardedLauncher, init_process_group, partition
+    from hc_b200.launcher import (BandPlan, PeerOutput, ShardedLauncher, init_process_group,
+                                  partition)
     from hc_b200.workloads import make_kernels
 
     rank, world, local = init_process_group()
@@ -754,7 +763,43 @@ def run_gpu(args):
             shard_in = [plan.take_shard(t, rank).contiguous() if k in ROW_INPUTS[name] else t
                         for k, t in enumerate(ins)]
             sharded_outs = [torch.empty_like(t) for t in full_outs]
-            if name == "reduce":
+            fused = ((args.gather == "fused" and name in FUSED_GATHER)
+                     or (args.gather == "fused-all" and name in FUSED_GATHER_ALL))
+            if fused:
+                # Compute and all-gather in one kernel: the contiguous row shard of
+                # this rank is written into the full output of every rank.
+                plan = BandPlan(m, world, 1)
+                span = plan.block(0, rank)
+                shard_in = [t[span.begin:span.end].contiguous() if k in ROW_INPUTS[name] else t
+                            for k, t in enumerate(ins)]
+                if name == "reduce":
+                    peer = PeerOutput((2, m), torch.float32, dev)  # sums, then maxima
+                    sharded_outs = [peer.tensor[0], peer.tensor[1]]
+
+                    def kernel_only():
+                        native.reduce_rows_peers(ctx, shard_in[0], peer.bases(span.begin), m)
+                else:
+                    n_cols = full_outs[0].shape[1]
+                    peer = PeerOutput(tuple(full_outs[0].shape), full_outs[0].dtype, dev)
+                    sharded_outs = [peer.tensor]
+                    if name == "softmax":
+                        def kernel_only():
+                            native.softmax_rows_peers(ctx, shard_in[0],
+                                                      peer.bases(span.begin * n_cols), n_cols)
+                    else:
+                        def kernel_only():
+                            native.gemm_bf16_peers(ctx, shard_in[0], shard_in[1],
+                                                   peer.bases(span.begin * n_cols), n_cols)
+
+                def step(do_compute=True, do_gather=True):
+                    if do_compute:
+                        kernel_only()
+                    if do_gather:
+                        peer.fence()
+                out = sharded_outs[0]
+                gathered = (sum(t.numel() * t.element_size() for t in sharded_outs)
+                            * (world - 1) // world)
+            elif name == "reduce":
                 # One in-place all-gather for both vectors: rank r writes its sums and
                 # maxima into pair[r, 0] and pair[r, 1]; two small copies lay them out.
                 share = m // world
@@ -791,8 +836,12 @@ def run_gpu(args):
                 out = sharded_outs[0]
                 gathered = out.numel() * out.element_size() * (world - 1) // world
             units = 1.0
-            collective = (f"ncclAllGather (torch all_gather_into_tensor, in place), "
-                          f"{plan.bands} row band(s), each queued behind its kernel")
+            collective = (
+                "none: the kernel writes its rows into every rank's output over NVLink (peer "
+                "stores into symmetric memory); a 4-byte ncclAllReduce orders the ranks"
+                if fused else
+                f"ncclAllGather (torch all_gather_into_tensor, in place), {plan.bands} row "
+                f"band(s), each queued behind its kernel")
         else:  # "cols": N of the dequant GEMM
             a, w, sc = ins
             n = w.shape[1]
@@ -804,17 +853,34 @@ def run_gpu(args):
             out_s = torch.empty(a.shape[0], span.size, device=dev, dtype=torch.bfloat16)
             staging = torch.empty(world, a.shape[0], span.size, device=dev, dtype=torch.bfloat16)
             sharded_outs = [torch.empty_like(full_outs[0])]
+            fused = args.gather == "fused-all" and name in FUSED_GATHER_ALL
+            if fused:
+                # The epilogue writes this rank's column block into every rank's [M, N].
+                peer = PeerOutput(tuple(full_outs[0].shape), torch.bfloat16, dev)
+                sharded_outs = [peer.tensor]
+                ws = torch.empty(native.w8a16_workspace_bytes(span.size, w.shape[0]),
+                                 dtype=torch.uint8, device=dev)
 
-            def step(do_compute=True, do_gather=True):
-                if do_compute:
-                    call([a, w_s, sc_s], [out_s])
-                if do_gather:
-                    launcher.gather_cols_even(out_s, staging, sharded_outs[0],
-                                              lambda src, dst: native.copy2d(ctx, src, dst))
+                def step(do_compute=True, do_gather=True):
+                    if do_compute:
+                        native.gemm_w8a16_peers(ctx, a, w_s, sc_s, peer.bases(span.begin), n, ws)
+                    if do_gather:
+                        peer.fence()
+            else:
+                def step(do_compute=True, do_gather=True):
+                    if do_compute:
+                        call([a, w_s, sc_s], [out_s])
+                    if do_gather:
+                        launcher.gather_cols_even(out_s, staging, sharded_outs[0],
+                                                  lambda src, dst: native.copy2d(ctx, src, dst))
             units = 1.0
             gathered = out_s.numel() * 2 * (world - 1)
-            collective = ("ncclAllGather of [M, N/g] column blocks into [g, M, N/g], then g "
-                          "strided copies (hc_copy2d) into [M, N]")
+            collective = (
+                "none: the epilogue writes its column block into every rank's output over NVLink "
+                "(peer stores into symmetric memory); a 4-byte ncclAllReduce orders the ranks"
+                if fused else
+                "ncclAllGather of [M, N/g] column blocks into [g, M, N/g], then g strided copies "
+                "(hc_copy2d) into [M, N]")
 
         torch.cuda.synchronize(dev)
         if regions:
@@ -841,12 +907,21 @@ def run_gpu(args):
                       "single_gpu_ms": one_ms, "kernel_speedup": one_ms / k_ms,
                       "total_speedup": one_ms / ms_per_step,
                       "gather_bytes_in_per_rank": gathered,
-                      "gather_gbs_in_per_rank": gathered / g_ms / 1e6,
-                      "nvlink_peak_gbs_per_direction": 900, "collective": collective}
+                      # Bytes every rank receives (and sends) over NVLink per step, over
+                      # the phase that moves them: the collective, or - when the kernel
+                      # does the gather itself - the kernel.
+                      "gather_gbs_in_per_rank": gathered / (k_ms if fused else g_ms) / 1e6,
+                      "nvlink_gbs_per_direction": {"nominal": 900, "measured_peer_copy": 770},
+                      "fused": bool(fused), "collective": collective}
             # The roofline is the kernel's: this GPU's share of the problem in the
             # time its kernels take when nothing else runs.
             roof = roofline(name, k_ms, 1.0 / world)[1]
             roof["of"] = "the kernel phase of one GPU (its 1/%d share of the problem)" % world
+            if fused:
+                roof["of"] += ("; the kernel also writes its share into the other %d GPUs over "
+                               "NVLink, which is what bounds it when the output is large"
+                               % (world - 1))
+                roof["nvlink_frac_of_measured_peer_copy"] = gathered / k_ms / 1e6 / 770.0
             # Sharded == single GPU, bit for bit, on every rank.
             step()
             single()
@@ -1000,10 +1075,10 @@ def run_gpu(args):
             "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic: " + head["data"],
             "config": {"workload": describe(name),
                        "sharding": {"rows": "rows of the fixed full-size problem split over the "
-                                            "ranks in row bands; the output all-gather (NCCL) is "
-                                            "inside the timed step",
-                                    "cols": "output columns split over the ranks, all-gather inside "
-                                            "the timed step",
+                                            "ranks; every rank ends the timed step with the whole "
+                                            "output (phases.collective says how)",
+                                    "cols": "output columns split over the ranks; every rank ends "
+                                            "the timed step with the whole output",
                                     "replicas": "independent replicas, no collective",
                                     "single GPU": "one GPU"}[mode],
                        "l2": {"gemm_f32": "operands fit in L2 (latency-bound case)",
@@ -1053,6 +1128,10 @@ def main():
     ap.add_argument("--replicas", action="store_true",
                     help="with several GPUs: every rank runs the whole problem on its own "
                          "(weak scaling, no collective) instead of sharding the fixed problem")
+    ap.add_argument("--gather", default="fused", choices=["fused", "fused-all", "nccl"],
+                    help="how the sharded run assembles the full output on every rank: the "
+                         "kernels write into every rank's buffer themselves (peer stores over "
+                         "NVLink), or NCCL's all-gather runs behind them")
     ap.add_argument("--bands", type=int, default=0,
                     help="row bands of the sharded run (0: the workload's default)")
     ap.add_argument("--small", action="store_true",

@@ -69,6 +69,12 @@ class HcMapProgram(C.Structure):
     ]
 
 
+class HcPeerOutputs(C.Structure):
+    """include/hc_b200_kernels.h: where a rank's rows go in every rank's buffer."""
+
+    _fields_ = [("base", _vp * 8), ("count", C.c_int)]
+
+
 class HcItemProgram(C.Structure):
     """include/hc_b200_kernels.h: the arrays and the program of hcWorkItems."""
 
@@ -168,6 +174,19 @@ KERNELS_PROTOTYPES = {
     "hcSoftmaxRows": (C.c_int, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, C.c_int]),
     "hcReduceRows": (C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]),
     "hcReduceAll": (C.c_int, [_vp, _vp, _ll, _vp, C.c_int, C.c_int]),
+    "hcSoftmaxRowsPeers": (
+        C.c_int, [_vp, _vp, C.POINTER(HcPeerOutputs), _ll, _ll, _ll, _ll, C.c_int]
+    ),
+    "hcGemmBf16Peers": (
+        C.c_int, [_vp, _vp, _vp, C.POINTER(HcPeerOutputs), _ll, _ll, _ll, _ll, _ll, _ll]
+    ),
+    "hcGemmW8A16Peers": (
+        C.c_int, [_vp, _vp, _vp, _vp, C.POINTER(HcPeerOutputs), _vp, _sz, _ll, _ll, _ll, _ll,
+                  _ll, _ll]
+    ),
+    "hcReduceRowsPeers": (
+        C.c_int, [_vp, _vp, C.POINTER(HcPeerOutputs), _ll, _ll, _ll, _ll, C.c_int]
+    ),
     "hcPairwiseDistance": (
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, C.c_int]
     ),
@@ -339,6 +358,44 @@ class Context:
         self._check(
             self.lib.hcReduceRows(self.handle, x, sum_out, max_out, rows, cols, pitch, dtype),
             "hcReduceRows",
+        )
+
+    @staticmethod
+    def _peers(bases):
+        dsts = HcPeerOutputs()
+        for d, base in enumerate(bases):
+            dsts.base[d] = base
+        dsts.count = len(bases)
+        return dsts
+
+    def softmax_rows_peers(self, x, bases, rows, cols, x_pitch, y_pitch, dtype=HC_F32):
+        """``bases``: where this call's row 0 goes in every destination buffer."""
+        self._check(
+            self.lib.hcSoftmaxRowsPeers(self.handle, x, C.byref(self._peers(bases)), rows, cols,
+                                        x_pitch, y_pitch, dtype),
+            "hcSoftmaxRowsPeers",
+        )
+
+    def gemm_bf16_peers(self, a, b, bases, m, n, k, lda, ldb, ldc):
+        self._check(
+            self.lib.hcGemmBf16Peers(self.handle, a, b, C.byref(self._peers(bases)), m, n, k, lda,
+                                     ldb, ldc),
+            "hcGemmBf16Peers",
+        )
+
+    def gemm_w8a16_peers(self, a, w, scale, bases, workspace, workspace_bytes, m, n, k, lda, ldw,
+                         ldc):
+        self._check(
+            self.lib.hcGemmW8A16Peers(self.handle, a, w, scale, C.byref(self._peers(bases)),
+                                      workspace, workspace_bytes, m, n, k, lda, ldw, ldc),
+            "hcGemmW8A16Peers",
+        )
+
+    def reduce_rows_peers(self, x, bases, max_offset, rows, cols, pitch, dtype=HC_F32):
+        self._check(
+            self.lib.hcReduceRowsPeers(self.handle, x, C.byref(self._peers(bases)), max_offset,
+                                       rows, cols, pitch, dtype),
+            "hcReduceRowsPeers",
         )
 
     def reduce_all(self, a, n, result, in_dtype=HC_F32, result_dtype=HC_F32):

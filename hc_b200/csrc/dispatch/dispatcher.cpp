@@ -244,6 +244,67 @@ void gemmBf16Host(Context &ctx, py::handle a, py::handle b, py::handle out) {
   ctx.check(rc, "gemm_bf16_host");
 }
 
+// The same two workloads writing their rows into every rank's output buffer
+// (hcSoftmaxRowsPeers, hcReduceRowsPeers): `bases` are raw device addresses -
+// this GPU's memory or peer memory mapped into the process - of where the
+// call's row 0 goes in each destination.
+HcPeerOutputs peerOutputs(const std::vector<uintptr_t> &bases) {
+  if (bases.empty() || bases.size() > 8)
+    throw py::value_error("1..8 destination addresses expected");
+  HcPeerOutputs dsts{};
+  for (size_t d = 0; d < bases.size(); ++d)
+    dsts.base[d] = reinterpret_cast<void *>(bases[d]);
+  dsts.count = int(bases.size());
+  return dsts;
+}
+
+void softmaxRowsPeers(Context &ctx, py::handle x, const std::vector<uintptr_t> &bases,
+                      long long outPitch) {
+  ArrayArg a = deviceArray(ctx, x, "x", 2);
+  HcPeerOutputs dsts = peerOutputs(bases);
+  ctx.check(hcSoftmaxRowsPeers(ctx.get(), a.data, &dsts, a.shape[0], a.shape[1], pitch(a),
+                               outPitch, floatDType(a, "x")),
+            "softmax_rows_peers");
+}
+
+void gemmBf16Peers(Context &ctx, py::handle a, py::handle b, const std::vector<uintptr_t> &bases,
+                   long long outPitch) {
+  ArrayArg A = deviceArray(ctx, a, "a", 2), B = deviceArray(ctx, b, "b", 2);
+  if (A.kind != ElemKind::BF16 || B.kind != ElemKind::BF16)
+    throw py::type_error("gemm_bf16_peers: bfloat16 matrices expected");
+  if (A.shape[1] != B.shape[0])
+    throw py::value_error("gemm_bf16_peers: shapes do not form [M,K] @ [K,N]");
+  HcPeerOutputs dsts = peerOutputs(bases);
+  ctx.check(hcGemmBf16Peers(ctx.get(), A.data, B.data, &dsts, A.shape[0], B.shape[1], A.shape[1],
+                            pitch(A), pitch(B), outPitch),
+            "gemm_bf16_peers");
+}
+
+void gemmW8A16Peers(Context &ctx, py::handle a, py::handle w, py::handle scale,
+                    const std::vector<uintptr_t> &bases, long long outPitch,
+                    py::handle workspace) {
+  ArrayArg A = deviceArray(ctx, a, "a", 2), W = deviceArray(ctx, w, "w", 2),
+           S = deviceArray(ctx, scale, "scale", 1), ws = deviceArray(ctx, workspace, "workspace", 1);
+  if (A.kind != ElemKind::BF16 || W.kind != ElemKind::I8 || S.kind != ElemKind::F32)
+    throw py::type_error("gemm_w8a16_peers: a bfloat16, w int8, scale float32 expected");
+  if (A.shape[1] != W.shape[0] || S.shape[0] != W.shape[1])
+    throw py::value_error("gemm_w8a16_peers: shapes do not form [M,K] @ [K,N] with scale [N]");
+  HcPeerOutputs dsts = peerOutputs(bases);
+  ctx.check(hcGemmW8A16Peers(ctx.get(), A.data, W.data, static_cast<const float *>(S.data), &dsts,
+                             ws.data, size_t(ws.shape[0]) * size_t(ws.itemsize), A.shape[0],
+                             W.shape[1], A.shape[1], pitch(A), pitch(W), outPitch),
+            "gemm_w8a16_peers");
+}
+
+void reduceRowsPeers(Context &ctx, py::handle x, const std::vector<uintptr_t> &bases,
+                     long long maxOffset) {
+  ArrayArg a = deviceArray(ctx, x, "x", 2);
+  HcPeerOutputs dsts = peerOutputs(bases);
+  ctx.check(hcReduceRowsPeers(ctx.get(), a.data, &dsts, maxOffset, a.shape[0], a.shape[1],
+                              pitch(a), floatDType(a, "x")),
+            "reduce_rows_peers");
+}
+
 void reduceAll(Context &ctx, py::handle a, py::handle result) {
   ArrayArg A = deviceArray(ctx, a, "a", 1), R = deviceArray(ctx, result, "result", 1);
   if (A.shape[0] > 1 && A.strides[0] != 1)
@@ -587,6 +648,14 @@ PYBIND11_MODULE(_dispatcher, m) {
   m.def("reduce_rows", &reduceRows, py::arg("ctx"), py::arg("x"),
         py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());
   m.def("reduce_all", &reduceAll, py::arg("ctx"), py::arg("a"), py::arg("result"));
+  m.def("softmax_rows_peers", &softmaxRowsPeers, py::arg("ctx"), py::arg("x"), py::arg("bases"),
+        py::arg("out_pitch"));
+  m.def("gemm_bf16_peers", &gemmBf16Peers, py::arg("ctx"), py::arg("a"), py::arg("b"),
+        py::arg("bases"), py::arg("out_pitch"));
+  m.def("gemm_w8a16_peers", &gemmW8A16Peers, py::arg("ctx"), py::arg("a"), py::arg("w"),
+        py::arg("scale"), py::arg("bases"), py::arg("out_pitch"), py::arg("workspace"));
+  m.def("reduce_rows_peers", &reduceRowsPeers, py::arg("ctx"), py::arg("x"), py::arg("bases"),
+        py::arg("max_offset"));
   m.def("softmax_rows_host", &softmaxRowsHost, py::arg("ctx"), py::arg("x"), py::arg("out"));
   m.def("reduce_rows_host", &reduceRowsHost, py::arg("ctx"), py::arg("x"),
         py::arg("sum_out") = py::none(), py::arg("max_out") = py::none());

@@ -32,7 +32,13 @@
 // Every mbarrier wait is bounded (hc_ptx.cuh); a wait that runs out records a
 // code in `status`, raises a CTA-wide abort flag that makes all roles leave
 // their loops, and the kernel exits through the normal teardown.
+//
+// PEERS: the epilogue writes every output tile to all destinations of `peers`
+// (this GPU's copy of C and the copies of the other GPUs of a multi-GPU job,
+// peer memory reached with plain stores over NVLink) - the output all-gather of
+// an M- or N-sharded product done by the kernel itself.
 #include "hc_ptx.cuh"
+#include "peer_params.h"
 
 namespace {
 
@@ -85,11 +91,12 @@ __device__ __forceinline__ void tileCoords(int t, const Params &p, int &tm,
   tn = rem / rowsInBand;
 }
 
-template <bool PAIR, bool SCALED>
+template <bool PAIR, bool SCALED, bool PEERS = false>
 __device__ __forceinline__ void
 gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
          __nv_bfloat16 *__restrict__ c, const float *__restrict__ scale,
-         const Params &p, int *status, unsigned char *smemRaw) {
+         const Params &p, int *status, unsigned char *smemRaw,
+         const HcPeerDsts *peers = nullptr) {
   using Cfg = Config<PAIR>;
   // The swizzled stages need 1024-byte alignment.
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
@@ -272,7 +279,7 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
       const long long colBase = (long long)tn * BN;
       const uint32_t taddr =
           tmemBase + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
-      __nv_bfloat16 *crow = c + row * p.ldc;
+      const int destinations = PEERS ? peers->count : 1;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
         uint32_t v[32];
@@ -280,48 +287,53 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
         tmemLoad32x32(taddr + uint32_t(ch * 32), v);
         tmemLoadWait();
         const long long col = colBase + ch * 32;
-        if (row >= p.M || col >= p.N)
-          continue;
-        float f[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          f[j] = __uint_as_float(v[j]);
-        if constexpr (SCALED) {
-          if (col + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float4 s =
-                  __ldg(reinterpret_cast<const float4 *>(scale + col + j));
-              f[j] *= s.x;
-              f[j + 1] *= s.y;
-              f[j + 2] *= s.z;
-              f[j + 3] *= s.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col + j < p.N)
-                f[j] *= __ldg(scale + col + j);
-          }
-        }
-        if (p.vecStore && col + 32 <= p.N) {
-          uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              __nv_bfloat162 h =
-                  __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
-              w[j] = *reinterpret_cast<uint32_t *>(&h);
-            }
-            dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        } else {
+        if (col >= p.N) // the same for the whole warp
+          break;
+        if (row < p.M) { // per lane: only loads and stores are predicated
+          float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col + j < p.N)
-              crow[col + j] = __float2bfloat16_rn(f[j]);
+            f[j] = __uint_as_float(v[j]);
+          if constexpr (SCALED) {
+            if (col + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 s =
+                    __ldg(reinterpret_cast<const float4 *>(scale + col + j));
+                f[j] *= s.x;
+                f[j + 1] *= s.y;
+                f[j + 2] *= s.z;
+                f[j + 3] *= s.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N)
+                  f[j] *= __ldg(scale + col + j);
+            }
+          }
+          uint32_t w[16]; // the 32 values rounded to bf16, two per word
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t *>(&h);
+          }
+          for (int d = 0; d < destinations; ++d) {
+            __nv_bfloat16 *crow =
+                (PEERS ? static_cast<__nv_bfloat16 *>(peers->base[d]) : c) + row * p.ldc;
+            if (p.vecStore && col + 32 <= p.N) {
+              uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < p.N)
+                  crow[col + j] = __ushort_as_bfloat16(
+                      static_cast<unsigned short>(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xffffu));
+            }
+          }
         }
       }
       // This warp has read its quarter of the accumulator.
@@ -384,4 +396,33 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1)
     __launch_bounds__(NUM_THREADS, 1)
         hc_gemm_bf16_umma_pair_scaled(HC_GEMM_ARGS) {
   HC_GEMM_BODY(true, true)
+}
+
+// The same four kernels writing every tile to all destinations of `peers`.
+#define HC_GEMM_PEERS_BODY(PAIR, SCALED)                                       \
+  extern __shared__ __align__(1024) unsigned char smemRaw[];                   \
+  Params p{M, N, K, ldc, tilesM, tilesN, bandM, vecStore};                     \
+  gemmUmma<PAIR, SCALED, true>(&mapA, &mapB, c, scale, p, status, smemRaw,     \
+                               &peers);
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma_peers(HC_GEMM_ARGS, const __grid_constant__ HcPeerDsts peers) {
+  HC_GEMM_PEERS_BODY(false, false)
+}
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma_scaled_peers(HC_GEMM_ARGS,
+                                   const __grid_constant__ HcPeerDsts peers) {
+  HC_GEMM_PEERS_BODY(false, true)
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma_pair_peers(HC_GEMM_ARGS, const __grid_constant__ HcPeerDsts peers) {
+  HC_GEMM_PEERS_BODY(true, false)
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_bf16_umma_pair_scaled_peers(HC_GEMM_ARGS,
+                                        const __grid_constant__ HcPeerDsts peers) {
+  HC_GEMM_PEERS_BODY(true, true)
 }

@@ -16,6 +16,7 @@
 // the outputs are 4 or 8 bytes per row, so the kernel moves
 // rows*cols*sizeof(T) bytes and is HBM-bound.
 #include "hc_ptx.cuh"
+#include "peer_params.h"
 
 #include <math.h>
 
@@ -155,7 +156,37 @@ reduceBlockRows(const T *__restrict__ x, T *__restrict__ sumOut,
   }
 }
 
+// One warp per row, the two results of a row written to every destination of
+// `peers`: base[d] holds the sums of this kernel's rows, followed `maxOffset`
+// elements later by their maxima (the output all-gather of a multi-GPU run done
+// by the kernel itself).
+template <typename T>
+__device__ __forceinline__ void reduceWarpRowsPeers(const T *__restrict__ x, long long rows,
+                                                    long long cols, long long pitch, int vec,
+                                                    long long maxOffset,
+                                                    const HcPeerDsts &peers) {
+  const int lane = threadIdx.x & 31;
+  const long long warpsPerGrid = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows;
+       r += warpsPerGrid) {
+    Acc<T> a = warpCombine(rowPartial<T>(x + r * pitch, cols, lane, 32, vec));
+    // Lane d writes destination d.
+    if (lane < peers.count) {
+      T *out = static_cast<T *>(peers.base[lane]);
+      out[r] = a.sum;
+      out[maxOffset + r] = a.max;
+    }
+  }
+}
+
 } // namespace
+
+extern "C" __global__ void __launch_bounds__(256)
+    hc_reduce_rows_warp_f32_peers(const float *x, long long rows, long long cols,
+                                  long long pitch, int vec, long long maxOffset,
+                                  const __grid_constant__ HcPeerDsts peers) {
+  reduceWarpRowsPeers<float>(x, rows, cols, pitch, vec, maxOffset, peers);
+}
 
 extern "C" __global__ void __launch_bounds__(256)
     hc_reduce_rows_warp_f32(const float *x, float *sumOut, float *maxOut,

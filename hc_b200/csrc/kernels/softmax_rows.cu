@@ -16,6 +16,7 @@
 //       pitch or alignment; the row is cached in shared memory when it fits
 //       and re-read otherwise.
 #include "hc_ptx.cuh"
+#include "peer_params.h"
 
 #include <float.h>
 #include <math.h>
@@ -47,10 +48,16 @@ __device__ __forceinline__ float fastExp2(float x) {
 // One warp per row.  `cols` is a multiple of 4 and at most 128 * V; both row
 // pitches are multiples of 4 elements and both bases 16-byte aligned (the
 // host dispatcher guarantees all of it).
-template <int V>
+//
+// PEERS: the result row is written to every destination of `peers` (row r at
+// base[d] + r * yPitch) instead of `y` - the output all-gather of a multi-GPU run
+// done by the kernel itself: every GPU writes its rows straight into the full
+// output of every GPU, over NVLink for the others.
+template <int V, bool PEERS = false>
 __device__ __forceinline__ void
 softmaxWarpRows(const float *__restrict__ x, float *__restrict__ y,
-                long long rows, int cols, long long xPitch, long long yPitch) {
+                long long rows, int cols, long long xPitch, long long yPitch,
+                const HcPeerDsts *peers = nullptr) {
   const int lane = threadIdx.x & 31;
   const long long warpsPerGrid = (long long)gridDim.x * (blockDim.x >> 5);
   const long long firstRow =
@@ -91,12 +98,28 @@ softmaxWarpRows(const float *__restrict__ x, float *__restrict__ y,
       s1 += v[i].y + v[i].w;
     }
     const float inv = 1.0f / warpSum(s0 + s1);
+    if constexpr (PEERS) {
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      int p = lane + 32 * i;
-      if (p < packets)
-        hc::storeStream(dst + p, make_float4(v[i].x * inv, v[i].y * inv,
-                                             v[i].z * inv, v[i].w * inv));
+      for (int i = 0; i < V; ++i)
+        v[i] = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+      for (int d = 0; d < peers->count; ++d) {
+        float4 *out = reinterpret_cast<float4 *>(static_cast<float *>(peers->base[d]) +
+                                                 r * yPitch);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          int p = lane + 32 * i;
+          if (p < packets)
+            out[p] = v[i];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        int p = lane + 32 * i;
+        if (p < packets)
+          hc::storeStream(dst + p, make_float4(v[i].x * inv, v[i].y * inv,
+                                               v[i].z * inv, v[i].w * inv));
+      }
     }
   }
 }
@@ -179,6 +202,22 @@ HC_SOFTMAX_WARP(4, 8)
 HC_SOFTMAX_WARP(8, 8)
 HC_SOFTMAX_WARP(16, 5)
 HC_SOFTMAX_WARP(32, 3)
+
+// The same kernels writing every row to all destinations of `peers`.
+#define HC_SOFTMAX_WARP_PEERS(V, MINB)                                         \
+  extern "C" __global__ void __launch_bounds__(128, MINB)                      \
+      hc_softmax_rows_f32_w##V##_peers(const float *x, long long rows, int cols, \
+                                       long long xPitch, long long yPitch,     \
+                                       const __grid_constant__ HcPeerDsts peers) { \
+    softmaxWarpRows<V, true>(x, nullptr, rows, cols, xPitch, yPitch, &peers);  \
+  }
+
+HC_SOFTMAX_WARP_PEERS(1, 8)
+HC_SOFTMAX_WARP_PEERS(2, 8)
+HC_SOFTMAX_WARP_PEERS(4, 8)
+HC_SOFTMAX_WARP_PEERS(8, 8)
+HC_SOFTMAX_WARP_PEERS(16, 5)
+HC_SOFTMAX_WARP_PEERS(32, 3)
 
 // ---- bulk-copy pipelined variant --------------------------------------------------
 // One persistent CTA per SM: a producer thread streams whole rows into a ring

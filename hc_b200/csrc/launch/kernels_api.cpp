@@ -13,6 +13,7 @@
 #include "../kernels/items_params.h"
 #include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
+#include "../kernels/peer_params.h"
 
 #include <cuda.h> // CUtensorMap (type only; no driver call is made here)
 #include <dlfcn.h>
@@ -71,6 +72,13 @@ const KernelEntry kKernelTable[] = {
     {"hc_softmax_rows_f32_w8", "softmax_rows"},
     {"hc_softmax_rows_f32_w16", "softmax_rows"},
     {"hc_softmax_rows_f32_w32", "softmax_rows"},
+    {"hc_softmax_rows_f32_w1_peers", "softmax_rows"},
+    {"hc_softmax_rows_f32_w2_peers", "softmax_rows"},
+    {"hc_softmax_rows_f32_w4_peers", "softmax_rows"},
+    {"hc_softmax_rows_f32_w8_peers", "softmax_rows"},
+    {"hc_softmax_rows_f32_w16_peers", "softmax_rows"},
+    {"hc_softmax_rows_f32_w32_peers", "softmax_rows"},
+    {"hc_reduce_rows_warp_f32_peers", "reduce_rows"},
     {"hc_softmax_rows_f32_tma_v16", "softmax_rows"},
     {"hc_softmax_rows_f32_tma_v32", "softmax_rows"},
     {"hc_softmax_rows_generic_f32", "softmax_rows"},
@@ -102,6 +110,10 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_bf16_umma_scaled", "gemm_bf16_umma"},
     {"hc_gemm_bf16_umma_pair", "gemm_bf16_umma"},
     {"hc_gemm_bf16_umma_pair_scaled", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_peers", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_scaled_peers", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_pair_peers", "gemm_bf16_umma"},
+    {"hc_gemm_bf16_umma_pair_scaled_peers", "gemm_bf16_umma"},
     {"hc_dequant_w8_bf16", "dequant_w8"},
     {"hc_split_tf32", "gemm_f32_umma"},
     {"hc_split_tf32_t", "gemm_f32_umma"},
@@ -915,6 +927,76 @@ int hcSoftmaxRows(HcContext c, const void *x, void *y, long long rows,
                    size_t(grid), 1, 1, 256, args, 7, smem);
 }
 
+// ---- compute and all-gather in one kernel ------------------------------------------
+static_assert(sizeof(HcPeerOutputs) == sizeof(HcPeerDsts) &&
+                  offsetof(HcPeerOutputs, count) == offsetof(HcPeerDsts, count),
+              "public destination list and kernel parameter block differ");
+
+static int checkPeers(HcContext c, const char *who, const HcPeerOutputs *dsts) {
+  if (!dsts || dsts->count < 1 || dsts->count > HC_MAX_PEERS)
+    return c->fail("%s: 1..%d destinations expected", who, HC_MAX_PEERS);
+  for (int d = 0; d < dsts->count; ++d)
+    if (!dsts->base[d] || !aligned(dsts->base[d], 16))
+      return c->fail("%s: destination %d is null or not 16-byte aligned", who, d);
+  return 0;
+}
+
+int hcSoftmaxRowsPeers(HcContext c, const void *x, const HcPeerOutputs *dsts, long long rows,
+                       long long cols, long long xPitch, long long yPitch, int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32)
+    return c->fail("hcSoftmaxRowsPeers: float32 only");
+  if (rows < 0 || cols < 0 || xPitch < cols || yPitch < cols)
+    return c->fail("hcSoftmaxRowsPeers: invalid shape %lld x %lld", rows, cols);
+  if (checkPeers(c, "hcSoftmaxRowsPeers", dsts))
+    return 1;
+  if (rows == 0 || cols == 0)
+    return 0;
+  if (!x)
+    return c->fail("hcSoftmaxRowsPeers: null buffer");
+  if (cols % 4 || cols > 4096 || xPitch % 4 || yPitch % 4 || !aligned(x, 16))
+    return c->fail("hcSoftmaxRowsPeers: rows of at most 4096 columns, a multiple of 4, and "
+                   "16-byte aligned bases and pitches (use hcSoftmaxRows and a collective "
+                   "otherwise)");
+  int v = 1;
+  while (128 * v < cols)
+    v <<= 1;
+  char name[48];
+  snprintf(name, sizeof(name), "hc_softmax_rows_f32_w%d_peers", v);
+  long long grid = std::min<long long>(ceilDiv(rows, 4), 0x7fffffffLL);
+  int icols = int(cols);
+  HcPeerDsts peers;
+  std::memcpy(&peers, dsts, sizeof peers);
+  void *args[] = {&x, &rows, &icols, &xPitch, &yPitch, &peers};
+  return c->launch(name, size_t(grid), 1, 1, 128, args, 6, 0);
+}
+
+int hcReduceRowsPeers(HcContext c, const void *x, const HcPeerOutputs *dsts,
+                      long long maxOffset, long long rows, long long cols, long long pitch,
+                      int dtype) {
+  if (!c)
+    return 1;
+  if (dtype != HC_F32)
+    return c->fail("hcReduceRowsPeers: float32 only");
+  if (rows < 0 || cols < 0 || pitch < cols || maxOffset < rows)
+    return c->fail("hcReduceRowsPeers: invalid shape %lld x %lld (maxima %lld elements after "
+                   "the sums)",
+                   rows, cols, maxOffset);
+  if (checkPeers(c, "hcReduceRowsPeers", dsts))
+    return 1;
+  if (rows == 0)
+    return 0;
+  if (!x && cols > 0)
+    return c->fail("hcReduceRowsPeers: null buffer");
+  int vec = cols % 4 == 0 && pitch % 4 == 0 && aligned(x, 16);
+  long long grid = std::min<long long>(ceilDiv(rows, 8), 0x7fffffffLL);
+  HcPeerDsts peers;
+  std::memcpy(&peers, dsts, sizeof peers);
+  void *args[] = {&x, &rows, &cols, &pitch, &vec, &maxOffset, &peers};
+  return c->launch("hc_reduce_rows_warp_f32_peers", size_t(grid), 1, 1, 256, args, 7, 0);
+}
+
 // ---- reductions -----------------------------------------------------------------
 int hcReduceRows(HcContext c, const void *x, void *sumOut, void *maxOut,
                  long long rows, long long cols, long long pitch, int dtype) {
@@ -1121,7 +1203,7 @@ int hcGemmTiled(HcContext c, const void *a, const void *b, void *out,
 static int launchUmma(HcContext c, const void *a, const void *b,
                       const float *scale, void *out, long long M, long long N,
                       long long K, long long lda, long long ldb, long long ldc,
-                      bool pair) {
+                      bool pair, const HcPeerOutputs *dsts = nullptr) {
   alignas(64) CUtensorMap mapA, mapB;
   if (olxEncodeTensorMap2D(c->device, &mapA, /*bf16*/ 0, a, size_t(M), size_t(K),
                            size_t(lda) * 2, kUmmaBM, kUmmaBK, 128) ||
@@ -1134,11 +1216,18 @@ static int launchUmma(HcContext c, const void *a, const void *b,
   // that the A and B panels they share stay in L2.
   int bandM = 16;
   int vecStore = aligned(out, 16) && ldc % 8 == 0;
+  HcPeerDsts peers{};
+  if (dsts) {
+    // Every destination takes the same tiles: all must allow 16-byte stores.
+    std::memcpy(&peers, dsts, sizeof peers);
+    vecStore = ldc % 8 == 0;
+    for (int d = 0; d < peers.count; ++d)
+      vecStore = vecStore && aligned(peers.base[d], 16);
+  }
   long long tiles = (long long)tilesM * tilesN;
-  const char *name = pair ? (scale ? "hc_gemm_bf16_umma_pair_scaled"
-                                   : "hc_gemm_bf16_umma_pair")
-                          : (scale ? "hc_gemm_bf16_umma_scaled"
-                                   : "hc_gemm_bf16_umma");
+  char name[56];
+  std::snprintf(name, sizeof name, "hc_gemm_bf16_umma%s%s%s", pair ? "_pair" : "",
+                scale ? "_scaled" : "", dsts ? "_peers" : "");
   long long grid = std::min<long long>(tiles, c->smCount);
   if (pair) {
     // The kernel is persistent: CTA pairs beyond what the GPU can hold at once
@@ -1153,9 +1242,9 @@ static int launchUmma(HcContext c, const void *a, const void *b,
     }
     grid = 2 * std::min<long long>(tiles, c->pairSlots);
   }
-  void *args[] = {&mapA,   &mapB,   &out,   &scale,    &M,           &N, &K,
-                  &ldc,    &tilesM, &tilesN, &bandM,   &vecStore, &c->statusWord};
-  return c->launch(name, size_t(grid), 1, 1, kUmmaThreads, args, 13,
+  void *args[] = {&mapA,   &mapB,   &out,   &scale,    &M,           &N,    &K,
+                  &ldc,    &tilesM, &tilesN, &bandM,   &vecStore, &c->statusWord, &peers};
+  return c->launch(name, size_t(grid), 1, 1, kUmmaThreads, args, dsts ? 14 : 13,
                    kUmmaSmemBytes);
 }
 
@@ -1247,6 +1336,53 @@ int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *
   void *args[] = {&maps[0], &maps[1], &maps[2], &maps[3], &out,    &M,        &N,
                   &K,       &ldc,     &tilesM,  &tilesN,  &bandM, &vecStore, &c->statusWord};
   return c->launch("hc_gemm_f32_umma", size_t(grid), 1, 1, 192, args, 14, smem);
+}
+
+int hcGemmBf16Peers(HcContext c, const void *a, const void *b, const HcPeerOutputs *dsts,
+                    long long M, long long N, long long K, long long lda, long long ldb,
+                    long long ldc) {
+  if (!c)
+    return 1;
+  if (checkPeers(c, "hcGemmBf16Peers", dsts))
+    return 1;
+  if (checkGemmShape(c, "hcGemmBf16Peers", a, b, dsts->base[0], M, N, K, lda, ldb, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  if (!ummaEligible(c, a, b, K, lda, ldb))
+    return c->fail("hcGemmBf16Peers: operands the tensor-core kernel cannot take (pitches that "
+                   "are multiples of 8 elements and 16-byte aligned bases; use hcGemmBf16 and a "
+                   "collective otherwise)");
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant != 1 && M > kUmmaBM);
+  return launchUmma(c, a, b, nullptr, dsts->base[0], M, N, K, lda, ldb, ldc, pair, dsts);
+}
+
+int hcGemmW8A16Peers(HcContext c, const void *a, const void *w, const float *scale,
+                     const HcPeerOutputs *dsts, void *workspace, size_t workspaceBytes,
+                     long long M, long long N, long long K, long long lda, long long ldw,
+                     long long ldc) {
+  if (!c)
+    return 1;
+  if (checkPeers(c, "hcGemmW8A16Peers", dsts))
+    return 1;
+  if (checkGemmShape(c, "hcGemmW8A16Peers", a, w, dsts->base[0], M, N, K, lda, ldw, ldc))
+    return 1;
+  if (M == 0 || N == 0)
+    return 0;
+  if (!scale)
+    return c->fail("hcGemmW8A16Peers: null scale");
+  const long long wsPitch = roundUp(N, 16);
+  if (!ummaEligible(c, a, workspace, K, lda, wsPitch))
+    return c->fail("hcGemmW8A16Peers: operands the tensor-core kernel cannot take (use "
+                   "hcGemmW8A16 and a collective)");
+  if (!workspace || workspaceBytes < hcGemmW8A16WorkspaceBytes(N, K))
+    return c->fail("hcGemmW8A16Peers: workspace of %zu bytes is too small, need %zu",
+                   workspaceBytes, hcGemmW8A16WorkspaceBytes(N, K));
+  if (hcDequantW8(c, w, workspace, K, N, ldw, wsPitch))
+    return 1;
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant != 1 && M > kUmmaBM);
+  return launchUmma(c, a, workspace, scale, dsts->base[0], M, N, K, lda, wsPitch, ldc, pair,
+                    dsts);
 }
 
 size_t hcGemmW8A16WorkspaceBytes(long long N, long long K) {

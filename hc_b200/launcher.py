@@ -18,6 +18,17 @@ in the environment) and talk through ``torch.distributed``: NCCL over
 NVLink/NVSwitch for device tensors, gloo when the tensors live on the host
 (which is how the sharding and gathering logic is tested without GPUs).  No
 kernel ever reads another GPU's memory.
+
+Two ways to the gathered output:
+
+* the collective: every rank computes into its block of the full output and
+  ``gather_band`` / ``gather_cols_even`` run NCCL's all-gather (in row bands, so
+  that the gather of one band overlaps the kernel of the next);
+* the kernel itself: with a :class:`PeerOutput` (the full output of every rank in
+  symmetric memory) the ``*_peers`` kernels write a rank's rows straight into
+  every rank's buffer over NVLink - compute and all-gather in one launch, no
+  second pass over the output and no separate collective; a 4-byte all-reduce
+  orders the ranks afterwards.  Kernels only ever *write* peer memory.
 """
 
 from __future__ import annotations
@@ -100,6 +111,39 @@ class BandPlan:
         parts = [full[self.blocks[b][rank].begin:self.blocks[b][rank].end]
                  for b in range(self.bands)]
         return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+
+
+class PeerOutput:
+    """A full output array that every rank holds and every rank can write: one
+    buffer per GPU in symmetric memory (torch.distributed._symmetric_memory),
+    each mapped into every process of the job.
+
+    It is what lets a kernel do the output all-gather itself: the ``*_peers``
+    entry points (include/hc_b200_kernels.h: hcSoftmaxRowsPeers,
+    hcReduceRowsPeers, hcGemmBf16Peers, hcGemmW8A16Peers) take the addresses
+    ``bases(offset)`` and write a rank's rows into all of them with plain stores
+    over NVLink.  No kernel waits for another; ``fence()`` orders the ranks
+    afterwards on the stream (a 4-byte all-reduce), after which every rank may
+    read its ``tensor``."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.tensor = symm_mem.empty(*shape, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.addresses = [int(p) for p in self.handle.buffer_ptrs]
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def bases(self, element_offset: int = 0):
+        """Address of element ``element_offset`` (row-major) in every rank's buffer."""
+        step = element_offset * self.tensor.element_size()
+        return [a + step for a in self.addresses]
+
+    def fence(self):
+        """Every rank's stores issued so far (on the current stream) are complete
+        and visible before any rank's later work on its stream starts."""
+        dist.all_reduce(self._token, group=self.group)
 
 
 def init_process_group(backend: str | None = None):

@@ -220,6 +220,47 @@ HC_B200_API int hcReduceRows(HcContext c, const void *x, void *sumOut,
                              void *maxOut, long long rows, long long cols,
                              long long pitch, int dtype);
 
+/* ---- compute and all-gather in one kernel (multi-GPU) ---------------------------
+ * In a job with one process per GPU every rank computes its rows of the result
+ * and all ranks need the whole of it.  Instead of computing into local memory
+ * and running an all-gather afterwards, these variants write every result row
+ * straight into the full output buffer of EVERY rank: `dsts->base[d]` is where
+ * this rank's row 0 goes in rank d's buffer (its own included) - device memory
+ * of this GPU or peer memory of another GPU mapped into this process (CUDA IPC,
+ * torch symmetric memory).  Plain stores over NVLink; no kernel waits for
+ * another, so nothing can hang: the caller orders the ranks afterwards (any
+ * cross-rank barrier on the stream) before anyone reads the buffers.  No
+ * counterpart in the reference, which drives one device per process
+ * (python/cpp/py-runtime/src/GpuRuntime.cpp:23-24).
+ *
+ * hcSoftmaxRowsPeers: float32 rows of at most 4096 columns, a multiple of 4,
+ * 16-byte aligned bases and pitches (the register kernel of hcSoftmaxRows).
+ * hcReduceRowsPeers: sums to base[d][r], maxima to base[d][maxOffset + r]. */
+typedef struct HcPeerOutputs {
+  void *base[8];
+  int count; /* 1..8 */
+} HcPeerOutputs;
+HC_B200_API int hcSoftmaxRowsPeers(HcContext c, const void *x, const HcPeerOutputs *dsts,
+                                   long long rows, long long cols, long long xPitch,
+                                   long long yPitch, int dtype);
+HC_B200_API int hcReduceRowsPeers(HcContext c, const void *x, const HcPeerOutputs *dsts,
+                                  long long maxOffset, long long rows, long long cols,
+                                  long long pitch, int dtype);
+
+/* The tensor-core GEMMs with the same kind of output (hcGemmBf16 / hcGemmW8A16
+ * otherwise): base[d] is where element [0, 0] of this call's output block goes
+ * in rank d's copy of C, `ldc` the pitch of the full C - an M-shard passes its
+ * row block's address, an N-shard its column block's.  Operands that the
+ * tensor-core kernel cannot take are refused (there is no CUDA-core form). */
+HC_B200_API int hcGemmBf16Peers(HcContext c, const void *a, const void *b,
+                                const HcPeerOutputs *dsts, long long M, long long N,
+                                long long K, long long lda, long long ldb, long long ldc);
+HC_B200_API int hcGemmW8A16Peers(HcContext c, const void *a, const void *w,
+                                 const float *scale, const HcPeerOutputs *dsts,
+                                 void *workspace, size_t workspaceBytes, long long M,
+                                 long long N, long long K, long long lda, long long ldw,
+                                 long long ldc);
+
 /* Whole-array sum added to one element: result[0] += sum(a[0:n]).  `a` is
  * HC_F32, HC_F64, HC_I32 or HC_I64; `result` is HC_F32 or HC_F64 and is not
  * cleared first (the reference's atomic_ref(result)[0] += tile.sum(),

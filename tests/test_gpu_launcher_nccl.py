@@ -1,5 +1,6 @@
 """Two-GPU run of the sharded launcher with the real kernels and NCCL: every
-rank computes its shard on its own GPU, the outputs are all-gathered, and each
+rank computes its shard on its own GPU, the outputs are all-gathered - by NCCL,
+and by the kernels that write into both ranks' buffers themselves - and each
 rank checks the gathered result against the CPU oracle of the whole problem.
 Skipped on a box with fewer than two GPUs (the single-GPU suite covers the
 kernels; tests/test_launcher_gloo.py covers the sharding logic on CPU)."""
@@ -125,6 +126,85 @@ def _worker(rank, world, port, results):
         L.gather_rows(ys, full)
         ok["map_body"] = bool(np.array_equal(full.cpu().numpy(),
                                              np.maximum(x * np.float32(2) - np.float32(1), 0)))
+
+        # Compute and all-gather in one kernel: every rank writes its shard into the
+        # full output of both ranks (symmetric memory, stores over NVLink); a small
+        # all-reduce orders the ranks; then every rank holds the whole result.
+        from hc_b200._native import _dispatcher as native
+        from hc_b200.launcher import PeerOutput
+
+        ctx = get_context(f"cuda:{rank}")
+        stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+        rows, cols = 600, 2048
+        (x,) = oracle.make_inputs("softmax", shape=(rows, cols))
+        span = L.rows(rows)
+        xs = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        peer = PeerOutput((rows, cols), torch.float32, dev)
+        peer.tensor.fill_(float("nan"))
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            native.softmax_rows_peers(ctx, xs, peer.bases(span.begin * cols), cols)
+            peer.fence()
+            stream.synchronize()
+        expect = np.zeros_like(x)
+        oracle.softmax_rows(x, expect, 256)
+        got = peer.tensor.cpu().numpy()
+        ok["softmax_peers"] = bool(np.all(np.abs(got - expect) <= 1e-6 + 1e-5 * np.abs(expect)))
+
+        (x,) = oracle.make_inputs("reduce", shape=(rows, 1024))
+        xs = torch.from_numpy(x[span.begin:span.end]).to(dev)
+        both = PeerOutput((2, rows), torch.float32, dev)
+        both.tensor.fill_(float("nan"))
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            native.reduce_rows_peers(ctx, xs, both.bases(span.begin), rows)
+            both.fence()
+            stream.synchronize()
+        got = both.tensor.cpu().numpy()
+        bound = 1e-5 * np.abs(x).astype(np.float64).sum(axis=1)
+        ok["reduce_peers"] = bool(np.array_equal(got[1], x.max(axis=1)) and np.all(
+            np.abs(got[0] - x.astype(np.float64).sum(axis=1)) <= bound))
+
+        m, n, k = 512, 768, 256
+        a, b = oracle.make_inputs("gemm_bf16", shape=(m, n, k))
+        span = L.rows(m)
+        a_s = torch.from_numpy(a[span.begin:span.end]).to(dev).bfloat16()
+        b_d = torch.from_numpy(b).to(dev).bfloat16()
+        c_all = PeerOutput((m, n), torch.bfloat16, dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            native.gemm_bf16_peers(ctx, a_s, b_d, c_all.bases(span.begin * n), n)
+            c_all.fence()
+            stream.synchronize()
+        expect = np.zeros((m, n), np.float32)
+        oracle.gemm_bf16(a, b, expect, (256, 256))
+        got = c_all.tensor.float().cpu().numpy()
+        ok["gemm_peers"] = bool(np.all(np.abs(got - expect) <= 1e-2 * np.abs(expect)
+                                       + 1e-4 * (np.abs(a) @ np.abs(b))))
+
+        m, n, k = 256, 512, 512  # column shards of 256 each
+        a, w, s = oracle.make_inputs("gemm_w8a16", shape=(m, n, k))
+        cs = L.cols(n)
+        a_d = torch.from_numpy(a).to(dev).bfloat16()
+        w_d, s_d = torch.from_numpy(w).to(dev), torch.from_numpy(s).to(dev)
+        o_all = PeerOutput((m, n), torch.bfloat16, dev)
+        ws = torch.empty(native.w8a16_workspace_bytes(cs.size, k), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            native.gemm_w8a16_peers(ctx, a_d, w_d[:, cs.begin:cs.end],
+                                    s_d[cs.begin:cs.end].contiguous(), o_all.bases(cs.begin), n, ws)
+            o_all.fence()
+            stream.synchronize()
+        expect = np.zeros((m, n), np.float32)
+        oracle.gemm_w8a16(a, w, s, expect, (256, 256))
+        mag = np.abs(a) @ (np.abs(w.astype(np.float32)) * s)
+        got = o_all.tensor.float().cpu().numpy()
+        ok["dequant_peers"] = bool(np.all(np.abs(got - expect)
+                                          <= 1e-2 * np.abs(expect) + 1e-4 * mag))
 
         ok["status"] = get_context(f"cuda:{rank}").kernel_status() == 0
         results[rank] = ok
