@@ -8,19 +8,28 @@
 // `result` is NOT cleared: like the reference, the kernel adds to whatever
 // the caller put there.
 //
-// Each thread accumulates a strided share of the array in the result type,
-// a CTA combines its threads with shuffles and shared memory, and one thread
-// per CTA issues a single atomicAdd, so the number of atomics is the grid
-// size (a few hundred), not the element count.  Floating-point partial sums
-// are combined in an order that depends on CTA scheduling; integer inputs
-// summed in float64 are exact as long as the total is below 2^53.
+// Each thread accumulates a strided share of the array, a CTA combines its
+// threads with shuffles and shared memory, and one thread per CTA issues a
+// single atomicAdd, so the number of atomics is the grid size (a few hundred),
+// not the element count.  The partial sums are kept in the wider of the input
+// and the result type - double for float64 and integer inputs whatever the
+// result, as the reference sums a group's slice in the input dtype and only
+// the per-group partial sum meets the (possibly float32) result - and are
+// converted to the result type for the atomicAdd alone.  Floating-point
+// partial sums are combined in an order that depends on CTA scheduling;
+// integer inputs summed in float64 are exact as long as the total is below
+// 2^53.
 #include <stdint.h>
 
 namespace {
 
-template <typename TIn, typename TAcc>
+template <typename TIn, typename TOut> struct Wide { using type = double; };
+template <> struct Wide<float, float> { using type = float; };
+
+template <typename TIn, typename TOut>
 __device__ __forceinline__ void reduceAll(const TIn *__restrict__ a, long long n,
-                                          TAcc *result) {
+                                          TOut *result) {
+  using TAcc = typename Wide<TIn, TOut>::type;
   TAcc acc = TAcc(0);
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -40,7 +49,7 @@ __device__ __forceinline__ void reduceAll(const TIn *__restrict__ a, long long n
     for (int o = 16; o > 0; o >>= 1)
       acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0)
-      atomicAdd(result, acc);
+      atomicAdd(result, TOut(acc));
   }
 }
 

@@ -96,6 +96,7 @@ class MapProgram:
         self.inputs, self.code, self.consts = [], [], []
         self._free = list(range(TEMPS))
         self.index_sources = index_sources  # work axis -> operand name (work-item level only)
+        self.uses_index = False  # a work-item index is an operand of the expression
         self.scalars = []  # row programs: the reductions already computed, in scalar order
         # Row programs: expressions of row scalars and constants only are computed
         # once per row, in a uniform prologue of the pass that first needs them,
@@ -209,6 +210,7 @@ class MapProgram:
         if node.op == "index":  # the work-item's own index as a value
             if self.index_sources is None:
                 raise UnsupportedKernel("a work-item index outside a work-item function")
+            self.uses_index = True
             return self.index_sources[node.attrs["axis"]]
         if node.op in ("const", "alloc"):
             value = float(node.args[0])
@@ -303,6 +305,23 @@ def match_map(stores, counts, covers):
                 f"{dst.buffer.name} is stored")
     covers(dst.origin, expr.shape, dst.buffer.shape, counts, "element-wise kernel")
     return program, dst
+
+
+def refuse_inexact_indices(program, dst, what):
+    """The machine computes in the arrays' element type, indices included, with
+    a rounding per operation; the reference computes index arithmetic in Python
+    integers and rounds once, on the store.  float32 holds every integer up to
+    2**24 exactly, so as long as the array has no more elements than that, an
+    expression such as ``gid[0] * shape[1] + gid[1]`` gives the same float32
+    either way; beyond it the two can differ by an ulp, so the kernel is refused."""
+    elements = 1
+    for extent in dst.shape:
+        elements *= int(extent)
+    if program.uses_index and dst.dtype == "float32" and elements > 1 << 24:
+        raise UnsupportedKernel(
+            f"{what}: {dst.name} has {elements} float32 elements and the body computes with the "
+            f"work-item's index; index arithmetic is exact in float32 only up to 2**24 elements - "
+            f"use a float64 array")
 
 
 def match_rows(stores, counts, covers):
@@ -426,4 +445,5 @@ def match_items(item_stores, guards, work_shape):
             raise UnsupportedKernel(
                 f"{what}: {src.name} must be read at the work-item's own index and match "
                 f"{dst.name} in shape and element type")
+    refuse_inexact_indices(program, dst, what)
     return program, dst

@@ -30,7 +30,7 @@ and runs on the pairwise-distance kernel.
 """
 
 from .elementwise import (EQ, LOAD, SAVE0, SRC_CONST, SRC_TEMP, TEMPS, MapProgram, _BINARY,
-                          _UNARY, check_types)
+                          _UNARY, check_types, refuse_inexact_indices)
 from .kernel_api import Tile, UnsupportedKernel
 
 STORE_TILE, BARRIER, STORE_OUT = 64, 65, 66
@@ -140,6 +140,7 @@ class ItemProgram(MapProgram):
                 self.slots.append(key)
             return self.slots.index(key)
         if node.op == "index":
+            self.uses_index = True
             local = node.attrs.get("kind") == "local"
             row, col = (SRC_LOCAL_ROW, SRC_LOCAL_COL) if local else (SRC_ROW, SRC_COL)
             if self.rank == 1:  # one-dimensional work runs along the columns
@@ -236,4 +237,5 @@ def match_work_items(recorder, work, group):
     if group2[0] * group2[1] > 1024:
         raise UnsupportedKernel(f"{what}: work-groups of at most 1024 work-items")
     fill = float(program.tile.args[0]) if program.tile is not None else 0.0
+    refuse_inexact_indices(program, out, what)
     return program, out, group2, guards, fill

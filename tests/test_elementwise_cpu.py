@@ -280,6 +280,23 @@ def test_work_item_bodies_of_the_reference_tests():
     got = run_program(plan.roles["code"], plan.roles["consts"], [], "float64", (12, 5))
     assert np.array_equal(got, np.arange(60).reshape(12, 5))
 
+    # The machine computes indices in the element type.  float32 holds integers up
+    # to 2**24 exactly: at that many elements the program still gives what integer
+    # arithmetic rounded once gives (checked on the last rows, where the values are
+    # largest); one row more is refused, float64 is not.
+    rows, cols = 4096, 4096
+    plan = dims2.plan_for((F((rows, cols), "float32"),))
+    last = np.arange(rows - 8, rows, dtype=np.float32)[:, None]
+    col = np.arange(cols, dtype=np.float32)[None, :]
+    with np.errstate(all="ignore"):  # the machine's own order: one rounding per operation
+        got = last * np.float32(cols) + col
+    exact = (np.arange(rows - 8, rows, dtype=np.int64)[:, None] * cols
+             + np.arange(cols, dtype=np.int64)[None, :])
+    assert got.dtype == np.float32 and np.array_equal(got, exact.astype(np.float32))
+    with pytest.raises(UnsupportedKernel, match="exact in float32 only up to"):
+        dims2.plan_for((F((rows + 1, cols), "float32"),))
+    assert dims2.plan_for((F((rows + 1, cols), "float64"),)).family == "map_elements"
+
 
 def test_work_item_bodies_with_reads_and_their_limits():
     W, H, DT = sym.W, sym.H, typename.DT

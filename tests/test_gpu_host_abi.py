@@ -63,7 +63,8 @@ def test_softmax_rows_host_many_chunks(hc):
         hc.host_unpin(_addr(x))
         hc.host_unpin(_addr(hy))
     d_y = empty_like_dev((rows, cols), torch.float32)
-    hc.softmax_rows(dev(x).data_ptr(), d_y.data_ptr(), rows, cols, cols, cols)
+    d_x = dev(x)  # kept alive until the kernel has run
+    hc.softmax_rows(d_x.data_ptr(), d_y.data_ptr(), rows, cols, cols, cols)
     finish(hc)
     assert np.array_equal(hy, d_y.cpu().numpy())
 
@@ -84,7 +85,8 @@ def test_reduce_rows_host(hc):
     finally:
         hc.host_unpin(_addr(x))
     d_s, d_m = empty_like_dev((rows,), torch.float32), empty_like_dev((rows,), torch.float32)
-    hc.reduce_rows(dev(x).data_ptr(), d_s.data_ptr(), d_m.data_ptr(), rows, cols, cols)
+    d_x = dev(x)  # kept alive until the kernel has run
+    hc.reduce_rows(d_x.data_ptr(), d_s.data_ptr(), d_m.data_ptr(), rows, cols, cols)
     finish(hc)
     # (A chunk may take the other reduction kernel than the whole matrix does: same
     # sums up to the order of the additions.)
@@ -107,7 +109,8 @@ def test_gemm_bf16_host(hc, m, n, k):
     finally:
         hc.host_unpin(_addr(ha))
     d_c = empty_like_dev((m, n), torch.bfloat16)
-    hc.gemm_bf16(dev_bf16(a).data_ptr(), dev_bf16(b).data_ptr(), d_c.data_ptr(), m, n, k, k, n, n)
+    d_a, d_b = dev_bf16(a), dev_bf16(b)  # kept alive until the kernel has run
+    hc.gemm_bf16(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), m, n, k, k, n, n)
     finish(hc)
     got = oracle.bf16_from_bits(hc_out)
     assert np.array_equal(got, host_bf16(d_c))  # row blocks of a product are independent
