@@ -113,10 +113,25 @@ def build_cubins(verbose=False, force=False):
     return outs
 
 
+# Kernel sources embedded as text: what a run-time specialisation compiles
+# (csrc/launch/specialise.cpp).
+EMBEDDED_SOURCES = ["map_fused.cu", "row_fused.cu", "fused_machine.cuh", "map_machine.cuh",
+                    "map_params.h"]
+
+
 def _write_images_asm(cubins, path: Path):
-    """Assembly that embeds each cubin and a name/begin/end table.  The cubins
-    are named by file name only; the assembler finds them through ``-I``."""
+    """Assembly that embeds each cubin and a name/begin/end table, and the same
+    for the kernel sources of EMBEDDED_SOURCES.  The files are named by file
+    name only; the assembler finds them through ``-I``."""
     lines = ['.section .rodata', '.balign 16']
+    for i, name in enumerate(EMBEDDED_SOURCES):
+        lines += [
+            f"hc_src_name_{i}: .asciz \"{name}\"",
+            ".balign 16",
+            f"hc_src_begin_{i}: .incbin \"{name}\"",
+            f"hc_src_end_{i}: .byte 0",
+            ".balign 16",
+        ]
     for i, c in enumerate(cubins):
         lines += [
             f"hc_img_name_{i}: .asciz \"{c.stem}\"",
@@ -130,8 +145,15 @@ def _write_images_asm(cubins, path: Path):
               "hc_b200_images:"]
     for i in range(len(cubins)):
         lines += [f"  .quad hc_img_name_{i}", f"  .quad hc_img_begin_{i}", f"  .quad hc_img_end_{i}"]
+    lines += [".globl hc_b200_sources", ".balign 8", "hc_b200_sources:"]
+    for i in range(len(EMBEDDED_SOURCES)):
+        lines += [f"  .quad hc_src_name_{i}", f"  .quad hc_src_begin_{i}", f"  .quad hc_src_end_{i}"]
     lines += [
         ".section .rodata",
+        ".globl hc_b200_source_count",
+        ".balign 4",
+        "hc_b200_source_count:",
+        f"  .long {len(EMBEDDED_SOURCES)}",
         ".globl hc_b200_image_count",
         ".balign 4",
         "hc_b200_image_count:",
@@ -160,7 +182,10 @@ def build_libs(verbose=False, force=False):
 
     kernels = OUT / "libhc-b200-kernels.so"
     host_src = CSRC / "launch" / "host_api.cpp"
-    srcs = [CSRC / "launch" / "kernels_api.cpp", host_src, CSRC / "launch" / "context.hpp",
+    spec_src = CSRC / "launch" / "specialise.cpp"
+    srcs = [CSRC / "launch" / "kernels_api.cpp", host_src, spec_src,
+            CSRC / "launch" / "context.hpp",
+            *(CSRC / "kernels" / name for name in EMBEDDED_SOURCES),
             INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h",
             CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h",
@@ -177,7 +202,8 @@ def build_libs(verbose=False, force=False):
         static_obj = OUT / "w8a16_static.o"
         _run([cuda / "bin" / "nvcc", *NVCC_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "-cudart", "static", *inc, "-c", "-o", static_obj, static_src], verbose)
-        _run([cxx, *CXX_FLAGS, *inc, "-I", OUT, "-o", kernels, srcs[0], host_src, asm, static_obj,
+        _run([cxx, *CXX_FLAGS, *inc, "-I", OUT, "-I", CSRC / "kernels", "-o", kernels, srcs[0],
+              host_src, spec_src, asm, static_obj,
               "-L", OUT, "-lhc-gpu-runtime-loader", "-L", cuda / "lib64", "-lcudart_static",
               "-lrt", "-lpthread", "-ldl"], verbose)
 

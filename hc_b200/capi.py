@@ -166,6 +166,12 @@ KERNELS_PROTOTYPES = {
     "hcLaunchCount": (_ll, [_vp]),
     "hcKernelStatus": (C.c_int, [_vp, C.POINTER(C.c_int)]),
     "hcSetOption": (C.c_int, [_vp, C.c_char_p, _ll]),
+    "hcSpecialisedPrograms": (_ll, [_vp, C.c_int]),
+    "hcSpecialiseNote": (C.c_char_p, [_vp]),
+    "hcSpecialiseCompile": (
+        _ll, [C.POINTER(HcMapProgram), C.c_int, C.c_int, C.c_int, C.c_int, _vp, _sz, C.c_char_p,
+              _sz]
+    ),
     "hcSelfTestWaitTimeout": (
         C.c_int,
         [_vp, C.c_ulonglong, C.POINTER(C.c_int), C.POINTER(C.c_ulonglong), C.POINTER(C.c_int)],
@@ -263,6 +269,24 @@ def load_loader():
     return _declare(lib, LOADER_EXTRA_PROTOTYPES)
 
 
+def specialise_compile(program, row_program=False, dtype=HC_F32, cc=(10, 0)):
+    """hcSpecialiseCompile: the device image NVRTC makes of ``program`` (an
+    :class:`HcMapProgram`) for compute capability ``cc`` - no GPU needed.  Returns
+    ``(image bytes, tag)``; raises RuntimeError with the library's message."""
+    lib = load_kernels()
+    message = C.create_string_buffer(8192)
+    size = lib.hcSpecialiseCompile(C.byref(program), int(row_program), dtype, cc[0], cc[1], None,
+                                   0, message, len(message))
+    if size < 0:
+        raise RuntimeError(message.value.decode(errors="replace"))
+    image = C.create_string_buffer(size)
+    size = lib.hcSpecialiseCompile(C.byref(program), int(row_program), dtype, cc[0], cc[1], image,
+                                   size, message, len(message))
+    if size < 0:
+        raise RuntimeError(message.value.decode(errors="replace"))
+    return image.raw[:size], message.value.decode()
+
+
 def load_kernels():
     """libhc-b200-kernels.so (images + workload launchers)."""
     return _declare(_open("libhc-b200-kernels.so"), KERNELS_PROTOTYPES)
@@ -341,6 +365,15 @@ class Context:
 
     def set_option(self, name: str, value: int):
         self._check(self.lib.hcSetOption(self.handle, name.encode(), value), "hcSetOption")
+
+    def specialised_programs(self, from_disk: bool = False) -> int:
+        """Programs this context compiled at run time (or loaded from the directory of
+        HC_B200_KERNEL_CACHE)."""
+        return self.lib.hcSpecialisedPrograms(self.handle, int(from_disk))
+
+    @property
+    def specialise_note(self) -> str:
+        return (self.lib.hcSpecialiseNote(self.handle) or b"").decode()
 
     def copy2d(self, src, dst, rows, cols, src_pitch, dst_pitch, elem_bytes):
         self._check(

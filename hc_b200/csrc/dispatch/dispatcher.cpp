@@ -641,6 +641,14 @@ PYBIND11_MODULE(_dispatcher, m) {
            })
       .def("set_option", [](Context &c, const std::string &name, long long v) {
         c.check(hcSetOption(c.get(), name.c_str(), v), "set_option");
+      })
+      // Programs compiled at run time by this context (or loaded from the directory
+      // of HC_B200_KERNEL_CACHE), and why the latest attempt failed.
+      .def("specialised_programs",
+           [](Context &c, bool fromDisk) { return hcSpecialisedPrograms(c.get(), fromDisk); },
+           py::arg("from_disk") = false)
+      .def_property_readonly("specialise_note", [](Context &c) {
+        return std::string(hcSpecialiseNote(c.get()));
       });
 
   m.def("copy2d", &copy2d, py::arg("ctx"), py::arg("src"), py::arg("dst"));

@@ -61,7 +61,7 @@ template <typename T, uint32_t OP> __device__ __forceinline__ T unaryOp(T a) {
 
 // What a thread holds while it runs a program on W elements.
 template <typename T, int W, int NIN> struct Frame {
-  T x[NIN][W];  // the inputs
+  T x[NIN > 0 ? NIN : 1][W];  // the inputs (a program may have none: it computes from indices)
   T t[3][W];    // the temporaries (only those a program saves to become registers)
   T s[4];       // row scalars
   uint32_t ok = ~0u;                   // validity bits of the accumulator's elements

@@ -25,7 +25,8 @@
 //   hc_split_tf32_t      B[K, N] -> hi, lo of B transposed, [N, Kp]: both MMA
 //                        operands are then K-major, the layout of A in the bf16
 //                        kernel (gemm_bf16_umma.cu);
-//   hc_gemm_f32_umma     the product: one persistent CTA per SM, 192 threads -
+//   hc_gemm_f32_umma[_pair]  the product: one persistent CTA per SM (or a CTA pair
+//                        on a 256 x 256 tile, cta_group::2), 192 threads -
 //                        warp 0 TMA producer (four boxes per 32-deep K-block:
 //                        A hi, A lo, B hi, B lo; 128-byte swizzle, zero fill at
 //                        the edges, no multicast), warp 1 MMA issuer (M128 N256
@@ -47,31 +48,50 @@ constexpr int BK = 32;     // K depth of one stage: 32 floats = one 128-byte row
 constexpr int UMMA_K = 8;  // K depth of one tcgen05.mma with tf32 inputs
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int kABytes = BM * BK * 4;  // one of hi / lo
-constexpr int kBBytes = BN * BK * 4;
-constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes; // 96 KiB
-constexpr int kStages = 2;
+constexpr int kABytes = BM * BK * 4;  // one of hi / lo: 128 rows of A per CTA
 
-// Instruction descriptor for kind::tf32 with f32 accumulation: bits 4-5 D format
-// (1 = f32), 7-9 A format (2 = tf32), 10-12 B format, 15 / 16 A / B major
-// (0 = K), 17-22 N >> 3, 24-28 M >> 4.
-constexpr uint32_t kInstrDesc =
-    (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+// PAIR: two CTAs (a cluster of 2) work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2; each stages its own 128 rows of A and its own 128
+// columns of B (128 rows of B transposed), 64 KiB per K-block instead of 96.
+template <bool PAIR> struct Config {
+  static constexpr int kCtas = PAIR ? 2 : 1;
+  static constexpr int kTileM = BM * kCtas;
+  static constexpr int kBRows = BN / kCtas; // rows of B transposed a CTA stages
+  static constexpr int kBBytes = kBRows * BK * 4;
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes; // 96 / 64 KiB
+  static constexpr int kStages = PAIR ? 3 : 2;
+  // Instruction descriptor for kind::tf32 with f32 accumulation: bits 4-5 D format
+  // (1 = f32), 7-9 A format (2 = tf32), 10-12 B format, 15 / 16 A / B major
+  // (0 = K), 17-22 N >> 3, 24-28 M >> 4.
+  static constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) |
+                                         (uint32_t(BN >> 3) << 17) |
+                                         (uint32_t(kTileM >> 4) << 24);
+};
 
+template <int CtaGroup>
 __device__ __forceinline__ void ummaTf32(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,
-                                         uint32_t accumulate) {
-  asm volatile("{\n"
-               ".reg .pred p;\n"
-               "setp.ne.b32 p, %4, 0;\n"
-               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-               "}\n" ::"r"(dTmem),
-               "l"(aDesc), "l"(bDesc), "r"(kInstrDesc), "r"(accumulate)
-               : "memory");
+                                         uint32_t iDesc, uint32_t accumulate) {
+  if constexpr (CtaGroup == 1)
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(dTmem),
+                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
+                 : "memory");
+  else
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(dTmem),
+                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
+                 : "memory");
 }
 
 struct alignas(8) Barriers {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[4];
+  uint64_t empty[4];
   uint64_t tmemFull[2];
   uint64_t tmemEmpty[2];
   uint32_t tmemBase;
@@ -139,18 +159,22 @@ extern "C" __global__ void __launch_bounds__(256)
   }
 }
 
-extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
-    hc_gemm_f32_umma(const __grid_constant__ CUtensorMap mapAHi,
-                     const __grid_constant__ CUtensorMap mapALo,
-                     const __grid_constant__ CUtensorMap mapBHi,
-                     const __grid_constant__ CUtensorMap mapBLo, float *__restrict__ c,
-                     long long M, long long N, long long K, long long ldc, int tilesM,
-                     int tilesN, int bandM, int vecStore, int *status) {
-  extern __shared__ __align__(1024) unsigned char smemRaw[];
+namespace {
+
+template <bool PAIR>
+__device__ __forceinline__ void
+gemmF32(const CUtensorMap &mapAHi, const CUtensorMap &mapALo, const CUtensorMap &mapBHi,
+        const CUtensorMap &mapBLo, float *__restrict__ c, long long M, long long N, long long K,
+        long long ldc, int tilesM, int tilesN, int bandM, int vecStore, int *status,
+        unsigned char *smemRaw) {
+  using Cfg = Config<PAIR>;
+  constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kBBytes = Cfg::kBBytes;
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
   Barriers *bars = reinterpret_cast<Barriers *>(smemRaw + (smemBase - smemAddr(smemRaw)) +
                                                 kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ctaRank = PAIR ? clusterCtaRank() : 0u;
+  const bool leader = ctaRank == 0;
   volatile int *abortFlag = &bars->abortFlag;
 
   if (threadIdx.x == 0) {
@@ -160,7 +184,7 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbarInit(smemAddr(&bars->tmemFull[a]), 1);
-      mbarInit(smemAddr(&bars->tmemEmpty[a]), 4);
+      mbarInit(smemAddr(&bars->tmemEmpty[a]), 4 * Cfg::kCtas);
     }
     bars->abortFlag = 0;
     fenceBarrierInit();
@@ -170,16 +194,21 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     prefetchTensorMap(&mapBLo);
   }
   if (warp == 1) {
-    tmemAlloc<1>(smemAddr(&bars->tmemBase), TMEM_COLS);
-    tmemRelinquish<1>();
+    tmemAlloc<Cfg::kCtas>(smemAddr(&bars->tmemBase), TMEM_COLS);
+    tmemRelinquish<Cfg::kCtas>();
   }
   tcgen05FenceBefore();
-  __syncthreads();
+  if constexpr (PAIR)
+    clusterSync();
+  else
+    __syncthreads();
   tcgen05FenceAfter();
   const uint32_t tmemBase = bars->tmemBase;
 
   const int kBlocks = int((K + BK - 1) / BK);
   const int numTiles = tilesM * tilesN;
+  const int firstTile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tileStep = PAIR ? (gridDim.x >> 1) : gridDim.x;
   auto tileCoords = [&](int t, int &tm, int &tn) {
     const int perBand = bandM * tilesN;
     const int band = t / perBand, rem = t - band * perBand;
@@ -192,21 +221,35 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t it = 0;
-      for (int t = blockIdx.x; t < numTiles && !*abortFlag; t += gridDim.x) {
+      for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep) {
         int tm, tn;
         tileCoords(t, tm, tn);
+        const int row0 = tm * Cfg::kTileM + int(ctaRank) * BM;
+        const int col0 = tn * BN + int(ctaRank) * Cfg::kBRows;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
           const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
           if (!mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
                         kStatusProducerWait))
             break;
-          const uint32_t fullBar = smemAddr(&bars->full[s]);
+          uint32_t fullBar = smemAddr(&bars->full[s]);
           const uint32_t stage = smemBase + s * kStageBytes;
-          mbarExpectTx(fullBar, kStageBytes);
-          tmaLoad2D(stage, &mapAHi, fullBar, kb * BK, tm * BM);
-          tmaLoad2D(stage + kABytes, &mapALo, fullBar, kb * BK, tm * BM);
-          tmaLoad2D(stage + 2 * kABytes, &mapBHi, fullBar, kb * BK, tn * BN);
-          tmaLoad2D(stage + 2 * kABytes + kBBytes, &mapBLo, fullBar, kb * BK, tn * BN);
+          if constexpr (PAIR) {
+            // Completion bytes of both CTAs are counted on the leader's barrier,
+            // and only the leader arrives, expecting the bytes of both.
+            fullBar = mapSharedToCta(fullBar, 0);
+            if (leader)
+              mbarExpectTx(smemAddr(&bars->full[s]), 2 * kStageBytes);
+            tmaLoad2DPair(stage, &mapAHi, fullBar, kb * BK, row0);
+            tmaLoad2DPair(stage + kABytes, &mapALo, fullBar, kb * BK, row0);
+            tmaLoad2DPair(stage + 2 * kABytes, &mapBHi, fullBar, kb * BK, col0);
+            tmaLoad2DPair(stage + 2 * kABytes + kBBytes, &mapBLo, fullBar, kb * BK, col0);
+          } else {
+            mbarExpectTx(fullBar, kStageBytes);
+            tmaLoad2D(stage, &mapAHi, fullBar, kb * BK, row0);
+            tmaLoad2D(stage + kABytes, &mapALo, fullBar, kb * BK, row0);
+            tmaLoad2D(stage + 2 * kABytes, &mapBHi, fullBar, kb * BK, col0);
+            tmaLoad2D(stage + 2 * kABytes + kBBytes, &mapBLo, fullBar, kb * BK, col0);
+          }
         }
       }
       // Tail: the commits that free the last stages must have landed before the
@@ -226,10 +269,10 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       uint32_t it = 0;
       int tileIter = 0;
-      for (int t = blockIdx.x; t < numTiles && !*abortFlag; t += gridDim.x, ++tileIter) {
+      for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep, ++tileIter) {
         const int acc = tileIter & 1;
         const uint32_t accPhase = (tileIter >> 1) & 1u;
         if (!mbarWait(smemAddr(&bars->tmemEmpty[acc]), accPhase ^ 1u, abortFlag, status,
@@ -257,22 +300,35 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // 8 K-elements further: 32 bytes along a row.  The small terms first.
             const uint64_t step = uint64_t(kk * 2);
-            ummaTf32(dTmem, aLo + step, bHi + step, (kb | kk) != 0);
-            ummaTf32(dTmem, aHi + step, bLo + step, 1);
-            ummaTf32(dTmem, aHi + step, bHi + step, 1);
+            ummaTf32<Cfg::kCtas>(dTmem, aLo + step, bHi + step, Cfg::kInstrDesc, (kb | kk) != 0);
+            ummaTf32<Cfg::kCtas>(dTmem, aHi + step, bLo + step, Cfg::kInstrDesc, 1);
+            ummaTf32<Cfg::kCtas>(dTmem, aHi + step, bHi + step, Cfg::kInstrDesc, 1);
           }
-          ummaCommit(smemAddr(&bars->empty[s]));
+          // Frees the stage (in both CTAs of a pair) once these MMAs are done.
+          if constexpr (PAIR)
+            ummaCommitPair(smemAddr(&bars->empty[s]), 0x3);
+          else
+            ummaCommit(smemAddr(&bars->empty[s]));
         }
         if (!ok)
           break;
-        ummaCommit(smemAddr(&bars->tmemFull[acc]));
+        if constexpr (PAIR)
+          ummaCommitPair(smemAddr(&bars->tmemFull[acc]), 0x3);
+        else
+          ummaCommit(smemAddr(&bars->tmemFull[acc]));
       }
     }
   } else {
     // -------------------------------- epilogue --------------------------------
     const int quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32) for this warp
+    uint32_t tmemEmptyBar[2];
+    for (int a = 0; a < 2; ++a) {
+      tmemEmptyBar[a] = smemAddr(&bars->tmemEmpty[a]);
+      if constexpr (PAIR)
+        tmemEmptyBar[a] = mapSharedToCta(tmemEmptyBar[a], 0);
+    }
     int tileIter = 0;
-    for (int t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileIter) {
+    for (int t = firstTile; t < numTiles; t += tileStep, ++tileIter) {
       int tm, tn;
       tileCoords(t, tm, tn);
       const int acc = tileIter & 1;
@@ -285,7 +341,7 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
       if (!ok)
         break;
       tcgen05FenceAfter();
-      const long long row = (long long)tm * BM + quad * 32 + lane;
+      const long long row = (long long)tm * Cfg::kTileM + int(ctaRank) * BM + quad * 32 + lane;
       const long long colBase = (long long)tn * BN;
       const uint32_t taddr = tmemBase + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
       float *crow = c + row * ldc;
@@ -316,17 +372,45 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
       // This warp has read its quarter of the accumulator.
       tcgen05FenceBefore();
       __syncwarp();
-      if (lane == 0)
-        mbarArrive(smemAddr(&bars->tmemEmpty[acc]));
+      if (lane == 0) {
+        if constexpr (PAIR)
+          mbarArriveCluster(tmemEmptyBar[acc]);
+        else
+          mbarArrive(tmemEmptyBar[acc]);
+      }
     }
   }
 
   // -------------------------------- teardown ----------------------------------
   __syncwarp();
   tcgen05FenceBefore();
-  __syncthreads();
+  if constexpr (PAIR)
+    clusterSync();
+  else
+    __syncthreads();
   if (warp == 1) {
     tcgen05FenceAfter();
-    tmemFree<1>(tmemBase, TMEM_COLS);
+    tmemFree<Cfg::kCtas>(tmemBase, TMEM_COLS);
   }
+}
+
+} // namespace
+
+#define HC_GEMM_F32_ARGS                                                                 \
+  const __grid_constant__ CUtensorMap mapAHi, const __grid_constant__ CUtensorMap mapALo, \
+      const __grid_constant__ CUtensorMap mapBHi, const __grid_constant__ CUtensorMap mapBLo, \
+      float *c, long long M, long long N, long long K, long long ldc, int tilesM, int tilesN, \
+      int bandM, int vecStore, int *status
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1) hc_gemm_f32_umma(HC_GEMM_F32_ARGS) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  gemmF32<false>(mapAHi, mapALo, mapBHi, mapBLo, c, M, N, K, ldc, tilesM, tilesN, bandM,
+                 vecStore, status, smemRaw);
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    hc_gemm_f32_umma_pair(HC_GEMM_F32_ARGS) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  gemmF32<true>(mapAHi, mapALo, mapBHi, mapBLo, c, M, N, K, ldc, tilesM, tilesN, bandM,
+                vecStore, status, smemRaw);
 }

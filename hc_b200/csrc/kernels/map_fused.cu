@@ -23,7 +23,7 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
   constexpr int W = V * UNROLL;
   const long long perRow = p.cols / V;
   for (long long r = blockIdx.y; r < p.rows; r += gridDim.y) {
-    const T *rowIn[NIN];
+    const T *rowIn[NIN > 0 ? NIN : 1];
 #pragma unroll
     for (int k = 0; k < NIN; ++k)
       rowIn[k] = static_cast<const T *>(p.in[k]) + r * p.inPitch[k];
@@ -62,7 +62,7 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
 
 } // namespace
 
-#define HC_MAP_FUSED(body)                                                                       \
+#define HC_MAP_FUSED_F32(body)                                                                      \
   extern "C" __global__ void __launch_bounds__(THREADS, 3) hc_map_fused_##body##_f32_v4(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     mapFused<float, 4, hcfused::map_##body>(p);                                                  \
@@ -70,7 +70,8 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
   extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f32_v1(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     mapFused<float, 1, hcfused::map_##body>(p);                                                  \
-  }                                                                                              \
+  }
+#define HC_MAP_FUSED_F64(body)                                                                   \
   extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_f64_v2(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     mapFused<double, 2, hcfused::map_##body>(p);                                                 \
@@ -80,4 +81,11 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
     mapFused<double, 1, hcfused::map_##body>(p);                                                 \
   }
 
-HC_FUSED_MAP_LIST(HC_MAP_FUSED)
+// A run-time specialisation (launch/specialise.cpp) compiles this file for one
+// program and one element type.
+#ifndef HC_FUSED_NO_F32
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_F32)
+#endif
+#ifndef HC_FUSED_NO_F64
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_F64)
+#endif

@@ -211,7 +211,7 @@ __device__ __forceinline__ void rowFusedHeld(const HcMapProgramDev &p) {
 
 // Per body: float rows held by a CTA of 64 or 128 threads, and walked rows for
 // float (16-byte packets or single elements) and double.
-#define HC_ROW_FUSED(body)                                                                       \
+#define HC_ROW_FUSED_F32(body)                                                                      \
   extern "C" __global__ void __launch_bounds__(64) hc_row_fused_##body##_f32_held_t64(           \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     rowFusedHeld<float, 4, 8, 64, hcfused::row_##body>(p);                                       \
@@ -227,7 +227,8 @@ __device__ __forceinline__ void rowFusedHeld(const HcMapProgramDev &p) {
   extern "C" __global__ void __launch_bounds__(THREADS) hc_row_fused_##body##_f32_v1(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     rowFusedWalk<float, 1, hcfused::row_##body>(p);                                              \
-  }                                                                                              \
+  }
+#define HC_ROW_FUSED_F64(body)                                                                   \
   extern "C" __global__ void __launch_bounds__(THREADS) hc_row_fused_##body##_f64_v2(            \
       const __grid_constant__ HcMapProgramDev p) {                                               \
     rowFusedWalk<double, 2, hcfused::row_##body>(p);                                             \
@@ -237,4 +238,11 @@ __device__ __forceinline__ void rowFusedHeld(const HcMapProgramDev &p) {
     rowFusedWalk<double, 1, hcfused::row_##body>(p);                                             \
   }
 
-HC_FUSED_ROW_LIST(HC_ROW_FUSED)
+// A run-time specialisation (launch/specialise.cpp) compiles this file for one
+// program and one element type.
+#ifndef HC_FUSED_NO_F32
+HC_FUSED_ROW_LIST(HC_ROW_FUSED_F32)
+#endif
+#ifndef HC_FUSED_NO_F64
+HC_FUSED_ROW_LIST(HC_ROW_FUSED_F64)
+#endif

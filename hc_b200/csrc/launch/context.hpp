@@ -22,6 +22,7 @@ struct HcContextImpl {
   long long launches = 0;
   long long smCount = 0;
   long long ccMajor = 0;
+  long long ccMinor = 0;
   long long gemmVariant = 0;
   long long softmaxVariant = 0; // 0 auto, 1 register kernel, 2 bulk-copy pipeline
   long long tiledVariant = 0;
@@ -30,6 +31,11 @@ struct HcContextImpl {
   long long rowVariant = 0;
   long long fusedVariant = 0; // 1: never use the precompiled bodies
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
+  int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel
+  // Programs without a precompiled body: 0 interpret them, 1 compile them at their
+  // first launch and interpret where that is not possible, 2 fail where it is not.
+  long long specialiseMode = 1;
+  struct HcSpecialiser *specialiser = nullptr; // specialise.cpp
 
   int fail(const char *fmt, ...) __attribute__((format(printf, 2, 3))) {
     char text[320];
@@ -63,3 +69,11 @@ struct HcContextImpl {
 
 // Frees what the host-buffer entry points keep in a context (host_api.cpp).
 void hcReleaseHostPipeline(HcContextImpl *c);
+
+// Run-time specialisation (specialise.cpp).
+struct HcMapProgramDev;
+bool hcSpecialisable(const HcMapProgramDev &p);
+const char *hcSpecialise(HcContextImpl *c, bool row, bool f64, const HcMapProgramDev &p);
+const char *hcSpecialiserNote(HcContextImpl *c);
+long long hcSpecialiserCount(HcContextImpl *c, int which);
+void hcReleaseSpecialiser(HcContextImpl *c);

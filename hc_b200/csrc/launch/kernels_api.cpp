@@ -118,6 +118,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_split_tf32", "gemm_f32_umma"},
     {"hc_split_tf32_t", "gemm_f32_umma"},
     {"hc_gemm_f32_umma", "gemm_f32_umma"},
+    {"hc_gemm_f32_umma_pair", "gemm_f32_umma"},
 };
 
 // Image that defines `kernel`; a table entry ending in '_' stands for every
@@ -285,6 +286,7 @@ HcContext hcCreateContext(const char *deviceDesc, OlErrorCallback errCallback,
   }
   olxDeviceAttribute(c->device, OLX_DEVICE_SM_COUNT, &c->smCount);
   olxDeviceAttribute(c->device, OLX_DEVICE_CC_MAJOR, &c->ccMajor);
+  olxDeviceAttribute(c->device, OLX_DEVICE_CC_MINOR, &c->ccMinor);
   if (c->smCount <= 0)
     c->smCount = 1;
   c->statusWord = static_cast<int *>(olAllocDevice(c->queue, 256, 256));
@@ -307,6 +309,7 @@ void hcReleaseContext(HcContext c) {
     if (m)
       olReleaseModule(m);
   hcReleaseHostPipeline(c);
+  hcReleaseSpecialiser(c);
   if (c->statusWord)
     olDeallocDevice(c->queue, c->statusWord);
   if (c->queue)
@@ -324,6 +327,12 @@ void *hcContextStream(HcContext c) {
 int hcSynchronize(HcContext c) { return c ? olSyncQueue(c->queue) : 1; }
 const char *hcLastError(HcContext c) { return c ? c->lastError.c_str() : ""; }
 long long hcLaunchCount(HcContext c) { return c ? c->launches : 0; }
+
+long long hcSpecialisedPrograms(HcContext c, int fromDisk) {
+  return c ? hcSpecialiserCount(c, fromDisk ? 1 : 0) : 0;
+}
+
+const char *hcSpecialiseNote(HcContext c) { return c ? hcSpecialiserNote(c) : ""; }
 
 int hcKernelStatus(HcContext c, int *statusRet) {
   if (!c || !statusRet)
@@ -398,6 +407,13 @@ int hcSetOption(HcContext c, const char *name, long long value) {
   }
   if (std::strcmp(name, "fused") == 0 && value >= 0 && value <= 1) {
     c->fusedVariant = value; // 1: interpret every program, precompiled or not
+    return 0;
+  }
+  if (std::strcmp(name, "specialise") == 0 && value >= 0 && value <= 2) {
+    // 0: programs without a precompiled body are interpreted; 1: they are compiled
+    // at their first launch, and interpreted where that is not possible; 2: as 1,
+    // but the launch fails where it is not possible.
+    c->specialiseMode = value;
     return 0;
   }
   if (std::strcmp(name, "row_variant") == 0 && value >= 0 && value <= 3) {
@@ -628,6 +644,13 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   // other program is interpreted.
   const char *fused =
       c->fusedVariant == 1 || integer ? nullptr : matchFused(kFusedMaps, p);
+  if (!fused && c->fusedVariant != 1 && !integer && c->specialiseMode != 0 &&
+      hcSpecialisable(p)) {
+    fused = hcSpecialise(c, false, dtype == HC_F64, p);
+    if (!fused && c->specialiseMode == 2)
+      return c->fail("hcMapElements: the program could not be compiled: %s",
+                     hcSpecialiserNote(c));
+  }
   if (fused)
     std::snprintf(name, sizeof name, "hc_map_fused_%s_%s_v%d", fused, tname, v);
   else {
@@ -692,6 +715,13 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
   void *args[] = {&p};
   const char *fused =
       c->fusedVariant == 1 || c->rowVariant >= 2 ? nullptr : matchFused(kFusedRows, p);
+  if (!fused && c->fusedVariant != 1 && c->rowVariant < 2 && c->specialiseMode != 0 &&
+      hcSpecialisable(p)) {
+    fused = hcSpecialise(c, true, dtype == HC_F64, p);
+    if (!fused && c->specialiseMode == 2)
+      return c->fail("hcRowProgram: the program could not be compiled: %s",
+                     hcSpecialiserNote(c));
+  }
   // Rows of 257..1024 packets can be held in the registers of one CTA per row:
   // eight packets per thread on 64, 96 or 128 threads.  That pays when the row
   // fills most of the CTA's slots; otherwise a warp that walks the row is
@@ -1319,23 +1349,38 @@ int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *
     if (c->launch("hc_split_tf32_t", size_t(grid), 1, 1, 256, args, 7, 0))
       return 1;
   }
+  // A CTA pair per 256 x 256 tile stages 64 KiB per K-block and CTA instead of 96
+  // (three stages fit instead of two); it needs two row blocks to be worth a cluster.
+  const bool pair = c->gemmVariant == 2 || (c->gemmVariant == 0 && M > 128);
   alignas(64) CUtensorMap maps[4];
   const void *parts[4] = {aHi, aLo, bHi, bLo};
   for (int i = 0; i < 4; ++i) {
     const bool isA = i < 2;
     if (olxEncodeTensorMap2D(c->device, &maps[i], /*f32*/ 1, parts[i], size_t(isA ? M : N),
-                             size_t(kp), size_t(kp) * 4, isA ? 128 : 256, 32, 128))
+                             size_t(kp), size_t(kp) * 4, (isA || pair) ? 128 : 256, 32, 128))
       return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
   }
-  int tilesM = int(ceilDiv(M, 128)), tilesN = int(ceilDiv(N, 256));
-  int bandM = 16;
+  int tilesM = int(ceilDiv(M, pair ? 256 : 128)), tilesN = int(ceilDiv(N, 256));
+  int bandM = pair ? 8 : 16;
   int vecStore = aligned(out, 16) && ldc % 4 == 0;
   const long long tiles = (long long)tilesM * tilesN;
-  const long long grid = std::min<long long>(tiles, c->smCount);
-  const size_t smem = 2 * 96 * 1024 /*stages*/ + 1024 /*align*/ + 256 /*barriers*/;
+  long long grid = std::min<long long>(tiles, c->smCount);
+  const size_t smem = (pair ? 3 * 64 : 2 * 96) * 1024 /*stages*/ + 1024 /*align*/ + 256 /*barriers*/;
+  const char *name = pair ? "hc_gemm_f32_umma_pair" : "hc_gemm_f32_umma";
+  if (pair) {
+    // Persistent kernel: no more CTA pairs than the GPU holds at once.
+    if (c->pairSlotsF32 == 0) {
+      OlKernel k = c->kernel(name);
+      int slots = 0;
+      if (!k || olxMaxActiveClusters(c->queue, k, 192, smem, 2, &slots) || slots <= 0)
+        return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
+      c->pairSlotsF32 = slots;
+    }
+    grid = 2 * std::min<long long>(tiles, c->pairSlotsF32);
+  }
   void *args[] = {&maps[0], &maps[1], &maps[2], &maps[3], &out,    &M,        &N,
                   &K,       &ldc,     &tilesM,  &tilesN,  &bandM, &vecStore, &c->statusWord};
-  return c->launch("hc_gemm_f32_umma", size_t(grid), 1, 1, 192, args, 14, smem);
+  return c->launch(name, size_t(grid), 1, 1, 192, args, 14, smem);
 }
 
 int hcGemmBf16Peers(HcContext c, const void *a, const void *b, const HcPeerOutputs *dsts,

@@ -95,8 +95,31 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * 2 = as 3, with 256 threads and four packets each beyond 512 packets,
  * 3 = hold such rows whatever the fill.  "fused": 0 = programs that match a body
  * compiled ahead of time run as straight-line kernels, 1 = every program is
- * interpreted. */
+ * interpreted.  "specialise": what happens to a float program of hcMapElements /
+ * hcRowProgram that has no such body - 1 (default) = it is compiled at its first
+ * launch (see hcSpecialisedPrograms) and interpreted where that is not possible,
+ * 0 = it is interpreted, 2 = as 1, but the launch fails where compiling is not
+ * possible. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
+
+/* Run-time specialisation.  The reference compiles every kernel body at its
+ * first call and keeps the result per argument signature
+ * (python/cpp/native/DispatcherBase.cpp:250-256,542-585).  Here a program of
+ * hcMapElements / hcRowProgram that uses the operations up to `set` on float32
+ * or float64 and has no body compiled ahead of time is compiled the first time
+ * a context launches it: NVRTC (looked up with dlopen; libnvrtc.so.12, or the
+ * path in HC_B200_NVRTC) turns the kernel templates, embedded in this library as
+ * text, into straight-line code for the program's instruction words; the image
+ * is loaded and kept until the context is released.  Constants stay launch
+ * parameters, so bodies that differ in constants alone share one image.  Results
+ * equal the interpreter's bit for bit.  The first launch takes the time of the
+ * compilation (about half a second); with HC_B200_KERNEL_CACHE naming a
+ * directory, images are also kept there and later processes load them instead.
+ * hcSpecialisedPrograms: how many programs this context compiled (fromDisk = 0)
+ * or loaded from the directory (1).  hcSpecialiseNote: why the latest attempt
+ * failed ("" if none did; the string lives until the next attempt). */
+HC_B200_API long long hcSpecialisedPrograms(HcContext c, int fromDisk);
+HC_B200_API const char *hcSpecialiseNote(HcContext c);
 
 /* ---- workloads -------------------------------------------------------------
  * 2-D copy; the reference's compiled copy kernels
@@ -170,6 +193,20 @@ HC_B200_API int hcMapElements(HcContext c, const HcMapProgram *program, int dtyp
  * stored.  Temporaries do not carry over from one pass to the next; element
  * indices (src 16/17) are not available. */
 HC_B200_API int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype);
+
+/* The compilation alone, without a context or a GPU (to fill the directory of
+ * HC_B200_KERNEL_CACHE ahead of time, or to check that NVRTC is usable): the
+ * device image of `program` (rowProgram: 0 = for hcMapElements, 1 = for
+ * hcRowProgram; dtype HC_F32 or HC_F64) for compute capability ccMajor.ccMinor.
+ * Returns the size of the image and copies up to `capacity` bytes of it to `image`
+ * (which may be null); `message` receives the tag that stands for the program in
+ * the kernel names (hc_map_fused_<tag>_f32_v4 ...).  On failure returns -1 and
+ * `message` says why.  No counterpart in the reference, whose compiler is not
+ * reachable without its Python front end. */
+HC_B200_API long long hcSpecialiseCompile(const HcMapProgram *program, int rowProgram,
+                                          int dtype, int ccMajor, int ccMinor, void *image,
+                                          size_t capacity, char *message,
+                                          size_t messageCapacity);
 
 /* Work-item program: a body written at work-item level
  * (CurrentGroup.workitems, python/hckernel/kernel_api.py:395-414) that an

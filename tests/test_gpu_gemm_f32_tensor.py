@@ -26,9 +26,21 @@ def _workspace(hc, m, n, k):
     return buf, buf.data_ptr() + offset, need
 
 
+# gemm_variant: 1 = one CTA per 128 x 256 tile, 2 = a CTA pair per 256 x 256 tile
+# (tcgen05 cta_group::2), 0 = the library's choice (the pair from two row blocks on).
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 32), (256, 512, 64), (300, 500, 100), (1, 1, 1),
-                                   (129, 257, 33), (1024, 1024, 1024), (70, 45, 333)])
-def test_matches_float64_product(hc, m, n, k):
+                                   (129, 257, 33), (1024, 1024, 1024), (70, 45, 333),
+                                   (2048 + 256, 4096 + 8, 520)])
+def test_matches_float64_product(hc, m, n, k, variant):
+    hc.set_option("gemm_variant", variant)
+    try:
+        _matches_float64_product(hc, m, n, k)
+    finally:
+        hc.set_option("gemm_variant", 0)
+
+
+def _matches_float64_product(hc, m, n, k):
     rng = np.random.default_rng(m * 7 + n * 3 + k)
     a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
     b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
