@@ -111,6 +111,23 @@ def relu_axpby(a, b):
     return np.maximum(a * 2.0 - b, 0.0)
 
 
+def scaled_log_softmax(t):
+    """A row body that is NOT compiled ahead of time (the log-softmax of half the
+    input): the library compiles it at its first launch."""
+    import numpy as np
+
+    shifted = (t - t.max(axis=1, keepdims=True)) * 0.5
+    return shifted - np.log(np.exp(shifted).sum(axis=1, keepdims=True))
+
+
+def leaky_axpby(a, b):
+    """An element-wise body that is NOT compiled ahead of time."""
+    import numpy as np
+
+    d = a * 2.0 - b
+    return np.maximum(d, d * 0.125)
+
+
 def log_softmax(t):
     """The row body of the ``rows`` workload."""
     import numpy as np
@@ -738,6 +755,46 @@ def run_gpu(args):
             worst = max(worst, float((err / scale).max())) if b.any() else worst
         return {"rows_checked": int(len(rows)), "worst_error_over_bound": worst, "ok": True}
 
+    def other_forms(name, ins, outs, precompiled_call, steps):
+        """The same arrays through the two other ways a body can run: interpreted
+        (the precompiled body switched off) and compiled at its first launch (a
+        body of the same traffic that is not in the ahead-of-time list)."""
+        from hc_b200.workloads import make_elementwise, make_rowwise
+
+        nbytes = algorithmic(name)[0]
+        figures = {}
+        ctx.set_option("fused", 1)
+        try:
+            ms, _ = timed(precompiled_call, steps, 3)
+        finally:
+            ctx.set_option("fused", 0)
+        figures["interpreted"] = {"ms_per_step": ms / steps, "gbs": nbytes / (ms / steps) / 1e6}
+        before = ctx.specialised_programs() + ctx.specialised_programs(True)
+        if name == "rows":
+            roles = make_rowwise(scaled_log_softmax, 1, desc).plan_for(
+                (ins[0], outs[0], 256)).roles
+            call = lambda: native.row_program(ctx, [ins[0]], outs[0], roles["code"],  # noqa: E731
+                                              roles["consts"])
+            body = "log-softmax of (x - max) / 2"
+        else:
+            roles = make_elementwise(leaky_axpby, 2, 2, (4, 256), desc).plan_for(
+                (ins[0], ins[1], outs[0])).roles
+            order = roles["inputs"]
+            call = lambda: native.map_elements(ctx, [ins[k] for k in order], outs[0],  # noqa: E731
+                                               roles["code"], roles["consts"])
+            body = "max(d, d / 8) with d = 2a - b"
+        t0 = time.perf_counter()
+        call()
+        torch.cuda.synchronize(dev)
+        first_call_s = time.perf_counter() - t0
+        ms, _ = timed(call, steps, 3)
+        compiled = ctx.specialised_programs() + ctx.specialised_programs(True) - before
+        figures["compiled_at_first_launch"] = {
+            "body": body, "ms_per_step": ms / steps, "gbs": nbytes / (ms / steps) / 1e6,
+            "first_call_s": first_call_s, "programs_compiled": int(compiled),
+            "note": ctx.specialise_note or None}
+        return figures
+
     # ---- one workload -----------------------------------------------------------------
     def measure(name, steps, warmup, regions=True):
         """Device-resident throughput of one workload; returns a result dict."""
@@ -953,6 +1010,8 @@ def run_gpu(args):
         roof["step_ms"] = {"min": each[0], "median": statistics.median(each), "steps": len(each)}
         result.update({"status": ctx.kernel_status(), "value": value, "unit": roof["unit"],
                        "roofline": roof, "sharding": mode})
+        if name in ("rows", "map") and mode == "single" and not args.no_extras:
+            result["other_forms"] = other_forms(name, ins, full_outs, single, steps)
         if phases:
             result["phases"] = phases
         if parity:

@@ -44,6 +44,7 @@ KERNEL_SOURCES = [
     "gemm_tiled",
     "gemm_bf16_umma",
     "gemm_f32_umma",
+    "conv_f32_umma",
     "dequant_w8",
     "selftest",
 ]
@@ -189,7 +190,7 @@ def build_libs(verbose=False, force=False):
             INCLUDE / "hc_b200_kernels.h",
             INCLUDE / "offload_api.h", CSRC / "kernels" / "mapped_params.h",
             CSRC / "kernels" / "map_params.h", CSRC / "kernels" / "fused_programs.h",
-            CSRC / "kernels" / "items_params.h", loader,
+            CSRC / "kernels" / "items_params.h", CSRC / "kernels" / "conv_params.h", loader,
             *cubins]
     static_src = CSRC / "launch" / "w8a16_static.cu"
     srcs.append(static_src)

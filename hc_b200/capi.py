@@ -210,6 +210,10 @@ KERNELS_PROTOTYPES = {
     "hcGemmF32Tensor": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll]
     ),
+    "hcConvF32TensorWorkspaceBytes": (_sz, [_ll, _ll, _ll, _ll]),
+    "hcConvF32Tensor": (
+        C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _vp, _sz]
+    ),
     "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
     "hcGemmW8A16": (
         C.c_int,
@@ -466,6 +470,14 @@ class Context:
         self._check(
             self.lib.hcGemmTiled(self.handle, a, b, c, m, n, k, lda, ldb, ldc, dtype),
             "hcGemmTiled",
+        )
+
+    def conv_f32_tensor(self, x, f, out, n, c, h, w, nf, hf, wf, stride, workspace,
+                        workspace_bytes):
+        self._check(
+            self.lib.hcConvF32Tensor(self.handle, x, f, out, n, c, h, w, nf, hf, wf, stride,
+                                     workspace, workspace_bytes),
+            "hcConvF32Tensor",
         )
 
     def gemm_f32_tensor(self, a, b, c, workspace, workspace_bytes, m, n, k, lda, ldb, ldc):

@@ -552,6 +552,46 @@ size_t gemmF32WorkspaceBytes(long long m, long long n, long long k) {
   return hcGemmF32TensorWorkspaceBytes(m, n, k);
 }
 
+// float32 convolution without padding on the tensor cores (hcConvF32Tensor):
+// x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, HO, WO], all contiguous.
+size_t convF32WorkspaceBytes(long long nf, long long c, long long hf, long long wf) {
+  return hcConvF32TensorWorkspaceBytes(nf, c, hf, wf);
+}
+
+bool contiguous(const ArrayArg &a) {
+  long long expect = 1;
+  for (int d = a.rank() - 1; d >= 0; --d) {
+    if (a.shape[d] > 1 && a.strides[d] != expect)
+      return false;
+    expect *= a.shape[d];
+  }
+  return true;
+}
+
+void convF32Tensor(Context &ctx, py::handle x, py::handle f, py::handle out, long long stride,
+                   py::handle workspace) {
+  ArrayArg X = deviceArray(ctx, x, "x", 4), F = deviceArray(ctx, f, "f", 4),
+           O = deviceArray(ctx, out, "out", 4);
+  ArrayArg ws = deviceArray(ctx, workspace, "workspace", 1);
+  if (X.kind != ElemKind::F32 || F.kind != ElemKind::F32 || O.kind != ElemKind::F32)
+    throw py::type_error("conv_f32_tensor: float32 arrays");
+  if (!contiguous(X) || !contiguous(F) || !contiguous(O))
+    throw py::value_error("conv_f32_tensor: x, f and out must be contiguous");
+  if (stride < 1 || F.shape[1] != X.shape[1] || F.shape[2] > X.shape[2] ||
+      F.shape[3] > X.shape[3])
+    throw py::value_error("conv_f32_tensor: shapes do not form a convolution");
+  const long long ho = (X.shape[2] - F.shape[2]) / stride + 1,
+                  wo = (X.shape[3] - F.shape[3]) / stride + 1;
+  if (O.shape[0] != X.shape[0] || O.shape[1] != F.shape[0] || O.shape[2] != ho ||
+      O.shape[3] != wo)
+    throw py::value_error("conv_f32_tensor: out must be [N, NF, (H-HF)/stride+1, "
+                          "(W-WF)/stride+1]");
+  ctx.check(hcConvF32Tensor(ctx.get(), X.data, F.data, O.data, X.shape[0], X.shape[1],
+                            X.shape[2], X.shape[3], F.shape[0], F.shape[2], F.shape[3], stride,
+                            ws.data, size_t(ws.shape[0]) * size_t(ws.itemsize)),
+            "conv_f32_tensor");
+}
+
 // `workspace` (a uint8 device buffer of gemm_f32_workspace_bytes) sends a
 // float32 product to the tensor cores (hcGemmF32Tensor).
 void gemm(Context &ctx, py::handle a, py::handle b, py::handle out, py::object workspace) {
@@ -685,6 +725,10 @@ PYBIND11_MODULE(_dispatcher, m) {
         py::arg("workspace") = py::none());
   m.def("gemm_f32_workspace_bytes", &gemmF32WorkspaceBytes, py::arg("m"), py::arg("n"),
         py::arg("k"));
+  m.def("conv_f32_tensor", &convF32Tensor, py::arg("ctx"), py::arg("x"), py::arg("f"),
+        py::arg("out"), py::arg("stride"), py::arg("workspace"));
+  m.def("conv_f32_workspace_bytes", &convF32WorkspaceBytes, py::arg("nf"), py::arg("c"),
+        py::arg("hf"), py::arg("wf"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());
   m.def("w8a16_workspace_bytes", &w8a16WorkspaceBytes, py::arg("n"), py::arg("k"));

@@ -1,0 +1,24 @@
+// Kernel parameter block of the tensor-core convolution (conv_f32_umma.cu),
+// shared by the kernel and the host code that fills it.
+#pragma once
+
+#include <stdint.h>
+
+// out[n, q, oh, ow] = sum over (c, kh, kw) of
+//   x[n, c, oh * stride + kh, ow * stride + kw] * f[q, c, kh, kw]
+// x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, HO, WO], all float32 and
+// contiguous; no padding: HO = (H - HF) / stride + 1, WO likewise.
+struct HcConvParams {
+  const float *x;
+  float *out;
+  int32_t N, C, H, W;
+  int32_t NF, HF, WF, stride;
+  int32_t HO, WO;
+  int32_t K;             // C * HF * WF, the reduction length
+  int32_t kBlocks;       // ceil(K / 32)
+  int32_t nPad;          // NF rounded up to 16: the N of the MMA
+  int32_t tilesPerImage; // ceil(HO * WO / 128)
+  int32_t stages;        // shared-memory stages the launch has room for
+  int32_t reserved;
+  int *status;           // the context's status word
+};

@@ -13,7 +13,18 @@
 
 namespace hcfused {
 
-template <typename T> struct Arith;
+// Integers: the interpreter's own wrapping arithmetic (nothing to contract).
+template <typename T> struct Arith {
+  static __device__ __forceinline__ T add(T a, T b) { return hcmap::addOf(a, b); }
+  static __device__ __forceinline__ T sub(T a, T b) { return hcmap::subOf(a, b); }
+  static __device__ __forceinline__ T mul(T a, T b) { return hcmap::mulOf(a, b); }
+  static __device__ __forceinline__ T div(T a, T b) { return hcmap::Num<T>::div(a, b); }
+  static __device__ __forceinline__ T sqrt(T a) { return hcmap::Num<T>::sqrtOf(a); }
+  static __device__ __forceinline__ T exp(T a) { return hcmap::Num<T>::exp(a); }
+  static __device__ __forceinline__ T log(T a) { return hcmap::Num<T>::log(a); }
+  static __device__ __forceinline__ T max(T a, T b) { return hcmap::maxOf(a, b); }
+  static __device__ __forceinline__ T min(T a, T b) { return hcmap::minOf(a, b); }
+};
 template <> struct Arith<float> {
   static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
   static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
@@ -47,16 +58,37 @@ template <typename T, uint32_t OP> __device__ __forceinline__ T binaryOp(T a, T 
   else if constexpr (OP == HC_MAP_DIV) return Arith<T>::div(a, b);
   else if constexpr (OP == HC_MAP_RDIV) return Arith<T>::div(b, a);
   else if constexpr (OP == HC_MAP_MAX) return Arith<T>::max(a, b);
-  else return Arith<T>::min(a, b);
+  else if constexpr (OP == HC_MAP_MIN) return Arith<T>::min(a, b);
+  // The later operators, as the extended interpreter computes them.
+  else if constexpr (OP == HC_MAP_LT) return T(a < b);
+  else if constexpr (OP == HC_MAP_LE) return T(a <= b);
+  else if constexpr (OP == HC_MAP_EQ) return T(a == b);
+  else if constexpr (OP == HC_MAP_NE) return T(a != b);
+  else if constexpr (OP == HC_MAP_GE) return T(a >= b);
+  else if constexpr (OP == HC_MAP_GT) return T(a > b);
+  else if constexpr (OP == HC_MAP_AND) return hcmap::Num<T>::bitAnd(a, b);
+  else if constexpr (OP == HC_MAP_OR) return hcmap::Num<T>::bitOr(a, b);
+  else if constexpr (OP == HC_MAP_XOR) return hcmap::Num<T>::bitXor(a, b);
+  else if constexpr (OP == HC_MAP_SHL) return hcmap::Num<T>::shl(a, b);
+  else if constexpr (OP == HC_MAP_SHR) return hcmap::Num<T>::shr(a, b);
+  else if constexpr (OP == HC_MAP_RSHL) return hcmap::Num<T>::shl(b, a);
+  else {
+    static_assert(OP == HC_MAP_RSHR, "not an operation of two operands on registers");
+    return hcmap::Num<T>::shr(b, a);
+  }
 }
 
 template <typename T, uint32_t OP> __device__ __forceinline__ T unaryOp(T a) {
-  if constexpr (OP == HC_MAP_NEG) return -a;
+  if constexpr (OP == HC_MAP_NEG) return hcmap::negOf(a);
   // As the interpreter writes it: -0 becomes +0, a NaN keeps its bits.
-  else if constexpr (OP == HC_MAP_ABS) return a < T(0) ? -a : (a == T(0) ? T(0) : a);
+  else if constexpr (OP == HC_MAP_ABS) return hcmap::Num<T>::absOf(a);
   else if constexpr (OP == HC_MAP_EXP) return Arith<T>::exp(a);
   else if constexpr (OP == HC_MAP_SQRT) return Arith<T>::sqrt(a);
-  else return Arith<T>::log(a);
+  else if constexpr (OP == HC_MAP_INV) return hcmap::Num<T>::inv(a);
+  else {
+    static_assert(OP == HC_MAP_LOG, "not an operation of one operand");
+    return Arith<T>::log(a);
+  }
 }
 
 // What a thread holds while it runs a program on W elements.
@@ -79,6 +111,23 @@ __device__ __forceinline__ void noteDivision(uint32_t &ok, int i, T a, T b) {
   }
 }
 
+// acc = acc OP b for element i, with the validity bit kept up to date.  Floor
+// division, remainder and power go through the interpreter's out-of-line
+// routine (map_machine.cuh: rareBinary), which also says whether numpy.ma would
+// mask the result.
+template <typename T, uint32_t OP, bool MASKED>
+__device__ __forceinline__ void apply(uint32_t &ok, int i, T &acc, T b) {
+  if constexpr (OP >= HC_MAP_FLOORDIV && OP <= HC_MAP_RPOW) {
+    bool valid;
+    acc = hcmap::rareBinary<T>(OP, acc, b, valid);
+    if (MASKED && !valid)
+      ok &= ~(1u << i);
+  } else {
+    noteDivision<T, OP, MASKED>(ok, i, acc, b);
+    acc = binaryOp<T, OP>(acc, b);
+  }
+}
+
 // First instruction at or after `pc` that is not part of a uniform prologue.
 template <typename P> __host__ __device__ constexpr int afterUniform(int pc) {
   while (pc < P::n && (P::code[pc] & HC_MAP_UNIFORM))
@@ -95,7 +144,7 @@ template <typename P> __host__ __device__ constexpr int passEnd(int pc) {
 template <typename P> __host__ __device__ constexpr bool usesIndices() {
   for (int pc = 0; pc < P::n; ++pc) {
     const uint32_t op = P::code[pc] & 0xffu, src = P::code[pc] >> 8;
-    if (op <= HC_MAP_MIN && (src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL))
+    if (hcMapIsBinary(op) && (src == HC_MAP_SRC_ROW || src == HC_MAP_SRC_COL))
       return true;
   }
   return false;
@@ -110,37 +159,32 @@ __device__ __forceinline__ void run(const HcMapProgramDev &p, Frame<T, W, NIN> &
                                     long long row, long long packet) {
   if constexpr (PC < END) {
     constexpr uint32_t ins = P::code[PC], op = ins & 0xffu, src = ins >> 8;
-    static_assert(op < HC_MAP_FLOORDIV, "only the operations up to `set` are compiled ahead");
     if constexpr (MASKED && op == HC_MAP_LOAD)
       f.ok = ~0u; // a fresh value (a parked one brings its own bits, below)
-    if constexpr (op <= HC_MAP_MIN) {
+    if constexpr (hcMapIsBinary(op)) {
       if constexpr (src >= HC_MAP_SRC_SCALAR) {
         const T one = f.s[src - HC_MAP_SRC_SCALAR];
 #pragma unroll
         for (int i = 0; i < W; ++i) {
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
-          acc[i] = binaryOp<T, op>(acc[i], one);
+          apply<T, op, MASKED>(f.ok, i, acc[i], one);
         }
       } else if constexpr (src == HC_MAP_SRC_COL) {
 #pragma unroll
         for (int i = 0; i < W; ++i) {
           const T col = T((packet + (long long)(i / V) * STRIDE) * V + i % V);
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], col);
-          acc[i] = binaryOp<T, op>(acc[i], col);
+          apply<T, op, MASKED>(f.ok, i, acc[i], col);
         }
       } else if constexpr (src == HC_MAP_SRC_ROW) {
         const T one = T(row);
 #pragma unroll
         for (int i = 0; i < W; ++i) {
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
-          acc[i] = binaryOp<T, op>(acc[i], one);
+          apply<T, op, MASKED>(f.ok, i, acc[i], one);
         }
       } else if constexpr (src >= HC_MAP_SRC_CONST) {
         const T one = T(p.consts[src - HC_MAP_SRC_CONST]);
 #pragma unroll
         for (int i = 0; i < W; ++i) {
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], one);
-          acc[i] = binaryOp<T, op>(acc[i], one);
+          apply<T, op, MASKED>(f.ok, i, acc[i], one);
         }
       } else if constexpr (src >= HC_MAP_SRC_TEMP) {
         if constexpr (MASKED)
@@ -148,15 +192,13 @@ __device__ __forceinline__ void run(const HcMapProgramDev &p, Frame<T, W, NIN> &
                                    : f.ok & f.okT[src - HC_MAP_SRC_TEMP];
 #pragma unroll
         for (int i = 0; i < W; ++i) {
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
-          acc[i] = binaryOp<T, op>(acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
+          apply<T, op, MASKED>(f.ok, i, acc[i], f.t[src - HC_MAP_SRC_TEMP][i]);
         }
       } else {
         static_assert(src < uint32_t(NIN), "the program reads an input the kernel does not load");
 #pragma unroll
         for (int i = 0; i < W; ++i) {
-          noteDivision<T, op, MASKED>(f.ok, i, acc[i], f.x[src][i]);
-          acc[i] = binaryOp<T, op>(acc[i], f.x[src][i]);
+          apply<T, op, MASKED>(f.ok, i, acc[i], f.x[src][i]);
         }
       }
     } else if constexpr (op >= HC_MAP_SAVE0 && op <= HC_MAP_SAVE2) {

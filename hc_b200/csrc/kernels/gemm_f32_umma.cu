@@ -68,27 +68,6 @@ template <bool PAIR> struct Config {
                                          (uint32_t(kTileM >> 4) << 24);
 };
 
-template <int CtaGroup>
-__device__ __forceinline__ void ummaTf32(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,
-                                         uint32_t iDesc, uint32_t accumulate) {
-  if constexpr (CtaGroup == 1)
-    asm volatile("{\n"
-                 ".reg .pred p;\n"
-                 "setp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-                 "}\n" ::"r"(dTmem),
-                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
-                 : "memory");
-  else
-    asm volatile("{\n"
-                 ".reg .pred p;\n"
-                 "setp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
-                 "}\n" ::"r"(dTmem),
-                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
-                 : "memory");
-}
-
 struct alignas(8) Barriers {
   uint64_t full[4];
   uint64_t empty[4];
@@ -97,19 +76,6 @@ struct alignas(8) Barriers {
   uint32_t tmemBase;
   int abortFlag;
 };
-
-// The nearest tf32 number, as a float whose low 13 fraction bits are zero.
-__device__ __forceinline__ float toTf32(float v) {
-  uint32_t bits;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(v));
-  return __uint_as_float(bits);
-}
-
-__device__ __forceinline__ void splitTf32(float v, float &hi, float &lo) {
-  hi = toTf32(v);
-  // Infinities and NaNs stay in the high part alone (inf - inf would poison lo).
-  lo = (hi - hi == 0.0f) ? toTf32(v - hi) : 0.0f;
-}
 
 } // namespace
 

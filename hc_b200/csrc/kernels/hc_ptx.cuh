@@ -271,6 +271,28 @@ __device__ __forceinline__ void umma(uint32_t dTmem, uint64_t aDesc,
                  : "memory");
 }
 
+// The same with tf32 inputs (kind::tf32, K = 8 per instruction).
+template <int CtaGroup>
+__device__ __forceinline__ void ummaTf32(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,
+                                         uint32_t iDesc, uint32_t accumulate) {
+  if constexpr (CtaGroup == 1)
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(dTmem),
+                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
+                 : "memory");
+  else
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(dTmem),
+                 "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
+                 : "memory");
+}
+
 // Makes `bar` (this CTA) complete one arrival once every MMA issued so far by
 // this thread has finished.
 __device__ __forceinline__ void ummaCommit(uint32_t bar) {
@@ -309,6 +331,21 @@ __device__ __forceinline__ void tmemLoad32x32(uint32_t taddr, uint32_t (&v)[32])
 
 __device__ __forceinline__ void tmemLoadWait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- float32 as two tf32 numbers ----------------------------------------------
+// The nearest tf32 number, as a float whose low 13 fraction bits are zero.
+__device__ __forceinline__ float toTf32(float v) {
+  uint32_t bits;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(v));
+  return __uint_as_float(bits);
+}
+
+// v = hi + lo with hi = tf32(v) and lo = tf32(v - hi).
+__device__ __forceinline__ void splitTf32(float v, float &hi, float &lo) {
+  hi = toTf32(v);
+  // Infinities and NaNs stay in the high part alone (inf - inf would poison lo).
+  lo = (hi - hi == 0.0f) ? toTf32(v - hi) : 0.0f;
 }
 
 // ---- global memory with cache hints ------------------------------------------

@@ -81,11 +81,38 @@ __device__ __forceinline__ void mapFused(const HcMapProgramDev &p) {
     mapFused<double, 1, hcfused::map_##body>(p);                                                 \
   }
 
-// A run-time specialisation (launch/specialise.cpp) compiles this file for one
-// program and one element type.
-#ifndef HC_FUSED_NO_F32
+#define HC_MAP_FUSED_I32(body)                                                                   \
+  extern "C" __global__ void __launch_bounds__(THREADS, 3) hc_map_fused_##body##_i32_v4(         \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<int32_t, 4, hcfused::map_##body>(p);                                                \
+  }                                                                                              \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_i32_v1(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<int32_t, 1, hcfused::map_##body>(p);                                                \
+  }
+#define HC_MAP_FUSED_I64(body)                                                                   \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_i64_v2(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<int64_t, 2, hcfused::map_##body>(p);                                                \
+  }                                                                                              \
+  extern "C" __global__ void __launch_bounds__(THREADS) hc_map_fused_##body##_i64_v1(            \
+      const __grid_constant__ HcMapProgramDev p) {                                               \
+    mapFused<int64_t, 1, hcfused::map_##body>(p);                                                \
+  }
+
+// The bodies compiled ahead of time are float bodies, in both float types.  A
+// run-time specialisation (launch/specialise.cpp) compiles this file for one
+// program and one element type, named by HC_FUSED_ONLY (0 float32, 1 float64,
+// 2 int32, 3 int64).
+#ifndef HC_FUSED_ONLY
 HC_FUSED_MAP_LIST(HC_MAP_FUSED_F32)
-#endif
-#ifndef HC_FUSED_NO_F64
 HC_FUSED_MAP_LIST(HC_MAP_FUSED_F64)
+#elif HC_FUSED_ONLY == 0
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_F32)
+#elif HC_FUSED_ONLY == 1
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_F64)
+#elif HC_FUSED_ONLY == 2
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_I32)
+#else
+HC_FUSED_MAP_LIST(HC_MAP_FUSED_I64)
 #endif

@@ -239,10 +239,12 @@ __device__ __forceinline__ void rowFusedHeld(const HcMapProgramDev &p) {
   }
 
 // A run-time specialisation (launch/specialise.cpp) compiles this file for one
-// program and one element type.
-#ifndef HC_FUSED_NO_F32
+// program and one element type, named by HC_FUSED_ONLY (0 float32, 1 float64).
+#ifndef HC_FUSED_ONLY
 HC_FUSED_ROW_LIST(HC_ROW_FUSED_F32)
-#endif
-#ifndef HC_FUSED_NO_F64
+HC_FUSED_ROW_LIST(HC_ROW_FUSED_F64)
+#elif HC_FUSED_ONLY == 0
+HC_FUSED_ROW_LIST(HC_ROW_FUSED_F32)
+#else
 HC_FUSED_ROW_LIST(HC_ROW_FUSED_F64)
 #endif

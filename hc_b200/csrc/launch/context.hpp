@@ -30,6 +30,7 @@ struct HcContextImpl {
   long long mappedStack = 0;
   long long rowVariant = 0;
   long long fusedVariant = 0; // 1: never use the precompiled bodies
+  long long convStages = 0;   // 2..4: shared-memory stages of the convolution (0: as many as fit)
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
   int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel
   // Programs without a precompiled body: 0 interpret them, 1 compile them at their
@@ -72,8 +73,8 @@ void hcReleaseHostPipeline(HcContextImpl *c);
 
 // Run-time specialisation (specialise.cpp).
 struct HcMapProgramDev;
-bool hcSpecialisable(const HcMapProgramDev &p);
-const char *hcSpecialise(HcContextImpl *c, bool row, bool f64, const HcMapProgramDev &p);
+bool hcSpecialisable(const HcMapProgramDev &p, bool row, int dtype);
+const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgramDev &p);
 const char *hcSpecialiserNote(HcContextImpl *c);
 long long hcSpecialiserCount(HcContextImpl *c, int which);
 void hcReleaseSpecialiser(HcContextImpl *c);

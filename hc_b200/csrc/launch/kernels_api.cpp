@@ -10,6 +10,7 @@
 #include "context.hpp"
 
 #include "../kernels/fused_programs.h"
+#include "../kernels/conv_params.h"
 #include "../kernels/items_params.h"
 #include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
@@ -119,6 +120,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_split_tf32_t", "gemm_f32_umma"},
     {"hc_gemm_f32_umma", "gemm_f32_umma"},
     {"hc_gemm_f32_umma_pair", "gemm_f32_umma"},
+    {"hc_conv_f32_umma", "conv_f32_umma"},
 };
 
 // Image that defines `kernel`; a table entry ending in '_' stands for every
@@ -409,6 +411,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->fusedVariant = value; // 1: interpret every program, precompiled or not
     return 0;
   }
+  if (std::strcmp(name, "conv_stages") == 0 && (value == 0 || (value >= 2 && value <= 4))) {
+    c->convStages = value; // hcConvF32Tensor: fewer stages leave more of the SM's L1
+    return 0;
+  }
   if (std::strcmp(name, "specialise") == 0 && value >= 0 && value <= 2) {
     // 0: programs without a precompiled body are interpreted; 1: they are compiled
     // at their first launch, and interpreted where that is not possible; 2: as 1,
@@ -644,9 +650,9 @@ int hcMapElements(HcContext c, const HcMapProgram *program, int dtype) {
   // other program is interpreted.
   const char *fused =
       c->fusedVariant == 1 || integer ? nullptr : matchFused(kFusedMaps, p);
-  if (!fused && c->fusedVariant != 1 && !integer && c->specialiseMode != 0 &&
-      hcSpecialisable(p)) {
-    fused = hcSpecialise(c, false, dtype == HC_F64, p);
+  if (!fused && c->fusedVariant != 1 && c->specialiseMode != 0 &&
+      hcSpecialisable(p, false, dtype)) {
+    fused = hcSpecialise(c, false, dtype, p);
     if (!fused && c->specialiseMode == 2)
       return c->fail("hcMapElements: the program could not be compiled: %s",
                      hcSpecialiserNote(c));
@@ -716,8 +722,8 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
   const char *fused =
       c->fusedVariant == 1 || c->rowVariant >= 2 ? nullptr : matchFused(kFusedRows, p);
   if (!fused && c->fusedVariant != 1 && c->rowVariant < 2 && c->specialiseMode != 0 &&
-      hcSpecialisable(p)) {
-    fused = hcSpecialise(c, true, dtype == HC_F64, p);
+      hcSpecialisable(p, true, dtype)) {
+    fused = hcSpecialise(c, true, dtype, p);
     if (!fused && c->specialiseMode == 2)
       return c->fail("hcRowProgram: the program could not be compiled: %s",
                      hcSpecialiserNote(c));
@@ -1381,6 +1387,91 @@ int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *
   void *args[] = {&maps[0], &maps[1], &maps[2], &maps[3], &out,    &M,        &N,
                   &K,       &ldc,     &tilesM,  &tilesN,  &bandM, &vecStore, &c->statusWord};
   return c->launch(name, size_t(grid), 1, 1, 192, args, 14, smem);
+}
+
+// ---- float32 convolution on the tensor cores (conv_f32_umma.cu) ---------------------
+size_t hcConvF32TensorWorkspaceBytes(long long NF, long long C, long long HF, long long WF) {
+  if (NF <= 0 || C <= 0 || HF <= 0 || WF <= 0)
+    return 0;
+  // hi and lo parts of f as a matrix [NF, Kp], each 1 KiB aligned.
+  return 2 * size_t(roundUp(NF * f32Pitch(C * HF * WF) * 4, 1024));
+}
+
+int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long long N,
+                    long long C, long long H, long long W, long long NF, long long HF,
+                    long long WF, long long stride, void *workspace, size_t workspaceBytes) {
+  if (!c)
+    return 1;
+  const char *who = "hcConvF32Tensor";
+  if (N < 0 || C <= 0 || H <= 0 || W <= 0 || NF <= 0 || HF <= 0 || WF <= 0 || stride <= 0 ||
+      HF > H || WF > W)
+    return c->fail("%s: invalid shape x [%lld, %lld, %lld, %lld], f [%lld, %lld, %lld, %lld], "
+                   "stride %lld", who, N, C, H, W, NF, C, HF, WF, stride);
+  if (N == 0)
+    return 0;
+  if (!x || !f || !out)
+    return c->fail("%s: null array", who);
+  if (c->ccMajor != 10)
+    return c->fail("%s: needs the tcgen05 tensor cores (compute capability 10.x, this device "
+                   "has %lld.%lld); hcMappedGemm runs the same convolution anywhere", who,
+                   c->ccMajor, c->ccMinor);
+  const long long HO = (H - HF) / stride + 1, WO = (W - WF) / stride + 1;
+  const long long K = C * HF * WF, kp = f32Pitch(K), kBlocks = ceilDiv(K, 32);
+  const long long nPad = roundUp(NF, 16), pixels = HO * WO;
+  const long long tilesPerImage = ceilDiv(pixels, 128);
+  if (NF > 256)
+    return c->fail("%s: at most 256 filters per call, got %lld", who, NF);
+  if (C * H * W >= (1ll << 31) || N * tilesPerImage >= (1ll << 31) || NF * pixels >= (1ll << 31))
+    return c->fail("%s: an image of %lld x %lld x %lld exceeds 32-bit element offsets", who, C, H,
+                   W);
+  // Shared memory: the stages, the offset of every k, the barriers.
+  const long long stageBytes = 2 * 128 * 32 * 4 + 2 * nPad * 32 * 4;
+  const long long fixed = kBlocks * 32 * 4 + 1024 /*align*/ + 256 /*barriers*/;
+  const long long room = 227 * 1024 - fixed;
+  long long stages = std::min<long long>(4, room / stageBytes);
+  if (c->convStages)
+    stages = std::min(stages, c->convStages);
+  if (stages < 2)
+    return c->fail("%s: a reduction over %lld elements with %lld filters does not fit in "
+                   "shared memory", who, K, NF);
+  const size_t need = hcConvF32TensorWorkspaceBytes(NF, C, HF, WF);
+  if (!workspace || workspaceBytes < need || !aligned(workspace, 1024))
+    return c->fail("%s: workspace of %zu bytes (1 KiB aligned) needed, got %zu", who, need,
+                   workspaceBytes);
+  if (!aligned(x, 4) || !aligned(out, 4) || !aligned(f, 4))
+    return c->fail("%s: arrays must be 4-byte aligned", who);
+  auto *base = static_cast<unsigned char *>(workspace);
+  float *fHi = reinterpret_cast<float *>(base);
+  float *fLo = reinterpret_cast<float *>(base + need / 2);
+  {
+    // f is the K-major [NF, K] operand as it lies in memory.
+    long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(kp, 256), 64));
+    long long gy = std::max<long long>(1, std::min<long long>(NF, 65535));
+    void *args[] = {&f, &fHi, &fLo, &NF, (void *)&K, (void *)&K, (void *)&kp};
+    if (c->launch("hc_split_tf32", size_t(gx), size_t(gy), 1, 256, args, 7, 0))
+      return 1;
+  }
+  alignas(64) CUtensorMap maps[2];
+  const void *parts[2] = {fHi, fLo};
+  for (int i = 0; i < 2; ++i)
+    if (olxEncodeTensorMap2D(c->device, &maps[i], /*f32*/ 1, parts[i], size_t(NF), size_t(kp),
+                             size_t(kp) * 4, size_t(nPad), 32, 128))
+      return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
+  HcConvParams p{};
+  p.x = static_cast<const float *>(x);
+  p.out = static_cast<float *>(out);
+  p.N = int(N), p.C = int(C), p.H = int(H), p.W = int(W);
+  p.NF = int(NF), p.HF = int(HF), p.WF = int(WF), p.stride = int(stride);
+  p.HO = int(HO), p.WO = int(WO);
+  p.K = int(K), p.kBlocks = int(kBlocks), p.nPad = int(nPad);
+  p.tilesPerImage = int(tilesPerImage);
+  p.stages = int(stages);
+  p.status = c->statusWord;
+  const long long tiles = N * tilesPerImage;
+  const long long grid = std::min<long long>(tiles, c->smCount);
+  const size_t smem = size_t(stages * stageBytes + fixed);
+  void *args[] = {&maps[0], &maps[1], &p};
+  return c->launch("hc_conv_f32_umma", size_t(grid), 1, 1, 448, args, 3, smem);
 }
 
 int hcGemmBf16Peers(HcContext c, const void *a, const void *b, const HcPeerOutputs *dsts,

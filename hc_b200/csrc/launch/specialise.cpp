@@ -169,19 +169,33 @@ long long hcSpecialiserCount(HcContextImpl *c, int which) {
   return which == 0 ? c->specialiser->compiled : c->specialiser->fromDisk;
 }
 
-// The straight-line kernels of fused_machine.cuh cover the operations up to `set`.
-bool hcSpecialisable(const HcMapProgramDev &p) {
-  for (int pc = 0; pc < p.nInstr; ++pc)
-    if ((p.code[pc] & 0x7fu) >= HC_MAP_FLOORDIV)
+// What the straight-line kernels cover: element-wise programs of any operation
+// on the four element types; row programs of the operations up to `set` on
+// floats (the later operators are not allowed in row programs at all).
+bool hcSpecialisable(const HcMapProgramDev &p, bool row, int dtype) {
+  const bool floating = dtype == HC_F32 || dtype == HC_F64;
+  if (!floating && (row || (dtype != HC_I32 && dtype != HC_I64)))
+    return false;
+  for (int pc = 0; pc < p.nInstr; ++pc) {
+    const uint32_t op = p.code[pc] & 0x7fu;
+    if (row ? op >= HC_MAP_FLOORDIV
+            : op >= HC_MAP_OP_COUNT || op == HC_MAP_RSUM || op == HC_MAP_RMAX || op == HC_MAP_SET)
       return false;
+  }
   return true;
 }
 
 namespace {
 
-std::string programKey(bool row, bool f64, const HcMapProgramDev &p) {
+// 0 float32, 1 float64, 2 int32, 3 int64: the value of HC_FUSED_ONLY.
+int typeIndex(int dtype) {
+  return dtype == HC_F32 ? 0 : dtype == HC_F64 ? 1 : dtype == HC_I32 ? 2 : 3;
+}
+const char *const kTypeNames[] = {"f32", "f64", "i32", "i64"};
+
+std::string programKey(bool row, int dtype, const HcMapProgramDev &p) {
   std::string key(row ? "r" : "m");
-  key += f64 ? "d" : "f";
+  key += kTypeNames[typeIndex(dtype)];
   key += char('0' + p.nInputs);
   key.append(reinterpret_cast<const char *>(p.code), size_t(p.nInstr) * sizeof(uint32_t));
   return key;
@@ -191,7 +205,7 @@ std::string programKey(bool row, bool f64, const HcMapProgramDev &p) {
 // major.minor, from the directory of HC_B200_KERNEL_CACHE or from NVRTC.  `tag`
 // is the part of the kernel names that stands for the program.  False, with the
 // reason in `why`, when there is no way to get one.
-bool buildImage(bool row, bool f64, const HcMapProgramDev &p, long long ccMajor,
+bool buildImage(bool row, int dtype, const HcMapProgramDev &p, long long ccMajor,
                 long long ccMinor, std::string &image, std::string &tag, bool &fromDisk,
                 std::string &why) {
   const char *kind = row ? "row" : "map";
@@ -201,7 +215,7 @@ bool buildImage(bool row, bool f64, const HcMapProgramDev &p, long long ccMajor,
     why = "the kernel sources are not embedded in this library";
     return false;
   }
-  const std::string key = programKey(row, f64, p);
+  const std::string key = programKey(row, dtype, p);
   char tagText[32];
   std::snprintf(tagText, sizeof tagText, "j%016" PRIx64,
                 fnv1a(0xcbf29ce484222325ull, key.data(), key.size()));
@@ -215,7 +229,7 @@ bool buildImage(bool row, bool f64, const HcMapProgramDev &p, long long ccMajor,
   for (int pc = 0; pc < p.nInstr; ++pc)
     programs << (pc ? ", " : "") << p.code[pc] << "u";
   programs << "};\n};\n}\n#define HC_FUSED_" << (row ? "ROW" : "MAP") << "_LIST(X) X(" << tag
-           << ")\n#define " << (f64 ? "HC_FUSED_NO_F32" : "HC_FUSED_NO_F64") << " 1\n";
+           << ")\n#define HC_FUSED_ONLY " << typeIndex(dtype) << "\n";
 
   std::vector<std::string> texts = {programs.str(), kStdint, kMath, kTypeTraits};
   std::vector<const char *> names = {"fused_programs.h", "stdint.h", "math.h", "type_traits"};
@@ -309,11 +323,11 @@ bool buildImage(bool row, bool f64, const HcMapProgramDev &p, long long ccMajor,
 // element-wise; `f64`: the element type), compiling them first if this context
 // has not seen the program yet.  nullptr when that is not possible; the reason
 // is then in hcSpecialiserNote().
-const char *hcSpecialise(HcContextImpl *c, bool row, bool f64, const HcMapProgramDev &p) {
+const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgramDev &p) {
   if (!c->specialiser)
     c->specialiser = new HcSpecialiser;
   HcSpecialiser &s = *c->specialiser;
-  const std::string key = programKey(row, f64, p);
+  const std::string key = programKey(row, dtype, p);
   auto found = s.entries.find(key);
   if (found != s.entries.end())
     return found->second.failed ? nullptr : found->second.tag.c_str();
@@ -321,7 +335,7 @@ const char *hcSpecialise(HcContextImpl *c, bool row, bool f64, const HcMapProgra
   entry.failed = true; // until the kernels are there
   std::string image, tag;
   bool fromDisk = false;
-  if (!buildImage(row, f64, p, c->ccMajor, c->ccMinor, image, tag, fromDisk, s.note))
+  if (!buildImage(row, dtype, p, c->ccMajor, c->ccMinor, image, tag, fromDisk, s.note))
     return nullptr;
   OlModule module = olCreateModule(c->device, image.data(), image.size());
   if (!module) {
@@ -329,13 +343,14 @@ const char *hcSpecialise(HcContextImpl *c, bool row, bool f64, const HcMapProgra
     return nullptr;
   }
   // Every kernel of the image, under its name, beside those of the embedded images.
-  static const char *const mapVariants[] = {"f32_v4", "f32_v1", "f64_v2", "f64_v1"};
+  static const char *const mapVariants[] = {"f32_v4", "f32_v1", "f64_v2", "f64_v1",
+                                            "i32_v4", "i32_v1", "i64_v2", "i64_v1"};
   static const char *const rowVariants[] = {"f32_held_t64", "f32_held_t128", "f32_v4",
                                             "f32_v1",       "f64_v2",        "f64_v1"};
   const char *const *variants = row ? rowVariants : mapVariants;
-  const int count = row ? 6 : 4;
+  const int count = row ? 6 : 8;
   for (int i = 0; i < count; ++i) {
-    if ((variants[i][1] == '6') != f64) // "f64..." or "f32..."
+    if (std::strncmp(variants[i], kTypeNames[typeIndex(dtype)], 3) != 0)
       continue;
     char name[96];
     std::snprintf(name, sizeof name, "hc_%s_fused_%s_%s", row ? "row" : "map", tag.c_str(),
@@ -366,17 +381,19 @@ extern "C" HC_B200_API long long hcSpecialiseCompile(const HcMapProgram *program
       std::snprintf(message, messageCapacity, "%s", text.c_str());
     return -1ll;
   };
-  if (!program || (dtype != HC_F32 && dtype != HC_F64))
-    return say("hcSpecialiseCompile: a program on float32 or float64");
+  if (!program)
+    return say("hcSpecialiseCompile: null program");
   HcMapProgramDev p;
   std::memcpy(&p, program, sizeof p);
   if (p.nInstr < 1 || p.nInstr > HC_MAP_MAX_INSTR || p.nInputs < 0 ||
-      p.nInputs > HC_MAP_MAX_INPUTS || !hcSpecialisable(p))
-    return say("hcSpecialiseCompile: the program uses operations beyond `set`, or has no valid "
-               "size");
+      p.nInputs > HC_MAP_MAX_INPUTS)
+    return say("hcSpecialiseCompile: the program has no valid size");
+  if (!hcSpecialisable(p, rowProgram != 0, dtype))
+    return say("hcSpecialiseCompile: element-wise programs on float32, float64, int32 or int64; "
+               "row programs of the operations up to `set` on float32 or float64");
   std::string bytes, tag, why;
   bool fromDisk = false;
-  if (!buildImage(rowProgram != 0, dtype == HC_F64, p, ccMajor, ccMinor, bytes, tag, fromDisk, why))
+  if (!buildImage(rowProgram != 0, dtype, p, ccMajor, ccMinor, bytes, tag, fromDisk, why))
     return say(why);
   if (image && capacity)
     std::memcpy(image, bytes.data(), std::min(capacity, bytes.size()));

@@ -627,7 +627,11 @@ class KernelDispatcher:
         if plan.family == "mapped_gemm":
             # Upload the index tables (first call only) on torch's stream, before
             # the fence orders the launch after that stream.
-            r["spec"].device_tables((args[r["x"]], args[r["f"]], args[r["out"]]))
+            operands = (args[r["x"]], args[r["f"]], args[r["out"]])
+            if _tensor_convolution(r["spec"], *operands) is None:
+                r["spec"].device_tables(operands)
+            else:
+                _conv_workspace_for(self.device, operands[1])
         fence = _StreamFence(ctx, args)
         fence.before()
         for name, value in self.options.items():
@@ -665,6 +669,13 @@ class KernelDispatcher:
         elif plan.family == "mapped_gemm":
             spec = r["spec"]
             x, f, out = args[r["x"]], args[r["f"]], args[r["out"]]
+            stride = _tensor_convolution(spec, x, f, out)
+            if stride is not None:
+                # The groups together are a plain float32 convolution: the same sums,
+                # tiled by output pixels, on the tensor cores.
+                native.conv_f32_tensor(ctx, x, f, out, stride,
+                                       _conv_workspace_for(self.device, f))
+                return
             tx, tf, to = spec.device_tables((x, f, out))
             native.mapped_gemm(ctx, x, tx, f, tf, out, to, spec.groups, spec.tm, spec.tn, spec.k)
         elif plan.family == "gemm":
@@ -729,6 +740,43 @@ class _StreamFence:
 
 _workspaces = {}
 _F32_TENSOR_MIN = 1024
+
+
+# Convolutions of at least this many multiply-adds go to the tensor-core kernel
+# (below, the launch and the filter split cost more than the gathered kernel).
+_CONV_TENSOR_MIN = 1 << 24
+
+
+def _tensor_convolution(spec, x, f, out):
+    """The stride, when these mapped work-groups are a float32 convolution that
+    hcConvF32Tensor takes (contiguous arrays, at most 256 filters, a tcgen05
+    device, large enough, not switched off with HC_CONV_VARIANT=1); else None."""
+    import torch
+
+    if settings.CONV_VARIANT == 1 or not all(
+            dtype_name(t.dtype) == "float32" and t.dim() == 4 and t.is_contiguous()
+            for t in (x, f, out)):
+        return None
+    if f.shape[0] > 256 or torch.cuda.get_device_capability(x.device)[0] != 10:
+        return None
+    if out.numel() * f.shape[1] * f.shape[2] * f.shape[3] < _CONV_TENSOR_MIN:
+        return None
+    return spec.as_convolution(tuple(x.shape), tuple(f.shape), tuple(out.shape))
+
+
+def _conv_workspace_for(device, f):
+    """Scratch for the split filters of hcConvF32Tensor, kept per (device, filter shape)."""
+    import torch
+    from .._native import _dispatcher as native
+
+    nf, c, hf, wf = f.shape
+    need = native.conv_f32_workspace_bytes(nf, c, hf, wf)
+    key = (device, "conv", nf, c, hf, wf)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need:
+        buf = _workspaces[key] = torch.empty(need + 1024, dtype=torch.uint8, device=f.device)
+    offset = (-buf.data_ptr()) % 1024  # the entry point wants 1 KiB alignment
+    return buf[offset:offset + need]
 
 
 def _f32_workspace_for(device, a, m, n, k):

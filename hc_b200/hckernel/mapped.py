@@ -169,6 +169,7 @@ class MappedSpec:
         self.groups = int(np.prod(self.counts, dtype=np.int64))
         self._host = None   # tables as NumPy arrays, independent of strides
         self._device = {}   # (device, strides) -> tables as device tensors
+        self._conv = {}     # array shapes -> stride of the convolution, or None
 
     # -- evaluation ---------------------------------------------------------------
     @staticmethod
@@ -234,6 +235,93 @@ class MappedSpec:
                     "element; the reference resolves that by running groups in order, which a "
                     "parallel launch cannot reproduce")
             seen[flat] = True
+
+    def as_convolution(self, x_shape, f_shape, out_shape):
+        """The stride, when the work-groups together compute the plain convolution
+        without padding
+
+            out[n, q, oh, ow] = sum over (c, kh, kw) of
+                x[n, c, oh*s + kh, ow*s + kw] * f[q, c, kh, kw]
+
+        of arrays with these shapes - whatever the tiling, and in whatever order the
+        body enumerates the output positions and the filter taps (the reference's
+        example walks both transposed, python/hckernel/tests/test_examples.py:220-240,
+        which comes to the same sums for square outputs and filters).  None
+        otherwise.  Decided on the evaluated tables, not on the body's text."""
+        key = (tuple(x_shape), tuple(f_shape), tuple(out_shape))
+        if key not in self._conv:
+            try:
+                self._conv[key] = self._find_convolution(*key)
+            except UnsupportedKernel:
+                self._conv[key] = None
+        return self._conv[key]
+
+    def _find_convolution(self, x_shape, f_shape, out_shape):
+        if not (len(x_shape) == len(f_shape) == len(out_shape) == 4) or self.groups == 0:
+            return None
+        n, c, h, w = x_shape
+        nf, cf, hf, wf = f_shape
+        if cf != c or out_shape[:2] != (n, nf) or self.k != c * hf * wf:
+            return None
+        host = self.host_tables()
+        (xm, xo), (fm, fo), (om, oo) = host["x"], host["f"], host["out"]
+        tm, tn, k = self.tm, self.tn, self.k
+        xm, fm, om = xm.reshape(tm, k, 4), fm.reshape(k, tn, 4), om.reshape(tm, tn, 4)
+        rows, cols = np.arange(tm)[:, None], np.arange(tn)[None, :]
+        # Tile rows are images, tile columns filters; the output tile is one position.
+        if not (np.array_equal(om[:, :, 0], np.broadcast_to(rows, (tm, tn)))
+                and np.array_equal(om[:, :, 1], np.broadcast_to(cols, (tm, tn)))
+                and not om[:, :, 2:].any()):
+            return None
+        if not (np.array_equal(xm[:, :, 0], np.broadcast_to(rows, (tm, k)))
+                and np.array_equal(fm[:, :, 0], np.broadcast_to(cols, (k, tn)))):
+            return None
+        # (c, kh, kw) of every k: the same for every row of x and column of f, the
+        # same in x and f, and every tap of every channel exactly once.
+        taps = xm[0, :, 1:]
+        if not (np.array_equal(xm[:, :, 1:], np.broadcast_to(taps, (tm, k, 3)))
+                and np.array_equal(fm[:, :, 1:], np.broadcast_to(taps[:, None, :], (k, tn, 3)))):
+            return None
+        if taps.min() < 0 or (taps >= np.array([c, hf, wf])).any():
+            return None
+        flat = (taps[:, 0] * hf + taps[:, 1]) * wf + taps[:, 2]
+        if np.unique(flat).size != k:
+            return None
+        # Origins: image block, filter block and one output position per group; every
+        # (block, block, position) exactly once.
+        if fo[:, 1:].any() or xo[:, 1].any():
+            return None
+        if not (np.array_equal(xo[:, 0], oo[:, 0]) and np.array_equal(fo[:, 0], oo[:, 1])):
+            return None
+        if (oo[:, 0] % tm).any() or (oo[:, 1] % tn).any():
+            return None
+        ho, wo = out_shape[2:]
+        inside = (oo[:, 2] < ho) & (oo[:, 3] < wo)
+        if not inside.all():
+            return None
+        blocks_n, blocks_q = -(-n // tm), -(-nf // tn)
+        code = ((oo[:, 0] // tm) * blocks_q + oo[:, 1] // tn) * (ho * wo) + oo[:, 2] * wo + oo[:, 3]
+        if self.groups != blocks_n * blocks_q * ho * wo or np.unique(code).size != self.groups:
+            return None
+        if code.max() >= self.groups:
+            return None
+        # x origin = stride x output position.
+        moved = oo[:, 2:].max(axis=0)
+        stride = None
+        for axis in (0, 1):
+            if moved[axis] > 0:
+                at = np.argmax(oo[:, 2 + axis])
+                s_axis, rest = divmod(int(xo[at, 2 + axis]), int(oo[at, 2 + axis]))
+                if rest or s_axis < 1 or (stride is not None and stride != s_axis):
+                    return None
+                stride = s_axis
+        if stride is None:
+            stride = 1
+        if not np.array_equal(xo[:, 2:], oo[:, 2:] * stride):
+            return None
+        if (h - hf) // stride + 1 != ho or (w - wf) // stride + 1 != wo:
+            return None
+        return stride
 
     def host_tables(self):
         if self._host is None:

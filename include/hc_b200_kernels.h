@@ -378,6 +378,27 @@ HC_B200_API int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void 
                                 long long N, long long K, long long lda, long long ldb,
                                 long long ldc);
 
+/* float32 convolution on the tensor cores, without padding:
+ *   out[n, q, oh, ow] = sum over (c, kh, kw) of
+ *       x[n, c, oh * stride + kh, ow * stride + kw] * f[q, c, kh, kw]
+ * x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, HO, WO] with
+ * HO = (H - HF) / stride + 1 and WO = (W - WF) / stride + 1, all float32 and
+ * contiguous.  The sums of the reference's implicit-GEMM convolution
+ * (python/hckernel/tests/test_examples.py:203-252) for square outputs, tiled by
+ * output pixels instead of by (images x filters) per position: an implicit GEMM
+ * whose image operand is gathered by the kernel's threads and whose products run
+ * as three tf32 products each on tcgen05 (float32-class results, as
+ * hcGemmF32Tensor).  NF <= 256; `workspace` must hold
+ * hcConvF32TensorWorkspaceBytes(NF, C, HF, WF) bytes of device memory, 1 KiB
+ * aligned (the split filters), and is written by every call.  Fails on a device
+ * without tcgen05, where hcMappedGemm computes the same convolution. */
+HC_B200_API size_t hcConvF32TensorWorkspaceBytes(long long NF, long long C, long long HF,
+                                                 long long WF);
+HC_B200_API int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out,
+                                long long N, long long C, long long H, long long W,
+                                long long NF, long long HF, long long WF, long long stride,
+                                void *workspace, size_t workspaceBytes);
+
 /* bf16 GEMM with fp32 accumulation on the tensor cores (tcgen05); falls back
  * to the bf16 tiled kernel for layouts TMA cannot describe (a pitch that is
  * not a multiple of 8 elements or a base that is not 16-byte aligned). */

@@ -2,8 +2,8 @@
 time is compiled by NVRTC at its first launch and from then on runs as a
 straight-line kernel.  It must give bit for bit what the interpreter gives
 (option ``fused`` = 1 sends every program to the interpreter), be compiled once
-per context and program whatever the constants and shapes, and leave programs
-with the later operators (``//``, comparisons ...) to the interpreter."""
+per context and program whatever the constants and shapes.  Element-wise programs
+are compiled whatever their operators and element type; row programs on floats."""
 
 import numpy as np
 import pytest
@@ -43,6 +43,8 @@ MAP_BODIES = [
     ("quotient", lambda a, b: (a - b) / (b * b + a), 2),           # divisions: masked stores
     ("three_inputs", lambda a, b, c: np.sqrt(np.abs(a * b - c * 0.5)) + a, 3),
     ("one_input", lambda a: np.minimum(a * a * 0.5 - a, a * 0.125), 1),
+    ("select", lambda a, b: (a < b) * a + (a >= b) * b, 2),          # comparisons
+    ("divmod", lambda a, b: (a // b) * b + a % b, 2),                # out-of-line routines, masks
 ]
 MAP_SHAPES = [((64, 1024), 1024), ((33, 1001), 1001), ((17, 100), 104), ((1, 7), 7),
               ((1024, 2048), 2048)]
@@ -58,14 +60,14 @@ def test_specialised_elementwise_bodies_equal_the_interpreter(body, dtype):
     for shape, pitch in MAP_SHAPES:
         rng = np.random.default_rng(shape[1])
         arrays = [(rng.standard_normal(shape) + 0.25).astype(dtype) for _ in range(count)]
-        if name == "quotient":
+        if name in ("quotient", "divmod"):
             arrays[1][::3, ::5] = 0  # some divisors are zero: b*b + a == a ... and
             arrays[0][::3, ::5] = 0  # ... a too: 0 / 0, which numpy.ma masks
         d_in = _place(arrays, shape, pitch)
         compiled = _run(kernel, d_in, shape, pitch, (), interpret=False)
         interpreted = _run(kernel, d_in, shape, pitch, (), interpret=True)
         assert np.array_equal(compiled, interpreted, equal_nan=True), (name, shape)
-        if name == "quotient":
+        if name in ("quotient", "divmod"):
             assert (compiled[::3, ::5] == -77.0).all()  # masked elements are not stored
         else:
             with np.errstate(all="ignore"):
@@ -105,35 +107,54 @@ def test_specialised_row_bodies_equal_the_interpreter(body, dtype):
     assert after == before + 1, ctx.specialise_note
 
 
+@pytest.mark.parametrize("dtype", ["int32", "int64"])
+def test_specialised_integer_bodies_equal_the_interpreter(dtype):
+    ctx = get_context("cuda:0")
+    fn = lambda a, b: ((a << 2) ^ b) // 7 + (a % 5) * (b & 12) - abs(a)  # noqa: E731
+    kernel = make_elementwise(fn, 2, 2, (4, 64))
+    before = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
+    for shape, pitch in MAP_SHAPES:
+        rng = np.random.default_rng(shape[1] + 5)
+        arrays = [rng.integers(-1000, 1000, shape).astype(dtype) for _ in range(2)]
+        d_in = _place(arrays, shape, pitch)
+        compiled = _run(kernel, d_in, shape, pitch, (), interpret=False)
+        interpreted = _run(kernel, d_in, shape, pitch, (), interpret=True)
+        assert np.array_equal(compiled, interpreted), shape
+        assert np.array_equal(compiled, fn(*arrays)), shape  # NumPy's integer arithmetic
+    after = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
+    assert after == before + 1, ctx.specialise_note
+
+
 def test_switch_and_scope():
     ctx = get_context("cuda:0")
     x = torch.randn(256, 512, device="cuda")
     out = torch.empty_like(x)
-    count = lambda: ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
+    count = lambda: ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)  # noqa: E731
+    body = lambda a: a * 0.75 + np.exp(a) * 0.375  # noqa: E731
     # Off: interpreted, nothing compiled.
     before = count()
     ctx.set_option("specialise", 0)
     try:
-        make_elementwise(lambda a: a * 0.75 + np.exp(a) * 0.5, 1, 2, (4, 64))(x, out)
+        make_elementwise(body, 1, 2, (4, 64))(x, out)
     finally:
         ctx.set_option("specialise", 1)
     torch.cuda.synchronize()
     assert count() == before
-    assert torch.allclose(out, x * 0.75 + x.exp() * 0.5, rtol=1e-5, atol=1e-6)
-    # The later operators stay with the interpreter, also when compiling is demanded.
+    assert torch.allclose(out, x * 0.75 + x.exp() * 0.375, rtol=1e-5, atol=1e-6)
+    # Demanded: compiled (NVRTC is there), and the launch succeeds.
     ctx.set_option("specialise", 2)
     try:
-        make_elementwise(lambda a: a // 0.5 + (a > 0.0), 1, 2, (4, 64))(x, out)
-        torch.cuda.synchronize()
-        assert count() == before
-        assert torch.equal(out, torch.floor(x / 0.5) + (x > 0).float())
-        # ... and a plain body is compiled under it.
-        make_elementwise(lambda a: a * 0.75 + np.exp(a) * 0.5, 1, 2, (4, 64))(x, out)
+        make_elementwise(body, 1, 2, (4, 64))(x, out)
         torch.cuda.synchronize()
         assert count() == before + 1, ctx.specialise_note
     finally:
         ctx.set_option("specialise", 1)
-    assert torch.allclose(out, x * 0.75 + x.exp() * 0.5, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(out, x * 0.75 + x.exp() * 0.375, rtol=1e-5, atol=1e-6)
+    # Another constant is the same program: nothing new is compiled.
+    make_elementwise(lambda a: a * 0.5 + np.exp(a) * 2.0, 1, 2, (4, 64))(x, out)
+    torch.cuda.synchronize()
+    assert count() == before + 1
+    assert torch.allclose(out, x * 0.5 + x.exp() * 2.0, rtol=1e-5, atol=1e-6)
 
 
 def test_a_specialised_body_runs_at_the_speed_of_a_precompiled_one():

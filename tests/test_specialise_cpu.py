@@ -2,7 +2,8 @@
 turns a program for the accumulator machine into an sm_100a image with NVRTC
 (the kernel templates are embedded in the library as text), gives the same image
 for the same program, keeps images in the directory of HC_B200_KERNEL_CACHE, and
-refuses what the straight-line kernels do not cover."""
+refuses what the straight-line kernels do not cover (row programs on integers
+or with the later operators)."""
 
 import os
 import subprocess
@@ -54,12 +55,23 @@ def test_constants_are_not_part_of_the_key():
     assert capi.specialise_compile(c)[1] != capi.specialise_compile(a)[1]
 
 
-def test_operations_beyond_set_are_refused():
-    p = _program([ew.LOAD, ew.FLOORDIV | (8 << 8)], 1)
-    with pytest.raises(RuntimeError, match="beyond `set`"):
-        capi.specialise_compile(p)
-    with pytest.raises(RuntimeError, match="float32 or float64"):
-        capi.specialise_compile(_program(MAP_CODE, 2), dtype=capi.HC_I32)
+def test_the_later_operators_and_integer_tiles():
+    """Element-wise programs compile with the whole operator table and on integer
+    tiles; row programs take the operations up to `set` on floats only."""
+    later = [ew.LOAD, ew.FLOORDIV | (1 << 8), ew.SAVE0, ew.LOAD, ew.LT | (1 << 8),
+             ew.ADD | (4 << 8)]
+    image, tag = capi.specialise_compile(_program(later, 2))
+    assert f"hc_map_fused_{tag}_f32_v4".encode() in image
+    for dtype, name in ((capi.HC_I32, "i32_v4"), (capi.HC_I64, "i64_v2")):
+        ints = [ew.LOAD, ew.SHL | (8 << 8), ew.XOR | (1 << 8), ew.MOD | (9 << 8), ew.INV]
+        image, tag = capi.specialise_compile(_program(ints, 2), dtype=dtype)
+        assert f"hc_map_fused_{tag}_{name}".encode() in image
+    with pytest.raises(RuntimeError, match="row programs of the operations up to `set`"):
+        capi.specialise_compile(_program([ew.LOAD, ew.FLOORDIV | (8 << 8)], 1), row_program=True)
+    with pytest.raises(RuntimeError, match="row programs of the operations up to `set`"):
+        capi.specialise_compile(_program(ROW_CODE, 1), row_program=True, dtype=capi.HC_I32)
+    with pytest.raises(RuntimeError, match="element-wise programs on float32"):
+        capi.specialise_compile(_program(MAP_CODE, 2), dtype=capi.HC_BF16)
 
 
 def test_images_are_kept_in_the_cache_directory(tmp_path):
