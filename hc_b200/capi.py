@@ -210,7 +210,7 @@ KERNELS_PROTOTYPES = {
     "hcGemmF32Tensor": (
         C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll]
     ),
-    "hcConvF32TensorWorkspaceBytes": (_sz, [_ll, _ll, _ll, _ll]),
+    "hcConvF32TensorWorkspaceBytes": (_sz, [_ll, _ll, _ll, _ll, _ll, _ll, _ll]),
     "hcConvF32Tensor": (
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _vp, _sz]
     ),

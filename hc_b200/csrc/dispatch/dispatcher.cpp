@@ -554,8 +554,9 @@ size_t gemmF32WorkspaceBytes(long long m, long long n, long long k) {
 
 // float32 convolution without padding on the tensor cores (hcConvF32Tensor):
 // x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, HO, WO], all contiguous.
-size_t convF32WorkspaceBytes(long long nf, long long c, long long hf, long long wf) {
-  return hcConvF32TensorWorkspaceBytes(nf, c, hf, wf);
+size_t convF32WorkspaceBytes(long long n, long long c, long long h, long long w, long long nf,
+                             long long hf, long long wf) {
+  return hcConvF32TensorWorkspaceBytes(n, c, h, w, nf, hf, wf);
 }
 
 bool contiguous(const ArrayArg &a) {
@@ -727,8 +728,8 @@ PYBIND11_MODULE(_dispatcher, m) {
         py::arg("k"));
   m.def("conv_f32_tensor", &convF32Tensor, py::arg("ctx"), py::arg("x"), py::arg("f"),
         py::arg("out"), py::arg("stride"), py::arg("workspace"));
-  m.def("conv_f32_workspace_bytes", &convF32WorkspaceBytes, py::arg("nf"), py::arg("c"),
-        py::arg("hf"), py::arg("wf"));
+  m.def("conv_f32_workspace_bytes", &convF32WorkspaceBytes, py::arg("n"), py::arg("c"),
+        py::arg("h"), py::arg("w"), py::arg("nf"), py::arg("hf"), py::arg("wf"));
   m.def("gemm_w8a16", &gemmW8A16, py::arg("ctx"), py::arg("a"), py::arg("w"),
         py::arg("scale"), py::arg("out"), py::arg("workspace") = py::none());
   m.def("w8a16_workspace_bytes", &w8a16WorkspaceBytes, py::arg("n"), py::arg("k"));

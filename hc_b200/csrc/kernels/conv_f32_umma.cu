@@ -21,7 +21,10 @@
 // hi*hi accumulate in fp32 in TMEM - float32-class results (the parity bound
 // of the float32 kernels is 1e-5 * sum|x||f|).
 //
-// One persistent CTA per SM, 448 threads:
+// Two kernels.  hc_split_tf32_pairs writes x once as (hi, lo) pairs - the nine
+// taps of a 3 x 3 filter read every element nine times, and splitting it in the
+// main loop cost three times the instructions of loading it.  hc_conv_f32_umma:
+// one persistent CTA per SM, 704 threads:
 //   warp 0      TMA producer of the filter tiles: per 32-deep K block two boxes
 //               (f hi, f lo; [NF rows, 32 k], 128-byte swizzle, rows beyond NF
 //               and k beyond K zero-filled; no multicast);
@@ -29,12 +32,17 @@
 //               twelve per K block, small terms first;
 //   warps 2-5   epilogue: tcgen05.ld, then for every filter a store that is
 //               contiguous across the warp's 32 pixels;
-//   warps 6-13  the image operand: thread (row m, half h) loads its 16 elements
-//               of the K block straight from x (read-only path, L1 keeps the
-//               lines that the nine taps share), splits them and writes hi and
-//               lo into the stage in the 128-byte-swizzled K-major layout the
-//               MMA descriptors expect; fence.proxy.async, then one arrival
-//               per warp on the stage's barrier.
+//   warps 6-21  the image operand: thread (row m, quarter h) loads its 8
+//               (hi, lo) pairs of the K block with 8-byte loads (read-only
+//               path, L1 keeps the lines that the taps share), two blocks
+//               ahead of their use, and writes hi and lo into the stage in the
+//               128-byte-swizzled K-major layout the MMA descriptors expect,
+//               then fence.proxy.async.  The 512 threads meet once per K block
+//               at a named barrier (bar.sync 1); only their leader touches the
+//               mbarriers - it waits for the next free stage before the meeting
+//               and reports the stage filled after it.  (Sixteen warps polling
+//               and arriving on the stage barriers themselves cost 900 cycles
+//               per K block in barrier traffic alone.)
 // Two accumulators in TMEM let the epilogue of a tile overlap the next tile's
 // main loop.  Every mbarrier wait is bounded (hc_ptx.cuh).
 #include "conv_params.h"
@@ -47,7 +55,8 @@ using namespace hc;
 constexpr int BM = 128;   // output pixels per tile (TMEM lanes)
 constexpr int BK = 32;    // K depth of a stage: one 128-byte row
 constexpr int UMMA_K = 8;
-constexpr int GATHER_WARPS = 8;
+constexpr int GATHER_WARPS = 16;
+constexpr int PER_THREAD = BM * BK / (32 * GATHER_WARPS); // k of a block per thread: 8
 constexpr int NUM_THREADS = 32 * (6 + GATHER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // TMEM columns between the two accumulators
@@ -61,11 +70,23 @@ struct alignas(8) Barriers {
   uint64_t tmemEmpty[2];
   uint32_t tmemBase;
   int abortFlag;
+  int gatherGo[2]; // what the gatherers' leader found: go on (1) or leave (0), per parity
 };
 
 enum : int { kStatusGatherWait = 6 }; // the image gatherers waiting for a free stage
 
 } // namespace
+
+// (hi, lo) of every element, interleaved: out[i] = {tf32(in[i]), tf32(in[i] - hi)}.
+extern "C" __global__ void __launch_bounds__(256)
+    hc_split_tf32_pairs(const float *__restrict__ in, float2 *__restrict__ out, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float hi, lo;
+    splitTf32(in[i], hi, lo);
+    out[i] = make_float2(hi, lo);
+  }
+}
 
 extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     hc_conv_f32_umma(const __grid_constant__ CUtensorMap mapFHi,
@@ -85,7 +106,7 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbarInit(smemAddr(&bars->full[s]), 1 + GATHER_WARPS);
+      mbarInit(smemAddr(&bars->full[s]), 2); // the filter tile's expect_tx, the gatherers' leader
       mbarInit(smemAddr(&bars->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -159,23 +180,24 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ------------------------ image operand by the threads ----------------------
     const int g = warp - 6;
     const int m = (g & 3) * 32 + lane; // row of the tile
-    const int half = g >> 2;           // which 16 of the 32 k of a block
+    const int part = g >> 2;           // which 8 of the 32 k of a block
     const long long xsN = (long long)p.C * p.H * p.W;
+    const float2 *pairs = static_cast<const float2 *>(p.x);
     // Where row m keeps chunk c (16 bytes, four k) of its 128-byte row.
     const uint32_t rowOffset = uint32_t(m >> 3) * 1024u + uint32_t(m & 7) * 128u;
-    // Where the elements of K block `kb` of tile `t` start for this row.
+    // Where the elements of tile `t` start for this row.
     auto rowSource = [&](int t) {
       const int n = t / p.tilesPerImage, tp = t - n * p.tilesPerImage;
       int pix = tp * BM + m;
       if (pix >= pixels)
         pix = 0; // a row past the image computes something that is never stored
       const int oh = pix / p.WO, ow = pix - oh * p.WO;
-      return p.x + n * xsN + (long long)oh * p.stride * p.W + ow * p.stride;
+      return pairs + n * xsN + (long long)oh * p.stride * p.W + ow * p.stride;
     };
-    auto loadBlock = [&](const float *src, int kb, float (&v)[16]) {
-      const int k0 = kb * BK + half * 16;
+    auto loadBlock = [&](const float2 *src, int kb, float2 (&v)[PER_THREAD]) {
+      const int k0 = kb * BK + part * PER_THREAD;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < PER_THREAD / 4; ++q) {
         const int4 o = *reinterpret_cast<const int4 *>(koff + k0 + 4 * q);
         v[4 * q + 0] = __ldg(src + o.x);
         v[4 * q + 1] = __ldg(src + o.y);
@@ -185,11 +207,11 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     };
     // The loads of a K block are issued two blocks ahead of its stores, into one
     // of three register buffers that the unrolled loop names at compile time, so
-    // that their latency is covered by the splitting and storing of the blocks
-    // before (nothing is copied between buffers, which would wait for the loads).
+    // that their latency is covered by the storing of the blocks before (nothing
+    // is copied between buffers, which would wait for the loads).
     struct Cursor {
       int t, kb;
-      const float *src;
+      const float2 *src;
       bool have;
     };
     auto advance = [&](Cursor &c) {
@@ -202,46 +224,66 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
     };
     constexpr int AHEAD = 2, BUFFERS = AHEAD + 1;
-    Cursor fetch{int(blockIdx.x), 0, p.x, int(blockIdx.x) < numTiles};
+    Cursor fetch{int(blockIdx.x), 0, pairs, int(blockIdx.x) < numTiles};
     if (fetch.have)
       fetch.src = rowSource(fetch.t);
     Cursor use = fetch;
-    float buf[BUFFERS][16];
+    float2 buf[BUFFERS][PER_THREAD];
 #pragma unroll
     for (int r = 0; r < AHEAD; ++r) {
       if (fetch.have)
         loadBlock(fetch.src, fetch.kb, buf[r]);
       advance(fetch);
     }
+    const bool leader = threadIdx.x == 6 * 32;
+    auto meet = [] { asm volatile("bar.sync 1, %0;" ::"r"(32 * GATHER_WARPS) : "memory"); };
+    // The leader waits for the stage of block `index` and notes the outcome where
+    // the others read it after the next meeting.
+    auto awaitStage = [&](uint32_t index) {
+      const uint32_t s = index % stages, phase = (index / stages) & 1u;
+      const bool ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, p.status,
+                               kStatusGatherWait);
+      *(volatile int *)&bars->gatherGo[index & 1u] = ok ? 1 : 0;
+    };
     uint32_t it = 0;
-    bool ok = true;
-    while (use.have && ok) {
+    if (leader && use.have)
+      awaitStage(0);
+    bool go = use.have;
+    bool pending = false; // block it - 1 is stored but not yet reported
+    while (go) {
 #pragma unroll
       for (int r = 0; r < BUFFERS; ++r) {
-        if (!use.have || !ok)
+        if (!go)
           break;
         if (fetch.have)
           loadBlock(fetch.src, fetch.kb, buf[(r + AHEAD) % BUFFERS]);
         advance(fetch);
-        const uint32_t s = it % stages, phase = (it / stages) & 1u;
-        if (lane == 0)
-          ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, p.status,
-                        kStatusGatherWait);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok)
+        // Everybody's stores of the block before are done and fenced, and the
+        // leader knows whether the stage of this block is free.
+        meet();
+        if (leader && pending)
+          mbarArrive(smemAddr(&bars->full[(it - 1) % stages]));
+        pending = false;
+        if (*(volatile int *)&bars->gatherGo[it & 1u] == 0) {
+          go = false; // a wait gave up: everybody leaves here, together
           break;
-        const int k0 = use.kb * BK + half * 16;
+        }
+        const uint32_t s = it % stages;
+        const int k0 = use.kb * BK + part * PER_THREAD;
+        // Beyond K the filter tile is zero; the image side must then be finite
+        // (only the last block can reach beyond K).
+        const bool ragged = k0 + PER_THREAD > p.K;
         unsigned char *stage = aligned + s * stageBytes;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < PER_THREAD / 4; ++q) {
           float hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            // Beyond K the filter tile is zero; the image side must be finite.
-            const float value = (k0 + 4 * q + e < p.K) ? buf[r][4 * q + e] : 0.0f;
-            splitTf32(value, hi[e], lo[e]);
+            const bool beyond = ragged && k0 + 4 * q + e >= p.K;
+            hi[e] = beyond ? 0.0f : buf[r][4 * q + e].x;
+            lo[e] = beyond ? 0.0f : buf[r][4 * q + e].y;
           }
-          const uint32_t chunk = uint32_t(half * 4 + q);
+          const uint32_t chunk = uint32_t(part * (PER_THREAD / 4) + q);
           const uint32_t at = rowOffset + ((chunk ^ uint32_t(m & 7)) << 4);
           *reinterpret_cast<float4 *>(stage + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<float4 *>(stage + kABytes + at) =
@@ -249,13 +291,19 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         // The MMA reads shared memory through the async proxy.
         fenceProxyAsync();
-        __syncwarp();
-        if (lane == 0)
-          mbarArrive(smemAddr(&bars->full[s]));
+        pending = true;
         advance(use);
         ++it;
+        if (!use.have)
+          go = false; // the last block: the meeting below closes it
+        else if (leader)
+          awaitStage(it);
       }
     }
+    // The stores of the last block (none are left if a wait gave up).
+    meet();
+    if (leader && pending)
+      mbarArrive(smemAddr(&bars->full[(it - 1) % stages]));
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {

@@ -9,7 +9,7 @@
 // x [N, C, H, W], f [NF, C, HF, WF], out [N, NF, HO, WO], all float32 and
 // contiguous; no padding: HO = (H - HF) / stride + 1, WO likewise.
 struct HcConvParams {
-  const float *x;
+  const void *x;   // the image as (hi, lo) float pairs (hc_split_tf32_pairs), layout of x
   float *out;
   int32_t N, C, H, W;
   int32_t NF, HF, WF, stride;

@@ -293,6 +293,19 @@ __device__ __forceinline__ void ummaTf32(uint32_t dTmem, uint64_t aDesc, uint64_
                  : "memory");
 }
 
+// The same with the A operand in tensor memory: 128 lanes (the rows) by 8 columns
+// (the K elements, 32 bits each) starting at `aTmem`.
+__device__ __forceinline__ void ummaTf32TmemA(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc,
+                                              uint32_t iDesc, uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+               "}\n" ::"r"(dTmem),
+               "r"(aTmem), "l"(bDesc), "r"(iDesc), "r"(accumulate)
+               : "memory");
+}
+
 // Makes `bar` (this CTA) complete one arrival once every MMA issued so far by
 // this thread has finished.
 __device__ __forceinline__ void ummaCommit(uint32_t bar) {
@@ -327,6 +340,20 @@ __device__ __forceinline__ void tmemLoad32x32(uint32_t taddr, uint32_t (&v)[32])
         "=r"(v[31])
       : "r"(taddr)
       : "memory");
+}
+
+// 32 lanes x 8 consecutive 32-bit columns: thread i of the warp writes columns
+// [col, col+8) of TMEM lane (laneBase + i).
+__device__ __forceinline__ void tmemStore32x8(uint32_t taddr, const uint32_t (&v)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::
+                   "r"(taddr),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+               "r"(v[7])
+               : "memory");
+}
+
+__device__ __forceinline__ void tmemStoreWait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmemLoadWait() {

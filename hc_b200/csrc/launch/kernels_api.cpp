@@ -121,6 +121,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_f32_umma", "gemm_f32_umma"},
     {"hc_gemm_f32_umma_pair", "gemm_f32_umma"},
     {"hc_conv_f32_umma", "conv_f32_umma"},
+    {"hc_split_tf32_pairs", "conv_f32_umma"},
 };
 
 // Image that defines `kernel`; a table entry ending in '_' stands for every
@@ -1390,11 +1391,17 @@ int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *
 }
 
 // ---- float32 convolution on the tensor cores (conv_f32_umma.cu) ---------------------
-size_t hcConvF32TensorWorkspaceBytes(long long NF, long long C, long long HF, long long WF) {
-  if (NF <= 0 || C <= 0 || HF <= 0 || WF <= 0)
-    return 0;
+static size_t convFilterBytes(long long NF, long long C, long long HF, long long WF) {
   // hi and lo parts of f as a matrix [NF, Kp], each 1 KiB aligned.
   return 2 * size_t(roundUp(NF * f32Pitch(C * HF * WF) * 4, 1024));
+}
+
+size_t hcConvF32TensorWorkspaceBytes(long long N, long long C, long long H, long long W,
+                                     long long NF, long long HF, long long WF) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || NF <= 0 || HF <= 0 || WF <= 0)
+    return 0;
+  // The split filters, then the image as (hi, lo) pairs.
+  return convFilterBytes(NF, C, HF, WF) + size_t(roundUp(N * C * H * W * 8, 1024));
 }
 
 int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long long N,
@@ -1434,15 +1441,26 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   if (stages < 2)
     return c->fail("%s: a reduction over %lld elements with %lld filters does not fit in "
                    "shared memory", who, K, NF);
-  const size_t need = hcConvF32TensorWorkspaceBytes(NF, C, HF, WF);
+  const size_t need = hcConvF32TensorWorkspaceBytes(N, C, H, W, NF, HF, WF);
   if (!workspace || workspaceBytes < need || !aligned(workspace, 1024))
     return c->fail("%s: workspace of %zu bytes (1 KiB aligned) needed, got %zu", who, need,
                    workspaceBytes);
   if (!aligned(x, 4) || !aligned(out, 4) || !aligned(f, 4))
     return c->fail("%s: arrays must be 4-byte aligned", who);
   auto *base = static_cast<unsigned char *>(workspace);
+  const size_t filterBytes = convFilterBytes(NF, C, HF, WF);
   float *fHi = reinterpret_cast<float *>(base);
-  float *fLo = reinterpret_cast<float *>(base + need / 2);
+  float *fLo = reinterpret_cast<float *>(base + filterBytes / 2);
+  void *xPairs = base + filterBytes;
+  {
+    // x once as (hi, lo) pairs: every element is read once per filter tap.
+    long long count = N * C * H * W;
+    long long grid = std::max<long long>(1, std::min<long long>(ceilDiv(count, 256),
+                                                                c->smCount * 8));
+    void *args[] = {&x, &xPairs, &count};
+    if (c->launch("hc_split_tf32_pairs", size_t(grid), 1, 1, 256, args, 3, 0))
+      return 1;
+  }
   {
     // f is the K-major [NF, K] operand as it lies in memory.
     long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(kp, 256), 64));
@@ -1458,7 +1476,7 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
                              size_t(kp) * 4, size_t(nPad), 32, 128))
       return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
   HcConvParams p{};
-  p.x = static_cast<const float *>(x);
+  p.x = xPairs;
   p.out = static_cast<float *>(out);
   p.N = int(N), p.C = int(C), p.H = int(H), p.W = int(W);
   p.NF = int(NF), p.HF = int(HF), p.WF = int(WF), p.stride = int(stride);
@@ -1471,7 +1489,7 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   const long long grid = std::min<long long>(tiles, c->smCount);
   const size_t smem = size_t(stages * stageBytes + fixed);
   void *args[] = {&maps[0], &maps[1], &p};
-  return c->launch("hc_conv_f32_umma", size_t(grid), 1, 1, 448, args, 3, smem);
+  return c->launch("hc_conv_f32_umma", size_t(grid), 1, 1, 704, args, 3, smem);
 }
 
 int hcGemmBf16Peers(HcContext c, const void *a, const void *b, const HcPeerOutputs *dsts,

@@ -631,7 +631,7 @@ class KernelDispatcher:
             if _tensor_convolution(r["spec"], *operands) is None:
                 r["spec"].device_tables(operands)
             else:
-                _conv_workspace_for(self.device, operands[1])
+                _conv_workspace_for(self.device, operands[0], operands[1])
         fence = _StreamFence(ctx, args)
         fence.before()
         for name, value in self.options.items():
@@ -674,7 +674,7 @@ class KernelDispatcher:
                 # The groups together are a plain float32 convolution: the same sums,
                 # tiled by output pixels, on the tensor cores.
                 native.conv_f32_tensor(ctx, x, f, out, stride,
-                                       _conv_workspace_for(self.device, f))
+                                       _conv_workspace_for(self.device, x, f))
                 return
             tx, tf, to = spec.device_tables((x, f, out))
             native.mapped_gemm(ctx, x, tx, f, tf, out, to, spec.groups, spec.tm, spec.tn, spec.k)
@@ -764,14 +764,15 @@ def _tensor_convolution(spec, x, f, out):
     return spec.as_convolution(tuple(x.shape), tuple(f.shape), tuple(out.shape))
 
 
-def _conv_workspace_for(device, f):
-    """Scratch for the split filters of hcConvF32Tensor, kept per (device, filter shape)."""
+def _conv_workspace_for(device, x, f):
+    """Scratch for the split operands of hcConvF32Tensor, kept per (device, shapes)."""
     import torch
     from .._native import _dispatcher as native
 
-    nf, c, hf, wf = f.shape
-    need = native.conv_f32_workspace_bytes(nf, c, hf, wf)
-    key = (device, "conv", nf, c, hf, wf)
+    n, c, h, w = x.shape
+    nf, _, hf, wf = f.shape
+    need = native.conv_f32_workspace_bytes(n, c, h, w, nf, hf, wf)
+    key = (device, "conv", n, c, h, w, nf, hf, wf)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < need:
         buf = _workspaces[key] = torch.empty(need + 1024, dtype=torch.uint8, device=f.device)

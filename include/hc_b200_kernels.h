@@ -389,10 +389,12 @@ HC_B200_API int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void 
  * whose image operand is gathered by the kernel's threads and whose products run
  * as three tf32 products each on tcgen05 (float32-class results, as
  * hcGemmF32Tensor).  NF <= 256; `workspace` must hold
- * hcConvF32TensorWorkspaceBytes(NF, C, HF, WF) bytes of device memory, 1 KiB
- * aligned (the split filters), and is written by every call.  Fails on a device
- * without tcgen05, where hcMappedGemm computes the same convolution. */
-HC_B200_API size_t hcConvF32TensorWorkspaceBytes(long long NF, long long C, long long HF,
+ * hcConvF32TensorWorkspaceBytes(N, C, H, W, NF, HF, WF) bytes of device memory,
+ * 1 KiB aligned (the split filters and the image as (hi, lo) pairs: twice the
+ * size of x), and is written by every call.  Fails on a device without tcgen05,
+ * where hcMappedGemm computes the same convolution. */
+HC_B200_API size_t hcConvF32TensorWorkspaceBytes(long long N, long long C, long long H,
+                                                 long long W, long long NF, long long HF,
                                                  long long WF);
 HC_B200_API int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out,
                                 long long N, long long C, long long H, long long W,

@@ -18,8 +18,8 @@ from tests.gpu_util import dev, empty_like_dev, finish
 pytestmark = pytest.mark.gpu
 
 
-def _workspace(hc, nf, c, hf, wf):
-    need = hc.lib.hcConvF32TensorWorkspaceBytes(nf, c, hf, wf)
+def _workspace(hc, n, c, h, w, nf, hf, wf):
+    need = hc.lib.hcConvF32TensorWorkspaceBytes(n, c, h, w, nf, hf, wf)
     buf = torch.empty(need + 1024, dtype=torch.uint8, device="cuda")
     return buf, buf.data_ptr() + (-buf.data_ptr()) % 1024, need
 
@@ -28,7 +28,7 @@ def _conv(hc, x, f, stride):
     n, c, h, w = x.shape
     nf, _, hf, wf = f.shape
     ho, wo = (h - hf) // stride + 1, (w - wf) // stride + 1
-    keep, ws, need = _workspace(hc, nf, c, hf, wf)
+    keep, ws, need = _workspace(hc, n, c, h, w, nf, hf, wf)
     d_x, d_f = dev(x), dev(f)
     d_o = torch.full((n, nf, ho, wo), float("nan"), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
@@ -92,7 +92,7 @@ def test_agrees_with_the_gathered_kernel_and_the_oracle(hc):
 
 
 def test_refusals(hc):
-    keep, ws, need = _workspace(hc, 4, 3, 3, 3)
+    keep, ws, need = _workspace(hc, 2, 3, 8, 8, 4, 3, 3)
     with pytest.raises(RuntimeError, match="invalid shape"):
         hc.conv_f32_tensor(1, 1, 1, 2, 3, 2, 8, 4, 3, 3, 1, ws, need)  # filter taller than image
     with pytest.raises(RuntimeError, match="at most 256 filters"):
@@ -108,7 +108,8 @@ def test_refusals(hc):
 def test_the_front_door_sends_convolution_bodies_to_the_tensor_cores():
     """The reference's implicit-GEMM body (python/hckernel/tests/test_examples.py:203-252):
     its work-groups are recognised from their evaluated index tables as a plain
-    convolution and run on hcConvF32Tensor (two launches: filter split, convolution);
+    convolution and run on hcConvF32Tensor (three launches: the two operand splits and the
+    convolution);
     with ``settings.CONV_VARIANT = 1`` they run as the body tiles them (one launch of
     the gathered kernel).  Both within the float32 parity bound of the exact sums."""
     from hc_b200.hckernel import settings
@@ -134,7 +135,7 @@ def test_the_front_door_sends_convolution_bodies_to_the_tensor_cores():
         finally:
             settings.CONV_VARIANT = 0
         assert np.all(np.abs(out.cpu().numpy().astype(np.float64) - exact) <= bound)
-    assert launches == {0: 2, 1: 1}
+    assert launches == {0: 3, 1: 1}
     # A rectangular image is not the plain convolution (the body walks the output
     # positions transposed): it stays with the gathered kernel.
     xr, fr = oracle.make_conv_inputs((8, 16, 34, 66), (32, 16, 3, 3), "float32")
