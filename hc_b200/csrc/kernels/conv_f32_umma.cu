@@ -61,7 +61,7 @@ constexpr int NUM_THREADS = 32 * (6 + GATHER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // TMEM columns between the two accumulators
 constexpr int kABytes = BM * BK * 4;
-constexpr int MAX_STAGES = 4;
+constexpr int MAX_STAGES = 6;
 
 struct alignas(8) Barriers {
   uint64_t full[MAX_STAGES];
@@ -88,13 +88,25 @@ extern "C" __global__ void __launch_bounds__(256)
   }
 }
 
-extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
-    hc_conv_f32_umma(const __grid_constant__ CUtensorMap mapFHi,
-                     const __grid_constant__ CUtensorMap mapFLo,
-                     const __grid_constant__ HcConvParams p) {
-  extern __shared__ __align__(1024) unsigned char smemRaw[];
+namespace {
+
+// TMEM_A: the image operand of a K block goes to tensor memory (tcgen05.st: lane =
+// row, 32 columns hi then 32 columns lo per stage) and the MMA reads it from
+// there, so that shared memory carries the filter tiles alone.  With the image
+// operand in shared memory every MMA of N = 64 reads 4 KiB of A for 2 KiB of B,
+// and the shared-memory port, not the tensor pipe, sets the pace.  Needs room in
+// TMEM: two accumulators of at most 128 columns and four to six stages of 64.
+template <bool TMEM_A>
+__device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtensorMap &mapFLo,
+                                        const HcConvParams &p, unsigned char *smemRaw) {
+  constexpr int kAStage = TMEM_A ? 0 : 2 * kABytes; // bytes of A in a shared-memory stage
+  // TMEM columns: the two accumulators, then (TMEM_A) the A stages of 64 columns
+  // each - with at most 64 filters the accumulators take 128 columns and leave
+  // room for six stages, with at most 128 they take 256 and leave room for four.
+  const int kAccStride = TMEM_A ? (p.nPad <= 64 ? 64 : 128) : ACC_STRIDE;
+  const uint32_t kATmemBase = uint32_t(2 * kAccStride);
   const int bBytes = p.nPad * BK * 4; // one of f hi / f lo
-  const int stageBytes = 2 * kABytes + 2 * bBytes;
+  const int stageBytes = kAStage + 2 * bBytes;
   const int stages = p.stages;
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
   unsigned char *aligned = smemRaw + (smemBase - smemAddr(smemRaw));
@@ -157,8 +169,8 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint32_t fullBar = smemAddr(&bars->full[s]);
           const uint32_t stage = smemBase + s * stageBytes;
           mbarExpectTx(fullBar, 2 * bBytes);
-          tmaLoad2D(stage + 2 * kABytes, &mapFHi, fullBar, kb * BK, 0);
-          tmaLoad2D(stage + 2 * kABytes + bBytes, &mapFLo, fullBar, kb * BK, 0);
+          tmaLoad2D(stage + kAStage, &mapFHi, fullBar, kb * BK, 0);
+          tmaLoad2D(stage + kAStage + bBytes, &mapFLo, fullBar, kb * BK, 0);
         }
       }
       // Tail: the commits that free the last stages must have landed before the
@@ -179,8 +191,9 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
   } else if (warp >= 6) {
     // ------------------------ image operand by the threads ----------------------
     const int g = warp - 6;
-    const int m = (g & 3) * 32 + lane; // row of the tile
-    const int part = g >> 2;           // which 8 of the 32 k of a block
+    // A warp reaches the TMEM lanes of its quarter (warp index mod 4) only.
+    const int m = (warp & 3) * 32 + lane; // row of the tile
+    const int part = g >> 2;              // which 8 of the 32 k of a block
     const long long xsN = (long long)p.C * p.H * p.W;
     const float2 *pairs = static_cast<const float2 *>(p.x);
     // Where row m keeps chunk c (16 bytes, four k) of its 128-byte row.
@@ -273,24 +286,40 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
         // Beyond K the filter tile is zero; the image side must then be finite
         // (only the last block can reach beyond K).
         const bool ragged = k0 + PER_THREAD > p.K;
-        unsigned char *stage = aligned + s * stageBytes;
+        if constexpr (TMEM_A) {
+          uint32_t hi[PER_THREAD], lo[PER_THREAD];
 #pragma unroll
-        for (int q = 0; q < PER_THREAD / 4; ++q) {
-          float hi[4], lo[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const bool beyond = ragged && k0 + 4 * q + e >= p.K;
-            hi[e] = beyond ? 0.0f : buf[r][4 * q + e].x;
-            lo[e] = beyond ? 0.0f : buf[r][4 * q + e].y;
+          for (int e = 0; e < PER_THREAD; ++e) {
+            const bool beyond = ragged && k0 + e >= p.K;
+            hi[e] = beyond ? 0u : __float_as_uint(buf[r][e].x);
+            lo[e] = beyond ? 0u : __float_as_uint(buf[r][e].y);
           }
-          const uint32_t chunk = uint32_t(part * (PER_THREAD / 4) + q);
-          const uint32_t at = rowOffset + ((chunk ^ uint32_t(m & 7)) << 4);
-          *reinterpret_cast<float4 *>(stage + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<float4 *>(stage + kABytes + at) =
-              make_float4(lo[0], lo[1], lo[2], lo[3]);
+          const uint32_t at = tmemBase + (uint32_t((warp & 3) * 32) << 16) + kATmemBase +
+                              s * 64u + uint32_t(part * PER_THREAD);
+          tmemStore32x8(at, hi);
+          tmemStore32x8(at + 32u, lo);
+          tmemStoreWait();
+          tcgen05FenceBefore();
+        } else {
+          unsigned char *stage = aligned + s * stageBytes;
+#pragma unroll
+          for (int q = 0; q < PER_THREAD / 4; ++q) {
+            float hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const bool beyond = ragged && k0 + 4 * q + e >= p.K;
+              hi[e] = beyond ? 0.0f : buf[r][4 * q + e].x;
+              lo[e] = beyond ? 0.0f : buf[r][4 * q + e].y;
+            }
+            const uint32_t chunk = uint32_t(part * (PER_THREAD / 4) + q);
+            const uint32_t at = rowOffset + ((chunk ^ uint32_t(m & 7)) << 4);
+            *reinterpret_cast<float4 *>(stage + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<float4 *>(stage + kABytes + at) =
+                make_float4(lo[0], lo[1], lo[2], lo[3]);
+          }
+          // The MMA reads shared memory through the async proxy.
+          fenceProxyAsync();
         }
-        // The MMA reads shared memory through the async proxy.
-        fenceProxyAsync();
         pending = true;
         advance(use);
         ++it;
@@ -318,7 +347,7 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
                       kStatusMmaWaitTmem))
           break;
         tcgen05FenceAfter();
-        const uint32_t dTmem = tmemBase + uint32_t(acc * ACC_STRIDE);
+        const uint32_t dTmem = tmemBase + uint32_t(acc * kAccStride);
         bool ok = true;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
           const uint32_t s = it % stages, phase = (it / stages) & 1u;
@@ -329,19 +358,32 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
           tcgen05FenceAfter();
           const uint32_t stage = smemBase + s * stageBytes;
-          // All four operands are K-major: rows of 128 bytes, 8-row groups 1024
-          // bytes apart.
-          const uint64_t aHi = makeSmemDesc(stage, 16, 1024);
-          const uint64_t aLo = makeSmemDesc(stage + kABytes, 16, 1024);
-          const uint64_t bHi = makeSmemDesc(stage + 2 * kABytes, 16, 1024);
-          const uint64_t bLo = makeSmemDesc(stage + 2 * kABytes + bBytes, 16, 1024);
+          // The filter tiles are K-major: rows of 128 bytes, 8-row groups 1024
+          // bytes apart; so are the image tiles when they are in shared memory.
+          const uint64_t bHi = makeSmemDesc(stage + kAStage, 16, 1024);
+          const uint64_t bLo = makeSmemDesc(stage + kAStage + bBytes, 16, 1024);
+          if constexpr (TMEM_A) {
+            const uint32_t aHi = tmemBase + kATmemBase + s * 64u, aLo = aHi + 32u;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            // 8 K-elements further: 32 bytes along a row.  The small terms first.
-            const uint64_t step = uint64_t(kk * 2);
-            ummaTf32<1>(dTmem, aLo + step, bHi + step, iDesc, (kb | kk) != 0);
-            ummaTf32<1>(dTmem, aHi + step, bLo + step, iDesc, 1);
-            ummaTf32<1>(dTmem, aHi + step, bHi + step, iDesc, 1);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // 8 K-elements further: 8 columns of A, 32 bytes along a row of B.
+              const uint32_t col = uint32_t(kk * UMMA_K);
+              const uint64_t step = uint64_t(kk * 2);
+              ummaTf32TmemA(dTmem, aLo + col, bHi + step, iDesc, (kb | kk) != 0);
+              ummaTf32TmemA(dTmem, aHi + col, bLo + step, iDesc, 1);
+              ummaTf32TmemA(dTmem, aHi + col, bHi + step, iDesc, 1);
+            }
+          } else {
+            const uint64_t aHi = makeSmemDesc(stage, 16, 1024);
+            const uint64_t aLo = makeSmemDesc(stage + kABytes, 16, 1024);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // 8 K-elements further: 32 bytes along a row.  The small terms first.
+              const uint64_t step = uint64_t(kk * 2);
+              ummaTf32<1>(dTmem, aLo + step, bHi + step, iDesc, (kb | kk) != 0);
+              ummaTf32<1>(dTmem, aHi + step, bLo + step, iDesc, 1);
+              ummaTf32<1>(dTmem, aHi + step, bHi + step, iDesc, 1);
+            }
           }
           ummaCommit(smemAddr(&bars->empty[s])); // frees the stage when these are done
         }
@@ -370,7 +412,7 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
       const int pix = tp * BM + quad * 32 + lane;
       // Pixel `pix` of filter q: consecutive lanes write consecutive floats.
       float *dst = p.out + n * osN + pix;
-      const uint32_t taddr = tmemBase + (uint32_t(quad * 32) << 16) + uint32_t(acc * ACC_STRIDE);
+      const uint32_t taddr = tmemBase + (uint32_t(quad * 32) << 16) + uint32_t(acc * kAccStride);
 #pragma unroll 1
       for (int ch = 0; ch * 32 < p.NF; ++ch) { // uniform over the warp
         uint32_t v[32];
@@ -400,4 +442,23 @@ extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
     tcgen05FenceAfter();
     tmemFree<1>(tmemBase, TMEM_COLS);
   }
+}
+
+} // namespace
+
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_conv_f32_umma(const __grid_constant__ CUtensorMap mapFHi,
+                     const __grid_constant__ CUtensorMap mapFLo,
+                     const __grid_constant__ HcConvParams p) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  convF32<false>(mapFHi, mapFLo, p, smemRaw);
+}
+
+// The image operand in tensor memory: up to 128 filters.
+extern "C" __global__ void __launch_bounds__(NUM_THREADS, 1)
+    hc_conv_f32_umma_ta(const __grid_constant__ CUtensorMap mapFHi,
+                        const __grid_constant__ CUtensorMap mapFLo,
+                        const __grid_constant__ HcConvParams p) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  convF32<true>(mapFHi, mapFLo, p, smemRaw);
 }

@@ -30,7 +30,8 @@ struct HcContextImpl {
   long long mappedStack = 0;
   long long rowVariant = 0;
   long long fusedVariant = 0; // 1: never use the precompiled bodies
-  long long convStages = 0;   // 2..4: shared-memory stages of the convolution (0: as many as fit)
+  long long convVariant = 0;  // 1: image operand in shared memory, 2: in tensor memory
+  long long convStages = 0;   // 2..6: pipeline stages of the convolution (0: as many as fit)
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
   int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel
   // Programs without a precompiled body: 0 interpret them, 1 compile them at their

@@ -121,6 +121,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_f32_umma", "gemm_f32_umma"},
     {"hc_gemm_f32_umma_pair", "gemm_f32_umma"},
     {"hc_conv_f32_umma", "conv_f32_umma"},
+    {"hc_conv_f32_umma_ta", "conv_f32_umma"},
     {"hc_split_tf32_pairs", "conv_f32_umma"},
 };
 
@@ -412,7 +413,13 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->fusedVariant = value; // 1: interpret every program, precompiled or not
     return 0;
   }
-  if (std::strcmp(name, "conv_stages") == 0 && (value == 0 || (value >= 2 && value <= 4))) {
+  if (std::strcmp(name, "conv_variant") == 0 && value >= 0 && value <= 2) {
+    // hcConvF32Tensor: 1 = the image operand through shared memory, 2 = through
+    // tensor memory (at most 128 filters), 0 = tensor memory where it fits.
+    c->convVariant = value;
+    return 0;
+  }
+  if (std::strcmp(name, "conv_stages") == 0 && (value == 0 || (value >= 2 && value <= 6))) {
     c->convStages = value; // hcConvF32Tensor: fewer stages leave more of the SM's L1
     return 0;
   }
@@ -1431,11 +1438,17 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   if (C * H * W >= (1ll << 31) || N * tilesPerImage >= (1ll << 31) || NF * pixels >= (1ll << 31))
     return c->fail("%s: an image of %lld x %lld x %lld exceeds 32-bit element offsets", who, C, H,
                    W);
+  // The image operand of a K block goes through tensor memory when there is room
+  // beside the accumulators (at most 128 filters), else through shared memory.
+  const bool tmemA = c->convVariant == 2 || (c->convVariant == 0 && nPad <= 128);
+  if (tmemA && nPad > 128)
+    return c->fail("%s: the tensor-memory form takes at most 128 filters, got %lld", who, NF);
   // Shared memory: the stages, the offset of every k, the barriers.
-  const long long stageBytes = 2 * 128 * 32 * 4 + 2 * nPad * 32 * 4;
+  const long long stageBytes = (tmemA ? 0 : 2 * 128 * 32 * 4) + 2 * nPad * 32 * 4;
   const long long fixed = kBlocks * 32 * 4 + 1024 /*align*/ + 256 /*barriers*/;
   const long long room = 227 * 1024 - fixed;
-  long long stages = std::min<long long>(4, room / stageBytes);
+  // (In tensor memory: six stages beside accumulators of 64 columns, else four.)
+  long long stages = std::min<long long>(tmemA && nPad <= 64 ? 6 : 4, room / stageBytes);
   if (c->convStages)
     stages = std::min(stages, c->convStages);
   if (stages < 2)
@@ -1489,7 +1502,8 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   const long long grid = std::min<long long>(tiles, c->smCount);
   const size_t smem = size_t(stages * stageBytes + fixed);
   void *args[] = {&maps[0], &maps[1], &p};
-  return c->launch("hc_conv_f32_umma", size_t(grid), 1, 1, 704, args, 3, smem);
+  return c->launch(tmemA ? "hc_conv_f32_umma_ta" : "hc_conv_f32_umma", size_t(grid), 1, 1, 704,
+                   args, 3, smem);
 }
 
 int hcGemmBf16Peers(HcContext c, const void *a, const void *b, const HcPeerOutputs *dsts,

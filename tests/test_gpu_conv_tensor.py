@@ -42,6 +42,7 @@ def _conv(hc, x, f, stride):
 
 CASES = [
     # x shape, f shape, stride
+    ((2, 8, 30, 30), (128, 8, 3, 3), 1),    # 128 filters: the most the tensor-memory form takes
     ((2, 3, 8, 8), (4, 3, 3, 3), 1),        # K = 27: one partial K block, 36 pixels
     ((1, 1, 5, 5), (1, 1, 1, 1), 1),        # a 1 x 1 filter, one filter
     ((3, 8, 20, 20), (5, 8, 3, 3), 1),      # 324 pixels: three tiles, the last ragged; NF = 5
@@ -53,8 +54,21 @@ CASES = [
 ]
 
 
+# conv_variant: 1 = the image operand of a K block goes through shared memory,
+# 2 = through tensor memory (at most 128 filters), 0 = the library's choice.
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("xs,fs,stride", CASES)
-def test_matches_the_float64_correlation(hc, xs, fs, stride):
+def test_matches_the_float64_correlation(hc, xs, fs, stride, variant):
+    if variant == 2 and fs[0] > 128:
+        pytest.skip("more filters than the tensor-memory form takes")
+    hc.set_option("conv_variant", variant)
+    try:
+        _matches_the_float64_correlation(hc, xs, fs, stride)
+    finally:
+        hc.set_option("conv_variant", 0)
+
+
+def _matches_the_float64_correlation(hc, xs, fs, stride):
     rng = np.random.default_rng(sum(xs) * 31 + sum(fs))
     x = rng.uniform(-1, 1, xs).astype(np.float32)
     f = rng.uniform(-1, 1, fs).astype(np.float32)
