@@ -28,8 +28,9 @@
 //   warp 0      TMA producer of the filter tiles: per 32-deep K block two boxes
 //               (f hi, f lo; [NF rows, 32 k], 128-byte swizzle, rows beyond NF
 //               and k beyond K zero-filled; no multicast);
-//   warp 1      MMA issuer: tcgen05.mma.kind::tf32, M128 N=NF(padded to 16) K8,
-//               twelve per K block, small terms first;
+//   warp 1      MMA issuer (one elected lane of the converged warp):
+//               tcgen05.mma.kind::tf32, M128 N=NF(padded to 16) K8, twelve per K
+//               block, small terms first;
 //   warps 2-5   epilogue: tcgen05.ld, then for every filter a store that is
 //               contiguous across the warp's 32 pixels;
 //   warps 6-21  the image operand: thread (row m, quarter h) loads its 8
@@ -335,7 +336,13 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
       mbarArrive(smemAddr(&bars->full[(it - 1) % stages]));
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop, converged, and one elected lane issues: what
+    // the instructions take (descriptors, addresses) is then uniform over the warp
+    // as far as the compiler can see and stays in uniform registers.  With one
+    // lane alone in a divergent branch every tcgen05.mma paid for moving its
+    // operands there - 77 cycles per instruction, more than an N = 64 MMA runs.
+    {
+      const bool issuer = electOne();
       const uint32_t iDesc = (1u << 4) | (2u << 7) | (2u << 10) |
                              (uint32_t(p.nPad >> 3) << 17) | (uint32_t(BM >> 4) << 24);
       uint32_t it = 0;
@@ -343,19 +350,19 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
       for (int t = blockIdx.x; t < numTiles && !*abortFlag; t += gridDim.x, ++tileIter) {
         const int acc = tileIter & 1;
         const uint32_t accPhase = (tileIter >> 1) & 1u;
-        if (!mbarWait(smemAddr(&bars->tmemEmpty[acc]), accPhase ^ 1u, abortFlag, p.status,
-                      kStatusMmaWaitTmem))
+        bool ok = mbarWait(smemAddr(&bars->tmemEmpty[acc]), accPhase ^ 1u, abortFlag, p.status,
+                           kStatusMmaWaitTmem);
+        if (!__all_sync(0xffffffffu, ok))
           break;
         tcgen05FenceAfter();
         const uint32_t dTmem = tmemBase + uint32_t(acc * kAccStride);
-        bool ok = true;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
           const uint32_t s = it % stages, phase = (it / stages) & 1u;
-          if (!mbarWait(smemAddr(&bars->full[s]), phase, abortFlag, p.status,
-                        kStatusMmaWaitData)) {
-            ok = false;
+          ok = mbarWait(smemAddr(&bars->full[s]), phase, abortFlag, p.status,
+                        kStatusMmaWaitData);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok)
             break;
-          }
           tcgen05FenceAfter();
           const uint32_t stage = smemBase + s * stageBytes;
           // The filter tiles are K-major: rows of 128 bytes, 8-row groups 1024
@@ -364,32 +371,40 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
           const uint64_t bLo = makeSmemDesc(stage + kAStage + bBytes, 16, 1024);
           if constexpr (TMEM_A) {
             const uint32_t aHi = tmemBase + kATmemBase + s * 64u, aLo = aHi + 32u;
+            if (issuer) {
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              // 8 K-elements further: 8 columns of A, 32 bytes along a row of B.
-              const uint32_t col = uint32_t(kk * UMMA_K);
-              const uint64_t step = uint64_t(kk * 2);
-              ummaTf32TmemA(dTmem, aLo + col, bHi + step, iDesc, (kb | kk) != 0);
-              ummaTf32TmemA(dTmem, aHi + col, bLo + step, iDesc, 1);
-              ummaTf32TmemA(dTmem, aHi + col, bHi + step, iDesc, 1);
+              for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                // 8 K-elements further: 8 columns of A, 32 bytes along a row of B.
+                const uint32_t col = uint32_t(kk * UMMA_K);
+                const uint64_t step = uint64_t(kk * 2);
+                ummaTf32TmemA(dTmem, aLo + col, bHi + step, iDesc, (kb | kk) != 0);
+                ummaTf32TmemA(dTmem, aHi + col, bLo + step, iDesc, 1);
+                ummaTf32TmemA(dTmem, aHi + col, bHi + step, iDesc, 1);
+              }
             }
           } else {
             const uint64_t aHi = makeSmemDesc(stage, 16, 1024);
             const uint64_t aLo = makeSmemDesc(stage + kABytes, 16, 1024);
+            if (issuer) {
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              // 8 K-elements further: 32 bytes along a row.  The small terms first.
-              const uint64_t step = uint64_t(kk * 2);
-              ummaTf32<1>(dTmem, aLo + step, bHi + step, iDesc, (kb | kk) != 0);
-              ummaTf32<1>(dTmem, aHi + step, bLo + step, iDesc, 1);
-              ummaTf32<1>(dTmem, aHi + step, bHi + step, iDesc, 1);
+              for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                // 8 K-elements further: 32 bytes along a row.  The small terms first.
+                const uint64_t step = uint64_t(kk * 2);
+                ummaTf32<1>(dTmem, aLo + step, bHi + step, iDesc, (kb | kk) != 0);
+                ummaTf32<1>(dTmem, aHi + step, bLo + step, iDesc, 1);
+                ummaTf32<1>(dTmem, aHi + step, bHi + step, iDesc, 1);
+              }
             }
           }
-          ummaCommit(smemAddr(&bars->empty[s])); // frees the stage when these are done
+          if (issuer)
+            ummaCommit(smemAddr(&bars->empty[s])); // frees the stage when these are done
+          __syncwarp();
         }
         if (!ok)
           break;
-        ummaCommit(smemAddr(&bars->tmemFull[acc]));
+        if (issuer)
+          ummaCommit(smemAddr(&bars->tmemFull[acc]));
+        __syncwarp();
       }
     }
   } else {

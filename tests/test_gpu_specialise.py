@@ -75,7 +75,9 @@ def test_specialised_elementwise_bodies_equal_the_interpreter(body, dtype):
             np.testing.assert_allclose(compiled, want, rtol=4e-6 if dtype == "float32" else 1e-13,
                                        atol=2e-6, equal_nan=True)
     after = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
-    assert after == before + 1, ctx.specialise_note  # one program, compiled once
+    # One program, compiled once for all shapes (not at all when an earlier test of the
+    # session, which shares the context, launched the same program).
+    assert after - before in (0, 1), ctx.specialise_note
 
 
 ROW_BODIES = [
@@ -104,7 +106,7 @@ def test_specialised_row_bodies_equal_the_interpreter(body, dtype):
         assert np.array_equal(compiled, interpreted, equal_nan=True), (name, shape)
         assert np.isfinite(compiled).all()
     after = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
-    assert after == before + 1, ctx.specialise_note
+    assert after - before in (0, 1), ctx.specialise_note
 
 
 @pytest.mark.parametrize("dtype", ["int32", "int64"])
@@ -122,7 +124,7 @@ def test_specialised_integer_bodies_equal_the_interpreter(dtype):
         assert np.array_equal(compiled, interpreted), shape
         assert np.array_equal(compiled, fn(*arrays)), shape  # NumPy's integer arithmetic
     after = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
-    assert after == before + 1, ctx.specialise_note
+    assert after - before in (0, 1), ctx.specialise_note
 
 
 def test_switch_and_scope():
