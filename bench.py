@@ -193,11 +193,12 @@ NCU_TRAFFIC = {
     # profiles/reduce_rows_warp_f32_16384x8192.md: (536.89 + 3.88) MB for a quarter of the
     # rows; the read traffic grows with the rows, so four times that.
     "reduce": 2163.1e6,
-    # profiles/gemm_bf16_umma_pair_2048.md, full-size section: 1418.1 MB read + 128.5 MB written.
-    "gemm_bf16": 1546.6e6,
-    "gemm_w8a16": None,
+    # profiles/gemm_umma_full_size_tensor_pipe.md (one full-size launch each; the GEMM kernel
+    # alone, without the operand conversion passes of w8a16 and float32).
+    "gemm_bf16": 1259.3e6 + 128.1e6,
+    "gemm_w8a16": 593.8e6 + 59.8e6,
     "gemm_f32": None,
-    "gemm_f32_tensor": None,
+    "gemm_f32_tensor": 628.8e6 + 61.5e6,
     "conv": None,
     "map": 1073761280 + 495959040,
     "rows": 536891392 + 481583104,

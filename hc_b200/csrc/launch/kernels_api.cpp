@@ -413,6 +413,11 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->fusedVariant = value; // 1: interpret every program, precompiled or not
     return 0;
   }
+  if (std::strcmp(name, "gemm_band") == 0 && value >= 0 && value <= 64) {
+    // Row tiles per band of the tcgen05 GEMMs' tile order (0: the default).
+    c->gemmBand = value;
+    return 0;
+  }
   if (std::strcmp(name, "conv_variant") == 0 && value >= 0 && value <= 2) {
     // hcConvF32Tensor: 1 = the image operand through shared memory, 2 = through
     // tensor memory (at most 128 filters), 0 = tensor memory where it fits.
@@ -1258,7 +1263,7 @@ static int launchUmma(HcContext c, const void *a, const void *b,
   int tilesM = int(ceilDiv(M, tileM)), tilesN = int(ceilDiv(N, kUmmaBN));
   // Tiles that run concurrently should form a compact block of the output so
   // that the A and B panels they share stay in L2.
-  int bandM = 16;
+  int bandM = c->gemmBand ? int(c->gemmBand) : 16;
   int vecStore = aligned(out, 16) && ldc % 8 == 0;
   HcPeerDsts peers{};
   if (dsts) {

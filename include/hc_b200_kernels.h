@@ -95,19 +95,23 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * 2 = as 3, with 256 threads and four packets each beyond 512 packets,
  * 3 = hold such rows whatever the fill.  "fused": 0 = programs that match a body
  * compiled ahead of time run as straight-line kernels, 1 = every program is
- * interpreted.  "specialise": what happens to a float program of hcMapElements /
+ * interpreted.  "specialise": what happens to a program of hcMapElements /
  * hcRowProgram that has no such body - 1 (default) = it is compiled at its first
  * launch (see hcSpecialisedPrograms) and interpreted where that is not possible,
  * 0 = it is interpreted, 2 = as 1, but the launch fails where compiling is not
- * possible. */
+ * possible.  "conv_variant" (hcConvF32Tensor): 0 = the image operand of a K block goes
+ * through tensor memory when at most 128 filters leave room there, 1 = always
+ * through shared memory, 2 = always through tensor memory (more filters are
+ * refused); "conv_stages": 0 or 2..6 pipeline stages.  "gemm_band": row tiles per
+ * band in the tile order of the tcgen05 GEMMs (0 = 16). */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* Run-time specialisation.  The reference compiles every kernel body at its
  * first call and keeps the result per argument signature
  * (python/cpp/native/DispatcherBase.cpp:250-256,542-585).  Here a program of
- * hcMapElements / hcRowProgram that uses the operations up to `set` on float32
- * or float64 and has no body compiled ahead of time is compiled the first time
- * a context launches it: NVRTC (looked up with dlopen; libnvrtc.so.12, or the
+ * hcMapElements (any operation; float32, float64, int32, int64) or hcRowProgram
+ * (float32, float64) that has no body compiled ahead of time is compiled the
+ * first time a context launches it: NVRTC (looked up with dlopen; libnvrtc.so.12, or the
  * path in HC_B200_NVRTC) turns the kernel templates, embedded in this library as
  * text, into straight-line code for the program's instruction words; the image
  * is loaded and kept until the context is released.  Constants stay launch
@@ -197,7 +201,8 @@ HC_B200_API int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype
 /* The compilation alone, without a context or a GPU (to fill the directory of
  * HC_B200_KERNEL_CACHE ahead of time, or to check that NVRTC is usable): the
  * device image of `program` (rowProgram: 0 = for hcMapElements, 1 = for
- * hcRowProgram; dtype HC_F32 or HC_F64) for compute capability ccMajor.ccMinor.
+ * hcRowProgram; dtype as the entry point takes it) for compute capability
+ * ccMajor.ccMinor.
  * Returns the size of the image and copies up to `capacity` bytes of it to `image`
  * (which may be null); `message` receives the tag that stands for the program in
  * the kernel names (hc_map_fused_<tag>_f32_v4 ...).  On failure returns -1 and
