@@ -170,6 +170,34 @@ def algorithmic(name):
     return m * k * 2 + k * n + n * 4 + m * n * 2, 2 * m * n * k, "tensor"
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Restricts this process to the CPUs of the NUMA node that GPU `local_rank` is
+    attached to (read from sysfs), so that memory it pins afterwards is local to
+    the GPU's PCIe root.  Returns what was done, for the record; never raises."""
+    try:
+        import torch
+
+        props = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as fh:
+            node = int(fh.read().strip())
+        if node < 0:
+            return {"gpu": bdf, "node": node, "bound": False, "why": "no NUMA information"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"gpu": bdf, "node": node, "bound": False,
+                    "why": "none of the node's CPUs is available to this process"}
+        os.sched_setaffinity(0, allowed)
+        return {"gpu": bdf, "node": node, "bound": True, "cpus": len(allowed)}
+    except Exception as err:  # no sysfs, no such attribute: carry on unbound
+        return {"bound": False, "why": f"{type(err).__name__}: {err}"}
+
+
 def unit_of(name):
     return "GB/s" if algorithmic(name)[2] == "hbm" else "TFLOP/s"
 
@@ -1056,8 +1084,22 @@ def run_gpu(args):
             outs = [t[span.begin:span.end] for t in outs]
         else:
             share = float(world) if world > 1 else 1.0
+        # With several ranks, each one's staging buffers should live on the NUMA node
+        # its GPU hangs off: bind the process there before the buffers are made.
+        numa = bind_to_gpu_numa_node(local) if world > 1 else None
         h_ins = [t.cpu().pin_memory() for t in ins]
         h_outs = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+        # What the host side alone gives: a pinned-to-pinned copy of the step's output
+        # bytes by this rank's cores (every rank at the same time).
+        host_gbs = None
+        if world > 1 and h_outs:
+            twin = torch.empty_like(h_outs[0]).pin_memory()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                twin.copy_(h_outs[0])
+            host_gbs = 3 * 2 * twin.numel() * twin.element_size() / (time.perf_counter() - t0) / 1e9
+            del twin
 
         if name in ("softmax", "reduce", "gemm_bf16"):
             # The host-buffer entry points of the C-ABI (hcSoftmaxRowsHost,
@@ -1127,6 +1169,7 @@ def run_gpu(args):
         return {"value": ach, "unit": roof["unit"], "h2d_bytes_per_step": up,
                 "d2h_bytes_per_step": down, "ms_per_step": ms / steps, "steps": steps,
                 "via": via, "link_only_ms_per_step": link_ms,
+                "numa": numa, "host_memcpy_gbs_rank0": host_gbs,
                 "what": "every rank streams its rows from pinned host memory and back"
                 if world > 1 else "pinned host memory in, pinned host memory out"}
 
