@@ -101,10 +101,18 @@ template <bool TMEM_A>
 __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtensorMap &mapFLo,
                                         const HcConvParams &p, unsigned char *smemRaw) {
   constexpr int kAStage = TMEM_A ? 0 : 2 * kABytes; // bytes of A in a shared-memory stage
+  // Stacked (p.stacked): the two products that share a_hi run as ONE MMA of twice
+  // the width - B = [b_hi; b_lo], which lie behind one another in the stage, N =
+  // 2 NF - into an accumulator of two halves that the epilogue adds: a_hi * b_hi
+  // (+ a_lo * b_hi, a second MMA of width NF) in the first, a_hi * b_lo in the
+  // second.  An M128 K8 MMA has to fetch its 4 KiB of A whatever its width, which
+  // takes longer than the arithmetic of 64 columns: two instructions per K step
+  // instead of three are a third less of that.
   // TMEM columns: the two accumulators, then (TMEM_A) the A stages of 64 columns
-  // each - with at most 64 filters the accumulators take 128 columns and leave
-  // room for six stages, with at most 128 they take 256 and leave room for four.
-  const int kAccStride = TMEM_A ? (p.nPad <= 64 ? 64 : 128) : ACC_STRIDE;
+  // each - six stages beside accumulators of 64 columns, four beside 128.
+  const bool stacked = p.stacked != 0;
+  const int kAccStride =
+      TMEM_A ? ((stacked ? 2 * p.nPad : p.nPad) <= 64 ? 64 : 128) : ACC_STRIDE;
   const uint32_t kATmemBase = uint32_t(2 * kAccStride);
   const int bBytes = p.nPad * BK * 4; // one of f hi / f lo
   const int stageBytes = kAStage + 2 * bBytes;
@@ -345,6 +353,8 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
       const bool issuer = electOne();
       const uint32_t iDesc = (1u << 4) | (2u << 7) | (2u << 10) |
                              (uint32_t(p.nPad >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+      const uint32_t iDescWide = (1u << 4) | (2u << 7) | (2u << 10) |
+                                 (uint32_t(2 * p.nPad >> 3) << 17) | (uint32_t(BM >> 4) << 24);
       uint32_t it = 0;
       int tileIter = 0;
       for (int t = blockIdx.x; t < numTiles && !*abortFlag; t += gridDim.x, ++tileIter) {
@@ -371,7 +381,15 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
           const uint64_t bLo = makeSmemDesc(stage + kAStage + bBytes, 16, 1024);
           if constexpr (TMEM_A) {
             const uint32_t aHi = tmemBase + kATmemBase + s * 64u, aLo = aHi + 32u;
-            if (issuer) {
+            if (issuer && stacked) {
+#pragma unroll
+              for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                const uint32_t col = uint32_t(kk * UMMA_K);
+                const uint64_t step = uint64_t(kk * 2);
+                ummaTf32TmemA(dTmem, aHi + col, bHi + step, iDescWide, (kb | kk) != 0);
+                ummaTf32TmemA(dTmem, aLo + col, bHi + step, iDesc, 1);
+              }
+            } else if (issuer) {
 #pragma unroll
               for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                 // 8 K-elements further: 8 columns of A, 32 bytes along a row of B.
@@ -385,7 +403,14 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
           } else {
             const uint64_t aHi = makeSmemDesc(stage, 16, 1024);
             const uint64_t aLo = makeSmemDesc(stage + kABytes, 16, 1024);
-            if (issuer) {
+            if (issuer && stacked) {
+#pragma unroll
+              for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                const uint64_t step = uint64_t(kk * 2);
+                ummaTf32<1>(dTmem, aHi + step, bHi + step, iDescWide, (kb | kk) != 0);
+                ummaTf32<1>(dTmem, aLo + step, bHi + step, iDesc, 1);
+              }
+            } else if (issuer) {
 #pragma unroll
               for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                 // 8 K-elements further: 32 bytes along a row.  The small terms first.
@@ -433,6 +458,14 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
         uint32_t v[32];
         __syncwarp(); // tcgen05.ld needs the whole warp, converged
         tmemLoad32x32(taddr + uint32_t(ch * 32), v);
+        if (stacked) { // the second half of the accumulator: the a_hi * b_lo sums
+          uint32_t w[32];
+          tmemLoad32x32(taddr + uint32_t(p.nPad + ch * 32), w);
+          tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+        }
         tmemLoadWait();
         if (pix < pixels) {
 #pragma unroll

@@ -19,6 +19,6 @@ struct HcConvParams {
   int32_t nPad;          // NF rounded up to 16: the N of the MMA
   int32_t tilesPerImage; // ceil(HO * WO / 128)
   int32_t stages;        // shared-memory stages the launch has room for
-  int32_t reserved;
+  int32_t stacked;       // 1: a_hi * [b_hi; b_lo] as one MMA of width 2 nPad (nPad <= 128)
   int *status;           // the context's status word
 };

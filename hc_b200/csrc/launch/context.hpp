@@ -32,6 +32,7 @@ struct HcContextImpl {
   long long fusedVariant = 0; // 1: never use the precompiled bodies
   long long gemmBand = 0;     // row tiles per band of the tcgen05 GEMMs' tile order (0: default)
   long long convVariant = 0;  // 1: image operand in shared memory, 2: in tensor memory
+  long long convStacked = 0;  // 1: never run a_hi * [b_hi; b_lo] as one MMA of double width
   long long convStages = 0;   // 2..6: pipeline stages of the convolution (0: as many as fit)
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
   int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel

@@ -424,6 +424,10 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->convVariant = value;
     return 0;
   }
+  if (std::strcmp(name, "conv_stacked") == 0 && value >= 0 && value <= 1) {
+    c->convStacked = value; // 1: hcConvF32Tensor never stacks b_hi and b_lo into one MMA
+    return 0;
+  }
   if (std::strcmp(name, "conv_stages") == 0 && (value == 0 || (value >= 2 && value <= 6))) {
     c->convStages = value; // hcConvF32Tensor: fewer stages leave more of the SM's L1
     return 0;
@@ -1443,17 +1447,24 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   if (C * H * W >= (1ll << 31) || N * tilesPerImage >= (1ll << 31) || NF * pixels >= (1ll << 31))
     return c->fail("%s: an image of %lld x %lld x %lld exceeds 32-bit element offsets", who, C, H,
                    W);
+  // The two products that share a_hi run as one MMA of twice the width when the
+  // accumulator has room for both halves (at most 128 filters; at most 64 when the
+  // tensor-memory form is demanded, which needs room there too).
+  const bool stacked = nPad <= 128 && c->convStacked != 1 &&
+                       !(c->convVariant == 2 && nPad > 64);
   // The image operand of a K block goes through tensor memory when there is room
-  // beside the accumulators (at most 128 filters), else through shared memory.
-  const bool tmemA = c->convVariant == 2 || (c->convVariant == 0 && nPad <= 128);
-  if (tmemA && nPad > 128)
-    return c->fail("%s: the tensor-memory form takes at most 128 filters, got %lld", who, NF);
+  // beside the accumulators, else through shared memory.
+  const long long accColumns = stacked ? 2 * nPad : nPad;
+  const bool tmemA = c->convVariant == 2 || (c->convVariant == 0 && accColumns <= 128);
+  if (tmemA && accColumns > 128)
+    return c->fail("%s: the tensor-memory form takes at most %d filters, got %lld", who,
+                   stacked ? 64 : 128, NF);
   // Shared memory: the stages, the offset of every k, the barriers.
   const long long stageBytes = (tmemA ? 0 : 2 * 128 * 32 * 4) + 2 * nPad * 32 * 4;
   const long long fixed = kBlocks * 32 * 4 + 1024 /*align*/ + 256 /*barriers*/;
   const long long room = 227 * 1024 - fixed;
   // (In tensor memory: six stages beside accumulators of 64 columns, else four.)
-  long long stages = std::min<long long>(tmemA && nPad <= 64 ? 6 : 4, room / stageBytes);
+  long long stages = std::min<long long>(tmemA && accColumns <= 64 ? 6 : 4, room / stageBytes);
   if (c->convStages)
     stages = std::min(stages, c->convStages);
   if (stages < 2)
@@ -1502,6 +1513,7 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   p.K = int(K), p.kBlocks = int(kBlocks), p.nPad = int(nPad);
   p.tilesPerImage = int(tilesPerImage);
   p.stages = int(stages);
+  p.stacked = stacked ? 1 : 0;
   p.status = c->statusWord;
   const long long tiles = N * tilesPerImage;
   const long long grid = std::min<long long>(tiles, c->smCount);

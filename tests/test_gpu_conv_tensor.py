@@ -56,16 +56,21 @@ CASES = [
 
 # conv_variant: 1 = the image operand of a K block goes through shared memory,
 # 2 = through tensor memory (at most 128 filters), 0 = the library's choice.
+# conv_stacked: 0 = with at most 128 filters the two products that share a_hi run as
+# one MMA of twice the width, 1 = three MMAs per K step throughout.
+@pytest.mark.parametrize("unstacked", [0, 1])
 @pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("xs,fs,stride", CASES)
-def test_matches_the_float64_correlation(hc, xs, fs, stride, variant):
+def test_matches_the_float64_correlation(hc, xs, fs, stride, variant, unstacked):
     if variant == 2 and fs[0] > 128:
         pytest.skip("more filters than the tensor-memory form takes")
     hc.set_option("conv_variant", variant)
+    hc.set_option("conv_stacked", unstacked)
     try:
         _matches_the_float64_correlation(hc, xs, fs, stride)
     finally:
         hc.set_option("conv_variant", 0)
+        hc.set_option("conv_stacked", 0)
 
 
 def _matches_the_float64_correlation(hc, xs, fs, stride):
