@@ -41,9 +41,7 @@
 //               then fence.proxy.async.  The 512 threads meet once per K block
 //               at a named barrier (bar.sync 1); only their leader touches the
 //               mbarriers - it waits for the next free stage before the meeting
-//               and reports the stage filled after it.  (Sixteen warps polling
-//               and arriving on the stage barriers themselves cost 900 cycles
-//               per K block in barrier traffic alone.)
+//               and reports the stage filled after it.
 // Two accumulators in TMEM let the epilogue of a tile overlap the next tile's
 // main loop.  Every mbarrier wait is bounded (hc_ptx.cuh).
 #include "conv_params.h"
@@ -346,9 +344,8 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
     // ------------------------------- MMA issuer -------------------------------
     // The whole warp walks the loop, converged, and one elected lane issues: what
     // the instructions take (descriptors, addresses) is then uniform over the warp
-    // as far as the compiler can see and stays in uniform registers.  With one
-    // lane alone in a divergent branch every tcgen05.mma paid for moving its
-    // operands there - 77 cycles per instruction, more than an N = 64 MMA runs.
+    // as far as the compiler can see (4 % faster than one lane alone in a
+    // divergent branch).
     {
       const bool issuer = electOne();
       const uint32_t iDesc = (1u << 4) | (2u << 7) | (2u << 10) |

@@ -102,7 +102,9 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * possible.  "conv_variant" (hcConvF32Tensor): 0 = the image operand of a K block goes
  * through tensor memory when at most 128 filters leave room there, 1 = always
  * through shared memory, 2 = always through tensor memory (more filters are
- * refused); "conv_stages": 0 or 2..6 pipeline stages.  "gemm_band": row tiles per
+ * refused); "conv_stages": 0 or 2..6 pipeline stages; "conv_stacked": 0 = with at
+ * most 128 filters the two products that share a_hi run as one MMA of double
+ * width, 1 = three MMAs per K step throughout.  "gemm_band": row tiles per
  * band in the tile order of the tcgen05 GEMMs (0 = 16). */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
