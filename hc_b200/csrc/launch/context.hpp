@@ -36,6 +36,8 @@ struct HcContextImpl {
   long long convStages = 0;   // 2..6: pipeline stages of the convolution (0: as many as fit)
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
   int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel
+  int pairSlotsW8 = 0;  // the same for the dequant GEMM that converts in its pipeline
+  long long w8Variant = 0; // 1: convert the weights in a pass of its own, 2: never
   // Programs without a precompiled body: 0 interpret them, 1 compile them at their
   // first launch and interpret where that is not possible, 2 fail where it is not.
   long long specialiseMode = 1;
