@@ -10,13 +10,13 @@
 // cross HBM, L2 and the SM boundary as one byte per element instead of two.
 //
 // A cluster of two CTAs works on one 256 x 256 output tile with
-// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 512 threads:
+// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 480 threads:
 //   warp 0     TMA producer of A: per 64-deep K block its 128 rows (bf16, 128-byte
-//              swizzle, completion counted on the leader CTA's barrier);
-//   warp 15    TMA producer of w: its 64 x 128 tile as raw bytes (no swizzle,
-//              completion on this CTA's own `raw` barrier) into a ring of eight
-//              slots of its own; no multicast anywhere;
-//   warps 6-13 converters: 16 weights per 16-byte shared-memory load -> two
+//              swizzle, completion counted on the leader CTA's barrier; no
+//              multicast);
+//   warps 6-13 converters: 16 weights per 16-byte global load, issued two K
+//              blocks ahead (w never passes through shared memory as bytes:
+//              the shared-memory port carries what the bf16 kernel carries) -> two
 //              16-byte stores of bf16 into the stage, in the N-major 128-byte-
 //              swizzled layout a TMA box of bf16 would have produced
 //              (int8 -> bf16 by byte permute and one packed subtract, exact);
@@ -46,8 +46,7 @@ constexpr int BK = 64;     // K depth of one stage
 constexpr int UMMA_K = 16;
 constexpr int CONVERTER_WARPS = 8;
 constexpr int REPORTER_WARP = 6 + CONVERTER_WARPS;
-constexpr int RAW_PRODUCER_WARP = 7 + CONVERTER_WARPS;
-constexpr int NUM_THREADS = 32 * (8 + CONVERTER_WARPS);
+constexpr int NUM_THREADS = 32 * (7 + CONVERTER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int kTileM = 2 * BM;
 constexpr int kBCols = BN / 2;             // columns of w a CTA stages
@@ -55,19 +54,14 @@ constexpr int PACKETS = BK * kBCols / 16 / (32 * CONVERTER_WARPS); // 16-weight 
 constexpr int kABytes = BM * BK * 2;       // 16 KiB
 constexpr int kBChunkBytes = BK * 64 * 2;  // 64 columns of bf16, 64 deep: 8 KiB
 constexpr int kBBytes = 2 * kBChunkBytes;  // 16 KiB
-constexpr int kRawBytes = BK * kBCols;     // the same tile as int8: 8 KiB
 constexpr int kStageBytes = kABytes + kBBytes; // 32 KiB: A and the converted B
-constexpr int kStages = 5;
-// The int8 tiles wait in a ring of their own, deeper than the stages: their way
-// into an MMA is the longest (TMA, conversion, a report to the other CTA).
-constexpr int kRawSlots = 8;
+constexpr int kStages = 6;
+
 constexpr uint32_t kInstrDesc = makeInstrDescBf16(kTileM, BN, /*aMnMajor=*/false,
                                                   /*bMnMajor=*/true);
 
 struct alignas(8) Barriers {
   uint64_t full[kStages];  // leader CTA: A of both CTAs landed, both CTAs' B converted
-  uint64_t raw[kRawSlots];      // this CTA: the int8 tile landed
-  uint64_t rawEmpty[kRawSlots]; // this CTA: every converter warp has read the tile
   uint64_t converted[kStages]; // this CTA: every converter warp has stored its share
   uint64_t empty[kStages]; // the MMAs that read the stage are done (both CTAs)
   uint64_t tmemFull[2];
@@ -110,7 +104,7 @@ __device__ __forceinline__ uint32_t int8PairToBf16(uint32_t word, uint32_t sel) 
 
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     hc_gemm_w8a16_umma_pair(const __grid_constant__ CUtensorMap mapA,
-                            const __grid_constant__ CUtensorMap mapW,
+                            const int8_t *__restrict__ w, long long ldw,
                             __nv_bfloat16 *__restrict__ c, const float *__restrict__ scale,
                             long long M, long long N, long long K, long long ldc, int tilesM,
                             int tilesN, int bandM, int vecStore, int *status) {
@@ -118,8 +112,7 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
   const Params p{M, N, K, ldc, tilesM, tilesN, bandM, vecStore};
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
   unsigned char *aligned = smemRaw + (smemBase - smemAddr(smemRaw));
-  unsigned char *rawRing = aligned + kStages * kStageBytes;
-  Barriers *bars = reinterpret_cast<Barriers *>(rawRing + kRawSlots * kRawBytes);
+  Barriers *bars = reinterpret_cast<Barriers *>(aligned + kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ctaRank = clusterCtaRank();
   const bool leaderCta = ctaRank == 0;
@@ -132,10 +125,6 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
       mbarInit(smemAddr(&bars->converted[s]), CONVERTER_WARPS);
       mbarInit(smemAddr(&bars->empty[s]), 1);
     }
-    for (int q = 0; q < kRawSlots; ++q) {
-      mbarInit(smemAddr(&bars->raw[q]), 1);
-      mbarInit(smemAddr(&bars->rawEmpty[q]), CONVERTER_WARPS);
-    }
     for (int a = 0; a < 2; ++a) {
       mbarInit(smemAddr(&bars->tmemFull[a]), 1);
       mbarInit(smemAddr(&bars->tmemEmpty[a]), 8); // epilogue warps of both CTAs
@@ -143,7 +132,6 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     bars->abortFlag = 0;
     fenceBarrierInit();
     prefetchTensorMap(&mapA);
-    prefetchTensorMap(&mapW);
   }
   if (warp == 1) {
     tmemAlloc<2>(smemAddr(&bars->tmemBase), TMEM_COLS);
@@ -195,35 +183,6 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         }
       }
     }
-  } else if (warp == RAW_PRODUCER_WARP) {
-    // ------------------------- TMA producer of the int8 tiles -------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep) {
-        int tm, tn;
-        tileCoords(t, p, tm, tn);
-        const int col0 = tn * BN + int(ctaRank) * kBCols;
-        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const uint32_t q = it % kRawSlots, phase = (it / kRawSlots) & 1u;
-          if (!mbarWait(smemAddr(&bars->rawEmpty[q]), phase ^ 1u, abortFlag, status,
-                        kStatusProducerWait))
-            break;
-          // The weights as bytes: rows of 128 bytes, this CTA's own barrier.
-          const uint32_t rawBar = smemAddr(&bars->raw[q]);
-          mbarExpectTx(rawBar, kRawBytes);
-          tmaLoad2D(smemBase + kStages * kStageBytes + q * kRawBytes, &mapW, rawBar, col0,
-                    kb * BK);
-        }
-      }
-      // Nothing may still be landing when this CTA's shared memory goes away: the
-      // converters read every tile before they finish (the teardown's cluster
-      // barrier waits for them); after a wait that gave up, give the copies time.
-      if (*abortFlag) {
-        const unsigned long long t0 = globalTimerNs();
-        while (globalTimerNs() - t0 < 1000000ull) {
-        }
-      }
-    }
   } else if (warp == REPORTER_WARP) {
     // ---------------------------------- reporter ----------------------------------
     // Tells the leader CTA that this CTA's share of a stage is converted.  A thread
@@ -244,62 +203,103 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     }
   } else if (warp >= 6) {
     // -------------------------------- converters --------------------------------
-    // Every warp converts its share of a tile as soon as the tile has landed and
-    // reports it on this CTA's `converted` barrier; the warps run up to a ring of
-    // stages ahead of the MMAs and wait for nothing else.
+    // Every thread owns two 16-weight packets of a tile (row k = id / 8, columns
+    // 16 (id % 8) ... of this CTA's 128 columns).  It loads them straight from
+    // global memory two K blocks ahead of their use (read-only path; a warp reads
+    // four whole 128-byte rows per load), converts them when the stage is free and
+    // stores the bf16 where a TMA box of bf16 would have put them.  The warps run
+    // up to the ring of stages ahead of the MMAs and wait for nothing else.
     const int tid = threadIdx.x - 6 * 32; // 0 .. 32 * CONVERTER_WARPS - 1
-    int myTiles = 0;
-    for (int t = firstTile; t < numTiles; t += tileStep)
-      ++myTiles;
-    const uint32_t blocks = uint32_t(myTiles) * uint32_t(kBlocks);
-    for (uint32_t it = 0; it < blocks; ++it) {
-      const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
-      const uint32_t q = it % kRawSlots, rawPhase = (it / kRawSlots) & 1u;
-      bool ok = true;
-      if (lane == 0)
-        // The tile has landed, and the MMAs that read the stage before are done.
-        ok = mbarWait(smemAddr(&bars->raw[q]), rawPhase, abortFlag, status,
-                      kStatusConverterWait) &&
-             mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
-                      kStatusConverterWait);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok)
-        break;
-      const unsigned char *raw = rawRing + q * kRawBytes;
-      unsigned char *bStage = aligned + s * kStageBytes + kABytes;
-      // 512 packets of 16 weights: row k = id / 8, columns 16 (id % 8) ...
-      int4 loaded[PACKETS];
-#pragma unroll
-      for (int i = 0; i < PACKETS; ++i) {
-        const int id = tid + 32 * CONVERTER_WARPS * i;
-        loaded[i] = *reinterpret_cast<const int4 *>(raw + (id >> 3) * kBCols + (id & 7) * 16);
+    struct Cursor {
+      int t, kb;
+      long long col0; // first column of this CTA's share of the tile
+      bool have;
+    };
+    auto columnOf = [&](int t) {
+      int tm, tn;
+      tileCoords(t, p, tm, tn);
+      return (long long)tn * BN + (long long)ctaRank * kBCols;
+    };
+    auto advance = [&](Cursor &c) {
+      if (c.have && ++c.kb == kBlocks) {
+        c.kb = 0;
+        c.t += tileStep;
+        c.have = c.t < numTiles;
+        if (c.have)
+          c.col0 = columnOf(c.t);
       }
+    };
+    auto loadBlock = [&](const Cursor &c, int4 (&v)[PACKETS]) {
 #pragma unroll
       for (int i = 0; i < PACKETS; ++i) {
         const int id = tid + 32 * CONVERTER_WARPS * i;
-        const int k = id >> 3, pkt = id & 7;
-        const int4 q = loaded[i];
-        const uint32_t words[4] = {uint32_t(q.x), uint32_t(q.y), uint32_t(q.z), uint32_t(q.w)};
-        uint32_t o[8];
+        const long long k = (long long)c.kb * BK + (id >> 3);
+        const long long col = c.col0 + (id & 7) * 16;
+        // Past K or N the tile is zero, as a TMA box would have filled it (N is a
+        // multiple of 16, so a packet lies wholly inside or outside).
+        v[i] = (k < p.K && col < p.N)
+                   ? __ldg(reinterpret_cast<const int4 *>(w + k * ldw + col))
+                   : make_int4(0, 0, 0, 0);
+      }
+    };
+    constexpr int AHEAD = 2, BUFFERS = AHEAD + 1;
+    Cursor fetch{firstTile, 0, 0, firstTile < numTiles};
+    if (fetch.have)
+      fetch.col0 = columnOf(fetch.t);
+    Cursor use = fetch;
+    int4 buf[BUFFERS][PACKETS];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          o[2 * j] = int8PairToBf16(words[j], 0x5140u);     // bytes 0 and 1
-          o[2 * j + 1] = int8PairToBf16(words[j], 0x7362u); // bytes 2 and 3
+    for (int r = 0; r < AHEAD; ++r) {
+      if (fetch.have)
+        loadBlock(fetch, buf[r]);
+      advance(fetch);
+    }
+    uint32_t it = 0;
+    bool ok = true;
+    while (use.have && ok) {
+#pragma unroll
+      for (int r = 0; r < BUFFERS; ++r) {
+        if (!use.have || !ok)
+          break;
+        if (fetch.have)
+          loadBlock(fetch, buf[(r + AHEAD) % BUFFERS]);
+        advance(fetch);
+        const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
+        if (lane == 0) // the MMAs that read the stage before are done
+          ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
+                        kStatusConverterWait);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok)
+          break;
+        unsigned char *bStage = aligned + s * kStageBytes + kABytes;
+#pragma unroll
+        for (int i = 0; i < PACKETS; ++i) {
+          const int id = tid + 32 * CONVERTER_WARPS * i;
+          const int k = id >> 3, pkt = id & 7;
+          const int4 q = buf[r][i];
+          const uint32_t words[4] = {uint32_t(q.x), uint32_t(q.y), uint32_t(q.z), uint32_t(q.w)};
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            o[2 * j] = int8PairToBf16(words[j], 0x5140u);     // bytes 0 and 1
+            o[2 * j + 1] = int8PairToBf16(words[j], 0x7362u); // bytes 2 and 3
+          }
+          // The 16 columns are the 16-byte slots 2 (pkt % 4) and the next of row k
+          // in the chunk of 64 columns pkt / 4; slots are swizzled with the row.
+          unsigned char *row = bStage + (pkt >> 2) * kBChunkBytes + k * 128;
+          const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
+          *reinterpret_cast<uint4 *>(row + ((slot ^ x) << 4)) =
+              make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4 *>(row + (((slot + 1u) ^ x) << 4)) =
+              make_uint4(o[4], o[5], o[6], o[7]);
         }
-        // ... which are the 16-byte slots 2 (pkt % 4) and the next of row k in the
-        // chunk of 64 columns pkt / 4; slots are swizzled with the row.
-        unsigned char *row = bStage + (pkt >> 2) * kBChunkBytes + k * 128;
-        const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
-        *reinterpret_cast<uint4 *>(row + ((slot ^ x) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4 *>(row + (((slot + 1u) ^ x) << 4)) =
-            make_uint4(o[4], o[5], o[6], o[7]);
-      }
-      // The MMA reads shared memory through the async proxy.
-      fenceProxyAsync();
-      __syncwarp();
-      if (lane == 0) {
-        mbarArrive(smemAddr(&bars->converted[s]));
-        mbarArrive(smemAddr(&bars->rawEmpty[q]));
+        // The MMA reads shared memory through the async proxy.
+        fenceProxyAsync();
+        __syncwarp();
+        if (lane == 0)
+          mbarArrive(smemAddr(&bars->converted[s]));
+        advance(use);
+        ++it;
       }
     }
   } else if (warp == 1) {

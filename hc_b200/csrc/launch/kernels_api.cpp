@@ -426,9 +426,9 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     return 0;
   }
   if (std::strcmp(name, "w8a16_variant") == 0 && value >= 0 && value <= 2) {
-    // hcGemmW8A16: 0 = the weights are converted inside the GEMM's pipeline where the
-    // layout allows, 1 = always in a pass of their own (needs the workspace), 2 = in
-    // the pipeline or fail.
+    // hcGemmW8A16: 0 and 1 = the weights are converted in a pass of their own (needs
+    // the workspace; the faster form at the benchmark size), 2 = inside the GEMM's
+    // pipeline (no workspace; fails where the layout does not allow it).
     c->w8Variant = value;
     return 0;
   }
@@ -1622,37 +1622,34 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
   // Conversion inside the pipeline (gemm_w8a16_umma.cu): a CTA pair per 256 x 256
   // tile, TMA boxes of A (bf16) and of w (bytes).
   const bool fusedFits = c->ccMajor == 10 && K > 0 && M > kUmmaBM && lda % 8 == 0 &&
-                         ldw % 16 == 0 && aligned(a, 16) && aligned(w, 16) &&
+                         ldw % 16 == 0 && N % 16 == 0 && aligned(a, 16) && aligned(w, 16) &&
                          (c->gemmVariant == 0 || c->gemmVariant == 2);
   if (c->w8Variant == 2 && !fusedFits)
     return c->fail("hcGemmW8A16: the layout does not allow converting in the pipeline "
-                   "(tcgen05 device, M > 128, lda %% 8 == 0, ldw %% 16 == 0, 16-byte aligned "
-                   "a and w)");
-  if (fusedFits && c->w8Variant != 1) {
-    alignas(64) CUtensorMap mapA, mapW;
+                   "(tcgen05 device, M > 128, lda %% 8 == 0, N and ldw multiples of 16, 16-byte "
+                   "aligned a and w)");
+  if (fusedFits && c->w8Variant == 2) {
+    alignas(64) CUtensorMap mapA;
     if (olxEncodeTensorMap2D(c->device, &mapA, /*bf16*/ 0, a, size_t(M), size_t(K),
-                             size_t(lda) * 2, kUmmaBM, kUmmaBK, 128) ||
-        olxEncodeTensorMap2D(c->device, &mapW, /*bytes*/ 2, w, size_t(K), size_t(N), size_t(ldw),
-                             kUmmaBK, 128, 0))
+                             size_t(lda) * 2, kUmmaBM, kUmmaBK, 128))
       return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
     int tilesM = int(ceilDiv(M, 2 * kUmmaBM)), tilesN = int(ceilDiv(N, kUmmaBN));
     int bandM = c->gemmBand ? int(c->gemmBand) : 16;
     int vecStore = aligned(out, 16) && ldc % 8 == 0;
     const long long tiles = (long long)tilesM * tilesN;
-    const size_t smem = 5 * 32 * 1024 /*stages*/ + 8 * 8 * 1024 /*int8 tiles*/ + 1024 /*align*/ +
-                        512 /*barriers*/;
+    const size_t smem = 6 * 32 * 1024 /*stages*/ + 1024 /*align*/ + 512 /*barriers*/;
     const char *name = "hc_gemm_w8a16_umma_pair";
     if (c->pairSlotsW8 == 0) {
       OlKernel k = c->kernel(name);
       int slots = 0;
-      if (!k || olxMaxActiveClusters(c->queue, k, 512, smem, 2, &slots) || slots <= 0)
+      if (!k || olxMaxActiveClusters(c->queue, k, 480, smem, 2, &slots) || slots <= 0)
         return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
       c->pairSlotsW8 = slots;
     }
     const long long grid = 2 * std::min<long long>(tiles, c->pairSlotsW8);
-    void *args[] = {&mapA, &mapW, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
+    void *args[] = {&mapA, &w, &ldw, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
                     &vecStore, &c->statusWord};
-    return c->launch(name, size_t(grid), 1, 1, 512, args, 13, smem);
+    return c->launch(name, size_t(grid), 1, 1, 480, args, 14, smem);
   }
   const long long wsPitch = roundUp(N, 16);
   if (c->gemmVariant == 3 || !ummaEligible(c, a, workspace, K, lda, wsPitch)) {
