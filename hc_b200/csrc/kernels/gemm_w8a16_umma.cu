@@ -10,7 +10,7 @@
 // cross HBM, L2 and the SM boundary as one byte per element instead of two.
 //
 // A cluster of two CTAs works on one 256 x 256 output tile with
-// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 480 threads:
+// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 448 threads:
 //   warp 0     TMA producer of A: per 64-deep K block its 128 rows (bf16, 128-byte
 //              swizzle, completion counted on the leader CTA's barrier; no
 //              multicast);
@@ -20,16 +20,21 @@
 //              16-byte stores of bf16 into the stage, in the N-major 128-byte-
 //              swizzled layout a TMA box of bf16 would have produced
 //              (int8 -> bf16 by byte permute and one packed subtract, exact);
-//              fence.proxy.async, then one arrival per warp on this CTA's
-//              `converted` barrier; the warps run ahead of the MMAs by up to
-//              the ring of stages;
-//   warp 14    reporter: passes every completed `converted` phase on to the
-//              leader CTA's `full` barrier (an arrival in the other CTA is slow
-//              and must not sit in the converters' loop);
+//              fence.proxy.async, then one arrival per warp on the leader CTA's
+//              `full` barrier (release at CTA scope: the data is read by this
+//              SM's own tensor core; a cluster-scope release cost 1000 cycles
+//              per arrival); the warps run ahead of the MMAs by up to the ring
+//              of stages;
 //   warp 1     (leader CTA) MMA issuer, M256 N256 K16, four per K block;
 //   warps 2-5  epilogue: tcgen05.ld, per-column scale, bf16, 16-byte stores.
 // Every weight tile is converted once per 256-row block of activations - work
 // the CUDA cores do while the tensor cores run the block before.
+//
+// Measured at 4096 x 8192 x 8192: 0.58-0.61 ms, against 0.42-0.45 ms for the
+// conversion pass plus the bf16 kernel; the MMA warp waits for converted stages
+// about as long as it issues.  It is therefore not the default (option
+// "w8a16_variant" = 2 selects it): it is the form for callers that cannot spare
+// the 2 bytes per weight of scratch memory.
 //
 // Every mbarrier wait is bounded (hc_ptx.cuh); the roles synchronise through
 // mbarriers alone, so a wait that gives up raises the abort flag and every
@@ -45,8 +50,7 @@ constexpr int BN = 256;    // accumulator columns per tile
 constexpr int BK = 64;     // K depth of one stage
 constexpr int UMMA_K = 16;
 constexpr int CONVERTER_WARPS = 8;
-constexpr int REPORTER_WARP = 6 + CONVERTER_WARPS;
-constexpr int NUM_THREADS = 32 * (7 + CONVERTER_WARPS);
+constexpr int NUM_THREADS = 32 * (6 + CONVERTER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int kTileM = 2 * BM;
 constexpr int kBCols = BN / 2;             // columns of w a CTA stages
@@ -62,7 +66,6 @@ constexpr uint32_t kInstrDesc = makeInstrDescBf16(kTileM, BN, /*aMnMajor=*/false
 
 struct alignas(8) Barriers {
   uint64_t full[kStages];  // leader CTA: A of both CTAs landed, both CTAs' B converted
-  uint64_t converted[kStages]; // this CTA: every converter warp has stored its share
   uint64_t empty[kStages]; // the MMAs that read the stage are done (both CTAs)
   uint64_t tmemFull[2];
   uint64_t tmemEmpty[2];
@@ -120,9 +123,9 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      // The leader's expect_tx for both CTAs' A, and one report per CTA's converters.
-      mbarInit(smemAddr(&bars->full[s]), 3);
-      mbarInit(smemAddr(&bars->converted[s]), CONVERTER_WARPS);
+      // The leader's expect_tx for both CTAs' A, and one report per converter warp of
+      // both CTAs.
+      mbarInit(smemAddr(&bars->full[s]), 1 + 2 * CONVERTER_WARPS);
       mbarInit(smemAddr(&bars->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -183,24 +186,6 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         }
       }
     }
-  } else if (warp == REPORTER_WARP) {
-    // ---------------------------------- reporter ----------------------------------
-    // Tells the leader CTA that this CTA's share of a stage is converted.  A thread
-    // of its own: the arrival on a barrier in the other CTA takes long enough that
-    // it must not sit in the converters' loop.
-    if (lane == 0) {
-      int myTiles = 0;
-      for (int t = firstTile; t < numTiles; t += tileStep)
-        ++myTiles;
-      const uint32_t blocks = uint32_t(myTiles) * uint32_t(kBlocks);
-      for (uint32_t it = 0; it < blocks; ++it) {
-        const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
-        if (!mbarWait(smemAddr(&bars->converted[s]), phase, abortFlag, status,
-                      kStatusConverterWait))
-          break;
-        mbarArriveRemote(mapSharedToCta(smemAddr(&bars->full[s]), 0));
-      }
-    }
   } else if (warp >= 6) {
     // -------------------------------- converters --------------------------------
     // Every thread owns two 16-weight packets of a tile (row k = id / 8, columns
@@ -210,42 +195,67 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     // stores the bf16 where a TMA box of bf16 would have put them.  The warps run
     // up to the ring of stages ahead of the MMAs and wait for nothing else.
     const int tid = threadIdx.x - 6 * 32; // 0 .. 32 * CONVERTER_WARPS - 1
+    // What does not change from block to block, per packet of this thread: where it
+    // lies in the tile of w (row k, byte column) and in the stage (two 16-byte slots
+    // of row k in the chunk of 64 columns pkt / 4, swizzled with the row).
+    int rowOf[PACKETS], colOf[PACKETS];
+    long long offsetOf[PACKETS];
+    uint32_t slotA[PACKETS], slotB[PACKETS];
+#pragma unroll
+    for (int i = 0; i < PACKETS; ++i) {
+      const int id = tid + 32 * CONVERTER_WARPS * i;
+      const int k = id >> 3, pkt = id & 7;
+      rowOf[i] = k;
+      colOf[i] = pkt * 16;
+      offsetOf[i] = (long long)k * ldw + pkt * 16;
+      const uint32_t base = uint32_t(kABytes + (pkt >> 2) * kBChunkBytes + k * 128);
+      const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
+      slotA[i] = base + ((slot ^ x) << 4);
+      slotB[i] = base + (((slot + 1u) ^ x) << 4);
+    }
+    // The blocks of this CTA in order: (tile, K block), walked by two cursors - the
+    // loads run AHEAD blocks in front of the conversions.
     struct Cursor {
       int t, kb;
-      long long col0; // first column of this CTA's share of the tile
+      const int8_t *at; // first byte of the block's tile of w
+      long long col0;   // first column of this CTA's share of the tile
       bool have;
     };
-    auto columnOf = [&](int t) {
+    auto enterTile = [&](Cursor &c) {
       int tm, tn;
-      tileCoords(t, p, tm, tn);
-      return (long long)tn * BN + (long long)ctaRank * kBCols;
+      tileCoords(c.t, p, tm, tn);
+      c.col0 = (long long)tn * BN + (long long)ctaRank * kBCols;
+      c.at = w + c.col0;
     };
     auto advance = [&](Cursor &c) {
-      if (c.have && ++c.kb == kBlocks) {
+      if (!c.have)
+        return;
+      c.at += (long long)BK * ldw;
+      if (++c.kb == kBlocks) {
         c.kb = 0;
         c.t += tileStep;
         c.have = c.t < numTiles;
         if (c.have)
-          c.col0 = columnOf(c.t);
+          enterTile(c);
       }
     };
     auto loadBlock = [&](const Cursor &c, int4 (&v)[PACKETS]) {
+      // Past K or N the tile is zero, as a TMA box would have filled it (N is a
+      // multiple of 16, so a packet lies wholly inside or outside); only the last
+      // K block and the last column of tiles can reach there.
+      const bool inside = (long long)(c.kb + 1) * BK <= p.K && c.col0 + kBCols <= p.N;
 #pragma unroll
       for (int i = 0; i < PACKETS; ++i) {
-        const int id = tid + 32 * CONVERTER_WARPS * i;
-        const long long k = (long long)c.kb * BK + (id >> 3);
-        const long long col = c.col0 + (id & 7) * 16;
-        // Past K or N the tile is zero, as a TMA box would have filled it (N is a
-        // multiple of 16, so a packet lies wholly inside or outside).
-        v[i] = (k < p.K && col < p.N)
-                   ? __ldg(reinterpret_cast<const int4 *>(w + k * ldw + col))
-                   : make_int4(0, 0, 0, 0);
+        const bool take = inside || ((long long)c.kb * BK + rowOf[i] < p.K &&
+                                     c.col0 + colOf[i] < p.N);
+        v[i] = take ? __ldg(reinterpret_cast<const int4 *>(c.at + offsetOf[i]))
+                    : make_int4(0, 0, 0, 0);
       }
     };
     constexpr int AHEAD = 2, BUFFERS = AHEAD + 1;
-    Cursor fetch{firstTile, 0, 0, firstTile < numTiles};
+    Cursor fetch{firstTile, 0, w, 0, firstTile < numTiles};
     if (fetch.have)
-      fetch.col0 = columnOf(fetch.t);
+      enterTile(fetch);
     Cursor use = fetch;
     int4 buf[BUFFERS][PACKETS];
 #pragma unroll
@@ -254,7 +264,7 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         loadBlock(fetch, buf[r]);
       advance(fetch);
     }
-    uint32_t it = 0;
+    uint32_t s = 0, phase = 0; // stage and parity of the block being converted
     bool ok = true;
     while (use.have && ok) {
 #pragma unroll
@@ -264,18 +274,15 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         if (fetch.have)
           loadBlock(fetch, buf[(r + AHEAD) % BUFFERS]);
         advance(fetch);
-        const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
         if (lane == 0) // the MMAs that read the stage before are done
           ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
                         kStatusConverterWait);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok)
           break;
-        unsigned char *bStage = aligned + s * kStageBytes + kABytes;
+        unsigned char *stage = aligned + s * kStageBytes;
 #pragma unroll
         for (int i = 0; i < PACKETS; ++i) {
-          const int id = tid + 32 * CONVERTER_WARPS * i;
-          const int k = id >> 3, pkt = id & 7;
           const int4 q = buf[r][i];
           const uint32_t words[4] = {uint32_t(q.x), uint32_t(q.y), uint32_t(q.z), uint32_t(q.w)};
           uint32_t o[8];
@@ -284,22 +291,23 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
             o[2 * j] = int8PairToBf16(words[j], 0x5140u);     // bytes 0 and 1
             o[2 * j + 1] = int8PairToBf16(words[j], 0x7362u); // bytes 2 and 3
           }
-          // The 16 columns are the 16-byte slots 2 (pkt % 4) and the next of row k
-          // in the chunk of 64 columns pkt / 4; slots are swizzled with the row.
-          unsigned char *row = bStage + (pkt >> 2) * kBChunkBytes + k * 128;
-          const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
-          *reinterpret_cast<uint4 *>(row + ((slot ^ x) << 4)) =
-              make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4 *>(row + (((slot + 1u) ^ x) << 4)) =
-              make_uint4(o[4], o[5], o[6], o[7]);
+          *reinterpret_cast<uint4 *>(stage + slotA[i]) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4 *>(stage + slotB[i]) = make_uint4(o[4], o[5], o[6], o[7]);
         }
         // The MMA reads shared memory through the async proxy.
         fenceProxyAsync();
         __syncwarp();
-        if (lane == 0)
-          mbarArrive(smemAddr(&bars->converted[s]));
-        advance(use);
-        ++it;
+        if (lane == 0) // straight to the leader CTA's barrier (release at CTA scope)
+          mbarArriveRemote(mapSharedToCta(smemAddr(&bars->full[s]), 0));
+        use.kb = use.kb + 1 == kBlocks ? 0 : use.kb + 1; // (only `have` and the count matter)
+        if (use.kb == 0) {
+          use.t += tileStep;
+          use.have = use.t < numTiles;
+        }
+        if (++s == kStages) {
+          s = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else if (warp == 1) {

@@ -99,6 +99,22 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// The same, letting the hardware keep the thread suspended for up to `hintNs`
+// while the phase is incomplete (it wakes when the phase completes): a waiting
+// thread then leaves the issue slots to the warps that have work.
+__device__ __forceinline__ bool mbarTryWaitFor(uint32_t bar, uint32_t parity, uint32_t hintNs) {
+  uint32_t done;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1, %3;\n"
+               "selp.u32 %2, 1, 0, p;\n"
+               "}\n"
+               : "+r"(bar), "+r"(parity), "=r"(done)
+               : "r"(hintNs)
+               : "memory");
+  return done != 0;
+}
+
 // Waits for the phase with the given parity.  Returns false when the wait was
 // abandoned: either it ran out of time (then `*abortFlag` is raised and `code`
 // is published in `*status`), or another thread of the CTA had already raised
@@ -111,9 +127,9 @@ __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity,
     return true;
   unsigned long long start = globalTimerNs();
   for (uint32_t spin = 1;; ++spin) {
-    if (mbarTryWait(bar, parity))
+    if (mbarTryWaitFor(bar, parity, 20000u))
       return true;
-    if ((spin & 63u) == 0) {
+    if ((spin & 1u) == 0) { // (a failed poll may have slept for its whole hint)
       if (*abortFlag)
         return false;
       if (globalTimerNs() - start > limitNs) {

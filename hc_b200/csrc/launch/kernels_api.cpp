@@ -1642,14 +1642,14 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
     if (c->pairSlotsW8 == 0) {
       OlKernel k = c->kernel(name);
       int slots = 0;
-      if (!k || olxMaxActiveClusters(c->queue, k, 480, smem, 2, &slots) || slots <= 0)
+      if (!k || olxMaxActiveClusters(c->queue, k, 448, smem, 2, &slots) || slots <= 0)
         return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
       c->pairSlotsW8 = slots;
     }
     const long long grid = 2 * std::min<long long>(tiles, c->pairSlotsW8);
     void *args[] = {&mapA, &w, &ldw, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
                     &vecStore, &c->statusWord};
-    return c->launch(name, size_t(grid), 1, 1, 480, args, 14, smem);
+    return c->launch(name, size_t(grid), 1, 1, 448, args, 14, smem);
   }
   const long long wsPitch = roundUp(N, 16);
   if (c->gemmVariant == 3 || !ummaEligible(c, a, workspace, K, lda, wsPitch)) {
