@@ -24,7 +24,7 @@
 // Two kernels.  hc_split_tf32_pairs writes x once as (hi, lo) pairs - the nine
 // taps of a 3 x 3 filter read every element nine times, and splitting it in the
 // main loop cost three times the instructions of loading it.  hc_conv_f32_umma:
-// one persistent CTA per SM, 704 threads:
+// one persistent CTA per SM, 448 threads:
 //   warp 0      TMA producer of the filter tiles: per 32-deep K block two boxes
 //               (f hi, f lo; [NF rows, 32 k], 128-byte swizzle, rows beyond NF
 //               and k beyond K zero-filled; no multicast);
@@ -33,12 +33,12 @@
 //               block, small terms first;
 //   warps 2-5   epilogue: tcgen05.ld, then for every filter a store that is
 //               contiguous across the warp's 32 pixels;
-//   warps 6-21  the image operand: thread (row m, quarter h) loads its 8
+//   warps 6-13  the image operand: thread (row m, half h) loads its 16
 //               (hi, lo) pairs of the K block with 8-byte loads (read-only
-//               path, L1 keeps the lines that the taps share), two blocks
+//               path, L1 keeps the lines that the taps share), one block
 //               ahead of their use, and writes hi and lo into the stage in the
 //               128-byte-swizzled K-major layout the MMA descriptors expect,
-//               then fence.proxy.async.  The 512 threads meet once per K block
+//               then fence.proxy.async.  The 256 threads meet once per K block
 //               at a named barrier (bar.sync 1); only their leader touches the
 //               mbarriers - it waits for the next free stage before the meeting
 //               and reports the stage filled after it.
@@ -54,8 +54,8 @@ using namespace hc;
 constexpr int BM = 128;   // output pixels per tile (TMEM lanes)
 constexpr int BK = 32;    // K depth of a stage: one 128-byte row
 constexpr int UMMA_K = 8;
-constexpr int GATHER_WARPS = 16;
-constexpr int PER_THREAD = BM * BK / (32 * GATHER_WARPS); // k of a block per thread: 8
+constexpr int GATHER_WARPS = 8;
+constexpr int PER_THREAD = BM * BK / (32 * GATHER_WARPS); // k of a block per thread: 16
 constexpr int NUM_THREADS = 32 * (6 + GATHER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_STRIDE = 256; // TMEM columns between the two accumulators
@@ -200,7 +200,7 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
     const int g = warp - 6;
     // A warp reaches the TMEM lanes of its quarter (warp index mod 4) only.
     const int m = (warp & 3) * 32 + lane; // row of the tile
-    const int part = g >> 2;              // which 8 of the 32 k of a block
+    const int part = g >> 2;              // which 16 of the 32 k of a block
     const long long xsN = (long long)p.C * p.H * p.W;
     const float2 *pairs = static_cast<const float2 *>(p.x);
     // Where row m keeps chunk c (16 bytes, four k) of its 128-byte row.
@@ -225,10 +225,13 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
         v[4 * q + 3] = __ldg(src + o.w);
       }
     };
-    // The loads of a K block are issued two blocks ahead of its stores, into one
-    // of three register buffers that the unrolled loop names at compile time, so
-    // that their latency is covered by the storing of the blocks before (nothing
-    // is copied between buffers, which would wait for the loads).
+    // The loads of a K block are issued one block ahead of its stores, into one of
+    // two register buffers that the unrolled loop names at compile time, so that
+    // their latency is covered by the storing of the block before (nothing is
+    // copied between buffers, which would wait for the loads).  Eight warps with
+    // 16 pairs per thread measured 10 % faster than sixteen with 8 (the work a
+    // warp does per K block besides its elements is the same) and four with 32
+    // spill.
     struct Cursor {
       int t, kb;
       const float2 *src;
@@ -243,7 +246,7 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
           c.src = rowSource(c.t);
       }
     };
-    constexpr int AHEAD = 2, BUFFERS = AHEAD + 1;
+    constexpr int AHEAD = 1, BUFFERS = AHEAD + 1;
     Cursor fetch{int(blockIdx.x), 0, pairs, int(blockIdx.x) < numTiles};
     if (fetch.have)
       fetch.src = rowSource(fetch.t);
@@ -303,8 +306,17 @@ __device__ __forceinline__ void convF32(const CUtensorMap &mapFHi, const CUtenso
           }
           const uint32_t at = tmemBase + (uint32_t((warp & 3) * 32) << 16) + kATmemBase +
                               s * 64u + uint32_t(part * PER_THREAD);
-          tmemStore32x8(at, hi);
-          tmemStore32x8(at + 32u, lo);
+#pragma unroll
+          for (int h8 = 0; h8 < PER_THREAD / 8; ++h8) {
+            uint32_t a8[8], b8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              a8[e] = hi[8 * h8 + e];
+              b8[e] = lo[8 * h8 + e];
+            }
+            tmemStore32x8(at + uint32_t(8 * h8), a8);
+            tmemStore32x8(at + 32u + uint32_t(8 * h8), b8);
+          }
           tmemStoreWait();
           tcgen05FenceBefore();
         } else {

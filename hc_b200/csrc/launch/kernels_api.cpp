@@ -1527,7 +1527,7 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
   const long long grid = std::min<long long>(tiles, c->smCount);
   const size_t smem = size_t(stages * stageBytes + fixed);
   void *args[] = {&maps[0], &maps[1], &p};
-  return c->launch(tmemA ? "hc_conv_f32_umma_ta" : "hc_conv_f32_umma", size_t(grid), 1, 1, 704,
+  return c->launch(tmemA ? "hc_conv_f32_umma_ta" : "hc_conv_f32_umma", size_t(grid), 1, 1, 448,
                    args, 3, smem);
 }
 
