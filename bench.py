@@ -491,6 +491,8 @@ def run_gpu(args):
     desc = f"cuda:{local}"
     kernels = make_kernels(desc)
     ctx = get_context(desc)
+    if args.w8a16_fused:
+        ctx.set_option("w8a16_variant", 2)  # convert the weights inside the GEMM's pipeline
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
     peaks = load_peaks()
     launcher = ShardedLauncher(kernels, rank, world)
@@ -1260,6 +1262,9 @@ def main():
                          "NVLink), or NCCL's all-gather runs behind them")
     ap.add_argument("--bands", type=int, default=0,
                     help="row bands of the sharded run (0: the workload's default)")
+    ap.add_argument("--w8a16-fused", action="store_true",
+                    help="gemm_w8a16: convert the int8 weights inside the GEMM's pipeline "
+                         "(no scratch matrix) instead of in a pass of their own")
     ap.add_argument("--small", action="store_true",
                     help="reduced shapes, for profiler captures; not a benchmark result")
     args = ap.parse_args()

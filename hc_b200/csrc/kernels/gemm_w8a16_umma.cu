@@ -14,8 +14,9 @@
 //   warp 0     TMA producer of A: per 64-deep K block its 128 rows (bf16, 128-byte
 //              swizzle, completion counted on the leader CTA's barrier; no
 //              multicast);
-//   warps 6-13 converters: 16 weights per 16-byte global load, issued two K
-//              blocks ahead (w never passes through shared memory as bytes:
+//   warps 6-13 converters, four groups of two warps that take the K blocks in
+//              turn: 16 weights per 16-byte global load, issued one of the
+//              group's blocks ahead (w never passes through shared memory as bytes:
 //              the shared-memory port carries what the bf16 kernel carries) -> two
 //              16-byte stores of bf16 into the stage, in the N-major 128-byte-
 //              swizzled layout a TMA box of bf16 would have produced
@@ -30,7 +31,7 @@
 // Every weight tile is converted once per 256-row block of activations - work
 // the CUDA cores do while the tensor cores run the block before.
 //
-// Measured at 4096 x 8192 x 8192: 0.58-0.61 ms, against 0.42-0.45 ms for the
+// Measured at 4096 x 8192 x 8192: 0.58-0.59 ms, against 0.42-0.45 ms for the
 // conversion pass plus the bf16 kernel; the MMA warp waits for converted stages
 // about as long as it issues.  It is therefore not the default (option
 // "w8a16_variant" = 2 selects it): it is the form for callers that cannot spare
@@ -54,7 +55,11 @@ constexpr int NUM_THREADS = 32 * (6 + CONVERTER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int kTileM = 2 * BM;
 constexpr int kBCols = BN / 2;             // columns of w a CTA stages
-constexpr int PACKETS = BK * kBCols / 16 / (32 * CONVERTER_WARPS); // 16-weight packets per thread: 2
+// The converter warps work in groups that take the K blocks in turn, so that a
+// group has GROUPS block times for one block.
+constexpr int GROUPS = 4;
+constexpr int GROUP_WARPS = CONVERTER_WARPS / GROUPS;
+constexpr int PACKETS = BK * kBCols / 16 / (32 * GROUP_WARPS); // 16-weight packets per thread: 8
 constexpr int kABytes = BM * BK * 2;       // 16 KiB
 constexpr int kBChunkBytes = BK * 64 * 2;  // 64 columns of bf16, 64 deep: 8 KiB
 constexpr int kBBytes = 2 * kBChunkBytes;  // 16 KiB
@@ -92,6 +97,17 @@ __device__ __forceinline__ void tileCoords(int t, const Params &p, int &tm, int 
   tn = rem / rowsInBand;
 }
 
+// Which 16-weight packet of a 64 x 128 tile has number `id` (0..511): row k and
+// packet column 0..7.  32 consecutive numbers cover four rows, as a warp's load
+// wants it (whole 128-byte rows); within them, 8 consecutive numbers are the four
+// packets of one 64-column chunk in two neighbouring rows, whose 16-byte slots in
+// the swizzled stage fall into eight different bank groups - a 16-byte store is
+// served eight lanes at a time.
+__device__ __forceinline__ int rowOfPacket(int id) {
+  return 4 * (id >> 5) + 2 * ((id >> 4) & 1) + ((id >> 2) & 1);
+}
+__device__ __forceinline__ int columnOfPacket(int id) { return 4 * ((id >> 3) & 1) + (id & 3); }
+
 // Two int8 (the bytes `sel` picks out of `word`) -> two bf16, exactly (see
 // dequant_w8.cu: the byte under exponent 0x43, minus 128 or 256).
 __device__ __forceinline__ uint32_t int8PairToBf16(uint32_t word, uint32_t sel) {
@@ -125,7 +141,7 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     for (int s = 0; s < kStages; ++s) {
       // The leader's expect_tx for both CTAs' A, and one report per converter warp of
       // both CTAs.
-      mbarInit(smemAddr(&bars->full[s]), 1 + 2 * CONVERTER_WARPS);
+      mbarInit(smemAddr(&bars->full[s]), 1 + 2 * GROUP_WARPS);
       mbarInit(smemAddr(&bars->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -188,92 +204,71 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     }
   } else if (warp >= 6) {
     // -------------------------------- converters --------------------------------
-    // Every thread owns two 16-weight packets of a tile (row k = id / 8, columns
+    // The eight warps form four groups that take the K blocks in turn; a thread owns
+    // eight 16-weight packets of its group's tile (row k = id / 8, columns
     // 16 (id % 8) ... of this CTA's 128 columns).  It loads them straight from
-    // global memory two K blocks ahead of their use (read-only path; a warp reads
-    // four whole 128-byte rows per load), converts them when the stage is free and
-    // stores the bf16 where a TMA box of bf16 would have put them.  The warps run
-    // up to the ring of stages ahead of the MMAs and wait for nothing else.
-    const int tid = threadIdx.x - 6 * 32; // 0 .. 32 * CONVERTER_WARPS - 1
+    // global memory one of its blocks ahead (read-only path; a warp reads four
+    // whole 128-byte rows per load), converts them when the stage is free and
+    // stores the bf16 where a TMA box of bf16 would have put them.  What a warp does
+    // per block besides its packets (waiting, fencing, reporting) is then done a
+    // quarter as often per warp, and four blocks are in the making at once.
+    const int group = (warp - 6) / GROUP_WARPS;              // takes blocks group, group + GROUPS ...
+    const int tid = threadIdx.x - (6 + group * GROUP_WARPS) * 32; // 0 .. 32 * GROUP_WARPS - 1
     // What does not change from block to block, per packet of this thread: where it
     // lies in the tile of w (row k, byte column) and in the stage (two 16-byte slots
     // of row k in the chunk of 64 columns pkt / 4, swizzled with the row).
-    int rowOf[PACKETS], colOf[PACKETS];
     long long offsetOf[PACKETS];
     uint32_t slotA[PACKETS], slotB[PACKETS];
 #pragma unroll
     for (int i = 0; i < PACKETS; ++i) {
-      const int id = tid + 32 * CONVERTER_WARPS * i;
-      const int k = id >> 3, pkt = id & 7;
-      rowOf[i] = k;
-      colOf[i] = pkt * 16;
+      const int id = tid + 32 * GROUP_WARPS * i;
+      const int k = rowOfPacket(id), pkt = columnOfPacket(id);
       offsetOf[i] = (long long)k * ldw + pkt * 16;
       const uint32_t base = uint32_t(kABytes + (pkt >> 2) * kBChunkBytes + k * 128);
       const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
       slotA[i] = base + ((slot ^ x) << 4);
       slotB[i] = base + (((slot + 1u) ^ x) << 4);
     }
-    // The blocks of this CTA in order: (tile, K block), walked by two cursors - the
-    // loads run AHEAD blocks in front of the conversions.
-    struct Cursor {
-      int t, kb;
-      const int8_t *at; // first byte of the block's tile of w
-      long long col0;   // first column of this CTA's share of the tile
-      bool have;
-    };
-    auto enterTile = [&](Cursor &c) {
+    int myTiles = 0;
+    for (int t = firstTile; t < numTiles; t += tileStep)
+      ++myTiles;
+    const uint32_t blocks = uint32_t(myTiles) * uint32_t(kBlocks);
+    // Block `index` of this CTA: K block index % kBlocks of its tile index / kBlocks.
+    auto loadBlock = [&](uint32_t index, int4 (&v)[PACKETS]) {
+      const int kb = int(index % uint32_t(kBlocks));
+      const int t = firstTile + int(index / uint32_t(kBlocks)) * tileStep;
       int tm, tn;
-      tileCoords(c.t, p, tm, tn);
-      c.col0 = (long long)tn * BN + (long long)ctaRank * kBCols;
-      c.at = w + c.col0;
-    };
-    auto advance = [&](Cursor &c) {
-      if (!c.have)
-        return;
-      c.at += (long long)BK * ldw;
-      if (++c.kb == kBlocks) {
-        c.kb = 0;
-        c.t += tileStep;
-        c.have = c.t < numTiles;
-        if (c.have)
-          enterTile(c);
-      }
-    };
-    auto loadBlock = [&](const Cursor &c, int4 (&v)[PACKETS]) {
+      tileCoords(t, p, tm, tn);
+      const long long col0 = (long long)tn * BN + (long long)ctaRank * kBCols;
+      const int8_t *at = w + (long long)kb * BK * ldw + col0;
       // Past K or N the tile is zero, as a TMA box would have filled it (N is a
       // multiple of 16, so a packet lies wholly inside or outside); only the last
       // K block and the last column of tiles can reach there.
-      const bool inside = (long long)(c.kb + 1) * BK <= p.K && c.col0 + kBCols <= p.N;
+      const bool inside = (long long)(kb + 1) * BK <= p.K && col0 + kBCols <= p.N;
 #pragma unroll
       for (int i = 0; i < PACKETS; ++i) {
-        const bool take = inside || ((long long)c.kb * BK + rowOf[i] < p.K &&
-                                     c.col0 + colOf[i] < p.N);
-        v[i] = take ? __ldg(reinterpret_cast<const int4 *>(c.at + offsetOf[i]))
+        const int id = tid + 32 * GROUP_WARPS * i;
+        const bool take = inside || ((long long)kb * BK + rowOfPacket(id) < p.K &&
+                                     col0 + columnOfPacket(id) * 16 < p.N);
+        v[i] = take ? __ldg(reinterpret_cast<const int4 *>(at + offsetOf[i]))
                     : make_int4(0, 0, 0, 0);
       }
     };
-    constexpr int AHEAD = 2, BUFFERS = AHEAD + 1;
-    Cursor fetch{firstTile, 0, w, 0, firstTile < numTiles};
-    if (fetch.have)
-      enterTile(fetch);
-    Cursor use = fetch;
-    int4 buf[BUFFERS][PACKETS];
-#pragma unroll
-    for (int r = 0; r < AHEAD; ++r) {
-      if (fetch.have)
-        loadBlock(fetch, buf[r]);
-      advance(fetch);
-    }
-    uint32_t s = 0, phase = 0; // stage and parity of the block being converted
+    // Two register buffers that the unrolled loop names at compile time: the loads
+    // of the group's next block are in flight while this one is converted.
+    int4 buf[2][PACKETS];
+    uint32_t it = uint32_t(group);
+    if (it < blocks)
+      loadBlock(it, buf[0]);
     bool ok = true;
-    while (use.have && ok) {
+    while (it < blocks && ok) {
 #pragma unroll
-      for (int r = 0; r < BUFFERS; ++r) {
-        if (!use.have || !ok)
+      for (int r = 0; r < 2; ++r) {
+        if (it >= blocks || !ok)
           break;
-        if (fetch.have)
-          loadBlock(fetch, buf[(r + AHEAD) % BUFFERS]);
-        advance(fetch);
+        if (it + GROUPS < blocks)
+          loadBlock(it + GROUPS, buf[r ^ 1]);
+        const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
         if (lane == 0) // the MMAs that read the stage before are done
           ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
                         kStatusConverterWait);
@@ -299,15 +294,7 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         __syncwarp();
         if (lane == 0) // straight to the leader CTA's barrier (release at CTA scope)
           mbarArriveRemote(mapSharedToCta(smemAddr(&bars->full[s]), 0));
-        use.kb = use.kb + 1 == kBlocks ? 0 : use.kb + 1; // (only `have` and the count matter)
-        if (use.kb == 0) {
-          use.t += tileStep;
-          use.have = use.t < numTiles;
-        }
-        if (++s == kStages) {
-          s = 0;
-          phase ^= 1u;
-        }
+        it += GROUPS;
       }
     }
   } else if (warp == 1) {
