@@ -10,14 +10,16 @@
 // cross HBM, L2 and the SM boundary as one byte per element instead of two.
 //
 // A cluster of two CTAs works on one 256 x 256 output tile with
-// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 448 threads:
+// tcgen05.mma.cta_group::2 (as hc_gemm_bf16_umma_pair).  Per CTA, 480 threads:
 //   warp 0     TMA producer of A: per 64-deep K block its 128 rows (bf16, 128-byte
 //              swizzle, completion counted on the leader CTA's barrier; no
 //              multicast);
+//   warp 14    TMA producer of w: its 64 x 128 tile as raw bytes (no swizzle,
+//              completion on this CTA's own `raw` barrier) into a ring of eight
+//              slots of its own - deeper than the stages, because the way of a
+//              weight into an MMA is the longest; no multicast anywhere;
 //   warps 6-13 converters, four groups of two warps that take the K blocks in
-//              turn: 16 weights per 16-byte global load, issued one of the
-//              group's blocks ahead (w never passes through shared memory as bytes:
-//              the shared-memory port carries what the bf16 kernel carries) -> two
+//              turn: 16 weights per 16-byte shared-memory load -> two
 //              16-byte stores of bf16 into the stage, in the N-major 128-byte-
 //              swizzled layout a TMA box of bf16 would have produced
 //              (int8 -> bf16 by byte permute and one packed subtract, exact);
@@ -31,9 +33,10 @@
 // Every weight tile is converted once per 256-row block of activations - work
 // the CUDA cores do while the tensor cores run the block before.
 //
-// Measured at 4096 x 8192 x 8192: 0.58-0.59 ms, against 0.42-0.45 ms for the
-// conversion pass plus the bf16 kernel; the MMA warp waits for converted stages
-// about as long as it issues.  It is therefore not the default (option
+// Measured at 4096 x 8192 x 8192: 0.51-0.52 ms, against 0.42-0.45 ms for the
+// conversion pass plus the bf16 kernel: per K block the shared-memory port now
+// carries 80 KiB (A and the bytes of w in, the bytes out again, bf16 in, A and
+// bf16 out to the tensor core) where the bf16 kernel carries 64.  It is therefore not the default (option
 // "w8a16_variant" = 2 selects it): it is the form for callers that cannot spare
 // the 2 bytes per weight of scratch memory.
 //
@@ -51,7 +54,8 @@ constexpr int BN = 256;    // accumulator columns per tile
 constexpr int BK = 64;     // K depth of one stage
 constexpr int UMMA_K = 16;
 constexpr int CONVERTER_WARPS = 8;
-constexpr int NUM_THREADS = 32 * (6 + CONVERTER_WARPS);
+constexpr int RAW_PRODUCER_WARP = 6 + CONVERTER_WARPS;
+constexpr int NUM_THREADS = 32 * (7 + CONVERTER_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int kTileM = 2 * BM;
 constexpr int kBCols = BN / 2;             // columns of w a CTA stages
@@ -64,7 +68,13 @@ constexpr int kABytes = BM * BK * 2;       // 16 KiB
 constexpr int kBChunkBytes = BK * 64 * 2;  // 64 columns of bf16, 64 deep: 8 KiB
 constexpr int kBBytes = 2 * kBChunkBytes;  // 16 KiB
 constexpr int kStageBytes = kABytes + kBBytes; // 32 KiB: A and the converted B
-constexpr int kStages = 6;
+constexpr int kStages = 5;
+// The int8 tiles wait in a ring of their own, deeper than the stages: what must be
+// in flight to cover the latency of L2 under this kernel's traffic is more than
+// registers can hold, so TMA brings the bytes and the converters read them from
+// shared memory.
+constexpr int kRawBytes = BK * kBCols; // 8 KiB
+constexpr int kRawSlots = 8;
 
 constexpr uint32_t kInstrDesc = makeInstrDescBf16(kTileM, BN, /*aMnMajor=*/false,
                                                   /*bMnMajor=*/true);
@@ -72,6 +82,8 @@ constexpr uint32_t kInstrDesc = makeInstrDescBf16(kTileM, BN, /*aMnMajor=*/false
 struct alignas(8) Barriers {
   uint64_t full[kStages];  // leader CTA: A of both CTAs landed, both CTAs' B converted
   uint64_t empty[kStages]; // the MMAs that read the stage are done (both CTAs)
+  uint64_t raw[kRawSlots];      // this CTA: the int8 tile landed
+  uint64_t rawEmpty[kRawSlots]; // this CTA: the group that converts the tile has read it
   uint64_t tmemFull[2];
   uint64_t tmemEmpty[2];
   uint32_t tmemBase;
@@ -123,7 +135,7 @@ __device__ __forceinline__ uint32_t int8PairToBf16(uint32_t word, uint32_t sel) 
 
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     hc_gemm_w8a16_umma_pair(const __grid_constant__ CUtensorMap mapA,
-                            const int8_t *__restrict__ w, long long ldw,
+                            const __grid_constant__ CUtensorMap mapW,
                             __nv_bfloat16 *__restrict__ c, const float *__restrict__ scale,
                             long long M, long long N, long long K, long long ldc, int tilesM,
                             int tilesN, int bandM, int vecStore, int *status) {
@@ -131,7 +143,8 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
   const Params p{M, N, K, ldc, tilesM, tilesN, bandM, vecStore};
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
   unsigned char *aligned = smemRaw + (smemBase - smemAddr(smemRaw));
-  Barriers *bars = reinterpret_cast<Barriers *>(aligned + kStages * kStageBytes);
+  unsigned char *rawRing = aligned + kStages * kStageBytes;
+  Barriers *bars = reinterpret_cast<Barriers *>(rawRing + kRawSlots * kRawBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ctaRank = clusterCtaRank();
   const bool leaderCta = ctaRank == 0;
@@ -144,6 +157,10 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
       mbarInit(smemAddr(&bars->full[s]), 1 + 2 * GROUP_WARPS);
       mbarInit(smemAddr(&bars->empty[s]), 1);
     }
+    for (int q = 0; q < kRawSlots; ++q) {
+      mbarInit(smemAddr(&bars->raw[q]), 1);
+      mbarInit(smemAddr(&bars->rawEmpty[q]), GROUP_WARPS);
+    }
     for (int a = 0; a < 2; ++a) {
       mbarInit(smemAddr(&bars->tmemFull[a]), 1);
       mbarInit(smemAddr(&bars->tmemEmpty[a]), 8); // epilogue warps of both CTAs
@@ -151,6 +168,7 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     bars->abortFlag = 0;
     fenceBarrierInit();
     prefetchTensorMap(&mapA);
+    prefetchTensorMap(&mapW);
   }
   if (warp == 1) {
     tmemAlloc<2>(smemAddr(&bars->tmemBase), TMEM_COLS);
@@ -202,28 +220,55 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
         }
       }
     }
+  } else if (warp == RAW_PRODUCER_WARP) {
+    // ------------------------- TMA producer of the int8 tiles -------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep) {
+        int tm, tn;
+        tileCoords(t, p, tm, tn);
+        const int col0 = tn * BN + int(ctaRank) * kBCols;
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+          const uint32_t q = it % kRawSlots, phase = (it / kRawSlots) & 1u;
+          if (!mbarWait(smemAddr(&bars->rawEmpty[q]), phase ^ 1u, abortFlag, status,
+                        kStatusProducerWait))
+            break;
+          // The weights as bytes: rows of 128 bytes, no swizzle, this CTA's own barrier;
+          // past K or N the box is zero-filled.
+          const uint32_t rawBar = smemAddr(&bars->raw[q]);
+          mbarExpectTx(rawBar, kRawBytes);
+          tmaLoad2D(smemBase + kStages * kStageBytes + q * kRawBytes, &mapW, rawBar, col0,
+                    kb * BK);
+        }
+      }
+      // Nothing may still be landing when this CTA's shared memory goes away: the
+      // converters read every tile before they finish (the teardown's cluster
+      // barrier waits for them); after a wait that gave up, give the copies time.
+      if (*abortFlag) {
+        const unsigned long long t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull) {
+        }
+      }
+    }
   } else if (warp >= 6) {
     // -------------------------------- converters --------------------------------
     // The eight warps form four groups that take the K blocks in turn; a thread owns
-    // eight 16-weight packets of its group's tile (row k = id / 8, columns
-    // 16 (id % 8) ... of this CTA's 128 columns).  It loads them straight from
-    // global memory one of its blocks ahead (read-only path; a warp reads four
-    // whole 128-byte rows per load), converts them when the stage is free and
+    // eight 16-weight packets of its group's tile.  When the tile has landed and the
+    // stage is free it reads them from the ring of int8 tiles, converts them and
     // stores the bf16 where a TMA box of bf16 would have put them.  What a warp does
-    // per block besides its packets (waiting, fencing, reporting) is then done a
-    // quarter as often per warp, and four blocks are in the making at once.
+    // per block besides its packets (waiting, fencing, reporting) is done a quarter
+    // as often per warp, and four blocks are in the making at once.
     const int group = (warp - 6) / GROUP_WARPS;              // takes blocks group, group + GROUPS ...
     const int tid = threadIdx.x - (6 + group * GROUP_WARPS) * 32; // 0 .. 32 * GROUP_WARPS - 1
     // What does not change from block to block, per packet of this thread: where it
     // lies in the tile of w (row k, byte column) and in the stage (two 16-byte slots
     // of row k in the chunk of 64 columns pkt / 4, swizzled with the row).
-    long long offsetOf[PACKETS];
-    uint32_t slotA[PACKETS], slotB[PACKETS];
+    uint32_t rawOf[PACKETS], slotA[PACKETS], slotB[PACKETS];
 #pragma unroll
     for (int i = 0; i < PACKETS; ++i) {
       const int id = tid + 32 * GROUP_WARPS * i;
       const int k = rowOfPacket(id), pkt = columnOfPacket(id);
-      offsetOf[i] = (long long)k * ldw + pkt * 16;
+      rawOf[i] = uint32_t(k * kBCols + pkt * 16);
       const uint32_t base = uint32_t(kABytes + (pkt >> 2) * kBChunkBytes + k * 128);
       const uint32_t slot = uint32_t(pkt & 3) * 2u, x = uint32_t(k & 7);
       slotA[i] = base + ((slot ^ x) << 4);
@@ -233,68 +278,46 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREA
     for (int t = firstTile; t < numTiles; t += tileStep)
       ++myTiles;
     const uint32_t blocks = uint32_t(myTiles) * uint32_t(kBlocks);
-    // Block `index` of this CTA: K block index % kBlocks of its tile index / kBlocks.
-    auto loadBlock = [&](uint32_t index, int4 (&v)[PACKETS]) {
-      const int kb = int(index % uint32_t(kBlocks));
-      const int t = firstTile + int(index / uint32_t(kBlocks)) * tileStep;
-      int tm, tn;
-      tileCoords(t, p, tm, tn);
-      const long long col0 = (long long)tn * BN + (long long)ctaRank * kBCols;
-      const int8_t *at = w + (long long)kb * BK * ldw + col0;
-      // Past K or N the tile is zero, as a TMA box would have filled it (N is a
-      // multiple of 16, so a packet lies wholly inside or outside); only the last
-      // K block and the last column of tiles can reach there.
-      const bool inside = (long long)(kb + 1) * BK <= p.K && col0 + kBCols <= p.N;
+    for (uint32_t it = uint32_t(group); it < blocks; it += GROUPS) {
+      const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
+      const uint32_t q = it % kRawSlots, rawPhase = (it / kRawSlots) & 1u;
+      bool ok = true;
+      if (lane == 0)
+        // The tile has landed, and the MMAs that read the stage before are done.
+        ok = mbarWait(smemAddr(&bars->raw[q]), rawPhase, abortFlag, status,
+                      kStatusConverterWait) &&
+             mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
+                      kStatusConverterWait);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok)
+        break;
+      const unsigned char *raw = rawRing + q * kRawBytes;
+      unsigned char *stage = aligned + s * kStageBytes;
+      int4 loaded[PACKETS];
+#pragma unroll
+      for (int i = 0; i < PACKETS; ++i)
+        loaded[i] = *reinterpret_cast<const int4 *>(raw + rawOf[i]);
 #pragma unroll
       for (int i = 0; i < PACKETS; ++i) {
-        const int id = tid + 32 * GROUP_WARPS * i;
-        const bool take = inside || ((long long)kb * BK + rowOfPacket(id) < p.K &&
-                                     col0 + columnOfPacket(id) * 16 < p.N);
-        v[i] = take ? __ldg(reinterpret_cast<const int4 *>(at + offsetOf[i]))
-                    : make_int4(0, 0, 0, 0);
-      }
-    };
-    // Two register buffers that the unrolled loop names at compile time: the loads
-    // of the group's next block are in flight while this one is converted.
-    int4 buf[2][PACKETS];
-    uint32_t it = uint32_t(group);
-    if (it < blocks)
-      loadBlock(it, buf[0]);
-    bool ok = true;
-    while (it < blocks && ok) {
+        const int4 v = loaded[i];
+        const uint32_t words[4] = {uint32_t(v.x), uint32_t(v.y), uint32_t(v.z), uint32_t(v.w)};
+        uint32_t o[8];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        if (it >= blocks || !ok)
-          break;
-        if (it + GROUPS < blocks)
-          loadBlock(it + GROUPS, buf[r ^ 1]);
-        const uint32_t s = it % kStages, phase = (it / kStages) & 1u;
-        if (lane == 0) // the MMAs that read the stage before are done
-          ok = mbarWait(smemAddr(&bars->empty[s]), phase ^ 1u, abortFlag, status,
-                        kStatusConverterWait);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok)
-          break;
-        unsigned char *stage = aligned + s * kStageBytes;
-#pragma unroll
-        for (int i = 0; i < PACKETS; ++i) {
-          const int4 q = buf[r][i];
-          const uint32_t words[4] = {uint32_t(q.x), uint32_t(q.y), uint32_t(q.z), uint32_t(q.w)};
-          uint32_t o[8];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            o[2 * j] = int8PairToBf16(words[j], 0x5140u);     // bytes 0 and 1
-            o[2 * j + 1] = int8PairToBf16(words[j], 0x7362u); // bytes 2 and 3
-          }
-          *reinterpret_cast<uint4 *>(stage + slotA[i]) = make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4 *>(stage + slotB[i]) = make_uint4(o[4], o[5], o[6], o[7]);
+        for (int j = 0; j < 4; ++j) {
+          o[2 * j] = int8PairToBf16(words[j], 0x5140u);     // bytes 0 and 1
+          o[2 * j + 1] = int8PairToBf16(words[j], 0x7362u); // bytes 2 and 3
         }
-        // The MMA reads shared memory through the async proxy.
-        fenceProxyAsync();
-        __syncwarp();
-        if (lane == 0) // straight to the leader CTA's barrier (release at CTA scope)
-          mbarArriveRemote(mapSharedToCta(smemAddr(&bars->full[s]), 0));
-        it += GROUPS;
+        *reinterpret_cast<uint4 *>(stage + slotA[i]) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4 *>(stage + slotB[i]) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      // The MMA reads shared memory through the async proxy.
+      fenceProxyAsync();
+      __syncwarp();
+      if (lane == 0) {
+        // Straight to the leader CTA's barrier (release at CTA scope); the slot of
+        // the int8 tile is free again.
+        mbarArriveRemote(mapSharedToCta(smemAddr(&bars->full[s]), 0));
+        mbarArrive(smemAddr(&bars->rawEmpty[q]));
       }
     }
   } else if (warp == 1) {

@@ -1629,27 +1629,30 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
                    "(tcgen05 device, M > 128, lda %% 8 == 0, N and ldw multiples of 16, 16-byte "
                    "aligned a and w)");
   if (fusedFits && c->w8Variant == 2) {
-    alignas(64) CUtensorMap mapA;
+    alignas(64) CUtensorMap mapA, mapW;
     if (olxEncodeTensorMap2D(c->device, &mapA, /*bf16*/ 0, a, size_t(M), size_t(K),
-                             size_t(lda) * 2, kUmmaBM, kUmmaBK, 128))
+                             size_t(lda) * 2, kUmmaBM, kUmmaBK, 128) ||
+        olxEncodeTensorMap2D(c->device, &mapW, /*bytes*/ 2, w, size_t(K), size_t(N), size_t(ldw),
+                             kUmmaBK, 128, 0))
       return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
     int tilesM = int(ceilDiv(M, 2 * kUmmaBM)), tilesN = int(ceilDiv(N, kUmmaBN));
     int bandM = c->gemmBand ? int(c->gemmBand) : 16;
     int vecStore = aligned(out, 16) && ldc % 8 == 0;
     const long long tiles = (long long)tilesM * tilesN;
-    const size_t smem = 6 * 32 * 1024 /*stages*/ + 1024 /*align*/ + 512 /*barriers*/;
+    const size_t smem = 5 * 32 * 1024 /*stages*/ + 8 * 8 * 1024 /*int8 tiles*/ + 1024 /*align*/ +
+                        512 /*barriers*/;
     const char *name = "hc_gemm_w8a16_umma_pair";
     if (c->pairSlotsW8 == 0) {
       OlKernel k = c->kernel(name);
       int slots = 0;
-      if (!k || olxMaxActiveClusters(c->queue, k, 448, smem, 2, &slots) || slots <= 0)
+      if (!k || olxMaxActiveClusters(c->queue, k, 480, smem, 2, &slots) || slots <= 0)
         return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
       c->pairSlotsW8 = slots;
     }
     const long long grid = 2 * std::min<long long>(tiles, c->pairSlotsW8);
-    void *args[] = {&mapA, &w, &ldw, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
+    void *args[] = {&mapA, &mapW, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
                     &vecStore, &c->statusWord};
-    return c->launch(name, size_t(grid), 1, 1, 448, args, 14, smem);
+    return c->launch(name, size_t(grid), 1, 1, 480, args, 13, smem);
   }
   const long long wsPitch = roundUp(N, 16);
   if (c->gemmVariant == 3 || !ummaEligible(c, a, workspace, K, lda, wsPitch)) {
