@@ -873,6 +873,10 @@ def run_gpu(args):
 
                     def kernel_only():
                         native.reduce_rows_peers(ctx, shard_in[0], peer.bases(span.begin), m)
+
+                    def compute_only():  # the same kernel writing this rank's copy alone
+                        native.reduce_rows_peers(ctx, shard_in[0],
+                                                 peer.bases(span.begin)[rank:rank + 1], m)
                 else:
                     n_cols = full_outs[0].shape[1]
                     peer = PeerOutput(tuple(full_outs[0].shape), full_outs[0].dtype, dev)
@@ -881,10 +885,20 @@ def run_gpu(args):
                         def kernel_only():
                             native.softmax_rows_peers(ctx, shard_in[0],
                                                       peer.bases(span.begin * n_cols), n_cols)
+
+                        def compute_only():  # the same kernel writing this rank's copy alone
+                            native.softmax_rows_peers(
+                                ctx, shard_in[0],
+                                peer.bases(span.begin * n_cols)[rank:rank + 1], n_cols)
                     else:
                         def kernel_only():
                             native.gemm_bf16_peers(ctx, shard_in[0], shard_in[1],
                                                    peer.bases(span.begin * n_cols), n_cols)
+
+                        def compute_only():
+                            native.gemm_bf16_peers(
+                                ctx, shard_in[0], shard_in[1],
+                                peer.bases(span.begin * n_cols)[rank:rank + 1], n_cols)
 
                 def step(do_compute=True, do_gather=True):
                     if do_compute:
@@ -1008,6 +1022,12 @@ def run_gpu(args):
                       "gather_gbs_in_per_rank": gathered / (k_ms if fused else g_ms) / 1e6,
                       "nvlink_gbs_per_direction": {"nominal": 900, "measured_peer_copy": 770},
                       "fused": bool(fused), "collective": collective}
+            if fused and mode == "rows":
+                # The kernel phase above includes the stores into the other GPUs; the
+                # same kernel writing only this GPU's copy shows how the compute scales.
+                c_ms, _ = timed(compute_only, steps, 2)
+                phases["compute_only_ms"] = c_ms / steps
+                phases["compute_speedup"] = one_ms / (c_ms / steps)
             # The roofline is the kernel's: this GPU's share of the problem in the
             # time its kernels take when nothing else runs.
             roof = roofline(name, k_ms, 1.0 / world)[1]
