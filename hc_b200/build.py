@@ -117,8 +117,8 @@ def build_cubins(verbose=False, force=False):
 
 # Kernel sources embedded as text: what a run-time specialisation compiles
 # (csrc/launch/specialise.cpp).
-EMBEDDED_SOURCES = ["map_fused.cu", "row_fused.cu", "fused_machine.cuh", "map_machine.cuh",
-                    "map_params.h"]
+EMBEDDED_SOURCES = ["map_fused.cu", "row_fused.cu", "work_items.cu", "fused_machine.cuh",
+                    "map_machine.cuh", "map_params.h", "items_params.h"]
 
 
 def _write_images_asm(cubins, path: Path):

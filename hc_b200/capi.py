@@ -172,6 +172,10 @@ KERNELS_PROTOTYPES = {
         _ll, [C.POINTER(HcMapProgram), C.c_int, C.c_int, C.c_int, C.c_int, _vp, _sz, C.c_char_p,
               _sz]
     ),
+    "hcSpecialiseCompileItems": (
+        _ll, [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int, C.c_int, _vp, _sz, C.c_char_p,
+              _sz]
+    ),
     "hcSelfTestWaitTimeout": (
         C.c_int,
         [_vp, C.c_ulonglong, C.POINTER(C.c_int), C.POINTER(C.c_ulonglong), C.POINTER(C.c_int)],
@@ -286,6 +290,24 @@ def specialise_compile(program, row_program=False, dtype=HC_F32, cc=(10, 0)):
     image = C.create_string_buffer(size)
     size = lib.hcSpecialiseCompile(C.byref(program), int(row_program), dtype, cc[0], cc[1], image,
                                    size, message, len(message))
+    if size < 0:
+        raise RuntimeError(message.value.decode(errors="replace"))
+    return image.raw[:size], message.value.decode()
+
+
+def specialise_compile_items(code, dtype=HC_F32, cc=(10, 0)):
+    """hcSpecialiseCompileItems: the device image of a work-item program given by its
+    instruction words - no GPU needed.  Returns ``(image bytes, tag)``."""
+    lib = load_kernels()
+    words = (C.c_uint32 * len(code))(*code)
+    message = C.create_string_buffer(8192)
+    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, cc[0], cc[1], None, 0, message,
+                                        len(message))
+    if size < 0:
+        raise RuntimeError(message.value.decode(errors="replace"))
+    image = C.create_string_buffer(size)
+    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, cc[0], cc[1], image, size,
+                                        message, len(message))
     if size < 0:
         raise RuntimeError(message.value.decode(errors="replace"))
     return image.raw[:size], message.value.decode()

@@ -6,32 +6,38 @@
 // lowering puts group tiles in work-group memory,
 // mlir/lib/Transforms/LowerScope.cpp:246-309).
 //
-// One thread per work-item, one CTA per work-group, exactly the reference's
+// One thread per work-item, a CTA per work-group at a time (a CTA takes the
+// groups blockIdx.x, blockIdx.x + gridDim.x, ... in turn: a group of 256
+// work-items is too little work to pay for a CTA of its own), the reference's
 // execution model; the group's tile lives in shared memory and the barrier is
 // the CTA barrier.  The body arrives as a program for the accumulator machine
 // of map_params.h, interpreted on single values (items_params.h).  A work-item
 // outside a phase's guard (the `if gid < n` of the body) computes nothing in
 // that phase but still takes part in the barrier, as in the reference, where
 // every work-item of a group runs to the barrier.
+//
+// FIXED: the program is a compile-time constant (a type with `n` and `code[n]`,
+// as in fused_programs.h) and the instruction loop is unrolled, so that every
+// decision the interpreter takes per instruction and work-item is taken by the
+// compiler - the form that a run-time specialisation compiles
+// (launch/specialise.cpp).  Same operations in the same order: same results.
 #include "items_params.h"
 #include "map_machine.cuh"
+#ifdef HC_ITEM_FIXED_PROGRAM
+#include "fused_programs.h"
+#endif
 
 namespace {
 
 using namespace hcmap;
 
-template <typename T>
-__device__ __forceinline__ void workItems(const HcItemProgramDev &p) {
-  extern __shared__ __align__(16) unsigned char raw[];
-  T *const tile = reinterpret_cast<T *>(raw);
-  using N = Num<T>;
-  const int localCol = threadIdx.x % p.groupCols, localRow = threadIdx.x / p.groupCols;
-  const int groupsX = int((p.cols + p.groupCols - 1) / p.groupCols);
-  const long long row = (long long)(blockIdx.x / groupsX) * p.groupRows + localRow;
-  const long long col = (long long)(blockIdx.x % groupsX) * p.groupCols + localCol;
-  tile[threadIdx.x] = T(p.tileFill);
-  __syncthreads();
+struct Interpreted {}; // the program is read from the parameter block
 
+template <typename T, typename P>
+__device__ __forceinline__ void workGroup(const HcItemProgramDev &p, T *tile, int localRow,
+                                          int localCol, long long row, long long col) {
+  using N = Num<T>;
+  constexpr bool fixed = !std::is_same<P, Interpreted>::value;
   int phase = 0;
   auto inside = [&]() {
     return row >= p.guardLo[phase][0] && row < p.guardHi[phase][0] &&
@@ -39,8 +45,19 @@ __device__ __forceinline__ void workItems(const HcItemProgramDev &p) {
   };
   bool active = inside();
   T acc = T(0), temps[3] = {T(0), T(0), T(0)};
-  for (int pc = 0; pc < p.nInstr; ++pc) {
-    const uint32_t ins = p.code[pc], op = ins & 0xffu, src = (ins >> 8) & 0xffu;
+  int count;
+  if constexpr (fixed)
+    count = P::n;
+  else
+    count = p.nInstr;
+#pragma unroll
+  for (int pc = 0; pc < count; ++pc) {
+    uint32_t ins;
+    if constexpr (fixed)
+      ins = P::code[pc];
+    else
+      ins = p.code[pc];
+    const uint32_t op = ins & 0xffu, src = (ins >> 8) & 0xffu;
     if (op == HC_ITEM_BARRIER) {
       __syncthreads(); // uniform: every thread of the CTA runs the same instructions
       phase = 1;
@@ -127,13 +144,49 @@ __device__ __forceinline__ void workItems(const HcItemProgramDev &p) {
   }
 }
 
+template <typename T, typename P>
+__device__ __forceinline__ void workItems(const HcItemProgramDev &p) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  T *const tile = reinterpret_cast<T *>(raw);
+  const int localCol = threadIdx.x % p.groupCols, localRow = threadIdx.x / p.groupCols;
+  const long long groupsX = (p.cols + p.groupCols - 1) / p.groupCols;
+  const long long groups = groupsX * ((p.rows + p.groupRows - 1) / p.groupRows);
+  for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
+    const long long row = (g / groupsX) * p.groupRows + localRow;
+    const long long col = (g % groupsX) * p.groupCols + localCol;
+    tile[threadIdx.x] = T(p.tileFill);
+    __syncthreads();
+    workGroup<T, P>(p, tile, localRow, localCol, row, col);
+    __syncthreads(); // the tile belongs to the next group from here on
+  }
+}
+
 } // namespace
 
+#ifndef HC_ITEM_FIXED_PROGRAM
 extern "C" __global__ void __launch_bounds__(1024)
     hc_work_items_f32(const __grid_constant__ HcItemProgramDev p) {
-  workItems<float>(p);
+  workItems<float, Interpreted>(p);
 }
 extern "C" __global__ void __launch_bounds__(1024)
     hc_work_items_f64(const __grid_constant__ HcItemProgramDev p) {
-  workItems<double>(p);
+  workItems<double, Interpreted>(p);
 }
+#else
+// One program, one element type (HC_FUSED_ONLY: 0 float32, 1 float64), named by
+// the list macro of the generated header.
+#if HC_FUSED_ONLY == 0
+#define HC_ITEM_FIXED(body)                                                              \
+  extern "C" __global__ void __launch_bounds__(1024)                                     \
+      hc_work_items_fused_##body##_f32(const __grid_constant__ HcItemProgramDev p) {     \
+    workItems<float, hcfused::item_##body>(p);                                           \
+  }
+#else
+#define HC_ITEM_FIXED(body)                                                              \
+  extern "C" __global__ void __launch_bounds__(1024)                                     \
+      hc_work_items_fused_##body##_f64(const __grid_constant__ HcItemProgramDev p) {     \
+    workItems<double, hcfused::item_##body>(p);                                          \
+  }
+#endif
+HC_FUSED_ITEM_LIST(HC_ITEM_FIXED)
+#endif

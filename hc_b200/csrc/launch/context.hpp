@@ -5,6 +5,7 @@
 #include "hc_b200_kernels.h"
 
 #include <cstdarg>
+#include <cstdint>
 #include <cstdio>
 #include <map>
 #include <string>
@@ -80,6 +81,7 @@ void hcReleaseHostPipeline(HcContextImpl *c);
 struct HcMapProgramDev;
 bool hcSpecialisable(const HcMapProgramDev &p, bool row, int dtype);
 const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgramDev &p);
+const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr);
 const char *hcSpecialiserNote(HcContextImpl *c);
 long long hcSpecialiserCount(HcContextImpl *c, int which);
 void hcReleaseSpecialiser(HcContextImpl *c);

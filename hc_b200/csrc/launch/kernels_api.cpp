@@ -917,9 +917,23 @@ int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype) {
   if (groups > 0x7fffffffLL)
     return c->fail("%s: %lld work-groups exceed one launch", who, groups);
   const size_t threads = size_t(p.groupRows) * size_t(p.groupCols);
+  // A CTA takes several work-groups in turn: a few CTAs per SM's worth of threads.
+  const long long resident = std::max<long long>(1, 2048 / (long long)threads);
+  const long long grid = std::min<long long>(groups, c->smCount * resident * 4);
   void *args[] = {&p};
-  return c->launch(dtype == HC_F32 ? "hc_work_items_f32" : "hc_work_items_f64", size_t(groups),
-                   1, 1, threads, args, 1, threads * (dtype == HC_F32 ? 4 : 8));
+  // The program compiled at its first launch, as for element-wise and row programs.
+  char name[64];
+  std::snprintf(name, sizeof name, "%s", dtype == HC_F32 ? "hc_work_items_f32" : "hc_work_items_f64");
+  if (c->fusedVariant != 1 && c->specialiseMode != 0) {
+    const char *tag = hcSpecialiseItems(c, dtype, p.code, p.nInstr);
+    if (tag)
+      std::snprintf(name, sizeof name, "hc_work_items_fused_%s_%s", tag,
+                    dtype == HC_F32 ? "f32" : "f64");
+    else if (c->specialiseMode == 2)
+      return c->fail("%s: the program could not be compiled: %s", who, hcSpecialiserNote(c));
+  }
+  return c->launch(name, size_t(grid), 1, 1, threads, args, 1,
+                   threads * (dtype == HC_F32 ? 4 : 8));
 }
 
 // ---- softmax --------------------------------------------------------------------

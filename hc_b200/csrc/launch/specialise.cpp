@@ -20,6 +20,7 @@
 // With the directory named by HC_B200_KERNEL_CACHE the compiled images are also
 // kept on disk, under a hash of everything that went into them.
 #include "context.hpp"
+#include "../kernels/items_params.h"
 
 #include "../kernels/map_params.h"
 
@@ -120,6 +121,8 @@ const char kTypeTraits[] =
     "template <> struct make_unsigned<int> { using type = unsigned int; };\n"
     "template <> struct make_unsigned<long> { using type = unsigned long; };\n"
     "template <> struct make_unsigned<long long> { using type = unsigned long long; };\n"
+    "template <typename A, typename B> struct is_same { static constexpr bool value = false; };\n"
+    "template <typename A> struct is_same<A, A> { static constexpr bool value = true; };\n"
     "}\n";
 
 const HcSourceText *embedded(const char *name) {
@@ -193,11 +196,22 @@ int typeIndex(int dtype) {
 }
 const char *const kTypeNames[] = {"f32", "f64", "i32", "i64"};
 
-std::string programKey(bool row, int dtype, const HcMapProgramDev &p) {
-  std::string key(row ? "r" : "m");
+// What is compiled: an element-wise program, a row program, a work-item program.
+enum Kind { kMap = 0, kRow = 1, kItem = 2 };
+struct KindText {
+  const char *name;     // part of the kernel and structure names
+  const char *source;   // the embedded translation unit
+  const char *listName; // the list macro of the generated header
+};
+const KindText kKinds[] = {{"map", "map_fused.cu", "MAP"},
+                           {"row", "row_fused.cu", "ROW"},
+                           {"item", "work_items.cu", "ITEM"}};
+
+std::string programKey(Kind kind, int dtype, int nInputs, const uint32_t *code, int nInstr) {
+  std::string key(kKinds[kind].name);
   key += kTypeNames[typeIndex(dtype)];
-  key += char('0' + p.nInputs);
-  key.append(reinterpret_cast<const char *>(p.code), size_t(p.nInstr) * sizeof(uint32_t));
+  key += char('0' + nInputs);
+  key.append(reinterpret_cast<const char *>(code), size_t(nInstr) * sizeof(uint32_t));
   return key;
 }
 
@@ -205,17 +219,18 @@ std::string programKey(bool row, int dtype, const HcMapProgramDev &p) {
 // major.minor, from the directory of HC_B200_KERNEL_CACHE or from NVRTC.  `tag`
 // is the part of the kernel names that stands for the program.  False, with the
 // reason in `why`, when there is no way to get one.
-bool buildImage(bool row, int dtype, const HcMapProgramDev &p, long long ccMajor,
-                long long ccMinor, std::string &image, std::string &tag, bool &fromDisk,
-                std::string &why) {
-  const char *kind = row ? "row" : "map";
-  const HcSourceText *main = embedded(row ? "row_fused.cu" : "map_fused.cu");
-  const char *headerNames[] = {"fused_machine.cuh", "map_machine.cuh", "map_params.h"};
+bool buildImage(Kind what, int dtype, int nInputs, const uint32_t *code, int nInstr,
+                long long ccMajor, long long ccMinor, std::string &image, std::string &tag,
+                bool &fromDisk, std::string &why) {
+  const char *kind = kKinds[what].name;
+  const HcSourceText *main = embedded(kKinds[what].source);
+  const char *headerNames[] = {"fused_machine.cuh", "map_machine.cuh", "map_params.h",
+                               "items_params.h"};
   if (!main) {
     why = "the kernel sources are not embedded in this library";
     return false;
   }
-  const std::string key = programKey(row, dtype, p);
+  const std::string key = programKey(what, dtype, nInputs, code, nInstr);
   char tagText[32];
   std::snprintf(tagText, sizeof tagText, "j%016" PRIx64,
                 fnv1a(0xcbf29ce484222325ull, key.data(), key.size()));
@@ -224,12 +239,12 @@ bool buildImage(bool row, int dtype, const HcMapProgramDev &p, long long ccMajor
   // The program as the header the kernel source includes.
   std::ostringstream programs;
   programs << "#pragma once\n#include <stdint.h>\nnamespace hcfused {\nstruct " << kind << "_" << tag
-           << " {\n  static constexpr int nin = " << p.nInputs << ", n = " << p.nInstr
-           << ";\n  static constexpr uint32_t code[" << p.nInstr << "] = {";
-  for (int pc = 0; pc < p.nInstr; ++pc)
-    programs << (pc ? ", " : "") << p.code[pc] << "u";
-  programs << "};\n};\n}\n#define HC_FUSED_" << (row ? "ROW" : "MAP") << "_LIST(X) X(" << tag
-           << ")\n#define HC_FUSED_ONLY " << typeIndex(dtype) << "\n";
+           << " {\n  static constexpr int nin = " << nInputs << ", n = " << nInstr
+           << ";\n  static constexpr uint32_t code[" << nInstr << "] = {";
+  for (int pc = 0; pc < nInstr; ++pc)
+    programs << (pc ? ", " : "") << code[pc] << "u";
+  programs << "};\n};\n}\n#define HC_FUSED_" << kKinds[what].listName << "_LIST(X) X(" << tag
+           << ")\n";
 
   std::vector<std::string> texts = {programs.str(), kStdint, kMath, kTypeTraits};
   std::vector<const char *> names = {"fused_programs.h", "stdint.h", "math.h", "type_traits"};
@@ -247,7 +262,13 @@ bool buildImage(bool row, int dtype, const HcMapProgramDev &p, long long ccMajor
   // The arch-specific suffix exists from sm_90a on.
   std::snprintf(arch, sizeof arch, "--gpu-architecture=sm_%lld%lld%s", ccMajor, ccMinor,
                 ccMajor >= 9 ? "a" : "");
-  const char *options[] = {arch, "--std=c++17", "-lineinfo"};
+  // One element type per image; the work-item source compiles its fixed-program
+  // form when told so.
+  char only[32];
+  std::snprintf(only, sizeof only, "-DHC_FUSED_ONLY=%d", typeIndex(dtype));
+  const char *options[] = {arch, "--std=c++17", "-lineinfo", only,
+                           what == kItem ? "-DHC_ITEM_FIXED_PROGRAM=1" : "-DHC_UNUSED=1"};
+  const int optionCount = 5;
 
   // On disk, under a hash of all the text and the options.
   std::string cachePath;
@@ -281,13 +302,13 @@ bool buildImage(bool row, int dtype, const HcMapProgramDev &p, long long ccMajor
   for (const std::string &t : texts)
     headerTexts.push_back(t.c_str());
   Nvrtc::Program prog = nullptr;
-  int rc = rtc.createProgram(&prog, mainText.c_str(), row ? "row_fused.cu" : "map_fused.cu",
-                             int(names.size()), headerTexts.data(), names.data());
+  int rc = rtc.createProgram(&prog, mainText.c_str(), kKinds[what].source, int(names.size()),
+                             headerTexts.data(), names.data());
   if (rc != 0) {
     why = std::string("nvrtcCreateProgram: ") + rtc.getErrorString(rc);
     return false;
   }
-  rc = rtc.compileProgram(prog, 3, options);
+  rc = rtc.compileProgram(prog, optionCount, options);
   if (rc != 0) {
     size_t n = 0;
     rtc.getProgramLogSize(prog, &n);
@@ -327,7 +348,8 @@ const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgr
   if (!c->specialiser)
     c->specialiser = new HcSpecialiser;
   HcSpecialiser &s = *c->specialiser;
-  const std::string key = programKey(row, dtype, p);
+  const Kind what = row ? kRow : kMap;
+  const std::string key = programKey(what, dtype, p.nInputs, p.code, p.nInstr);
   auto found = s.entries.find(key);
   if (found != s.entries.end())
     return found->second.failed ? nullptr : found->second.tag.c_str();
@@ -335,7 +357,8 @@ const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgr
   entry.failed = true; // until the kernels are there
   std::string image, tag;
   bool fromDisk = false;
-  if (!buildImage(row, dtype, p, c->ccMajor, c->ccMinor, image, tag, fromDisk, s.note))
+  if (!buildImage(what, dtype, p.nInputs, p.code, p.nInstr, c->ccMajor, c->ccMinor, image, tag,
+                  fromDisk, s.note))
     return nullptr;
   OlModule module = olCreateModule(c->device, image.data(), image.size());
   if (!module) {
@@ -370,6 +393,45 @@ const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgr
   return entry.tag.c_str();
 }
 
+// The same for a work-item program (hcWorkItems): the tag of the kernel
+// hc_work_items_fused_<tag>_{f32,f64}, or nullptr.
+const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr) {
+  if (!c->specialiser)
+    c->specialiser = new HcSpecialiser;
+  HcSpecialiser &s = *c->specialiser;
+  const std::string key = programKey(kItem, dtype, 0, code, nInstr);
+  auto found = s.entries.find(key);
+  if (found != s.entries.end())
+    return found->second.failed ? nullptr : found->second.tag.c_str();
+  HcSpecialiser::Entry &entry = s.entries[key];
+  entry.failed = true;
+  std::string image, tag;
+  bool fromDisk = false;
+  if (!buildImage(kItem, dtype, 0, code, nInstr, c->ccMajor, c->ccMinor, image, tag, fromDisk,
+                  s.note))
+    return nullptr;
+  OlModule module = olCreateModule(c->device, image.data(), image.size());
+  if (!module) {
+    s.note = "olCreateModule failed for a specialised image: " + c->lastError;
+    return nullptr;
+  }
+  char name[96];
+  std::snprintf(name, sizeof name, "hc_work_items_fused_%s_%s", tag.c_str(),
+                kTypeNames[typeIndex(dtype)]);
+  OlKernel k = olGetKernel(module, name);
+  if (!k) {
+    olReleaseModule(module);
+    s.note = std::string("a specialised image lacks ") + name + ": " + c->lastError;
+    return nullptr;
+  }
+  c->kernels[name] = k;
+  entry.tag = tag;
+  entry.module = module;
+  entry.failed = false;
+  ++(fromDisk ? s.fromDisk : s.compiled);
+  return entry.tag.c_str();
+}
+
 // Compiles without a context or a GPU: the image for compute capability
 // major.minor, copied to `image` as far as `capacity` allows.
 extern "C" HC_B200_API long long hcSpecialiseCompile(const HcMapProgram *program, int rowProgram,
@@ -393,7 +455,33 @@ extern "C" HC_B200_API long long hcSpecialiseCompile(const HcMapProgram *program
                "row programs of the operations up to `set` on float32 or float64");
   std::string bytes, tag, why;
   bool fromDisk = false;
-  if (!buildImage(rowProgram != 0, dtype, p, ccMajor, ccMinor, bytes, tag, fromDisk, why))
+  if (!buildImage(rowProgram != 0 ? kRow : kMap, dtype, p.nInputs, p.code, p.nInstr, ccMajor,
+                  ccMinor, bytes, tag, fromDisk, why))
+    return say(why);
+  if (image && capacity)
+    std::memcpy(image, bytes.data(), std::min(capacity, bytes.size()));
+  say(tag);
+  return (long long)bytes.size();
+}
+
+// The same for a work-item program: `code` holds nInstr instruction words of
+// hcWorkItems' program; dtype HC_F32 or HC_F64.
+extern "C" HC_B200_API long long hcSpecialiseCompileItems(const unsigned *code, int nInstr,
+                                                          int dtype, int ccMajor, int ccMinor,
+                                                          void *image, size_t capacity,
+                                                          char *message, size_t messageCapacity) {
+  auto say = [&](const std::string &text) {
+    if (message && messageCapacity)
+      std::snprintf(message, messageCapacity, "%s", text.c_str());
+    return -1ll;
+  };
+  if (!code || nInstr < 1 || nInstr > HC_ITEM_MAX_INSTR)
+    return say("hcSpecialiseCompileItems: the program has no valid size");
+  if (dtype != HC_F32 && dtype != HC_F64)
+    return say("hcSpecialiseCompileItems: work-item programs run on float32 or float64");
+  std::string bytes, tag, why;
+  bool fromDisk = false;
+  if (!buildImage(kItem, dtype, 0, code, nInstr, ccMajor, ccMinor, bytes, tag, fromDisk, why))
     return say(why);
   if (image && capacity)
     std::memcpy(image, bytes.data(), std::min(capacity, bytes.size()));

@@ -252,6 +252,15 @@ typedef struct HcItemProgram {
 } HcItemProgram;
 HC_B200_API int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype);
 
+/* hcSpecialiseCompile for a work-item program: `code` holds the nInstr
+ * instruction words of an HcItemProgram, dtype HC_F32 or HC_F64; the kernel of
+ * the image is hc_work_items_fused_<tag>_f32 or _f64.  hcWorkItems compiles its
+ * program the same way at the first launch, under the option `specialise`. */
+HC_B200_API long long hcSpecialiseCompileItems(const unsigned *code, int nInstr, int dtype,
+                                               int ccMajor, int ccMinor, void *image,
+                                               size_t capacity, char *message,
+                                               size_t messageCapacity);
+
 /* Row softmax over the last axis, HC_F32 or HC_F64
  * (python/hckernel/tests/test_examples.py:304-321). */
 HC_B200_API int hcSoftmaxRows(HcContext c, const void *x, void *y,

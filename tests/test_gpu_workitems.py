@@ -19,6 +19,7 @@ from hc_b200 import capi
 from hc_b200.hckernel import elementwise as ew
 from hc_b200.hckernel import workitems as wi
 from hc_b200.hckernel.kernel import *  # noqa: F401,F403
+from hc_b200.hckernel.kernel import get_context
 from oracle import workitems as oracle_items
 from tests.gpu_util import finish
 
@@ -118,3 +119,31 @@ def test_work_items_entry_point_refuses_bad_programs(hc):
     with pytest.raises(capi.HcError, match="unsupported dtype"):
         hc.work_items(program(copy), capi.HC_I32)
     finish(hc)
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if "pairwise" not in c["name"]],
+                         ids=lambda c: c["name"])
+def test_compiled_work_item_programs_equal_the_interpreter(case):
+    """hcWorkItems compiles its program with NVRTC at the first launch (option
+    `specialise`; 2 = refuse instead of interpreting); the straight-line kernel
+    writes bit for bit what the interpreting kernel writes (option `fused` = 1)."""
+    ctx = get_context("cuda:0")
+    shape, _ = case["out"]
+    k = case["make"](NS)
+    d_in = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in case["inputs"]]
+    outs = []
+    for interpret in (True, False):
+        d_out = torch.full(shape, -77, dtype=d_in[0].dtype, device="cuda")
+        ctx.set_option("fused", int(interpret))
+        ctx.set_option("specialise", 2)
+        before = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
+        try:
+            k(*d_in, d_out)
+        finally:
+            ctx.set_option("fused", 0)
+            ctx.set_option("specialise", 1)
+        torch.cuda.synchronize()
+        after = ctx.specialised_programs() + ctx.specialised_programs(from_disk=True)
+        assert after - before == 0 if interpret else after - before in (0, 1), ctx.specialise_note
+        outs.append(d_out.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1], equal_nan=True)

@@ -186,3 +186,26 @@ def test_what_a_work_item_function_may_not_do():
     plan = build(rotate).plan_for(arrays)
     assert plan.family == "work_items" and plan.roles["tiles"] == [(0, 0, 0, 1, 3, 8)]
     assert plan.roles["group"] == (1, 8) and plan.roles["guards"] == [(0, 1, 0, 20), (0, 1, 0, 20)]
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if "pairwise" not in c["name"]],
+                         ids=lambda c: c["name"])
+def test_work_item_programs_compile_to_device_images(case):
+    """hcWorkItems' program as straight-line code: NVRTC makes an sm_100a image of
+    the recorded program without a GPU, one element type per image."""
+    from hc_b200 import capi
+
+    shape, dtype = case["out"]
+    k = case["make"](NS)
+    plan = k.plan_for(tuple(F(a.shape, a.dtype) for a in case["inputs"]) + (F(shape, dtype),))
+    code = [int(w) for w in plan.roles["code"]]
+    hc_dtype = capi.HC_F32 if dtype == np.float32 else capi.HC_F64
+    image, tag = capi.specialise_compile_items(code, dtype=hc_dtype)
+    assert image[:4] == b"\x7fELF"
+    name = "f32" if dtype == np.float32 else "f64"
+    other = "f64" if dtype == np.float32 else "f32"
+    assert f"hc_work_items_fused_{tag}_{name}".encode() in image
+    assert f"hc_work_items_fused_{tag}_{other}".encode() not in image
+    assert capi.specialise_compile_items(code, dtype=hc_dtype)[1] == tag
+    with pytest.raises(RuntimeError, match="valid size"):
+        capi.specialise_compile_items([0] * 49, dtype=hc_dtype)
