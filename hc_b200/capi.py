@@ -173,8 +173,8 @@ KERNELS_PROTOTYPES = {
               _sz]
     ),
     "hcSpecialiseCompileItems": (
-        _ll, [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int, C.c_int, _vp, _sz, C.c_char_p,
-              _sz]
+        _ll, [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _sz,
+              C.c_char_p, _sz]
     ),
     "hcSelfTestWaitTimeout": (
         C.c_int,
@@ -295,19 +295,20 @@ def specialise_compile(program, row_program=False, dtype=HC_F32, cc=(10, 0)):
     return image.raw[:size], message.value.decode()
 
 
-def specialise_compile_items(code, dtype=HC_F32, cc=(10, 0)):
+def specialise_compile_items(code, dtype=HC_F32, group_threads=256, cc=(10, 0)):
     """hcSpecialiseCompileItems: the device image of a work-item program given by its
-    instruction words - no GPU needed.  Returns ``(image bytes, tag)``."""
+    instruction words, for work-groups of ``group_threads`` work-items - no GPU
+    needed.  Returns ``(image bytes, tag)``."""
     lib = load_kernels()
     words = (C.c_uint32 * len(code))(*code)
     message = C.create_string_buffer(8192)
-    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, cc[0], cc[1], None, 0, message,
-                                        len(message))
+    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, group_threads, cc[0], cc[1],
+                                        None, 0, message, len(message))
     if size < 0:
         raise RuntimeError(message.value.decode(errors="replace"))
     image = C.create_string_buffer(size)
-    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, cc[0], cc[1], image, size,
-                                        message, len(message))
+    size = lib.hcSpecialiseCompileItems(words, len(code), dtype, group_threads, cc[0], cc[1],
+                                        image, size, message, len(message))
     if size < 0:
         raise RuntimeError(message.value.decode(errors="replace"))
     return image.raw[:size], message.value.decode()

@@ -18,6 +18,12 @@ enum HcItemOp : uint32_t {
 constexpr uint32_t HC_ITEM_SRC_LOCAL_ROW = 18, HC_ITEM_SRC_LOCAL_COL = 19;
 constexpr uint32_t HC_ITEM_SRC_TILE = 24;
 constexpr int HC_ITEM_MAX_INSTR = 48, HC_ITEM_MAX_TILE_READS = 4, HC_ITEM_MAX_PHASES = 2;
+// A CTA works on several consecutive work-groups at a time (one pass): a kernel
+// compiled for work-groups of up to HC_ITEM_WIDE_THREADS work-items takes
+// HC_ITEM_WIDE_BYTES / element size of them, every other kernel
+// HC_ITEM_NARROW_GROUPS.  The launch gives the kernel one tile per group of a
+// pass in shared memory.
+constexpr int HC_ITEM_WIDE_THREADS = 256, HC_ITEM_WIDE_BYTES = 32, HC_ITEM_NARROW_GROUPS = 2;
 
 struct HcItemProgramDev {
   const void *in[HC_MAP_MAX_INPUTS]; // read at (row + inRow[k], col + inCol[k])
@@ -38,4 +44,9 @@ struct HcItemProgramDev {
   int32_t tileScale[HC_ITEM_MAX_TILE_READS][2], tileOffset[HC_ITEM_MAX_TILE_READS][2],
       tileMod[HC_ITEM_MAX_TILE_READS][2];
   double tileFill; // what the group's tile holds before anything is stored to it
+  // Filled by the launch, not by the caller.  The grid of work-groups, and the
+  // groups all of whose work-items pass the guards of every phase of the program:
+  // insideLo[a] <= group coordinate[a] < insideHi[a] ([0] rows, [1] columns).
+  uint32_t groupsY, groupsX;
+  uint32_t insideLo[2], insideHi[2];
 };

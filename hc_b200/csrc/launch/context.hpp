@@ -81,7 +81,8 @@ void hcReleaseHostPipeline(HcContextImpl *c);
 struct HcMapProgramDev;
 bool hcSpecialisable(const HcMapProgramDev &p, bool row, int dtype);
 const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgramDev &p);
-const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr);
+const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr,
+                              bool wide);
 const char *hcSpecialiserNote(HcContextImpl *c);
 long long hcSpecialiserCount(HcContextImpl *c, int which);
 void hcReleaseSpecialiser(HcContextImpl *c);

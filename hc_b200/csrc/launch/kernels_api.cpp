@@ -801,7 +801,7 @@ int hcRowProgram(HcContext c, const HcMapProgram *program, int dtype) {
 }
 
 // ---- work-item programs ---------------------------------------------------------------
-static_assert(sizeof(HcItemProgram) == sizeof(HcItemProgramDev) &&
+static_assert(sizeof(HcItemProgram) == offsetof(HcItemProgramDev, groupsY) &&
                   offsetof(HcItemProgram, out) == offsetof(HcItemProgramDev, out) &&
                   offsetof(HcItemProgram, groupRows) == offsetof(HcItemProgramDev, groupRows) &&
                   offsetof(HcItemProgram, code) == offsetof(HcItemProgramDev, code) &&
@@ -818,8 +818,8 @@ int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype) {
     return c->fail("%s: unsupported dtype %d", who, dtype);
   if (!program)
     return c->fail("%s: null program", who);
-  HcItemProgramDev p;
-  std::memcpy(&p, program, sizeof p);
+  HcItemProgramDev p = {};
+  std::memcpy(&p, program, sizeof *program);
   if (p.nInputs < 0 || p.nInputs > HC_MAP_MAX_INPUTS || p.nInstr < 1 ||
       p.nInstr > HC_ITEM_MAX_INSTR)
     return c->fail("%s: %d inputs, %d instructions (at most %d and 1..%d)", who, p.nInputs,
@@ -917,23 +917,48 @@ int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype) {
   if (groups > 0x7fffffffLL)
     return c->fail("%s: %lld work-groups exceed one launch", who, groups);
   const size_t threads = size_t(p.groupRows) * size_t(p.groupCols);
-  // A CTA takes several work-groups in turn: a few CTAs per SM's worth of threads.
-  const long long resident = std::max<long long>(1, 2048 / (long long)threads);
-  const long long grid = std::min<long long>(groups, c->smCount * resident * 4);
+  // The groups that lie inside the guards of every phase the program has: the
+  // kernel runs them without evaluating a guard.
+  p.groupsY = uint32_t(ceilDiv(p.rows, p.groupRows));
+  p.groupsX = uint32_t(ceilDiv(p.cols, p.groupCols));
+  {
+    const long long extent[2] = {p.groupRows, p.groupCols};
+    long long lo[2] = {0, 0}, hi[2] = {(long long)p.groupsY, (long long)p.groupsX};
+    for (int ph = 0; ph <= phase; ++ph)
+      for (int a = 0; a < 2; ++a) {
+        lo[a] = std::max(lo[a], ceilDiv(p.guardLo[ph][a], extent[a]));
+        hi[a] = std::min(hi[a], std::max<long long>(p.guardHi[ph][a], 0) / extent[a]);
+      }
+    for (int a = 0; a < 2; ++a) {
+      p.insideLo[a] = uint32_t(lo[a]);
+      p.insideHi[a] = uint32_t(std::max(hi[a], lo[a]));
+    }
+  }
   void *args[] = {&p};
   // The program compiled at its first launch, as for element-wise and row programs.
+  const int elemSize = dtype == HC_F32 ? 4 : 8;
+  const bool wide = threads <= size_t(HC_ITEM_WIDE_THREADS);
+  int perPass = HC_ITEM_NARROW_GROUPS;
   char name[64];
   std::snprintf(name, sizeof name, "%s", dtype == HC_F32 ? "hc_work_items_f32" : "hc_work_items_f64");
   if (c->fusedVariant != 1 && c->specialiseMode != 0) {
-    const char *tag = hcSpecialiseItems(c, dtype, p.code, p.nInstr);
-    if (tag)
+    const char *tag = hcSpecialiseItems(c, dtype, p.code, p.nInstr, wide);
+    if (tag) {
       std::snprintf(name, sizeof name, "hc_work_items_fused_%s_%s", tag,
                     dtype == HC_F32 ? "f32" : "f64");
-    else if (c->specialiseMode == 2)
+      if (wide)
+        perPass = HC_ITEM_WIDE_BYTES / elemSize;
+    } else if (c->specialiseMode == 2) {
       return c->fail("%s: the program could not be compiled: %s", who, hcSpecialiserNote(c));
+    }
   }
+  // A CTA takes `perPass` work-groups at a time and several such passes in turn:
+  // a few CTAs per SM's worth of threads.
+  const long long passes = ceilDiv(groups, (long long)perPass);
+  const long long resident = std::max<long long>(1, 2048 / (long long)threads);
+  const long long grid = std::min<long long>(passes, c->smCount * resident * 4);
   return c->launch(name, size_t(grid), 1, 1, threads, args, 1,
-                   threads * (dtype == HC_F32 ? 4 : 8));
+                   threads * size_t(perPass) * size_t(elemSize));
 }
 
 // ---- softmax --------------------------------------------------------------------

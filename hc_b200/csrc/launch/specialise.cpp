@@ -263,12 +263,14 @@ bool buildImage(Kind what, int dtype, int nInputs, const uint32_t *code, int nIn
   std::snprintf(arch, sizeof arch, "--gpu-architecture=sm_%lld%lld%s", ccMajor, ccMinor,
                 ccMajor >= 9 ? "a" : "");
   // One element type per image; the work-item source compiles its fixed-program
-  // form when told so.
+  // form when told so, for one class of work-group sizes (nInputs: 1 = the wide
+  // form for small groups).
   char only[32];
   std::snprintf(only, sizeof only, "-DHC_FUSED_ONLY=%d", typeIndex(dtype));
   const char *options[] = {arch, "--std=c++17", "-lineinfo", only,
-                           what == kItem ? "-DHC_ITEM_FIXED_PROGRAM=1" : "-DHC_UNUSED=1"};
-  const int optionCount = 5;
+                           what == kItem ? "-DHC_ITEM_FIXED_PROGRAM=1" : "-DHC_UNUSED=1",
+                           what == kItem && nInputs == 1 ? "-DHC_ITEM_WIDE=1" : "-DHC_UNUSED2=1"};
+  const int optionCount = 6;
 
   // On disk, under a hash of all the text and the options.
   std::string cachePath;
@@ -395,11 +397,12 @@ const char *hcSpecialise(HcContextImpl *c, bool row, int dtype, const HcMapProgr
 
 // The same for a work-item program (hcWorkItems): the tag of the kernel
 // hc_work_items_fused_<tag>_{f32,f64}, or nullptr.
-const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr) {
+const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code, int nInstr,
+                              bool wide) {
   if (!c->specialiser)
     c->specialiser = new HcSpecialiser;
   HcSpecialiser &s = *c->specialiser;
-  const std::string key = programKey(kItem, dtype, 0, code, nInstr);
+  const std::string key = programKey(kItem, dtype, wide ? 1 : 0, code, nInstr);
   auto found = s.entries.find(key);
   if (found != s.entries.end())
     return found->second.failed ? nullptr : found->second.tag.c_str();
@@ -407,8 +410,8 @@ const char *hcSpecialiseItems(HcContextImpl *c, int dtype, const uint32_t *code,
   entry.failed = true;
   std::string image, tag;
   bool fromDisk = false;
-  if (!buildImage(kItem, dtype, 0, code, nInstr, c->ccMajor, c->ccMinor, image, tag, fromDisk,
-                  s.note))
+  if (!buildImage(kItem, dtype, wide ? 1 : 0, code, nInstr, c->ccMajor, c->ccMinor, image, tag,
+                  fromDisk, s.note))
     return nullptr;
   OlModule module = olCreateModule(c->device, image.data(), image.size());
   if (!module) {
@@ -465,9 +468,11 @@ extern "C" HC_B200_API long long hcSpecialiseCompile(const HcMapProgram *program
 }
 
 // The same for a work-item program: `code` holds nInstr instruction words of
-// hcWorkItems' program; dtype HC_F32 or HC_F64.
+// hcWorkItems' program; dtype HC_F32 or HC_F64; groupThreads the work-group size
+// the kernel is to serve (one kernel up to HC_ITEM_WIDE_THREADS, another beyond).
 extern "C" HC_B200_API long long hcSpecialiseCompileItems(const unsigned *code, int nInstr,
-                                                          int dtype, int ccMajor, int ccMinor,
+                                                          int dtype, int groupThreads,
+                                                          int ccMajor, int ccMinor,
                                                           void *image, size_t capacity,
                                                           char *message, size_t messageCapacity) {
   auto say = [&](const std::string &text) {
@@ -479,9 +484,12 @@ extern "C" HC_B200_API long long hcSpecialiseCompileItems(const unsigned *code, 
     return say("hcSpecialiseCompileItems: the program has no valid size");
   if (dtype != HC_F32 && dtype != HC_F64)
     return say("hcSpecialiseCompileItems: work-item programs run on float32 or float64");
+  if (groupThreads < 1 || groupThreads > 1024)
+    return say("hcSpecialiseCompileItems: work-groups have 1 to 1024 work-items");
   std::string bytes, tag, why;
   bool fromDisk = false;
-  if (!buildImage(kItem, dtype, 0, code, nInstr, ccMajor, ccMinor, bytes, tag, fromDisk, why))
+  if (!buildImage(kItem, dtype, groupThreads <= HC_ITEM_WIDE_THREADS ? 1 : 0, code, nInstr,
+                  ccMajor, ccMinor, bytes, tag, fromDisk, why))
     return say(why);
   if (image && capacity)
     std::memcpy(image, bytes.data(), std::min(capacity, bytes.size()));

@@ -253,11 +253,16 @@ typedef struct HcItemProgram {
 HC_B200_API int hcWorkItems(HcContext c, const HcItemProgram *program, int dtype);
 
 /* hcSpecialiseCompile for a work-item program: `code` holds the nInstr
- * instruction words of an HcItemProgram, dtype HC_F32 or HC_F64; the kernel of
- * the image is hc_work_items_fused_<tag>_f32 or _f64.  hcWorkItems compiles its
- * program the same way at the first launch, under the option `specialise`. */
+ * instruction words of an HcItemProgram, dtype HC_F32 or HC_F64, groupThreads the
+ * work-group size (groupRows * groupCols) the kernel is to serve: work-groups of
+ * up to 256 work-items get a kernel that keeps 32 bytes of loads in flight per
+ * thread, larger ones a kernel within the register budget of 1024 threads.  The
+ * kernel of the image is hc_work_items_fused_<tag>_f32 or _f64.  hcWorkItems
+ * compiles its program the same way at the first launch, under the option
+ * `specialise`. */
 HC_B200_API long long hcSpecialiseCompileItems(const unsigned *code, int nInstr, int dtype,
-                                               int ccMajor, int ccMinor, void *image,
+                                               int groupThreads, int ccMajor, int ccMinor,
+                                               void *image,
                                                size_t capacity, char *message,
                                                size_t messageCapacity);
 
