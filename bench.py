@@ -833,6 +833,36 @@ def run_gpu(args):
             "note": ctx.specialise_note or None}
         return figures
 
+    def work_item_bodies(a, out, steps):
+        """Two bodies written at work-item level on the first input of the
+        element-wise workload, through the @kernel call: one array read, one
+        written, each checked against the same arithmetic in torch (the
+        operations round once each, so equal means bit for bit)."""
+        from hc_b200.workloads import make_work_item_bodies
+
+        bodies = make_work_item_bodies(desc)
+        nbytes = 2 * a.numel() * 4
+        figures = {}
+        for label, call in (("rotate_through_the_group_tile", bodies.rotate),
+                            ("stencil_with_the_right_neighbour", bodies.stencil)):
+            out.fill_(-77.0)
+            t0 = time.perf_counter()
+            call(a, out)
+            torch.cuda.synchronize(dev)
+            first_call_s = time.perf_counter() - t0
+            rows = slice(0, 64)  # sixteen rows of groups
+            if label.startswith("rotate"):
+                tile = (a[rows] + 1.0).view(64, -1, 64)
+                want = (torch.roll(tile, -5, dims=2) * 0.5).reshape(64, -1)
+            else:
+                want = torch.full_like(a[rows], -77.0)
+                want[:, :-1] = a[rows, :-1] + a[rows, 1:] * 0.5
+            equal = bool(torch.equal(out[rows], want))
+            ms, _ = timed(lambda: call(a, out), steps, 3)
+            figures[label] = {"ms_per_step": ms / steps, "gbs": nbytes / (ms / steps) / 1e6,
+                              "first_call_s": first_call_s, "equals_torch_on_64_rows": equal}
+        return figures
+
     # ---- one workload -----------------------------------------------------------------
     def measure(name, steps, warmup, regions=True):
         """Device-resident throughput of one workload; returns a result dict."""
@@ -1070,6 +1100,9 @@ def run_gpu(args):
                        "roofline": roof, "sharding": mode})
         if name in ("rows", "map") and mode == "single" and not args.no_extras:
             result["other_forms"] = other_forms(name, ins, full_outs, single, steps)
+            if name == "map":
+                result["other_forms"]["work_item_bodies"] = work_item_bodies(
+                    ins[0], full_outs[0], steps)
         if name == "conv" and not args.no_extras:
             # The same body as it tiles the problem itself: (images x filters) per output
             # position, every operand element gathered through the index tables.
@@ -1237,7 +1270,7 @@ def run_gpu(args):
             "kernel_status": head["status"], "regions": head["regions"],
             "clocks": sampler.summary(), "e2e": e2e,
         }
-        for key in ("phases", "parity"):
+        for key in ("phases", "parity", "other_forms"):
             if key in head:
                 line[key] = head[key]
         if args.small:
@@ -1251,6 +1284,11 @@ def run_gpu(args):
                                        "total_speedup": round(v["phases"]["total_speedup"], 2)}
                                       if "phases" in v else {})}
                                for k, v in extras.items()}
+            items = extras.get("map", {}).get("other_forms", {}).get("work_item_bodies")
+            if items:
+                line["summary"]["work_items"] = {
+                    k: {"value": round(v["gbs"], 1), "unit": "GB/s",
+                        "frac": round(v["gbs"] / load_peaks()["hbm_gbs"], 3)} for k, v in items.items()}
         if world == 1 and not args.no_cpu_baseline:
             value, dt, what = cpu_sample(name, 1, 3)
             line["cpu_baseline"] = {"value": value, "unit": unit_of(name), "cores": 1,

@@ -164,6 +164,46 @@ def make_rowwise(fn, inputs=1, device="cuda:0"):
     raise ValueError("one or two inputs")
 
 
+def make_work_item_bodies(device="cuda:0"):
+    """Two bodies written at work-item level (python/hckernel/kernel_api.py:395-431),
+    on matrices [W, H] with work-groups of 4 x 64 work-items:
+
+    ``rotate(a, out)``: every work-item puts ``a + 1`` into the group's tile,
+    the group meets at a barrier, and each takes half of the element five
+    columns on (wrapping inside its row of the tile);
+    ``stencil(a, out)``: ``out[i, j] = a[i, j] + a[i, j + 1] / 2`` wherever the
+    neighbour exists."""
+    target = dict(backend="nvvm", device=device)
+    W, H = sym.W, sym.H
+
+    @kernel(work_shape=(W, H), group_shape=(4, 64), **target)
+    def rotate(group: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        tmp = group.zeros(shape=group.shape, dtype=a.dtype)
+
+        @group.workitems
+        def inner(w):
+            (li, lj), (i, j) = w.local_id()[:2], w.global_id()[:2]
+            if i < a.shape[0] and j < a.shape[1]:
+                tmp[li, lj] = a[i, j] + 1.0
+            group.barrier()
+            if i < a.shape[0] and j < a.shape[1]:
+                out[i, j] = tmp.data[li, (lj + 5) % 64] * 0.5
+
+        inner()
+
+    @kernel(work_shape=(W, H), group_shape=(4, 64), **target)
+    def stencil(group: CurrentGroup, a: Buffer[W, H, DT], out: Buffer[W, H, DT]):
+        @group.workitems
+        def inner(w):
+            i, j = w.global_id()[:2]
+            if i < a.shape[0] and j + 1 < a.shape[1]:
+                out[i, j] = a[i, j] + a[i, j + 1] * 0.5
+
+        inner()
+
+    return types.SimpleNamespace(rotate=rotate, stencil=stencil)
+
+
 def make_conv(stride=1, device="cuda:0"):
     """The convolution written as an implicit GEMM, as in the reference's
     example (python/hckernel/tests/test_examples.py:203-252): ``conv(x, f, out)``
