@@ -218,6 +218,8 @@ def _covers(origin, tile_shape, extents, group_counts, what):
                 raise UnsupportedKernel(f"{what}: dimension {d} is only covered up to {t} of {e}")
             continue
         ((axis, step),) = o.coefs.items()
+        if not isinstance(axis, int):
+            raise UnsupportedKernel(f"{what}: tile origin {o!r} depends on the sub-group id alone")
         if axis in used:
             raise UnsupportedKernel(f"{what}: group axis {axis} drives two dimensions")
         used.add(axis)
@@ -538,7 +540,12 @@ class KernelDispatcher:
 
         group_cls = (CurrentGroup1, CurrentGroup2, CurrentGroup3)[len(work) - 1]
         body = _resolve_symbols(self.func, subs, {CurrentGroup: group_cls})
-        recorder = group_cls(group, self.subgroup_size)
+        subgroup = self.subgroup_size
+        if subgroup is None:
+            subgroup = 16  # the reference simulator's default (kernel_sim.py:10)
+        elif not isinstance(subgroup, int):
+            subgroup = _to_int(subgroup, subs, "subgroup_size")
+        recorder = group_cls(group, subgroup)
         params = list(inspect.signature(self.func).parameters)[1:]
         stand_ins = []
         for i, a in enumerate(args):
@@ -554,6 +561,13 @@ class KernelDispatcher:
             body(recorder, *stand_ins)
         finally:
             _api._RECORDING.pop()
+        if recorder.refined is not None:
+            # A sub-group function ran: its tiles belong to the grid of sub-groups.
+            if (recorder.item_events or recorder.atomics or recorder.scatters
+                    or recorder.stores_outside_subgroups):
+                raise UnsupportedKernel("kernels that mix sub-group functions with stores at "
+                                        "group or work-item level")
+            counts = tuple(c * (g // t) for c, g, t in zip(counts, group, recorder.refined))
         if recorder.item_events:
             if recorder.stores or recorder.atomics or recorder.scatters:
                 raise UnsupportedKernel("kernels that mix work-item stores with tile stores")

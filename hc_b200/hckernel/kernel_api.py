@@ -208,7 +208,7 @@ class Affine:
 
     def __repr__(self):
         terms = [str(self.const)] if self.const or not self.coefs else []
-        terms += [f"{c}*gid{d}" for d, c in sorted(self.coefs.items())]
+        terms += [f"{c}*gid{d}" for d, c in sorted(self.coefs.items(), key=repr)]
         return " + ".join(terms)
 
 
@@ -834,7 +834,8 @@ def _dot(a, b):
 
 
 class CurrentSubGroup:
-    """Importable for source compatibility (reference: kernel_api.py:231-240)."""
+    """The sub-group a ``group.subgroups`` function sees (reference:
+    kernel_api.py:231-240): its size and its id inside the work-group."""
 
     def __init__(self, size, subgroup_id):
         self._size, self._subgroup_id = size, subgroup_id
@@ -943,6 +944,12 @@ class CurrentGroup:
         self.item_events = []
         self.item_ranges = [{}]
         self.in_workitems = False
+        # Sub-group scope: while a sub-group function is recorded, the group axes
+        # stand for the grid of sub-groups (`refined` holds that grid's tile per
+        # axis once a sub-group function has run).
+        self.in_subgroups = False
+        self.refined = None
+        self.stores_outside_subgroups = 0
 
     def note_guard(self, axis, scale, offset, op, bound):
         """``scale * gid[axis] + offset  OP  bound`` was taken as true."""
@@ -968,6 +975,9 @@ class CurrentGroup:
 
     @property
     def id(self):
+        if self.in_subgroups and any(t != g for t, g in zip(self.refined, self._group_shape)):
+            raise UnsupportedKernel("group.id inside a sub-group function (use group.work_offset "
+                                    "and the sub-group's id)")
         return self._group_id
 
     @property
@@ -980,6 +990,11 @@ class CurrentGroup:
 
     @property
     def work_offset(self):
+        if self.in_subgroups:
+            # Axis d of the recording counts sub-groups: v = id * (shape / tile) + s with
+            # s the sub-group's id, so id * shape = (v - s) * tile.  The s terms
+            # cancel in `work_offset + s * tile`, the origin of the sub-group's part.
+            return tuple(Affine(0, {d: t, ("sg", d): -t}) for d, t in enumerate(self.refined))
         return tuple(g * s for g, s in zip(self._group_id, self._group_shape))
 
     # -- memory ------------------------------------------------------------------
@@ -1019,6 +1034,8 @@ class CurrentGroup:
                 raise TypeError("mapping must come from create_mapping")
             self.scatters.append((dst, Tile._wrap(src), mapping))
             return
+        if not self.in_subgroups:
+            self.stores_outside_subgroups += 1
         self.stores.append((dst, Tile._wrap(src)))
 
     # -- allocators ---------------------------------------------------------------
@@ -1039,9 +1056,35 @@ class CurrentGroup:
             raise UnsupportedKernel("group.vec with a different shape")
         return src
 
-    # -- scopes the precompiled kernels do not need ---------------------------------
+    # -- scopes ---------------------------------------------------------------------
     def subgroups(self, func):
-        raise UnsupportedKernel("group.subgroups is not supported by the precompiled kernels")
+        """Sub-group scope (reference kernel_api.py:378-393, which runs ``func``
+        once per sub-group: every index of the leading group axes, and
+        ``ceil(shape[-1] / subgroup_size)`` pieces of the last one).  ``func`` is
+        recorded once; the tiles it loads and stores at
+        ``work_offset + subgroup_id * (1, ..., 1, size)`` are the tiles of a finer
+        grid of work-groups, one per sub-group, and the launch is planned on that
+        grid.  The sub-group size has to divide the last group axis."""
+        size = self._subgroup_size
+        last = self._group_shape[-1]
+        if not isinstance(size, int) or size <= 0:
+            raise UnsupportedKernel(f"group.subgroups needs a numeric subgroup_size, got {size!r}")
+        if last % size:
+            raise UnsupportedKernel(f"a sub-group size of {size} does not divide the group's "
+                                    f"last axis ({last})")
+
+        def run():
+            if self.in_workitems or self.in_subgroups:
+                raise UnsupportedKernel("group.subgroups inside another scope")
+            dims = len(self._group_shape)
+            self.refined = (1,) * (dims - 1) + (size,)
+            self.in_subgroups = True
+            try:
+                func(CurrentSubGroup(size, tuple(Affine(0, {("sg", d): 1}) for d in range(dims))))
+            finally:
+                self.in_subgroups = False
+
+        return run
 
     def workitems(self, func):
         """Work-item scope (reference kernel_api.py:395-414, which runs ``func``
@@ -1068,7 +1111,9 @@ class CurrentGroup:
         goes on.  Splits the function into two phases; values cross it through a
         tile of the group (``group.zeros(...)`` written at ``tile[lid]``)."""
         if not self.in_workitems:
-            return  # at group level nothing runs concurrently: nothing to wait for
+            # At group level nothing runs concurrently, and the sub-groups of a group
+            # share nothing that a recorded body can express: nothing to wait for.
+            return
         if any(e[0] == "barrier" for e in self.item_events):
             raise UnsupportedKernel("more than one group.barrier() in a work-item function")
         self.item_events.append(("barrier",))

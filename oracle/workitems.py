@@ -208,3 +208,92 @@ def work_item_cases():
              inputs=[rng.standard_normal((10, 19)).astype(f32),
                      rng.standard_normal((10, 19)).astype(f32)], out=((10, 19), f32)),
     ]
+
+
+def run_subgroups(body, work_shape, group_shape, subgroup_size) -> None:
+    """Sub-group scope (python/hckernel/kernel_api.py:266-272, 378-393): per
+    work-group, ``body(work offset, sub-group id, size)`` once for every index
+    of the leading group axes and every ``size``-wide piece of the last one, in
+    row-major order."""
+    group_shape_t = tuple(np.atleast_1d(group_shape).tolist())
+    pieces = -(-group_shape_t[-1] // subgroup_size)
+    for _, offset in iter_groups(work_shape, group_shape):
+        for sgid in np.ndindex(*group_shape_t[:-1], pieces):
+            body(offset, sgid, subgroup_size)
+
+
+def subgroup_cases():
+    """Bodies written at sub-group level, pinned under ``tests/golden`` like the
+    work-item cases: every sub-group loads its part of the group's tile at
+    ``work_offset + subgroup_id * (1, ..., size)``, computes, and stores it at
+    the same place.  Elements beyond the arrays are masked by the load and
+    skipped by the store (python/hckernel/kernel_api.py:297-340)."""
+    rng = np.random.default_rng(23)
+
+    def scale_shift(ns):
+        G = ns.sym.G
+
+        @ns.kernel(work_shape=G, group_shape=64, subgroup_size=16, **ns.target)
+        def k(gr: ns.CurrentGroup, a: ns.Buffer[G, ns.DT], out: ns.Buffer[G, ns.DT]):
+            @gr.subgroups
+            def inner(sg):
+                n = sg.size()
+                x = gr.work_offset[0] + sg.subgroup_id()[0] * n
+                gr.store(out[x:], gr.load(a[x:], shape=n) * 2.0 + 1.0)
+
+            inner()
+
+        return k
+
+    def scale_shift_oracle(ins, out):
+        (a,) = ins
+
+        def body(offset, sgid, n):
+            x = offset[0] + sgid[0] * n
+            out[x:x + n] = a[x:x + n] * 2.0 + 1.0
+
+        run_subgroups(body, out.shape, 64, 16)
+
+    def rows_of_pieces(ns):
+        W, H = ns.sym.W, ns.sym.H
+
+        @ns.kernel(work_shape=(W, H), group_shape=(2, 64), subgroup_size=32, **ns.target)
+        def k(gr: ns.CurrentGroup, a: ns.Buffer[W, H, ns.DT], b: ns.Buffer[W, H, ns.DT],
+              out: ns.Buffer[W, H, ns.DT]):
+            @gr.subgroups
+            def inner(sg):
+                n, sid = sg.size(), sg.subgroup_id()
+                i = gr.work_offset[0] + sid[0]
+                j = gr.work_offset[1] + sid[1] * n
+                x = gr.load(a[i:, j:], shape=(1, n))
+                y = gr.load(b[i:, j:], shape=(1, n))
+                gr.store(out[i:, j:], np.maximum(x * y - 0.5, y))
+
+            inner()
+
+        return k
+
+    def rows_of_pieces_oracle(ins, out):
+        a, b = ins
+
+        def body(offset, sgid, n):
+            i, j = offset[0] + sgid[0], offset[1] + sgid[1] * n
+            if i < out.shape[0]:
+                x, y = a[i, j:j + n], b[i, j:j + n]
+                out[i, j:j + n] = np.maximum(x * y - 0.5, y)
+
+        run_subgroups(body, out.shape, (2, 64), 32)
+
+    f32, f64 = np.float32, np.float64
+    return [
+        dict(name="sg_scale_shift_f32", make=scale_shift, oracle=scale_shift_oracle,
+             inputs=[rng.standard_normal(1000).astype(f32)], out=((1000,), f32)),
+        dict(name="sg_scale_shift_f64", make=scale_shift, oracle=scale_shift_oracle,
+             inputs=[rng.standard_normal(130)], out=((130,), f64)),
+        dict(name="sg_rows_of_pieces_f64", make=rows_of_pieces, oracle=rows_of_pieces_oracle,
+             inputs=[rng.standard_normal((9, 200)), rng.standard_normal((9, 200))],
+             out=((9, 200), f64)),
+        dict(name="sg_rows_of_pieces_f32", make=rows_of_pieces, oracle=rows_of_pieces_oracle,
+             inputs=[rng.standard_normal((4, 64)).astype(f32),
+                     rng.standard_normal((4, 64)).astype(f32)], out=((4, 64), f32)),
+    ]

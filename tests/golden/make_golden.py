@@ -487,6 +487,16 @@ def main():
         same(case["name"], r, o)
         out[case["name"]] = r
 
+    # 6d. Sub-group bodies: every sub-group works on its part of the group's tile.
+    for case in oracle_items.subgroup_cases():
+        shape, dtype = case["out"]
+        r = np.full(shape, -77, dtype)
+        case["make"](ns)(*case["inputs"], r)
+        o = np.full(shape, -77, dtype)
+        case["oracle"](case["inputs"], o)
+        same(case["name"], r, o)
+        out[case["name"]] = r
+
     # 7. Row bodies: reductions along the rows used again in the same expression.
     for name, fn, count, shape, dtype, group_rows in oracle.rowwise_cases():
         inputs = oracle.make_elementwise_inputs(count, shape, dtype, seed=8)

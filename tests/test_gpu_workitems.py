@@ -147,3 +147,20 @@ def test_compiled_work_item_programs_equal_the_interpreter(case):
         assert after - before == 0 if interpret else after - before in (0, 1), ctx.specialise_note
         outs.append(d_out.cpu().numpy())
     assert np.array_equal(outs[0], outs[1], equal_nan=True)
+
+
+@pytest.mark.parametrize("case", oracle_items.subgroup_cases(), ids=lambda c: c["name"])
+def test_subgroup_bodies_match_the_reference(golden, case):
+    """group.subgroups: every sub-group works on its part of the group's tile; the
+    launch runs on the grid of sub-groups (element-wise kernels)."""
+    shape, dtype = case["out"]
+    k = case["make"](NS)
+    d_in = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in case["inputs"]]
+    d_out = torch.full(shape, -77, dtype=d_in[0].dtype, device="cuda")
+    k(*d_in, d_out)
+    torch.cuda.synchronize()
+    got, want = d_out.cpu().numpy(), golden[case["name"]]
+    if dtype == np.float32:
+        np.testing.assert_allclose(got, want, rtol=3e-7)
+    else:
+        assert np.array_equal(got, want)
