@@ -219,6 +219,7 @@ KERNELS_PROTOTYPES = {
         C.c_int, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _vp, _sz]
     ),
     "hcGemmW8A16WorkspaceBytes": (_sz, [_ll, _ll]),
+    "hcGemmW8A16BandedBytes": (_sz, [_ll, _ll]),
     "hcGemmW8A16": (
         C.c_int,
         [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _ll, _ll, _ll, _ll, _ll, _ll],
@@ -517,6 +518,9 @@ class Context:
 
     def gemm_w8a16_workspace_bytes(self, n, k) -> int:
         return self.lib.hcGemmW8A16WorkspaceBytes(n, k)
+
+    def gemm_w8a16_banded_bytes(self, n, k) -> int:
+        return self.lib.hcGemmW8A16BandedBytes(n, k)
 
     def gemm_w8a16(self, a, w, scale, out, workspace, workspace_bytes, m, n, k, lda, ldw, ldc):
         self._check(

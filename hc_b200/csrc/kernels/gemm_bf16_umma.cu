@@ -37,6 +37,7 @@
 // (this GPU's copy of C and the copies of the other GPUs of a multi-GPU job,
 // peer memory reached with plain stores over NVLink) - the output all-gather of
 // an M- or N-sharded product done by the kernel itself.
+#include "gemm_band_params.h"
 #include "hc_ptx.cuh"
 #include "peer_params.h"
 
@@ -81,6 +82,121 @@ struct Params {
   int vecStore;      // C base 16-byte aligned and ldc % 8 == 0
 };
 
+// The dequantising form that converts inside the GEMM kernel (BANDED):
+// gemm_band_params.h describes the ring of converted bands and its counters.
+using BandPlan = HcBandPlan;
+constexpr int kConverterWarps = 4;
+constexpr int kBandedThreads = NUM_THREADS + 32 * kConverterWarps;
+constexpr int kStatusBandWait = 6;  // TMA producer waiting for a converted band
+constexpr int kStatusSlotWait = 7;  // converters waiting for a consumed band
+
+// Waits (bounded like mbarWait) until *counter >= want.
+__device__ __forceinline__ bool counterWait(const unsigned *counter, unsigned want,
+                                            volatile int *abortFlag, int *status, int code) {
+  const unsigned long long start = globalTimerNs();
+  for (uint32_t spin = 1;; ++spin) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= want)
+      return true;
+    __nanosleep(100);
+    if ((spin & 15u) == 0) {
+      if (*abortFlag)
+        return false;
+      if (globalTimerNs() - start > kWaitLimitNs) {
+        *abortFlag = 1;
+        atomicCAS(status, kStatusOk, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Generic-proxy writes to global memory before, async-proxy (TMA) reads after.
+__device__ __forceinline__ void fenceProxyAsyncAll() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// int8 -> bf16, exact, two at a time: the bytes of `word` picked by `sel` become
+// the low bytes of 0x43xx.  With bit 7 of the byte cleared that is 128 + (b & 127);
+// subtracting 0x4300 (128) or, for a negative byte, 0x4380 (256) gives b.
+__device__ __forceinline__ uint32_t bytesToBf16(uint32_t word, uint32_t sel) {
+  const uint32_t t = __byte_perm(word, 0x43434343u, sel);
+  const uint32_t biased = t & 0xFF7FFF7Fu;
+  const uint32_t bias = t & 0xFF80FF80u;
+  const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&biased),
+                                   *reinterpret_cast<const __nv_bfloat162 *>(&bias));
+  return *reinterpret_cast<const uint32_t *>(&d);
+}
+
+// The first bands are needed before any tile can start, when the epilogue warps
+// have nothing to do yet: they convert a share of those bands too.
+constexpr int kHelpedBands = 2;
+
+// Warp `me` of `total` converts rows me, me + total, ... of the band, eight rows
+// at a time (the weights come from HBM: what is in flight per warp sets the
+// pace); a lane takes 16 weights (16 bytes in, 32 out) per row.  Then it reports
+// its share as written.
+__device__ __forceinline__ void convertShare(const Params &p, const BandPlan &bp, int band,
+                                             unsigned me, unsigned total, int lane) {
+  const long long bandCols = (long long)bp.bandTiles * BN;
+  const long long col0 = (long long)band * bandCols;
+  const int packets = int(min(bandCols, p.N - col0) >> 4);
+  const int8_t *src = bp.w + col0;
+  __nv_bfloat16 *dst =
+      static_cast<__nv_bfloat16 *>(bp.ring) + (long long)(band % bp.slots) * p.K * bandCols;
+  constexpr int R = 8;
+  for (long long r = me; r < p.K; r += (long long)total * R) {
+    for (int pk = lane; pk < packets; pk += 32) {
+      int4 q[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const long long row = r + (long long)i * total;
+        q[i] = make_int4(0, 0, 0, 0);
+        if (row < p.K)
+          asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
+                       : "l"(reinterpret_cast<const int4 *>(src + row * bp.ldw) + pk));
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const long long row = r + (long long)i * total;
+        if (row < p.K) {
+          const uint32_t words[4] = {uint32_t(q[i].x), uint32_t(q[i].y), uint32_t(q[i].z),
+                                     uint32_t(q[i].w)};
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            o[2 * j] = bytesToBf16(words[j], 0x5140u);     // bytes 0 and 1
+            o[2 * j + 1] = bytesToBf16(words[j], 0x7362u); // bytes 2 and 3
+          }
+          uint4 *out = reinterpret_cast<uint4 *>(dst + row * bandCols) + 2 * pk;
+          out[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+    }
+  }
+  // This warp's share is written: visible to the TMA reads of every CTA.
+  fenceProxyAsyncAll();
+  __threadfence();
+  __syncwarp();
+  if (lane == 0)
+    atomicAdd(bp.converted + band, 1u);
+}
+
+// Tile t of the band-by-band order: bands of `bandTiles` tile columns, inside a
+// band the tile columns run fastest (the tiles in flight share rows of A).
+__device__ __forceinline__ void bandTileCoords(int t, const Params &p, const BandPlan &bp,
+                                               int &tm, int &tn, int &band) {
+  const int full = p.tilesM * bp.bandTiles;
+  band = t / full;
+  const int rem = t - band * full;
+  const int cols = min(bp.bandTiles, p.tilesN - band * bp.bandTiles);
+  tm = rem / cols;
+  tn = band * bp.bandTiles + rem % cols;
+}
+
 __device__ __forceinline__ void tileCoords(int t, const Params &p, int &tm,
                                            int &tn) {
   const int perBand = p.bandM * p.tilesN;
@@ -91,12 +207,12 @@ __device__ __forceinline__ void tileCoords(int t, const Params &p, int &tm,
   tn = rem / rowsInBand;
 }
 
-template <bool PAIR, bool SCALED, bool PEERS = false>
+template <bool PAIR, bool SCALED, bool PEERS = false, bool BANDED = false>
 __device__ __forceinline__ void
 gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
          __nv_bfloat16 *__restrict__ c, const float *__restrict__ scale,
          const Params &p, int *status, unsigned char *smemRaw,
-         const HcPeerDsts *peers = nullptr) {
+         const HcPeerDsts *peers = nullptr, const BandPlan *bp = nullptr) {
   using Cfg = Config<PAIR>;
   // The swizzled stages need 1024-byte alignment.
   const uint32_t smemBase = (smemAddr(smemRaw) + 1023u) & ~1023u;
@@ -144,9 +260,27 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t it = 0;
+      int readyBand = -1;
       for (int t = firstTile; t < numTiles && !*abortFlag; t += tileStep) {
         int tm, tn;
-        tileCoords(t, p, tm, tn);
+        int bRow0 = 0; // row of B's map at K block 0
+        if constexpr (BANDED) {
+          int band;
+          bandTileCoords(t, p, *bp, tm, tn, band);
+          if (band != readyBand) {
+            // Every converter warp of the grid has written its share of the band.
+            const unsigned writers =
+                gridDim.x * (band < kHelpedBands ? kConverterWarps + 4 : kConverterWarps);
+            if (!counterWait(bp->converted + band, writers, abortFlag, status, kStatusBandWait))
+              break;
+            fenceProxyAsyncAll();
+            readyBand = band;
+          }
+          bRow0 = (band % bp->slots) * int(p.K);
+          tn -= band * bp->bandTiles; // the column inside the band's buffer
+        } else {
+          tileCoords(t, p, tm, tn);
+        }
         const int row0 = tm * Cfg::kTileM + int(ctaRank) * BM;
         const int col0 = tn * BN + int(ctaRank) * Cfg::kBColsPerCta;
         for (int kb = 0; kb < kBlocks; ++kb, ++it) {
@@ -172,7 +306,7 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
             tmaLoad2DPair(stage, mapA, fullBar, kb * BK, row0);
             for (int ch = 0; ch < Cfg::kBChunks; ++ch)
               tmaLoad2DPair(stage + Cfg::kABytes + ch * Cfg::kBChunkBytes, mapB,
-                            fullBar, col0 + ch * 64, kb * BK);
+                            fullBar, col0 + ch * 64, bRow0 + kb * BK);
           } else {
             mbarExpectTx(fullBar, Cfg::kStageBytes);
             tmaLoad2D(stage, mapA, fullBar, kb * BK, row0);
@@ -251,7 +385,7 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
           ummaCommit(smemAddr(&bars->tmemFull[acc]));
       }
     }
-  } else {
+  } else if (warp < NUM_THREADS / 32) {
     // -------------------------------- epilogue --------------------------------
     const int quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32) for this warp
     uint32_t tmemEmptyBar[2];
@@ -260,10 +394,21 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
       if constexpr (PAIR)
         tmemEmptyBar[a] = mapSharedToCta(tmemEmptyBar[a], 0);
     }
+    if constexpr (BANDED) {
+      // Nothing to drain yet: convert a share of the first bands (warps 2..5 take
+      // the places after the converter warps).
+      for (int band = 0; band < min(kHelpedBands, bp->numBands); ++band)
+        convertShare(p, *bp, band,
+                     blockIdx.x * (kConverterWarps + 4) + unsigned(kConverterWarps + warp - 2),
+                     gridDim.x * (kConverterWarps + 4), lane);
+    }
     int tileIter = 0;
     for (int t = firstTile; t < numTiles; t += tileStep, ++tileIter) {
-      int tm, tn;
-      tileCoords(t, p, tm, tn);
+      int tm, tn, band = 0;
+      if constexpr (BANDED)
+        bandTileCoords(t, p, *bp, tm, tn, band);
+      else
+        tileCoords(t, p, tm, tn);
       const int acc = tileIter & 1;
       const uint32_t accPhase = (tileIter >> 1) & 1u;
       bool ok = true;
@@ -274,6 +419,11 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
       if (!ok)
         break;
       tcgen05FenceAfter();
+      if constexpr (BANDED) {
+        // The tile's MMAs are complete: nothing reads its part of the band any more.
+        if (leader && quad == 0 && lane == 0)
+          atomicAdd(bp->consumed + band, 1u);
+      }
       const long long row =
           (long long)tm * Cfg::kTileM + int(ctaRank) * BM + quad * 32 + lane;
       const long long colBase = (long long)tn * BN;
@@ -348,6 +498,27 @@ gemmUmma(const CUtensorMap *mapA, const CUtensorMap *mapB,
     }
   }
 
+  else if constexpr (BANDED) {
+    // ------------------------------- converters -------------------------------
+    // Every band in turn, as soon as its slot of the ring is free.
+    for (int band = 0; band < bp->numBands && !*abortFlag; ++band) {
+      if (band >= bp->slots) {
+        // The slot still belongs to the band `slots` before until its tiles are done.
+        const int old = band - bp->slots;
+        const unsigned tiles =
+            unsigned(p.tilesM * min(bp->bandTiles, p.tilesN - old * bp->bandTiles));
+        bool ok = true;
+        if (lane == 0)
+          ok = counterWait(bp->consumed + old, tiles, abortFlag, status, kStatusSlotWait);
+        if (!__shfl_sync(0xffffffffu, ok, 0))
+          break;
+      }
+      const unsigned width = band < kHelpedBands ? kConverterWarps + 4 : kConverterWarps;
+      convertShare(p, *bp, band, blockIdx.x * width + unsigned(warp - NUM_THREADS / 32),
+                   gridDim.x * width, lane);
+    }
+  }
+
   // -------------------------------- teardown ----------------------------------
   __syncwarp();
   tcgen05FenceBefore();
@@ -396,6 +567,15 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1)
     __launch_bounds__(NUM_THREADS, 1)
         hc_gemm_bf16_umma_pair_scaled(HC_GEMM_ARGS) {
   HC_GEMM_BODY(true, true)
+}
+
+// The dequantising GEMM that converts its weights inside the kernel, band by
+// band (BandPlan): mapB covers the ring of converted bands, [slots * K, bandCols].
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBandedThreads, 1)
+    hc_gemm_w8a16_umma_banded(HC_GEMM_ARGS, const __grid_constant__ BandPlan plan) {
+  extern __shared__ __align__(1024) unsigned char smemRaw[];
+  Params p{M, N, K, ldc, tilesM, tilesN, bandM, vecStore};
+  gemmUmma<true, true, false, true>(&mapA, &mapB, c, scale, p, status, smemRaw, nullptr, &plan);
 }
 
 // The same four kernels writing every tile to all destinations of `peers`.

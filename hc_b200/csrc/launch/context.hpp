@@ -37,6 +37,7 @@ struct HcContextImpl {
   long long convStages = 0;   // 2..6: pipeline stages of the convolution (0: as many as fit)
   long long pairSlots = 0; // CTA pairs of the tcgen05 kernels resident at once
   int pairSlotsF32 = 0; // the same for the float32 tensor-core kernel
+  int pairSlotsBanded = 0; // the same for the dequant GEMM that converts band by band
   int pairSlotsW8 = 0;  // the same for the dequant GEMM that converts in its pipeline
   long long w8Variant = 0; // 1: convert the weights in a pass of its own, 2: never
   // Programs without a precompiled body: 0 interpret them, 1 compile them at their

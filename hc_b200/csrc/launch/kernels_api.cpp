@@ -11,6 +11,7 @@
 
 #include "../kernels/fused_programs.h"
 #include "../kernels/conv_params.h"
+#include "../kernels/gemm_band_params.h"
 #include "../kernels/items_params.h"
 #include "../kernels/map_params.h"
 #include "../kernels/mapped_params.h"
@@ -121,6 +122,7 @@ const KernelEntry kKernelTable[] = {
     {"hc_gemm_f32_umma", "gemm_f32_umma"},
     {"hc_gemm_f32_umma_pair", "gemm_f32_umma"},
     {"hc_gemm_w8a16_umma_pair", "gemm_w8a16_umma"},
+    {"hc_gemm_w8a16_umma_banded", "gemm_bf16_umma"},
     {"hc_conv_f32_umma", "conv_f32_umma"},
     {"hc_conv_f32_umma_ta", "conv_f32_umma"},
     {"hc_split_tf32_pairs", "conv_f32_umma"},
@@ -154,6 +156,8 @@ bool aligned(const void *p, size_t a) {
 // Geometry of the tensor-core GEMM kernels (gemm_bf16_umma.cu).
 constexpr int kUmmaBM = 128, kUmmaBN = 256, kUmmaBK = 64;
 constexpr int kUmmaThreads = 192;
+// The banded dequantising GEMM: converted columns per band, bands in its ring.
+constexpr int kBandCols = 1024, kBandSlots = 3;
 constexpr size_t kUmmaSmemBytes = 4 * 48 * 1024 /*stages*/ + 1024 /*align*/ +
                                   512 /*barriers*/;
 
@@ -425,10 +429,12 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->convVariant = value;
     return 0;
   }
-  if (std::strcmp(name, "w8a16_variant") == 0 && value >= 0 && value <= 2) {
+  if (std::strcmp(name, "w8a16_variant") == 0 && value >= 0 && value <= 3) {
     // hcGemmW8A16: 0 and 1 = the weights are converted in a pass of their own (needs
     // the workspace; the faster form at the benchmark size), 2 = inside the GEMM's
-    // pipeline (no workspace; fails where the layout does not allow it).
+    // pipeline (no workspace; fails where the layout does not allow it), 3 = inside
+    // the GEMM kernel band by band, by warps of their own (the first
+    // hcGemmW8A16BandedBytes of the workspace; fails where the layout does not allow it).
     c->w8Variant = value;
     return 0;
   }
@@ -1617,6 +1623,15 @@ int hcGemmW8A16Peers(HcContext c, const void *a, const void *w, const float *sca
                     dsts);
 }
 
+// The banded form's part of the workspace: a ring of kBandSlots bands of
+// kBandCols converted columns, and two counters per band.
+size_t hcGemmW8A16BandedBytes(long long N, long long K) {
+  if (N <= 0 || K <= 0)
+    return 0;
+  const size_t bands = size_t(ceilDiv(N, (long long)kBandCols));
+  return size_t(kBandSlots) * size_t(K) * kBandCols * 2 + roundUp(bands * 8, 256);
+}
+
 size_t hcGemmW8A16WorkspaceBytes(long long N, long long K) {
   if (N <= 0 || K <= 0)
     return 0;
@@ -1692,6 +1707,56 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
     void *args[] = {&mapA, &mapW, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
                     &vecStore, &c->statusWord};
     return c->launch(name, size_t(grid), 1, 1, 480, args, 13, smem);
+  }
+  // Conversion inside the GEMM kernel, band by band (hc_gemm_w8a16_umma_banded):
+  // the converted weights live in a ring of three bands of 1024 columns.
+  const size_t bandedBytes = hcGemmW8A16BandedBytes(N, K);
+  const bool bandedFits = fusedFits && K % kUmmaBK == 0 && N >= 4 * kBandCols && workspace &&
+                          aligned(workspace, 1024) && workspaceBytes >= bandedBytes &&
+                          (long long)kBandSlots * K < (1ll << 31);
+  if (c->w8Variant == 3 && !bandedFits)
+    return c->fail("hcGemmW8A16: the banded form needs a tcgen05 device, M > 128, K %% 64 == 0, "
+                   "N >= %d and a multiple of 16, lda %% 8 == 0, ldw %% 16 == 0, 16-byte aligned "
+                   "a and w, and a 1024-byte aligned workspace of %zu bytes",
+                   4 * kBandCols, bandedBytes);
+  if (bandedFits && c->w8Variant == 3) {
+    int tilesM = int(ceilDiv(M, 2 * kUmmaBM)), tilesN = int(ceilDiv(N, kUmmaBN));
+    HcBandPlan plan{};
+    plan.w = static_cast<const int8_t *>(w);
+    plan.ldw = ldw;
+    plan.ring = workspace;
+    plan.bandTiles = kBandCols / kUmmaBN;
+    plan.numBands = int(ceilDiv(tilesN, plan.bandTiles));
+    plan.slots = kBandSlots;
+    const size_t ringBytes = size_t(kBandSlots) * size_t(K) * kBandCols * 2;
+    plan.converted = reinterpret_cast<unsigned *>(static_cast<char *>(workspace) + ringBytes);
+    plan.consumed = plan.converted + plan.numBands;
+    if (olxMemsetD8(c->queue, plan.converted, 0, size_t(plan.numBands) * 2 * sizeof(unsigned)))
+      return c->fail("hcGemmW8A16: clearing the band counters failed: %s", c->lastError.c_str());
+    alignas(64) CUtensorMap mapA, mapB;
+    if (olxEncodeTensorMap2D(c->device, &mapA, /*bf16*/ 0, a, size_t(M), size_t(K),
+                             size_t(lda) * 2, kUmmaBM, kUmmaBK, 128) ||
+        olxEncodeTensorMap2D(c->device, &mapB, /*bf16*/ 0, workspace, size_t(kBandSlots) * K,
+                             size_t(kBandCols), size_t(kBandCols) * 2, kUmmaBK, 64, 128))
+      return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
+    int bandM = 16; // unused by the band-by-band tile order
+    int vecStore = aligned(out, 16) && ldc % 8 == 0;
+    const char *name = "hc_gemm_w8a16_umma_banded";
+    if (c->pairSlotsBanded == 0) {
+      OlKernel k = c->kernel(name);
+      int slots = 0;
+      if (!k || olxMaxActiveClusters(c->queue, k, kUmmaThreads + 128, kUmmaSmemBytes, 2, &slots) ||
+          slots <= 0)
+        return c->fail("cluster occupancy query failed: %s", c->lastError.c_str());
+      c->pairSlotsBanded = slots;
+    }
+    // Every CTA converts a share of every band, so all of the grid has to be
+    // resident at once: never more clusters than the device holds.
+    const long long tiles = (long long)tilesM * tilesN;
+    const long long grid = 2 * std::min<long long>(tiles, c->pairSlotsBanded);
+    void *args[] = {&mapA, &mapB, &out, &scale, &M, &N, &K, &ldc, &tilesM, &tilesN, &bandM,
+                    &vecStore, &c->statusWord, &plan};
+    return c->launch(name, size_t(grid), 1, 1, kUmmaThreads + 128, args, 14, kUmmaSmemBytes);
   }
   const long long wsPitch = roundUp(N, 16);
   if (c->gemmVariant == 3 || !ummaEligible(c, a, workspace, K, lda, wsPitch)) {
