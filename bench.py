@@ -493,6 +493,8 @@ def run_gpu(args):
     ctx = get_context(desc)
     if args.w8a16_fused:
         ctx.set_option("w8a16_variant", 2)  # convert the weights inside the GEMM's pipeline
+    if args.w8a16_variant:
+        ctx.set_option("w8a16_variant", args.w8a16_variant)
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
     peaks = load_peaks()
     launcher = ShardedLauncher(kernels, rank, world)
@@ -1323,6 +1325,10 @@ def main():
     ap.add_argument("--w8a16-fused", action="store_true",
                     help="gemm_w8a16: convert the int8 weights inside the GEMM's pipeline "
                          "(no scratch matrix) instead of in a pass of their own")
+    ap.add_argument("--w8a16-variant", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="gemm_w8a16: 1 = conversion pass then GEMM (the default), 2 = as "
+                         "--w8a16-fused, 3 = converted inside the GEMM kernel band by band "
+                         "into a ring of three bands")
     ap.add_argument("--small", action="store_true",
                     help="reduced shapes, for profiler captures; not a benchmark result")
     args = ap.parse_args()

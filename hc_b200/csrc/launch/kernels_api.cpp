@@ -1712,12 +1712,12 @@ int hcGemmW8A16(HcContext c, const void *a, const void *w, const float *scale,
   // the converted weights live in a ring of three bands of 1024 columns.
   const size_t bandedBytes = hcGemmW8A16BandedBytes(N, K);
   const bool bandedFits = fusedFits && K % kUmmaBK == 0 && N >= 4 * kBandCols && workspace &&
-                          aligned(workspace, 1024) && workspaceBytes >= bandedBytes &&
+                          aligned(workspace, 256) && workspaceBytes >= bandedBytes &&
                           (long long)kBandSlots * K < (1ll << 31);
   if (c->w8Variant == 3 && !bandedFits)
     return c->fail("hcGemmW8A16: the banded form needs a tcgen05 device, M > 128, K %% 64 == 0, "
                    "N >= %d and a multiple of 16, lda %% 8 == 0, ldw %% 16 == 0, 16-byte aligned "
-                   "a and w, and a 1024-byte aligned workspace of %zu bytes",
+                   "a and w, and a 256-byte aligned workspace of %zu bytes",
                    4 * kBandCols, bandedBytes);
   if (bandedFits && c->w8Variant == 3) {
     int tilesM = int(ceilDiv(M, 2 * kUmmaBM)), tilesN = int(ceilDiv(N, kUmmaBN));

@@ -436,7 +436,7 @@ HC_B200_API int hcGemmBf16(HcContext c, const void *a, const void *b, void *cOut
  * weights converted to bf16); it is written by every call. */
 HC_B200_API size_t hcGemmW8A16WorkspaceBytes(long long N, long long K);
 /* What the form selected with the option `w8a16_variant` = 3 uses of the
- * workspace (its first bytes, 1024-byte aligned): the weights are converted
+ * workspace (its first bytes, 256-byte aligned): the weights are converted
  * inside the GEMM kernel, one band of 1024 columns at a time, into a ring of
  * three bands that the tiles read from L2 - 3 * K * 1024 * 2 bytes and a few
  * counters instead of the whole converted matrix. */
