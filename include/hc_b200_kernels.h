@@ -96,7 +96,7 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * 3 = hold such rows whatever the fill.  "fused": 0 = programs that match a body
  * compiled ahead of time run as straight-line kernels, 1 = every program is
  * interpreted.  "specialise": what happens to a program of hcMapElements /
- * hcRowProgram that has no such body - 1 (default) = it is compiled at its first
+ * hcRowProgram that has no such body, and to every program of hcWorkItems - 1 (default) = it is compiled at its first
  * launch (see hcSpecialisedPrograms) and interpreted where that is not possible,
  * 0 = it is interpreted, 2 = as 1, but the launch fails where compiling is not
  * possible.  "conv_variant" (hcConvF32Tensor): 0 = the image operand of a K block goes
@@ -105,7 +105,12 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * refused); "conv_stages": 0 or 2..6 pipeline stages; "conv_stacked": 0 = with at
  * most 128 filters the two products that share a_hi run as one MMA of double
  * width, 1 = three MMAs per K step throughout.  "gemm_band": row tiles per
- * band in the tile order of the tcgen05 GEMMs (0 = 16). */
+ * band in the tile order of the tcgen05 GEMMs (0 = 16).  "w8a16_variant"
+ * (hcGemmW8A16): 0 and 1 = the weights are converted by a pass of their own into
+ * the workspace, 2 = inside the GEMM's pipeline (no workspace), 3 = inside the
+ * GEMM kernel band by band into a ring of three bands (hcGemmW8A16BandedBytes of
+ * workspace); 2 and 3 fail where the layout does not allow them, and all give
+ * the same result bit for bit. */
 HC_B200_API int hcSetOption(HcContext c, const char *name, long long value);
 
 /* Run-time specialisation.  The reference compiles every kernel body at its
