@@ -563,10 +563,9 @@ class KernelDispatcher:
             _api._RECORDING.pop()
         if recorder.refined is not None:
             # A sub-group function ran: its tiles belong to the grid of sub-groups.
-            if (recorder.item_events or recorder.atomics or recorder.scatters
-                    or recorder.stores_outside_subgroups):
-                raise UnsupportedKernel("kernels that mix sub-group functions with stores at "
-                                        "group or work-item level")
+            if recorder.item_events or recorder.scatters or recorder.stores_outside_subgroups:
+                raise UnsupportedKernel("kernels that mix sub-group functions with stores or "
+                                        "updates at group or work-item level")
             counts = tuple(c * (g // t) for c, g, t in zip(counts, group, recorder.refined))
         if recorder.item_events:
             if recorder.stores or recorder.atomics or recorder.scatters:

@@ -410,6 +410,8 @@ class BufferRef:
         if isinstance(value, AtomicUpdate) and self._is_element(key):
             if self.recorder is None:
                 raise UnsupportedKernel("element update outside a kernel body")
+            if not self.recorder.in_subgroups:
+                self.recorder.stores_outside_subgroups += 1
             self.recorder.atomics.append(value)
             return
         item = self._item_axes(key)

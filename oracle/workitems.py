@@ -284,8 +284,39 @@ def subgroup_cases():
 
         run_subgroups(body, out.shape, (2, 64), 32)
 
+    def partial_sums(ns):
+        G = ns.sym.G
+
+        @ns.kernel(work_shape=G, group_shape=64, subgroup_size=16, **ns.target)
+        def k(gr: ns.CurrentGroup, a: ns.Buffer[G, ns.DT], result: ns.Buffer[1, ns.DT]):
+            # The whole-array sum of python/hckernel/tests/test_examples.py:31-49, one
+            # partial sum per sub-group.
+            @gr.subgroups
+            def inner(sg):
+                n = sg.size()
+                x = gr.work_offset[0] + sg.subgroup_id()[0] * n
+                ns.atomic_ref(result)[0] += gr.load(a[x:], shape=n).sum()
+
+            inner()
+
+        return k
+
+    def partial_sums_oracle(ins, out):
+        (a,) = ins
+
+        def body(offset, sgid, n):
+            x = offset[0] + sgid[0] * n
+            # The sum of a wholly masked tile is masked, and adding it to the element
+            # makes that NaN in the reference (NumPy converts the masked value with
+            # a warning): the pinned case has no such piece.
+            out[0] += a[x:x + n].sum() if x < a.shape[0] else np.nan
+
+        run_subgroups(body, a.shape, 64, 16)
+
     f32, f64 = np.float32, np.float64
     return [
+        dict(name="sg_partial_sums_f64", make=partial_sums, oracle=partial_sums_oracle,
+             inputs=[rng.standard_normal(1010)], out=((1,), f64)),
         dict(name="sg_scale_shift_f32", make=scale_shift, oracle=scale_shift_oracle,
              inputs=[rng.standard_normal(1000).astype(f32)], out=((1000,), f32)),
         dict(name="sg_scale_shift_f64", make=scale_shift, oracle=scale_shift_oracle,

@@ -475,7 +475,7 @@ def main():
     import hckernel.kernel_sim as ref_sim
 
     ns = types.SimpleNamespace(kernel=ref_sim.kernel, sym=sym, CurrentGroup=CurrentGroup,
-                               Buffer=Buffer, DT=DT, target={})
+                               Buffer=Buffer, DT=DT, target={}, atomic_ref=atomic_ref)
     from oracle import workitems as oracle_items
 
     for case in oracle_items.work_item_cases():

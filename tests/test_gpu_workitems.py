@@ -27,7 +27,8 @@ pytestmark = pytest.mark.gpu
 
 CASES = oracle_items.work_item_cases()
 NS = types.SimpleNamespace(kernel=kernel, sym=sym, CurrentGroup=CurrentGroup, Buffer=Buffer,
-                           DT=typename.DT, target=dict(backend="nvvm", device="cuda:0"))
+                           DT=typename.DT, atomic_ref=atomic_ref,
+                           target=dict(backend="nvvm", device="cuda:0"))
 
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: c["name"])
@@ -160,7 +161,10 @@ def test_subgroup_bodies_match_the_reference(golden, case):
     k(*d_in, d_out)
     torch.cuda.synchronize()
     got, want = d_out.cpu().numpy(), golden[case["name"]]
-    if dtype == np.float32:
+    if "sums" in case["name"]:
+        # Partial sums are added in another order than the simulator's: 1e-13 of sum|a|.
+        assert abs(got[0] - want[0]) <= 1e-13 * np.abs(case["inputs"][0]).sum()
+    elif dtype == np.float32:
         np.testing.assert_allclose(got, want, rtol=3e-7)
     else:
         assert np.array_equal(got, want)
