@@ -44,7 +44,7 @@ KERNEL_SOURCES = [
     "gemm_tiled",
     "gemm_bf16_umma",
     "gemm_f32_umma",
-    "conv_f32_umma",
+    "conv_f32_umma", "conv_f32_taps",
     "gemm_w8a16_umma",
     "dequant_w8",
     "selftest",

@@ -131,6 +131,11 @@ OLX_PROTOTYPES = {
         C.c_int,
         [_vp, _vp, C.c_int, _vp, _sz, _sz, _sz, C.c_uint, C.c_uint, C.c_int],
     ),
+    "olxEncodeTensorMapTiled": (
+        C.c_int,
+        [_vp, _vp, C.c_int, _vp, C.c_int, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(C.c_uint),
+         C.c_int],
+    ),
     "olxMaxActiveClusters": (
         C.c_int,
         [_vp, _vp, C.c_uint, _sz, C.c_uint, C.POINTER(C.c_int)],

@@ -22,3 +22,25 @@ struct HcConvParams {
   int32_t stacked;       // 1: a_hi * [b_hi; b_lo] as one MMA of width 2 nPad (nPad <= 128)
   int *status;           // the context's status word
 };
+
+// Parameter block of the convolution whose image tiles come by TMA
+// (conv_f32_taps.cu): stride 1, the image rewritten as [N, H, W, Cp] (hi and lo),
+// the filters as [NF, taps * Cp]; the tensor maps are kernel arguments of their own.
+struct HcConvTapParams {
+  float *out;
+  int32_t N, C, H, W;
+  int32_t NF, HF, WF;
+  int32_t HO, WO;
+  int32_t cBlocks;        // Cp / 32
+  int32_t kBlocks;        // HF * WF * cBlocks
+  int32_t nPad;           // NF rounded up to 16: the N of the MMA
+  int32_t boxW, boxH;     // the tile's rectangle of output pixels, boxW * boxH = 128
+  int32_t tilesW, tilesH; // tiles per image along W and H
+  int32_t stages;         // shared-memory stages the launch has room for
+  int32_t stacked;        // 1: a_hi * [b_hi; b_lo] as one MMA of width 2 nPad (nPad <= 128)
+  int *status;            // the context's status word
+  // hc_conv_f32_rows only: tiles of 128 consecutive positions of the flattened
+  // image (oh * W + ow) and the rows of a stage's image patch, 128 + WF - 1
+  // rounded up to 8.
+  int32_t tilesFlat, patchRows;
+};

@@ -64,6 +64,10 @@ const KernelEntry kKernelTable[] = {
     // hc_row_fused_<body>_{f32_held_t64,f32_held_t128,f32_v4,f32_v1,f64_v2,f64_v1} and
     // hc_map_fused_<body>_{f32_v4,f32_v1,f64_v2,f64_v1}: the bodies of
     // fused_programs.h compiled ahead of time.
+    {"hc_conv_f32_taps", "conv_f32_taps"},
+    {"hc_conv_f32_rows", "conv_f32_taps"},
+    {"hc_split_tf32_nhwc", "conv_f32_taps"},
+    {"hc_split_tf32_taps", "conv_f32_taps"},
     {"hc_work_items_f32", "work_items"},
     {"hc_work_items_f64", "work_items"},
     {"hc_row_fused_", "row_fused"},
@@ -423,7 +427,7 @@ int hcSetOption(HcContext c, const char *name, long long value) {
     c->gemmBand = value;
     return 0;
   }
-  if (std::strcmp(name, "conv_variant") == 0 && value >= 0 && value <= 2) {
+  if (std::strcmp(name, "conv_variant") == 0 && value >= 0 && value <= 4) {
     // hcConvF32Tensor: 1 = the image operand through shared memory, 2 = through
     // tensor memory (at most 128 filters), 0 = tensor memory where it fits.
     c->convVariant = value;
@@ -1469,8 +1473,117 @@ size_t hcConvF32TensorWorkspaceBytes(long long N, long long C, long long H, long
                                      long long NF, long long HF, long long WF) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || NF <= 0 || HF <= 0 || WF <= 0)
     return 0;
-  // The split filters, then the image as (hi, lo) pairs.
-  return convFilterBytes(NF, C, HF, WF) + size_t(roundUp(N * C * H * W * 8, 1024));
+  // The split filters, then the image as (hi, lo) pairs; or, for the form whose image
+  // tiles come by TMA, filters and image with the channels padded to 32.
+  const long long cp = roundUp(C, 32);
+  const size_t gathered = convFilterBytes(NF, C, HF, WF) + size_t(roundUp(N * C * H * W * 8, 1024));
+  const size_t taps = 2 * size_t(roundUp(NF * HF * WF * cp * 4, 1024)) +
+                      2 * size_t(roundUp(N * H * W * cp * 4, 1024));
+  return std::max(gathered, taps);
+}
+
+// The rectangle of 128 output pixels (a power of two wide, inside the image) that
+// wastes least of the tiles; false when the image is smaller than every rectangle.
+static bool pickConvBox(long long H, long long W, long long HO, long long WO, long long &boxW,
+                        long long &boxH) {
+  double best = -1.0;
+  boxW = boxH = 0;
+  for (long long bw = 128; bw >= 8; bw /= 2) {
+    const long long bh = 128 / bw;
+    if (bw > W || bh > H)
+      continue;
+    const double use = double(WO) / double(roundUp(WO, bw)) * double(HO) / double(roundUp(HO, bh));
+    if (use > best + 1e-9)
+      best = use, boxW = bw, boxH = bh;
+  }
+  return boxW != 0;
+}
+
+// The convolution with both operands by TMA (conv_f32_taps.cu): stride 1.
+static long long convRowsStages(long long NF, long long WF) {
+  // hc_conv_f32_rows: a stage holds the image patch (hi, lo) and WF filter tiles (hi, lo).
+  const long long nPad = roundUp(NF, 16), patchRows = roundUp(128 + WF - 1, 8);
+  const long long stageBytes = 2 * patchRows * 128 + WF * 2 * nPad * 32 * 4;
+  return std::min<long long>(6, (227 * 1024 - 1024 - 256) / stageBytes);
+}
+
+static int convF32Taps(HcContext c, const void *x, const void *f, void *out, long long N,
+                       long long C, long long H, long long W, long long NF, long long HF,
+                       long long WF, void *workspace, bool stacked, bool rows) {
+  const char *who = "hcConvF32Tensor";
+  const long long HO = H - HF + 1, WO = W - WF + 1, nPad = roundUp(NF, 16);
+  const long long cp = roundUp(C, 32), cBlocks = cp / 32, taps = HF * WF;
+  const long long kBlocks = taps * cBlocks, kp = taps * cp;
+  long long boxW = 0, boxH = 0;
+  if (!rows && !pickConvBox(H, W, HO, WO, boxW, boxH))
+    return c->fail("%s: an image of %lld x %lld is too small for the TMA form", who, H, W);
+  const long long tilesW = rows ? 0 : ceilDiv(WO, boxW), tilesH = rows ? 0 : ceilDiv(HO, boxH);
+  const long long patchRows = roundUp(128 + WF - 1, 8);
+  const long long tilesFlat = ceilDiv((HO - 1) * W + WO, 128);
+  const long long stageBytes = rows ? 2 * patchRows * 128 + WF * 2 * nPad * 32 * 4
+                                    : 2 * 128 * 32 * 4 + 2 * nPad * 32 * 4;
+  const long long fixed = 1024 /*align*/ + 256 /*barriers*/;
+  long long stages = std::min<long long>(6, (227 * 1024 - fixed) / stageBytes);
+  if (c->convStages)
+    stages = std::min(stages, c->convStages);
+  if (stages < 2)
+    return c->fail("%s: %lld filters do not fit in shared memory", who, NF);
+  auto *base = static_cast<unsigned char *>(workspace);
+  const size_t filterBytes = size_t(roundUp(NF * kp * 4, 1024));
+  const size_t imageBytes = size_t(roundUp(N * H * W * cp * 4, 1024));
+  float *fHi = reinterpret_cast<float *>(base), *fLo = reinterpret_cast<float *>(base + filterBytes);
+  float *xHi = reinterpret_cast<float *>(base + 2 * filterBytes);
+  float *xLo = reinterpret_cast<float *>(base + 2 * filterBytes + imageBytes);
+  {
+    int ci = int(C), hw = int(H * W), cpi = int(cp);
+    const long long work = ceilDiv(H * W, 32) * cBlocks;
+    const long long gx = std::max<long long>(1, std::min<long long>(work, c->smCount * 8));
+    void *args[] = {&x, &xHi, &xLo, &ci, &hw, &cpi};
+    if (c->launch("hc_split_tf32_nhwc", size_t(gx), size_t(N), 1, 256, args, 6, 0))
+      return 1;
+  }
+  {
+    int nf = int(NF), ci = int(C), ti = int(taps), cpi = int(cp);
+    const long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(NF * kp, 256), 1024));
+    void *args[] = {&f, &fHi, &fLo, &nf, &ci, &ti, &cpi};
+    if (c->launch("hc_split_tf32_taps", size_t(gx), 1, 1, 256, args, 7, 0))
+      return 1;
+  }
+  alignas(64) CUtensorMap maps[4];
+  // The image as [N, H, W, Cp] for boxes of pixels, as [N, H * W, Cp] for runs of
+  // positions.
+  const size_t dims4[4] = {size_t(cp), size_t(W), size_t(H), size_t(N)};
+  const size_t pitches4[3] = {size_t(cp) * 4, size_t(W * cp) * 4, size_t(H * W * cp) * 4};
+  const unsigned box4[4] = {32, unsigned(boxW), unsigned(boxH), 1};
+  const size_t dims3[3] = {size_t(cp), size_t(H * W), size_t(N)};
+  const size_t pitches3[2] = {size_t(cp) * 4, size_t(H * W * cp) * 4};
+  const unsigned box3[3] = {32, unsigned(patchRows), 1};
+  const void *images[2] = {xHi, xLo}, *filters[2] = {fHi, fLo};
+  for (int i = 0; i < 2; ++i)
+    if ((rows ? olxEncodeTensorMapTiled(c->device, &maps[i], /*f32*/ 1, images[i], 3, dims3,
+                                        pitches3, box3, 128)
+              : olxEncodeTensorMapTiled(c->device, &maps[i], /*f32*/ 1, images[i], 4, dims4,
+                                        pitches4, box4, 128)) ||
+        olxEncodeTensorMap2D(c->device, &maps[2 + i], /*f32*/ 1, filters[i], size_t(NF),
+                             size_t(kp), size_t(kp) * 4, size_t(nPad), 32, 128))
+      return c->fail("tensor map encoding failed: %s", c->lastError.c_str());
+  HcConvTapParams p{};
+  p.out = static_cast<float *>(out);
+  p.N = int(N), p.C = int(C), p.H = int(H), p.W = int(W);
+  p.NF = int(NF), p.HF = int(HF), p.WF = int(WF);
+  p.HO = int(HO), p.WO = int(WO);
+  p.cBlocks = int(cBlocks), p.kBlocks = int(kBlocks), p.nPad = int(nPad);
+  p.boxW = int(boxW), p.boxH = int(boxH), p.tilesW = int(tilesW), p.tilesH = int(tilesH);
+  p.stages = int(stages);
+  p.stacked = stacked ? 1 : 0;
+  p.status = c->statusWord;
+  p.tilesFlat = int(tilesFlat), p.patchRows = int(patchRows);
+  const long long tiles = rows ? N * tilesFlat : N * tilesW * tilesH;
+  const long long grid = std::min<long long>(tiles, c->smCount);
+  const size_t smem = size_t(stages * stageBytes + fixed);
+  void *args[] = {&maps[0], &maps[1], &maps[2], &maps[3], &p};
+  return c->launch(rows ? "hc_conv_f32_rows" : "hc_conv_f32_taps", size_t(grid), 1, 1, 192, args,
+                   5, smem);
 }
 
 int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long long N,
@@ -1529,6 +1642,26 @@ int hcConvF32Tensor(HcContext c, const void *x, const void *f, void *out, long l
                    workspaceBytes);
   if (!aligned(x, 4) || !aligned(out, 4) || !aligned(f, 4))
     return c->fail("%s: arrays must be 4-byte aligned", who);
+  // Stride 1: both operands by TMA, no gathering threads (conv_f32_taps.cu).
+  long long boxW = 0, boxH = 0;
+  const bool tapsFit = stride == 1 && pickConvBox(H, W, HO, WO, boxW, boxH) &&
+                       N * H * W < (1ll << 31) && N * HO * ceilDiv(WO, 8) < (1ll << 31);
+  if (c->convVariant == 3 && !tapsFit)
+    return c->fail("%s: the TMA form takes stride 1 and images that hold a rectangle of 128 "
+                   "pixels (8 x 16 ... 128 x 1)", who);
+  // Runs of 128 positions of the flattened image, the patch of a filter row shared
+  // by its taps: the patch has to fit a TMA box and two stages shared memory.
+  const bool rowsFit = stride == 1 && 128 + WF - 1 <= 256 && H * W >= roundUp(128 + WF - 1, 8) &&
+                       convRowsStages(NF, WF) >= 2 && N * H * W < (1ll << 31);
+  if (c->convVariant == 4 && !rowsFit)
+    return c->fail("%s: the form that shares an image patch among the taps of a filter row "
+                   "takes stride 1, images of at least %lld positions and filters of which "
+                   "two stages fit in shared memory", who, roundUp(128 + WF - 1, 8));
+  const bool tapsStacked = nPad <= 128 && c->convStacked != 1;
+  if (rowsFit && (c->convVariant == 4 || c->convVariant == 0))
+    return convF32Taps(c, x, f, out, N, C, H, W, NF, HF, WF, workspace, tapsStacked, true);
+  if (tapsFit && (c->convVariant == 3 || c->convVariant == 0))
+    return convF32Taps(c, x, f, out, N, C, H, W, NF, HF, WF, workspace, tapsStacked, false);
   auto *base = static_cast<unsigned char *>(workspace);
   const size_t filterBytes = convFilterBytes(NF, C, HF, WF);
   float *fHi = reinterpret_cast<float *>(base);

@@ -91,6 +91,7 @@ struct Backend {
   decltype(&olxMemsetD8) MemsetD8 = nullptr;
   decltype(&olxDeviceAttribute) DeviceAttribute = nullptr;
   decltype(&olxEncodeTensorMap2D) EncodeTensorMap2D = nullptr;
+  decltype(&olxEncodeTensorMapTiled) EncodeTensorMapTiled = nullptr;
   decltype(&olxMaxActiveClusters) MaxActiveClusters = nullptr;
   decltype(&olxDeviceContextEnter) DeviceContextEnter = nullptr;
   decltype(&olxDeviceContextLeave) DeviceContextLeave = nullptr;
@@ -171,6 +172,7 @@ std::unique_ptr<Backend> openBackend(const std::string &path,
   HC_BIND_OPT(MemsetD8);
   HC_BIND_OPT(DeviceAttribute);
   HC_BIND_OPT(EncodeTensorMap2D);
+  HC_BIND_OPT(EncodeTensorMapTiled);
   HC_BIND_OPT(MaxActiveClusters);
   HC_BIND_OPT(DeviceContextEnter);
   HC_BIND_OPT(DeviceContextLeave);
@@ -452,6 +454,17 @@ int olxEncodeTensorMap2D(OlDevice d, void *mapOut, int elemKind,
   return fn ? fn(dev->inner, mapOut, elemKind, base, rows, cols, rowPitchBytes,
                  boxRows, boxCols, swizzle)
             : missing(dev, "olxEncodeTensorMap2D");
+}
+
+int olxEncodeTensorMapTiled(OlDevice d, void *mapOut, int elemKind, const void *base,
+                            int rank, const size_t *dims, const size_t *stridesBytes,
+                            const unsigned *box, int swizzle) noexcept {
+  auto *dev = static_cast<DeviceHandle *>(d);
+  if (!dev)
+    return 1;
+  auto fn = dev->api->EncodeTensorMapTiled;
+  return fn ? fn(dev->inner, mapOut, elemKind, base, rank, dims, stridesBytes, box, swizzle)
+            : missing(dev, "olxEncodeTensorMapTiled");
 }
 
 int olxMaxActiveClusters(OlQueue q, OlKernel k, unsigned blockThreads,

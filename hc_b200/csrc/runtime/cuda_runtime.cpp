@@ -506,6 +506,62 @@ int olxMaxActiveClusters(OlQueue queue, OlKernel kernel, unsigned blockThreads,
                                                   &config));
 }
 
+int olxEncodeTensorMapTiled(OlDevice d, void *mapOut, int elemKind, const void *base,
+                            int rank, const size_t *dims, const size_t *stridesBytes,
+                            const unsigned *box, int swizzle) noexcept {
+  auto *dev = static_cast<DeviceState *>(d);
+  if (!dev || !mapOut || !dims || !stridesBytes || !box)
+    return 1;
+  CUtensorMapDataType type;
+  size_t elemBytes;
+  switch (elemKind) {
+  case 0:
+    type = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    elemBytes = 2;
+    break;
+  case 1:
+    type = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    elemBytes = 4;
+    break;
+  case 2:
+    type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    elemBytes = 1;
+    break;
+  default:
+    dev->report(OlSeverity::Error, "Invalid tensor map element kind: %d", elemKind);
+    return 1;
+  }
+  bool ok = rank >= 2 && rank <= 5 && reinterpret_cast<uintptr_t>(base) % 16 == 0 &&
+            reinterpret_cast<uintptr_t>(mapOut) % 64 == 0 && (swizzle == 0 || swizzle == 128);
+  cuuint64_t d64[5] = {1, 1, 1, 1, 1}, s64[4] = {0, 0, 0, 0};
+  cuuint32_t b32[5] = {1, 1, 1, 1, 1}, e32[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; ok && i < rank; ++i) {
+    d64[i] = dims[i];
+    b32[i] = box[i];
+    ok = dims[i] > 0 && box[i] > 0 && box[i] <= 256;
+    if (ok && i > 0) {
+      s64[i - 1] = stridesBytes[i - 1];
+      ok = stridesBytes[i - 1] % 16 == 0;
+    }
+  }
+  ok = ok && (box[0] * elemBytes) % 16 == 0 && (swizzle != 128 || box[0] * elemBytes <= 128);
+  if (!ok) {
+    dev->report(OlSeverity::Error, "Invalid tensor map geometry: rank %d base %p swizzle %d",
+                rank, base, swizzle);
+    return 1;
+  }
+  ContextScope scope(dev);
+  if (!scope)
+    return 1;
+  return dev->check(
+      "cuTensorMapEncodeTiled",
+      DriverApi::get().TensorMapEncodeTiled(
+          static_cast<CUtensorMap *>(mapOut), type, cuuint32_t(rank), const_cast<void *>(base),
+          d64, s64, b32, e32, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+}
+
 int olxEncodeTensorMap2D(OlDevice d, void *mapOut, int elemKind,
                          const void *base, size_t rows, size_t cols,
                          size_t rowPitchBytes, unsigned boxRows,

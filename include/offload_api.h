@@ -129,6 +129,16 @@ OFFLOAD_API_EXPORT int olxEncodeTensorMap2D(OlDevice dev, void *mapOut,
                                             unsigned boxRows, unsigned boxCols,
                                             int swizzle) HC_NOEXCEPT;
 
+/* The same for a tensor of rank 2..5: `dims[rank]` and `box[rank]` innermost
+ * first, `stridesBytes[rank - 1]` the pitch of every dimension but the
+ * innermost (which is contiguous).  Coordinates outside the tensor read zeros. */
+OFFLOAD_API_EXPORT int olxEncodeTensorMapTiled(OlDevice dev, void *mapOut,
+                                               int elemKind, const void *base,
+                                               int rank, const size_t *dims,
+                                               const size_t *stridesBytes,
+                                               const unsigned *box,
+                                               int swizzle) HC_NOEXCEPT;
+
 /* How many clusters of `clusterSize` CTAs (each `blockThreads` threads and
  * `sharedMemSize` bytes of dynamic shared memory) of kernel `k` the device can
  * hold at once.  A persistent kernel launched with more CTAs than that runs

@@ -51,19 +51,32 @@ CASES = [
     ((1, 64, 14, 14), (64, 64, 3, 3), 1),   # K = 576 as at the benchmark size
     ((5, 7, 9, 40), (200, 7, 3, 3), 3),     # many filters (two stages of shared memory)
     ((1, 2, 3, 3), (2, 2, 3, 3), 1),        # one output pixel
+    ((2, 40, 16, 70), (24, 40, 3, 3), 1),   # 40 channels: a partial channel block; wide rows
+    ((1, 32, 130, 9), (16, 32, 5, 2), 1),   # tall and narrow: rectangles of 8 x 16
+    ((3, 96, 28, 28), (192, 96, 1, 1), 1),  # a 1 x 1 filter over three channel blocks, 192 filters
 ]
 
 
-# conv_variant: 1 = the image operand of a K block goes through shared memory,
-# 2 = through tensor memory (at most 128 filters), 0 = the library's choice.
+# conv_variant: 1 = the image operand of a K block is gathered by threads into shared
+# memory, 2 = into tensor memory (at most 128 filters), 3 = both operands come by TMA
+# (stride 1, images that hold a rectangle of 128 pixels), 4 = both by TMA with the image
+# patch of a filter row shared by its taps, 0 = the library's choice.
 # conv_stacked: 0 = with at most 128 filters the two products that share a_hi run as
 # one MMA of twice the width, 1 = three MMAs per K step throughout.
 @pytest.mark.parametrize("unstacked", [0, 1])
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("xs,fs,stride", CASES)
 def test_matches_the_float64_correlation(hc, xs, fs, stride, variant, unstacked):
     if variant == 2 and fs[0] > 128:
         pytest.skip("more filters than the tensor-memory form takes")
+    if variant == 3 and (stride != 1 or not any(bw <= xs[3] and 128 // bw <= xs[2]
+                                                for bw in (8, 16, 32, 64, 128))):
+        pytest.skip("the TMA form takes stride 1 and images that hold 128 pixels")
+    patch = -(-(128 + fs[3] - 1) // 8) * 8
+    stage = 2 * patch * 128 + fs[3] * 2 * (-(-fs[0] // 16) * 16) * 128
+    if variant == 4 and (stride != 1 or xs[2] * xs[3] < patch or 2 * stage > 227 * 1024 - 1280):
+        pytest.skip("the shared-patch form takes stride 1, images of 128 + WF - 1 positions "
+                    "and filters of which two stages fit in shared memory")
     hc.set_option("conv_variant", variant)
     hc.set_option("conv_stacked", unstacked)
     try:
