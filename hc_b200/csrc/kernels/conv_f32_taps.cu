@@ -17,8 +17,8 @@
 // shared memory exactly as the K-major MMA descriptor reads it.  A tap shifts
 // the box along W and H, which are not the innermost dimension, so no alignment
 // rule is in the way; pixels beyond the image read zeros and are not stored.
-// The filters are rewritten to the same K order (hc_split_tf32_taps:
-// f [NF, C, HF, WF] -> hi, lo as [NF, taps * Cp]).
+// The filters are rewritten to the same K order by the same launch
+// (f [NF, C, HF, WF] -> hi, lo as [NF, taps * Cp]).
 //
 // Arithmetic as in gemm_f32_umma.cu: three tf32 products lo*hi + hi*lo + hi*hi
 // per float32 product, accumulated in fp32 in TMEM; with at most 128 filters the
@@ -77,11 +77,27 @@ __device__ __forceinline__ void tmaLoad4D(uint32_t dst, const CUtensorMap *map, 
 
 } // namespace
 
-// x [N, C, HW] -> hi, lo [N, HW, Cp]: the tf32 parts of every element, channels
-// innermost, zeros in the channels beyond C.  blockIdx.y is the image.
+// Both operands rewritten in one launch.  blockIdx.y < images: image blockIdx.y,
+// x [C, HW] -> hi, lo [HW, Cp] - the tf32 parts of every element, channels
+// innermost, zeros in the channels beyond C.  blockIdx.y == images: the filters,
+// f [NF, C, taps] -> hi, lo [NF, taps * Cp] in the K order of the kernels below.
 extern "C" __global__ void __launch_bounds__(256)
     hc_split_tf32_nhwc(const float *__restrict__ x, float *__restrict__ hi, float *__restrict__ lo,
-                       int C, int HW, int Cp) {
+                       int C, int HW, int Cp, int images, const float *__restrict__ f,
+                       float *__restrict__ fHi, float *__restrict__ fLo, int NF, int taps) {
+  if (int(blockIdx.y) == images) {
+    const long long total = (long long)NF * taps * Cp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+      const int c = int(i % Cp), tap = int((i / Cp) % taps), q = int(i / ((long long)Cp * taps));
+      float h = 0.0f, l = 0.0f;
+      if (c < C)
+        splitTf32(f[((long long)q * C + c) * taps + tap], h, l);
+      fHi[i] = h;
+      fLo[i] = l;
+    }
+    return;
+  }
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8 threads
   const float *in = x + (long long)blockIdx.y * C * HW;
@@ -106,22 +122,6 @@ extern "C" __global__ void __launch_bounds__(256)
         outLo[(long long)p * Cp + c] = l;
       }
     }
-  }
-}
-
-// f [NF, C, taps] -> hi, lo [NF, taps * Cp] in the K order of the kernel below.
-extern "C" __global__ void __launch_bounds__(256)
-    hc_split_tf32_taps(const float *__restrict__ f, float *__restrict__ hi, float *__restrict__ lo,
-                       int NF, int C, int taps, int Cp) {
-  const long long total = (long long)NF * taps * Cp;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c = int(i % Cp), tap = int((i / Cp) % taps), q = int(i / ((long long)Cp * taps));
-    float h = 0.0f, l = 0.0f;
-    if (c < C)
-      splitTf32(f[((long long)q * C + c) * taps + tap], h, l);
-    hi[i] = h;
-    lo[i] = l;
   }
 }
 

@@ -67,7 +67,6 @@ const KernelEntry kKernelTable[] = {
     {"hc_conv_f32_taps", "conv_f32_taps"},
     {"hc_conv_f32_rows", "conv_f32_taps"},
     {"hc_split_tf32_nhwc", "conv_f32_taps"},
-    {"hc_split_tf32_taps", "conv_f32_taps"},
     {"hc_work_items_f32", "work_items"},
     {"hc_work_items_f64", "work_items"},
     {"hc_row_fused_", "row_fused"},
@@ -1535,18 +1534,12 @@ static int convF32Taps(HcContext c, const void *x, const void *f, void *out, lon
   float *xHi = reinterpret_cast<float *>(base + 2 * filterBytes);
   float *xLo = reinterpret_cast<float *>(base + 2 * filterBytes + imageBytes);
   {
-    int ci = int(C), hw = int(H * W), cpi = int(cp);
+    // Image and filters rewritten by one launch (the last row of the grid takes the filters).
+    int ci = int(C), hw = int(H * W), cpi = int(cp), images = int(N), nf = int(NF), ti = int(taps);
     const long long work = ceilDiv(H * W, 32) * cBlocks;
     const long long gx = std::max<long long>(1, std::min<long long>(work, c->smCount * 8));
-    void *args[] = {&x, &xHi, &xLo, &ci, &hw, &cpi};
-    if (c->launch("hc_split_tf32_nhwc", size_t(gx), size_t(N), 1, 256, args, 6, 0))
-      return 1;
-  }
-  {
-    int nf = int(NF), ci = int(C), ti = int(taps), cpi = int(cp);
-    const long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(NF * kp, 256), 1024));
-    void *args[] = {&f, &fHi, &fLo, &nf, &ci, &ti, &cpi};
-    if (c->launch("hc_split_tf32_taps", size_t(gx), 1, 1, 256, args, 7, 0))
+    void *args[] = {&x, &xHi, &xLo, &ci, &hw, &cpi, &images, &f, &fHi, &fLo, &nf, &ti};
+    if (c->launch("hc_split_tf32_nhwc", size_t(gx), size_t(N + 1), 1, 256, args, 12, 0))
       return 1;
   }
   alignas(64) CUtensorMap maps[4];

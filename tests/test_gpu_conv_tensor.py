@@ -140,8 +140,8 @@ def test_refusals(hc):
 def test_the_front_door_sends_convolution_bodies_to_the_tensor_cores():
     """The reference's implicit-GEMM body (python/hckernel/tests/test_examples.py:203-252):
     its work-groups are recognised from their evaluated index tables as a plain
-    convolution and run on hcConvF32Tensor (three launches: the two operand splits and the
-    convolution);
+    convolution and run on hcConvF32Tensor (two launches: the rewriting of both operands and
+    the convolution);
     with ``settings.CONV_VARIANT = 1`` they run as the body tiles them (one launch of
     the gathered kernel).  Both within the float32 parity bound of the exact sums."""
     from hc_b200.hckernel import settings
@@ -167,7 +167,7 @@ def test_the_front_door_sends_convolution_bodies_to_the_tensor_cores():
         finally:
             settings.CONV_VARIANT = 0
         assert np.all(np.abs(out.cpu().numpy().astype(np.float64) - exact) <= bound)
-    assert launches == {0: 3, 1: 1}
+    assert launches == {0: 2, 1: 1}
     # A rectangular image is not the plain convolution (the body walks the output
     # positions transposed): it stays with the gathered kernel.
     xr, fr = oracle.make_conv_inputs((8, 16, 34, 66), (32, 16, 3, 3), "float32")
