@@ -98,28 +98,39 @@ extern "C" __global__ void __launch_bounds__(256)
     }
     return;
   }
-  __shared__ float tile[32][33];
+  // Tiles of 32 positions x 64 channels: eight loads in flight per thread, and a
+  // position's 64 channels leave as 256 contiguous bytes.
+  __shared__ float tile[64][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8 threads
   const float *in = x + (long long)blockIdx.y * C * HW;
   float *outHi = hi + (long long)blockIdx.y * HW * Cp, *outLo = lo + (long long)blockIdx.y * HW * Cp;
-  const int tilesP = (HW + 31) / 32, tilesC = Cp / 32;
+  const int tilesP = (HW + 31) / 32, tilesC = (Cp + 63) / 64;
   for (int t = blockIdx.x; t < tilesP * tilesC; t += gridDim.x) {
-    const int p0 = (t % tilesP) * 32, c0 = (t / tilesP) * 32;
-    __syncthreads();
+    const int p0 = (t % tilesP) * 32, c0 = (t / tilesP) * 64;
+    const int p = p0 + tx;
+    float v[8];
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const int c = c0 + ty + j, p = p0 + tx;
-      tile[ty + j][tx] = (c < C && p < HW) ? in[(long long)c * HW + p] : 0.0f;
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + ty + 8 * j;
+      v[j] = (c < C && p < HW) ? in[c * HW + p] : 0.0f;
     }
+    __syncthreads(); // the tile of the round before has been read
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      tile[ty + 8 * j][tx] = v[j];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const int p = p0 + ty + j, c = c0 + tx;
-      if (p < HW) {
-        float h, l;
-        splitTf32(tile[tx][ty + j], h, l);
-        outHi[(long long)p * Cp + c] = h;
-        outLo[(long long)p * Cp + c] = l;
+    for (int j = 0; j < 4; ++j) {
+      const int q = p0 + ty + 8 * j; // position
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = c0 + 32 * half + tx;
+        if (q < HW && c < Cp) {
+          float h, l;
+          splitTf32(tile[32 * half + tx][ty + 8 * j], h, l);
+          outHi[(long long)q * Cp + c] = h;
+          outLo[(long long)q * Cp + c] = l;
+        }
       }
     }
   }

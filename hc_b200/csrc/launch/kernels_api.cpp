@@ -1536,7 +1536,7 @@ static int convF32Taps(HcContext c, const void *x, const void *f, void *out, lon
   {
     // Image and filters rewritten by one launch (the last row of the grid takes the filters).
     int ci = int(C), hw = int(H * W), cpi = int(cp), images = int(N), nf = int(NF), ti = int(taps);
-    const long long work = ceilDiv(H * W, 32) * cBlocks;
+    const long long work = ceilDiv(H * W, 32) * ceilDiv(cp, 64);
     const long long gx = std::max<long long>(1, std::min<long long>(work, c->smCount * 8));
     void *args[] = {&x, &xHi, &xLo, &ci, &hw, &cpi, &images, &f, &fHi, &fLo, &nf, &ti};
     if (c->launch("hc_split_tf32_nhwc", size_t(gx), size_t(N + 1), 1, 256, args, 12, 0))
