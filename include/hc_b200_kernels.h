@@ -99,10 +99,15 @@ HC_B200_API int hcSelfTestWaitTimeout(HcContext c, unsigned long long limitNs,
  * hcRowProgram that has no such body, and to every program of hcWorkItems - 1 (default) = it is compiled at its first
  * launch (see hcSpecialisedPrograms) and interpreted where that is not possible,
  * 0 = it is interpreted, 2 = as 1, but the launch fails where compiling is not
- * possible.  "conv_variant" (hcConvF32Tensor): 0 = the image operand of a K block goes
- * through tensor memory when at most 128 filters leave room there, 1 = always
- * through shared memory, 2 = always through tensor memory (more filters are
- * refused); "conv_stages": 0 or 2..6 pipeline stages; "conv_stacked": 0 = with at
+ * possible.  "conv_variant" (hcConvF32Tensor): 0 = the library's choice - with
+ * stride 1 both operands come by TMA (4 where two of its stages fit in shared
+ * memory, else 3), otherwise threads gather the image operand (2 where at most
+ * 128 filters leave room in tensor memory, else 1); 1 = gathered into shared
+ * memory, 2 = gathered into tensor memory (more filters are refused), 3 = by
+ * TMA, a rectangle of 128 pixels per filter tap, 4 = by TMA, runs of 128
+ * positions of the flattened image, the patch of a filter row shared by its
+ * taps; 3 and 4 take stride 1 and fail on images too small for their boxes.
+ * "conv_stages": 0 or 2..6 pipeline stages; "conv_stacked": 0 = with at
  * most 128 filters the two products that share a_hi run as one MMA of double
  * width, 1 = three MMAs per K step throughout.  "gemm_band": row tiles per
  * band in the tile order of the tcgen05 GEMMs (0 = 16).  "w8a16_variant"
@@ -412,12 +417,14 @@ HC_B200_API int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void 
  * contiguous.  The sums of the reference's implicit-GEMM convolution
  * (python/hckernel/tests/test_examples.py:203-252) for square outputs, tiled by
  * output pixels instead of by (images x filters) per position: an implicit GEMM
- * whose image operand is gathered by the kernel's threads and whose products run
- * as three tf32 products each on tcgen05 (float32-class results, as
- * hcGemmF32Tensor).  NF <= 256; `workspace` must hold
- * hcConvF32TensorWorkspaceBytes(N, C, H, W, NF, HF, WF) bytes of device memory,
- * 1 KiB aligned (the split filters and the image as (hi, lo) pairs: twice the
- * size of x), and is written by every call.  Fails on a device without tcgen05,
+ * whose products run as three tf32 products each on tcgen05 (float32-class
+ * results, as hcGemmF32Tensor).  With stride 1 the image is rewritten once with
+ * the channels innermost and both operands reach the MMA by TMA; with other
+ * strides the kernel's threads gather the image operand.  NF <= 256;
+ * `workspace` must hold hcConvF32TensorWorkspaceBytes(N, C, H, W, NF, HF, WF)
+ * bytes of device memory, 1 KiB aligned (the split filters and the image as its
+ * hi and lo parts: twice the size of x, channels rounded up to 32), and is
+ * written by every call.  Fails on a device without tcgen05,
  * where hcMappedGemm computes the same convolution. */
 HC_B200_API size_t hcConvF32TensorWorkspaceBytes(long long N, long long C, long long H,
                                                  long long W, long long NF, long long HF,
