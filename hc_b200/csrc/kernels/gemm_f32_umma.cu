@@ -80,9 +80,40 @@ struct alignas(8) Barriers {
 } // namespace
 
 // hi / lo parts of a row-major matrix, rows padded to `outPitch` with zeros.
+// Packets of four columns where the layout allows 16-byte accesses (all pitches
+// and `cols` multiples of 4, 16-byte aligned bases), two rows in flight per thread.
 extern "C" __global__ void __launch_bounds__(256)
     hc_split_tf32(const float *__restrict__ in, float *__restrict__ hi, float *__restrict__ lo,
                   long long rows, long long cols, long long inPitch, long long outPitch) {
+  const bool packets = ((inPitch | outPitch | cols) & 3) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(hi) |
+                         reinterpret_cast<uintptr_t>(lo)) & 15) == 0;
+  if (packets) {
+    const long long perRow = outPitch >> 2, live = cols >> 2;
+    auto one = [&](float4 v, long long r, long long c) {
+      float4 h, l;
+      splitTf32(v.x, h.x, l.x);
+      splitTf32(v.y, h.y, l.y);
+      splitTf32(v.z, h.z, l.z);
+      splitTf32(v.w, h.w, l.w);
+      reinterpret_cast<float4 *>(hi + r * outPitch)[c] = h;
+      reinterpret_cast<float4 *>(lo + r * outPitch)[c] = l;
+    };
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (long long r = 2ll * blockIdx.y; r < rows; r += 2ll * gridDim.y)
+      for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < perRow;
+           c += (long long)gridDim.x * blockDim.x) {
+        const bool second = r + 1 < rows;
+        const float4 v0 = c < live ? reinterpret_cast<const float4 *>(in + r * inPitch)[c] : zero;
+        const float4 v1 = second && c < live
+                              ? reinterpret_cast<const float4 *>(in + (r + 1) * inPitch)[c]
+                              : zero;
+        one(v0, r, c);
+        if (second)
+          one(v1, r + 1, c);
+      }
+    return;
+  }
   const long long perRow = outPitch;
   for (long long r = blockIdx.y; r < rows; r += gridDim.y)
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < perRow;
@@ -96,30 +127,40 @@ extern "C" __global__ void __launch_bounds__(256)
 }
 
 // hi / lo parts of the transpose: in [rows, cols] -> out [cols, outPitch >= rows].
+// Tiles of 64 rows x 32 columns: eight loads in flight per thread, and an output
+// row gets 256 contiguous bytes per tile.
 extern "C" __global__ void __launch_bounds__(256)
     hc_split_tf32_t(const float *__restrict__ in, float *__restrict__ hi,
                     float *__restrict__ lo, long long rows, long long cols, long long inPitch,
                     long long outPitch) {
-  __shared__ float tile[32][33];
+  __shared__ float tile[64][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8 threads
-  const long long tilesX = (cols + 31) / 32, tilesY = (outPitch + 31) / 32;
+  const long long tilesX = (cols + 31) / 32, tilesY = (outPitch + 63) / 64;
   for (long long t = blockIdx.x; t < tilesX * tilesY; t += gridDim.x) {
-    const long long c0 = (t % tilesX) * 32, r0 = (t / tilesX) * 32;
-    __syncthreads();
+    const long long c0 = (t % tilesX) * 32, r0 = (t / tilesX) * 64;
+    float v[8];
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const long long r = r0 + ty + j, c = c0 + tx;
-      tile[ty + j][tx] = (r < rows && c < cols) ? in[r * inPitch + c] : 0.0f;
+    for (int j = 0; j < 8; ++j) {
+      const long long r = r0 + ty + 8 * j, c = c0 + tx;
+      v[j] = (r < rows && c < cols) ? in[r * inPitch + c] : 0.0f;
     }
+    __syncthreads(); // the tile of the round before has been read
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      tile[ty + 8 * j][tx] = v[j];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const long long c = c0 + ty + j, r = r0 + tx; // out[c][r]
-      if (c < cols && r < outPitch) {
-        float h, l;
-        splitTf32(tile[tx][ty + j], h, l);
-        hi[c * outPitch + r] = h;
-        lo[c * outPitch + r] = l;
+    for (int j = 0; j < 4; ++j) {
+      const long long c = c0 + ty + 8 * j; // out[c][r]
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const long long r = r0 + 32 * half + tx;
+        if (c < cols && r < outPitch) {
+          float h, l;
+          splitTf32(tile[32 * half + tx][ty + 8 * j], h, l);
+          hi[c * outPitch + r] = h;
+          lo[c * outPitch + r] = l;
+        }
       }
     }
   }

@@ -1415,14 +1415,15 @@ int hcGemmF32Tensor(HcContext c, const void *a, const void *b, void *out, void *
   float *bHi = reinterpret_cast<float *>(base + 2 * aBytes);
   float *bLo = reinterpret_cast<float *>(base + 2 * aBytes + bBytes);
   {
-    long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(kp, 256), 64));
-    long long gy = std::max<long long>(1, std::min<long long>(M, 65535));
+    // (Packets of four columns and two rows per thread where the layout allows.)
+    long long gx = std::max<long long>(1, std::min<long long>(ceilDiv(kp, 1024), 64));
+    long long gy = std::max<long long>(1, std::min<long long>(ceilDiv(M, 2), 65535));
     void *args[] = {&a, &aHi, &aLo, &M, &K, &lda, (void *)&kp};
     if (c->launch("hc_split_tf32", size_t(gx), size_t(gy), 1, 256, args, 7, 0))
       return 1;
   }
   {
-    const long long tiles = ceilDiv(N, 32) * ceilDiv(kp, 32);
+    const long long tiles = ceilDiv(N, 32) * ceilDiv(kp, 64);
     long long grid = std::max<long long>(1, std::min<long long>(tiles, c->smCount * 16));
     void *args[] = {&b, &bHi, &bLo, &K, &N, &ldb, (void *)&kp};
     if (c->launch("hc_split_tf32_t", size_t(grid), 1, 1, 256, args, 7, 0))
