@@ -54,6 +54,8 @@ CASES = [
     ((2, 40, 16, 70), (24, 40, 3, 3), 1),   # 40 channels: a partial channel block; wide rows
     ((1, 32, 130, 9), (16, 32, 5, 2), 1),   # tall and narrow: rectangles of 8 x 16
     ((3, 96, 28, 28), (192, 96, 1, 1), 1),  # a 1 x 1 filter over three channel blocks, 192 filters
+    ((2, 16, 40, 40), (16, 16, 7, 7), 1),   # seven taps per filter row share a patch of 136 rows
+    ((1, 8, 64, 64), (32, 8, 5, 3), 1),     # 64-wide rows: tiles of two whole rows
 ]
 
 

@@ -161,3 +161,45 @@ def test_hcgpu_get_kernel_and_launch_like_jit_host_code():
     grid, block = (C.c_size_t * 3)(4, 111, 1), (C.c_size_t * 3)(256, 1, 1)
     rt.hcgpuLaunchKernel(k, grid, block, 3, args, 7, 0)  # returns after the kernel finished
     assert torch.equal(dst, src)
+
+
+@pytest.mark.parametrize("which", ["loader", "backend"])
+def test_tensor_map_encoders_accept_and_refuse(which):
+    """olxEncodeTensorMap2D / olxEncodeTensorMapTiled: descriptors of rank 2 to 5 for
+    aligned tensors; a bad rank, a pitch that is not a multiple of 16 bytes, a box
+    wider than the swizzle span and an unaligned base are refused with a message."""
+    lib = capi.load_loader() if which == "loader" else capi.load_backend()
+    if which == "loader":
+        paths = (C.c_char_p * 1)(str(capi.NATIVE_DIR).encode())
+        lib.setGPULoaderSearchPaths(paths, 1)
+    seen = []
+    cb = capi.OlErrorCallback(lambda ctx, sev, text: seen.append((sev, text.decode())))
+    dev = lib.olCreateDevice(b"cuda:0", cb, None)
+    assert dev, seen
+    q = lib.olCreateQueue(dev)
+    base = lib.olAllocDevice(q, 1 << 20, 1024)
+    raw = C.create_string_buffer(128 + 64)
+    desc = C.c_void_p((C.addressof(raw) + 63) & ~63)  # 64-byte aligned, 128 bytes
+
+    def tiled(rank, dims, pitches, box, swizzle=128, at=base):
+        return lib.olxEncodeTensorMapTiled(dev, desc, 1, at, rank, (C.c_size_t * len(dims))(*dims),
+                                           (C.c_size_t * max(1, len(pitches)))(*pitches),
+                                           (C.c_uint * len(box))(*box), swizzle)
+
+    assert lib.olxEncodeTensorMap2D(dev, desc, 1, base, 64, 128, 512, 16, 32, 128) == 0, seen
+    # [N = 2][H * W = 400][C = 64] floats, a box of 32 channels x 136 positions.
+    assert tiled(3, [64, 400, 2], [256, 400 * 256], [32, 136, 1]) == 0, seen
+    # [N = 2][H = 20][W = 20][C = 64], a box of 32 channels x 64 x 2 pixels.
+    assert tiled(4, [64, 20, 20, 2], [256, 20 * 256, 400 * 256], [32, 16, 8, 1]) == 0, seen
+    assert tiled(5, [64, 5, 4, 20, 2], [256, 5 * 256, 20 * 256, 400 * 256], [32, 2, 2, 4, 1]) == 0
+    seen.clear()
+    assert tiled(6, [64] * 6, [256] * 5, [32] * 6) == 1
+    assert "Invalid tensor map geometry" in seen[-1][1]
+    assert tiled(3, [64, 400, 2], [250, 400 * 256], [32, 136, 1]) == 1   # pitch % 16 != 0
+    assert tiled(3, [64, 400, 2], [256, 400 * 256], [64, 136, 1]) == 1   # 256-byte box, swizzle 128
+    assert tiled(3, [64, 400, 2], [256, 400 * 256], [32, 300, 1]) == 1   # a box dimension > 256
+    assert tiled(3, [64, 400, 2], [256, 400 * 256], [32, 136, 1], at=base + 4) == 1
+    assert all("Invalid tensor map geometry" in text for _, text in seen)
+    lib.olDeallocDevice(q, base)
+    lib.olReleaseQueue(q)
+    lib.olReleaseDevice(dev)
