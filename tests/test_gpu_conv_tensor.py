@@ -56,6 +56,7 @@ CASES = [
     ((3, 96, 28, 28), (192, 96, 1, 1), 1),  # a 1 x 1 filter over three channel blocks, 192 filters
     ((2, 16, 40, 40), (16, 16, 7, 7), 1),   # seven taps per filter row share a patch of 136 rows
     ((1, 8, 64, 64), (32, 8, 5, 3), 1),     # 64-wide rows: tiles of two whole rows
+    ((2, 8, 20, 40), (8, 8, 1, 9), 1),      # nine taps in a row: shifts of more than 1 KiB
 ]
 
 
