@@ -227,7 +227,9 @@ NCU_TRAFFIC = {
     "gemm_w8a16": 593.8e6 + 59.8e6,
     "gemm_f32": None,
     "gemm_f32_tensor": 628.8e6 + 61.5e6,
-    "conv": None,
+    # profiles/conv_f32_rows_32x64x56x56.md (the convolution kernel alone, one full-size
+    # launch: x as hi and lo parts read once; the output was still in L2 at kernel end).
+    "conv": 51.7e6 + 1.5e6,
     "map": 1073761280 + 495959040,
     "rows": 536891392 + 481583104,
 }
