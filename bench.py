@@ -469,6 +469,10 @@ DEFAULT_BANDS = {"softmax": 0, "rows": 0, "map": 0, "reduce": 1, "gemm_bf16": 2}
 # of the softmax's 512-byte rows, and the stalled epilogue holds the tensor cores
 # back: on 2 GPUs 0.61 ms against 0.55 ms with NCCL's gather behind the kernel.
 FUSED_GATHER = ("softmax", "reduce")
+# ... up to this many GPUs: with 8, every rank of the softmax stores 7 x 64 MiB and the
+# step measured 1.07 ms against 0.93 ms for the same bytes through NCCL's all-gather
+# behind the kernels (at 4: 0.71 against 0.82).
+FUSED_GATHER_MAX_WORLD = {"softmax": 4}
 FUSED_GATHER_ALL = ("softmax", "reduce", "gemm_bf16", "gemm_w8a16")
 # Which inputs of a row-sharded workload are split by rows (the others are replicated).
 ROW_INPUTS = {"softmax": (0,), "rows": (0,), "map": (0, 1), "reduce": (0,), "gemm_bf16": (0,)}
@@ -892,7 +896,8 @@ def run_gpu(args):
             shard_in = [plan.take_shard(t, rank).contiguous() if k in ROW_INPUTS[name] else t
                         for k, t in enumerate(ins)]
             sharded_outs = [torch.empty_like(t) for t in full_outs]
-            fused = ((args.gather == "fused" and name in FUSED_GATHER)
+            fused = ((args.gather == "fused" and name in FUSED_GATHER
+                      and world <= FUSED_GATHER_MAX_WORLD.get(name, world))
                      or (args.gather == "fused-all" and name in FUSED_GATHER_ALL))
             if fused:
                 # Compute and all-gather in one kernel: the contiguous row shard of
