@@ -31,7 +31,13 @@ Semantics the recording keeps from the reference:
   keeps the mapping object; the launch plan evaluates it into index tables;
 * ``@group.workitems`` (kernel_api.py:395-414): the function is recorded once
   with a :class:`WorkIndex` per axis in place of ``global_id()``; reads and one
-  guarded write of the work-item's own element become an element-wise program.
+  guarded write of the work-item's own element become an element-wise program,
+  local ids, neighbour reads and two phases around ``group.barrier()`` a
+  work-item program (``hckernel/workitems.py``);
+* ``@group.subgroups`` (kernel_api.py:378-393): the function is recorded once with
+  the sub-group id as a symbol; the tiles it loads and stores at
+  ``work_offset + subgroup_id * (1, ..., size)`` are tiles of the finer grid of
+  sub-groups, on which the launch is planned.
 """
 
 import fractions
