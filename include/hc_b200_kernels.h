@@ -451,7 +451,11 @@ HC_B200_API size_t hcGemmW8A16WorkspaceBytes(long long N, long long K);
  * workspace (its first bytes, 256-byte aligned): the weights are converted
  * inside the GEMM kernel, one band of 1024 columns at a time, into a ring of
  * three bands that the tiles read from L2 - 3 * K * 1024 * 2 bytes and a few
- * counters instead of the whole converted matrix. */
+ * counters instead of the whole converted matrix.  The CTAs of that kernel wait
+ * for one another (every CTA converts a share of every band), so its grid is
+ * what the idle device holds at once: do not run it beside other kernels on
+ * the same GPU - a CTA that cannot start makes the others' bounded waits run
+ * out, and the call's result is then reported through hcKernelStatus (6 or 7). */
 HC_B200_API size_t hcGemmW8A16BandedBytes(long long N, long long K);
 HC_B200_API int hcGemmW8A16(HcContext c, const void *a, const void *w,
                             const float *scale, void *out, void *workspace,
