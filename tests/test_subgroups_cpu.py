@@ -119,3 +119,24 @@ def test_subgroup_and_group_level_stores_do_not_mix():
 
     with pytest.raises(UnsupportedKernel, match="mix sub-group functions"):
         k.plan_for(tuple(F((256,), np.float32) for _ in range(3)))
+
+
+def test_subgroup_size_as_a_literal_symbol():
+    """subgroup_size may be a symbol listed in `literals`, bound by a call argument
+    (reference kernel_api.py:26-31, tests/test_kernel_sim.py:254-283)."""
+    G, DT, SG = sym.G, typename.DT, sym.SG
+
+    @kernel(work_shape=G, group_shape=64, subgroup_size=SG, literals={SG}, backend="nvvm",
+            device="cuda:0")
+    def k(gr: CurrentGroup, a: Buffer[G, DT], out: Buffer[G, DT], size: SG):
+        @gr.subgroups
+        def inner(sg):
+            x = gr.work_offset[0] + sg.subgroup_id()[0] * sg.size()
+            gr.store(out[x:], gr.load(a[x:], shape=sg.size()) * 2.0 + 1.0)
+
+        inner()
+
+    arrays = (F((1000,), np.float32), F((1000,), np.float32))
+    assert k.plan_for(arrays + (16,)).family == "map_elements"
+    with pytest.raises(UnsupportedKernel, match="does not divide"):
+        k.plan_for(arrays + (24,))
